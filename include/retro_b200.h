@@ -1,0 +1,253 @@
+/* C ABI of libretro_b200: the batched decode step of the step-wise generation engine,
+ * implemented with CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * Every `retro_engine_*` / `retro_last_error` declaration below replaces the entry point of the
+ * same name in the reference's runtime header
+ * crates/retrograd-ffi/runtime/include/retro_lora_train.h (line ranges cited per group); struct
+ * layouts are byte-identical to it (checked by static_asserts in the implementation, mirroring
+ * crates/retrograd-ffi/src/lib.rs:2825-3060). Status codes: 0 ok, -1 runtime error, -2 buffer
+ * too small, -3 invalid argument (reported before anything is decoded); constructors return
+ * NULL. The message of the last failure on the calling thread is read with retro_last_error().
+ *
+ * `retro_b200_*` entry points have no counterpart in the reference: they are the inspection
+ * hooks the parity tests and the benchmark need (packing maps, block tables, logits, timing,
+ * model synthesis).
+ */
+#ifndef RETRO_B200_H
+#define RETRO_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* retro_lora_train.h:3038 */
+const char * retro_last_error(void);
+
+/* ---- shared value types (retro_lora_train.h:1229-1242,1255-1393,1472-1482) ---- */
+
+typedef struct retro_sampling_params {
+    float    temperature;
+    float    top_p;
+    uint32_t max_new_tokens;
+    uint32_t seed;
+} retro_sampling_params;
+
+#define RETRO_STATE_SEQ_FLAGS_NONE         0u
+#define RETRO_STATE_SEQ_FLAGS_PARTIAL_ONLY 1u
+#define RETRO_STATE_SEQ_FLAGS_ON_DEVICE    2u
+
+#define RETRO_STEP_ADAPTER_BASE (-1)
+
+typedef struct retro_step_row {
+    uint32_t struct_size;
+    int32_t  request;
+    int32_t  slot;
+    const int32_t * tokens;
+    uint32_t n;
+    int32_t  pos0;
+    bool     sample;
+    retro_sampling_params sampling;
+    uint32_t n_top_logprobs;
+    int32_t  adapter;
+} retro_step_row;
+
+typedef struct retro_adapter_rows_info {
+    uint32_t struct_size;
+    uint32_t n_adapters;
+    uint32_t max_rank;
+    uint64_t stacked_bytes;
+    uint64_t unpadded_bytes;
+} retro_adapter_rows_info;
+
+typedef struct retro_step_out_row {
+    uint32_t struct_size;
+    int32_t  token;
+    float    logprob;
+    uint32_t n_top;
+    uint8_t  forced;
+    uint8_t  sampled;
+} retro_step_out_row;
+
+typedef struct retro_grammar retro_grammar;
+
+typedef struct retro_sampling_params_v2 {
+    uint32_t struct_size;
+    float    temperature;
+    float    top_p;
+    uint32_t max_new_tokens;
+    uint32_t seed;
+    int32_t  top_k;
+    float    min_p;
+    float    repeat_penalty;
+    float    frequency_penalty;
+    float    presence_penalty;
+    uint32_t penalty_window;
+    uint32_t n_logit_bias;
+    const int32_t * logit_bias_ids;
+    const float   * logit_bias_values;
+    const retro_grammar * grammar;
+} retro_sampling_params_v2;
+
+typedef struct retro_step_row_v2 {
+    uint32_t struct_size;
+    int32_t  request;
+    int32_t  slot;
+    const int32_t * tokens;
+    uint32_t n;
+    int32_t  pos0;
+    bool     sample;
+    retro_sampling_params_v2 sampling;
+    uint32_t n_top_logprobs;
+    uint8_t  want_logprob;
+    int32_t  adapter;
+} retro_step_row_v2;
+
+typedef struct retro_step_out_row_v2 {
+    uint32_t struct_size;
+    int32_t  token;
+    float    logprob;
+    uint32_t n_top;
+    uint8_t  forced;
+    uint8_t  sampled;
+    float    sampled_logprob;
+} retro_step_out_row_v2;
+
+typedef struct retro_engine_memory_info {
+    uint32_t struct_size;
+    uint32_t n_slots;
+    uint64_t cells_total;
+    uint64_t cells_used;
+    uint64_t kv_bytes;
+    uint64_t recurrent_bytes;
+} retro_engine_memory_info;
+
+/* ---- engine handle (retro_lora_train.h:2465-2509) ---- */
+
+typedef struct retro_engine retro_engine;
+
+enum retro_engine_kv_dtype {
+    RETRO_ENGINE_KV_DTYPE_F32 = 0,
+    RETRO_ENGINE_KV_DTYPE_F16 = 1,
+    RETRO_ENGINE_KV_DTYPE_Q8_0 = 2,
+    RETRO_ENGINE_KV_DTYPE_Q4_0 = 3,
+};
+
+enum retro_device {
+    RETRO_DEVICE_AUTO = 0,
+    RETRO_DEVICE_CPU = 1,
+    RETRO_DEVICE_GPU = 2,
+};
+
+enum retro_expert_placement {
+    RETRO_EXPERT_PLACEMENT_DEVICE = 0,
+    RETRO_EXPERT_PLACEMENT_HOST = 1,
+};
+
+typedef struct retro_engine_config {
+    uint32_t struct_size;
+    uint32_t n_ctx;
+    uint32_t n_seq_max;
+    uint32_t n_batch;
+    uint32_t n_ubatch;
+    int32_t  kv_dtype;
+    bool     flash_attn;
+    int32_t  device;
+    uint32_t threads;
+    bool     verbose;
+    uint32_t kv_unified;
+    int32_t  expert_placement;
+    uint32_t expert_host_layers;
+    uint64_t expert_device_cache_bytes;
+} retro_engine_config;
+
+retro_engine * retro_engine_new(const char * model_path, const retro_engine_config * config);
+retro_engine * retro_engine_new_checked(const char * model_path, const retro_engine_config * config,
+                                        bool * out_invalid_placement);
+void retro_engine_free(retro_engine * engine);
+
+/* ---- vocabulary introspection (retro_lora_train.h:2538-2561) ---- */
+int retro_engine_eos_token(retro_engine * engine, int32_t * out_token);
+int retro_engine_vocab_size(retro_engine * engine, uint32_t * out_n_vocab);
+int retro_engine_is_eog_token(retro_engine * engine, int32_t token, bool * out_is_eog);
+int retro_engine_context_size(retro_engine * engine, uint32_t * out_n_ctx);
+int retro_engine_detokenize(retro_engine * engine, const int32_t * tokens, size_t n_tokens, bool unparse_special,
+                            char * buffer, size_t n_buffer, size_t * out_n_bytes);
+int retro_engine_tokenize_text(retro_engine * engine, const char * text, int32_t * tokens, size_t n_tokens_max,
+                               size_t * out_n_tokens);
+int retro_engine_tokenize_fragment(retro_engine * engine, const char * text, int32_t * tokens, size_t n_tokens_max,
+                                   size_t * out_n_tokens);
+
+/* ---- per-row adapters (retro_lora_train.h:2597-2612) ---- */
+int retro_engine_adapter_load(retro_engine * engine, const char * adapter_path, float scale, int32_t * out_id);
+int retro_engine_adapter_unload(retro_engine * engine, int32_t id);
+int retro_engine_adapter_rows_info(retro_engine * engine, retro_adapter_rows_info * out_info);
+int retro_engine_graphs_reused(retro_engine * engine, uint64_t * out_n_reused);
+
+/* ---- step-wise generation (retro_lora_train.h:2712-2719,1410-1417) ---- */
+int retro_engine_step(retro_engine * engine, const retro_step_row * rows, size_t n_rows, retro_step_out_row * out_rows,
+                      int32_t * out_top_ids, float * out_top_logprobs, size_t n_top_stride);
+int retro_engine_step_v2(retro_engine * engine, const retro_step_row_v2 * rows, size_t n_rows,
+                         retro_step_out_row_v2 * out_rows, int32_t * out_top_ids, float * out_top_logprobs,
+                         size_t n_top_stride);
+
+/* ---- sequence memory (retro_lora_train.h:2721-2775) ---- */
+int retro_engine_seq_rm(retro_engine * engine, int32_t slot, int32_t p0, int32_t p1);
+int retro_engine_seq_cp(retro_engine * engine, int32_t src, int32_t dst, int32_t p0, int32_t p1);
+int retro_engine_seq_save(retro_engine * engine, int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_buffer,
+                          size_t * out_n_bytes);
+int retro_engine_seq_load(retro_engine * engine, int32_t slot, uint32_t flags, const uint8_t * buffer, size_t n_bytes,
+                          size_t * out_n_read);
+int retro_engine_seq_pos(retro_engine * engine, int32_t slot, int32_t * out_pos_min, int32_t * out_pos_max);
+int retro_engine_memory(retro_engine * engine, retro_engine_memory_info * out);
+int retro_engine_request_free(retro_engine * engine, int32_t request);
+int retro_engine_kv_unified(retro_engine * engine, bool * out_unified);
+
+/* ---- cache keys (retro_lora_train.h:2796-2808) ---- */
+int retro_engine_weights_version(retro_engine * engine, uint64_t * out_version);
+int retro_engine_model_fingerprint(retro_engine * engine, uint64_t * out_fingerprint);
+int retro_engine_is_hybrid(retro_engine * engine, bool * out_is_hybrid);
+
+/* ---- MoE routing telemetry (retro_lora_train.h:2791-2794) ---- */
+int retro_engine_expert_route_enable(retro_engine * engine, uint32_t sample_every);
+int retro_engine_expert_route_counts(retro_engine * engine, uint32_t layer, uint32_t * out, size_t n_expert);
+int retro_engine_expert_route_reset(retro_engine * engine);
+
+/* ================= extensions without a counterpart in the reference ================= */
+
+/* Writes a seeded random model as GGUF. `spec` is whitespace-separated key=value pairs:
+ * arch(llama|qwen2|olmoe) layers d heads kv_heads head_dim ff vocab experts experts_used
+ * dtype expert_dtype embd_dtype (f32|f16|q8_0|q4_k|mxfp4) std seed bias rope_base eps dist. */
+int retro_b200_synth_gguf(const char * path, const char * spec, uint64_t * out_bytes);
+
+/* Encodes `n` floats as one stored row of `ggml_type` (0 f32, 1 f16, 8 q8_0, 12 q4_K, 39 mxfp4)
+ * with the same encoders the synthesiser uses. */
+int retro_b200_quantize_row(uint32_t ggml_type, const float * values, size_t n, uint8_t * out, size_t n_out, size_t * out_bytes);
+
+/* Batch maps the GPU packing kernel built for the last step: tok_slot/tok_pos/tok_row/tok_cell
+ * are `n_tokens` entries, out_index `n_out`, cu_rows `n_rows + 1`. Pass NULL to skip an array. */
+int retro_b200_engine_last_pack(retro_engine * engine, size_t * n_tokens, size_t * n_out, int32_t * tok_slot,
+                                int32_t * tok_pos, int32_t * tok_row, int32_t * tok_cell, int32_t * out_index,
+                                int32_t * cu_rows, size_t capacity);
+/* Logits row `index` (0-based among the sampling rows, row order) of the last step. */
+int retro_b200_engine_last_logits(retro_engine * engine, size_t index, float * out, size_t n_vocab);
+/* Expert ids chosen by the router in the last step: [layer][token][k], selection order. */
+int retro_b200_engine_last_routes(retro_engine * engine, int32_t * out, size_t n_max, size_t * out_count);
+/* Block table of a slot: physical block ids covering positions [0, pos_max]; the KV block
+ * size (tokens per block) is written to *out_block_tokens. */
+int retro_b200_engine_block_table(retro_engine * engine, int32_t slot, int32_t * out_blocks, size_t n_max,
+                                  size_t * out_count, uint32_t * out_block_tokens);
+/* Physical KV blocks in use (shared blocks counted once) and the total. */
+int retro_b200_engine_blocks(retro_engine * engine, uint64_t * out_used, uint64_t * out_total);
+/* Device time of the last step in milliseconds (CUDA events around its kernels) and the number
+ * of kernels it launched. */
+int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uint64_t * out_launches);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* RETRO_B200_H */

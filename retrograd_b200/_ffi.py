@@ -1,0 +1,193 @@
+"""ctypes declarations of libretro_b200's C ABI (include/retro_b200.h)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libretro_b200.so"
+
+
+class SamplingParamsC(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("max_new_tokens", C.c_uint32), ("seed", C.c_uint32)]
+
+
+class StepRowC(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("request", C.c_int32),
+        ("slot", C.c_int32),
+        ("tokens", C.POINTER(C.c_int32)),
+        ("n", C.c_uint32),
+        ("pos0", C.c_int32),
+        ("sample", C.c_bool),
+        ("sampling", SamplingParamsC),
+        ("n_top_logprobs", C.c_uint32),
+        ("adapter", C.c_int32),
+    ]
+
+
+class StepOutRowC(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("token", C.c_int32),
+        ("logprob", C.c_float),
+        ("n_top", C.c_uint32),
+        ("forced", C.c_uint8),
+        ("sampled", C.c_uint8),
+    ]
+
+
+class SamplingParamsV2C(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("temperature", C.c_float),
+        ("top_p", C.c_float),
+        ("max_new_tokens", C.c_uint32),
+        ("seed", C.c_uint32),
+        ("top_k", C.c_int32),
+        ("min_p", C.c_float),
+        ("repeat_penalty", C.c_float),
+        ("frequency_penalty", C.c_float),
+        ("presence_penalty", C.c_float),
+        ("penalty_window", C.c_uint32),
+        ("n_logit_bias", C.c_uint32),
+        ("logit_bias_ids", C.POINTER(C.c_int32)),
+        ("logit_bias_values", C.POINTER(C.c_float)),
+        ("grammar", C.c_void_p),
+    ]
+
+
+class StepRowV2C(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("request", C.c_int32),
+        ("slot", C.c_int32),
+        ("tokens", C.POINTER(C.c_int32)),
+        ("n", C.c_uint32),
+        ("pos0", C.c_int32),
+        ("sample", C.c_bool),
+        ("sampling", SamplingParamsV2C),
+        ("n_top_logprobs", C.c_uint32),
+        ("want_logprob", C.c_uint8),
+        ("adapter", C.c_int32),
+    ]
+
+
+class StepOutRowV2C(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("token", C.c_int32),
+        ("logprob", C.c_float),
+        ("n_top", C.c_uint32),
+        ("forced", C.c_uint8),
+        ("sampled", C.c_uint8),
+        ("sampled_logprob", C.c_float),
+    ]
+
+
+class EngineConfigC(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("n_ctx", C.c_uint32),
+        ("n_seq_max", C.c_uint32),
+        ("n_batch", C.c_uint32),
+        ("n_ubatch", C.c_uint32),
+        ("kv_dtype", C.c_int32),
+        ("flash_attn", C.c_bool),
+        ("device", C.c_int32),
+        ("threads", C.c_uint32),
+        ("verbose", C.c_bool),
+        ("kv_unified", C.c_uint32),
+        ("expert_placement", C.c_int32),
+        ("expert_host_layers", C.c_uint32),
+        ("expert_device_cache_bytes", C.c_uint64),
+    ]
+
+
+class MemoryInfoC(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("n_slots", C.c_uint32),
+        ("cells_total", C.c_uint64),
+        ("cells_used", C.c_uint64),
+        ("kv_bytes", C.c_uint64),
+        ("recurrent_bytes", C.c_uint64),
+    ]
+
+
+class AdapterRowsInfoC(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("n_adapters", C.c_uint32),
+        ("max_rank", C.c_uint32),
+        ("stacked_bytes", C.c_uint64),
+        ("unpadded_bytes", C.c_uint64),
+    ]
+
+
+# Every symbol include/retro_b200.h declares: name -> (restype, argtypes).
+_P = C.POINTER
+SYMBOLS = {
+    "retro_last_error": (C.c_char_p, []),
+    "retro_engine_new": (C.c_void_p, [C.c_char_p, _P(EngineConfigC)]),
+    "retro_engine_new_checked": (C.c_void_p, [C.c_char_p, _P(EngineConfigC), _P(C.c_bool)]),
+    "retro_engine_free": (None, [C.c_void_p]),
+    "retro_engine_eos_token": (C.c_int, [C.c_void_p, _P(C.c_int32)]),
+    "retro_engine_vocab_size": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
+    "retro_engine_is_eog_token": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_bool)]),
+    "retro_engine_context_size": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
+    "retro_engine_detokenize": (C.c_int, [C.c_void_p, _P(C.c_int32), C.c_size_t, C.c_bool, C.c_char_p, C.c_size_t, _P(C.c_size_t)]),
+    "retro_engine_tokenize_text": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_int32), C.c_size_t, _P(C.c_size_t)]),
+    "retro_engine_tokenize_fragment": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_int32), C.c_size_t, _P(C.c_size_t)]),
+    "retro_engine_adapter_load": (C.c_int, [C.c_void_p, C.c_char_p, C.c_float, _P(C.c_int32)]),
+    "retro_engine_adapter_unload": (C.c_int, [C.c_void_p, C.c_int32]),
+    "retro_engine_adapter_rows_info": (C.c_int, [C.c_void_p, _P(AdapterRowsInfoC)]),
+    "retro_engine_graphs_reused": (C.c_int, [C.c_void_p, _P(C.c_uint64)]),
+    "retro_engine_step": (C.c_int, [C.c_void_p, _P(StepRowC), C.c_size_t, _P(StepOutRowC), _P(C.c_int32), _P(C.c_float), C.c_size_t]),
+    "retro_engine_step_v2": (C.c_int, [C.c_void_p, _P(StepRowV2C), C.c_size_t, _P(StepOutRowV2C), _P(C.c_int32), _P(C.c_float), C.c_size_t]),
+    "retro_engine_seq_rm": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32]),
+    "retro_engine_seq_cp": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "retro_engine_seq_save": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint32, _P(C.c_uint8), C.c_size_t, _P(C.c_size_t)]),
+    "retro_engine_seq_load": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint32, _P(C.c_uint8), C.c_size_t, _P(C.c_size_t)]),
+    "retro_engine_seq_pos": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_int32), _P(C.c_int32)]),
+    "retro_engine_memory": (C.c_int, [C.c_void_p, _P(MemoryInfoC)]),
+    "retro_engine_request_free": (C.c_int, [C.c_void_p, C.c_int32]),
+    "retro_engine_kv_unified": (C.c_int, [C.c_void_p, _P(C.c_bool)]),
+    "retro_engine_weights_version": (C.c_int, [C.c_void_p, _P(C.c_uint64)]),
+    "retro_engine_model_fingerprint": (C.c_int, [C.c_void_p, _P(C.c_uint64)]),
+    "retro_engine_is_hybrid": (C.c_int, [C.c_void_p, _P(C.c_bool)]),
+    "retro_engine_expert_route_enable": (C.c_int, [C.c_void_p, C.c_uint32]),
+    "retro_engine_expert_route_counts": (C.c_int, [C.c_void_p, C.c_uint32, _P(C.c_uint32), C.c_size_t]),
+    "retro_engine_expert_route_reset": (C.c_int, [C.c_void_p]),
+    "retro_b200_synth_gguf": (C.c_int, [C.c_char_p, C.c_char_p, _P(C.c_uint64)]),
+    "retro_b200_quantize_row": (C.c_int, [C.c_uint32, _P(C.c_float), C.c_size_t, _P(C.c_uint8), C.c_size_t, _P(C.c_size_t)]),
+    "retro_b200_engine_last_pack": (
+        C.c_int,
+        [C.c_void_p, _P(C.c_size_t), _P(C.c_size_t), _P(C.c_int32), _P(C.c_int32), _P(C.c_int32), _P(C.c_int32), _P(C.c_int32), _P(C.c_int32), C.c_size_t],
+    ),
+    "retro_b200_engine_last_logits": (C.c_int, [C.c_void_p, C.c_size_t, _P(C.c_float), C.c_size_t]),
+    "retro_b200_engine_last_routes": (C.c_int, [C.c_void_p, _P(C.c_int32), C.c_size_t, _P(C.c_size_t)]),
+    "retro_b200_engine_block_table": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_int32), C.c_size_t, _P(C.c_size_t), _P(C.c_uint32)]),
+    "retro_b200_engine_blocks": (C.c_int, [C.c_void_p, _P(C.c_uint64), _P(C.c_uint64)]),
+    "retro_b200_engine_last_step_stats": (C.c_int, [C.c_void_p, _P(C.c_float), _P(C.c_uint64)]),
+}
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """Loads libretro_b200.so and binds every declared symbol; raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} has not been built: run `python -m retrograd_b200.build` (there is no fallback implementation)"
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib

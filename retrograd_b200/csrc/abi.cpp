@@ -1,0 +1,745 @@
+// extern "C" surface of libretro_b200. Each entry point mirrors the reference entry point of the
+// same name (crates/retrograd-ffi/runtime/src/retro_engine.cpp:454-1709): struct_size-prefixed
+// config copy, validation messages, status codes, thread-local error, exception fence.
+
+#include "engine.hpp"
+#include "blocks.hpp"
+
+#include <algorithm>
+#include <climits>
+#include <cstddef>
+#include <cstring>
+
+namespace rb200 {
+uint64_t synth_gguf(const char * path, const char * spec_text);
+size_t quantize_row(uint32_t type, const float * x, size_t n, uint8_t * out);
+}
+
+using namespace rb200;
+
+// Layouts of the published header (crates/retrograd-ffi/src/lib.rs:2899-3052).
+static_assert(sizeof(retro_engine_config) == 64 && alignof(retro_engine_config) == 8, "retro_engine_config layout");
+static_assert(offsetof(retro_engine_config, n_ctx) == 4 && offsetof(retro_engine_config, n_seq_max) == 8 &&
+              offsetof(retro_engine_config, n_batch) == 12 && offsetof(retro_engine_config, n_ubatch) == 16 &&
+              offsetof(retro_engine_config, kv_dtype) == 20 && offsetof(retro_engine_config, flash_attn) == 24 &&
+              offsetof(retro_engine_config, device) == 28 && offsetof(retro_engine_config, threads) == 32 &&
+              offsetof(retro_engine_config, verbose) == 36 && offsetof(retro_engine_config, kv_unified) == 40 &&
+              offsetof(retro_engine_config, expert_placement) == 44 && offsetof(retro_engine_config, expert_host_layers) == 48 &&
+              offsetof(retro_engine_config, expert_device_cache_bytes) == 56, "retro_engine_config offsets");
+static_assert(sizeof(retro_sampling_params) == 16, "retro_sampling_params layout");
+static_assert(sizeof(retro_step_row) == 64 && alignof(retro_step_row) == 8, "retro_step_row layout");
+static_assert(offsetof(retro_step_row, request) == 4 && offsetof(retro_step_row, slot) == 8 && offsetof(retro_step_row, tokens) == 16 &&
+              offsetof(retro_step_row, n) == 24 && offsetof(retro_step_row, pos0) == 28 && offsetof(retro_step_row, sample) == 32 &&
+              offsetof(retro_step_row, sampling) == 36 && offsetof(retro_step_row, n_top_logprobs) == 52 &&
+              offsetof(retro_step_row, adapter) == 56, "retro_step_row offsets");
+static_assert(sizeof(retro_step_out_row) == 20 && alignof(retro_step_out_row) == 4, "retro_step_out_row layout");
+static_assert(offsetof(retro_step_out_row, token) == 4 && offsetof(retro_step_out_row, logprob) == 8 && offsetof(retro_step_out_row, n_top) == 12 &&
+              offsetof(retro_step_out_row, forced) == 16 && offsetof(retro_step_out_row, sampled) == 17, "retro_step_out_row offsets");
+static_assert(sizeof(retro_sampling_params_v2) == 72 && alignof(retro_sampling_params_v2) == 8, "retro_sampling_params_v2 layout");
+static_assert(offsetof(retro_sampling_params_v2, temperature) == 4 && offsetof(retro_sampling_params_v2, top_p) == 8 &&
+              offsetof(retro_sampling_params_v2, max_new_tokens) == 12 && offsetof(retro_sampling_params_v2, seed) == 16 &&
+              offsetof(retro_sampling_params_v2, top_k) == 20 && offsetof(retro_sampling_params_v2, min_p) == 24 &&
+              offsetof(retro_sampling_params_v2, repeat_penalty) == 28 && offsetof(retro_sampling_params_v2, frequency_penalty) == 32 &&
+              offsetof(retro_sampling_params_v2, presence_penalty) == 36 && offsetof(retro_sampling_params_v2, penalty_window) == 40 &&
+              offsetof(retro_sampling_params_v2, n_logit_bias) == 44 && offsetof(retro_sampling_params_v2, logit_bias_ids) == 48 &&
+              offsetof(retro_sampling_params_v2, logit_bias_values) == 56 && offsetof(retro_sampling_params_v2, grammar) == 64,
+              "retro_sampling_params_v2 offsets");
+static_assert(sizeof(retro_step_row_v2) == 128 && alignof(retro_step_row_v2) == 8, "retro_step_row_v2 layout");
+static_assert(offsetof(retro_step_row_v2, request) == 4 && offsetof(retro_step_row_v2, slot) == 8 && offsetof(retro_step_row_v2, tokens) == 16 &&
+              offsetof(retro_step_row_v2, n) == 24 && offsetof(retro_step_row_v2, pos0) == 28 && offsetof(retro_step_row_v2, sample) == 32 &&
+              offsetof(retro_step_row_v2, sampling) == 40 && offsetof(retro_step_row_v2, n_top_logprobs) == 112 &&
+              offsetof(retro_step_row_v2, want_logprob) == 116 && offsetof(retro_step_row_v2, adapter) == 120, "retro_step_row_v2 offsets");
+static_assert(sizeof(retro_step_out_row_v2) == 24 && offsetof(retro_step_out_row_v2, sampled_logprob) == 20, "retro_step_out_row_v2 layout");
+static_assert(sizeof(retro_engine_memory_info) == 40 && offsetof(retro_engine_memory_info, n_slots) == 4 &&
+              offsetof(retro_engine_memory_info, cells_total) == 8 && offsetof(retro_engine_memory_info, cells_used) == 16 &&
+              offsetof(retro_engine_memory_info, kv_bytes) == 24 && offsetof(retro_engine_memory_info, recurrent_bytes) == 32,
+              "retro_engine_memory_info layout");
+static_assert(sizeof(retro_adapter_rows_info) == 32 && offsetof(retro_adapter_rows_info, n_adapters) == 4 &&
+              offsetof(retro_adapter_rows_info, max_rank) == 8 && offsetof(retro_adapter_rows_info, stacked_bytes) == 16 &&
+              offsetof(retro_adapter_rows_info, unpadded_bytes) == 24, "retro_adapter_rows_info layout");
+
+namespace {
+
+retro_engine_config default_engine_config() {
+    retro_engine_config c{};
+    c.struct_size = sizeof(retro_engine_config);
+    c.n_ctx = 4096;
+    c.n_seq_max = 8;
+    c.n_batch = 512;
+    c.n_ubatch = 512;
+    c.kv_dtype = RETRO_ENGINE_KV_DTYPE_F16;
+    c.flash_attn = true;
+    c.device = RETRO_DEVICE_AUTO;
+    c.threads = 0;
+    c.verbose = false;
+    c.kv_unified = 1;
+    c.expert_placement = RETRO_EXPERT_PLACEMENT_DEVICE;
+    c.expert_host_layers = 0;
+    c.expert_device_cache_bytes = 0;
+    return c;
+}
+
+bool validate_engine_config(const retro_engine_config & c) {
+    if (c.n_ctx == 0 || c.n_seq_max == 0) {
+        set_error("engine n_ctx and n_seq_max must be greater than zero");
+        return false;
+    }
+    if (c.n_batch == 0 || c.n_ubatch == 0 || c.n_ubatch > c.n_batch) {
+        set_error("engine n_ubatch must be in (0, n_batch]");
+        return false;
+    }
+    if (c.n_ctx > INT32_MAX || c.n_batch > INT32_MAX || c.n_ubatch > INT32_MAX || c.threads > INT32_MAX) {
+        set_error("engine context, batch and thread counts must fit in int32_t");
+        return false;
+    }
+    if (c.n_seq_max > kMaxSeq || c.n_seq_max > std::min(c.n_batch, c.n_ctx)) {
+        set_error("engine n_seq_max must not exceed LLAMA_MAX_SEQ, n_batch or n_ctx");
+        return false;
+    }
+    if (c.kv_dtype < RETRO_ENGINE_KV_DTYPE_F32 || c.kv_dtype > RETRO_ENGINE_KV_DTYPE_Q4_0) {
+        set_error("engine kv_dtype must be one of retro_engine_kv_dtype");
+        return false;
+    }
+    if ((c.kv_dtype == RETRO_ENGINE_KV_DTYPE_Q8_0 || c.kv_dtype == RETRO_ENGINE_KV_DTYPE_Q4_0) && !c.flash_attn) {
+        set_error("a quantized engine kv_dtype requires flash_attn");
+        return false;
+    }
+    if (c.device < RETRO_DEVICE_AUTO || c.device > RETRO_DEVICE_GPU) {
+        set_error("engine device must be one of retro_device");
+        return false;
+    }
+    if (c.expert_placement != RETRO_EXPERT_PLACEMENT_DEVICE && c.expert_placement != RETRO_EXPERT_PLACEMENT_HOST) {
+        set_error("engine expert_placement must be one of retro_expert_placement");
+        return false;
+    }
+    return true;
+}
+
+Engine * checked(retro_engine * engine) {
+    if (!engine) {
+        set_error("engine handle is null");
+        return nullptr;
+    }
+    return reinterpret_cast<Engine *>(engine);
+}
+
+bool is_blank(const char * s) {
+    if (!s) return true;
+    for (; *s; ++s) if (!isspace((unsigned char)*s)) return false;
+    return true;
+}
+
+int write_string_out(const std::string & s, char * buffer, size_t n_buffer, size_t * out_n) {
+    if (!out_n) {
+        set_error("out_n_bytes is required");
+        return STATUS_RUNTIME;
+    }
+    *out_n = s.size();
+    if (!buffer || n_buffer == 0) return STATUS_OK;
+    if (n_buffer < s.size()) {
+        set_error("the output buffer is too small");
+        return STATUS_BUFFER_TOO_SMALL;
+    }
+    std::memcpy(buffer, s.data(), s.size());
+    return STATUS_OK;
+}
+
+// Byte-fallback SentencePiece-style pieces: `<0xNN>` is one byte, U+2581 is a space.
+std::string piece_bytes(const Model & m, int32_t token, bool unparse_special) {
+    if (token < 0 || (size_t)token >= m.vocab_tokens.size()) return "";
+    const std::string & t = m.vocab_tokens[token];
+    const int32_t type = (size_t)token < m.vocab_types.size() ? m.vocab_types[token] : 1;
+    if (type == 6 && t.size() == 6 && t[0] == '<' && t[1] == '0' && t[2] == 'x') {
+        return std::string(1, (char)std::stoi(t.substr(3, 2), nullptr, 16));
+    }
+    if (type == 3 || type == 2) return unparse_special ? t : "";
+    std::string out;
+    for (size_t i = 0; i < t.size();) {
+        if (i + 2 < t.size() && (uint8_t)t[i] == 0xE2 && (uint8_t)t[i + 1] == 0x96 && (uint8_t)t[i + 2] == 0x81) {
+            out.push_back(' ');
+            i += 3;
+        } else {
+            out.push_back(t[i++]);
+        }
+    }
+    return out;
+}
+
+int tokenize_into(Engine & e, const char * text, bool add_special, int32_t * tokens, size_t n_max, size_t * out_n) {
+    if (!text || !out_n) {
+        set_error("text and out_n_tokens are required");
+        return STATUS_RUNTIME;
+    }
+    const Model & m = *e.model;
+    // byte id lookup, built on first use from the `<0xNN>` pieces
+    static thread_local const Model * cached = nullptr;
+    static thread_local int32_t byte_id[256];
+    if (cached != &m) {
+        std::fill(byte_id, byte_id + 256, -1);
+        for (size_t i = 0; i < m.vocab_tokens.size(); ++i) {
+            const std::string & t = m.vocab_tokens[i];
+            if (t.size() == 6 && t[0] == '<' && t[1] == '0' && t[2] == 'x' && t[5] == '>') byte_id[std::stoi(t.substr(3, 2), nullptr, 16)] = (int32_t)i;
+        }
+        cached = &m;
+    }
+    std::vector<int32_t> out;
+    if (add_special && m.add_bos) out.push_back(m.bos);
+    for (const unsigned char * p = (const unsigned char *)text; *p; ++p) {
+        if (byte_id[*p] < 0) {
+            set_error("the model's vocabulary has no byte-fallback pieces");
+            return STATUS_RUNTIME;
+        }
+        out.push_back(byte_id[*p]);
+    }
+    *out_n = out.size();
+    if (!tokens || n_max == 0) return STATUS_OK;
+    if (n_max < out.size()) {
+        set_error("the token buffer is too small");
+        return STATUS_BUFFER_TOO_SMALL;
+    }
+    std::memcpy(tokens, out.data(), out.size() * 4);
+    return STATUS_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+const char * retro_last_error(void) { return last_error().c_str(); }
+
+retro_engine * retro_engine_new(const char * model_path, const retro_engine_config * config) {
+    return retro_engine_new_checked(model_path, config, nullptr);
+}
+
+retro_engine * retro_engine_new_checked(const char * model_path, const retro_engine_config * config, bool * out_invalid_placement) {
+    if (out_invalid_placement) *out_invalid_placement = false;
+    try {
+        clear_error();
+        if (is_blank(model_path)) {
+            set_error("model_path is required");
+            return nullptr;
+        }
+        retro_engine_config resolved = default_engine_config();
+        if (config) {
+            uint32_t size = 0;
+            std::memcpy(&size, config, sizeof size);
+            constexpr size_t required = offsetof(retro_engine_config, verbose) + sizeof(bool);
+            if (size < required) {
+                set_error("retro_engine_config.struct_size is too small for this build");
+                return nullptr;
+            }
+            std::memcpy(&resolved, config, std::min<size_t>(size, sizeof resolved));
+        }
+        if (!validate_engine_config(resolved)) return nullptr;
+        if (resolved.device == RETRO_DEVICE_CPU) {
+            set_error("device=cpu requested but this library only runs on a CUDA GPU");
+            return nullptr;
+        }
+        if (resolved.kv_dtype != RETRO_ENGINE_KV_DTYPE_F16) {
+            set_error("this backend stores the KV cache as F16 only: engine kv_dtype must be RETRO_ENGINE_KV_DTYPE_F16");
+            return nullptr;
+        }
+        if (resolved.expert_placement != RETRO_EXPERT_PLACEMENT_DEVICE) {
+            if (out_invalid_placement) *out_invalid_placement = true;
+            set_error("this backend keeps every expert bank in device memory: expert_placement must be DEVICE");
+            return nullptr;
+        }
+        return reinterpret_cast<retro_engine *>(new Engine(model_path, resolved));
+    } catch (const std::exception & err) {
+        set_error(err.what());
+        return nullptr;
+    } catch (...) {
+        set_error("unknown C++ exception");
+        return nullptr;
+    }
+}
+
+void retro_engine_free(retro_engine * engine) { delete reinterpret_cast<Engine *>(engine); }
+
+int retro_engine_eos_token(retro_engine * engine, int32_t * out_token) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_token) {
+            if (e) set_error("out_token is required");
+            return STATUS_RUNTIME;
+        }
+        *out_token = e->model->eos;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_vocab_size(retro_engine * engine, uint32_t * out_n_vocab) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_n_vocab) {
+            if (e) set_error("out_n_vocab is required");
+            return STATUS_RUNTIME;
+        }
+        *out_n_vocab = e->model->hp.vocab;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_is_eog_token(retro_engine * engine, int32_t token, bool * out_is_eog) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_is_eog) {
+            if (e) set_error("out_is_eog is required");
+            return STATUS_RUNTIME;
+        }
+        if (token < 0 || (uint32_t)token >= e->model->hp.vocab) {
+            set_error("token is outside the vocabulary");
+            return STATUS_RUNTIME;
+        }
+        *out_is_eog = token == e->model->eos;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_context_size(retro_engine * engine, uint32_t * out_n_ctx) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_n_ctx) {
+            if (e) set_error("out_n_ctx is required");
+            return STATUS_RUNTIME;
+        }
+        *out_n_ctx = e->n_ctx_seq;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_detokenize(retro_engine * engine, const int32_t * tokens, size_t n_tokens, bool unparse_special, char * buffer,
+                            size_t n_buffer, size_t * out_n_bytes) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (!out_n_bytes) {
+            set_error("out_n_bytes is required");
+            return STATUS_RUNTIME;
+        }
+        if (n_tokens > 0 && !tokens) {
+            set_error("tokens are required");
+            return STATUS_RUNTIME;
+        }
+        std::string text;
+        for (size_t i = 0; i < n_tokens; ++i) {
+            if (tokens[i] < 0 || (uint32_t)tokens[i] >= e->model->hp.vocab) {
+                set_error("token is outside the vocabulary");
+                return STATUS_RUNTIME;
+            }
+            text += piece_bytes(*e->model, tokens[i], unparse_special);
+        }
+        return write_string_out(text, buffer, n_buffer, out_n_bytes);
+    });
+}
+
+int retro_engine_tokenize_text(retro_engine * engine, const char * text, int32_t * tokens, size_t n_tokens_max, size_t * out_n_tokens) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        return tokenize_into(*e, text, true, tokens, n_tokens_max, out_n_tokens);
+    });
+}
+
+int retro_engine_tokenize_fragment(retro_engine * engine, const char * text, int32_t * tokens, size_t n_tokens_max, size_t * out_n_tokens) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        return tokenize_into(*e, text, false, tokens, n_tokens_max, out_n_tokens);
+    });
+}
+
+int retro_engine_adapter_load(retro_engine * engine, const char * adapter_path, float scale, int32_t * out_id) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        return e->adapter_load(adapter_path, scale, out_id);
+    });
+}
+
+int retro_engine_adapter_unload(retro_engine * engine, int32_t id) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        return e->adapter_unload(id);
+    });
+}
+
+int retro_engine_adapter_rows_info(retro_engine * engine, retro_adapter_rows_info * out_info) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_info) {
+            if (e) set_error("out_info is required");
+            return STATUS_RUNTIME;
+        }
+        e->adapter_info(out_info);
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_graphs_reused(retro_engine * engine, uint64_t * out_n_reused) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_n_reused) {
+            if (e) set_error("out_n_reused is required");
+            return STATUS_RUNTIME;
+        }
+        *out_n_reused = e->graphs_reused;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_step(retro_engine * engine, const retro_step_row * rows, size_t n_rows, retro_step_out_row * out_rows,
+                      int32_t * out_top_ids, float * out_top_logprobs, size_t n_top_stride) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (!rows || n_rows == 0 || !out_rows) {
+            set_error("step rows and output rows are required");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        std::vector<EffRow> eff(n_rows);
+        for (size_t r = 0; r < n_rows; ++r) {
+            const retro_step_row & row = rows[r];
+            if (row.struct_size < offsetof(retro_step_row, adapter) + sizeof(int32_t)) {
+                set_error("retro_step_row.struct_size is too small for this build");
+                return STATUS_INVALID_ARGUMENT;
+            }
+            eff[r] = EffRow{row.struct_size, row.request, row.slot, row.tokens, row.n, row.pos0, row.sample, row.sampling, nullptr,
+                            row.n_top_logprobs, false, row.adapter};
+        }
+        std::vector<OutRow> internal(n_rows);
+        const int status = e->step(eff.data(), n_rows, internal.data(), out_top_ids, out_top_logprobs, n_top_stride);
+        if (status != 0) return status;
+        for (size_t r = 0; r < n_rows; ++r) {
+            retro_step_out_row & o = out_rows[r];
+            o.struct_size = sizeof(retro_step_out_row);
+            o.token = internal[r].token;
+            o.logprob = internal[r].logprob;
+            o.n_top = internal[r].n_top;
+            o.forced = internal[r].forced;
+            o.sampled = internal[r].sampled;
+        }
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_step_v2(retro_engine * engine, const retro_step_row_v2 * rows, size_t n_rows, retro_step_out_row_v2 * out_rows,
+                         int32_t * out_top_ids, float * out_top_logprobs, size_t n_top_stride) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (!rows || n_rows == 0 || !out_rows) {
+            set_error("step rows and output rows are required");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        std::vector<EffRow> eff(n_rows);
+        for (size_t r = 0; r < n_rows; ++r) {
+            const retro_step_row_v2 & row = rows[r];
+            if (row.struct_size < offsetof(retro_step_row_v2, adapter) + sizeof(int32_t)) {
+                set_error("retro_step_row_v2.struct_size is too small for this build");
+                return STATUS_INVALID_ARGUMENT;
+            }
+            if (row.sampling.struct_size < sizeof(retro_sampling_params_v2)) {
+                set_error("retro_sampling_params_v2.struct_size is too small for this build");
+                return STATUS_INVALID_ARGUMENT;
+            }
+            eff[r] = EffRow{row.struct_size, row.request, row.slot, row.tokens, row.n, row.pos0, row.sample, retro_sampling_params{},
+                            &row.sampling, row.n_top_logprobs, row.want_logprob != 0, row.adapter};
+        }
+        std::vector<OutRow> internal(n_rows);
+        const int status = e->step(eff.data(), n_rows, internal.data(), out_top_ids, out_top_logprobs, n_top_stride);
+        if (status != 0) return status;
+        for (size_t r = 0; r < n_rows; ++r) {
+            retro_step_out_row_v2 & o = out_rows[r];
+            o.struct_size = sizeof(retro_step_out_row_v2);
+            o.token = internal[r].token;
+            o.logprob = internal[r].logprob;
+            o.n_top = internal[r].n_top;
+            o.forced = internal[r].forced;
+            o.sampled = internal[r].sampled;
+            o.sampled_logprob = internal[r].sampled_logprob;
+        }
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_seq_rm(retro_engine * engine, int32_t slot, int32_t p0, int32_t p1) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->seq_rm(slot, p0, p1) : STATUS_RUNTIME;
+    });
+}
+
+int retro_engine_seq_cp(retro_engine * engine, int32_t src, int32_t dst, int32_t p0, int32_t p1) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->seq_cp(src, dst, p0, p1) : STATUS_RUNTIME;
+    });
+}
+
+int retro_engine_seq_save(retro_engine * engine, int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_buffer, size_t * out_n_bytes) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->seq_save(slot, flags, buffer, n_buffer, out_n_bytes) : STATUS_RUNTIME;
+    });
+}
+
+int retro_engine_seq_load(retro_engine * engine, int32_t slot, uint32_t flags, const uint8_t * buffer, size_t n_bytes, size_t * out_n_read) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->seq_load(slot, flags, buffer, n_bytes, out_n_read) : STATUS_RUNTIME;
+    });
+}
+
+int retro_engine_seq_pos(retro_engine * engine, int32_t slot, int32_t * out_pos_min, int32_t * out_pos_max) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->seq_pos(slot, out_pos_min, out_pos_max) : STATUS_RUNTIME;
+    });
+}
+
+int retro_engine_memory(retro_engine * engine, retro_engine_memory_info * out) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->memory(out) : STATUS_RUNTIME;
+    });
+}
+
+int retro_engine_request_free(retro_engine * engine, int32_t request) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        e->requests.erase(request);
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_kv_unified(retro_engine * engine, bool * out_unified) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_unified) {
+            if (e) set_error("out_unified is required");
+            return STATUS_RUNTIME;
+        }
+        *out_unified = e->config.kv_unified != 0;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_weights_version(retro_engine * engine, uint64_t * out_version) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_version) {
+            if (e) set_error("out_version is required");
+            return STATUS_RUNTIME;
+        }
+        *out_version = e->weights_version;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_model_fingerprint(retro_engine * engine, uint64_t * out_fingerprint) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_fingerprint) {
+            if (e) set_error("out_fingerprint is required");
+            return STATUS_RUNTIME;
+        }
+        *out_fingerprint = e->fingerprint;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_is_hybrid(retro_engine * engine, bool * out_is_hybrid) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_is_hybrid) {
+            if (e) set_error("out_is_hybrid is required");
+            return STATUS_RUNTIME;
+        }
+        *out_is_hybrid = false;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_expert_route_enable(retro_engine * engine, uint32_t sample_every) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        e->route_enabled = sample_every != 0;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_expert_route_counts(retro_engine * engine, uint32_t layer, uint32_t * out, size_t n_expert) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out) {
+            if (e) set_error("out is required");
+            return STATUS_RUNTIME;
+        }
+        if (layer >= e->route_counts.size() || n_expert < e->model->hp.n_expert) {
+            set_error("layer or expert count is outside the model's MoE geometry");
+            return STATUS_RUNTIME;
+        }
+        std::memcpy(out, e->route_counts[layer].data(), e->model->hp.n_expert * 4);
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_expert_route_reset(retro_engine * engine) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        for (auto & l : e->route_counts) std::fill(l.begin(), l.end(), 0u);
+        return STATUS_OK;
+    });
+}
+
+// ---- extensions -----------------------------------------------------------------------------
+
+int retro_b200_synth_gguf(const char * path, const char * spec, uint64_t * out_bytes) {
+    return boundary([&]() -> int {
+        if (is_blank(path)) {
+            set_error("path is required");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        const uint64_t n = synth_gguf(path, spec);
+        if (out_bytes) *out_bytes = n;
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_quantize_row(uint32_t ggml_type, const float * values, size_t n, uint8_t * out, size_t n_out, size_t * out_bytes) {
+    return boundary([&]() -> int {
+        if (!values || !out) {
+            set_error("values and out are required");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        const size_t need = row_bytes(ggml_type, n);
+        if (need == 0) {
+            set_error("unsupported type or partial block");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        if (n_out < need) {
+            set_error("the output buffer is too small");
+            return STATUS_BUFFER_TOO_SMALL;
+        }
+        const size_t written = quantize_row(ggml_type, values, n, out);
+        if (written == 0) {
+            set_error("unsupported type");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        if (out_bytes) *out_bytes = written;
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_last_pack(retro_engine * engine, size_t * n_tokens, size_t * n_out, int32_t * tok_slot, int32_t * tok_pos,
+                                int32_t * tok_row, int32_t * tok_cell, int32_t * out_index, int32_t * cu_rows, size_t capacity) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (n_tokens) *n_tokens = e->last_T;
+        if (n_out) *n_out = e->last_S;
+        if (capacity < e->last_T || capacity < e->last_R + 1) {
+            if (tok_slot || tok_pos || tok_row || tok_cell || out_index || cu_rows) {
+                set_error("the map buffers are too small");
+                return STATUS_BUFFER_TOO_SMALL;
+            }
+            return STATUS_OK;
+        }
+        auto fetch = [&](int32_t * dst, const int32_t * src, size_t n) {
+            if (dst && n) RB_CUDA(cudaMemcpy(dst, src, n * 4, cudaMemcpyDeviceToHost));
+        };
+        fetch(tok_slot, e->maps.tok_slot, e->last_T);
+        fetch(tok_pos, e->maps.tok_pos, e->last_T);
+        fetch(tok_row, e->maps.tok_row, e->last_T);
+        fetch(tok_cell, e->maps.tok_cell, e->last_T);
+        fetch(out_index, e->maps.out_index, e->last_S);
+        fetch(cu_rows, e->maps.cu_rows, e->last_R + 1);
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_last_logits(retro_engine * engine, size_t index, float * out, size_t n_vocab) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out) {
+            if (e) set_error("out is required");
+            return STATUS_RUNTIME;
+        }
+        if (index >= e->last_S || n_vocab < e->model->hp.vocab) {
+            set_error("no such logits row in the last step");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        RB_CUDA(cudaMemcpy(out, e->logits.ptr + index * (size_t)e->model->hp.vocab, (size_t)e->model->hp.vocab * 4, cudaMemcpyDeviceToHost));
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_last_routes(retro_engine * engine, int32_t * out, size_t n_max, size_t * out_count) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        const size_t n = (size_t)e->model->hp.n_layer * e->last_T * e->model->hp.n_expert_used;
+        if (out_count) *out_count = n;
+        if (out && n) {
+            if (n_max < n) {
+                set_error("the route buffer is too small");
+                return STATUS_BUFFER_TOO_SMALL;
+            }
+            RB_CUDA(cudaMemcpy(out, e->route_ids.ptr, n * 4, cudaMemcpyDeviceToHost));
+        }
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_block_table(retro_engine * engine, int32_t slot, int32_t * out_blocks, size_t n_max, size_t * out_count,
+                                  uint32_t * out_block_tokens) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (slot < 0 || slot >= (int32_t)e->config.n_seq_max) {
+            set_error("slot is outside the context's sequence range");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        const KvSlot & s = e->kv->slot(slot);
+        if (out_block_tokens) *out_block_tokens = e->kv->block_tokens();
+        const size_t n = s.empty() ? 0 : (size_t)s.pos_max / e->kv->block_tokens() + 1;
+        if (out_count) *out_count = n;
+        if (out_blocks && n) {
+            if (n_max < n) {
+                set_error("the block buffer is too small");
+                return STATUS_BUFFER_TOO_SMALL;
+            }
+            // read the device copy: it is what the kernels resolve positions through
+            RB_CUDA(cudaMemcpy(out_blocks, e->kv_block_table_device() + (size_t)slot * e->kv->max_blocks(), n * 4, cudaMemcpyDeviceToHost));
+            for (size_t i = 0; i < n; ++i) if (s.blocks[i] < 0) out_blocks[i] = -1;
+        }
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_blocks(retro_engine * engine, uint64_t * out_used, uint64_t * out_total) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (out_used) *out_used = e->kv->blocks_used();
+        if (out_total) *out_total = e->kv->n_blocks();
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uint64_t * out_launches) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (out_ms) *out_ms = e->last_ms;
+        if (out_launches) *out_launches = e->last_launches;
+        return STATUS_OK;
+    });
+}
+
+} // extern "C"

@@ -1,0 +1,1120 @@
+// The step executor: validates a step plan exactly as the reference's runtime does
+// (crates/retrograd-ffi/runtime/src/retro_gen_core.cpp:2399-2516 - same order, same messages,
+// all-or-nothing before anything is decoded), then runs the whole decode on the GPU: packing maps
+// and block-table resolution, the transformer forward over the paged KV cache, and sampling.
+// One host->device copy carries the plan in, one device->host copy carries the sampled rows out.
+
+#include "engine.hpp"
+#include "blocks.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <sstream>
+
+namespace rb200 {
+
+std::string & last_error() {
+    thread_local std::string message;
+    return message;
+}
+
+namespace {
+
+uint64_t fnv1a(const void * data, size_t n, uint64_t h = 0xcbf29ce484222325ULL) {
+    const uint8_t * p = static_cast<const uint8_t *>(data);
+    for (size_t i = 0; i < n; ++i) {
+        h ^= p[i];
+        h *= 0x100000001b3ULL;
+    }
+    return h;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+} // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Model load
+
+void Engine::load_model(const std::string & path) {
+    GgufFile file(path);
+    model = std::make_unique<Model>();
+    Model & m = *model;
+    HParams & hp = m.hp;
+    hp.arch = file.str("general.architecture");
+    if (hp.arch != "llama" && hp.arch != "qwen2" && hp.arch != "olmoe") {
+        throw std::runtime_error("failed to load model GGUF: architecture '" + hp.arch + "' is not served by this backend");
+    }
+    const std::string a = hp.arch;
+    hp.neox = a != "llama";
+    hp.n_layer = file.u32(a + ".block_count", 0);
+    hp.d = file.u32(a + ".embedding_length", 0);
+    hp.n_head = file.u32(a + ".attention.head_count", 0);
+    hp.n_head_kv = file.u32(a + ".attention.head_count_kv", hp.n_head);
+    hp.ff = file.u32(a + ".feed_forward_length", 0);
+    if (!hp.n_layer || !hp.d || !hp.n_head || !hp.n_head_kv || !hp.ff) throw std::runtime_error("failed to load model GGUF: missing hyper-parameters");
+    hp.head_dim = file.u32(a + ".attention.key_length", hp.d / hp.n_head);
+    hp.n_rot = file.u32(a + ".rope.dimension_count", hp.head_dim);
+    hp.eps = file.f32(a + ".attention.layer_norm_rms_epsilon", 1e-5f);
+    hp.rope_base = file.f32(a + ".rope.freq_base", 10000.f);
+    hp.n_expert = file.u32(a + ".expert_count", 0);
+    hp.n_expert_used = file.u32(a + ".expert_used_count", 0);
+    if (hp.head_dim > 256 || hp.head_dim % 8 != 0) throw std::runtime_error("failed to load model GGUF: unsupported head size");
+    if (hp.n_expert > 256) throw std::runtime_error("failed to load model GGUF: more than 256 experts");
+
+    auto upload = [&](const void * src, size_t bytes) -> uint8_t * {
+        void * p = nullptr;
+        RB_CUDA(cudaMalloc(&p, align_up(bytes, 256)));
+        m.allocations.push_back(p);
+        RB_CUDA(cudaMemcpy(p, src, bytes, cudaMemcpyHostToDevice));
+        m.weight_bytes += bytes;
+        return static_cast<uint8_t *>(p);
+    };
+    auto need = [&](const std::string & name) -> const GgufTensor & {
+        const GgufTensor * t = file.find(name);
+        if (!t) throw std::runtime_error("failed to load model GGUF: missing tensor " + name);
+        return *t;
+    };
+    auto view_of = [&](const GgufTensor & t, const uint8_t * dev, uint64_t rows) {
+        WeightView w;
+        w.data = dev;
+        w.type = t.type;
+        w.n_in = (uint32_t)t.ne[0];
+        w.n_out = (uint32_t)rows;
+        w.row_bytes = (uint32_t)row_bytes(t.type, t.ne[0]);
+        return w;
+    };
+    auto matrix = [&](const std::string & name, uint64_t n_in, uint64_t n_out) {
+        const GgufTensor & t = need(name);
+        if (t.ne.size() != 2 || t.ne[0] != n_in || t.ne[1] != n_out) throw std::runtime_error("failed to load model GGUF: unexpected shape of " + name);
+        if (n_in % 8 != 0) throw std::runtime_error("failed to load model GGUF: row length of " + name + " is not a multiple of 8");
+        return view_of(t, upload(t.data, t.n_bytes), n_out);
+    };
+    auto vector_f32 = [&](const std::string & name, uint64_t n, bool optional) -> const float * {
+        const GgufTensor * t = file.find(name);
+        if (!t) {
+            if (optional) return nullptr;
+            throw std::runtime_error("failed to load model GGUF: missing tensor " + name);
+        }
+        if (t->type != GGML_F32 || t->ne[0] != n) throw std::runtime_error("failed to load model GGUF: " + name + " must be F32 of the expected length");
+        return reinterpret_cast<const float *>(upload(t->data, t->n_bytes));
+    };
+    // Several matrices with one row length and storage type, stacked row-wise into one allocation.
+    auto fused = [&](const std::vector<std::string> & names, uint64_t n_in, const std::vector<uint64_t> & n_out, WeightView & out) -> bool {
+        uint32_t type = need(names[0]).type;
+        size_t total = 0;
+        for (size_t i = 0; i < names.size(); ++i) {
+            const GgufTensor & t = need(names[i]);
+            if (t.type != type || t.ne.size() != 2 || t.ne[0] != n_in || t.ne[1] != n_out[i]) return false;
+            total += t.n_bytes;
+        }
+        if (n_in % 8 != 0) return false;
+        void * p = nullptr;
+        RB_CUDA(cudaMalloc(&p, align_up(total, 256)));
+        m.allocations.push_back(p);
+        size_t off = 0;
+        uint64_t rows = 0;
+        for (size_t i = 0; i < names.size(); ++i) {
+            const GgufTensor & t = need(names[i]);
+            RB_CUDA(cudaMemcpy(static_cast<uint8_t *>(p) + off, t.data, t.n_bytes, cudaMemcpyHostToDevice));
+            off += t.n_bytes;
+            rows += n_out[i];
+        }
+        m.weight_bytes += total;
+        out = view_of(need(names[0]), static_cast<uint8_t *>(p), rows);
+        return true;
+    };
+
+    const GgufTensor & embd = need("token_embd.weight");
+    hp.vocab = (uint32_t)embd.ne[1];
+    if (embd.ne[0] != hp.d) throw std::runtime_error("failed to load model GGUF: token_embd width differs from embedding_length");
+    m.token_embd = view_of(embd, upload(embd.data, embd.n_bytes), hp.vocab);
+
+    const uint64_t dq = hp.dq(), dkv = hp.dkv();
+    m.layers.resize(hp.n_layer);
+    for (uint32_t l = 0; l < hp.n_layer; ++l) {
+        const std::string p = "blk." + std::to_string(l) + ".";
+        LayerWeights & lw = m.layers[l];
+        lw.attn_norm = vector_f32(p + "attn_norm.weight", hp.d, false);
+        if (!fused({p + "attn_q.weight", p + "attn_k.weight", p + "attn_v.weight"}, hp.d, {dq, dkv, dkv}, lw.wqkv)) {
+            lw.wq = matrix(p + "attn_q.weight", hp.d, dq);
+            lw.wk = matrix(p + "attn_k.weight", hp.d, dkv);
+            lw.wv = matrix(p + "attn_v.weight", hp.d, dkv);
+        }
+        if (file.find(p + "attn_q.bias")) {
+            std::vector<float> b(dq + 2 * dkv);
+            const GgufTensor & bq = need(p + "attn_q.bias");
+            const GgufTensor & bk = need(p + "attn_k.bias");
+            const GgufTensor & bv = need(p + "attn_v.bias");
+            if (bq.type != GGML_F32 || bk.type != GGML_F32 || bv.type != GGML_F32 || bq.ne[0] != dq || bk.ne[0] != dkv || bv.ne[0] != dkv) {
+                throw std::runtime_error("failed to load model GGUF: attention biases must be F32 of the projection width");
+            }
+            std::memcpy(b.data(), bq.data, dq * 4);
+            std::memcpy(b.data() + dq, bk.data, dkv * 4);
+            std::memcpy(b.data() + dq + dkv, bv.data, dkv * 4);
+            lw.bqkv = reinterpret_cast<const float *>(upload(b.data(), b.size() * 4));
+        }
+        lw.q_norm = vector_f32(p + "attn_q_norm.weight", dq, true);
+        lw.k_norm = vector_f32(p + "attn_k_norm.weight", dkv, true);
+        lw.wo = matrix(p + "attn_output.weight", dq, hp.d);
+        lw.ffn_norm = vector_f32(p + "ffn_norm.weight", hp.d, false);
+        if (hp.n_expert == 0) {
+            if (!fused({p + "ffn_gate.weight", p + "ffn_up.weight"}, hp.d, {hp.ff, hp.ff}, lw.wgu)) {
+                lw.wgate = matrix(p + "ffn_gate.weight", hp.d, hp.ff);
+                lw.wup = matrix(p + "ffn_up.weight", hp.d, hp.ff);
+            }
+            lw.wdown = matrix(p + "ffn_down.weight", hp.ff, hp.d);
+        } else {
+            lw.router = matrix(p + "ffn_gate_inp.weight", hp.d, hp.n_expert);
+            if (lw.router.type != GGML_F32) throw std::runtime_error("failed to load model GGUF: the router must be F32");
+            auto bank = [&](const std::string & name, uint64_t n_in, uint64_t n_out, WeightView & w, uint64_t & stride) {
+                const GgufTensor & t = need(name);
+                if (t.ne.size() != 3 || t.ne[0] != n_in || t.ne[1] != n_out || t.ne[2] != hp.n_expert || n_in % 8 != 0) {
+                    throw std::runtime_error("failed to load model GGUF: unexpected shape of " + name);
+                }
+                w = view_of(t, upload(t.data, t.n_bytes), n_out);
+                stride = (uint64_t)w.row_bytes * n_out;
+            };
+            bank(p + "ffn_gate_exps.weight", hp.d, hp.ff, lw.gate_exps, lw.gate_stride);
+            bank(p + "ffn_up_exps.weight", hp.d, hp.ff, lw.up_exps, lw.up_stride);
+            bank(p + "ffn_down_exps.weight", hp.ff, hp.d, lw.down_exps, lw.down_stride);
+        }
+    }
+    m.output_norm = vector_f32("output_norm.weight", hp.d, false);
+    if (file.find("output.weight")) {
+        m.output = matrix("output.weight", hp.d, hp.vocab);
+    } else {
+        m.output = m.token_embd;   // tied head
+    }
+    m.output_bias = vector_f32("output.bias", hp.vocab, true);
+
+    std::vector<float> inv(hp.n_rot / 2);
+    for (uint32_t i = 0; i < hp.n_rot / 2; ++i) inv[i] = (float)std::pow((double)hp.rope_base, -2.0 * i / hp.n_rot);
+    m.inv_freq.ensure(inv.size());
+    RB_CUDA(cudaMemcpy(m.inv_freq.ptr, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice));
+
+    if (const auto * toks = file.str_array("tokenizer.ggml.tokens")) m.vocab_tokens = *toks;
+    if (const auto * types = file.i32_array("tokenizer.ggml.token_type")) m.vocab_types = *types;
+    m.eos = (int32_t)file.u32("tokenizer.ggml.eos_token_id", 2);
+    m.bos = (int32_t)file.u32("tokenizer.ggml.bos_token_id", 1);
+    m.add_bos = file.u32("tokenizer.ggml.add_bos_token", 1) != 0;
+
+    // fingerprint = FNV-1a(path || u64 file size), as the reference keys its prefix caches
+    uint64_t h = fnv1a(path.data(), path.size());
+    const uint64_t size = file.file_size();
+    fingerprint = fnv1a(&size, sizeof size, h);
+}
+
+// ---------------------------------------------------------------------------------------------
+
+Engine::Engine(const std::string & path, const retro_engine_config & cfg) : config(cfg), model_path(path) {
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) {
+        throw std::runtime_error("device=gpu requested but no GPU backend is available; this library has no CPU path");
+    }
+    RB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    RB_CUDA(cudaEventCreate(&ev_begin_));
+    RB_CUDA(cudaEventCreate(&ev_end_));
+    load_model(path);
+    const HParams & hp = model->hp;
+    n_ctx_seq = config.kv_unified ? config.n_ctx : config.n_ctx / config.n_seq_max;
+    if (n_ctx_seq == 0) throw std::runtime_error("failed to create the engine context: n_ctx is smaller than n_seq_max on a partitioned pool");
+
+    const uint32_t n_blocks = (config.n_ctx + kBlockTokens - 1) / kBlockTokens + config.n_seq_max;
+    const uint32_t max_blocks = (n_ctx_seq + kBlockTokens - 1) / kBlockTokens;
+    kv = std::make_unique<KvManager>(config.n_seq_max, n_blocks, kBlockTokens, max_blocks);
+    kv_layer_stride_ = (uint64_t)n_blocks * hp.n_head_kv * kBlockTokens * hp.head_dim;
+    kcache_.ensure(kv_layer_stride_ * hp.n_layer);
+    vcache_.ensure(kv_layer_stride_ * hp.n_layer);
+    RB_CUDA(cudaMemsetAsync(kcache_.ptr, 0, kcache_.count * sizeof(__half), stream));
+    RB_CUDA(cudaMemsetAsync(vcache_.ptr, 0, vcache_.count * sizeof(__half), stream));
+    block_table_.ensure((size_t)config.n_seq_max * max_blocks);
+    RB_CUDA(cudaMemsetAsync(block_table_.ptr, 0, block_table_.count * 4, stream));
+
+    const size_t T = config.n_batch;
+    maps_store_.ensure(T * 7 + 2 * (T + 1));
+    int32_t * p = maps_store_.ptr;
+    maps.cu_rows = p; p += T + 1;
+    maps.out_rank = p; p += T + 1;
+    maps.tok_slot = p; p += T;
+    maps.tok_pos = p; p += T;
+    maps.tok_row = p; p += T;
+    maps.tok_cell = p; p += T;
+    maps.tok_adapter = p; p += T;
+    maps.tok_pos_min = p; p += T;
+    maps.out_index = p;
+
+    x_.ensure(T * hp.d);
+    xn_.ensure(T * hp.d);
+    qkv_.ensure(T * (hp.dq() + 2 * hp.dkv()));
+    att_.ensure(T * hp.dq());
+    if (hp.n_expert == 0) {
+        gu_.ensure(T * 2 * hp.ff);
+        hff_.ensure(T * hp.ff);
+    } else {
+        const size_t P = T * hp.n_expert_used;
+        router_logits_.ensure(T * hp.n_expert);
+        moe_ids_.ensure(P);
+        moe_w_.ensure(P);
+        pair_gu_.ensure(P * 2 * hp.ff);
+        pair_h_.ensure(P * hp.ff);
+        pair_y_.ensure(P * hp.d);
+        route_ids.ensure((size_t)hp.n_layer * P);
+        route_counts.assign(hp.n_layer, std::vector<uint32_t>(hp.n_expert, 0));
+    }
+    RB_CUDA(cudaStreamSynchronize(stream));
+}
+
+Engine::~Engine() {
+    if (stream) cudaStreamSynchronize(stream);
+    if (h_stage_) cudaFreeHost(h_stage_);
+    if (h_result_) cudaFreeHost(h_result_);
+    if (ev_begin_) cudaEventDestroy(ev_begin_);
+    if (ev_end_) cudaEventDestroy(ev_end_);
+    if (stream) cudaStreamDestroy(stream);
+}
+
+KvLayout Engine::kv_layout() const {
+    KvLayout l;
+    l.k = kcache_.ptr;
+    l.v = vcache_.ptr;
+    l.layer_stride = kv_layer_stride_;
+    l.n_head_kv = (int32_t)model->hp.n_head_kv;
+    l.head_dim = (int32_t)model->hp.head_dim;
+    l.block_tokens = (int32_t)kBlockTokens;
+    l.block_table = block_table_.ptr;
+    l.max_blocks = (int32_t)kv->max_blocks();
+    return l;
+}
+
+// Applies queued block-table patches and copy-on-write block copies outside a step
+// (sequence operations issued between steps).
+void Engine::flush_kv_updates() {
+    std::vector<int32_t> & patches = kv->patches();
+    std::vector<int32_t> & copies = kv->copies();
+    if (patches.empty() && copies.empty()) return;
+    const size_t n = patches.size() + copies.size();
+    d_aux_.ensure(n);
+    std::vector<int32_t> host(patches);
+    host.insert(host.end(), copies.begin(), copies.end());
+    RB_CUDA(cudaMemcpyAsync(d_aux_.ptr, host.data(), n * 4, cudaMemcpyHostToDevice, stream));
+    launch_block_table_patch(block_table_.ptr, d_aux_.ptr, (int)(patches.size() / 2), stream);
+    launch_kv_block_copy(kv_layout(), (int)model->hp.n_layer, d_aux_.ptr + patches.size(), (int)(copies.size() / 2), stream);
+    RB_CUDA(cudaStreamSynchronize(stream));
+    patches.clear();
+    copies.clear();
+}
+
+void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual,
+                    int ldr) {
+    launch_gemm_rows(w, x, ldx, T, y, ldy, bias, residual, ldr, stream);
+    ++last_launches;
+}
+
+void Engine::lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy) {
+    if (!cur_any_adapter_) return;
+    auto it = lora_targets_.find(target);
+    if (it == lora_targets_.end() || !it->second->present) return;
+    LoraTarget & t = *it->second;
+    launch_lora_shrink(t.a.ptr, (int)r_max_, (int)t.n_in, cur_tok_adapter_, x, ldx, T, lora_tmp_.ptr, stream);
+    launch_lora_expand(t.b.ptr, (int)r_max_, (int)t.n_out, lora_scales_.ptr, cur_tok_adapter_, lora_tmp_.ptr, T, y, ldy, stream);
+    last_launches += 2;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The step
+
+namespace {
+
+bool validate_tokens(const int32_t * tokens, size_t n, int32_t n_vocab) {
+    for (size_t i = 0; i < n; ++i) {
+        if (tokens[i] < 0 || tokens[i] >= n_vocab) {
+            std::ostringstream message;
+            message << "token " << tokens[i] << " at index " << i << " is outside the vocabulary of size " << n_vocab;
+            set_error(message.str());
+            return false;
+        }
+    }
+    return true;
+}
+
+bool validate_sampling(const retro_sampling_params & s) {
+    if (!(s.temperature > 0.0f) || !std::isfinite(s.temperature)) {
+        set_error("sampling temperature must be finite and greater than zero");
+        return false;
+    }
+    if (!(s.top_p > 0.0f && s.top_p <= 1.0f)) {
+        set_error("sampling top_p must be in (0, 1]");
+        return false;
+    }
+    if (s.max_new_tokens == 0) {
+        set_error("sampling max_new_tokens must be greater than zero");
+        return false;
+    }
+    return true;
+}
+
+bool validate_sampling_v2(const retro_sampling_params_v2 & s, int32_t n_vocab) {
+    if (s.struct_size < sizeof(retro_sampling_params_v2)) {
+        set_error("retro_sampling_params_v2.struct_size is too small for this build");
+        return false;
+    }
+    if (!(s.temperature > 0.0f) || !std::isfinite(s.temperature)) {
+        set_error("sampling temperature must be finite and greater than zero");
+        return false;
+    }
+    if (!(s.top_p > 0.0f && s.top_p <= 1.0f)) {
+        set_error("sampling top_p must be in (0, 1]");
+        return false;
+    }
+    if (!(s.repeat_penalty > 0.0f) || !std::isfinite(s.repeat_penalty)) {
+        set_error("sampling repeat_penalty must be finite and greater than zero");
+        return false;
+    }
+    if (!(s.min_p >= 0.0f && s.min_p <= 1.0f) || !std::isfinite(s.min_p)) {
+        set_error("sampling min_p must be in [0, 1]");
+        return false;
+    }
+    if (!std::isfinite(s.frequency_penalty)) {
+        set_error("sampling frequency_penalty must be finite");
+        return false;
+    }
+    if (!std::isfinite(s.presence_penalty)) {
+        set_error("sampling presence_penalty must be finite");
+        return false;
+    }
+    if (s.n_logit_bias > 4096) {
+        set_error("sampling n_logit_bias must not exceed 4096");
+        return false;
+    }
+    if (s.n_logit_bias > 0) {
+        if (!s.logit_bias_ids || !s.logit_bias_values) {
+            set_error("logit_bias ids and values are required when n_logit_bias is nonzero");
+            return false;
+        }
+        if (!validate_tokens(s.logit_bias_ids, s.n_logit_bias, n_vocab)) return false;
+        for (uint32_t i = 0; i < s.n_logit_bias; ++i) {
+            if (!std::isfinite(s.logit_bias_values[i])) {
+                set_error("logit_bias values must be finite");
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+} // namespace
+
+int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t * out_top_ids, float * out_top_logprobs, size_t n_top_stride) {
+    const HParams & hp = model->hp;
+    if (!rows || n_rows == 0 || !out_rows) {
+        set_error("step rows and output rows are required");
+        return STATUS_INVALID_ARGUMENT;
+    }
+    const int32_t n_seq_max = (int32_t)config.n_seq_max;
+    const int32_t n_batch = (int32_t)config.n_batch;
+    const int64_t ctx_seq = n_ctx_seq;
+    if (n_rows > (size_t)n_batch || (n_top_stride != 0 && n_rows > SIZE_MAX / n_top_stride)) {
+        set_error("the step row count or output shape exceeds capacity");
+        return STATUS_INVALID_ARGUMENT;
+    }
+    constexpr size_t row_prefix_v1 = offsetof(retro_step_row, adapter) + sizeof(int32_t);
+    constexpr size_t row_prefix_v2 = offsetof(retro_step_row_v2, adapter) + sizeof(int32_t);
+    std::vector<int32_t> seen_requests;
+    size_t total = 0, n_sample = 0;
+    for (size_t r = 0; r < n_rows; ++r) {
+        const EffRow & row = rows[r];
+        const bool is_v2 = row.v2 != nullptr;
+        if (row.struct_size < (is_v2 ? row_prefix_v2 : row_prefix_v1)) {
+            set_error(is_v2 ? "retro_step_row_v2.struct_size is too small for this build"
+                            : "retro_step_row.struct_size is too small for this build");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        if (!row.tokens || row.n == 0) {
+            set_error("a step row requires at least one token");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        if (row.slot < 0 || row.slot >= n_seq_max) {
+            set_error("step row slot is outside the context's sequence range");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        if (row.adapter != 0) {
+            if (row.adapter != RETRO_STEP_ADAPTER_BASE && adapters_.find(row.adapter) == adapters_.end()) {
+                set_error("step row adapter " + std::to_string(row.adapter) + " is not a loaded per-row adapter");
+                return STATUS_INVALID_ARGUMENT;
+            }
+        }
+        if (row.pos0 < 0 || (int64_t)row.pos0 + row.n > ctx_seq) {
+            set_error("step row positions exceed the per-sequence context");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        for (size_t previous = 0; previous < r; ++previous) {
+            const EffRow & other = rows[previous];
+            if (row.slot == other.slot && row.pos0 < (int64_t)other.pos0 + other.n && other.pos0 < (int64_t)row.pos0 + row.n) {
+                set_error("step rows overlap in the same sequence slot");
+                return STATUS_INVALID_ARGUMENT;
+            }
+            if (row.slot == other.slot && row.adapter != other.adapter) {
+                set_error("step rows of one sequence slot select different adapters");
+                return STATUS_INVALID_ARGUMENT;
+            }
+        }
+        if (!validate_tokens(row.tokens, row.n, (int32_t)hp.vocab)) return STATUS_INVALID_ARGUMENT;
+        if (row.n > (uint32_t)n_batch || total + row.n > (size_t)n_batch) {
+            set_error("the step's tokens exceed the context's physical batch (n_batch)");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        total += row.n;
+        if (row.n_top_logprobs > 0 && (!out_top_ids || !out_top_logprobs)) {
+            set_error("top logprobs requested but the output buffers are missing");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        if (row.n_top_logprobs > n_top_stride) {
+            set_error("a step row's n_top_logprobs exceeds the output stride");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        if (row.sample) {
+            if (row.request < 0) {
+                set_error("a sampling step row requires a request id");
+                return STATUS_INVALID_ARGUMENT;
+            }
+            if (row.v2) {
+                if (!validate_sampling_v2(*row.v2, (int32_t)hp.vocab)) return STATUS_INVALID_ARGUMENT;
+            } else {
+                retro_sampling_params sampling = row.v1;
+                sampling.max_new_tokens = 1;
+                if (!validate_sampling(sampling)) return STATUS_INVALID_ARGUMENT;
+            }
+            ++n_sample;
+        }
+        if (row.request >= 0) {
+            if (std::find(seen_requests.begin(), seen_requests.end(), row.request) != seen_requests.end()) {
+                set_error("a request id appears twice in one step");
+                return STATUS_INVALID_ARGUMENT;
+            }
+            seen_requests.push_back(row.request);
+        }
+    }
+    for (size_t r = 0; r < n_rows; ++r) {
+        if (rows[r].sample && rows[r].v2 && rows[r].v2->grammar) {
+            set_error("grammar-constrained sampling is not available in this backend");
+            return STATUS_RUNTIME;
+        }
+    }
+
+    // ---- KV reservation: all rows or none
+    kv->begin();
+    for (size_t r = 0; r < n_rows; ++r) {
+        const KvManager::Reserve res = kv->reserve(rows[r].slot, rows[r].pos0, (int32_t)rows[r].n);
+        if (res != KvManager::OK) {
+            kv->rollback();
+            if (res == KvManager::GAP) {
+                set_error("a step row starts past the end of its slot's resident sequence: positions must extend the slot without a gap");
+            } else {
+                set_error("the KV cache is full: no free block for the step's tokens (query the extent with the seq_pos entry point)");
+            }
+            return STATUS_RUNTIME;
+        }
+    }
+    kv->commit();
+
+    // ---- stage the plan
+    const size_t T = total, R = n_rows, S = n_sample;
+    std::vector<int32_t> & patches = kv->patches();
+    std::vector<int32_t> & copies = kv->copies();
+    std::vector<SampleDesc> descs(S);
+    std::vector<LogitEdit> edits;
+    size_t top_stride = 0;
+    bool any_v2 = false;
+    {
+        size_t s = 0;
+        for (size_t r = 0; r < R; ++r) {
+            const EffRow & row = rows[r];
+            if (!row.sample) continue;
+            RequestState & req = requests[row.request];
+            if (!req.seeded) {
+                req.seed = row.v2 ? row.v2->seed : row.v1.seed;
+                req.seeded = true;
+            }
+            SampleDesc & d = descs[s++];
+            std::memset(&d, 0, sizeof d);
+            d.seed = req.seed;
+            d.draw_lo = (uint32_t)req.draws;
+            d.draw_hi = (uint32_t)(req.draws >> 32);
+            d.n_top = std::min<uint32_t>(row.n_top_logprobs, (uint32_t)std::min<size_t>(n_top_stride, hp.vocab));
+            top_stride = std::max<size_t>(top_stride, d.n_top);
+            d.edit_begin = d.edit_end = (uint32_t)edits.size();
+            if (row.v2) {
+                const retro_sampling_params_v2 & p = *row.v2;
+                d.temperature = p.temperature;
+                d.top_p = p.top_p;
+                d.top_k = p.top_k;
+                d.min_p = p.min_p;
+                d.flags = 1u | (row.want_logprob ? 2u : 0u);
+                any_v2 = true;
+                // one merged edit per distinct id: summed bias, then the penalties of the window
+                std::map<int32_t, LogitEdit> merged;
+                for (uint32_t i = 0; i < p.n_logit_bias; ++i) {
+                    LogitEdit & e = merged[p.logit_bias_ids[i]];
+                    if (e.repeat == 0.f) e = LogitEdit{p.logit_bias_ids[i], 0.f, 1.f, 0.f};
+                    e.bias += p.logit_bias_values[i];
+                }
+                const bool any_penalty = p.repeat_penalty != 1.0f || p.frequency_penalty != 0.0f || p.presence_penalty != 0.0f;
+                if (any_penalty && !req.history.empty()) {
+                    const size_t window = p.penalty_window == 0 ? req.history.size() : std::min<size_t>(p.penalty_window, req.history.size());
+                    std::map<int32_t, int32_t> counts;
+                    for (size_t i = req.history.size() - window; i < req.history.size(); ++i) counts[req.history[i]]++;
+                    for (const auto & c : counts) {
+                        LogitEdit & e = merged[c.first];
+                        if (e.repeat == 0.f) e = LogitEdit{c.first, 0.f, 1.f, 0.f};
+                        e.repeat = p.repeat_penalty;
+                        e.subtract = (float)c.second * p.frequency_penalty + (float)(c.second > 0) * p.presence_penalty;
+                    }
+                }
+                for (const auto & e : merged) edits.push_back(e.second);
+                d.edit_end = (uint32_t)edits.size();
+            } else {
+                d.temperature = row.v1.temperature;
+                d.top_p = row.v1.top_p;
+                d.top_k = 0;
+                d.min_p = 0.f;
+                d.flags = 0;
+            }
+        }
+    }
+
+    size_t off_rows = 0;
+    size_t off_tokens = align_up(off_rows + R * sizeof(RowDesc), 16);
+    size_t off_patches = align_up(off_tokens + T * 4, 16);
+    size_t off_copies = align_up(off_patches + patches.size() * 4, 16);
+    size_t off_descs = align_up(off_copies + copies.size() * 4, 16);
+    size_t off_edits = align_up(off_descs + S * sizeof(SampleDesc), 16);
+    size_t stage_total = align_up(off_edits + edits.size() * sizeof(LogitEdit), 16);
+    if (stage_total > stage_bytes_) {
+        if (h_stage_) cudaFreeHost(h_stage_);
+        h_stage_ = nullptr;
+        stage_bytes_ = std::max(stage_total * 2, (size_t)1 << 16);
+        RB_CUDA(cudaMallocHost(&h_stage_, stage_bytes_));
+        d_stage_.ensure(stage_bytes_);
+    }
+    RowDesc * h_rows = reinterpret_cast<RowDesc *>(h_stage_ + off_rows);
+    int32_t * h_tokens = reinterpret_cast<int32_t *>(h_stage_ + off_tokens);
+    bool any_adapter = false;
+    {
+        size_t t = 0;
+        for (size_t r = 0; r < R; ++r) {
+            const EffRow & row = rows[r];
+            RowDesc & d = h_rows[r];
+            d.slot = row.slot;
+            d.n = (int32_t)row.n;
+            d.pos0 = row.pos0;
+            d.sample = row.sample ? 1 : 0;
+            d.adapter = -1;
+            if (row.adapter > 0) {
+                d.adapter = adapter_index_.at(row.adapter);
+                any_adapter = true;
+            }
+            d.pos_min = kv->slot(row.slot).pos_min;
+            d.pad0 = d.pad1 = 0;
+            std::memcpy(h_tokens + t, row.tokens, row.n * 4);
+            t += row.n;
+        }
+    }
+    if (!patches.empty()) std::memcpy(h_stage_ + off_patches, patches.data(), patches.size() * 4);
+    if (!copies.empty()) std::memcpy(h_stage_ + off_copies, copies.data(), copies.size() * 4);
+    if (S) std::memcpy(h_stage_ + off_descs, descs.data(), S * sizeof(SampleDesc));
+    if (!edits.empty()) std::memcpy(h_stage_ + off_edits, edits.data(), edits.size() * sizeof(LogitEdit));
+    const int n_patches = (int)(patches.size() / 2), n_copies = (int)(copies.size() / 2);
+    patches.clear();
+    copies.clear();
+
+    // result buffer: [SampleOut x S][top ids S x stride][top logprobs S x stride]
+    const size_t res_ids = align_up(S * sizeof(SampleOut), 16);
+    const size_t res_lps = align_up(res_ids + S * top_stride * 4, 16);
+    const size_t res_total = align_up(res_lps + S * top_stride * 4, 16) + 16;
+    if (res_total > result_bytes_) {
+        if (h_result_) cudaFreeHost(h_result_);
+        h_result_ = nullptr;
+        result_bytes_ = std::max(res_total * 2, (size_t)1 << 16);
+        RB_CUDA(cudaMallocHost(&h_result_, result_bytes_));
+        d_result_.ensure(result_bytes_);
+    }
+    if (S) {
+        logits.ensure(S * (size_t)hp.vocab);
+        hs_.ensure(S * (size_t)hp.d);
+        if (any_v2) logits_work_.ensure(S * (size_t)hp.vocab);
+    }
+    if (any_adapter) lora_tmp_.ensure(T * (size_t)std::max<uint32_t>(r_max_, 1));
+
+    // ---- device work
+    last_launches = 0;
+    RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
+    RB_CUDA(cudaEventRecord(ev_begin_, stream));
+    const RowDesc * d_rows = reinterpret_cast<const RowDesc *>(d_stage_.ptr + off_rows);
+    const int32_t * d_tokens = reinterpret_cast<const int32_t *>(d_stage_.ptr + off_tokens);
+    const KvLayout kvl = kv_layout();
+    if (n_patches) {
+        launch_block_table_patch(block_table_.ptr, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_patches), n_patches, stream);
+        ++last_launches;
+    }
+    if (n_copies) {
+        launch_kv_block_copy(kvl, (int)hp.n_layer, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_copies), n_copies, stream);
+        ++last_launches;
+    }
+    launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, maps, stream);
+    last_launches += 2;
+    cur_tok_adapter_ = maps.tok_adapter;
+    cur_any_adapter_ = any_adapter;
+
+    const int d = (int)hp.d, dq = (int)hp.dq(), dkv = (int)hp.dkv(), ldqkv = dq + 2 * dkv, ff = (int)hp.ff;
+    const int Ti = (int)T;
+    launch_embed(model->token_embd, d_tokens, Ti, x_.ptr, stream);
+    ++last_launches;
+    for (uint32_t l = 0; l < hp.n_layer; ++l) {
+        const LayerWeights & lw = model->layers[l];
+        const std::string p = "blk." + std::to_string(l) + ".";
+        launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, xn_.ptr, d, Ti, stream);
+        ++last_launches;
+        if (lw.wqkv.data) {
+            linear(lw.wqkv, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0);
+        } else {
+            linear(lw.wq, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0);
+            linear(lw.wk, xn_.ptr, d, Ti, qkv_.ptr + dq, ldqkv, lw.bqkv ? lw.bqkv + dq : nullptr, nullptr, 0);
+            linear(lw.wv, xn_.ptr, d, Ti, qkv_.ptr + dq + dkv, ldqkv, lw.bqkv ? lw.bqkv + dq + dkv : nullptr, nullptr, 0);
+        }
+        if (any_adapter) {
+            lora(p + "attn_q.weight", xn_.ptr, d, Ti, qkv_.ptr, ldqkv);
+            lora(p + "attn_k.weight", xn_.ptr, d, Ti, qkv_.ptr + dq, ldqkv);
+            lora(p + "attn_v.weight", xn_.ptr, d, Ti, qkv_.ptr + dq + dkv, ldqkv);
+        }
+        if (lw.q_norm) {
+            launch_rms_norm(qkv_.ptr, ldqkv, nullptr, lw.q_norm, dq, hp.eps, qkv_.ptr, ldqkv, Ti, stream);
+            launch_rms_norm(qkv_.ptr + dq, ldqkv, nullptr, lw.k_norm, dkv, hp.eps, qkv_.ptr + dq, ldqkv, Ti, stream);
+            last_launches += 2;
+        }
+        launch_rope_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox, model->inv_freq.ptr,
+                          maps.tok_pos, maps.tok_cell, kvl, (int)l, stream);
+        launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, stream);
+        last_launches += 2;
+        // x = x + Wo att
+        linear(lw.wo, att_.ptr, dq, Ti, x_.ptr, d, nullptr, x_.ptr, d);
+        if (any_adapter) lora(p + "attn_output.weight", att_.ptr, dq, Ti, x_.ptr, d);
+        launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, xn_.ptr, d, Ti, stream);
+        ++last_launches;
+        if (hp.n_expert == 0) {
+            if (lw.wgu.data) {
+                linear(lw.wgu, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0);
+            } else {
+                linear(lw.wgate, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0);
+                linear(lw.wup, xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff, nullptr, nullptr, 0);
+            }
+            if (any_adapter) {
+                lora(p + "ffn_gate.weight", xn_.ptr, d, Ti, gu_.ptr, 2 * ff);
+                lora(p + "ffn_up.weight", xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff);
+            }
+            launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, hff_.ptr, ff, stream);
+            ++last_launches;
+            linear(lw.wdown, hff_.ptr, ff, Ti, x_.ptr, d, nullptr, x_.ptr, d);
+            if (any_adapter) lora(p + "ffn_down.weight", hff_.ptr, ff, Ti, x_.ptr, d);
+        } else {
+            const int E = (int)hp.n_expert, K = (int)hp.n_expert_used, P = Ti * K;
+            linear(lw.router, xn_.ptr, d, Ti, router_logits_.ptr, E, nullptr, nullptr, 0);
+            launch_moe_route(router_logits_.ptr, E, K, Ti, moe_ids_.ptr, moe_w_.ptr, stream);
+            RB_CUDA(cudaMemcpyAsync(route_ids.ptr + (size_t)l * P, moe_ids_.ptr, (size_t)P * 4, cudaMemcpyDeviceToDevice, stream));
+            launch_moe_gemm_rows(lw.gate_exps, lw.gate_stride, moe_ids_.ptr, xn_.ptr, d, K, P, pair_gu_.ptr, 2 * ff, stream);
+            launch_moe_gemm_rows(lw.up_exps, lw.up_stride, moe_ids_.ptr, xn_.ptr, d, K, P, pair_gu_.ptr + ff, 2 * ff, stream);
+            launch_swiglu(pair_gu_.ptr, 2 * ff, ff, P, pair_h_.ptr, ff, stream);
+            launch_moe_gemm_rows(lw.down_exps, lw.down_stride, moe_ids_.ptr, pair_h_.ptr, ff, 1, P, pair_y_.ptr, d, stream);
+            launch_moe_combine(pair_y_.ptr, d, moe_ids_.ptr, moe_w_.ptr, K, d, Ti, x_.ptr, x_.ptr, stream);
+            last_launches += 6;
+        }
+    }
+    SampleOut * d_out = reinterpret_cast<SampleOut *>(d_result_.ptr);
+    int32_t * d_top_ids = reinterpret_cast<int32_t *>(d_result_.ptr + res_ids);
+    float * d_top_lps = reinterpret_cast<float *>(d_result_.ptr + res_lps);
+    if (S) {
+        launch_rms_norm(x_.ptr, d, maps.out_index, model->output_norm, d, hp.eps, hs_.ptr, d, (int)S, stream);
+        ++last_launches;
+        linear(model->output, hs_.ptr, d, (int)S, logits.ptr, (int)hp.vocab, model->output_bias, nullptr, 0);
+        if (any_v2) {
+            RB_CUDA(cudaMemcpyAsync(logits_work_.ptr, logits.ptr, S * (size_t)hp.vocab * 4, cudaMemcpyDeviceToDevice, stream));
+        }
+        launch_sample(logits.ptr, any_v2 ? logits_work_.ptr : nullptr, (int)hp.vocab, (int)S,
+                      reinterpret_cast<const SampleDesc *>(d_stage_.ptr + off_descs),
+                      reinterpret_cast<const LogitEdit *>(d_stage_.ptr + off_edits), d_out, d_top_ids, d_top_lps,
+                      (int)std::max<size_t>(top_stride, 1), stream);
+        ++last_launches;
+    }
+    RB_CUDA(cudaEventRecord(ev_end_, stream));
+    if (S) RB_CUDA(cudaMemcpyAsync(h_result_, d_result_.ptr, res_total - 16, cudaMemcpyDeviceToHost, stream));
+    const cudaError_t sync = cudaStreamSynchronize(stream);
+    if (sync != cudaSuccess) {
+        set_error(std::string("the decode failed on the device (") + cudaGetErrorString(sync) +
+                  "): the KV may hold a prefix of the submitted tokens (query it with the seq_pos entry point) - do not resubmit tokens "
+                  "that are already resident");
+        return STATUS_RUNTIME;
+    }
+    const cudaError_t launch_status = cudaGetLastError();
+    if (launch_status != cudaSuccess) {
+        set_error(std::string("a kernel of the step failed to launch: ") + cudaGetErrorString(launch_status));
+        return STATUS_RUNTIME;
+    }
+    cudaEventElapsedTime(&last_ms, ev_begin_, ev_end_);
+    last_T = T;
+    last_S = S;
+    last_R = R;
+
+    if (hp.n_expert && route_enabled) {
+        const size_t P = T * hp.n_expert_used;
+        std::vector<int32_t> ids((size_t)hp.n_layer * P);
+        RB_CUDA(cudaMemcpy(ids.data(), route_ids.ptr, ids.size() * 4, cudaMemcpyDeviceToHost));
+        for (uint32_t l = 0; l < hp.n_layer; ++l)
+            for (size_t i = 0; i < P; ++i) ++route_counts[l][ids[(size_t)l * P + i]];
+    }
+
+    // ---- outputs
+    const SampleOut * h_out = reinterpret_cast<const SampleOut *>(h_result_);
+    const int32_t * h_ids = reinterpret_cast<const int32_t *>(h_result_ + res_ids);
+    const float * h_lps = reinterpret_cast<const float *>(h_result_ + res_lps);
+    size_t s = 0;
+    for (size_t r = 0; r < R; ++r) {
+        const EffRow & row = rows[r];
+        OutRow & o = out_rows[r];
+        o = OutRow{};
+        if (!row.sample) continue;
+        const SampleOut & so = h_out[s];
+        o.token = so.token;
+        o.logprob = so.logprob;
+        o.sampled = 1;
+        o.forced = 0;
+        o.n_top = so.n_top;
+        o.sampled_logprob = row.v2 && row.want_logprob ? so.sampled_logprob : 0.f;
+        for (uint32_t j = 0; j < so.n_top; ++j) {
+            out_top_ids[r * n_top_stride + j] = h_ids[s * top_stride + j];
+            out_top_logprobs[r * n_top_stride + j] = h_lps[s * top_stride + j];
+        }
+        RequestState & req = requests[row.request];
+        ++req.draws;
+        if (row.v2) req.history.push_back(so.token);
+        ++s;
+    }
+    return STATUS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Sequence memory
+
+int Engine::seq_rm(int32_t slot, int32_t p0, int32_t p1) {
+    if (slot < 0 || slot >= (int32_t)config.n_seq_max) {
+        set_error("slot is outside the context's sequence range");
+        return STATUS_RUNTIME;
+    }
+    if (!kv->seq_rm(slot, p0, p1)) {
+        set_error("the memory cannot remove that partial range; remove the whole sequence instead");
+        return STATUS_RUNTIME;
+    }
+    return STATUS_OK;
+}
+
+int Engine::seq_cp(int32_t src, int32_t dst, int32_t p0, int32_t p1) {
+    const int32_t n = (int32_t)config.n_seq_max;
+    if (src < 0 || src >= n || dst < 0 || dst >= n) {
+        set_error("seq_cp slots are outside the context's sequence range");
+        return STATUS_RUNTIME;
+    }
+    if (!config.kv_unified && !(p0 <= 0 && p1 < 0)) {
+        set_error("a partitioned KV pool only supports whole-sequence copies");
+        return STATUS_RUNTIME;
+    }
+    if (kv->seq_cp(src, dst, p0, p1) == KvManager::DST_NOT_EMPTY) {
+        set_error("the destination slot of a seq_cp must be empty: remove it first with seq_rm");
+        return STATUS_RUNTIME;
+    }
+    flush_kv_updates();
+    return STATUS_OK;
+}
+
+int Engine::seq_pos(int32_t slot, int32_t * pmin, int32_t * pmax) {
+    if (!pmin || !pmax) {
+        set_error("the position outputs are required");
+        return STATUS_RUNTIME;
+    }
+    if (slot < 0 || slot >= (int32_t)config.n_seq_max) {
+        set_error("slot is outside the context's sequence range");
+        return STATUS_RUNTIME;
+    }
+    const KvSlot & s = kv->slot(slot);
+    *pmin = s.empty() ? -1 : s.pos_min;
+    *pmax = s.empty() ? -1 : s.pos_max;
+    return STATUS_OK;
+}
+
+namespace {
+struct SnapshotHeader {
+    char magic[8];
+    uint32_t version;
+    uint32_t n_layer, n_head_kv, head_dim;
+    int32_t pos_min, pos_max;
+    uint64_t payload_bytes;
+    uint64_t checksum;
+};
+const char kSnapshotMagic[8] = {'R', 'B', '2', 'K', 'V', 'S', 'N', 'P'};
+} // namespace
+
+int Engine::seq_save(int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_buffer, size_t * out_n) {
+    if (!out_n) {
+        set_error("out_n_bytes is required");
+        return STATUS_RUNTIME;
+    }
+    if (flags & ~RETRO_STATE_SEQ_FLAGS_PARTIAL_ONLY) {
+        set_error("only host snapshots (flags 0 or PARTIAL_ONLY) are supported");
+        return STATUS_RUNTIME;
+    }
+    if (slot < 0 || slot >= (int32_t)config.n_seq_max) {
+        set_error("slot is outside the context's sequence range");
+        return STATUS_RUNTIME;
+    }
+    const HParams & hp = model->hp;
+    const KvSlot & s = kv->slot(slot);
+    // A dense attention model has no partial (recurrent) state: a PARTIAL_ONLY snapshot is a bare header.
+    const bool partial = (flags & RETRO_STATE_SEQ_FLAGS_PARTIAL_ONLY) != 0;
+    const size_t n_pos = (s.empty() || partial) ? 0 : (size_t)(s.pos_max - s.pos_min + 1);
+    const size_t payload = n_pos * hp.n_layer * 2 * hp.dkv() * sizeof(__half);
+    const size_t required = sizeof(SnapshotHeader) + payload;
+    *out_n = required;
+    if (!buffer) return STATUS_OK;
+    if (n_buffer < required) {
+        set_error("the save buffer is too small for this sequence's state");
+        return STATUS_BUFFER_TOO_SMALL;
+    }
+    SnapshotHeader h{};
+    std::memcpy(h.magic, kSnapshotMagic, 8);
+    h.version = partial ? 2 : 1;
+    h.n_layer = hp.n_layer;
+    h.n_head_kv = hp.n_head_kv;
+    h.head_dim = hp.head_dim;
+    h.pos_min = n_pos ? s.pos_min : -1;
+    h.pos_max = n_pos ? s.pos_max : -1;
+    h.payload_bytes = payload;
+    if (n_pos) {
+        DeviceBuffer<__half> dense;
+        dense.ensure(payload / sizeof(__half));
+        launch_kv_snapshot(kv_layout(), (int)hp.n_layer, block_table_.ptr + (size_t)slot * kv->max_blocks(), s.pos_min, (int)n_pos, dense.ptr, false,
+                           stream);
+        RB_CUDA(cudaMemcpyAsync(buffer + sizeof h, dense.ptr, payload, cudaMemcpyDeviceToHost, stream));
+        RB_CUDA(cudaStreamSynchronize(stream));
+    }
+    h.checksum = fnv1a(buffer + sizeof h, payload);
+    std::memcpy(buffer, &h, sizeof h);
+    return STATUS_OK;
+}
+
+int Engine::seq_load(int32_t slot, uint32_t flags, const uint8_t * buffer, size_t n_bytes, size_t * out_read) {
+    if (!out_read) {
+        set_error("out_n_read is required");
+        return STATUS_RUNTIME;
+    }
+    if (flags & ~RETRO_STATE_SEQ_FLAGS_PARTIAL_ONLY) {
+        set_error("only host snapshots (flags 0 or PARTIAL_ONLY) are supported");
+        return STATUS_RUNTIME;
+    }
+    if (slot < 0 || slot >= (int32_t)config.n_seq_max) {
+        set_error("slot is outside the context's sequence range");
+        return STATUS_RUNTIME;
+    }
+    if (!buffer || n_bytes == 0) {
+        set_error("a snapshot buffer is required");
+        return STATUS_RUNTIME;
+    }
+    const HParams & hp = model->hp;
+    const char * refused = "the snapshot was refused (wrong size, flags or corrupted data)";
+    SnapshotHeader h{};
+    if (n_bytes < sizeof h) { set_error(refused); return STATUS_RUNTIME; }
+    std::memcpy(&h, buffer, sizeof h);
+    const bool partial = (flags & RETRO_STATE_SEQ_FLAGS_PARTIAL_ONLY) != 0;
+    if (std::memcmp(h.magic, kSnapshotMagic, 8) != 0 || h.version != (partial ? 2u : 1u) || h.n_layer != hp.n_layer ||
+        h.n_head_kv != hp.n_head_kv || h.head_dim != hp.head_dim || n_bytes < sizeof h + h.payload_bytes) {
+        set_error(refused);
+        return STATUS_RUNTIME;
+    }
+    const size_t n_pos = h.pos_min < 0 ? 0 : (size_t)(h.pos_max - h.pos_min + 1);
+    if (h.payload_bytes != n_pos * hp.n_layer * 2 * hp.dkv() * sizeof(__half) || fnv1a(buffer + sizeof h, h.payload_bytes) != h.checksum ||
+        (n_pos && (h.pos_min < 0 || (uint32_t)h.pos_max >= n_ctx_seq))) {
+        set_error(refused);
+        return STATUS_RUNTIME;
+    }
+    if (n_pos) {
+        if (!kv->slot(slot).empty()) kv->seq_rm(slot, -1, -1);
+        kv->begin();
+        if (kv->reserve(slot, h.pos_min, (int32_t)n_pos) != KvManager::OK) {
+            kv->rollback();
+            set_error("the KV cache is full: no free block for the snapshot");
+            return STATUS_RUNTIME;
+        }
+        kv->commit();
+        flush_kv_updates();
+        DeviceBuffer<__half> dense;
+        dense.ensure(h.payload_bytes / sizeof(__half));
+        RB_CUDA(cudaMemcpyAsync(dense.ptr, buffer + sizeof h, h.payload_bytes, cudaMemcpyHostToDevice, stream));
+        launch_kv_snapshot(kv_layout(), (int)hp.n_layer, block_table_.ptr + (size_t)slot * kv->max_blocks(), h.pos_min, (int)n_pos, dense.ptr, true,
+                           stream);
+        RB_CUDA(cudaStreamSynchronize(stream));
+    }
+    *out_read = sizeof h + h.payload_bytes;
+    return STATUS_OK;
+}
+
+int Engine::memory(retro_engine_memory_info * out) {
+    if (!out) {
+        set_error("out is required");
+        return STATUS_RUNTIME;
+    }
+    out->struct_size = sizeof(retro_engine_memory_info);
+    out->n_slots = config.n_seq_max;
+    out->cells_total = config.n_ctx;
+    out->cells_used = kv->cells_used();
+    out->kv_bytes = (kcache_.count + vcache_.count) * sizeof(__half);
+    out->recurrent_bytes = 0;
+    return STATUS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-row adapters
+
+int Engine::adapter_load(const char * path, float scale, int32_t * out_id) {
+    if (!path || !*path || !out_id) {
+        set_error("adapter_path and out_id are required");
+        return STATUS_RUNTIME;
+    }
+    if (!std::isfinite(scale)) {
+        set_error("adapter scale must be finite");
+        return STATUS_RUNTIME;
+    }
+    GgufFile file(path);
+    if (file.str("general.type") != "adapter" || file.str("adapter.type") != "lora") {
+        set_error("the file is not a LoRA adapter GGUF (general.type=adapter, adapter.type=lora)");
+        return STATUS_RUNTIME;
+    }
+    const float alpha = file.f32("adapter.lora.alpha", 0.f);
+    Adapter ad;
+    const std::string suffix = ".lora_a";
+    for (const GgufTensor & A : file.tensors()) {
+        if (A.name.size() <= suffix.size() || A.name.compare(A.name.size() - suffix.size(), suffix.size(), suffix) != 0) continue;
+        const std::string target = A.name.substr(0, A.name.size() - suffix.size());
+        if (target == "token_embd.weight" || target.find("_exps") != std::string::npos) {
+            set_error("per-row adapters refuse token-embedding and expert targets: " + target);
+            return STATUS_RUNTIME;
+        }
+        const GgufTensor * B = file.find(target + ".lora_b");
+        if (!B || A.ne.size() != 2 || B->ne.size() != 2 || A.ne[1] != B->ne[0] || (A.type != GGML_F32 && A.type != GGML_F16) ||
+            (B->type != GGML_F32 && B->type != GGML_F16)) {
+            set_error("adapter tensor pair of " + target + " is malformed");
+            return STATUS_RUNTIME;
+        }
+        const uint32_t r = (uint32_t)A.ne[1];
+        if (ad.rank && ad.rank != r) {
+            set_error("adapter tensors disagree on their rank");
+            return STATUS_RUNTIME;
+        }
+        ad.rank = r;
+        auto to_f32 = [](const GgufTensor & t) {
+            const size_t n = t.ne[0] * t.ne[1];
+            std::vector<float> out(n);
+            if (t.type == GGML_F32) {
+                std::memcpy(out.data(), t.data, n * 4);
+            } else {
+                for (size_t i = 0; i < n; ++i) {
+                    uint16_t h;
+                    std::memcpy(&h, t.data + 2 * i, 2);
+                    out[i] = half_to_float(h);
+                }
+            }
+            return out;
+        };
+        ad.unpadded_bytes += (A.ne[0] * A.ne[1] + B->ne[0] * B->ne[1]) * 4;
+        ad.ab[target] = {to_f32(A), to_f32(*B)};
+    }
+    if (ad.rank == 0) {
+        set_error("the adapter holds no lora tensors");
+        return STATUS_RUNTIME;
+    }
+    ad.scale = (alpha != 0.f ? alpha / (float)ad.rank : 1.0f) * scale;
+    const int32_t id = next_adapter_id_++;
+    adapters_[id] = std::move(ad);
+    restack_adapters();
+    *out_id = id;
+    return STATUS_OK;
+}
+
+int Engine::adapter_unload(int32_t id) {
+    if (adapters_.erase(id) == 0) {
+        set_error("adapter " + std::to_string(id) + " is not a loaded per-row adapter");
+        return STATUS_RUNTIME;
+    }
+    restack_adapters();
+    return STATUS_OK;
+}
+
+// Every load restacks all adapters, zero-padded to the largest rank, in F32
+// (retro_lora_train.h:1298-1306).
+void Engine::restack_adapters() {
+    RB_CUDA(cudaStreamSynchronize(stream));
+    adapter_index_.clear();
+    lora_targets_.clear();
+    stacked_bytes_ = 0;
+    r_max_ = 0;
+    const size_t n = adapters_.size();
+    if (n == 0) return;
+    std::vector<float> scales;
+    std::map<std::string, std::pair<uint32_t, uint32_t>> shapes;   // target -> (n_in, n_out)
+    for (const auto & kvp : adapters_) {
+        adapter_index_[kvp.first] = (int32_t)scales.size();
+        scales.push_back(kvp.second.scale);
+        r_max_ = std::max(r_max_, kvp.second.rank);
+        for (const auto & t : kvp.second.ab) {
+            const uint32_t r = kvp.second.rank;
+            shapes[t.first] = {(uint32_t)(t.second.first.size() / r), (uint32_t)(t.second.second.size() / r)};
+        }
+    }
+    lora_scales_.ensure(n);
+    RB_CUDA(cudaMemcpy(lora_scales_.ptr, scales.data(), n * 4, cudaMemcpyHostToDevice));
+    for (const auto & sh : shapes) {
+        auto target = std::make_unique<LoraTarget>();
+        target->n_in = sh.second.first;
+        target->n_out = sh.second.second;
+        target->present = true;
+        std::vector<float> a(n * r_max_ * target->n_in, 0.f), b(n * (size_t)target->n_out * r_max_, 0.f);
+        size_t idx = 0;
+        for (const auto & kvp : adapters_) {
+            auto it = kvp.second.ab.find(sh.first);
+            if (it != kvp.second.ab.end()) {
+                const uint32_t r = kvp.second.rank;
+                // A: r rows of n_in; B: n_out rows of r
+                std::memcpy(&a[idx * r_max_ * target->n_in], it->second.first.data(), (size_t)r * target->n_in * 4);
+                for (uint32_t o = 0; o < target->n_out; ++o)
+                    std::memcpy(&b[(idx * target->n_out + o) * r_max_], &it->second.second[(size_t)o * r], r * 4);
+            }
+            ++idx;
+        }
+        target->a.ensure(a.size());
+        target->b.ensure(b.size());
+        RB_CUDA(cudaMemcpy(target->a.ptr, a.data(), a.size() * 4, cudaMemcpyHostToDevice));
+        RB_CUDA(cudaMemcpy(target->b.ptr, b.data(), b.size() * 4, cudaMemcpyHostToDevice));
+        stacked_bytes_ += (a.size() + b.size()) * 4;
+        lora_targets_[sh.first] = std::move(target);
+    }
+}
+
+void Engine::adapter_info(retro_adapter_rows_info * out) {
+    *out = retro_adapter_rows_info{};
+    out->struct_size = sizeof(retro_adapter_rows_info);
+    out->n_adapters = (uint32_t)adapters_.size();
+    out->max_rank = r_max_;
+    out->stacked_bytes = stacked_bytes_;
+    uint64_t unpadded = 0;
+    for (const auto & a : adapters_) unpadded += a.second.unpadded_bytes;
+    out->unpadded_bytes = unpadded;
+}
+
+} // namespace rb200

@@ -1,0 +1,201 @@
+// Engine state behind the `retro_engine` handle: model weights in device memory, the paged KV
+// cache with its block tables, per-request sampler state, per-row adapters and the step executor.
+#pragma once
+
+#include "common.hpp"
+#include "gguf.hpp"
+#include "kernels.cuh"
+#include "kv.hpp"
+
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/retro_b200.h"
+
+namespace rb200 {
+
+constexpr uint32_t kMaxSeq = 1024;        // sequence slots this backend accepts (the reference's fork caps at 256)
+constexpr uint32_t kBlockTokens = 16;     // KV cells per block
+
+template <class T> struct DeviceBuffer {
+    T * ptr = nullptr;
+    size_t count = 0;
+    DeviceBuffer() = default;
+    DeviceBuffer(const DeviceBuffer &) = delete;
+    DeviceBuffer & operator=(const DeviceBuffer &) = delete;
+    ~DeviceBuffer() { if (ptr) cudaFree(ptr); }
+    void ensure(size_t n) {
+        if (n <= count) return;
+        if (ptr) { cudaFree(ptr); ptr = nullptr; count = 0; }
+        RB_CUDA(cudaMalloc(&ptr, n * sizeof(T)));
+        count = n;
+    }
+};
+
+struct HParams {
+    std::string arch;
+    uint32_t n_layer = 0, d = 0, n_head = 0, n_head_kv = 0, head_dim = 0, ff = 0, vocab = 0;
+    uint32_t n_expert = 0, n_expert_used = 0, n_rot = 0;
+    float eps = 1e-5f, rope_base = 10000.f;
+    bool neox = false;
+    uint32_t dq() const { return n_head * head_dim; }
+    uint32_t dkv() const { return n_head_kv * head_dim; }
+};
+
+struct LayerWeights {
+    const float * attn_norm = nullptr;
+    WeightView wqkv;            // fused when the three projections share a storage type
+    WeightView wq, wk, wv;      // otherwise
+    const float * bqkv = nullptr;
+    const float * q_norm = nullptr;
+    const float * k_norm = nullptr;
+    WeightView wo;
+    const float * ffn_norm = nullptr;
+    WeightView wgu;             // fused gate|up
+    WeightView wgate, wup;
+    WeightView wdown;
+    // MoE
+    WeightView router;          // F32 [n_expert][d]
+    WeightView gate_exps, up_exps, down_exps;   // per-expert views (n_out = rows of one expert)
+    uint64_t gate_stride = 0, up_stride = 0, down_stride = 0;
+};
+
+struct Model {
+    HParams hp;
+    WeightView token_embd;
+    std::vector<LayerWeights> layers;
+    const float * output_norm = nullptr;
+    WeightView output;
+    const float * output_bias = nullptr;
+    DeviceBuffer<float> inv_freq;
+    std::vector<void *> allocations;
+    uint64_t weight_bytes = 0;
+    std::vector<std::string> vocab_tokens;
+    std::vector<int32_t> vocab_types;
+    int32_t eos = 2, bos = 1;
+    bool add_bos = true;
+    ~Model() { for (void * p : allocations) cudaFree(p); }
+};
+
+struct Adapter {
+    float scale = 1.f;
+    uint32_t rank = 0;
+    // target weight name -> (A [r][in], B [out][r]) in F32
+    std::map<std::string, std::pair<std::vector<float>, std::vector<float>>> ab;
+    uint64_t unpadded_bytes = 0;
+};
+
+struct LoraTarget {
+    DeviceBuffer<float> a;   // [n_adapters][r_max][n_in]
+    DeviceBuffer<float> b;   // [n_adapters][n_out][r_max]
+    uint32_t n_in = 0, n_out = 0;
+    bool present = false;
+};
+
+struct RequestState {
+    bool seeded = false;
+    uint32_t seed = 0;
+    uint64_t draws = 0;
+    std::vector<int32_t> history;
+};
+
+// A step row normalised from either ABI version.
+struct EffRow {
+    uint32_t struct_size;
+    int32_t request, slot;
+    const int32_t * tokens;
+    uint32_t n;
+    int32_t pos0;
+    bool sample;
+    retro_sampling_params v1;
+    const retro_sampling_params_v2 * v2;
+    uint32_t n_top_logprobs;
+    bool want_logprob;
+    int32_t adapter;
+};
+
+struct OutRow {
+    int32_t token = 0;
+    float logprob = 0.f;
+    uint32_t n_top = 0;
+    uint8_t forced = 0, sampled = 0;
+    float sampled_logprob = 0.f;
+};
+
+class Engine {
+public:
+    Engine(const std::string & path, const retro_engine_config & config);
+    ~Engine();
+
+    int step(const EffRow * rows, size_t n_rows, OutRow * out, int32_t * top_ids, float * top_lps, size_t stride);
+    int seq_rm(int32_t slot, int32_t p0, int32_t p1);
+    int seq_cp(int32_t src, int32_t dst, int32_t p0, int32_t p1);
+    int seq_pos(int32_t slot, int32_t * pmin, int32_t * pmax);
+    int seq_save(int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_buffer, size_t * out_n);
+    int seq_load(int32_t slot, uint32_t flags, const uint8_t * buffer, size_t n_bytes, size_t * out_read);
+    int memory(retro_engine_memory_info * out);
+    int adapter_load(const char * path, float scale, int32_t * out_id);
+    int adapter_unload(int32_t id);
+    void adapter_info(retro_adapter_rows_info * out);
+
+    retro_engine_config config{};
+    std::string model_path;
+    uint64_t fingerprint = 0;
+    uint64_t weights_version = 0;
+    uint32_t n_ctx_seq = 0;
+    std::unique_ptr<Model> model;
+    std::unique_ptr<KvManager> kv;
+    std::unordered_map<int32_t, RequestState> requests;
+
+    // inspection state of the last step
+    size_t last_T = 0, last_S = 0, last_R = 0;
+    float last_ms = 0.f;
+    uint64_t last_launches = 0;
+    uint64_t graphs_reused = 0;
+    bool route_enabled = false;
+    std::vector<std::vector<uint32_t>> route_counts;   // [layer][expert]
+
+    // device state exposed to the inspection entry points
+    PackMaps maps{};
+    DeviceBuffer<float> logits;
+    DeviceBuffer<int32_t> route_ids;     // [layer][T][k]
+    cudaStream_t stream = nullptr;
+    const int32_t * kv_block_table_device() const { return block_table_.ptr; }
+
+private:
+    void load_model(const std::string & path);
+    void restack_adapters();
+    void linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr);
+    void lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy);
+    void flush_kv_updates();
+    KvLayout kv_layout() const;
+
+    DeviceBuffer<__half> kcache_, vcache_;
+    uint64_t kv_layer_stride_ = 0;
+    DeviceBuffer<int32_t> block_table_;
+    DeviceBuffer<int32_t> maps_store_;
+    DeviceBuffer<uint8_t> d_stage_;
+    uint8_t * h_stage_ = nullptr;
+    size_t stage_bytes_ = 0;
+    DeviceBuffer<uint8_t> d_result_;
+    uint8_t * h_result_ = nullptr;
+    size_t result_bytes_ = 0;
+    DeviceBuffer<float> x_, xn_, qkv_, att_, gu_, hff_, hs_, router_logits_, moe_w_, pair_gu_, pair_h_, pair_y_, lora_tmp_, logits_work_;
+    DeviceBuffer<int32_t> moe_ids_, d_aux_;
+    cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
+
+    std::map<int32_t, Adapter> adapters_;
+    std::map<int32_t, int32_t> adapter_index_;   // id -> stack index
+    int32_t next_adapter_id_ = 1;
+    uint32_t r_max_ = 0;
+    std::map<std::string, std::unique_ptr<LoraTarget>> lora_targets_;
+    DeviceBuffer<float> lora_scales_;
+    uint64_t stacked_bytes_ = 0;
+    const int32_t * cur_tok_adapter_ = nullptr;
+    bool cur_any_adapter_ = false;
+};
+
+} // namespace rb200

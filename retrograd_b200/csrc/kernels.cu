@@ -1,0 +1,627 @@
+// Reference-grade CUDA kernels of the decode step: packing maps, block-table resolution,
+// embedding gather, RMSNorm, dequant-fused row GEMM, RoPE + paged KV store, paged attention,
+// SwiGLU, MoE routing, per-row LoRA. These are the simple, shape-agnostic implementations every
+// tuned kernel is checked against on the device; the tuned streaming kernels live in their own
+// files and take over for the shapes they cover.
+
+#include "kernels.cuh"
+#include "blocks.hpp"
+
+#include <cfloat>
+#include <type_traits>
+
+namespace rb200 {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+__device__ __forceinline__ float e8m0_half_dev(uint8_t x) {
+    const uint32_t bits = x == 0 ? 0x00200000u : x == 1 ? 0x00400000u : ((uint32_t)x - 1) << 23;
+    return __uint_as_float(bits);
+}
+
+__constant__ float c_fp4_doubled[16] = {0.f, 1.f, 2.f, 3.f, 4.f, 6.f, 8.f, 12.f, 0.f, -1.f, -2.f, -3.f, -4.f, -6.f, -8.f, -12.f};
+
+// Decodes 8 consecutive elements starting at k (k % 8 == 0) of a stored row.
+template <uint32_t TYPE>
+__device__ __forceinline__ void decode8(const uint8_t * __restrict__ row, uint32_t k, float (&w)[8]) {
+    if constexpr (TYPE == GGML_F32) {
+        const float4 a = *reinterpret_cast<const float4 *>(row + (size_t)k * 4);
+        const float4 b = *reinterpret_cast<const float4 *>(row + (size_t)k * 4 + 16);
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    } else if constexpr (TYPE == GGML_F16) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(row + (size_t)k * 2);
+        const __half2 * h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            w[2 * i] = f.x;
+            w[2 * i + 1] = f.y;
+        }
+    } else if constexpr (TYPE == GGML_BF16) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(row + (size_t)k * 2);
+        const uint16_t * h = reinterpret_cast<const uint16_t *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = __uint_as_float((uint32_t)h[i] << 16);
+    } else if constexpr (TYPE == GGML_Q8_0) {
+        const uint8_t * b = row + (size_t)(k >> 5) * 34;
+        const float d = half_bits_to_float((uint16_t)(b[0] | (b[1] << 8)));
+        const uint8_t * q = b + 2 + (k & 31);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = d * (float)(int8_t)q[i];
+    } else if constexpr (TYPE == GGML_Q4_K) {
+        const uint8_t * b = row + (size_t)(k >> 8) * 144;
+        const uint32_t in = k & 255;
+        const uint32_t grp = in >> 6, hi = (in >> 5) & 1, l = in & 31;
+        const float d = half_bits_to_float(*reinterpret_cast<const uint16_t *>(b));
+        const float dmin = half_bits_to_float(*reinterpret_cast<const uint16_t *>(b + 2));
+        const uint8_t * s = b + 4;
+        const int j = 2 * grp + hi;
+        uint32_t sc, mn;
+        if (j < 4) {
+            sc = s[j] & 63;
+            mn = s[j + 4] & 63;
+        } else {
+            sc = (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4);
+            mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+        }
+        const float dl = d * (float)sc, ml = dmin * (float)mn;
+        const uint8_t * q = b + 16 + grp * 32 + l;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = dl * (float)((q[i] >> (4 * hi)) & 0xF) - ml;
+    } else if constexpr (TYPE == GGML_MXFP4) {
+        const uint8_t * b = row + (size_t)(k >> 5) * 17;
+        const uint32_t in = k & 31, hi = in >> 4, l = in & 15;
+        const float d = e8m0_half_dev(b[0]);
+        const uint8_t * q = b + 1 + l;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = d * c_fp4_doubled[(q[i] >> (4 * hi)) & 0xF];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Packing: step plan -> batch maps, with block tables resolved to physical KV cells.
+
+__global__ void pack_scan_kernel(const RowDesc * __restrict__ rows, int n_rows, int32_t * __restrict__ cu, int32_t * __restrict__ out_rank) {
+    __shared__ int32_t warp_tok[32], warp_out[32];
+    __shared__ int32_t carry_tok, carry_out;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (tid == 0) { carry_tok = 0; carry_out = 0; }
+    __syncthreads();
+    for (int base = 0; base < n_rows; base += blockDim.x) {
+        const int r = base + tid;
+        const int32_t n = r < n_rows ? rows[r].n : 0;
+        const int32_t s = r < n_rows ? (rows[r].sample != 0) : 0;
+        int32_t in = n, is = s;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int32_t a = __shfl_up_sync(0xffffffffu, in, o);
+            const int32_t b = __shfl_up_sync(0xffffffffu, is, o);
+            if (lane >= o) { in += a; is += b; }
+        }
+        if (lane == 31) { warp_tok[wid] = in; warp_out[wid] = is; }
+        __syncthreads();
+        if (wid == 0) {
+            int32_t a = warp_tok[lane], b = warp_out[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int32_t ua = __shfl_up_sync(0xffffffffu, a, o);
+                const int32_t ub = __shfl_up_sync(0xffffffffu, b, o);
+                if (lane >= o) { a += ua; b += ub; }
+            }
+            warp_tok[lane] = a;
+            warp_out[lane] = b;
+        }
+        __syncthreads();
+        const int32_t pre_tok = carry_tok + (wid ? warp_tok[wid - 1] : 0);
+        const int32_t pre_out = carry_out + (wid ? warp_out[wid - 1] : 0);
+        if (r < n_rows) {
+            cu[r] = pre_tok + in - n;
+            out_rank[r] = pre_out + is - s;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            carry_tok += warp_tok[31];
+            carry_out += warp_out[31];
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        cu[n_rows] = carry_tok;
+        out_rank[n_rows] = carry_out;
+    }
+}
+
+__global__ void pack_fill_kernel(const RowDesc * __restrict__ rows, int n_rows, int n_tokens, const int32_t * __restrict__ block_table,
+                                 int max_blocks, int block_tokens, PackMaps maps) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens) return;
+    int lo = 0, hi = n_rows - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (maps.cu_rows[mid] <= i) lo = mid; else hi = mid - 1;
+    }
+    const RowDesc row = rows[lo];
+    const int j = i - maps.cu_rows[lo];
+    const int pos = row.pos0 + j;
+    maps.tok_slot[i] = row.slot;
+    maps.tok_pos[i] = pos;
+    maps.tok_row[i] = lo;
+    maps.tok_adapter[i] = row.adapter;
+    maps.tok_pos_min[i] = row.pos_min;
+    const int blk = block_table[(size_t)row.slot * max_blocks + pos / block_tokens];
+    maps.tok_cell[i] = blk * block_tokens + pos % block_tokens;
+    if (row.sample && j == row.n - 1) maps.out_index[maps.out_rank[lo]] = i;
+}
+
+__global__ void block_table_patch_kernel(int32_t * __restrict__ table, const int32_t * __restrict__ patches, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) table[patches[2 * i]] = patches[2 * i + 1];
+}
+
+// Copies whole KV blocks (all layers, K and V) for copy-on-write of a shared boundary block.
+__global__ void kv_block_copy_kernel(KvLayout kv, int n_layer, const int32_t * __restrict__ pairs) {
+    const int pair = blockIdx.x, layer = blockIdx.y;
+    const int32_t src = pairs[2 * pair], dst = pairs[2 * pair + 1];
+    const size_t block_elems = (size_t)kv.n_head_kv * kv.block_tokens * kv.head_dim;
+    const uint4 * ks = reinterpret_cast<const uint4 *>(kv.k + layer * kv.layer_stride + src * block_elems);
+    uint4 * kd = reinterpret_cast<uint4 *>(kv.k + layer * kv.layer_stride + dst * block_elems);
+    const uint4 * vs = reinterpret_cast<const uint4 *>(kv.v + layer * kv.layer_stride + src * block_elems);
+    uint4 * vd = reinterpret_cast<uint4 *>(kv.v + layer * kv.layer_stride + dst * block_elems);
+    const size_t n16 = block_elems * 2 / 16;
+    for (size_t i = threadIdx.x; i < n16; i += blockDim.x) {
+        kd[i] = ks[i];
+        vd[i] = vs[i];
+    }
+    (void)n_layer;
+}
+
+// Moves the cells of one slot between the paged cache and a dense [layer][K|V][pos][head][dim]
+// buffer (sequence snapshots). grid = (positions, layers * 2).
+__global__ void kv_snapshot_kernel(KvLayout kv, const int32_t * __restrict__ table, int pos_first, __half * __restrict__ dense, int n_pos,
+                                   int to_cache) {
+    const int p = blockIdx.x, layer = blockIdx.y >> 1, is_v = blockIdx.y & 1;
+    const int pos = pos_first + p;
+    const int blk = table[pos / kv.block_tokens], off = pos % kv.block_tokens;
+    __half * cache = (is_v ? kv.v : kv.k) + layer * kv.layer_stride;
+    const int row = kv.n_head_kv * kv.head_dim;
+    __half * d = dense + ((size_t)blockIdx.y * n_pos + p) * row;
+    for (int idx = threadIdx.x; idx < row; idx += blockDim.x) {
+        const int h = idx / kv.head_dim, i = idx % kv.head_dim;
+        const size_t c = (((size_t)blk * kv.n_head_kv + h) * kv.block_tokens + off) * kv.head_dim + i;
+        if (to_cache) cache[c] = d[idx]; else d[idx] = cache[c];
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+
+template <uint32_t TYPE>
+__global__ void embed_kernel(WeightView e, const int32_t * __restrict__ tokens, float * __restrict__ x) {
+    const int t = blockIdx.x;
+    const uint8_t * row = e.data + (size_t)tokens[t] * e.row_bytes;
+    for (uint32_t k = threadIdx.x * 8; k < e.n_in; k += blockDim.x * 8) {
+        float w[8];
+        decode8<TYPE>(row, k, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[(size_t)t * e.n_in + k + i] = w[i];
+    }
+}
+
+__global__ void rms_norm_kernel(const float * __restrict__ x, int ldx, const int32_t * __restrict__ gather, const float * __restrict__ w, int n,
+                                float eps, float * __restrict__ y, int ldy) {
+    __shared__ float partial[32];
+    const int t = blockIdx.x;
+    const float * xr = x + (size_t)(gather ? gather[t] : t) * ldx;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) partial[0] = v;
+    }
+    __syncthreads();
+    const float scale = 1.0f / sqrtf(partial[0] / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) y[(size_t)t * ldy + i] = xr[i] * scale * w[i];
+}
+
+// One warp per output row, eight tokens per pass.
+template <uint32_t TYPE>
+__global__ void gemm_rows_kernel(WeightView w, const float * __restrict__ x, int ldx, int n_tokens, float * __restrict__ y, int ldy,
+                                 const float * __restrict__ bias, const float * __restrict__ residual, int ldr) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (o >= w.n_out) return;
+    const uint8_t * row = w.data + (size_t)o * w.row_bytes;
+    for (int t0 = 0; t0 < n_tokens; t0 += 8) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (uint32_t k = lane * 8; k < w.n_in; k += 256) {
+            float wv[8];
+            decode8<TYPE>(row, k, wv);
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) {
+                if (t0 + tt < n_tokens) {
+                    const float4 a = *reinterpret_cast<const float4 *>(x + (size_t)(t0 + tt) * ldx + k);
+                    const float4 b = *reinterpret_cast<const float4 *>(x + (size_t)(t0 + tt) * ldx + k + 4);
+                    acc[tt] += wv[0] * a.x + wv[1] * a.y + wv[2] * a.z + wv[3] * a.w + wv[4] * b.x + wv[5] * b.y + wv[6] * b.z + wv[7] * b.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            const float v = warp_sum(acc[tt]);
+            if (lane == 0 && t0 + tt < n_tokens) {
+                float r = v;
+                if (bias) r += bias[o];
+                if (residual) r += residual[(size_t)(t0 + tt) * ldr + o];
+                y[(size_t)(t0 + tt) * ldy + o] = r;
+            }
+        }
+    }
+}
+
+// qkv row layout: [q: n_head*hd | k: n_head_kv*hd | v: n_head_kv*hd]
+__global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, int n_head_kv, int head_dim, int n_rot, int neox,
+                                  const float * __restrict__ inv_freq, const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_cell,
+                                  KvLayout kv, int layer) {
+    const int t = blockIdx.x;
+    float * row = qkv + (size_t)t * ld;
+    const int pos = tok_pos[t];
+    const int half_rot = n_rot / 2;
+    const int n_rot_heads = n_head + n_head_kv;
+    for (int idx = threadIdx.x; idx < n_rot_heads * half_rot; idx += blockDim.x) {
+        const int h = idx / half_rot, i = idx % half_rot;
+        float * p = row + (size_t)h * head_dim;   // k heads follow the q heads contiguously
+        const float theta = (float)pos * inv_freq[i];
+        float s, c;
+        sincosf(theta, &s, &c);
+        const int i0 = neox ? i : 2 * i, i1 = neox ? i + half_rot : 2 * i + 1;
+        const float a = p[i0], b = p[i1];
+        p[i0] = a * c - b * s;
+        p[i1] = a * s + b * c;
+    }
+    __syncthreads();
+    const int cell = tok_cell[t];
+    const int blk = cell / kv.block_tokens, off = cell % kv.block_tokens;
+    const float * ksrc = row + (size_t)n_head * head_dim;
+    const float * vsrc = ksrc + (size_t)n_head_kv * head_dim;
+    __half * kdst = kv.k + layer * kv.layer_stride;
+    __half * vdst = kv.v + layer * kv.layer_stride;
+    for (int idx = threadIdx.x; idx < n_head_kv * head_dim; idx += blockDim.x) {
+        const int h = idx / head_dim, i = idx % head_dim;
+        const size_t dst = (((size_t)blk * n_head_kv + h) * kv.block_tokens + off) * head_dim + i;
+        kdst[dst] = __float2half_rn(ksrc[idx]);
+        vdst[dst] = __float2half_rn(vsrc[idx]);
+    }
+}
+
+// One warp per (token, q head); lanes own head dimensions; positions in groups of four.
+__global__ void attention_ref_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer,
+                                     const int32_t * __restrict__ tok_slot, const int32_t * __restrict__ tok_pos,
+                                     const int32_t * __restrict__ tok_pos_min, float * __restrict__ out, int ldo) {
+    const int lane = threadIdx.x & 31;
+    const int h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int t = blockIdx.y;
+    if (h >= n_head) return;
+    const int hd = kv.head_dim, B = kv.block_tokens;
+    const int hk = h / (n_head / kv.n_head_kv);
+    const int slot = tok_slot[t], p_last = tok_pos[t], p_first = tok_pos_min[t];
+    const int32_t * table = kv.block_table + (size_t)slot * kv.max_blocks;
+    const __half * kbase = kv.k + layer * kv.layer_stride;
+    const __half * vbase = kv.v + layer * kv.layer_stride;
+    constexpr int MAXD = 8;  // head_dim <= 256
+    float q[MAXD], acc[MAXD];
+    const float scale = rsqrtf((float)hd);
+#pragma unroll
+    for (int j = 0; j < MAXD; ++j) {
+        const int i = lane + 32 * j;
+        q[j] = i < hd ? qkv[(size_t)t * ld + (size_t)h * hd + i] * scale : 0.f;
+        acc[j] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int p0 = p_first; p0 <= p_last; p0 += 4) {
+        float s[4];
+        const __half * vp[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int p = p0 + u;
+            s[u] = 0.f;
+            vp[u] = nullptr;
+            if (p <= p_last) {
+                const int blk = table[p / B];
+                const size_t base = (((size_t)blk * kv.n_head_kv + hk) * B + p % B) * hd;
+                const __half * kp = kbase + base;
+                vp[u] = vbase + base;
+#pragma unroll
+                for (int j = 0; j < MAXD; ++j) {
+                    const int i = lane + 32 * j;
+                    if (i < hd) s[u] += q[j] * __half2float(kp[i]);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) s[u] = warp_sum(s[u]);
+        float mn = m;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (p0 + u <= p_last) mn = fmaxf(mn, s[u]);
+        const float corr = expf(m - mn);
+        l *= corr;
+#pragma unroll
+        for (int j = 0; j < MAXD; ++j) acc[j] *= corr;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (p0 + u <= p_last) {
+                const float pr = expf(s[u] - mn);
+                l += pr;
+#pragma unroll
+                for (int j = 0; j < MAXD; ++j) {
+                    const int i = lane + 32 * j;
+                    if (i < hd) acc[j] += pr * __half2float(vp[u][i]);
+                }
+            }
+        }
+        m = mn;
+    }
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int j = 0; j < MAXD; ++j) {
+        const int i = lane + 32 * j;
+        if (i < hd) out[(size_t)t * ldo + (size_t)h * hd + i] = acc[j] * inv;
+    }
+}
+
+__global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= ff) return;
+    const float g = gu[(size_t)t * ld + i], u = gu[(size_t)t * ld + ff + i];
+    h[(size_t)t * ldh + i] = g / (1.0f + expf(-g)) * u;
+}
+
+// ------------------------------------------------------------------------------------------
+// MoE
+
+// One warp per token: softmax over experts, then k picks by (probability desc, id asc).
+__global__ void moe_route_kernel(const float * __restrict__ logits, int n_expert, int k, int n_tokens, int32_t * __restrict__ ids,
+                                 float * __restrict__ weights) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    constexpr int MAXE = 8;  // up to 256 experts
+    float p[MAXE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) {
+        const int e = lane + 32 * j;
+        p[j] = e < n_expert ? logits[(size_t)t * n_expert + e] : -INFINITY;
+        mx = fmaxf(mx, p[j]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) {
+        const int e = lane + 32 * j;
+        p[j] = e < n_expert ? expf(p[j] - mx) : 0.f;
+    }
+    // serial-order sum over experts so the value matches a scalar loop
+    for (int e = 0; e < n_expert; ++e) {
+        const float v = __shfl_sync(0xffffffffu, p[e >> 5], e & 31);
+        sum += v;
+    }
+#pragma unroll
+    for (int j = 0; j < MAXE; ++j) p[j] = p[j] / sum;
+    for (int pick = 0; pick < k; ++pick) {
+        float best = -1.f;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < MAXE; ++j) {
+            const int e = lane + 32 * j;
+            if (e < n_expert && (p[j] > best || (p[j] == best && e < best_e))) { best = p[j]; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (lane == 0) {
+            ids[(size_t)t * k + pick] = best_e;
+            weights[(size_t)t * k + pick] = best;
+        }
+        if ((best_e & 31) == lane) p[best_e >> 5] = -2.f;
+    }
+}
+
+// One warp per (pair, output row): y[pair][o] = deq(W[expert(pair)])[o] . x[pair / x_div]
+template <uint32_t TYPE>
+__global__ void moe_gemm_rows_kernel(WeightView w, uint64_t expert_stride, const int32_t * __restrict__ pair_expert,
+                                     const float * __restrict__ x, int ldx, int x_div, float * __restrict__ y, int ldy) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int pair = blockIdx.y;
+    if (o >= w.n_out) return;
+    const uint8_t * row = w.data + (size_t)pair_expert[pair] * expert_stride + (size_t)o * w.row_bytes;
+    const float * xr = x + (size_t)(pair / x_div) * ldx;
+    float acc = 0.f;
+    for (uint32_t k = lane * 8; k < w.n_in; k += 256) {
+        float wv[8];
+        decode8<TYPE>(row, k, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc += wv[i] * xr[k + i];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[(size_t)pair * ldy + o] = acc;
+}
+
+// out[t] = residual[t] + sum over the token's experts in ascending expert id of weight * y
+__global__ void moe_combine_kernel(const float * __restrict__ y, int ld, const int32_t * __restrict__ ids, const float * __restrict__ weights,
+                                   int k, int d, const float * __restrict__ residual, float * __restrict__ out) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= d) return;
+    float acc = 0.f;
+    int prev = -1;
+    for (int pick = 0; pick < k; ++pick) {
+        int best = 0x7fffffff, best_j = 0;
+        for (int j = 0; j < k; ++j) {
+            const int e = ids[(size_t)t * k + j];
+            if (e > prev && e < best) { best = e; best_j = j; }
+        }
+        prev = best;
+        acc += weights[(size_t)t * k + best_j] * y[((size_t)t * k + best_j) * ld + i];
+    }
+    out[(size_t)t * d + i] = (residual ? residual[(size_t)t * d + i] : 0.f) + acc;
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-row LoRA
+
+__global__ void lora_shrink_kernel(const float * __restrict__ a_stack, int r_max, int n_in, const int32_t * __restrict__ tok_adapter,
+                                   const float * __restrict__ x, int ldx, float * __restrict__ tmp) {
+    const int lane = threadIdx.x & 31;
+    const int j = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int t = blockIdx.y;
+    if (j >= r_max) return;
+    const int a = tok_adapter[t];
+    float acc = 0.f;
+    if (a >= 0) {
+        const float * ar = a_stack + ((size_t)a * r_max + j) * n_in;
+        for (int i = lane; i < n_in; i += 32) acc += ar[i] * x[(size_t)t * ldx + i];
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) tmp[(size_t)t * r_max + j] = acc;
+}
+
+__global__ void lora_expand_kernel(const float * __restrict__ b_stack, int r_max, int n_out, const float * __restrict__ scales,
+                                   const int32_t * __restrict__ tok_adapter, const float * __restrict__ tmp, float * __restrict__ y, int ldy) {
+    const int t = blockIdx.y;
+    const int o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= n_out) return;
+    const int a = tok_adapter[t];
+    if (a < 0) return;
+    const float * br = b_stack + ((size_t)a * n_out + o) * r_max;
+    float acc = 0.f;
+    for (int j = 0; j < r_max; ++j) acc += br[j] * tmp[(size_t)t * r_max + j];
+    y[(size_t)t * ldy + o] += scales[a] * acc;
+}
+
+template <class F> void dispatch_type(uint32_t type, F && f) {
+    switch (type) {
+        case GGML_F32: f(std::integral_constant<uint32_t, GGML_F32>{}); break;
+        case GGML_F16: f(std::integral_constant<uint32_t, GGML_F16>{}); break;
+        case GGML_BF16: f(std::integral_constant<uint32_t, GGML_BF16>{}); break;
+        case GGML_Q8_0: f(std::integral_constant<uint32_t, GGML_Q8_0>{}); break;
+        case GGML_Q4_K: f(std::integral_constant<uint32_t, GGML_Q4_K>{}); break;
+        case GGML_MXFP4: f(std::integral_constant<uint32_t, GGML_MXFP4>{}); break;
+        default: break;
+    }
+}
+
+} // namespace
+
+void launch_pack(const RowDesc * rows, int n_rows, int n_tokens, const int32_t * block_table, int max_blocks, int block_tokens,
+                 PackMaps maps, cudaStream_t stream) {
+    pack_scan_kernel<<<1, 1024, 0, stream>>>(rows, n_rows, maps.cu_rows, maps.out_rank);
+    pack_fill_kernel<<<(n_tokens + 255) / 256, 256, 0, stream>>>(rows, n_rows, n_tokens, block_table, max_blocks, block_tokens, maps);
+}
+
+void launch_block_table_patch(int32_t * block_table, const int32_t * patches, int n_patches, cudaStream_t stream) {
+    if (n_patches <= 0) return;
+    block_table_patch_kernel<<<(n_patches + 255) / 256, 256, 0, stream>>>(block_table, patches, n_patches);
+}
+
+void launch_kv_block_copy(KvLayout kv, int n_layer, const int32_t * pairs, int n_pairs, cudaStream_t stream) {
+    if (n_pairs <= 0) return;
+    kv_block_copy_kernel<<<dim3(n_pairs, n_layer), 256, 0, stream>>>(kv, n_layer, pairs);
+}
+
+void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int pos_first, int n_pos, __half * dense, bool to_cache,
+                        cudaStream_t stream) {
+    if (n_pos <= 0) return;
+    kv_snapshot_kernel<<<dim3(n_pos, n_layer * 2), 128, 0, stream>>>(kv, table_row, pos_first, dense, n_pos, to_cache ? 1 : 0);
+}
+
+void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream) {
+    dispatch_type(embd.type, [&](auto tag) {
+        embed_kernel<decltype(tag)::value><<<n_tokens, 128, 0, stream>>>(embd, tokens, x);
+    });
+}
+
+void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const float * w, int n, float eps, float * y, int ldy, int n_tokens,
+                     cudaStream_t stream) {
+    rms_norm_kernel<<<n_tokens, 256, 0, stream>>>(x, ldx, gather, w, n, eps, y, ldy);
+}
+
+void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
+                      int ldr, cudaStream_t stream) {
+    const int warps = 8;
+    dispatch_type(w.type, [&](auto tag) {
+        gemm_rows_kernel<decltype(tag)::value><<<(w.n_out + warps - 1) / warps, warps * 32, 0, stream>>>(w, x, ldx, n_tokens, y, ldy, bias,
+                                                                                                       residual, ldr);
+    });
+}
+
+void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
+                       const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream) {
+    rope_store_kernel<<<n_tokens, 256, 0, stream>>>(qkv, ld, n_head, n_head_kv, head_dim, n_rot, neox ? 1 : 0, inv_freq, tok_pos, tok_cell, kv,
+                                                    layer);
+}
+
+void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,
+                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream) {
+    const int warps = 4;
+    attention_ref_kernel<<<dim3((n_head + warps - 1) / warps, n_tokens), warps * 32, 0, stream>>>(qkv, ld, n_head, kv, layer, tok_slot, tok_pos,
+                                                                                                tok_pos_min, out, ldo);
+}
+
+void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream) {
+    swiglu_kernel<<<dim3((ff + 255) / 256, n_tokens), 256, 0, stream>>>(gu, ld, ff, h, ldh);
+}
+
+void launch_moe_route(const float * router_logits, int n_expert, int k, int n_tokens, int32_t * ids, float * weights, cudaStream_t stream) {
+    moe_route_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(router_logits, n_expert, k, n_tokens, ids, weights);
+}
+
+void launch_moe_gemm_rows(WeightView w_all, uint64_t expert_stride_bytes, const int32_t * pair_expert, const float * x, int ldx, int x_div,
+                          int n_pairs, float * y, int ldy, cudaStream_t stream) {
+    const int warps = 8;
+    dispatch_type(w_all.type, [&](auto tag) {
+        moe_gemm_rows_kernel<decltype(tag)::value><<<dim3((w_all.n_out + warps - 1) / warps, n_pairs), warps * 32, 0, stream>>>(
+            w_all, expert_stride_bytes, pair_expert, x, ldx, x_div, y, ldy);
+    });
+}
+
+void launch_moe_combine(const float * y_pairs, int ld, const int32_t * ids, const float * weights, int k, int d, int n_tokens,
+                        const float * residual, float * out, cudaStream_t stream) {
+    moe_combine_kernel<<<dim3((d + 255) / 256, n_tokens), 256, 0, stream>>>(y_pairs, ld, ids, weights, k, d, residual, out);
+}
+
+void launch_lora_shrink(const float * a_stack, int r_max, int n_in, const int32_t * tok_adapter, const float * x, int ldx, int n_tokens,
+                        float * tmp, cudaStream_t stream) {
+    const int warps = 4;
+    lora_shrink_kernel<<<dim3((r_max + warps - 1) / warps, n_tokens), warps * 32, 0, stream>>>(a_stack, r_max, n_in, tok_adapter, x, ldx, tmp);
+}
+
+void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float * scales, const int32_t * tok_adapter, const float * tmp,
+                        int n_tokens, float * y, int ldy, cudaStream_t stream) {
+    lora_expand_kernel<<<dim3((n_out + 255) / 256, n_tokens), 256, 0, stream>>>(b_stack, r_max, n_out, scales, tok_adapter, tmp, y, ldy);
+}
+
+} // namespace rb200

@@ -1,0 +1,128 @@
+// Device-side views and launch wrappers of the decode step's kernels.
+#pragma once
+
+#include <cstdint>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+namespace rb200 {
+
+// A weight matrix in device memory in its GGUF storage layout: n_out rows of n_in elements.
+struct WeightView {
+    const uint8_t * data = nullptr;
+    uint32_t type = 0;
+    uint32_t n_in = 0;
+    uint32_t n_out = 0;
+    uint32_t row_bytes = 0;
+};
+
+// One row of a step plan as the packing kernel reads it (32 bytes).
+struct RowDesc {
+    int32_t slot;
+    int32_t n;
+    int32_t pos0;
+    int32_t sample;     // 0/1
+    int32_t adapter;    // stacked adapter index, -1 = none
+    int32_t pos_min;    // first resident position of the slot once this step is applied
+    int32_t pad0;
+    int32_t pad1;
+};
+
+// Per sampling row parameters (64 bytes).
+struct SampleDesc {
+    float temperature;
+    float top_p;
+    int32_t top_k;        // <= 0 disabled
+    float min_p;          // <= 0 disabled
+    uint32_t seed;
+    uint32_t draw_lo;     // per-request draw counter
+    uint32_t draw_hi;
+    uint32_t n_top;       // top logprobs requested
+    uint32_t flags;       // bit0: v2 row (post-transform reporting), bit1: want sampled_logprob
+    uint32_t edit_begin;  // range in the logit-edit list
+    uint32_t edit_end;
+    uint32_t pad[5];
+};
+
+// One sparse change of a logits row before sampling (v2 rows): logit_bias adds, penalties.
+struct LogitEdit {
+    int32_t id;
+    float bias;        // added first
+    float repeat;      // repeat penalty (1 = none): multiplies non-positive, divides positive logits
+    float subtract;    // count * frequency + presence
+};
+
+struct SampleOut {
+    int32_t token;
+    float logprob;           // temperature-1 logprob of token under the raw logits
+    float sampled_logprob;   // post-transformation logprob (v2 + want_logprob)
+    uint32_t n_top;
+};
+
+// Batch maps the packing kernel writes.
+struct PackMaps {
+    int32_t * cu_rows;     // [R + 1]
+    int32_t * out_rank;    // [R + 1] exclusive scan of sample flags
+    int32_t * tok_slot;    // [T]
+    int32_t * tok_pos;     // [T]
+    int32_t * tok_row;     // [T]
+    int32_t * tok_cell;    // [T] physical KV cell = block * block_tokens + offset
+    int32_t * tok_adapter; // [T]
+    int32_t * tok_pos_min; // [T]
+    int32_t * out_index;   // [S]
+};
+
+struct KvLayout {
+    __half * k;            // [n_blocks][n_head_kv][block_tokens][head_dim] per layer, layers consecutive
+    __half * v;
+    uint64_t layer_stride; // elements per layer
+    int32_t n_head_kv;
+    int32_t head_dim;
+    int32_t block_tokens;
+    const int32_t * block_table;  // [n_slots][max_blocks]
+    int32_t max_blocks;
+};
+
+void launch_pack(const RowDesc * rows, int n_rows, int n_tokens, const int32_t * block_table, int max_blocks, int block_tokens,
+                 PackMaps maps, cudaStream_t stream);
+void launch_block_table_patch(int32_t * block_table, const int32_t * patches, int n_patches, cudaStream_t stream);
+void launch_kv_block_copy(KvLayout kv, int n_layer, const int32_t * pairs, int n_pairs, cudaStream_t stream);
+
+// Sequence snapshots: dense is [layer][K|V][pos][head][dim] f16 for positions pos_first .. pos_first + n_pos - 1.
+void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int pos_first, int n_pos, __half * dense, bool to_cache,
+                        cudaStream_t stream);
+
+void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream);
+// y[t] = x[gather ? gather[t] : t] * rsqrt(mean(x^2) + eps) * w
+void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const float * w, int n, float eps, float * y, int ldy, int n_tokens,
+                     cudaStream_t stream);
+// y[t][o] = sum_i deq(W)[o][i] x[t][i] (+ bias[o]) (+ residual[t][o]); reference kernel, any T.
+void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
+                      int ldr, cudaStream_t stream);
+// In-place RoPE on q and k (inside the fused qkv buffer) and the f16 store of k, v into the paged cache.
+void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
+                       const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream);
+void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,
+                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream);
+// h[t][i] = silu(gu[t][i]) * gu[t][ff + i]
+void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream);
+
+// MoE (reference kernels): router softmax + top-k, per-pair expert GEMMs, fixed-order combine.
+void launch_moe_route(const float * router_logits, int n_expert, int k, int n_tokens, int32_t * ids, float * weights, cudaStream_t stream);
+void launch_moe_gemm_rows(WeightView w_all, uint64_t expert_stride_bytes, const int32_t * pair_expert, const float * x, int ldx, int x_div,
+                          int n_pairs, float * y, int ldy, cudaStream_t stream);
+void launch_moe_combine(const float * y_pairs, int ld, const int32_t * ids, const float * weights, int k, int d, int n_tokens,
+                        const float * residual, float * out, cudaStream_t stream);
+
+// Per-row LoRA (reference kernels): tmp[t][j] = A[a_t][j] . x[t]; y[t][o] += scale[a_t] * B[a_t][o] . tmp[t]
+void launch_lora_shrink(const float * a_stack, int r_max, int n_in, const int32_t * tok_adapter, const float * x, int ldx, int n_tokens,
+                        float * tmp, cudaStream_t stream);
+void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float * scales, const int32_t * tok_adapter, const float * tmp,
+                        int n_tokens, float * y, int ldy, cudaStream_t stream);
+
+// Sampling over logits rows [S][n_vocab]. v2 rows transform their row of `work_logits`, which must
+// then hold a copy of `raw_logits`; with v1 rows only, `work_logits` may be null.
+void launch_sample(const float * raw_logits, float * work_logits, int n_vocab, int n_rows, const SampleDesc * desc, const LogitEdit * edits, SampleOut * out,
+                   int32_t * top_ids, float * top_logprobs, int top_stride, cudaStream_t stream);
+
+} // namespace rb200

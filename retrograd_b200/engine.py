@@ -1,0 +1,474 @@
+"""Host-side mirror of the reference's safe engine handle over libretro_b200's C ABI.
+
+Names and semantics follow `retrograd_engine` (crates/retrograd-engine/src/step.rs:93-301,
+412-505; crates/retrograd-engine/src/engine/step.rs:19-38; engine/mod.rs:57-102,151-208):
+`StepRow.prefill / StepRow.decode`, `StepOutput` reused across steps and exposing no rows after a
+failed call, status -3 mapped to `InvalidArgument`, every other failure to `EngineError`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Iterable, Sequence
+
+import numpy as np
+
+from . import _ffi
+
+ADAPTER_BASE = -1
+KV_DTYPE_F32, KV_DTYPE_F16, KV_DTYPE_Q8_0, KV_DTYPE_Q4_0 = 0, 1, 2, 3
+STATE_SEQ_FLAGS_NONE, STATE_SEQ_FLAGS_PARTIAL_ONLY, STATE_SEQ_FLAGS_ON_DEVICE = 0, 1, 2
+
+
+class EngineError(RuntimeError):
+    """A runtime failure reported by the library (status -1 or -2)."""
+
+
+class InvalidArgument(EngineError):
+    """A caller error reported before anything was decoded (status -3)."""
+
+
+def _last_error() -> str:
+    message = _ffi.load_library().retro_last_error()
+    return message.decode("utf-8", "replace") if message else ""
+
+
+def _check(status: int) -> None:
+    if status == 0:
+        return
+    if status == -3:
+        raise InvalidArgument(_last_error())
+    raise EngineError(_last_error())
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    max_new_tokens: int = 1
+    seed: int = 0
+
+
+@dataclass
+class SamplingParamsV2:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    max_new_tokens: int = 1
+    seed: int = 0
+    top_k: int = 0
+    min_p: float = 0.0
+    repeat_penalty: float = 1.0
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    penalty_window: int = 0
+    logit_bias: Sequence[tuple[int, float]] = ()
+
+    @classmethod
+    def greedy(cls) -> "SamplingParamsV2":
+        """Greedy decoding as the reference spells it: top_k = 1."""
+        return cls(top_k=1)
+
+    @classmethod
+    def from_v1(cls, p: SamplingParams) -> "SamplingParamsV2":
+        return cls(temperature=p.temperature, top_p=p.top_p, max_new_tokens=p.max_new_tokens, seed=p.seed)
+
+
+@dataclass
+class StepRow:
+    request: int
+    slot: int
+    tokens: Sequence[int]
+    pos0: int
+    sample: bool = False
+    sampling: SamplingParamsV2 = field(default_factory=SamplingParamsV2)
+    n_top_logprobs: int = 0
+    want_logprob: bool = False
+    adapter: int = 0  # 0 = the context's own adapter set, ADAPTER_BASE, or a loaded adapter id
+
+    @classmethod
+    def prefill(cls, request: int, slot: int, tokens: Sequence[int], pos0: int) -> "StepRow":
+        return cls(request, slot, tokens, pos0, False)
+
+    @classmethod
+    def decode(cls, request: int, slot: int, token: int, pos0: int, sampling: SamplingParamsV2 | SamplingParams) -> "StepRow":
+        if isinstance(sampling, SamplingParams):
+            sampling = SamplingParamsV2.from_v1(sampling)
+        return cls(request, slot, [token], pos0, True, sampling)
+
+
+@dataclass
+class StepOutRow:
+    token: int = 0
+    logprob: float = 0.0
+    forced: bool = False
+    sampled: bool = False
+    n_top: int = 0
+    sampled_logprob: float = 0.0
+
+
+class StepOutput:
+    """Reused output buffers of `Engine.step`; grown only when a call needs more."""
+
+    def __init__(self, n_rows: int = 0, n_top_stride: int = 0) -> None:
+        self._rows = (_ffi.StepOutRowV2C * max(n_rows, 1))()
+        self._cap = max(n_rows, 1)
+        self.n_top_stride = n_top_stride
+        self._top_ids = np.zeros(self._cap * max(n_top_stride, 1), dtype=np.int32)
+        self._top_logprobs = np.zeros(self._cap * max(n_top_stride, 1), dtype=np.float32)
+        self.n_rows = 0
+
+    def ensure(self, n_rows: int, n_top_stride: int) -> None:
+        if n_rows > self._cap:
+            self._rows = (_ffi.StepOutRowV2C * n_rows)()
+            self._cap = n_rows
+        self.n_top_stride = max(self.n_top_stride, n_top_stride)
+        need = self._cap * max(self.n_top_stride, 1)
+        if need > self._top_ids.size:
+            self._top_ids = np.zeros(need, dtype=np.int32)
+            self._top_logprobs = np.zeros(need, dtype=np.float32)
+
+    def row(self, r: int) -> StepOutRow:
+        if r >= self.n_rows:
+            raise IndexError(r)
+        o = self._rows[r]
+        return StepOutRow(o.token, o.logprob, bool(o.forced), bool(o.sampled), o.n_top, o.sampled_logprob)
+
+    def rows(self) -> list[StepOutRow]:
+        return [self.row(r) for r in range(self.n_rows)]
+
+    def top(self, r: int) -> tuple[np.ndarray, np.ndarray]:
+        n = self._rows[r].n_top
+        base = r * self.n_top_stride
+        return self._top_ids[base : base + n].copy(), self._top_logprobs[base : base + n].copy()
+
+
+@dataclass
+class EngineConfig:
+    n_ctx: int = 4096
+    n_seq_max: int = 8
+    n_batch: int = 512
+    n_ubatch: int = 512
+    kv_dtype: int = KV_DTYPE_F16
+    flash_attn: bool = True
+    device: int = 0
+    threads: int = 0
+    verbose: bool = False
+    kv_unified: int = 1
+
+    def to_c(self) -> _ffi.EngineConfigC:
+        c = _ffi.EngineConfigC()
+        c.struct_size = C.sizeof(_ffi.EngineConfigC)
+        c.n_ctx, c.n_seq_max, c.n_batch, c.n_ubatch = self.n_ctx, self.n_seq_max, self.n_batch, self.n_ubatch
+        c.kv_dtype, c.flash_attn, c.device, c.threads = self.kv_dtype, self.flash_attn, self.device, self.threads
+        c.verbose, c.kv_unified = self.verbose, self.kv_unified
+        c.expert_placement, c.expert_host_layers, c.expert_device_cache_bytes = 0, 0, 0
+        return c
+
+
+@dataclass
+class EngineMemory:
+    n_slots: int
+    cells_total: int
+    cells_used: int
+    kv_bytes: int
+    recurrent_bytes: int
+
+
+def synth_gguf(path: str, **spec) -> int:
+    """Writes a seeded random model as GGUF (see retro_b200_synth_gguf). Returns the file size."""
+    lib = _ffi.load_library()
+    text = " ".join(f"{k}={v}" for k, v in spec.items())
+    n = C.c_uint64(0)
+    _check(lib.retro_b200_synth_gguf(str(path).encode(), text.encode(), C.byref(n)))
+    return n.value
+
+
+def quantize_row(ggml_type: int, values) -> bytes:
+    """One stored row of `ggml_type` from float values (the synthesiser's encoders)."""
+    lib = _ffi.load_library()
+    v = np.ascontiguousarray(values, dtype=np.float32)
+    out = np.zeros(v.size * 4 + 64, dtype=np.uint8)
+    n = C.c_size_t()
+    _check(lib.retro_b200_quantize_row(ggml_type, v.ctypes.data_as(C.POINTER(C.c_float)), v.size, out.ctypes.data_as(C.POINTER(C.c_uint8)), out.size, C.byref(n)))
+    return out[: n.value].tobytes()
+
+
+class Engine:
+    def __init__(self, model_path: str, config: EngineConfig | None = None) -> None:
+        self._lib = _ffi.load_library()
+        self.config = config or EngineConfig()
+        c = self.config.to_c()
+        self._h = self._lib.retro_engine_new(str(model_path).encode(), C.byref(c))
+        if not self._h:
+            raise EngineError(_last_error())
+        self._keep: list = []
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.retro_engine_free(self._h)
+            self._h = None
+
+    def __del__(self) -> None:  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self) -> "Engine":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+    # ---- introspection
+    def vocab_size(self) -> int:
+        v = C.c_uint32()
+        _check(self._lib.retro_engine_vocab_size(self._h, C.byref(v)))
+        return v.value
+
+    def context_size(self) -> int:
+        v = C.c_uint32()
+        _check(self._lib.retro_engine_context_size(self._h, C.byref(v)))
+        return v.value
+
+    def eos_token(self) -> int:
+        v = C.c_int32()
+        _check(self._lib.retro_engine_eos_token(self._h, C.byref(v)))
+        return v.value
+
+    def is_eog_token(self, token: int) -> bool:
+        v = C.c_bool()
+        _check(self._lib.retro_engine_is_eog_token(self._h, token, C.byref(v)))
+        return v.value
+
+    def kv_unified(self) -> bool:
+        v = C.c_bool()
+        _check(self._lib.retro_engine_kv_unified(self._h, C.byref(v)))
+        return v.value
+
+    def weights_version(self) -> int:
+        v = C.c_uint64()
+        _check(self._lib.retro_engine_weights_version(self._h, C.byref(v)))
+        return v.value
+
+    def model_fingerprint(self) -> int:
+        v = C.c_uint64()
+        _check(self._lib.retro_engine_model_fingerprint(self._h, C.byref(v)))
+        return v.value
+
+    def is_hybrid(self) -> bool:
+        v = C.c_bool()
+        _check(self._lib.retro_engine_is_hybrid(self._h, C.byref(v)))
+        return v.value
+
+    def detokenize(self, tokens: Sequence[int], unparse_special: bool = False) -> bytes:
+        arr = (C.c_int32 * len(tokens))(*tokens)
+        n = C.c_size_t()
+        _check(self._lib.retro_engine_detokenize(self._h, arr, len(tokens), unparse_special, None, 0, C.byref(n)))
+        buf = C.create_string_buffer(max(n.value, 1))
+        _check(self._lib.retro_engine_detokenize(self._h, arr, len(tokens), unparse_special, buf, n.value, C.byref(n)))
+        return buf.raw[: n.value]
+
+    def tokenize_text(self, text: str) -> list[int]:
+        n = C.c_size_t()
+        _check(self._lib.retro_engine_tokenize_text(self._h, text.encode(), None, 0, C.byref(n)))
+        arr = (C.c_int32 * max(n.value, 1))()
+        _check(self._lib.retro_engine_tokenize_text(self._h, text.encode(), arr, n.value, C.byref(n)))
+        return list(arr[: n.value])
+
+    # ---- the step
+    def step(self, rows: Sequence[StepRow], out: StepOutput) -> None:
+        out.n_rows = 0  # a failed call exposes nothing
+        stride = max((r.n_top_logprobs for r in rows), default=0)
+        out.ensure(len(rows), stride)
+        n = len(rows)
+        c_rows = (_ffi.StepRowV2C * max(n, 1))()
+        keep = []
+        for i, r in enumerate(rows):
+            tokens = np.ascontiguousarray(r.tokens, dtype=np.int32)
+            keep.append(tokens)
+            if tokens.size < 1:
+                raise InvalidArgument("a step row requires at least one token")
+            if r.pos0 < 0:
+                raise InvalidArgument("step row pos0 must be non-negative")
+            if r.sample and r.request < 0:
+                raise InvalidArgument("a sampling step row requires a request id")
+            c = c_rows[i]
+            c.struct_size = C.sizeof(_ffi.StepRowV2C)
+            c.request, c.slot = r.request, r.slot
+            c.tokens = tokens.ctypes.data_as(C.POINTER(C.c_int32))
+            c.n, c.pos0, c.sample = tokens.size, r.pos0, r.sample
+            s = r.sampling
+            c.sampling.struct_size = C.sizeof(_ffi.SamplingParamsV2C)
+            c.sampling.temperature, c.sampling.top_p = s.temperature, s.top_p
+            c.sampling.max_new_tokens, c.sampling.seed = s.max_new_tokens, s.seed
+            c.sampling.top_k, c.sampling.min_p = s.top_k, s.min_p
+            c.sampling.repeat_penalty = s.repeat_penalty
+            c.sampling.frequency_penalty, c.sampling.presence_penalty = s.frequency_penalty, s.presence_penalty
+            c.sampling.penalty_window = s.penalty_window
+            if len(s.logit_bias) > 4096:
+                raise InvalidArgument("sampling n_logit_bias must not exceed 4096")
+            if s.logit_bias:
+                ids = np.ascontiguousarray([b[0] for b in s.logit_bias], dtype=np.int32)
+                vals = np.ascontiguousarray([b[1] for b in s.logit_bias], dtype=np.float32)
+                keep += [ids, vals]
+                c.sampling.n_logit_bias = ids.size
+                c.sampling.logit_bias_ids = ids.ctypes.data_as(C.POINTER(C.c_int32))
+                c.sampling.logit_bias_values = vals.ctypes.data_as(C.POINTER(C.c_float))
+            c.n_top_logprobs, c.want_logprob, c.adapter = r.n_top_logprobs, int(r.want_logprob), r.adapter
+        requests = [r.request for r in rows if r.request >= 0]
+        if len(requests) != len(set(requests)):
+            raise InvalidArgument("a request id appears twice in one step")
+        any_top = out.n_top_stride > 0
+        status = self._lib.retro_engine_step_v2(
+            self._h,
+            c_rows,
+            n,
+            out._rows,
+            out._top_ids.ctypes.data_as(C.POINTER(C.c_int32)) if any_top else None,
+            out._top_logprobs.ctypes.data_as(C.POINTER(C.c_float)) if any_top else None,
+            out.n_top_stride,
+        )
+        _check(status)
+        out.n_rows = n
+
+    def step_v1(self, rows: Sequence[StepRow], out_stride: int = 0):
+        """The v1 entry point (retro_engine_step); returns (out rows, top ids, top logprobs)."""
+        n = len(rows)
+        c_rows = (_ffi.StepRowC * max(n, 1))()
+        keep = []
+        for i, r in enumerate(rows):
+            tokens = np.ascontiguousarray(r.tokens, dtype=np.int32)
+            keep.append(tokens)
+            c = c_rows[i]
+            c.struct_size = C.sizeof(_ffi.StepRowC)
+            c.request, c.slot = r.request, r.slot
+            c.tokens = tokens.ctypes.data_as(C.POINTER(C.c_int32))
+            c.n, c.pos0, c.sample = tokens.size, r.pos0, r.sample
+            c.sampling.temperature, c.sampling.top_p = r.sampling.temperature, r.sampling.top_p
+            c.sampling.max_new_tokens, c.sampling.seed = r.sampling.max_new_tokens, r.sampling.seed
+            c.n_top_logprobs, c.adapter = r.n_top_logprobs, r.adapter
+        outs = (_ffi.StepOutRowC * max(n, 1))()
+        ids = np.zeros(max(n * out_stride, 1), dtype=np.int32)
+        lps = np.zeros(max(n * out_stride, 1), dtype=np.float32)
+        _check(
+            self._lib.retro_engine_step(
+                self._h,
+                c_rows,
+                n,
+                outs,
+                ids.ctypes.data_as(C.POINTER(C.c_int32)) if out_stride else None,
+                lps.ctypes.data_as(C.POINTER(C.c_float)) if out_stride else None,
+                out_stride,
+            )
+        )
+        rows_out = [StepOutRow(o.token, o.logprob, bool(o.forced), bool(o.sampled), o.n_top, 0.0) for o in outs[:n]]
+        return rows_out, ids.reshape(-1)[: n * out_stride].reshape(n, out_stride) if out_stride else ids[:0], (
+            lps.reshape(-1)[: n * out_stride].reshape(n, out_stride) if out_stride else lps[:0]
+        )
+
+    # ---- sequence memory
+    def seq_rm(self, slot: int, p0: int = -1, p1: int = -1) -> None:
+        _check(self._lib.retro_engine_seq_rm(self._h, slot, p0, p1))
+
+    def seq_cp(self, src: int, dst: int, p0: int = -1, p1: int = -1) -> None:
+        _check(self._lib.retro_engine_seq_cp(self._h, src, dst, p0, p1))
+
+    def seq_pos(self, slot: int) -> tuple[int, int]:
+        a, b = C.c_int32(), C.c_int32()
+        _check(self._lib.retro_engine_seq_pos(self._h, slot, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def seq_save(self, slot: int, flags: int = 0) -> bytes:
+        n = C.c_size_t()
+        _check(self._lib.retro_engine_seq_save(self._h, slot, flags, None, 0, C.byref(n)))
+        buf = (C.c_uint8 * n.value)()
+        _check(self._lib.retro_engine_seq_save(self._h, slot, flags, buf, n.value, C.byref(n)))
+        return bytes(buf[: n.value])
+
+    def seq_load(self, slot: int, data: bytes, flags: int = 0) -> int:
+        buf = (C.c_uint8 * max(len(data), 1)).from_buffer_copy(data if data else b"\0")
+        n = C.c_size_t()
+        _check(self._lib.retro_engine_seq_load(self._h, slot, flags, buf, len(data), C.byref(n)))
+        return n.value
+
+    def memory(self) -> EngineMemory:
+        m = _ffi.MemoryInfoC()
+        _check(self._lib.retro_engine_memory(self._h, C.byref(m)))
+        return EngineMemory(m.n_slots, m.cells_total, m.cells_used, m.kv_bytes, m.recurrent_bytes)
+
+    def request_free(self, request: int) -> None:
+        _check(self._lib.retro_engine_request_free(self._h, request))
+
+    # ---- per-row adapters
+    def adapter_load(self, path: str, scale: float = 1.0) -> int:
+        v = C.c_int32()
+        _check(self._lib.retro_engine_adapter_load(self._h, str(path).encode(), scale, C.byref(v)))
+        return v.value
+
+    def adapter_unload(self, adapter: int) -> None:
+        _check(self._lib.retro_engine_adapter_unload(self._h, adapter))
+
+    def adapter_rows_info(self) -> dict:
+        info = _ffi.AdapterRowsInfoC()
+        _check(self._lib.retro_engine_adapter_rows_info(self._h, C.byref(info)))
+        return dict(n_adapters=info.n_adapters, max_rank=info.max_rank, stacked_bytes=info.stacked_bytes, unpadded_bytes=info.unpadded_bytes)
+
+    # ---- MoE telemetry
+    def expert_route_enable(self, sample_every: int = 1) -> None:
+        _check(self._lib.retro_engine_expert_route_enable(self._h, sample_every))
+
+    def expert_route_counts(self, layer: int, n_expert: int) -> np.ndarray:
+        out = np.zeros(n_expert, dtype=np.uint32)
+        _check(self._lib.retro_engine_expert_route_counts(self._h, layer, out.ctypes.data_as(C.POINTER(C.c_uint32)), n_expert))
+        return out
+
+    # ---- inspection hooks (no counterpart in the reference)
+    def last_pack(self) -> dict:
+        nt, no = C.c_size_t(), C.c_size_t()
+        _check(self._lib.retro_b200_engine_last_pack(self._h, C.byref(nt), C.byref(no), None, None, None, None, None, None, 0))
+        cap = max(nt.value, self.config.n_batch) + 1
+        arrs = {k: np.zeros(cap, dtype=np.int32) for k in ("tok_slot", "tok_pos", "tok_row", "tok_cell", "out_index", "cu_rows")}
+        ptr = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+        _check(
+            self._lib.retro_b200_engine_last_pack(
+                self._h, C.byref(nt), C.byref(no), ptr(arrs["tok_slot"]), ptr(arrs["tok_pos"]), ptr(arrs["tok_row"]),
+                ptr(arrs["tok_cell"]), ptr(arrs["out_index"]), ptr(arrs["cu_rows"]), cap,
+            )
+        )
+        T, S = nt.value, no.value
+        out = {k: arrs[k][:T] for k in ("tok_slot", "tok_pos", "tok_row", "tok_cell")}
+        out["out_index"] = arrs["out_index"][:S]
+        out["cu_rows"] = arrs["cu_rows"]
+        out["n_tokens"], out["n_out"] = T, S
+        return out
+
+    def last_logits(self, index: int) -> np.ndarray:
+        v = self.vocab_size()
+        out = np.zeros(v, dtype=np.float32)
+        _check(self._lib.retro_b200_engine_last_logits(self._h, index, out.ctypes.data_as(C.POINTER(C.c_float)), v))
+        return out
+
+    def last_routes(self) -> np.ndarray:
+        n = C.c_size_t()
+        _check(self._lib.retro_b200_engine_last_routes(self._h, None, 0, C.byref(n)))
+        out = np.zeros(max(n.value, 1), dtype=np.int32)
+        _check(self._lib.retro_b200_engine_last_routes(self._h, out.ctypes.data_as(C.POINTER(C.c_int32)), out.size, C.byref(n)))
+        return out[: n.value]
+
+    def block_table(self, slot: int) -> tuple[np.ndarray, int]:
+        n, b = C.c_size_t(), C.c_uint32()
+        _check(self._lib.retro_b200_engine_block_table(self._h, slot, None, 0, C.byref(n), C.byref(b)))
+        out = np.zeros(max(n.value, 1), dtype=np.int32)
+        _check(self._lib.retro_b200_engine_block_table(self._h, slot, out.ctypes.data_as(C.POINTER(C.c_int32)), out.size, C.byref(n), C.byref(b)))
+        return out[: n.value], b.value
+
+    def blocks(self) -> tuple[int, int]:
+        a, b = C.c_uint64(), C.c_uint64()
+        _check(self._lib.retro_b200_engine_blocks(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def last_step_stats(self) -> tuple[float, int]:
+        ms, n = C.c_float(), C.c_uint64()
+        _check(self._lib.retro_b200_engine_last_step_stats(self._h, C.byref(ms), C.byref(n)))
+        return ms.value, n.value

@@ -1,0 +1,269 @@
+"""Engine behaviour through the C ABI on the GPU: validation, sequence memory, sampling, adapters."""
+import numpy as np
+import pytest
+
+from helpers import ParityReport, check_step, expect_greedy
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def pair(rb, oracle, c1_model):
+    engine = rb.Engine(str(c1_model), rb.EngineConfig(n_ctx=1024, n_seq_max=8, n_batch=128, n_ubatch=128))
+    om = oracle.Model(str(c1_model))
+    octx = oracle.Context(om, 8, engine.context_size())
+    yield engine, octx
+    engine.close()
+
+
+def _prompt(seed, n, vocab=4096):
+    return np.random.default_rng(seed).integers(3, vocab, n).tolist()
+
+
+def test_step_validation_messages(rb, pair):
+    """Same checks, order and messages as the reference's step (retro_gen_core.cpp:2409-2516);
+    nothing is decoded by a refused step."""
+    engine, _ = pair
+    out = rb.StepOutput()
+    g = rb.SamplingParamsV2.greedy()
+    cases = [
+        ([rb.StepRow(0, 9, [5], 0)], "step row slot is outside the context's sequence range"),
+        ([rb.StepRow(0, 0, [5], 1024)], "step row positions exceed the per-sequence context"),
+        ([rb.StepRow(0, 0, [5, 6, 7], 0), rb.StepRow(1, 0, [8], 2)], "step rows overlap in the same sequence slot"),
+        ([rb.StepRow(0, 0, [5], 0), rb.StepRow(1, 0, [8], 1, adapter=rb.ADAPTER_BASE)], "step rows of one sequence slot select different adapters"),
+        ([rb.StepRow(0, 0, [4096], 0)], "token 4096 at index 0 is outside the vocabulary of size 4096"),
+        ([rb.StepRow(0, 0, [5] * 129, 0)], "the step's tokens exceed the context's physical batch (n_batch)"),
+        ([rb.StepRow(0, 0, [5], 0, adapter=77)], "step row adapter 77 is not a loaded per-row adapter"),
+        ([rb.StepRow(0, 0, [5], 0, sample=True, sampling=rb.SamplingParamsV2(temperature=0.0))], "sampling temperature must be finite and greater than zero"),
+        ([rb.StepRow(0, 0, [5], 0, sample=True, sampling=rb.SamplingParamsV2(top_p=0.0))], "sampling top_p must be in (0, 1]"),
+        ([rb.StepRow(0, 0, [5], 0, sample=True, sampling=rb.SamplingParamsV2(min_p=2.0))], "sampling min_p must be in [0, 1]"),
+        ([rb.StepRow(0, 0, [5], 0, sample=True, sampling=rb.SamplingParamsV2(logit_bias=[(5000, 1.0)]))], "token 5000 at index 0 is outside the vocabulary of size 4096"),
+    ]
+    for rows, message in cases:
+        with pytest.raises(rb.InvalidArgument) as err:
+            engine.step(rows, out)
+        assert str(err.value) == message
+        assert out.n_rows == 0
+    assert engine.seq_pos(0) == (-1, -1) and engine.memory().cells_used == 0
+    # a gap is a runtime condition, reported with -1
+    engine.step([rb.StepRow(0, 0, [5, 6], 0)], out)
+    with pytest.raises(rb.EngineError) as err:
+        engine.step([rb.StepRow(0, 0, [7], 5)], out)
+    assert not isinstance(err.value, rb.InvalidArgument) and "without a gap" in str(err.value)
+    assert engine.seq_pos(0) == (0, 1)
+    # v1 entry point: struct_size is the evolution key
+    rows_out, _, _ = engine.step_v1([rb.StepRow(3, 1, [9, 10], 0, sample=True, sampling=g)])
+    assert rows_out[0].sampled
+
+
+def test_kv_full_is_a_capacity_condition(rb, c1_model):
+    engine = rb.Engine(str(c1_model), rb.EngineConfig(n_ctx=64, n_seq_max=2, n_batch=64, n_ubatch=64))
+    out = rb.StepOutput()
+    engine.step([rb.StepRow(0, 0, _prompt(1, 64), 0)], out)
+    used, total = engine.blocks()
+    assert (used, total) == (4, 6)
+    engine.step([rb.StepRow(1, 1, _prompt(2, 32), 0)], out)
+    with pytest.raises(rb.EngineError) as err:
+        engine.step([rb.StepRow(1, 1, _prompt(3, 16), 32)], out)   # would need a 7th block
+    assert "KV cache is full" in str(err.value)
+    assert engine.seq_pos(1) == (0, 31)                      # the refused step left nothing behind
+    engine.seq_rm(0)
+    engine.step([rb.StepRow(1, 1, _prompt(3, 16), 32)], out)
+    assert engine.memory().cells_used == 48
+    engine.close()
+
+
+def test_prefix_copy_continuation_equals_cold_and_oracle(rb, oracle, pair):
+    """seq_cp is metadata-only (shared blocks + copy-on-write of the boundary block) and a
+    continuation after it is bit-identical to a cold prefill (tests/engine_runtime.rs:822-998)."""
+    engine, octx = pair
+    out = rb.StepOutput()
+    rep = ParityReport()
+    g = rb.SamplingParamsV2.greedy()
+    prompt = _prompt(11, 53)
+    check_step(rb, engine, octx, oracle, [rb.StepRow(0, 0, prompt[:37], 0)], out, rep)
+    blocks_before = engine.blocks()[0]
+    engine.seq_cp(0, 1, 0, 37)
+    octx.seq_cp(0, 1, 0, 37)
+    assert engine.blocks()[0] == blocks_before                       # nothing copied yet
+    assert engine.seq_pos(1) == (0, 36) and engine.memory().cells_used == 74
+    t0, _ = engine.block_table(0)
+    t1, _ = engine.block_table(1)
+    assert np.array_equal(t0, t1)
+    toks = check_step(rb, engine, octx, oracle, [rb.StepRow(1, 1, prompt[37:], 37, sample=True, sampling=g)], out, rep)
+    expect_greedy(oracle, toks, rep)
+    warm = engine.last_logits(0)
+    t1b, _ = engine.block_table(1)
+    assert t1b[2] != t0[2] and np.array_equal(t1b[:2], t0[:2])        # boundary block copied, full blocks shared
+    # the source continues independently with other tokens
+    toks = check_step(rb, engine, octx, oracle, [rb.StepRow(2, 0, _prompt(12, 5), 37, sample=True, sampling=g)], out, rep)
+    expect_greedy(oracle, toks, rep)
+    # cold run of the whole prompt in a fresh slot
+    check_step(rb, engine, octx, oracle, [rb.StepRow(3, 2, prompt, 0, sample=True, sampling=g)], out, rep)
+    cold = engine.last_logits(0)
+    assert np.array_equal(warm, cold)
+
+
+def test_seq_rm_ranges_and_memory_accounting(rb, oracle, pair):
+    engine, octx = pair
+    out = rb.StepOutput()
+    rep = ParityReport()
+    g = rb.SamplingParamsV2.greedy()
+    prompt = _prompt(21, 40)
+    check_step(rb, engine, octx, oracle, [rb.StepRow(0, 0, prompt, 0)], out, rep)
+    info = engine.memory()
+    assert (info.n_slots, info.cells_total, info.cells_used, info.recurrent_bytes) == (8, 1024, 40, 0) and info.kv_bytes > 0
+    engine.seq_rm(0, 30, -1)
+    octx.seq_rm(0, 30, -1)
+    assert engine.seq_pos(0) == (0, 29)
+    with pytest.raises(rb.EngineError) as err:
+        engine.seq_rm(0, 5, 9)
+    assert str(err.value) == "the memory cannot remove that partial range; remove the whole sequence instead"
+    # re-decode the tail: same logits as an uninterrupted run
+    toks = check_step(rb, engine, octx, oracle, [rb.StepRow(0, 0, prompt[30:], 30, sample=True, sampling=g)], out, rep)
+    expect_greedy(oracle, toks, rep)
+    again = engine.last_logits(0)
+    check_step(rb, engine, octx, oracle, [rb.StepRow(1, 1, prompt, 0, sample=True, sampling=g)], out, rep)
+    assert np.array_equal(again, engine.last_logits(0))
+    engine.seq_rm(0)
+    assert engine.seq_pos(0) == (-1, -1)
+    engine.seq_rm(0)   # removing an empty slot is fine
+
+
+def test_snapshot_round_trip(rb, oracle, pair):
+    """seq_save / seq_load: two-call size contract, bit-identical continuation, corrupt or
+    truncated data refused (tests/engine_runtime.rs:907-943)."""
+    engine, octx = pair
+    out = rb.StepOutput()
+    g = rb.SamplingParamsV2.greedy()
+    prompt = _prompt(31, 45)
+    engine.step([rb.StepRow(0, 0, prompt[:33], 0)], out)
+    blob = engine.seq_save(0)
+    engine.step([rb.StepRow(0, 0, prompt[33:], 33, sample=True, sampling=g)], out)
+    direct = engine.last_logits(0)
+    assert engine.seq_load(5, blob) == len(blob)
+    assert engine.seq_pos(5) == (0, 32)
+    engine.step([rb.StepRow(1, 5, prompt[33:], 33, sample=True, sampling=g)], out)
+    assert np.array_equal(direct, engine.last_logits(0))
+    bad = bytearray(blob)
+    bad[-1] ^= 0xFF
+    for data in (bytes(bad), blob[: len(blob) // 2], b"junk"):
+        with pytest.raises(rb.EngineError) as err:
+            engine.seq_load(6, data)
+        assert str(err.value) == "the snapshot was refused (wrong size, flags or corrupted data)"
+    assert engine.seq_pos(6) == (-1, -1)
+    with pytest.raises(rb.EngineError):
+        engine.seq_save(0, flags=2)   # ON_DEVICE snapshots are refused
+
+
+def test_logprobs_and_top_logprobs_match_the_oracle(rb, oracle, pair):
+    engine, octx = pair
+    out = rb.StepOutput()
+    rows = [rb.StepRow(i, i, _prompt(40 + i, 12 + i), 0, sample=True, sampling=rb.SamplingParamsV2.from_v1(rb.SamplingParams(1e-4, 1e-6, 1, 0)), n_top_logprobs=5) for i in range(3)]
+    engine.step(rows, out)
+    for r in range(3):
+        logits = engine.last_logits(r)
+        o = out.row(r)
+        assert o.token == int(np.argmax(logits)) and o.n_top == 5
+        assert o.logprob == oracle.token_logprob(logits, o.token)
+        ids, lps = out.top(r)
+        want_ids, want_lps = oracle.top_token_logprobs(logits, 5)
+        assert np.array_equal(ids, want_ids)
+        assert np.allclose(lps, want_lps, rtol=0, atol=2e-6)
+
+
+def test_seeded_sampling_is_reproducible_and_matches_its_restatement(rb, oracle, c1_model):
+    """Seeded rows draw from a counter-based generator: same seed -> same stream; the token equals
+    the CPU restatement of the same draw unless the draw sits on a rounding boundary."""
+    def run(seed, temperature, top_p):
+        engine = rb.Engine(str(c1_model), rb.EngineConfig(n_ctx=512, n_seq_max=4, n_batch=64, n_ubatch=64))
+        out = rb.StepOutput()
+        sp = rb.SamplingParamsV2(temperature=temperature, top_p=top_p, seed=seed)
+        prompt = _prompt(50, 20)
+        engine.step([rb.StepRow(0, 0, prompt, 0, sample=True, sampling=sp)], out)
+        stream, checks = [], []
+        for i in range(24):
+            o = out.row(0)
+            logits = engine.last_logits(0)
+            want, margin = oracle.sample_philox(logits, temperature, top_p, seed, i)
+            checks.append((o.token, want, margin))
+            assert o.logprob == pytest.approx(float(oracle.token_logprob(logits, o.token)), abs=2e-6)
+            stream.append(o.token)
+            engine.step([rb.StepRow.decode(0, 0, o.token, len(prompt) + i, sp)], out)
+        engine.close()
+        return stream, checks
+
+    for temperature, top_p in ((1.0, 1.0), (0.8, 0.9), (1.3, 0.5)):
+        a, checks = run(7, temperature, top_p)
+        b, _ = run(7, temperature, top_p)
+        c, _ = run(8, temperature, top_p)
+        assert a == b and a != c
+        assert len(set(a)) > 4
+        for got, want, margin in checks:
+            assert got == want or margin < 1e-9, (got, want, margin)
+
+
+def test_nucleus_and_top_k_restrict_the_support(rb, oracle, pair):
+    engine, _ = pair
+    out = rb.StepOutput()
+    prompt = _prompt(60, 16)
+    engine.step([rb.StepRow(0, 0, prompt, 0, sample=True, sampling=rb.SamplingParamsV2.greedy())], out)
+    logits = engine.last_logits(0)
+    order = np.argsort(-logits, kind="stable")
+    p = np.exp((logits.astype(np.float64) - logits.max()))
+    p /= p.sum()
+    for trial in range(40):
+        engine.seq_rm(0)
+        sp = rb.SamplingParamsV2(temperature=1.0, top_p=0.02, seed=trial)
+        engine.step([rb.StepRow(100 + trial, 0, prompt, 0, sample=True, sampling=sp, want_logprob=True, n_top_logprobs=3)], out)
+        n_keep = int(np.searchsorted(np.cumsum(p[order]), 0.02 * (1 - 1e-12)) + 1)
+        assert out.row(0).token in set(order[: n_keep + 1].tolist())
+        ids, lps = out.top(0)
+        assert ids[0] == order[0] and np.all(np.diff(lps) <= 0)
+        engine.seq_rm(0)
+        sp = rb.SamplingParamsV2(temperature=1.5, top_k=4, seed=trial)
+        engine.step([rb.StepRow(200 + trial, 0, prompt, 0, sample=True, sampling=sp)], out)
+        assert out.row(0).token in set(order[:4].tolist())
+
+
+def test_v2_bias_and_penalties_match_the_oracle_when_greedy(rb, oracle, pair):
+    """v2 order logit_bias -> penalties(window) -> top_k (retro_lora_train.h:1364-1369): with
+    top_k = 1 the draw is deterministic, so token, policy logprob, post-transformation logprob
+    and top ids must equal the reference's CPU oracle on the same raw logits."""
+    engine, _ = pair
+    out = rb.StepOutput()
+    prompt = _prompt(70, 10)
+    sp = rb.SamplingParamsV2(top_k=1, repeat_penalty=1.3, frequency_penalty=0.4, presence_penalty=0.2, penalty_window=6,
+                             logit_bias=[(77, 3.0), (78, -2.0), (77, 1.5)])
+    engine.step([rb.StepRow(0, 0, prompt, 0, sample=True, sampling=sp, want_logprob=True, n_top_logprobs=2)], out)
+    history = []
+    for i in range(12):
+        o = out.row(0)
+        logits = engine.last_logits(0)
+        tok, lp, slp, ids, lps = oracle.sample_token_v2(logits, oracle.Rng(0), top_k=1, repeat_penalty=1.3, frequency_penalty=0.4,
+                                                        presence_penalty=0.2, penalty_window=6, logit_bias=list(sp.logit_bias),
+                                                        history=history, k=2)
+        assert o.token == tok
+        assert o.logprob == pytest.approx(lp, abs=2e-6)
+        assert o.sampled_logprob == pytest.approx(slp, abs=1e-6)
+        got_ids, got_lps = out.top(0)
+        assert list(got_ids) == list(ids)
+        assert got_lps[0] == pytest.approx(float(lps[0]), abs=1e-6) and got_lps[1] == -np.inf
+        history.append(o.token)
+        engine.step([rb.StepRow.decode(0, 0, o.token, len(prompt) + i, sp, ) if False else
+                     rb.StepRow(0, 0, [o.token], len(prompt) + i, sample=True, sampling=sp, want_logprob=True, n_top_logprobs=2)], out)
+
+
+def test_min_p_and_temperature_v2_rows_stay_inside_the_kept_set(rb, oracle, pair):
+    engine, _ = pair
+    out = rb.StepOutput()
+    prompt = _prompt(71, 14)
+    engine.step([rb.StepRow(0, 0, prompt, 0, sample=True, sampling=rb.SamplingParamsV2.greedy())], out)
+    logits = engine.last_logits(0)
+    keep = set(np.nonzero(logits >= logits.max() + np.log(np.float32(0.5)))[0].tolist())
+    for trial in range(30):
+        engine.seq_rm(0)
+        sp = rb.SamplingParamsV2(temperature=2.0, min_p=0.5, seed=trial)
+        engine.step([rb.StepRow(300 + trial, 0, prompt, 0, sample=True, sampling=sp, want_logprob=True)], out)
+        assert out.row(0).token in keep
+        assert out.row(0).sampled_logprob <= 0.0

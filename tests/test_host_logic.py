@@ -1,0 +1,119 @@
+"""Host-side logic that needs no GPU: the C-ABI surface, config validation, the KV bookkeeping."""
+import ctypes as C
+import re
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol(rb):
+    header = (ROOT / "include" / "retro_b200.h").read_text()
+    declared = set(re.findall(r"\b(retro_(?:b200_)?[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 39
+    lib = rb.load_library()
+    from retrograd_b200 import _ffi
+
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+        assert name in _ffi.SYMBOLS, f"{name} has no ctypes binding"
+
+
+def test_struct_layouts_match_the_published_header(rb):
+    """Sizes pinned by crates/retrograd-ffi/src/lib.rs:2899-3052."""
+    from retrograd_b200 import _ffi as F
+
+    assert C.sizeof(F.EngineConfigC) == 64 and F.EngineConfigC.kv_unified.offset == 40 and F.EngineConfigC.expert_device_cache_bytes.offset == 56
+    assert C.sizeof(F.SamplingParamsC) == 16
+    assert C.sizeof(F.StepRowC) == 64 and F.StepRowC.sampling.offset == 36 and F.StepRowC.adapter.offset == 56
+    assert C.sizeof(F.StepOutRowC) == 20 and F.StepOutRowC.sampled.offset == 17
+    assert C.sizeof(F.SamplingParamsV2C) == 72 and F.SamplingParamsV2C.grammar.offset == 64
+    assert C.sizeof(F.StepRowV2C) == 128 and F.StepRowV2C.sampling.offset == 40 and F.StepRowV2C.adapter.offset == 120
+    assert C.sizeof(F.StepOutRowV2C) == 24 and F.StepOutRowV2C.sampled_logprob.offset == 20
+    assert C.sizeof(F.MemoryInfoC) == 40
+    assert C.sizeof(F.AdapterRowsInfoC) == 32
+
+
+def _new(rb, path, **over):
+    cfg = rb.EngineConfig(**over).to_c()
+    lib = rb.load_library()
+    h = lib.retro_engine_new(path, C.byref(cfg))
+    return h, (lib.retro_last_error() or b"").decode()
+
+
+def test_engine_config_is_validated_before_anything_loads(rb):
+    """Messages of crates/retrograd-ffi/runtime/src/retro_engine.cpp:112-153,469-483."""
+    lib = rb.load_library()
+    assert not lib.retro_engine_new(None, None)
+    assert lib.retro_last_error().decode() == "model_path is required"
+    h, msg = _new(rb, b"/nonexistent.gguf", n_ctx=0)
+    assert not h and msg == "engine n_ctx and n_seq_max must be greater than zero"
+    h, msg = _new(rb, b"/nonexistent.gguf", n_ubatch=1024, n_batch=512)
+    assert not h and msg == "engine n_ubatch must be in (0, n_batch]"
+    h, msg = _new(rb, b"/nonexistent.gguf", n_seq_max=600, n_batch=512)
+    assert not h and msg == "engine n_seq_max must not exceed LLAMA_MAX_SEQ, n_batch or n_ctx"
+    h, msg = _new(rb, b"/nonexistent.gguf", kv_dtype=9)
+    assert not h and msg == "engine kv_dtype must be one of retro_engine_kv_dtype"
+    h, msg = _new(rb, b"/nonexistent.gguf", kv_dtype=2, flash_attn=False)
+    assert not h and msg == "a quantized engine kv_dtype requires flash_attn"
+    h, msg = _new(rb, b"/nonexistent.gguf", device=7)
+    assert not h and msg == "engine device must be one of retro_device"
+    cfg = rb.EngineConfig().to_c()
+    cfg.struct_size = 8
+    assert not lib.retro_engine_new(b"/nonexistent.gguf", C.byref(cfg))
+    assert lib.retro_last_error().decode() == "retro_engine_config.struct_size is too small for this build"
+
+
+def test_there_is_no_cpu_path(rb, c1_model):
+    """device=cpu is refused, and without a CUDA device the constructor fails loudly."""
+    h, msg = _new(rb, str(c1_model).encode(), device=1)
+    assert not h and "only runs on a CUDA GPU" in msg
+    import torch
+
+    if not torch.cuda.is_available():
+        with pytest.raises(rb.EngineError):
+            rb.Engine(str(c1_model))
+
+
+def test_null_handles_are_refused(rb):
+    lib = rb.load_library()
+    v = C.c_uint32()
+    assert lib.retro_engine_vocab_size(None, C.byref(v)) == -1
+    assert lib.retro_last_error().decode() == "engine handle is null"
+    lib.retro_engine_free(None)
+
+
+def test_synth_rejects_unknown_keys(rb, tmp_path):
+    with pytest.raises(rb.EngineError):
+        rb.synth_gguf(tmp_path / "x.gguf", bogus=1)
+
+
+def test_synth_models_are_deterministic_and_readable(rb, tmp_path, oracle):
+    a, b = tmp_path / "a.gguf", tmp_path / "b.gguf"
+    spec = dict(arch="llama", layers=1, d=256, heads=4, kv_heads=2, ff=512, vocab=512, dtype="q4_k", seed=5)
+    rb.synth_gguf(a, **spec)
+    rb.synth_gguf(b, **spec)
+    assert a.read_bytes() == b.read_bytes()
+    rb.synth_gguf(b, **{**spec, "seed": 6})
+    assert a.read_bytes() != b.read_bytes()
+    m = oracle.Model(str(a))
+    assert (m.n_layer, m.d, m.n_head, m.n_head_kv, m.head_dim, m.ff, m.vocab) == (1, 256, 4, 2, 64, 512, 512)
+
+
+@pytest.mark.parametrize("ggml_type,rel", [(8, 0.01), (12, 0.12), (39, 0.3)])
+def test_encoders_round_trip_within_their_step(rb, oracle, ggml_type, rel):
+    import numpy as np
+
+    x = np.random.default_rng(ggml_type).normal(0, 0.02, 1024).astype(np.float32)
+    raw = rb.quantize_row(ggml_type, x)
+    y = oracle.dequantize_row(ggml_type, raw, x.size)
+    assert np.abs(x - y).max() <= rel * np.abs(x).max()
+
+
+def test_kv_bookkeeping(tmp_path):
+    exe = tmp_path / "kv_manager_test"
+    subprocess.run(["g++", "-std=c++17", "-O1", "-o", str(exe), str(ROOT / "tests" / "cpp" / "kv_manager_test.cpp")], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr

@@ -1,0 +1,60 @@
+"""The oracle's step semantics: batch order, sequence memory, MoE routing known answer."""
+import numpy as np
+
+from conftest import GOLDEN
+
+
+def test_pack_follows_the_reference_batch_order(oracle):
+    """Row-major over rows, tokens in row order, the last token of a sampling row is its output
+    (crates/retrograd-ffi/runtime/src/retro_gen_core.cpp:2579-2603)."""
+    maps = oracle.pack([(3, 1, 17, True), (0, 4, 0, False), (5, 2, 9, True), (1, 1, 2, True)])
+    assert list(maps["tok_slot"]) == [3, 0, 0, 0, 0, 5, 5, 1]
+    assert list(maps["tok_pos"]) == [17, 0, 1, 2, 3, 9, 10, 2]
+    assert list(maps["tok_row"]) == [0, 1, 1, 1, 1, 2, 2, 3]
+    assert list(maps["out_index"]) == [0, 6, 7]
+    assert list(maps["cu_rows"]) == [0, 1, 5, 7, 8]
+
+
+def test_chunked_prefill_equals_one_shot_prefill(oracle, c1_model):
+    m = oracle.Model(str(c1_model))
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(3, 4096, 40).tolist()
+    a = oracle.Context(m, 2, 256)
+    one = a.step([(0, prompt, 0, True)])[0]
+    b = oracle.Context(m, 2, 256)
+    b.step([(0, prompt[:13], 0, False)])
+    b.step([(0, prompt[13:29], 13, False)])
+    two = b.step([(0, prompt[29:], 29, True)])[0]
+    assert np.abs(one - two).max() < 1e-5
+    assert int(np.argmax(one)) == int(np.argmax(two))
+
+
+def test_seq_cp_then_continue_equals_cold(oracle, c1_model):
+    m = oracle.Model(str(c1_model))
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(3, 4096, 30).tolist()
+    ctx = oracle.Context(m, 4, 256)
+    ctx.step([(0, prompt[:20], 0, False)])
+    assert ctx.seq_pos(0) == (0, 19)
+    assert ctx.seq_cp(0, 1, 0, 20) == 0
+    assert ctx.seq_pos(1) == (0, 19)
+    warm = ctx.step([(1, prompt[20:], 20, True)])[0]
+    cold = oracle.Context(m, 4, 256).step([(0, prompt, 0, True)])[0]
+    assert np.array_equal(warm, cold)
+    assert ctx.seq_rm(1, 25, -1) == 0 and ctx.seq_pos(1) == (0, 24)
+    assert ctx.seq_rm(1, 5, 10) == -1          # a hole is refused
+    assert ctx.seq_rm(1, -1, -1) == 0 and ctx.seq_pos(1) == (-1, -1)
+
+
+def test_moe_fixture_routes_every_token_to_experts_0_and_1(oracle):
+    """Known answer of the concentrated tiny OLMoE: every token selects experts {0, 1}
+    (scripts/gen-tiny-moe-fixture.py:177-190; tests/expert_placement.rs:379-425 expects counts
+    [n, n, 0, 0, 0, 0, 0, 0] in every bank)."""
+    m = oracle.Model(str(GOLDEN / "retrograd-tiny-olmoe-f32.gguf"))
+    ctx = oracle.Context(m, 1, 64)
+    prompt = [1] + [3 + b for b in b"The quick brown fox"][:8]
+    ctx.step([(0, prompt, 0, True)])
+    routes = ctx.last_routes().reshape(m.n_layer, len(prompt), m.n_expert_used)
+    assert np.array_equal(np.sort(routes, axis=-1), np.broadcast_to([0, 1], routes.shape))
+    counts = np.bincount(routes[0].reshape(-1), minlength=8)
+    assert list(counts) == [len(prompt), len(prompt), 0, 0, 0, 0, 0, 0]
