@@ -157,19 +157,32 @@ def test_snapshot_round_trip(rb, oracle, pair):
 
 
 def test_logprobs_and_top_logprobs_match_the_oracle(rb, oracle, pair):
+    """v1 rows report the raw temperature-1 top-k (logit desc, id asc); v2 rows report the top-k of
+    the post-transformation distribution, truncated to the nucleus (retro_lora_train.h:1364-1369)."""
     engine, octx = pair
+    sp = rb.SamplingParamsV2.from_v1(rb.SamplingParams(1e-4, 1e-6, 1, 0))
+    rows = [rb.StepRow(i, i, _prompt(40 + i, 12 + i), 0, sample=True, sampling=sp, n_top_logprobs=5) for i in range(3)]
+    outs, ids, lps = engine.step_v1(rows, out_stride=6)
+    for r in range(3):
+        logits = engine.last_logits(r)
+        o = outs[r]
+        assert o.token == int(np.argmax(logits)) and o.n_top == 5
+        assert o.logprob == oracle.token_logprob(logits, o.token)
+        want_ids, want_lps = oracle.top_token_logprobs(logits, 5)
+        assert np.array_equal(ids[r, :5], want_ids)
+        assert np.allclose(lps[r, :5], want_lps, rtol=0, atol=2e-6)
+    for i in range(3):
+        engine.seq_rm(i)
+        engine.request_free(i)
     out = rb.StepOutput()
-    rows = [rb.StepRow(i, i, _prompt(40 + i, 12 + i), 0, sample=True, sampling=rb.SamplingParamsV2.from_v1(rb.SamplingParams(1e-4, 1e-6, 1, 0)), n_top_logprobs=5) for i in range(3)]
     engine.step(rows, out)
     for r in range(3):
         logits = engine.last_logits(r)
+        tok, lp, slp, want_ids, want_lps = oracle.sample_token_v2(logits, oracle.Rng(0), temperature=1e-4, top_p=1e-6, k=5)
         o = out.row(r)
-        assert o.token == int(np.argmax(logits)) and o.n_top == 5
-        assert o.logprob == oracle.token_logprob(logits, o.token)
-        ids, lps = out.top(r)
-        want_ids, want_lps = oracle.top_token_logprobs(logits, 5)
-        assert np.array_equal(ids, want_ids)
-        assert np.allclose(lps, want_lps, rtol=0, atol=2e-6)
+        got_ids, got_lps = out.top(r)
+        assert o.token == tok and o.logprob == pytest.approx(lp, abs=2e-6)
+        assert np.array_equal(got_ids, want_ids) and np.array_equal(got_lps, want_lps)
 
 
 def test_seeded_sampling_is_reproducible_and_matches_its_restatement(rb, oracle, c1_model):
