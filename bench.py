@@ -1,0 +1,422 @@
+#!/usr/bin/env python3
+"""Benchmark of the batched decode step: decode tokens/s on the Llama-3-8B-shape Q4_K ragged workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload c2|c1]
+
+One "step" is one scheduler step of continuous batching: every live request's decode row plus
+chunked-prefill rows (512-token chunks) of newly admitted requests, through `retro_engine_step_v2`
+of libretro_b200 with HOST buffers. Model weights and prompts are synthetic: a seeded random
+8B-shape GGUF quantised to Q4_K, prompts of uniform-random token ids with log-uniform lengths
+64..4096, output lengths uniform 64..512 (no data set is involved).
+
+Printed keys beyond the base contract:
+  value        decode tokens / device time of the K timed steps (CUDA events around each step's
+               kernels; the few-KB plan is already in HBM when the timed region starts)
+  e2e          the same tokens / wall time of the K `retro_engine_step_v2` calls, host plan in,
+               sampled rows out (host<->device copies inside the timed region)
+  roofline     the dominant kernel class of the timed region, timed live with CUDA events on the
+               launching stream, against the measured peak of MEASURED_PEAKS.json
+  cpu_baseline the CPU oracle timed on this host's cores on a bounded sample (N=1, rank 0)
+
+`--impl reference` times the reference's CPU path for the same metric. The reference itself cannot
+be built in this image (no Rust toolchain, and its compute library is an un-vendored submodule), so
+the arm runs the CPU restatement under oracle/ with every host thread on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # BASELINE config 2
+    "c2": dict(
+        name="llama3-8b-shape Q4_K, 256 ragged requests, continuous batching, 512-token prefill chunks",
+        spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
+        n_requests=256, prompt=(64, 4096), output=(64, 512), chunk=512, n_batch=2048, n_ctx=420_000,
+    ),
+    # BASELINE config 1 (CPU-runnable shape; used to exercise this script quickly)
+    "c1": dict(
+        name="tiny llama-style Q8_0, 8 requests",
+        spec=dict(arch="llama", layers=2, d=256, heads=4, kv_heads=4, ff=688, vocab=4096, dtype="q8_0", seed=20261125),
+        n_requests=8, prompt=(48, 160), output=(32, 64), chunk=64, n_batch=128, n_ctx=4096,
+    ),
+}
+
+
+def model_path(workload: str) -> Path:
+    base = Path(os.environ.get("RB200_MODEL_DIR", "/dev/shm" if Path("/dev/shm").is_dir() else "/tmp"))
+    return base / f"retrograd_b200_{workload}.gguf"
+
+
+def ensure_model(workload: str, rank: int) -> Path:
+    import retrograd_b200 as rb
+
+    path = model_path(workload)
+    done = path.with_suffix(".done")
+    if rank == 0 and not done.exists():
+        rb.synth_gguf(path, **WORKLOADS[workload]["spec"])
+        done.write_text("ok")
+    while not done.exists():
+        time.sleep(0.5)
+    return path
+
+
+class Request:
+    __slots__ = ("rid", "prompt", "n_out", "slot", "pos", "done", "last", "times")
+
+    def __init__(self, rid, prompt, n_out):
+        self.rid, self.prompt, self.n_out = rid, prompt, n_out
+        self.slot, self.pos, self.done, self.last, self.times = -1, 0, 0, None, []
+
+
+class Workload:
+    """Seeded open-loop request source: a new request is ready whenever a slot frees."""
+
+    def __init__(self, cfg, seed):
+        self.cfg = cfg
+        self.rng = np.random.default_rng(seed)
+        self.next_id = 0
+        self.vocab = cfg["spec"]["vocab"]
+
+    def request(self, midflight: bool = False) -> Request:
+        lo, hi = self.cfg["prompt"]
+        n_prompt = int(round(math.exp(self.rng.uniform(math.log(lo), math.log(hi)))))
+        n_out = int(self.rng.integers(self.cfg["output"][0], self.cfg["output"][1] + 1))
+        if midflight:
+            # a request caught in the middle of its generation: the tokens it already produced
+            # are part of what has to be resident
+            produced = int(self.rng.integers(0, n_out))
+            n_prompt += produced
+            n_out -= produced
+        prompt = self.rng.integers(3, self.vocab, n_prompt, dtype=np.int32)
+        r = Request(self.next_id, prompt, max(n_out, 1))
+        self.next_id += 1
+        return r
+
+
+class Driver:
+    """Continuous batching as the reference's scheduler composes a step
+    (crates/retrograd-infer/src/scheduler.rs:933-1089): decode rows first, then prefill chunks of
+    at most `chunk` tokens per request while the step's token budget lasts."""
+
+    def __init__(self, rb, engine, cfg, workload, sampling):
+        self.rb, self.engine, self.cfg, self.wl, self.sampling = rb, engine, cfg, workload, sampling
+        self.free_slots = list(range(cfg["n_requests"]))[::-1]
+        self.live: list[Request] = []
+        self.out = rb.StepOutput(cfg["n_batch"], 0)
+        self.reserved = 0
+
+    def admit(self, midflight=False):
+        while self.free_slots:
+            r = self.wl.request(midflight)
+            need = len(r.prompt) + r.n_out
+            if self.reserved + need > self.cfg["n_ctx"]:
+                break
+            self.reserved += need
+            r.slot = self.free_slots.pop()
+            self.live.append(r)
+
+    def compose(self):
+        rb = self.rb
+        rows, kinds, budget = [], [], self.cfg["n_batch"]
+        for r in self.live:
+            if r.last is not None and budget > 0:
+                rows.append(rb.StepRow(r.rid, r.slot, [r.last], len(r.prompt) + r.done - 1, True, self.sampling))
+                kinds.append(r)
+                budget -= 1
+        for r in self.live:
+            if r.last is None and budget > 0:
+                take = min(budget, self.cfg["chunk"], len(r.prompt) - r.pos)
+                final = r.pos + take == len(r.prompt)
+                rows.append(rb.StepRow(r.rid, r.slot, r.prompt[r.pos : r.pos + take], r.pos, final, self.sampling))
+                kinds.append(r)
+                budget -= take
+        return rows, kinds
+
+    def step(self, now=None):
+        rows, reqs = self.compose()
+        if not rows:
+            return dict(decode=0, prefill=0, sampled=0, rows=rows)
+        self.engine.step(rows, self.out)
+        wall = self.engine.last_call_s
+        stamp = time.perf_counter()
+        n_decode = n_prefill = sampled = 0
+        ctx_tokens = 0
+        for i, (row, r) in enumerate(zip(rows, reqs)):
+            n = len(row.tokens)
+            if r.last is None:
+                r.pos += n
+                n_prefill += n
+            else:
+                n_decode += 1
+            ctx_tokens += row.pos0 * n + n * (n + 1) // 2
+            if row.sample:
+                r.last = self.out.row(i).token
+                r.done += 1
+                r.times.append(stamp)
+                sampled += 1
+        finished = [r for r in self.live if r.done >= r.n_out]
+        for r in finished:
+            self.engine.seq_rm(r.slot)
+            self.engine.request_free(r.rid)
+            self.free_slots.append(r.slot)
+            self.reserved -= len(r.prompt) + r.n_out
+            self.live.remove(r)
+        return dict(decode=n_decode, prefill=n_prefill, sampled=sampled, wall=wall, tokens=n_decode + n_prefill,
+                    ctx_tokens=ctx_tokens, finished=finished, rows=rows)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag = index, [], threading.Event()
+
+    def run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.2)
+
+    def summary(self):
+        mhz = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        reasons = set()
+        for s in self.samples:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        max_mhz = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(max_mhz) if max_mhz else None,
+                "reasons": sorted(reasons), "samples": len(self.samples)}
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def cpu_baseline(path: Path, cfg, steps: int = 2, rows: int = 8, prompt: int = 4):
+    """The CPU oracle (vectorised accumulation, all host threads) on a bounded sample: `rows`
+    concurrent requests, a `prompt`-token prefill each, then `steps` decode steps."""
+    from oracle import oracle as O
+
+    m = O.Model(str(path), fast=True)
+    ctx = O.Context(m, rows, 64)
+    rng = np.random.default_rng(1)
+    vocab = cfg["spec"]["vocab"]
+    logits = ctx.step([(i, rng.integers(3, vocab, prompt).tolist(), 0, True) for i in range(rows)])
+    times = []
+    for s in range(steps):
+        t0 = time.perf_counter()
+        logits = ctx.step([(i, [int(np.argmax(logits[i]))], prompt + s, True) for i in range(rows)])
+        times.append(time.perf_counter() - t0)
+    ctx.close()
+    m.close()
+    return rows / statistics.median(times), times
+
+
+def run_reference(args, cfg, rank, world):
+    """The reference's CPU path for the same metric: the CPU restatement with every host thread,
+    one bounded decode step per timed step."""
+    if rank != 0:
+        return
+    path = ensure_model(args.workload, 0)
+    from oracle import oracle as O
+
+    rows, prompt = 8, 4
+    m = O.Model(str(path), fast=True)
+    ctx = O.Context(m, rows, 64 + args.steps + args.warmup)
+    rng = np.random.default_rng(1)
+    vocab = cfg["spec"]["vocab"]
+    logits = ctx.step([(i, rng.integers(3, vocab, prompt).tolist(), 0, True) for i in range(rows)])
+    times = []
+    for s in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        logits = ctx.step([(i, [int(np.argmax(logits[i]))], prompt + s, True) for i in range(rows)])
+        if s >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = rows * len(times) / total
+    cores = os.cpu_count() or 1
+    sample = f"{rows} concurrent requests, {prompt}-token prompts, {len(times)} decode steps of the same GGUF"
+    print(json.dumps({
+        "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": cfg["name"], "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, cfg, rank, world)
+        return
+
+    import torch
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    import retrograd_b200 as rb
+    from retrograd_b200 import build as B
+
+    if rank == 0 and not rb.LIB_PATH.exists():
+        B.build()
+    if dist:
+        dist.barrier()
+    path = ensure_model(args.workload, local_rank if world > 1 else 0)
+    if dist:
+        dist.barrier()
+
+    engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=cfg["n_ctx"], n_seq_max=cfg["n_requests"], n_batch=cfg["n_batch"], n_ubatch=cfg["n_batch"]))
+    sampling = rb.SamplingParamsV2.greedy()
+    driver = Driver(rb, engine, cfg, Workload(cfg, seed=1000 + rank), sampling)
+
+    # ---- ramp (untimed): a steady-state snapshot - every slot holds a request caught mid-flight
+    driver.admit(midflight=True)
+    ramp_steps = 0
+    while any(r.last is None for r in driver.live):
+        driver.step()
+        ramp_steps += 1
+    for _ in range(args.warmup):
+        driver.step()
+        driver.admit()
+
+    # ---- timed region: exactly K steps
+    engine.profile(True, reset=True)
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    dev_ms, wall_s, decode_tokens, prefill_tokens, rows_per_step, launches, h2d, d2h = 0.0, 0.0, 0, 0, [], 0, 0, 0
+    attn_bytes = 0
+    gemm_flops = 0
+    kv_tok_bytes = 2 * cfg["spec"]["layers"] * cfg["spec"]["kv_heads"] * (cfg["spec"].get("head_dim") or cfg["spec"]["d"] // cfg["spec"]["heads"]) * 2
+    sp = cfg["spec"]
+    hd = sp.get("head_dim") or sp["d"] // sp["heads"]
+    w_elems_layer = sp["d"] * (sp["heads"] * hd + 2 * sp["kv_heads"] * hd) + sp["heads"] * hd * sp["d"] + 3 * sp["d"] * sp["ff"]
+    for _ in range(args.steps):
+        info = driver.step()
+        ms, n_launch = engine.last_step_stats()
+        a, b = engine.last_step_io()
+        dev_ms += ms
+        wall_s += info["wall"]
+        decode_tokens += info["sampled"]
+        prefill_tokens += info["prefill"]
+        rows_per_step.append(len(info["rows"]))
+        launches += n_launch
+        h2d += a
+        d2h += b
+        attn_bytes += info["ctx_tokens"] * kv_tok_bytes
+        gemm_flops += 2 * (info["tokens"] * w_elems_layer * sp["layers"] + info["sampled"] * sp["d"] * sp["vocab"])
+        driver.admit()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    clocks.stop_flag.set()
+    clocks.join()
+    profile = engine.profile_read()
+    engine.profile(False)
+
+    # inter-token gaps of every request that sampled more than once in the timed region
+    gaps = []
+    for r in driver.live:
+        t = r.times[-(args.steps + 1):]
+        gaps += [1e3 * (b - a) for a, b in zip(t, t[1:])]
+
+    stats = torch.tensor([dev_ms, wall_s, float(decode_tokens), float(prefill_tokens), float(launches)], dtype=torch.float64, device="cuda")
+    if dist:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        dev_ms, wall_s = float(mx[0]), float(mx[1])
+        decode_tokens, prefill_tokens, launches = float(sm[2]), float(sm[3]), float(sm[4])
+    if rank != 0:
+        engine.close()
+        return
+
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+    top = max(("gemm", "attention"), key=lambda k: profile[k]["ms"])
+    if top == "gemm":
+        achieved = gemm_flops / (profile["gemm"]["ms"] * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
+                "traffic": None, "kernel": "dequant-fused weight GEMM (all launches of the timed region)"}
+    else:
+        achieved = attn_bytes / (profile["attention"]["ms"] * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "traffic": None, "kernel": "paged ragged attention (all launches of the timed region)"}
+    roof["peak_source"] = f"of {peak_kind}"
+    roof["launches"] = profile[top]["launches"]
+    roof["avg_launch_ms"] = profile[top]["ms"] / max(profile[top]["launches"], 1)
+
+    line = {
+        "metric": "decode_tokens_per_s", "value": decode_tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": cfg["name"], "n_batch": cfg["n_batch"], "n_ctx": cfg["n_ctx"], "parallelism": f"replicas x{world}",
+                   "rows_per_step": statistics.mean(rows_per_step), "decode_tokens_per_step": decode_tokens / args.steps / world,
+                   "prefill_tokens_per_step": prefill_tokens / args.steps / world, "ramp_steps": ramp_steps,
+                   "l2": "inputs larger than L2: every step streams >4 GB of weights and the ragged KV"},
+        "e2e": {"value": decode_tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps},
+        "gpu_launches": int(launches),
+        "p50_inter_token_ms": statistics.median(gaps) if gaps else None,
+        "clocks": clocks.summary(),
+        "roofline": roof,
+        "kernel_classes_ms": {k: round(v["ms"], 3) for k, v in profile.items()},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        engine.close()
+        value, times = cpu_baseline(path, cfg)
+        line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                "sample": f"8 concurrent requests, 4-token prompts, {len(times)} decode steps of the same GGUF"}
+    else:
+        engine.close()
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

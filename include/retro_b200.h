@@ -246,6 +246,15 @@ int retro_b200_engine_blocks(retro_engine * engine, uint64_t * out_used, uint64_
  * of kernels it launched. */
 int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uint64_t * out_launches);
 
+/* Bytes the last step copied host->device (the plan) and device->host (the sampled rows). */
+int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes);
+/* Per-class kernel timing with CUDA events on the launching stream. Classes, in order:
+ * gemm, attention, sample, pack, moe, lora, other (RETRO_B200_PROFILE_CLASSES entries).
+ * `enabled` switches the bracketing on or off, `reset` clears the accumulated totals. */
+#define RETRO_B200_PROFILE_CLASSES 7
+int retro_b200_engine_profile(retro_engine * engine, int enabled, int reset);
+int retro_b200_engine_profile_read(retro_engine * engine, double * out_ms, uint64_t * out_launches, size_t n_classes);
+
 #ifdef __cplusplus
 }
 #endif

@@ -742,4 +742,40 @@ int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uin
     });
 }
 
+int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (out_h2d_bytes) *out_h2d_bytes = e->last_h2d_bytes;
+        if (out_d2h_bytes) *out_d2h_bytes = e->last_d2h_bytes;
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_profile(retro_engine * engine, int enabled, int reset) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        e->prof_.enabled = enabled != 0;
+        if (reset) e->prof_.reset();
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_profile_read(retro_engine * engine, double * out_ms, uint64_t * out_launches, size_t n_classes) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (n_classes < K_CLASS_COUNT) {
+            set_error("the profile buffers are too small");
+            return STATUS_BUFFER_TOO_SMALL;
+        }
+        for (int i = 0; i < K_CLASS_COUNT; ++i) {
+            if (out_ms) out_ms[i] = e->prof_.ms[i];
+            if (out_launches) out_launches[i] = e->prof_.launches[i];
+        }
+        return STATUS_OK;
+    });
+}
+
 } // extern "C"

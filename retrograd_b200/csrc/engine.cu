@@ -308,7 +308,9 @@ void Engine::flush_kv_updates() {
 
 void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual,
                     int ldr) {
+    prof_.begin(K_GEMM, stream);
     launch_gemm_rows(w, x, ldx, T, y, ldy, bias, residual, ldr, stream);
+    prof_.end(K_GEMM, 1, stream);
     ++last_launches;
 }
 
@@ -317,8 +319,10 @@ void Engine::lora(const std::string & target, const float * x, int ldx, int T, f
     auto it = lora_targets_.find(target);
     if (it == lora_targets_.end() || !it->second->present) return;
     LoraTarget & t = *it->second;
+    prof_.begin(K_LORA, stream);
     launch_lora_shrink(t.a.ptr, (int)r_max_, (int)t.n_in, cur_tok_adapter_, x, ldx, T, lora_tmp_.ptr, stream);
     launch_lora_expand(t.b.ptr, (int)r_max_, (int)t.n_out, lora_scales_.ptr, cur_tok_adapter_, lora_tmp_.ptr, T, y, ldy, stream);
+    prof_.end(K_LORA, 2, stream);
     last_launches += 2;
 }
 
@@ -649,33 +653,37 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
 
     // ---- device work
     last_launches = 0;
+    last_h2d_bytes = stage_total;
+    last_d2h_bytes = S ? res_total - 16 : 0;
     RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
     RB_CUDA(cudaEventRecord(ev_begin_, stream));
     const RowDesc * d_rows = reinterpret_cast<const RowDesc *>(d_stage_.ptr + off_rows);
     const int32_t * d_tokens = reinterpret_cast<const int32_t *>(d_stage_.ptr + off_tokens);
     const KvLayout kvl = kv_layout();
+#define RB_K(cls, n, ...)            \
+    do {                             \
+        prof_.begin(cls, stream);    \
+        __VA_ARGS__;                 \
+        prof_.end(cls, n, stream);   \
+        last_launches += (n);        \
+    } while (0)
     if (n_patches) {
-        launch_block_table_patch(block_table_.ptr, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_patches), n_patches, stream);
-        ++last_launches;
+        RB_K(K_OTHER, 1, launch_block_table_patch(block_table_.ptr, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_patches), n_patches, stream));
     }
     if (n_copies) {
-        launch_kv_block_copy(kvl, (int)hp.n_layer, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_copies), n_copies, stream);
-        ++last_launches;
+        RB_K(K_OTHER, 1, launch_kv_block_copy(kvl, (int)hp.n_layer, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_copies), n_copies, stream));
     }
-    launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, maps, stream);
-    last_launches += 2;
+    RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, maps, stream));
     cur_tok_adapter_ = maps.tok_adapter;
     cur_any_adapter_ = any_adapter;
 
     const int d = (int)hp.d, dq = (int)hp.dq(), dkv = (int)hp.dkv(), ldqkv = dq + 2 * dkv, ff = (int)hp.ff;
     const int Ti = (int)T;
-    launch_embed(model->token_embd, d_tokens, Ti, x_.ptr, stream);
-    ++last_launches;
+    RB_K(K_OTHER, 1, launch_embed(model->token_embd, d_tokens, Ti, x_.ptr, stream));
     for (uint32_t l = 0; l < hp.n_layer; ++l) {
         const LayerWeights & lw = model->layers[l];
         const std::string p = "blk." + std::to_string(l) + ".";
-        launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, xn_.ptr, d, Ti, stream);
-        ++last_launches;
+        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, xn_.ptr, d, Ti, stream));
         if (lw.wqkv.data) {
             linear(lw.wqkv, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0);
         } else {
@@ -689,19 +697,17 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             lora(p + "attn_v.weight", xn_.ptr, d, Ti, qkv_.ptr + dq + dkv, ldqkv);
         }
         if (lw.q_norm) {
-            launch_rms_norm(qkv_.ptr, ldqkv, nullptr, lw.q_norm, dq, hp.eps, qkv_.ptr, ldqkv, Ti, stream);
-            launch_rms_norm(qkv_.ptr + dq, ldqkv, nullptr, lw.k_norm, dkv, hp.eps, qkv_.ptr + dq, ldqkv, Ti, stream);
-            last_launches += 2;
+            RB_K(K_OTHER, 2, launch_rms_norm(qkv_.ptr, ldqkv, nullptr, lw.q_norm, dq, hp.eps, qkv_.ptr, ldqkv, Ti, stream);
+                 launch_rms_norm(qkv_.ptr + dq, ldqkv, nullptr, lw.k_norm, dkv, hp.eps, qkv_.ptr + dq, ldqkv, Ti, stream));
         }
-        launch_rope_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox, model->inv_freq.ptr,
-                          maps.tok_pos, maps.tok_cell, kvl, (int)l, stream);
-        launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, stream);
-        last_launches += 2;
+        RB_K(K_OTHER, 1, launch_rope_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox,
+                                           model->inv_freq.ptr, maps.tok_pos, maps.tok_cell, kvl, (int)l, stream));
+        RB_K(K_ATTN, 1, launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min,
+                                             att_.ptr, dq, stream));
         // x = x + Wo att
         linear(lw.wo, att_.ptr, dq, Ti, x_.ptr, d, nullptr, x_.ptr, d);
         if (any_adapter) lora(p + "attn_output.weight", att_.ptr, dq, Ti, x_.ptr, d);
-        launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, xn_.ptr, d, Ti, stream);
-        ++last_launches;
+        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, xn_.ptr, d, Ti, stream));
         if (hp.n_expert == 0) {
             if (lw.wgu.data) {
                 linear(lw.wgu, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0);
@@ -713,39 +719,36 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 lora(p + "ffn_gate.weight", xn_.ptr, d, Ti, gu_.ptr, 2 * ff);
                 lora(p + "ffn_up.weight", xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff);
             }
-            launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, hff_.ptr, ff, stream);
-            ++last_launches;
+            RB_K(K_OTHER, 1, launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, hff_.ptr, ff, stream));
             linear(lw.wdown, hff_.ptr, ff, Ti, x_.ptr, d, nullptr, x_.ptr, d);
             if (any_adapter) lora(p + "ffn_down.weight", hff_.ptr, ff, Ti, x_.ptr, d);
         } else {
             const int E = (int)hp.n_expert, K = (int)hp.n_expert_used, P = Ti * K;
             linear(lw.router, xn_.ptr, d, Ti, router_logits_.ptr, E, nullptr, nullptr, 0);
-            launch_moe_route(router_logits_.ptr, E, K, Ti, moe_ids_.ptr, moe_w_.ptr, stream);
+            RB_K(K_MOE, 1, launch_moe_route(router_logits_.ptr, E, K, Ti, moe_ids_.ptr, moe_w_.ptr, stream));
             RB_CUDA(cudaMemcpyAsync(route_ids.ptr + (size_t)l * P, moe_ids_.ptr, (size_t)P * 4, cudaMemcpyDeviceToDevice, stream));
-            launch_moe_gemm_rows(lw.gate_exps, lw.gate_stride, moe_ids_.ptr, xn_.ptr, d, K, P, pair_gu_.ptr, 2 * ff, stream);
-            launch_moe_gemm_rows(lw.up_exps, lw.up_stride, moe_ids_.ptr, xn_.ptr, d, K, P, pair_gu_.ptr + ff, 2 * ff, stream);
-            launch_swiglu(pair_gu_.ptr, 2 * ff, ff, P, pair_h_.ptr, ff, stream);
-            launch_moe_gemm_rows(lw.down_exps, lw.down_stride, moe_ids_.ptr, pair_h_.ptr, ff, 1, P, pair_y_.ptr, d, stream);
-            launch_moe_combine(pair_y_.ptr, d, moe_ids_.ptr, moe_w_.ptr, K, d, Ti, x_.ptr, x_.ptr, stream);
-            last_launches += 6;
+            RB_K(K_MOE, 2, launch_moe_gemm_rows(lw.gate_exps, lw.gate_stride, moe_ids_.ptr, xn_.ptr, d, K, P, pair_gu_.ptr, 2 * ff, stream);
+                 launch_moe_gemm_rows(lw.up_exps, lw.up_stride, moe_ids_.ptr, xn_.ptr, d, K, P, pair_gu_.ptr + ff, 2 * ff, stream));
+            RB_K(K_OTHER, 1, launch_swiglu(pair_gu_.ptr, 2 * ff, ff, P, pair_h_.ptr, ff, stream));
+            RB_K(K_MOE, 2, launch_moe_gemm_rows(lw.down_exps, lw.down_stride, moe_ids_.ptr, pair_h_.ptr, ff, 1, P, pair_y_.ptr, d, stream);
+                 launch_moe_combine(pair_y_.ptr, d, moe_ids_.ptr, moe_w_.ptr, K, d, Ti, x_.ptr, x_.ptr, stream));
         }
     }
     SampleOut * d_out = reinterpret_cast<SampleOut *>(d_result_.ptr);
     int32_t * d_top_ids = reinterpret_cast<int32_t *>(d_result_.ptr + res_ids);
     float * d_top_lps = reinterpret_cast<float *>(d_result_.ptr + res_lps);
     if (S) {
-        launch_rms_norm(x_.ptr, d, maps.out_index, model->output_norm, d, hp.eps, hs_.ptr, d, (int)S, stream);
-        ++last_launches;
+        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, maps.out_index, model->output_norm, d, hp.eps, hs_.ptr, d, (int)S, stream));
         linear(model->output, hs_.ptr, d, (int)S, logits.ptr, (int)hp.vocab, model->output_bias, nullptr, 0);
         if (any_v2) {
             RB_CUDA(cudaMemcpyAsync(logits_work_.ptr, logits.ptr, S * (size_t)hp.vocab * 4, cudaMemcpyDeviceToDevice, stream));
         }
-        launch_sample(logits.ptr, any_v2 ? logits_work_.ptr : nullptr, (int)hp.vocab, (int)S,
-                      reinterpret_cast<const SampleDesc *>(d_stage_.ptr + off_descs),
-                      reinterpret_cast<const LogitEdit *>(d_stage_.ptr + off_edits), d_out, d_top_ids, d_top_lps,
-                      (int)std::max<size_t>(top_stride, 1), stream);
-        ++last_launches;
+        RB_K(K_SAMPLE, 1, launch_sample(logits.ptr, any_v2 ? logits_work_.ptr : nullptr, (int)hp.vocab, (int)S,
+                                        reinterpret_cast<const SampleDesc *>(d_stage_.ptr + off_descs),
+                                        reinterpret_cast<const LogitEdit *>(d_stage_.ptr + off_edits), d_out, d_top_ids, d_top_lps,
+                                        (int)std::max<size_t>(top_stride, 1), stream));
     }
+#undef RB_K
     RB_CUDA(cudaEventRecord(ev_end_, stream));
     if (S) RB_CUDA(cudaMemcpyAsync(h_result_, d_result_.ptr, res_total - 16, cudaMemcpyDeviceToHost, stream));
     const cudaError_t sync = cudaStreamSynchronize(stream);
@@ -761,6 +764,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         return STATUS_RUNTIME;
     }
     cudaEventElapsedTime(&last_ms, ev_begin_, ev_end_);
+    prof_.collect();
     last_T = T;
     last_S = S;
     last_R = R;

@@ -35,6 +35,57 @@ template <class T> struct DeviceBuffer {
     }
 };
 
+// Kernel classes the optional per-step profile accumulates device time for.
+enum KernelClass { K_GEMM = 0, K_ATTN, K_SAMPLE, K_PACK, K_MOE, K_LORA, K_OTHER, K_CLASS_COUNT };
+
+// CUDA-event timing of kernel groups inside a step, on the stream the kernels are launched on.
+// Off by default; when on, every group is bracketed by two events and the elapsed times are
+// summed per class after the step's synchronisation.
+struct StepProfiler {
+    bool enabled = false;
+    std::vector<cudaEvent_t> pool;
+    size_t used = 0;
+    struct Span { int cls; size_t e0, e1; uint32_t launches; };
+    std::vector<Span> spans;
+    double ms[K_CLASS_COUNT] = {};
+    uint64_t launches[K_CLASS_COUNT] = {};
+    size_t open_event = 0;
+    ~StepProfiler() { for (cudaEvent_t e : pool) cudaEventDestroy(e); }
+    size_t take() {
+        if (used == pool.size()) {
+            cudaEvent_t e;
+            cudaEventCreate(&e);
+            pool.push_back(e);
+        }
+        return used++;
+    }
+    void begin(int, cudaStream_t stream) {
+        if (!enabled) return;
+        open_event = take();
+        cudaEventRecord(pool[open_event], stream);
+    }
+    void end(int cls, uint32_t n, cudaStream_t stream) {
+        if (!enabled) return;
+        const size_t e1 = take();
+        cudaEventRecord(pool[e1], stream);
+        spans.push_back({cls, open_event, e1, n});
+    }
+    void collect() {
+        for (const Span & s : spans) {
+            float t = 0.f;
+            if (cudaEventElapsedTime(&t, pool[s.e0], pool[s.e1]) == cudaSuccess) {
+                ms[s.cls] += t;
+                launches[s.cls] += s.launches;
+            }
+        }
+        spans.clear();
+        used = 0;
+    }
+    void reset() {
+        for (int i = 0; i < K_CLASS_COUNT; ++i) { ms[i] = 0; launches[i] = 0; }
+    }
+};
+
 struct HParams {
     std::string arch;
     uint32_t n_layer = 0, d = 0, n_head = 0, n_head_kv = 0, head_dim = 0, ff = 0, vocab = 0;
@@ -154,6 +205,8 @@ public:
     size_t last_T = 0, last_S = 0, last_R = 0;
     float last_ms = 0.f;
     uint64_t last_launches = 0;
+    uint64_t last_h2d_bytes = 0, last_d2h_bytes = 0;
+    StepProfiler prof_;
     uint64_t graphs_reused = 0;
     bool route_enabled = false;
     std::vector<std::vector<uint32_t>> route_counts;   // [layer][expert]

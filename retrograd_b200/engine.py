@@ -8,6 +8,7 @@ failed call, status -3 mapped to `InvalidArgument`, every other failure to `Engi
 from __future__ import annotations
 
 import ctypes as C
+import time
 from dataclasses import dataclass, field
 from typing import Iterable, Sequence
 
@@ -320,6 +321,7 @@ class Engine:
         if len(requests) != len(set(requests)):
             raise InvalidArgument("a request id appears twice in one step")
         any_top = out.n_top_stride > 0
+        t0 = time.perf_counter()
         status = self._lib.retro_engine_step_v2(
             self._h,
             c_rows,
@@ -329,6 +331,7 @@ class Engine:
             out._top_logprobs.ctypes.data_as(C.POINTER(C.c_float)) if any_top else None,
             out.n_top_stride,
         )
+        self.last_call_s = time.perf_counter() - t0   # wall time of the C call alone
         _check(status)
         out.n_rows = n
 
@@ -472,3 +475,19 @@ class Engine:
         ms, n = C.c_float(), C.c_uint64()
         _check(self._lib.retro_b200_engine_last_step_stats(self._h, C.byref(ms), C.byref(n)))
         return ms.value, n.value
+
+    def last_step_io(self) -> tuple[int, int]:
+        a, b = C.c_uint64(), C.c_uint64()
+        _check(self._lib.retro_b200_engine_last_step_io(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    PROFILE_CLASSES = ("gemm", "attention", "sample", "pack", "moe", "lora", "other")
+
+    def profile(self, enabled: bool, reset: bool = False) -> None:
+        _check(self._lib.retro_b200_engine_profile(self._h, int(enabled), int(reset)))
+
+    def profile_read(self) -> dict:
+        ms = (C.c_double * 7)()
+        n = (C.c_uint64 * 7)()
+        _check(self._lib.retro_b200_engine_profile_read(self._h, ms, n, 7))
+        return {name: {"ms": ms[i], "launches": n[i]} for i, name in enumerate(self.PROFILE_CLASSES)}
