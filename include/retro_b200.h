@@ -246,6 +246,13 @@ int retro_b200_engine_blocks(retro_engine * engine, uint64_t * out_used, uint64_
  * of kernels it launched. */
 int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uint64_t * out_launches);
 
+/* One dequant-fused GEMM on host data: y[t][o] = sum_k deq(w)[o][k] * x[t][k] with w stored as
+ * `ggml_type` rows. path: 0 engine's choice, 1 f32 row kernel, 2 single-term f16 tensor-core
+ * kernel, 3 exact tensor-core kernel. Runs `iters` timed launches after one warm-up; *out_ms is
+ * the mean device time per launch. */
+int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, uint32_t n_in, const float * x, uint32_t n_tokens, float * y,
+                       int path, uint32_t iters, float * out_ms);
+
 /* Bytes the last step copied host->device (the plan) and device->host (the sampled rows). */
 int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes);
 /* Per-class kernel timing with CUDA events on the launching stream. Classes, in order:

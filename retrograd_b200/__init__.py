@@ -17,6 +17,7 @@ from .engine import (
     SamplingParamsV2,
     StepOutput,
     StepRow,
+    op_gemm,
     quantize_row,
     synth_gguf,
 )
@@ -33,6 +34,7 @@ __all__ = [
     "StepOutput",
     "StepRow",
     "load_library",
+    "op_gemm",
     "quantize_row",
     "synth_gguf",
 ]

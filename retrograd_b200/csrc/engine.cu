@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 
@@ -233,7 +234,7 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     RB_CUDA(cudaMemsetAsync(block_table_.ptr, 0, block_table_.count * 4, stream));
 
     const size_t T = config.n_batch;
-    maps_store_.ensure(T * 7 + 2 * (T + 1));
+    maps_store_.ensure(T * 9 + 3 * (T + 1) + 8);
     int32_t * p = maps_store_.ptr;
     maps.cu_rows = p; p += T + 1;
     maps.out_rank = p; p += T + 1;
@@ -243,12 +244,23 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     maps.tok_cell = p; p += T;
     maps.tok_adapter = p; p += T;
     maps.tok_pos_min = p; p += T;
-    maps.out_index = p;
+    maps.out_index = p; p += T;
+    maps.tile_rank = p; p += T + 1;
+    p += (reinterpret_cast<uintptr_t>(p) & 7) ? 1 : 0;     // int2 alignment
+    maps.attn_items = reinterpret_cast<int2 *>(p);
+    attn_mma_ = attention_mma_supported((int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)kBlockTokens);
+    if (const char * env = std::getenv("RB200_ATTENTION")) attn_mma_ = attn_mma_ && std::string(env) != "ref";
+    attn_tile_tokens_ = attn_mma_ ? 64 / (int)(hp.n_head / hp.n_head_kv) : 64;
 
     x_.ensure(T * hp.d);
     xn_.ensure(T * hp.d);
     qkv_.ensure(T * (hp.dq() + 2 * hp.dkv()));
     att_.ensure(T * hp.dq());
+    xn_split_.ensure(T, hp.d);
+    att_split_.ensure(T, hp.dq());
+    if (hp.n_expert == 0) hff_split_.ensure(T, hp.ff);
+    if (const char * env = std::getenv("RB200_GEMM")) gemm_fast_f16 = std::string(env) == "fast";
+    if (const char * env = std::getenv("RB200_MMA_MIN_TOKENS")) mma_min_tokens = std::atoi(env);
     if (hp.n_expert == 0) {
         gu_.ensure(T * 2 * hp.ff);
         hff_.ensure(T * hp.ff);
@@ -307,9 +319,15 @@ void Engine::flush_kv_updates() {
 }
 
 void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual,
-                    int ldr) {
+                    int ldr, const SplitAct * xs) {
     prof_.begin(K_GEMM, stream);
-    launch_gemm_rows(w, x, ldx, T, y, ldy, bias, residual, ldr, stream);
+    if (xs && T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) {
+        launch_gemm_mma(w, xs->hi, ldx, T, y, ldy, bias, residual, ldr, stream);
+    } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {
+        launch_gemm_q4k_exact(w, *xs, T, y, ldy, bias, residual, ldr, stream);
+    } else {
+        launch_gemm_rows(w, x, ldx, T, y, ldy, bias, residual, ldr, stream);
+    }
     prof_.end(K_GEMM, 1, stream);
     ++last_launches;
 }
@@ -647,6 +665,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     if (S) {
         logits.ensure(S * (size_t)hp.vocab);
         hs_.ensure(S * (size_t)hp.d);
+        hs_split_.ensure(S, hp.d);
         if (any_v2) logits_work_.ensure(S * (size_t)hp.vocab);
     }
     if (any_adapter) lora_tmp_.ensure(T * (size_t)std::max<uint32_t>(r_max_, 1));
@@ -673,7 +692,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     if (n_copies) {
         RB_K(K_OTHER, 1, launch_kv_block_copy(kvl, (int)hp.n_layer, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_copies), n_copies, stream));
     }
-    RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, maps, stream));
+    RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, attn_tile_tokens_, maps, stream));
+    int n_attn_items = 0;
+    for (size_t r = 0; r < R; ++r) n_attn_items += ((int)rows[r].n + attn_tile_tokens_ - 1) / attn_tile_tokens_;
     cur_tok_adapter_ = maps.tok_adapter;
     cur_any_adapter_ = any_adapter;
 
@@ -683,9 +704,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     for (uint32_t l = 0; l < hp.n_layer; ++l) {
         const LayerWeights & lw = model->layers[l];
         const std::string p = "blk." + std::to_string(l) + ".";
-        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, xn_.ptr, d, Ti, stream));
+        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, xn_.ptr, d, Ti, stream, xn_split_.get()));
         if (lw.wqkv.data) {
-            linear(lw.wqkv, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0);
+            linear(lw.wqkv, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0, xn_split_.get());
         } else {
             linear(lw.wq, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0);
             linear(lw.wk, xn_.ptr, d, Ti, qkv_.ptr + dq, ldqkv, lw.bqkv ? lw.bqkv + dq : nullptr, nullptr, 0);
@@ -702,15 +723,21 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         }
         RB_K(K_OTHER, 1, launch_rope_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox,
                                            model->inv_freq.ptr, maps.tok_pos, maps.tok_cell, kvl, (int)l, stream));
-        RB_K(K_ATTN, 1, launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min,
-                                             att_.ptr, dq, stream));
+        if (attn_mma_) {
+            RB_K(K_ATTN, 1, launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot,
+                                                 maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, stream));
+            if (att_split_.get()) RB_K(K_OTHER, 1, launch_split_prep(att_.ptr, dq, dq, Ti, att_split_.view, stream));
+        } else {
+            RB_K(K_ATTN, 1, launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min,
+                                                 att_.ptr, dq, stream, att_split_.get()));
+        }
         // x = x + Wo att
-        linear(lw.wo, att_.ptr, dq, Ti, x_.ptr, d, nullptr, x_.ptr, d);
+        linear(lw.wo, att_.ptr, dq, Ti, x_.ptr, d, nullptr, x_.ptr, d, att_split_.get());
         if (any_adapter) lora(p + "attn_output.weight", att_.ptr, dq, Ti, x_.ptr, d);
-        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, xn_.ptr, d, Ti, stream));
+        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, xn_.ptr, d, Ti, stream, xn_split_.get()));
         if (hp.n_expert == 0) {
             if (lw.wgu.data) {
-                linear(lw.wgu, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0);
+                linear(lw.wgu, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0, xn_split_.get());
             } else {
                 linear(lw.wgate, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0);
                 linear(lw.wup, xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff, nullptr, nullptr, 0);
@@ -719,8 +746,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 lora(p + "ffn_gate.weight", xn_.ptr, d, Ti, gu_.ptr, 2 * ff);
                 lora(p + "ffn_up.weight", xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff);
             }
-            RB_K(K_OTHER, 1, launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, hff_.ptr, ff, stream));
-            linear(lw.wdown, hff_.ptr, ff, Ti, x_.ptr, d, nullptr, x_.ptr, d);
+            RB_K(K_OTHER, 1, launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, hff_.ptr, ff, stream, hff_split_.get()));
+            linear(lw.wdown, hff_.ptr, ff, Ti, x_.ptr, d, nullptr, x_.ptr, d, hff_split_.get());
             if (any_adapter) lora(p + "ffn_down.weight", hff_.ptr, ff, Ti, x_.ptr, d);
         } else {
             const int E = (int)hp.n_expert, K = (int)hp.n_expert_used, P = Ti * K;
@@ -738,8 +765,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     int32_t * d_top_ids = reinterpret_cast<int32_t *>(d_result_.ptr + res_ids);
     float * d_top_lps = reinterpret_cast<float *>(d_result_.ptr + res_lps);
     if (S) {
-        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, maps.out_index, model->output_norm, d, hp.eps, hs_.ptr, d, (int)S, stream));
-        linear(model->output, hs_.ptr, d, (int)S, logits.ptr, (int)hp.vocab, model->output_bias, nullptr, 0);
+        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, maps.out_index, model->output_norm, d, hp.eps, hs_.ptr, d, (int)S, stream, hs_split_.get()));
+        linear(model->output, hs_.ptr, d, (int)S, logits.ptr, (int)hp.vocab, model->output_bias, nullptr, 0, hs_split_.get());
         if (any_v2) {
             RB_CUDA(cudaMemcpyAsync(logits_work_.ptr, logits.ptr, S * (size_t)hp.vocab * 4, cudaMemcpyDeviceToDevice, stream));
         }

@@ -86,6 +86,23 @@ struct StepProfiler {
     }
 };
 
+// Device storage of one SplitAct for up to `rows` rows of `ld` columns.
+struct SplitBuffer {
+    DeviceBuffer<__half> store;
+    SplitAct view;
+    void ensure(size_t rows, size_t ld) {
+        if (ld % 32 != 0) return;
+        const size_t main = rows * ld, sums = rows * (ld / 32);
+        store.ensure(2 * main + 2 * sums + 64);
+        view.hi = store.ptr;
+        view.lo = store.ptr + main;
+        view.sum_hi = store.ptr + 2 * main;
+        view.sum_lo = store.ptr + 2 * main + sums + 32;
+        view.ld = (int)ld;
+    }
+    const SplitAct * get() const { return view.hi ? &view : nullptr; }
+};
+
 struct HParams {
     std::string arch;
     uint32_t n_layer = 0, d = 0, n_head = 0, n_head_kv = 0, head_dim = 0, ff = 0, vocab = 0;
@@ -205,6 +222,9 @@ public:
     size_t last_T = 0, last_S = 0, last_R = 0;
     float last_ms = 0.f;
     uint64_t last_launches = 0;
+    // steps with more tokens than this take the tensor-core GEMM (f16 operands); fewer take the f32 row kernel
+    int mma_min_tokens = 8;
+    bool gemm_fast_f16 = false;   // opt-in single-term f16 operands: faster, outside the 1e-2 logit tolerance on deep models
     uint64_t last_h2d_bytes = 0, last_d2h_bytes = 0;
     StepProfiler prof_;
     uint64_t graphs_reused = 0;
@@ -221,7 +241,8 @@ public:
 private:
     void load_model(const std::string & path);
     void restack_adapters();
-    void linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr);
+    void linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
+                const SplitAct * xs = nullptr);
     void lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy);
     void flush_kv_updates();
     KvLayout kv_layout() const;
@@ -238,6 +259,7 @@ private:
     size_t result_bytes_ = 0;
     DeviceBuffer<float> x_, xn_, qkv_, att_, gu_, hff_, hs_, router_logits_, moe_w_, pair_gu_, pair_h_, pair_y_, lora_tmp_, logits_work_;
     DeviceBuffer<int32_t> moe_ids_, d_aux_;
+    SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
 
     std::map<int32_t, Adapter> adapters_;
@@ -249,6 +271,8 @@ private:
     uint64_t stacked_bytes_ = 0;
     const int32_t * cur_tok_adapter_ = nullptr;
     bool cur_any_adapter_ = false;
+    bool attn_mma_ = false;
+    int attn_tile_tokens_ = 64;
 };
 
 } // namespace rb200

@@ -108,24 +108,28 @@ __global__ void __launch_bounds__(THREADS) gemm_q4k_mma_kernel(const uint8_t * _
         uint4 out[4];
         if (a_valid) {
             const int j = (((kt * BK) & 255) >> 6) * 2 + a_half;
-            const uint8_t * s = reinterpret_cast<const uint8_t *>(&f.hdr) + 4;
+            // the 12 packed scale bytes live in hdr.y, hdr.z, hdr.w
             uint32_t sc, mn;
             if (j < 4) {
-                sc = s[j] & 63;
-                mn = s[j + 4] & 63;
+                sc = (f.hdr.y >> (8 * j)) & 63u;
+                mn = (f.hdr.z >> (8 * j)) & 63u;
             } else {
-                sc = (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4);
-                mn = (s[j + 4] >> 4) | ((s[j] >> 6) << 4);
+                const int jj = j - 4;
+                const uint32_t lo = (f.hdr.w >> (8 * jj)) & 0xFFu;
+                sc = (lo & 0xFu) | ((((f.hdr.y >> (8 * jj)) & 0xFFu) >> 6) << 4);
+                mn = (lo >> 4) | ((((f.hdr.z >> (8 * jj)) & 0xFFu) >> 6) << 4);
             }
             const __half2 dd = *reinterpret_cast<const __half2 *>(&f.hdr.x);
             const float dl = __low2float(dd) * (float)sc, ml = __high2float(dd) * (float)mn;
             const __half2 dl2 = __float2half2_rn(dl), ml2 = __float2half2_rn(-ml);
-            const uint32_t words[8] = {f.q0.x, f.q0.y, f.q0.z, f.q0.w, f.q1.x, f.q1.y, f.q1.z, f.q1.w};
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                nibbles_to_half(words[2 * c], a_half, dl2, ml2, out[c].x, out[c].y);
-                nibbles_to_half(words[2 * c + 1], a_half, dl2, ml2, out[c].z, out[c].w);
-            }
+            nibbles_to_half(f.q0.x, a_half, dl2, ml2, out[0].x, out[0].y);
+            nibbles_to_half(f.q0.y, a_half, dl2, ml2, out[0].z, out[0].w);
+            nibbles_to_half(f.q0.z, a_half, dl2, ml2, out[1].x, out[1].y);
+            nibbles_to_half(f.q0.w, a_half, dl2, ml2, out[1].z, out[1].w);
+            nibbles_to_half(f.q1.x, a_half, dl2, ml2, out[2].x, out[2].y);
+            nibbles_to_half(f.q1.y, a_half, dl2, ml2, out[2].z, out[2].w);
+            nibbles_to_half(f.q1.z, a_half, dl2, ml2, out[3].x, out[3].y);
+            nibbles_to_half(f.q1.w, a_half, dl2, ml2, out[3].z, out[3].w);
         } else {
 #pragma unroll
             for (int c = 0; c < 4; ++c) out[c] = make_uint4(0, 0, 0, 0);
@@ -137,8 +141,9 @@ __global__ void __launch_bounds__(THREADS) gemm_q4k_mma_kernel(const uint8_t * _
         const uint32_t b_s = smem_u32(smem + stage * STAGE_BYTES + A_BYTES);
         const int k0 = kt * BK;
 #pragma unroll
-        for (int i = 0; i < BN * 8 / THREADS; ++i) {
+        for (int i = 0; i < (BN * 8 + THREADS - 1) / THREADS; ++i) {
             const int idx = tid + i * THREADS;
+            if (BN * 8 < THREADS && idx >= BN * 8) break;
             const int r = idx >> 3, c = idx & 7;
             const int t = t0 + r;
             const __half * src = X + (size_t)(t < T ? t : 0) * ldx + k0 + c * 8;

@@ -35,6 +35,22 @@ __device__ __forceinline__ float e8m0_half_dev(uint8_t x) {
 
 __constant__ float c_fp4_doubled[16] = {0.f, 1.f, 2.f, 3.f, 4.f, 6.f, 8.f, 12.f, 0.f, -1.f, -2.f, -3.f, -4.f, -6.f, -8.f, -12.f};
 
+// Writes v as hi + lo and, once per warp, the sub-block sum of v as hi + lo. Every lane of the
+// warp must call it, with 32 consecutive columns starting at a multiple of 32.
+__device__ __forceinline__ void emit_split(const SplitAct & s, size_t row, int col, float v) {
+    const __half hi = __float2half_rn(v);
+    const size_t at = row * s.ld + col;
+    s.hi[at] = hi;
+    s.lo[at] = __float2half_rn(v - __half2float(hi));
+    const float sum = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) {
+        const __half sh = __float2half_rn(sum);
+        const size_t sat = row * (s.ld >> 5) + (col >> 5);
+        s.sum_hi[sat] = sh;
+        s.sum_lo[sat] = __float2half_rn(sum - __half2float(sh));
+    }
+}
+
 // Decodes 8 consecutive elements starting at k (k % 8 == 0) of a stored row.
 template <uint32_t TYPE>
 __device__ __forceinline__ void decode8(const uint8_t * __restrict__ row, uint32_t k, float (&w)[8]) {
@@ -95,58 +111,67 @@ __device__ __forceinline__ void decode8(const uint8_t * __restrict__ row, uint32
 // ------------------------------------------------------------------------------------------
 // Packing: step plan -> batch maps, with block tables resolved to physical KV cells.
 
-__global__ void pack_scan_kernel(const RowDesc * __restrict__ rows, int n_rows, int32_t * __restrict__ cu, int32_t * __restrict__ out_rank) {
-    __shared__ int32_t warp_tok[32], warp_out[32];
-    __shared__ int32_t carry_tok, carry_out;
+__global__ void pack_scan_kernel(const RowDesc * __restrict__ rows, int n_rows, int tile_tokens, int32_t * __restrict__ cu,
+                                 int32_t * __restrict__ out_rank, int32_t * __restrict__ tile_rank) {
+    __shared__ int32_t warp_tok[32], warp_out[32], warp_tile[32];
+    __shared__ int32_t carry_tok, carry_out, carry_tile;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    if (tid == 0) { carry_tok = 0; carry_out = 0; }
+    if (tid == 0) { carry_tok = 0; carry_out = 0; carry_tile = 0; }
     __syncthreads();
     for (int base = 0; base < n_rows; base += blockDim.x) {
         const int r = base + tid;
         const int32_t n = r < n_rows ? rows[r].n : 0;
         const int32_t s = r < n_rows ? (rows[r].sample != 0) : 0;
-        int32_t in = n, is = s;
+        const int32_t nt = (n + tile_tokens - 1) / tile_tokens;
+        int32_t in = n, is = s, it = nt;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const int32_t a = __shfl_up_sync(0xffffffffu, in, o);
             const int32_t b = __shfl_up_sync(0xffffffffu, is, o);
-            if (lane >= o) { in += a; is += b; }
+            const int32_t c = __shfl_up_sync(0xffffffffu, it, o);
+            if (lane >= o) { in += a; is += b; it += c; }
         }
-        if (lane == 31) { warp_tok[wid] = in; warp_out[wid] = is; }
+        if (lane == 31) { warp_tok[wid] = in; warp_out[wid] = is; warp_tile[wid] = it; }
         __syncthreads();
         if (wid == 0) {
-            int32_t a = warp_tok[lane], b = warp_out[lane];
+            int32_t a = warp_tok[lane], b = warp_out[lane], c = warp_tile[lane];
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int32_t ua = __shfl_up_sync(0xffffffffu, a, o);
                 const int32_t ub = __shfl_up_sync(0xffffffffu, b, o);
-                if (lane >= o) { a += ua; b += ub; }
+                const int32_t uc = __shfl_up_sync(0xffffffffu, c, o);
+                if (lane >= o) { a += ua; b += ub; c += uc; }
             }
             warp_tok[lane] = a;
             warp_out[lane] = b;
+            warp_tile[lane] = c;
         }
         __syncthreads();
         const int32_t pre_tok = carry_tok + (wid ? warp_tok[wid - 1] : 0);
         const int32_t pre_out = carry_out + (wid ? warp_out[wid - 1] : 0);
+        const int32_t pre_tile = carry_tile + (wid ? warp_tile[wid - 1] : 0);
         if (r < n_rows) {
             cu[r] = pre_tok + in - n;
             out_rank[r] = pre_out + is - s;
+            tile_rank[r] = pre_tile + it - nt;
         }
         __syncthreads();
         if (tid == 0) {
             carry_tok += warp_tok[31];
             carry_out += warp_out[31];
+            carry_tile += warp_tile[31];
         }
         __syncthreads();
     }
     if (tid == 0) {
         cu[n_rows] = carry_tok;
         out_rank[n_rows] = carry_out;
+        tile_rank[n_rows] = carry_tile;
     }
 }
 
 __global__ void pack_fill_kernel(const RowDesc * __restrict__ rows, int n_rows, int n_tokens, const int32_t * __restrict__ block_table,
-                                 int max_blocks, int block_tokens, PackMaps maps) {
+                                 int max_blocks, int block_tokens, int tile_tokens, PackMaps maps) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_tokens) return;
     int lo = 0, hi = n_rows - 1;
@@ -165,6 +190,7 @@ __global__ void pack_fill_kernel(const RowDesc * __restrict__ rows, int n_rows, 
     const int blk = block_table[(size_t)row.slot * max_blocks + pos / block_tokens];
     maps.tok_cell[i] = blk * block_tokens + pos % block_tokens;
     if (row.sample && j == row.n - 1) maps.out_index[maps.out_rank[lo]] = i;
+    if (j % tile_tokens == 0) maps.attn_items[maps.tile_rank[lo] + j / tile_tokens] = make_int2(i, min(tile_tokens, row.n - j));
 }
 
 __global__ void block_table_patch_kernel(int32_t * __restrict__ table, const int32_t * __restrict__ patches, int n) {
@@ -221,7 +247,7 @@ __global__ void embed_kernel(WeightView e, const int32_t * __restrict__ tokens, 
 }
 
 __global__ void rms_norm_kernel(const float * __restrict__ x, int ldx, const int32_t * __restrict__ gather, const float * __restrict__ w, int n,
-                                float eps, float * __restrict__ y, int ldy) {
+                                float eps, float * __restrict__ y, int ldy, SplitAct split) {
     __shared__ float partial[32];
     const int t = blockIdx.x;
     const float * xr = x + (size_t)(gather ? gather[t] : t) * ldx;
@@ -237,7 +263,11 @@ __global__ void rms_norm_kernel(const float * __restrict__ x, int ldx, const int
     }
     __syncthreads();
     const float scale = 1.0f / sqrtf(partial[0] / (float)n + eps);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) y[(size_t)t * ldy + i] = xr[i] * scale * w[i];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = xr[i] * scale * w[i];
+        if (y) y[(size_t)t * ldy + i] = v;
+        if (split.hi) emit_split(split, t, i, v);
+    }
 }
 
 // One warp per output row, eight tokens per pass.
@@ -315,7 +345,7 @@ __global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, 
 // One warp per (token, q head); lanes own head dimensions; positions in groups of four.
 __global__ void attention_ref_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer,
                                      const int32_t * __restrict__ tok_slot, const int32_t * __restrict__ tok_pos,
-                                     const int32_t * __restrict__ tok_pos_min, float * __restrict__ out, int ldo) {
+                                     const int32_t * __restrict__ tok_pos_min, float * __restrict__ out, int ldo, SplitAct split) {
     const int lane = threadIdx.x & 31;
     const int h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int t = blockIdx.y;
@@ -384,15 +414,26 @@ __global__ void attention_ref_kernel(const float * __restrict__ qkv, int ld, int
     for (int j = 0; j < MAXD; ++j) {
         const int i = lane + 32 * j;
         if (i < hd) out[(size_t)t * ldo + (size_t)h * hd + i] = acc[j] * inv;
+        if (split.hi && 32 * j < hd) emit_split(split, t, h * hd + i, acc[j] * inv);
     }
 }
 
-__global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh) {
+// x [t][ld] f32 -> its SplitAct (n a multiple of 32)
+__global__ void split_prep_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    emit_split(split, t, i, x[(size_t)t * ldx + i]);
+}
+
+__global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh, SplitAct split) {
     const int t = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= ff) return;
     const float g = gu[(size_t)t * ld + i], u = gu[(size_t)t * ld + ff + i];
-    h[(size_t)t * ldh + i] = g / (1.0f + expf(-g)) * u;
+    const float v = g / (1.0f + expf(-g)) * u;
+    if (h) h[(size_t)t * ldh + i] = v;
+    if (split.hi) emit_split(split, t, i, v);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -537,9 +578,9 @@ template <class F> void dispatch_type(uint32_t type, F && f) {
 } // namespace
 
 void launch_pack(const RowDesc * rows, int n_rows, int n_tokens, const int32_t * block_table, int max_blocks, int block_tokens,
-                 PackMaps maps, cudaStream_t stream) {
-    pack_scan_kernel<<<1, 1024, 0, stream>>>(rows, n_rows, maps.cu_rows, maps.out_rank);
-    pack_fill_kernel<<<(n_tokens + 255) / 256, 256, 0, stream>>>(rows, n_rows, n_tokens, block_table, max_blocks, block_tokens, maps);
+                 int tile_tokens, PackMaps maps, cudaStream_t stream) {
+    pack_scan_kernel<<<1, 1024, 0, stream>>>(rows, n_rows, tile_tokens, maps.cu_rows, maps.out_rank, maps.tile_rank);
+    pack_fill_kernel<<<(n_tokens + 255) / 256, 256, 0, stream>>>(rows, n_rows, n_tokens, block_table, max_blocks, block_tokens, tile_tokens, maps);
 }
 
 void launch_block_table_patch(int32_t * block_table, const int32_t * patches, int n_patches, cudaStream_t stream) {
@@ -565,8 +606,8 @@ void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float *
 }
 
 void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const float * w, int n, float eps, float * y, int ldy, int n_tokens,
-                     cudaStream_t stream) {
-    rms_norm_kernel<<<n_tokens, 256, 0, stream>>>(x, ldx, gather, w, n, eps, y, ldy);
+                     cudaStream_t stream, const SplitAct * split) {
+    rms_norm_kernel<<<n_tokens, 256, 0, stream>>>(x, ldx, gather, w, n, eps, y, ldy, split && n % 32 == 0 ? *split : SplitAct{});
 }
 
 void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
@@ -585,14 +626,18 @@ void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head
 }
 
 void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,
-                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream) {
+                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream, const SplitAct * split) {
     const int warps = 4;
     attention_ref_kernel<<<dim3((n_head + warps - 1) / warps, n_tokens), warps * 32, 0, stream>>>(qkv, ld, n_head, kv, layer, tok_slot, tok_pos,
-                                                                                                tok_pos_min, out, ldo);
+                                                                                                tok_pos_min, out, ldo, split && kv.head_dim % 32 == 0 ? *split : SplitAct{});
 }
 
-void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream) {
-    swiglu_kernel<<<dim3((ff + 255) / 256, n_tokens), 256, 0, stream>>>(gu, ld, ff, h, ldh);
+void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream) {
+    split_prep_kernel<<<dim3((n + 255) / 256, n_tokens), 256, 0, stream>>>(x, ldx, n, split);
+}
+
+void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split) {
+    swiglu_kernel<<<dim3((ff + 255) / 256, n_tokens), 256, 0, stream>>>(gu, ld, ff, h, ldh, split && ff % 32 == 0 ? *split : SplitAct{});
 }
 
 void launch_moe_route(const float * router_logits, int n_expert, int k, int n_tokens, int32_t * ids, float * weights, cudaStream_t stream) {

@@ -16,6 +16,16 @@ struct WeightView {
     uint32_t row_bytes = 0;
 };
 
+// An activation matrix [t][ld] prepared for the exact tensor-core GEMM: the two-term f16 split
+// x = hi + lo, and per 32-element sub-block the sum of x, again as hi + lo ([t][ld / 32]).
+struct SplitAct {
+    __half * hi = nullptr;
+    __half * lo = nullptr;
+    __half * sum_hi = nullptr;
+    __half * sum_lo = nullptr;
+    int ld = 0;
+};
+
 // One row of a step plan as the packing kernel reads it (32 bytes).
 struct RowDesc {
     int32_t slot;
@@ -70,6 +80,8 @@ struct PackMaps {
     int32_t * tok_adapter; // [T]
     int32_t * tok_pos_min; // [T]
     int32_t * out_index;   // [S]
+    int32_t * tile_rank;   // [R + 1] exclusive scan of the rows' attention tile counts
+    int2 * attn_items;     // [sum of tiles] (first token index, tokens in the tile)
 };
 
 struct KvLayout {
@@ -83,8 +95,9 @@ struct KvLayout {
     int32_t max_blocks;
 };
 
+// `tile_tokens`: tokens per attention work item (a row of n tokens yields ceil(n / tile_tokens) items).
 void launch_pack(const RowDesc * rows, int n_rows, int n_tokens, const int32_t * block_table, int max_blocks, int block_tokens,
-                 PackMaps maps, cudaStream_t stream);
+                 int tile_tokens, PackMaps maps, cudaStream_t stream);
 void launch_block_table_patch(int32_t * block_table, const int32_t * patches, int n_patches, cudaStream_t stream);
 void launch_kv_block_copy(KvLayout kv, int n_layer, const int32_t * pairs, int n_pairs, cudaStream_t stream);
 
@@ -94,18 +107,33 @@ void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int
 
 void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream);
 // y[t] = x[gather ? gather[t] : t] * rsqrt(mean(x^2) + eps) * w
+// `split`, when given (n a multiple of 32), also receives the row prepared for the tensor-core GEMM.
 void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const float * w, int n, float eps, float * y, int ldy, int n_tokens,
-                     cudaStream_t stream);
+                     cudaStream_t stream, const SplitAct * split = nullptr);
 // y[t][o] = sum_i deq(W)[o][i] x[t][i] (+ bias[o]) (+ residual[t][o]); reference kernel, any T.
 void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
                       int ldr, cudaStream_t stream);
+// Tensor-core path of the same product for many tokens: f16 activations [t][ldx], Q4_K weights.
+bool gemm_mma_supported(const WeightView & w, int ldx);
+void launch_gemm_mma(const WeightView & w, const __half * x16, int ldx, int n_tokens, float * y, int ldy, const float * bias,
+                     const float * residual, int ldr, cudaStream_t stream);
+// Exact variant (f32-grade accuracy): integer weight operand, two-term activation split.
+bool gemm_q4k_exact_supported(const WeightView & w, const SplitAct & x);
+void launch_gemm_q4k_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
+                           const float * residual, int ldr, cudaStream_t stream);
 // In-place RoPE on q and k (inside the fused qkv buffer) and the f16 store of k, v into the paged cache.
 void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
                        const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream);
 void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,
+                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream,
+                          const SplitAct * split = nullptr);
+void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream);
+// Tensor-core paged attention (head_dim 64 or 128, 16-token KV blocks, power-of-two GQA group).
+bool attention_mma_supported(int n_head, int n_head_kv, int head_dim, int block_tokens);
+void launch_attention_mma(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
                           const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream);
 // h[t][i] = silu(gu[t][i]) * gu[t][ff + i]
-void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream);
+void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split = nullptr);
 
 // MoE (reference kernels): router softmax + top-k, per-pair expert GEMMs, fixed-order combine.
 void launch_moe_route(const float * router_logits, int n_expert, int k, int n_tokens, int32_t * ids, float * weights, cudaStream_t stream);

@@ -1,0 +1,77 @@
+// Operator-level entry points: one kernel of the decode step run on caller-provided host data.
+// They exist so a kernel can be checked against the CPU oracle and timed in isolation (small
+// cases for profiler captures) without building a model around it.
+
+#include "engine.hpp"
+#include "blocks.hpp"
+
+#include <vector>
+
+using namespace rb200;
+
+extern "C" {
+
+// y[t][o] = sum_k deq(w)[o][k] x[t][k]. `path`: 0 = what the engine would pick, 1 = f32 row kernel,
+// 2 = single-term f16 tensor-core kernel, 3 = exact tensor-core kernel. The kernel runs `iters`
+// times; *out_ms receives the mean device time per launch (CUDA events on the launching stream).
+int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, uint32_t n_in, const float * x, uint32_t n_tokens, float * y,
+                       int path, uint32_t iters, float * out_ms) {
+    return boundary([&]() -> int {
+        const size_t rb = row_bytes(ggml_type, n_in);
+        if (!w || !x || !y || rb == 0 || n_in % 8 != 0 || n_tokens == 0 || n_out == 0) {
+            set_error("op_gemm: bad arguments");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        DeviceBuffer<uint8_t> dw;
+        DeviceBuffer<float> dx, dy;
+        SplitBuffer xs;
+        dw.ensure(rb * n_out);
+        dx.ensure((size_t)n_tokens * n_in);
+        dy.ensure((size_t)n_tokens * n_out);
+        xs.ensure(n_tokens, n_in);
+        cudaStream_t stream;
+        RB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        cudaEvent_t e0, e1;
+        RB_CUDA(cudaEventCreate(&e0));
+        RB_CUDA(cudaEventCreate(&e1));
+        RB_CUDA(cudaMemcpyAsync(dw.ptr, w, rb * n_out, cudaMemcpyHostToDevice, stream));
+        RB_CUDA(cudaMemcpyAsync(dx.ptr, x, (size_t)n_tokens * n_in * 4, cudaMemcpyHostToDevice, stream));
+        WeightView wv;
+        wv.data = dw.ptr;
+        wv.type = ggml_type;
+        wv.n_in = n_in;
+        wv.n_out = n_out;
+        wv.row_bytes = (uint32_t)rb;
+        const bool have_split = xs.get() != nullptr;
+        if (have_split) launch_split_prep(dx.ptr, (int)n_in, (int)n_in, (int)n_tokens, xs.view, stream);
+        int chosen = path;
+        if (chosen == 0) chosen = have_split && n_tokens > 8 && gemm_q4k_exact_supported(wv, xs.view) ? 3 : 1;
+        if ((chosen == 3 && !(have_split && gemm_q4k_exact_supported(wv, xs.view))) ||
+            (chosen == 2 && !(have_split && gemm_mma_supported(wv, (int)n_in)))) {
+            cudaStreamDestroy(stream);
+            set_error("op_gemm: the requested kernel does not cover this type or shape");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        auto run = [&]() {
+            if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
+            else if (chosen == 2) launch_gemm_mma(wv, xs.view.hi, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
+            else launch_gemm_rows(wv, dx.ptr, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
+        };
+        run();   // warm-up, also the launch whose output is returned
+        RB_CUDA(cudaEventRecord(e0, stream));
+        for (uint32_t i = 0; i < iters; ++i) run();
+        RB_CUDA(cudaEventRecord(e1, stream));
+        RB_CUDA(cudaMemcpyAsync(y, dy.ptr, (size_t)n_tokens * n_out * 4, cudaMemcpyDeviceToHost, stream));
+        RB_CUDA(cudaStreamSynchronize(stream));
+        RB_CUDA(cudaGetLastError());
+        float ms = 0.f;
+        if (iters) cudaEventElapsedTime(&ms, e0, e1);
+        if (out_ms) *out_ms = iters ? ms / iters : 0.f;
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        cudaStreamDestroy(stream);
+        return STATUS_OK;
+    });
+}
+
+} // extern "C"

@@ -194,6 +194,18 @@ def quantize_row(ggml_type: int, values) -> bytes:
     return out[: n.value].tobytes()
 
 
+def op_gemm(ggml_type: int, w_bytes, n_out: int, n_in: int, x, path: int = 0, iters: int = 0):
+    """One dequant-fused GEMM through retro_b200_op_gemm. Returns (y [T, n_out], ms per launch)."""
+    lib = _ffi.load_library()
+    w = np.ascontiguousarray(np.frombuffer(w_bytes, dtype=np.uint8) if not isinstance(w_bytes, np.ndarray) else w_bytes)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, n_in)
+    y = np.zeros((x.shape[0], n_out), dtype=np.float32)
+    ms = C.c_float()
+    _check(lib.retro_b200_op_gemm(ggml_type, w.ctypes.data_as(C.POINTER(C.c_uint8)), n_out, n_in, x.ctypes.data_as(C.POINTER(C.c_float)),
+                                  x.shape[0], y.ctypes.data_as(C.POINTER(C.c_float)), path, iters, C.byref(ms)))
+    return y, ms.value
+
+
 class Engine:
     def __init__(self, model_path: str, config: EngineConfig | None = None) -> None:
         self._lib = _ffi.load_library()

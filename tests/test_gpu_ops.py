@@ -1,0 +1,31 @@
+"""Single kernels through their operator entry points against the CPU oracle."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _q4k_matrix(rb, rng, n_out, n_in):
+    w = rng.normal(0, 0.02, (n_out, n_in)).astype(np.float32)
+    raw = b"".join(rb.quantize_row(12, w[r]) for r in range(n_out))
+    return np.frombuffer(raw, dtype=np.uint8)
+
+
+@pytest.mark.parametrize("n_out,n_in,T", [(256, 512, 5), (384, 1024, 16), (200, 768, 33), (512, 2048, 100), (256, 4096, 300)])
+def test_q4k_gemm_kernels_against_the_oracle(rb, oracle, n_out, n_in, T):
+    rng = np.random.default_rng(n_out + T)
+    raw = _q4k_matrix(rb, rng, n_out, n_in)
+    x = rng.normal(0, 1.5, (T, n_in)).astype(np.float32)
+    serial = np.stack([oracle.mul_mat_vec(oracle.T_Q4_K, raw, n_out, n_in, x[t]) for t in range(T)])
+    # the yardstick is the exact product of the decoded weights; the oracle's serial f32 sum is itself ~1e-6 away from it
+    w = oracle.dequantize_row(oracle.T_Q4_K, raw, n_out * n_in).reshape(n_out, n_in).astype(np.float64)
+    want = x.astype(np.float64) @ w.T
+    scale = float(np.abs(want).max())
+    assert float(np.abs(serial - want).max()) / scale < 4e-6
+    rows, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=1)
+    exact, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=3)
+    fast, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=2)
+    e_rows, e_exact, e_fast = (float(np.abs(y - want).max()) / scale for y in (rows, exact, fast))
+    print(f"q4k {n_out}x{n_in} T={T}: rel err rows={e_rows:.2e} exact={e_exact:.2e} single-term f16={e_fast:.2e}")
+    assert e_rows < 4e-6 and e_exact < 4e-6
+    assert e_fast < 3e-3

@@ -147,3 +147,36 @@ def test_flat_router_moe_matches_oracle(rb, oracle, models):
     assert len(np.unique(got)) > 2  # the flat router really spreads tokens
     print(f"moe flat: max|dlogit|={rep.max_logit_diff:.3e}")
     engine.close()
+
+
+def test_tensor_core_gemm_path_wide_steps(rb, oracle, models):
+    """Steps with hundreds of tokens take the tensor-core GEMM (f16 operands, f32 accumulate);
+    the oracle stays f32 end to end, so this measures the path's real logit error."""
+    spec = dict(arch="llama", layers=4, d=1024, heads=8, kv_heads=2, ff=2816, vocab=2048, dtype="q4_k", seed=31)
+    rng = np.random.default_rng(31)
+    prompts = [rng.integers(3, 2048, n).tolist() for n in (301, 77, 190, 12, 129)]
+    rep = _greedy_workload(rb, oracle, models("q4k_wide", **spec), prompts, 4, n_batch=512, n_ctx=4096, chunk=256)
+    print(f"q4k wide: max|dlogit|={rep.max_logit_diff:.3e} min margin={rep.min_margin:.3e} ties={rep.tie_events}")
+
+
+def test_full_8b_shape_logits_within_tolerance(rb, oracle):
+    """BASELINE config 2's model at full size (32 layers, d 4096, Q4_K): a ragged prefill step on
+    the tensor-core path and decode steps on the row path, logits against the f32 CPU oracle."""
+    import bench
+
+    path = bench.ensure_model("c2", 0)
+    engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=4096, n_seq_max=4, n_batch=128, n_ubatch=128))
+    om = oracle.Model(str(path), fast=True)
+    octx = oracle.Context(om, 4, 4096)
+    out = rb.StepOutput()
+    rep = ParityReport()
+    rng = np.random.default_rng(8)
+    greedy = rb.SamplingParamsV2.greedy()
+    prompts = [rng.integers(3, 128256, n).tolist() for n in (40, 9, 23)]
+    rows = [rb.StepRow(i, i, p, 0, sample=True, sampling=greedy) for i, p in enumerate(prompts)]
+    for step in range(3):
+        toks = check_step(rb, engine, octx, oracle, rows, out, rep)
+        expect_greedy(oracle, toks, rep)
+        rows = [rb.StepRow.decode(i, i, out.row(i).token, len(prompts[i]) + step, greedy) for i in range(3)]
+    print(f"8B shape: max|dlogit|={rep.max_logit_diff:.3e} min margin={rep.min_margin:.3e} ties={rep.tie_events}")
+    engine.close()
