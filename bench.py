@@ -129,10 +129,12 @@ class Driver:
             r.slot = self.free_slots.pop()
             self.live.append(r)
 
-    def compose(self):
+    def compose(self, prefill_only=False):
         rb = self.rb
         rows, kinds, budget = [], [], self.cfg["n_batch"]
         for r in self.live:
+            if prefill_only:
+                break
             if r.last is not None and budget > 0:
                 rows.append(rb.StepRow(r.rid, r.slot, [r.last], len(r.prompt) + r.done - 1, True, self.sampling))
                 kinds.append(r)
@@ -146,8 +148,8 @@ class Driver:
                 budget -= take
         return rows, kinds
 
-    def step(self, now=None):
-        rows, reqs = self.compose()
+    def step(self, prefill_only=False):
+        rows, reqs = self.compose(prefill_only)
         if not rows:
             return dict(decode=0, prefill=0, sampled=0, rows=rows)
         self.engine.step(rows, self.out)
@@ -318,7 +320,7 @@ def main():
     driver.admit(midflight=True)
     ramp_steps = 0
     while any(r.last is None for r in driver.live):
-        driver.step()
+        driver.step(prefill_only=True)     # no request advances its generation during the ramp
         ramp_steps += 1
     for _ in range(args.warmup):
         driver.step()
@@ -331,6 +333,7 @@ def main():
     if dist:
         dist.barrier()
     torch.cuda.synchronize()
+    torch.cuda.nvtx.range_push("timed")
     dev_ms, wall_s, decode_tokens, prefill_tokens, rows_per_step, launches, h2d, d2h = 0.0, 0.0, 0, 0, [], 0, 0, 0
     attn_bytes = 0
     gemm_flops = 0
@@ -354,6 +357,7 @@ def main():
         gemm_flops += 2 * (info["tokens"] * w_elems_layer * sp["layers"] + info["sampled"] * sp["d"] * sp["vocab"])
         driver.admit()
     torch.cuda.synchronize()
+    torch.cuda.nvtx.range_pop()
     if dist:
         dist.barrier()
     clocks.stop_flag.set()
