@@ -371,14 +371,11 @@ def main():
         t = r.times[-(args.steps + 1):]
         gaps += [1e3 * (b - a) for a, b in zip(t, t[1:])]
 
-    stats = torch.tensor([dev_ms, wall_s, float(decode_tokens), float(prefill_tokens), float(launches)], dtype=torch.float64, device="cuda")
-    if dist:
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        dev_ms, wall_s = float(mx[0]), float(mx[1])
-        decode_tokens, prefill_tokens, launches = float(sm[2]), float(sm[3]), float(sm[4])
+    from retrograd_b200.replicas import aggregate
+
+    # whole job: the slowest rank's time, every rank's tokens (replicas, no data-path collective)
+    (dev_ms, wall_s), (decode_tokens, prefill_tokens, launches) = aggregate(
+        [dev_ms, wall_s], [decode_tokens, prefill_tokens, launches], dist, torch.device("cuda", local_rank))
     if rank != 0:
         engine.close()
         return
