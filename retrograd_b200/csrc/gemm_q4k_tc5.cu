@@ -1,0 +1,285 @@
+// Dequant-fused Q4_K weight GEMM on the 5th-generation tensor cores (tcgen05, accumulators in
+// tensor memory), with the same exact arithmetic as gemm_q4k_exact.cu:
+//   per 256-element super-block   acc += d * (sum_k (sc*q)_k * (x_hi + x_lo)_k) - dmin * (sum_sub m_sub * sum_x_sub)
+// The tensor cores only ever see values f16 holds exactly (integers sc*q <= 945, integer mins,
+// two-term activation splits); d and dmin are applied in f32 by the epilogue warps.
+//
+// One CTA computes 128 weight rows x 128 tokens. Warp roles (17 warps):
+//   0-3, 4-7   two producer groups, alternating pipeline stages: thread p decodes the 64 weights of
+//              row p into the K-major 128B-swizzled A tile and copies the activation rows of token p
+//              (hi and lo) with cp.async into the B tiles;
+//   16         lane 0 issues the MMAs (M 128, N 128, K 16) and commits them to the stage's
+//              "empty" barrier, and per super-block to the accumulator's "full" barrier;
+//   8-11,12-15 epilogue: each thread owns one weight row and 64 token columns, pulls both TMEM
+//              accumulators of a finished super-block with tcgen05.ld and folds them into its f32
+//              running sums while the tensor cores already work on the next super-block in the
+//              other TMEM buffer.
+// A super-block is five pipeline stages: four of 64 columns each (eight MMAs: hi and lo), then one
+// that carries the minimum term as a single K=16 step (A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]).
+// Every mbarrier wait is bounded: after about a second without progress the CTA raises an error
+// flag, drains its copies, frees its tensor memory and returns.
+
+#include "kernels.cuh"
+#include "blocks.hpp"
+#include "mma_common.cuh"
+#include "tc5_common.cuh"
+
+namespace rb200 {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
+constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
+constexpr int N_WARPS = 17;
+constexpr int THREADS = N_WARPS * 32;
+constexpr int TMEM_COLS = 512;                 // two buffers x (128 main + 128 min) columns
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+
+__device__ __forceinline__ void nibbles_times_scale(uint32_t word, int hi, __half2 sc2, __half2 off2, uint32_t & out01, uint32_t & out23) {
+    const uint32_t v = hi ? (word >> 4) : word;
+    uint32_t a = (v & 0x000F000Fu) | 0x64006400u;
+    uint32_t b = ((v >> 8) & 0x000F000Fu) | 0x64006400u;
+    const __half2 ha = __hfma2(*reinterpret_cast<__half2 *>(&a), sc2, off2);
+    const __half2 hb = __hfma2(*reinterpret_cast<__half2 *>(&b), sc2, off2);
+    const uint32_t ua = *reinterpret_cast<const uint32_t *>(&ha), ub = *reinterpret_cast<const uint32_t *>(&hb);
+    out01 = __byte_perm(ua, ub, 0x5410);
+    out23 = __byte_perm(ua, ub, 0x7632);
+}
+
+template <bool RESIDUAL>
+__global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes, SplitAct X,
+                                                                  int T, float * __restrict__ Y, int ldy, const float * __restrict__ bias,
+                                                                  const float * __restrict__ residual, int ldr, int * __restrict__ error_flag) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    // barriers: full[4], empty[4], tmem_full[2], tmem_empty[2]; then the TMEM base word and the abort flag
+    const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+    uint32_t * tmem_word = reinterpret_cast<uint32_t *>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_word + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int m0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
+    const int n_sb = n_in / 256;
+    const int n_it = n_sb * 5;
+    const int n_sub = n_in / 32;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc5::mbar_init(full_bar(s), 128);
+            tc5::mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc5::mbar_init(tfull_bar(b), 1);
+            tc5::mbar_init(tempty_bar(b), 256);
+        }
+        *abort_flag = 0;
+        tc5::fence_mbar_init();
+    }
+    if (warp == 16) tc5::tmem_alloc(smem_u32(tmem_word), TMEM_COLS);
+    tc5::fence_before_sync();
+    __syncthreads();
+    tc5::fence_after_sync();
+    const uint32_t tmem_base = *tmem_word;
+
+    if (warp < 8) {
+        // ------------------------------------------------------------------ producers
+        const int group = warp >> 2;
+        const int p = tid & 127;                       // weight row and token row of this thread
+        const bool a_valid = m0 + p < n_out;
+        const uint8_t * a_base = W + (size_t)(m0 + (a_valid ? p : 0)) * row_bytes;
+        const int t = t0 + p;
+        const bool t_valid = t < T;
+        for (int it = group; it < n_it; it += 2) {
+            const int stage = it % STAGES, use = it / STAGES;
+            if (!tc5::mbar_wait(empty_bar(stage), (use & 1) ^ 1, abort_flag)) break;
+            const int sb = it / 5, r = it % 5;
+            uint8_t * a_s = smem + stage * STAGE_BYTES;
+            uint8_t * bh_s = a_s + A_BYTES;
+            const uint8_t * blk = a_base + (size_t)sb * 144;
+            if (r < 4) {
+                const int k0 = sb * 256 + r * 64;
+                const uint32_t bh = smem_u32(bh_s), bl = bh + B_BYTES;
+                const size_t xoff = (size_t)(t_valid ? t : 0) * X.ld + k0;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    cp_async16(bh + swz(p, c), X.hi + xoff + c * 8, t_valid ? 16 : 0);
+                    cp_async16(bl + swz(p, c), X.lo + xoff + c * 8, t_valid ? 16 : 0);
+                }
+                cp_async_commit();
+                uint4 out[8];
+                if (a_valid) {
+                    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+                    const uint4 * qs = reinterpret_cast<const uint4 *>(blk + 16 + r * 32);
+                    const uint4 q0 = qs[0], q1 = qs[1];
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t sc, mn;
+                        q4k_scale_min_regs(hdr, r * 2 + half, sc, mn);
+                        const __half2 sc2 = __half2half2(__ushort2half_rn((unsigned short)sc));
+                        const __half2 off2 = __half2half2(__float2half_rn(-1024.0f * (float)sc));
+                        uint4 * o = out + half * 4;
+                        nibbles_times_scale(q0.x, half, sc2, off2, o[0].x, o[0].y);
+                        nibbles_times_scale(q0.y, half, sc2, off2, o[0].z, o[0].w);
+                        nibbles_times_scale(q0.z, half, sc2, off2, o[1].x, o[1].y);
+                        nibbles_times_scale(q0.w, half, sc2, off2, o[1].z, o[1].w);
+                        nibbles_times_scale(q1.x, half, sc2, off2, o[2].x, o[2].y);
+                        nibbles_times_scale(q1.y, half, sc2, off2, o[2].z, o[2].w);
+                        nibbles_times_scale(q1.z, half, sc2, off2, o[3].x, o[3].y);
+                        nibbles_times_scale(q1.w, half, sc2, off2, o[3].z, o[3].w);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(a_s + swz(p, c)) = out[c];
+                cp_async_wait<0>();
+            } else {
+                // minimum-term stage: one K = 16 step
+                uint4 mv = make_uint4(0, 0, 0, 0);
+                if (a_valid) {
+                    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+                    uint32_t mw[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t s0, n0, s1, n1;
+                        q4k_scale_min_regs(hdr, 2 * q, s0, n0);
+                        q4k_scale_min_regs(hdr, 2 * q + 1, s1, n1);
+                        const __half2 pr = __halves2half2(__ushort2half_rn((unsigned short)n0), __ushort2half_rn((unsigned short)n1));
+                        mw[q] = *reinterpret_cast<const uint32_t *>(&pr);
+                    }
+                    mv = make_uint4(mw[0], mw[1], mw[2], mw[3]);
+                }
+                *reinterpret_cast<uint4 *>(a_s + swz(p, 0)) = mv;
+                *reinterpret_cast<uint4 *>(a_s + swz(p, 1)) = mv;
+                uint4 sh = make_uint4(0, 0, 0, 0), sl = make_uint4(0, 0, 0, 0);
+                if (t_valid) {
+                    sh = *reinterpret_cast<const uint4 *>(X.sum_hi + (size_t)t * n_sub + sb * 8);
+                    sl = *reinterpret_cast<const uint4 *>(X.sum_lo + (size_t)t * n_sub + sb * 8);
+                }
+                *reinterpret_cast<uint4 *>(bh_s + swz(p, 0)) = sh;
+                *reinterpret_cast<uint4 *>(bh_s + swz(p, 1)) = sl;
+            }
+            tc5::fence_proxy_async();
+            tc5::mbar_arrive(full_bar(stage));
+        }
+        cp_async_wait<0>();
+    } else if (warp == 16) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = tc5::instr_desc_f16(BM, BN);
+            for (int it = 0; it < n_it; ++it) {
+                const int stage = it % STAGES, use = it / STAGES;
+                const int sb = it / 5, r = it % 5;
+                const int buf = sb & 1, buse = sb >> 1;
+                if (r == 0) {
+                    if (!tc5::mbar_wait(tempty_bar(buf), (buse & 1) ^ 1, abort_flag)) break;
+                    tc5::fence_after_sync();
+                }
+                if (!tc5::mbar_wait(full_bar(stage), use & 1, abort_flag)) break;
+                tc5::fence_after_sync();
+                const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+                const uint32_t bh_addr = a_addr + A_BYTES, bl_addr = bh_addr + B_BYTES;
+                const uint32_t d_main = tmem_base + buf * 256, d_min = d_main + 128;
+                if (r < 4) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t ad = tc5::smem_desc_sw128(a_addr + k * 32);
+                        tc5::mma_f16_ss(d_main, ad, tc5::smem_desc_sw128(bh_addr + k * 32), idesc, (r | k) != 0);
+                        tc5::mma_f16_ss(d_main, ad, tc5::smem_desc_sw128(bl_addr + k * 32), idesc, 1);
+                    }
+                } else {
+                    tc5::mma_f16_ss(d_min, tc5::smem_desc_sw128(a_addr), tc5::smem_desc_sw128(bh_addr), idesc, 0);
+                }
+                tc5::commit(empty_bar(stage));
+                if (r == 4) tc5::commit(tfull_bar(buf));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp & 3;                         // TMEM lane quarter this warp may read
+        const int colhalf = (warp - 8) >> 2;            // which 64 token columns
+        const int o_local = q * 32 + lane;
+        const int o = m0 + o_local;
+        const bool o_valid = o < n_out;
+        const uint8_t * hdr_base = W + (size_t)(o_valid ? o : 0) * row_bytes;
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        bool alive = true;
+        for (int sb = 0; sb < n_sb && alive; ++sb) {
+            const int buf = sb & 1, buse = sb >> 1;
+            if (!tc5::mbar_wait(tfull_bar(buf), buse & 1, abort_flag)) { alive = false; break; }
+            tc5::fence_after_sync();
+            float d = 0.f, dmin = 0.f;
+            if (o_valid) {
+                const __half2 h = *reinterpret_cast<const __half2 *>(hdr_base + (size_t)sb * 144);
+                d = __low2float(h);
+                dmin = __high2float(h);
+            }
+            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + colhalf * 64;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float v[16], w[16];
+                tc5::tmem_ld16x2(t_main + c * 16, t_main + 128 + c * 16, v, w);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[c * 16 + i] += d * v[i] - dmin * w[i];
+            }
+            tc5::fence_before_sync();
+            tc5::mbar_arrive(tempty_bar(buf));
+        }
+        if (alive && o_valid) {
+            const float b = bias ? bias[o] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                const int t = t0 + colhalf * 64 + i;
+                if (t < T) {
+                    float v = acc[i] + b;
+                    if (RESIDUAL) v += residual[(size_t)t * ldr + o];
+                    Y[(size_t)t * ldy + o] = v;
+                }
+            }
+        }
+    }
+
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (warp == 16) {
+        tc5::fence_after_sync();
+        tc5::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (tid == 0 && *abort_flag) atomicExch(error_flag, 1);
+}
+
+} // namespace
+
+bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x) {
+    return w.type == GGML_Q4_K && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in;
+}
+
+void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
+                         const float * residual, int ldr, int * error_flag, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(gemm_q4k_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_q4k_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        configured = true;
+    }
+    const dim3 grid((w.n_out + BM - 1) / BM, (n_tokens + BN - 1) / BN);
+    if (residual) {
+        gemm_q4k_tc5_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
+                                                                        residual, ldr, error_flag);
+    } else {
+        gemm_q4k_tc5_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
+                                                                         nullptr, 0, error_flag);
+    }
+}
+
+} // namespace rb200

@@ -121,6 +121,11 @@ void launch_gemm_mma(const WeightView & w, const __half * x16, int ldx, int n_to
 bool gemm_q4k_exact_supported(const WeightView & w, const SplitAct & x);
 void launch_gemm_q4k_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
                            const float * residual, int ldr, cudaStream_t stream);
+// tcgen05 / tensor-memory variant of the exact GEMM (128 x 128 tiles). `error_flag` (device int) is
+// raised if a pipeline wait inside the kernel timed out.
+bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x);
+void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
+                         const float * residual, int ldr, int * error_flag, cudaStream_t stream);
 // In-place RoPE on q and k (inside the fused qkv buffer) and the f16 store of k, v into the paged cache.
 void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
                        const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream);

@@ -12,7 +12,7 @@ using namespace rb200;
 extern "C" {
 
 // y[t][o] = sum_k deq(w)[o][k] x[t][k]. `path`: 0 = what the engine would pick, 1 = f32 row kernel,
-// 2 = single-term f16 tensor-core kernel, 3 = exact tensor-core kernel. The kernel runs `iters`
+// 2 = single-term f16 tensor-core kernel, 3 = exact tensor-core kernel (mma.sync), 4 = exact tcgen05 kernel. The kernel runs `iters`
 // times; *out_ms receives the mean device time per launch (CUDA events on the launching stream).
 int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, uint32_t n_in, const float * x, uint32_t n_tokens, float * y,
                        int path, uint32_t iters, float * out_ms) {
@@ -46,6 +46,14 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         if (have_split) launch_split_prep(dx.ptr, (int)n_in, (int)n_in, (int)n_tokens, xs.view, stream);
         int chosen = path;
         if (chosen == 0) chosen = have_split && n_tokens > 8 && gemm_q4k_exact_supported(wv, xs.view) ? 3 : 1;
+        DeviceBuffer<int> flag;
+        flag.ensure(1);
+        RB_CUDA(cudaMemsetAsync(flag.ptr, 0, sizeof(int), stream));
+        if (chosen == 4 && !(have_split && gemm_q4k_tc5_supported(wv, xs.view))) {
+            cudaStreamDestroy(stream);
+            set_error("op_gemm: the requested kernel does not cover this type or shape");
+            return STATUS_INVALID_ARGUMENT;
+        }
         if ((chosen == 3 && !(have_split && gemm_q4k_exact_supported(wv, xs.view))) ||
             (chosen == 2 && !(have_split && gemm_mma_supported(wv, (int)n_in)))) {
             cudaStreamDestroy(stream);
@@ -53,7 +61,8 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             return STATUS_INVALID_ARGUMENT;
         }
         auto run = [&]() {
-            if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
+            if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, stream);
+            else if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 2) launch_gemm_mma(wv, xs.view.hi, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else launch_gemm_rows(wv, dx.ptr, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
         };
@@ -62,8 +71,15 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         for (uint32_t i = 0; i < iters; ++i) run();
         RB_CUDA(cudaEventRecord(e1, stream));
         RB_CUDA(cudaMemcpyAsync(y, dy.ptr, (size_t)n_tokens * n_out * 4, cudaMemcpyDeviceToHost, stream));
+        int h_flag = 0;
+        RB_CUDA(cudaMemcpyAsync(&h_flag, flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream));
         RB_CUDA(cudaStreamSynchronize(stream));
         RB_CUDA(cudaGetLastError());
+        if (h_flag) {
+            cudaStreamDestroy(stream);
+            set_error("op_gemm: a pipeline wait inside the tensor-core kernel timed out");
+            return STATUS_RUNTIME;
+        }
         float ms = 0.f;
         if (iters) cudaEventElapsedTime(&ms, e0, e1);
         if (out_ms) *out_ms = iters ? ms / iters : 0.f;

@@ -29,3 +29,17 @@ def test_q4k_gemm_kernels_against_the_oracle(rb, oracle, n_out, n_in, T):
     print(f"q4k {n_out}x{n_in} T={T}: rel err rows={e_rows:.2e} exact={e_exact:.2e} single-term f16={e_fast:.2e}")
     assert e_rows < 4e-6 and e_exact < 4e-6
     assert e_fast < 3e-3
+
+
+@pytest.mark.parametrize("n_out,n_in,T", [(128, 256, 128), (256, 512, 130), (200, 768, 33), (512, 2048, 100), (256, 4096, 300)])
+def test_q4k_tcgen05_gemm_against_float64(rb, oracle, n_out, n_in, T):
+    """The tcgen05 / tensor-memory kernel computes the same exact products as the mma.sync one."""
+    rng = np.random.default_rng(7 * n_out + T)
+    raw = _q4k_matrix(rb, rng, n_out, n_in)
+    x = rng.normal(0, 1.5, (T, n_in)).astype(np.float32)
+    w = oracle.dequantize_row(oracle.T_Q4_K, raw, n_out * n_in).reshape(n_out, n_in).astype(np.float64)
+    want = x.astype(np.float64) @ w.T
+    got, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=4)
+    err = float(np.abs(got - want).max()) / float(np.abs(want).max())
+    print(f"q4k tcgen05 {n_out}x{n_in} T={T}: rel err {err:.2e}")
+    assert err < 4e-6
