@@ -99,6 +99,7 @@ struct SplitBuffer {
         view.sum_hi = store.ptr + 2 * main;
         view.sum_lo = store.ptr + 2 * main + sums + 32;
         view.ld = (int)ld;
+        split_act_encode_maps(view, rows);
     }
     const SplitAct * get() const { return view.hi ? &view : nullptr; }
 };

@@ -6,8 +6,8 @@
 //
 // One CTA computes 128 weight rows x 128 tokens. Warp roles (17 warps):
 //   0-3, 4-7   two producer groups, alternating pipeline stages: thread p decodes the 64 weights of
-//              row p into the K-major 128B-swizzled A tile and copies the activation rows of token p
-//              (hi and lo) with cp.async into the B tiles;
+//              row p into the K-major 128B-swizzled A tile; one thread of the group fetches the two
+//              activation tiles (hi and lo) with TMA, whose bytes complete on the stage's barrier;
 //   16         lane 0 issues the MMAs (M 128, N 128, K 16) and commits them to the stage's
 //              "empty" barrier, and per super-block to the accumulator's "full" barrier;
 //   8-11,12-15 epilogue: each thread owns one weight row and 64 token columns, pulls both TMEM
@@ -28,7 +28,7 @@ namespace rb200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
+constexpr int BM = 128, BN = 128;
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
 constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
@@ -49,8 +49,8 @@ __device__ __forceinline__ void nibbles_times_scale(uint32_t word, int hi, __hal
 }
 
 template <bool RESIDUAL>
-__global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes, SplitAct X,
-                                                                  int T, float * __restrict__ Y, int ldy, const float * __restrict__ bias,
+__global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes,
+                                                                  const __grid_constant__ SplitAct X, int T, float * __restrict__ Y, int ldy, const float * __restrict__ bias,
                                                                   const float * __restrict__ residual, int ldr, int * __restrict__ error_flag) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -65,14 +65,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
     volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_word + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int m0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
+    const int m0 = blockIdx.y * BM, t0 = blockIdx.x * BN;   // token tiles vary fastest: CTAs in flight share a weight tile in L2
     const int n_sb = n_in / 256;
     const int n_it = n_sb * 5;
     const int n_sub = n_in / 32;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            tc5::mbar_init(full_bar(s), 128);
+            tc5::mbar_init(full_bar(s), 128);   // the producer group's threads; the TMA bytes are tracked as transactions
             tc5::mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -96,43 +96,61 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         const uint8_t * a_base = W + (size_t)(m0 + (a_valid ? p : 0)) * row_bytes;
         const int t = t0 + p;
         const bool t_valid = t < T;
-        for (int it = group; it < n_it; it += 2) {
+        // Raw block bytes are prefetched into registers two own stages ahead, so the HBM latency of
+        // the weights never holds a pipeline slot; a slot is only held for the L2 latency of the
+        // activation copy, which overlaps the decode.
+        struct Raw { uint4 hdr, q0, q1; };
+        auto prefetch = [&](int it, Raw & raw) {
+            if (it >= n_it) return;
+            const int sb = it / 5, r = it % 5;
+            const uint8_t * blk = a_base + (size_t)sb * 144;
+            raw.hdr = a_valid ? *reinterpret_cast<const uint4 *>(blk) : make_uint4(0, 0, 0, 0);
+            if (r < 4) {
+                if (a_valid) {
+                    const uint4 * qs = reinterpret_cast<const uint4 *>(blk + 16 + r * 32);
+                    raw.q0 = qs[0];
+                    raw.q1 = qs[1];
+                }
+            } else {
+                raw.q0 = raw.q1 = make_uint4(0, 0, 0, 0);
+                if (t_valid) {
+                    raw.q0 = *reinterpret_cast<const uint4 *>(X.sum_hi + (size_t)t * n_sub + sb * 8);
+                    raw.q1 = *reinterpret_cast<const uint4 *>(X.sum_lo + (size_t)t * n_sub + sb * 8);
+                }
+            }
+        };
+        // returns false when the pipeline was aborted
+        auto produce = [&](int it, Raw & raw) -> bool {
             const int stage = it % STAGES, use = it / STAGES;
-            if (!tc5::mbar_wait(empty_bar(stage), (use & 1) ^ 1, abort_flag)) break;
+            if (!tc5::mbar_wait(empty_bar(stage), (use & 1) ^ 1, abort_flag)) return false;
             const int sb = it / 5, r = it % 5;
             uint8_t * a_s = smem + stage * STAGE_BYTES;
             uint8_t * bh_s = a_s + A_BYTES;
-            const uint8_t * blk = a_base + (size_t)sb * 144;
             if (r < 4) {
-                const int k0 = sb * 256 + r * 64;
-                const uint32_t bh = smem_u32(bh_s), bl = bh + B_BYTES;
-                const size_t xoff = (size_t)(t_valid ? t : 0) * X.ld + k0;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    cp_async16(bh + swz(p, c), X.hi + xoff + c * 8, t_valid ? 16 : 0);
-                    cp_async16(bl + swz(p, c), X.lo + xoff + c * 8, t_valid ? 16 : 0);
+                if (p == 0) {
+                    // the activation tiles (hi and lo, 128 tokens x 64 columns each) arrive by TMA
+                    const uint32_t bh = smem_u32(bh_s), bl = bh + B_BYTES;
+                    tc5::mbar_expect_tx(full_bar(stage), 2 * B_BYTES);
+                    tc5::tma_load_2d(bh, &X.map_hi, sb * 256 + r * 64, t0, full_bar(stage));
+                    tc5::tma_load_2d(bl, &X.map_lo, sb * 256 + r * 64, t0, full_bar(stage));
                 }
-                cp_async_commit();
                 uint4 out[8];
                 if (a_valid) {
-                    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-                    const uint4 * qs = reinterpret_cast<const uint4 *>(blk + 16 + r * 32);
-                    const uint4 q0 = qs[0], q1 = qs[1];
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         uint32_t sc, mn;
-                        q4k_scale_min_regs(hdr, r * 2 + half, sc, mn);
+                        q4k_scale_min_regs(raw.hdr, r * 2 + half, sc, mn);
                         const __half2 sc2 = __half2half2(__ushort2half_rn((unsigned short)sc));
                         const __half2 off2 = __half2half2(__float2half_rn(-1024.0f * (float)sc));
                         uint4 * o = out + half * 4;
-                        nibbles_times_scale(q0.x, half, sc2, off2, o[0].x, o[0].y);
-                        nibbles_times_scale(q0.y, half, sc2, off2, o[0].z, o[0].w);
-                        nibbles_times_scale(q0.z, half, sc2, off2, o[1].x, o[1].y);
-                        nibbles_times_scale(q0.w, half, sc2, off2, o[1].z, o[1].w);
-                        nibbles_times_scale(q1.x, half, sc2, off2, o[2].x, o[2].y);
-                        nibbles_times_scale(q1.y, half, sc2, off2, o[2].z, o[2].w);
-                        nibbles_times_scale(q1.z, half, sc2, off2, o[3].x, o[3].y);
-                        nibbles_times_scale(q1.w, half, sc2, off2, o[3].z, o[3].w);
+                        nibbles_times_scale(raw.q0.x, half, sc2, off2, o[0].x, o[0].y);
+                        nibbles_times_scale(raw.q0.y, half, sc2, off2, o[0].z, o[0].w);
+                        nibbles_times_scale(raw.q0.z, half, sc2, off2, o[1].x, o[1].y);
+                        nibbles_times_scale(raw.q0.w, half, sc2, off2, o[1].z, o[1].w);
+                        nibbles_times_scale(raw.q1.x, half, sc2, off2, o[2].x, o[2].y);
+                        nibbles_times_scale(raw.q1.y, half, sc2, off2, o[2].z, o[2].w);
+                        nibbles_times_scale(raw.q1.z, half, sc2, off2, o[3].x, o[3].y);
+                        nibbles_times_scale(raw.q1.w, half, sc2, off2, o[3].z, o[3].w);
                     }
                 } else {
 #pragma unroll
@@ -140,18 +158,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
                 }
 #pragma unroll
                 for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(a_s + swz(p, c)) = out[c];
-                cp_async_wait<0>();
+                prefetch(it + 4, raw);
             } else {
-                // minimum-term stage: one K = 16 step
+                // minimum-term stage: one K = 16 step, A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]
                 uint4 mv = make_uint4(0, 0, 0, 0);
                 if (a_valid) {
-                    const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
                     uint32_t mw[4];
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         uint32_t s0, n0, s1, n1;
-                        q4k_scale_min_regs(hdr, 2 * q, s0, n0);
-                        q4k_scale_min_regs(hdr, 2 * q + 1, s1, n1);
+                        q4k_scale_min_regs(raw.hdr, 2 * q, s0, n0);
+                        q4k_scale_min_regs(raw.hdr, 2 * q + 1, s1, n1);
                         const __half2 pr = __halves2half2(__ushort2half_rn((unsigned short)n0), __ushort2half_rn((unsigned short)n1));
                         mw[q] = *reinterpret_cast<const uint32_t *>(&pr);
                     }
@@ -159,18 +176,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
                 }
                 *reinterpret_cast<uint4 *>(a_s + swz(p, 0)) = mv;
                 *reinterpret_cast<uint4 *>(a_s + swz(p, 1)) = mv;
-                uint4 sh = make_uint4(0, 0, 0, 0), sl = make_uint4(0, 0, 0, 0);
-                if (t_valid) {
-                    sh = *reinterpret_cast<const uint4 *>(X.sum_hi + (size_t)t * n_sub + sb * 8);
-                    sl = *reinterpret_cast<const uint4 *>(X.sum_lo + (size_t)t * n_sub + sb * 8);
-                }
-                *reinterpret_cast<uint4 *>(bh_s + swz(p, 0)) = sh;
-                *reinterpret_cast<uint4 *>(bh_s + swz(p, 1)) = sl;
+                *reinterpret_cast<uint4 *>(bh_s + swz(p, 0)) = raw.q0;
+                *reinterpret_cast<uint4 *>(bh_s + swz(p, 1)) = raw.q1;
+                prefetch(it + 4, raw);
             }
             tc5::fence_proxy_async();
             tc5::mbar_arrive(full_bar(stage));
+            return true;
+        };
+        Raw raw0, raw1;
+        prefetch(group, raw0);
+        prefetch(group + 2, raw1);
+        for (int it = group; it < n_it; it += 4) {
+            if (!produce(it, raw0)) break;
+            if (it + 2 < n_it && !produce(it + 2, raw1)) break;
         }
-        cp_async_wait<0>();
     } else if (warp == 16) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
@@ -260,8 +280,39 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
 
 } // namespace
 
+bool split_act_encode_maps(SplitAct & s, size_t rows) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                 CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    static bool looked = false;
+    s.has_maps = 0;
+    if (!looked) {
+        looked = true;
+        void * fn = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query) == cudaSuccess &&
+            query == cudaDriverEntryPointSuccess) {
+            encode = reinterpret_cast<EncodeFn>(fn);
+        }
+    }
+    if (!encode || !s.hi || s.ld % 64 != 0 || rows == 0) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)s.ld, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)s.ld * sizeof(__half)};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t elem[2] = {1, 1};
+    for (int which = 0; which < 2; ++which) {
+        const CUresult r = encode(which ? &s.map_lo : &s.map_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, which ? (void *)s.lo : (void *)s.hi, dims,
+                                  strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return false;
+    }
+    s.has_maps = 1;
+    return true;
+}
+
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x) {
-    return w.type == GGML_Q4_K && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in;
+    return w.type == GGML_Q4_K && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
 }
 
 void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
@@ -272,7 +323,7 @@ void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens,
         cudaFuncSetAttribute(gemm_q4k_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         configured = true;
     }
-    const dim3 grid((w.n_out + BM - 1) / BM, (n_tokens + BN - 1) / BN);
+    const dim3 grid((n_tokens + BN - 1) / BN, (w.n_out + BM - 1) / BM);
     if (residual) {
         gemm_q4k_tc5_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
                                                                         residual, ldr, error_flag);

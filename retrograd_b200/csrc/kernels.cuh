@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cstdint>
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -24,7 +25,15 @@ struct SplitAct {
     __half * sum_hi = nullptr;
     __half * sum_lo = nullptr;
     int ld = 0;
+    int has_maps = 0;
+    // TMA descriptors over hi and lo ([rows][ld] f16, boxes of 64 columns x 128 rows, 128-byte swizzle)
+    alignas(64) CUtensorMap map_hi;
+    alignas(64) CUtensorMap map_lo;
 };
+
+// Fills the TMA descriptors of `s` for `rows` rows; returns false when the driver entry point is
+// unavailable (the kernels that need them are then not selected).
+bool split_act_encode_maps(SplitAct & s, size_t rows);
 
 // One row of a step plan as the packing kernel reads it (32 bytes).
 struct RowDesc {
