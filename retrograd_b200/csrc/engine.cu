@@ -259,7 +259,12 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     xn_split_.ensure(T, hp.d);
     att_split_.ensure(T, hp.dq());
     if (hp.n_expert == 0) hff_split_.ensure(T, hp.ff);
-    if (const char * env = std::getenv("RB200_GEMM")) gemm_fast_f16 = std::string(env) == "fast";
+    if (const char * env = std::getenv("RB200_GEMM")) {
+        gemm_fast_f16 = std::string(env) == "fast";
+        if (std::string(env) == "mma") tc5_min_tokens = 1 << 30;     // keep the mma.sync kernels for every token count
+    }
+    device_error_.ensure(1);
+    RB_CUDA(cudaMemsetAsync(device_error_.ptr, 0, sizeof(int), stream));
     if (const char * env = std::getenv("RB200_MMA_MIN_TOKENS")) mma_min_tokens = std::atoi(env);
     if (hp.n_expert == 0) {
         gu_.ensure(T * 2 * hp.ff);
@@ -323,6 +328,8 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
     prof_.begin(K_GEMM, stream);
     if (xs && T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) {
         launch_gemm_mma(w, xs->hi, ldx, T, y, ldy, bias, residual, ldr, stream);
+    } else if (xs && T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) {
+        launch_gemm_q4k_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, stream);
     } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {
         launch_gemm_q4k_exact(w, *xs, T, y, ldy, bias, residual, ldr, stream);
     } else {
@@ -778,6 +785,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
 #undef RB_K
     RB_CUDA(cudaEventRecord(ev_end_, stream));
     if (S) RB_CUDA(cudaMemcpyAsync(h_result_, d_result_.ptr, res_total - 16, cudaMemcpyDeviceToHost, stream));
+    RB_CUDA(cudaMemcpyAsync(h_result_ + result_bytes_ - 16, device_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream));
     const cudaError_t sync = cudaStreamSynchronize(stream);
     if (sync != cudaSuccess) {
         set_error(std::string("the decode failed on the device (") + cudaGetErrorString(sync) +
@@ -788,6 +796,12 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     const cudaError_t launch_status = cudaGetLastError();
     if (launch_status != cudaSuccess) {
         set_error(std::string("a kernel of the step failed to launch: ") + cudaGetErrorString(launch_status));
+        return STATUS_RUNTIME;
+    }
+    if (*reinterpret_cast<const int *>(h_result_ + result_bytes_ - 16) != 0) {
+        cudaMemsetAsync(device_error_.ptr, 0, sizeof(int), stream);
+        set_error("the decode failed on the device: a pipeline wait inside a tensor-core kernel timed out; the KV may hold a prefix of "
+                  "the submitted tokens (query it with the seq_pos entry point)");
         return STATUS_RUNTIME;
     }
     cudaEventElapsedTime(&last_ms, ev_begin_, ev_end_);

@@ -225,6 +225,7 @@ public:
     uint64_t last_launches = 0;
     // steps with more tokens than this take the tensor-core GEMM (f16 operands); fewer take the f32 row kernel
     int mma_min_tokens = 8;
+    int tc5_min_tokens = 64;      // above this the tcgen05 kernel (128-token tiles) takes over from mma.sync
     bool gemm_fast_f16 = false;   // opt-in single-term f16 operands: faster, outside the 1e-2 logit tolerance on deep models
     uint64_t last_h2d_bytes = 0, last_d2h_bytes = 0;
     StepProfiler prof_;
@@ -260,6 +261,7 @@ private:
     size_t result_bytes_ = 0;
     DeviceBuffer<float> x_, xn_, qkv_, att_, gu_, hff_, hs_, router_logits_, moe_w_, pair_gu_, pair_h_, pair_y_, lora_tmp_, logits_work_;
     DeviceBuffer<int32_t> moe_ids_, d_aux_;
+    DeviceBuffer<int> device_error_;
     SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
 
