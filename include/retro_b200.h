@@ -253,6 +253,18 @@ int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uin
 int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, uint32_t n_in, const float * x, uint32_t n_tokens, float * y,
                        int path, uint32_t iters, float * out_ms);
 
+/* No counterpart in the reference. The same exact Q4_K GEMM for callers that must not allocate
+ * device memory (a host whose own pool owns the whole device budget, a loop that cannot take the
+ * synchronisation an allocation may cause): d_w (Q4_K rows), d_x (f32 [n_tokens][n_in]) and d_y
+ * (f32 [n_tokens][n_out]) are DEVICE pointers of the caller, `stream` its cudaStream_t or NULL. The
+ * scratch the kernel needs lives in a fixed array inside the library (about 4.1 MiB per GPU that
+ * loads it). Limit: n_tokens * n_in <= 1 048 576, n_in % 256 == 0; beyond it the call returns -3.
+ * The first call on a device resolves the array's address: make it before any stream capture.
+ * All calls share the array, so calls that overlap on the GPU race; nothing needs clearing between
+ * calls. The work is enqueued on `stream`; the call does not wait for it. */
+int retro_b200_gemm_q4k_noalloc(const uint8_t * d_w, uint32_t n_out, uint32_t n_in, const float * d_x, uint32_t n_tokens, float * d_y,
+                                void * stream);
+
 /* Bytes the last step copied host->device (the plan) and device->host (the sampled rows). */
 int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes);
 /* Per-class kernel timing with CUDA events on the launching stream. Classes, in order:
