@@ -51,7 +51,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_mma_kernel(const float 
     const int g = lane >> 2, tq = lane & 3;
     const int hk = blockIdx.y;
     const int G = n_head / kv.n_head_kv;
-    const int2 item = items[blockIdx.x];
+    // items are listed in row order (decode rows first, long prefill chunks last): walk them backwards so
+    // the longest-running CTAs start first and the one-token rows fill the tail
+    const int2 item = items[gridDim.x - 1 - blockIdx.x];
     const int i0 = item.x, ntok = item.y;
     const int slot = tok_slot[i0], pos0 = tok_pos[i0], pmin = tok_pos_min[i0];
     const int last = pos0 + ntok - 1;

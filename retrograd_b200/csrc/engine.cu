@@ -84,6 +84,16 @@ void Engine::load_model(const std::string & path) {
         w.n_in = (uint32_t)t.ne[0];
         w.n_out = (uint32_t)rows;
         w.row_bytes = (uint32_t)row_bytes(t.type, t.ne[0]);
+        if (t.type == GGML_Q4_K && t.ne.size() == 2 && w.n_in % 256 == 0 && rows >= 128) {
+            // second copy regrouped for the tcgen05 kernel's coalesced weight stream
+            void * tiled = nullptr;
+            const size_t bytes = q4k_tiled_bytes(w.n_out, w.n_in);
+            RB_CUDA(cudaMalloc(&tiled, bytes));
+            m.allocations.push_back(tiled);
+            launch_q4k_retile(dev, w.n_out, w.n_in, w.row_bytes, static_cast<uint8_t *>(tiled), stream);
+            w.tiled = static_cast<const uint8_t *>(tiled);
+            m.tiled_bytes += bytes;
+        }
         return w;
     };
     auto matrix = [&](const std::string & name, uint64_t n_in, uint64_t n_out) {

@@ -142,6 +142,7 @@ struct Model {
     DeviceBuffer<float> inv_freq;
     std::vector<void *> allocations;
     uint64_t weight_bytes = 0;
+    uint64_t tiled_bytes = 0;
     std::vector<std::string> vocab_tokens;
     std::vector<int32_t> vocab_types;
     int32_t eos = 2, bos = 1;

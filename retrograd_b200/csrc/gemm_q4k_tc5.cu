@@ -48,6 +48,29 @@ __device__ __forceinline__ void nibbles_times_scale(uint32_t word, int hi, __hal
     out23 = __byte_perm(ua, ub, 0x7632);
 }
 
+// grid (super-blocks, row tiles), 128 threads: thread p moves the 144-byte block of row p
+__global__ void q4k_retile_kernel(const uint8_t * __restrict__ rows, uint32_t n_out, uint32_t n_sb, uint32_t row_bytes, uint8_t * __restrict__ tiled) {
+    const uint32_t sb = blockIdx.x, tile = blockIdx.y, p = threadIdx.x;
+    const uint32_t row = tile * 128 + p;
+    uint8_t * dst = tiled + ((size_t)tile * n_sb + sb) * kQ4kTileBytes;
+    uint4 v[9];
+    if (row < n_out) {
+        const uint4 * src = reinterpret_cast<const uint4 *>(rows + (size_t)row * row_bytes + (size_t)sb * 144);
+#pragma unroll
+        for (int i = 0; i < 9; ++i) v[i] = src[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < 9; ++i) v[i] = make_uint4(0, 0, 0, 0);
+    }
+    *reinterpret_cast<uint4 *>(dst + p * 16) = v[0];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        uint4 * q = reinterpret_cast<uint4 *>(dst + 2048 + r * 4096 + p * 32);
+        q[0] = v[1 + 2 * r];
+        q[1] = v[2 + 2 * r];
+    }
+}
+
 template <bool RESIDUAL>
 __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes,
                                                                   const __grid_constant__ SplitAct X, int T, float * __restrict__ Y, int ldy, const float * __restrict__ bias,
@@ -92,8 +115,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         // ------------------------------------------------------------------ producers
         const int group = warp >> 2;
         const int p = tid & 127;                       // weight row and token row of this thread
-        const bool a_valid = m0 + p < n_out;
-        const uint8_t * a_base = W + (size_t)(m0 + (a_valid ? p : 0)) * row_bytes;
+        const bool a_valid = true;                     // the tiled layout is zero-padded to whole row tiles
+        const uint8_t * tile_base = W + (size_t)blockIdx.y * n_sb * kQ4kTileBytes;
         const int t = t0 + p;
         const bool t_valid = t < T;
         // Raw block bytes are prefetched into registers two own stages ahead, so the HBM latency of
@@ -103,14 +126,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         auto prefetch = [&](int it, Raw & raw) {
             if (it >= n_it) return;
             const int sb = it / 5, r = it % 5;
-            const uint8_t * blk = a_base + (size_t)sb * 144;
-            raw.hdr = a_valid ? *reinterpret_cast<const uint4 *>(blk) : make_uint4(0, 0, 0, 0);
+            const uint8_t * blk = tile_base + (size_t)sb * kQ4kTileBytes;
+            raw.hdr = *reinterpret_cast<const uint4 *>(blk + p * 16);      // consecutive threads, consecutive bytes
             if (r < 4) {
-                if (a_valid) {
-                    const uint4 * qs = reinterpret_cast<const uint4 *>(blk + 16 + r * 32);
-                    raw.q0 = qs[0];
-                    raw.q1 = qs[1];
-                }
+                const uint4 * qs = reinterpret_cast<const uint4 *>(blk + 2048 + r * 4096 + p * 32);
+                raw.q0 = qs[0];
+                raw.q1 = qs[1];
             } else {
                 raw.q0 = raw.q1 = make_uint4(0, 0, 0, 0);
                 if (t_valid) {
@@ -229,7 +250,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         const int o_local = q * 32 + lane;
         const int o = m0 + o_local;
         const bool o_valid = o < n_out;
-        const uint8_t * hdr_base = W + (size_t)(o_valid ? o : 0) * row_bytes;
+        const uint8_t * hdr_base = W + (size_t)blockIdx.y * n_sb * kQ4kTileBytes + (size_t)o_local * 16;
         float acc[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
@@ -240,7 +261,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
             tc5::fence_after_sync();
             float d = 0.f, dmin = 0.f;
             if (o_valid) {
-                const __half2 h = *reinterpret_cast<const __half2 *>(hdr_base + (size_t)sb * 144);
+                const __half2 h = *reinterpret_cast<const __half2 *>(hdr_base + (size_t)sb * kQ4kTileBytes);
                 d = __low2float(h);
                 dmin = __high2float(h);
             }
@@ -312,7 +333,11 @@ bool split_act_encode_maps(SplitAct & s, size_t rows) {
 }
 
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x) {
-    return w.type == GGML_Q4_K && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
+    return w.type == GGML_Q4_K && w.tiled && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
+}
+
+void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream) {
+    q4k_retile_kernel<<<dim3(n_in / 256, (n_out + 127) / 128), 128, 0, stream>>>(rows, n_out, n_in / 256, row_bytes, tiled);
 }
 
 void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
@@ -325,10 +350,10 @@ void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens,
     }
     const dim3 grid((n_tokens + BN - 1) / BN, (w.n_out + BM - 1) / BM);
     if (residual) {
-        gemm_q4k_tc5_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
+        gemm_q4k_tc5_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
                                                                         residual, ldr, error_flag);
     } else {
-        gemm_q4k_tc5_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
+        gemm_q4k_tc5_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
                                                                          nullptr, 0, error_flag);
     }
 }

@@ -15,7 +15,16 @@ struct WeightView {
     uint32_t n_in = 0;
     uint32_t n_out = 0;
     uint32_t row_bytes = 0;
+    // Q4_K only, optional: the same blocks regrouped for the tcgen05 kernel. Per (128-row tile,
+    // 256-column super-block) 18432 contiguous bytes: 128 headers of 16 B (d, dmin, scales), then for
+    // each of the four 64-column groups 128 x 32 B of nibbles. Rows are padded to a multiple of 128.
+    const uint8_t * tiled = nullptr;
 };
+
+constexpr size_t kQ4kTileBytes = 18432;
+inline size_t q4k_tiled_bytes(uint32_t n_out, uint32_t n_in) { return (size_t)((n_out + 127) / 128) * (n_in / 256) * kQ4kTileBytes; }
+// Regroups GGUF-layout Q4_K rows into the tiled layout (device to device).
+void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream);
 
 // An activation matrix [t][ld] prepared for the exact tensor-core GEMM: the two-term f16 split
 // x = hi + lo, and per 32-element sub-block the sum of x, again as hi + lo ([t][ld / 32]).

@@ -42,10 +42,16 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         wv.n_in = n_in;
         wv.n_out = n_out;
         wv.row_bytes = (uint32_t)rb;
+        DeviceBuffer<uint8_t> dtiled;
+        if (ggml_type == GGML_Q4_K && n_in % 256 == 0 && (path == 4 || path == 0)) {
+            dtiled.ensure(q4k_tiled_bytes(n_out, n_in));
+            launch_q4k_retile(dw.ptr, n_out, n_in, (uint32_t)rb, dtiled.ptr, stream);
+            wv.tiled = dtiled.ptr;
+        }
         const bool have_split = xs.get() != nullptr;
         if (have_split) launch_split_prep(dx.ptr, (int)n_in, (int)n_in, (int)n_tokens, xs.view, stream);
         int chosen = path;
-        if (chosen == 0) chosen = have_split && n_tokens > 8 && gemm_q4k_exact_supported(wv, xs.view) ? 3 : 1;
+        if (chosen == 0) chosen = have_split && n_tokens > 64 && gemm_q4k_tc5_supported(wv, xs.view) ? 4 : have_split && n_tokens > 8 && gemm_q4k_exact_supported(wv, xs.view) ? 3 : 1;
         DeviceBuffer<int> flag;
         flag.ensure(1);
         RB_CUDA(cudaMemsetAsync(flag.ptr, 0, sizeof(int), stream));
