@@ -36,7 +36,7 @@ template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS) attention_mma_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer,
                                                                     const int2 * __restrict__ items, const int32_t * __restrict__ tok_slot,
                                                                     const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min,
-                                                                    float * __restrict__ out, int ldo) {
+                                                                    float * __restrict__ out, int ldo, int skip_small) {
     constexpr int PANELS = HD / 64;            // 128-byte panels per row
     constexpr int KSTEPS = HD / 16;
     constexpr int NT = HD / 8;
@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_mma_kernel(const float 
     // the longest-running CTAs start first and the one-token rows fill the tail
     const int2 item = items[gridDim.x - 1 - blockIdx.x];
     const int i0 = item.x, ntok = item.y;
+    if (skip_small && ntok * G <= 16) return;       // served by the split-KV kernel below
     const int slot = tok_slot[i0], pos0 = tok_pos[i0], pmin = tok_pos_min[i0];
     const int last = pos0 + ntok - 1;
     const int32_t * table = kv.block_table + (size_t)slot * kv.max_blocks;
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_mma_kernel(const float 
 
 template <int HD>
 void launch_hd(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
-               const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream) {
+               const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int skip_small, cudaStream_t stream) {
     constexpr int smem = 2 * (HD / 64) * ATT_ROWS * 128 + ATT_STAGES * 2 * (HD / 64) * 16 * 128;
     static bool configured = false;
     if (!configured) {
@@ -249,7 +250,7 @@ void launch_hd(const float * qkv, int ld, int n_head, KvLayout kv, int layer, co
         configured = true;
     }
     attention_mma_kernel<HD><<<dim3(n_items, kv.n_head_kv), ATT_THREADS, smem, stream>>>(qkv, ld, n_head, kv, layer, items, tok_slot, tok_pos,
-                                                                                       tok_pos_min, out, ldo);
+                                                                                       tok_pos_min, out, ldo, skip_small);
 }
 
 } // namespace
@@ -260,10 +261,10 @@ bool attention_mma_supported(int n_head, int n_head_kv, int head_dim, int block_
 }
 
 void launch_attention_mma(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
-                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream) {
+                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, bool skip_small, cudaStream_t stream) {
     if (n_items <= 0) return;
-    if (kv.head_dim == 128) launch_hd<128>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, stream);
-    else launch_hd<64>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, stream);
+    if (kv.head_dim == 128) launch_hd<128>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, skip_small, stream);
+    else launch_hd<64>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, skip_small, stream);
 }
 
 } // namespace rb200

@@ -711,7 +711,12 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     }
     RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, attn_tile_tokens_, maps, stream));
     int n_attn_items = 0;
-    for (size_t r = 0; r < R; ++r) n_attn_items += ((int)rows[r].n + attn_tile_tokens_ - 1) / attn_tile_tokens_;
+    bool any_wide_item = false;
+    const int attn_group = (int)(hp.n_head / hp.n_head_kv);
+    for (size_t r = 0; r < R; ++r) {
+        n_attn_items += ((int)rows[r].n + attn_tile_tokens_ - 1) / attn_tile_tokens_;
+        any_wide_item = any_wide_item || (int)rows[r].n * attn_group > 16;
+    }
     cur_tok_adapter_ = maps.tok_adapter;
     cur_any_adapter_ = any_adapter;
 
@@ -741,8 +746,10 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         RB_K(K_OTHER, 1, launch_rope_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox,
                                            model->inv_freq.ptr, maps.tok_pos, maps.tok_cell, kvl, (int)l, stream));
         if (attn_mma_) {
-            RB_K(K_ATTN, 1, launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot,
-                                                 maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, stream));
+            RB_K(K_ATTN, 2, if (any_wide_item) launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
+                                                                    maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, true, stream);
+                 launch_attention_decode(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot, maps.tok_pos,
+                                         maps.tok_pos_min, att_.ptr, dq, stream));
             if (att_split_.get()) RB_K(K_OTHER, 1, launch_split_prep(att_.ptr, dq, dq, Ti, att_split_.view, stream));
         } else {
             RB_K(K_ATTN, 1, launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min,

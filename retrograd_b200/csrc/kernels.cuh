@@ -153,8 +153,13 @@ void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, K
 void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream);
 // Tensor-core paged attention (head_dim 64 or 128, 16-token KV blocks, power-of-two GQA group).
 bool attention_mma_supported(int n_head, int n_head_kv, int head_dim, int block_tokens);
+// `skip_small`: leave items of at most 16 query vectors to launch_attention_decode.
 void launch_attention_mma(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
-                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream);
+                          const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, bool skip_small, cudaStream_t stream);
+// Items of at most 16 query vectors (decode rows): the CTA's four warps split the KV blocks.
+void launch_attention_decode(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items,
+                             const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo,
+                             cudaStream_t stream);
 // h[t][i] = silu(gu[t][i]) * gu[t][ff + i]
 void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split = nullptr);
 

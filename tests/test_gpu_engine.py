@@ -98,10 +98,16 @@ def test_prefix_copy_continuation_equals_cold_and_oracle(rb, oracle, pair):
     # the source continues independently with other tokens
     toks = check_step(rb, engine, octx, oracle, [rb.StepRow(2, 0, _prompt(12, 5), 37, sample=True, sampling=g)], out, rep)
     expect_greedy(oracle, toks, rep)
-    # cold run of the whole prompt in a fresh slot
-    check_step(rb, engine, octx, oracle, [rb.StepRow(3, 2, prompt, 0, sample=True, sampling=g)], out, rep)
+    # cold run in a fresh slot with the same step shapes: bit-identical logits (shared blocks + the
+    # copied boundary block hold exactly what a cold prefill writes)
+    check_step(rb, engine, octx, oracle, [rb.StepRow(3, 2, prompt[:37], 0)], out, rep)
+    check_step(rb, engine, octx, oracle, [rb.StepRow(3, 2, prompt[37:], 37, sample=True, sampling=g)], out, rep)
     cold = engine.last_logits(0)
     assert np.array_equal(warm, cold)
+    # one-shot prefill of the whole prompt: other kernels, other summation order - same greedy token
+    check_step(rb, engine, octx, oracle, [rb.StepRow(4, 3, prompt, 0, sample=True, sampling=g)], out, rep)
+    one_shot = engine.last_logits(0)
+    assert int(np.argmax(one_shot)) == int(np.argmax(warm)) and np.abs(one_shot - warm).max() < 1e-3
 
 
 def test_seq_rm_ranges_and_memory_accounting(rb, oracle, pair):
@@ -123,8 +129,12 @@ def test_seq_rm_ranges_and_memory_accounting(rb, oracle, pair):
     toks = check_step(rb, engine, octx, oracle, [rb.StepRow(0, 0, prompt[30:], 30, sample=True, sampling=g)], out, rep)
     expect_greedy(oracle, toks, rep)
     again = engine.last_logits(0)
-    check_step(rb, engine, octx, oracle, [rb.StepRow(1, 1, prompt, 0, sample=True, sampling=g)], out, rep)
+    # the same two steps in a fresh slot give the same bits; a one-shot prefill the same token
+    check_step(rb, engine, octx, oracle, [rb.StepRow(1, 1, prompt[:30], 0)], out, rep)
+    check_step(rb, engine, octx, oracle, [rb.StepRow(1, 1, prompt[30:], 30, sample=True, sampling=g)], out, rep)
     assert np.array_equal(again, engine.last_logits(0))
+    check_step(rb, engine, octx, oracle, [rb.StepRow(2, 2, prompt, 0, sample=True, sampling=g)], out, rep)
+    assert int(np.argmax(engine.last_logits(0))) == int(np.argmax(again)) and np.abs(engine.last_logits(0) - again).max() < 1e-3
     engine.seq_rm(0)
     assert engine.seq_pos(0) == (-1, -1)
     engine.seq_rm(0)   # removing an empty slot is fine
