@@ -273,6 +273,12 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
         gemm_fast_f16 = std::string(env) == "fast";
         if (std::string(env) == "mma") tc5_min_tokens = 1 << 30;     // keep the mma.sync kernels for every token count
     }
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sm_, cudaDevAttrMultiProcessorCount, dev);
+        if (const char * env = std::getenv("RB200_GEMM")) stream_gemm_ = std::string(env) != "rows";
+    }
     device_error_.ensure(1);
     RB_CUDA(cudaMemsetAsync(device_error_.ptr, 0, sizeof(int), stream));
     if (const char * env = std::getenv("RB200_MMA_MIN_TOKENS")) mma_min_tokens = std::atoi(env);
@@ -338,6 +344,10 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
     prof_.begin(K_GEMM, stream);
     if (xs && T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) {
         launch_gemm_mma(w, xs->hi, ldx, T, y, ldy, bias, residual, ldr, stream);
+    } else if (xs && stream_gemm_ && gemm_q4k_stream_supported(w, *xs, T)) {
+        stream_scratch_.ensure(gemm_q4k_stream_scratch_floats(w.n_out, w.n_in));
+        launch_gemm_q4k_stream(w, *xs, T, y, ldy, bias, residual, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
+        ++last_launches;
     } else if (xs && T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) {
         launch_gemm_q4k_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, stream);
     } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {

@@ -263,6 +263,9 @@ private:
     DeviceBuffer<float> x_, xn_, qkv_, att_, gu_, hff_, hs_, router_logits_, moe_w_, pair_gu_, pair_h_, pair_y_, lora_tmp_, logits_work_;
     DeviceBuffer<int32_t> moe_ids_, d_aux_;
     DeviceBuffer<int> device_error_;
+    DeviceBuffer<float> stream_scratch_;
+    int n_sm_ = 148;
+    bool stream_gemm_ = true;
     SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
 

@@ -62,10 +62,10 @@ __global__ void q4k_retile_kernel(const uint8_t * __restrict__ rows, uint32_t n_
 #pragma unroll
         for (int i = 0; i < 9; ++i) v[i] = make_uint4(0, 0, 0, 0);
     }
-    *reinterpret_cast<uint4 *>(dst + p * 16) = v[0];
+    *reinterpret_cast<uint4 *>(dst + q4k_tile_hdr_offset(p)) = v[0];
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-        uint4 * q = reinterpret_cast<uint4 *>(dst + 2048 + r * 4096 + p * 32);
+        uint4 * q = reinterpret_cast<uint4 *>(dst + q4k_tile_group_offset(p, r));
         q[0] = v[1 + 2 * r];
         q[1] = v[2 + 2 * r];
     }
@@ -127,9 +127,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
             if (it >= n_it) return;
             const int sb = it / 5, r = it % 5;
             const uint8_t * blk = tile_base + (size_t)sb * kQ4kTileBytes;
-            raw.hdr = *reinterpret_cast<const uint4 *>(blk + p * 16);      // consecutive threads, consecutive bytes
+            raw.hdr = *reinterpret_cast<const uint4 *>(blk + q4k_tile_hdr_offset(p));      // consecutive threads, consecutive bytes
             if (r < 4) {
-                const uint4 * qs = reinterpret_cast<const uint4 *>(blk + 2048 + r * 4096 + p * 32);
+                const uint4 * qs = reinterpret_cast<const uint4 *>(blk + q4k_tile_group_offset(p, r));
                 raw.q0 = qs[0];
                 raw.q1 = qs[1];
             } else {
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         const int o_local = q * 32 + lane;
         const int o = m0 + o_local;
         const bool o_valid = o < n_out;
-        const uint8_t * hdr_base = W + (size_t)blockIdx.y * n_sb * kQ4kTileBytes + (size_t)o_local * 16;
+        const uint8_t * hdr_base = W + (size_t)blockIdx.y * n_sb * kQ4kTileBytes + q4k_tile_hdr_offset(o_local);
         float acc[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;

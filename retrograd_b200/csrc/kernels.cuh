@@ -15,13 +15,23 @@ struct WeightView {
     uint32_t n_in = 0;
     uint32_t n_out = 0;
     uint32_t row_bytes = 0;
-    // Q4_K only, optional: the same blocks regrouped for the tcgen05 kernel. Per (128-row tile,
-    // 256-column super-block) 18432 contiguous bytes: 128 headers of 16 B (d, dmin, scales), then for
-    // each of the four 64-column groups 128 x 32 B of nibbles. Rows are padded to a multiple of 128.
+    // Q4_K only, optional: the same blocks in the tile-major layout described at kQ4kTileBytes, rows
+    // zero-padded to a multiple of 128. Read by the tcgen05 kernel and the weight-streaming kernel.
     const uint8_t * tiled = nullptr;
 };
 
+// Tile-major copy of a Q4_K matrix: one 18432-byte tile per (128 rows, 256-column super-block), tiles
+// of a row tile consecutive over the super-blocks. A tile is four 4608-byte quarters of 32 rows. A
+// quarter holds, for its rows, the 32 nibble bytes of 64-column groups 0 and 1 (2 x 1024 bytes), then
+// the 32 block headers of 16 bytes (d, dmin, packed scales), then groups 2 and 3: either half of the
+// columns together with the headers is one contiguous 2560-byte range, and a warp that takes one row
+// per lane reads consecutive bytes.
 constexpr size_t kQ4kTileBytes = 18432;
+constexpr size_t kQ4kQuarterBytes = 4608;
+__host__ __device__ inline size_t q4k_tile_hdr_offset(int p) { return (size_t)(p >> 5) * kQ4kQuarterBytes + 2048 + (size_t)(p & 31) * 16; }
+__host__ __device__ inline size_t q4k_tile_group_offset(int p, int r) {
+    return (size_t)(p >> 5) * kQ4kQuarterBytes + (size_t)r * 1024 + (r >= 2 ? 512 : 0) + (size_t)(p & 31) * 32;
+}
 inline size_t q4k_tiled_bytes(uint32_t n_out, uint32_t n_in) { return (size_t)((n_out + 127) / 128) * (n_in / 256) * kQ4kTileBytes; }
 // Regroups GGUF-layout Q4_K rows into the tiled layout (device to device).
 void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream);
@@ -144,6 +154,13 @@ void launch_gemm_q4k_exact(const WeightView & w, const SplitAct & x, int n_token
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x);
 void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
                          const float * residual, int ldr, int * error_flag, cudaStream_t stream);
+// Weight-streaming exact GEMM for at most 8 tokens. `scratch` holds gemm_q4k_stream_scratch_floats()
+// floats of per-K-chunk partial sums; `n_sm` is the device's SM count (grid sizing); `error_flag` is set
+// to 1 if a bounded wait on a copy gave up.
+bool gemm_q4k_stream_supported(const WeightView & w, const SplitAct & x, int n_tokens);
+size_t gemm_q4k_stream_scratch_floats(uint32_t n_out, uint32_t n_in);
+void launch_gemm_q4k_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
+                            const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream);
 // In-place RoPE on q and k (inside the fused qkv buffer) and the f16 store of k, v into the paged cache.
 void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
                        const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream);

@@ -12,7 +12,7 @@ using namespace rb200;
 extern "C" {
 
 // y[t][o] = sum_k deq(w)[o][k] x[t][k]. `path`: 0 = what the engine would pick, 1 = f32 row kernel,
-// 2 = single-term f16 tensor-core kernel, 3 = exact tensor-core kernel (mma.sync), 4 = exact tcgen05 kernel. The kernel runs `iters`
+// 2 = single-term f16 tensor-core kernel, 3 = exact tensor-core kernel (mma.sync), 4 = exact tcgen05 kernel, 5 = exact weight-streaming kernel (at most 8 tokens). The kernel runs `iters`
 // times; *out_ms receives the mean device time per launch (CUDA events on the launching stream).
 int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, uint32_t n_in, const float * x, uint32_t n_tokens, float * y,
                        int path, uint32_t iters, float * out_ms) {
@@ -43,7 +43,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         wv.n_out = n_out;
         wv.row_bytes = (uint32_t)rb;
         DeviceBuffer<uint8_t> dtiled;
-        if (ggml_type == GGML_Q4_K && n_in % 256 == 0 && (path == 4 || path == 0)) {
+        if (ggml_type == GGML_Q4_K && n_in % 256 == 0 && (path == 4 || path == 5 || path == 0)) {
             dtiled.ensure(q4k_tiled_bytes(n_out, n_in));
             launch_q4k_retile(dw.ptr, n_out, n_in, (uint32_t)rb, dtiled.ptr, stream);
             wv.tiled = dtiled.ptr;
@@ -55,6 +55,21 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         DeviceBuffer<int> flag;
         flag.ensure(1);
         RB_CUDA(cudaMemsetAsync(flag.ptr, 0, sizeof(int), stream));
+        DeviceBuffer<float> stream_scratch;
+        int n_sm = 148;
+        {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+        }
+        if (chosen == 5) {
+            if (!(have_split && gemm_q4k_stream_supported(wv, xs.view, (int)n_tokens))) {
+                cudaStreamDestroy(stream);
+                set_error("op_gemm: the requested kernel does not cover this type or shape");
+                return STATUS_INVALID_ARGUMENT;
+            }
+            stream_scratch.ensure(gemm_q4k_stream_scratch_floats(n_out, n_in));
+        }
         if (chosen == 4 && !(have_split && gemm_q4k_tc5_supported(wv, xs.view))) {
             cudaStreamDestroy(stream);
             set_error("op_gemm: the requested kernel does not cover this type or shape");
@@ -67,14 +82,33 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             return STATUS_INVALID_ARGUMENT;
         }
         auto run = [&]() {
-            if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, stream);
+            if (chosen == 5) launch_gemm_q4k_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
+            else if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, stream);
             else if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 2) launch_gemm_mma(wv, xs.view.hi, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else launch_gemm_rows(wv, dx.ptr, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
         };
         run();   // warm-up, also the launch whose output is returned
+        // Operands that fit in L2 would be re-read from it by back-to-back launches: then every timed
+        // launch is preceded by a write of a buffer larger than L2 and timed with its own event pair.
+        const size_t operand_bytes = (size_t)row_bytes(ggml_type, n_in) * n_out + (size_t)n_tokens * n_in * 4;
+        const bool flush = iters > 0 && operand_bytes < ((size_t)256 << 20);
+        DeviceBuffer<uint8_t> flush_buf;
+        std::vector<cudaEvent_t> marks;
+        if (flush) {
+            flush_buf.ensure((size_t)256 << 20);
+            marks.resize(2 * (size_t)iters);
+            for (auto & m : marks) RB_CUDA(cudaEventCreate(&m));
+        }
         RB_CUDA(cudaEventRecord(e0, stream));
-        for (uint32_t i = 0; i < iters; ++i) run();
+        for (uint32_t i = 0; i < iters; ++i) {
+            if (flush) {
+                RB_CUDA(cudaMemsetAsync(flush_buf.ptr, (int)i, (size_t)256 << 20, stream));
+                RB_CUDA(cudaEventRecord(marks[2 * i], stream));
+            }
+            run();
+            if (flush) RB_CUDA(cudaEventRecord(marks[2 * i + 1], stream));
+        }
         RB_CUDA(cudaEventRecord(e1, stream));
         RB_CUDA(cudaMemcpyAsync(y, dy.ptr, (size_t)n_tokens * n_out * 4, cudaMemcpyDeviceToHost, stream));
         int h_flag = 0;
@@ -88,6 +122,15 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         }
         float ms = 0.f;
         if (iters) cudaEventElapsedTime(&ms, e0, e1);
+        if (flush) {
+            ms = 0.f;
+            for (uint32_t i = 0; i < iters; ++i) {
+                float one = 0.f;
+                cudaEventElapsedTime(&one, marks[2 * i], marks[2 * i + 1]);
+                ms += one;
+            }
+            for (auto & m : marks) cudaEventDestroy(m);
+        }
         if (out_ms) *out_ms = iters ? ms / iters : 0.f;
         cudaEventDestroy(e0);
         cudaEventDestroy(e1);

@@ -4,7 +4,8 @@ profiler captures of a small case.
     python -m retrograd_b200.kernel_cases gemm --n-out 28672 --n-in 4096 --tokens 2048 --path 3 --iters 5
 
 `--path`: 0 engine's choice, 1 f32 row kernel, 2 single-term f16 tensor-core kernel, 3 exact
-tensor-core kernel. Weights are random Q4_K blocks (scales pinned to small f16 values), the
+tensor-core kernel (mma.sync), 4 exact tcgen05 kernel, 5 exact weight-streaming kernel (at most 8 tokens).
+Operands smaller than 256 MB are timed with a write of a buffer larger than L2 before every launch. Weights are random Q4_K blocks (scales pinned to small f16 values), the
 activations N(0, 1). Prints the mean device time per launch and the rates derived from it.
 """
 from __future__ import annotations

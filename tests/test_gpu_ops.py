@@ -43,3 +43,20 @@ def test_q4k_tcgen05_gemm_against_float64(rb, oracle, n_out, n_in, T):
     err = float(np.abs(got - want).max()) / float(np.abs(want).max())
     print(f"q4k tcgen05 {n_out}x{n_in} T={T}: rel err {err:.2e}")
     assert err < 4e-6
+
+
+@pytest.mark.parametrize("n_out,n_in,T", [(256, 512, 1), (384, 1024, 3), (200, 768, 8), (512, 2816, 5), (1040, 4096, 8), (128, 14336, 2)])
+def test_q4k_streaming_gemm_against_float64(rb, oracle, n_out, n_in, T):
+    """The weight-streaming kernel for at most eight tokens: exact products, ragged row counts, and
+    reduction lengths that leave a partial chunk of super-blocks."""
+    rng = np.random.default_rng(11 * n_out + T)
+    raw = _q4k_matrix(rb, rng, n_out, n_in)
+    x = rng.normal(0, 1.5, (T, n_in)).astype(np.float32)
+    w = oracle.dequantize_row(oracle.T_Q4_K, raw, n_out * n_in).reshape(n_out, n_in).astype(np.float64)
+    want = x.astype(np.float64) @ w.T
+    got, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=5)
+    err = float(np.abs(got - want).max()) / float(np.abs(want).max())
+    print(f"q4k stream {n_out}x{n_in} T={T}: rel err {err:.2e}")
+    assert err < 4e-6
+    again, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=5)
+    assert np.array_equal(got, again)
