@@ -47,6 +47,14 @@ WORKLOADS = {
         spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
         n_requests=256, prompt=(64, 4096), output=(64, 512), chunk=512, n_batch=2048, n_ctx=420_000,
     ),
+    # the same model with eight long-running requests: every timed step is a pure decode step of eight
+    # tokens, the regime where the weight stream from HBM bounds the step
+    "c2_decode8": dict(
+        name="llama3-8b-shape Q4_K, 8 requests, decode-only steps of 8 tokens",
+        model="c2",
+        spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
+        n_requests=8, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=65536,
+    ),
     # BASELINE config 1 (CPU-runnable shape; used to exercise this script quickly)
     "c1": dict(
         name="tiny llama-style Q8_0, 8 requests",
@@ -58,7 +66,7 @@ WORKLOADS = {
 
 def model_path(workload: str) -> Path:
     base = Path(os.environ.get("RB200_MODEL_DIR", "/dev/shm" if Path("/dev/shm").is_dir() else "/tmp"))
-    return base / f"retrograd_b200_{workload}.gguf"
+    return base / f"retrograd_b200_{WORKLOADS[workload].get('model', workload)}.gguf"
 
 
 def ensure_model(workload: str, rank: int) -> Path:
@@ -337,6 +345,7 @@ def main():
     dev_ms, wall_s, decode_tokens, prefill_tokens, rows_per_step, launches, h2d, d2h = 0.0, 0.0, 0, 0, [], 0, 0, 0
     attn_bytes = 0
     gemm_flops = 0
+    step_tokens = 0
     kv_tok_bytes = 2 * cfg["spec"]["layers"] * cfg["spec"]["kv_heads"] * (cfg["spec"].get("head_dim") or cfg["spec"]["d"] // cfg["spec"]["heads"]) * 2
     sp = cfg["spec"]
     hd = sp.get("head_dim") or sp["d"] // sp["heads"]
@@ -354,6 +363,7 @@ def main():
         h2d += a
         d2h += b
         attn_bytes += info["ctx_tokens"] * kv_tok_bytes
+        step_tokens += info["tokens"]
         gemm_flops += 2 * (info["tokens"] * w_elems_layer * sp["layers"] + info["sampled"] * sp["d"] * sp["vocab"])
         driver.admit()
     torch.cuda.synchronize()
@@ -382,7 +392,14 @@ def main():
 
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
     top = max(("gemm", "attention"), key=lambda k: profile[k]["ms"])
-    if top == "gemm":
+    bytes_per_weight = {"q4_k": 144 / 256, "q8_0": 34 / 32, "f16": 2.0, "f32": 4.0}.get(sp["dtype"], 1.0)
+    if top == "gemm" and step_tokens / args.steps / world <= 16:
+        # few tokens per step: the launches are bound by streaming every weight byte once per step
+        weight_bytes = (sp["layers"] * w_elems_layer + sp["d"] * sp["vocab"]) * bytes_per_weight * args.steps
+        achieved = weight_bytes / (profile["gemm"]["ms"] * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "traffic": None, "kernel": "dequant-fused weight-streaming GEMM (all launches of the timed region)"}
+    elif top == "gemm":
         achieved = gemm_flops / (profile["gemm"]["ms"] * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
                 "traffic": None, "kernel": "dequant-fused weight GEMM (all launches of the timed region)"}

@@ -2,8 +2,8 @@
 // the weights, so everything is arranged around reading each weight byte once, with many bytes in
 // flight per SM, and spending as few instructions per weight as possible.
 //
-// Arithmetic is the exact scheme of gemm_q4k_exact.cu (integer sc*q operand, activations as
-// hi + lo, minimum term as one extra MMA per super-block, d and dmin applied in f32), on
+// Arithmetic follows the exact scheme of gemm_q4k_exact.cu (integer weight operand, activations as
+// hi + lo, minimum term as one extra MMA per super-block, scales, d and dmin applied in f32), on
 // mma.sync m16n8k16 with the tokens as the N = 8 dimension. With at most four tokens the hi and lo
 // terms of a token sit in two columns of the same MMA (columns t and t + 4), which halves the MMAs.
 //
@@ -12,10 +12,11 @@
 // ITS columns in registers for the whole kernel (they are the same for every weight row) and walks
 // the units of the range. Each warp runs its own ring of bulk asynchronous copies (its 2560-byte half
 // of a quarter tile of the tile-major weight copy per stage, completion counted on an mbarrier), so
-// about 120 KB of weights are in flight per SM without holding registers. Weight nibbles go from
+// about 80 KB of weights are in flight per SM without holding registers. Weight nibbles go from
 // shared memory into MMA A fragments: because the K order inside a fragment is free as long as both
-// operands agree, the four nibbles of a 32-bit word map to the fragment with one shift, four logic ops
-// and four half2 FMAs per eight weights, no byte permutes. The sixteen warps' partial sums are added
+// operands agree, and because a nibble masked in place is a valid f16 (the subnormal q * 2^-24, or
+// 16 q * 2^-24 from bits 4..7), eight weights cost one shift and four logic ops, no arithmetic and
+// no byte permutes; the 6-bit scale is applied in f32 to each 32-column sub-block's sum. The sixteen warps' partial sums are added
 // in shared memory; partial sums per K chunk go to a small scratch array and are added in a fixed
 // order (plus bias and residual) by a second tiny kernel, so results do not depend on scheduling.
 
@@ -31,9 +32,10 @@ namespace {
 constexpr int SW = 8;                      // super-blocks per K chunk
 constexpr int NWARP = 2 * SW;              // two warps per super-block
 constexpr int STHREADS = NWARP * 32;
-constexpr int STAGES = 4;                  // ring depth per warp
+constexpr int STAGES = 3;                  // ring depth per warp
+constexpr int UB = 2;                      // 32-row units per block-wide reduction
 constexpr int STAGE_BYTES = 2560;          // two 64-column groups of 32 rows + their 32 headers
-constexpr int RED_BYTES = 2 * 2 * NWARP * 128 * 4;
+constexpr int RED_BYTES = 2 * UB * 2 * NWARP * 128 * 4;
 constexpr int RING_BYTES = NWARP * STAGES * STAGE_BYTES;
 constexpr int SMEM_BYTES = RED_BYTES + RING_BYTES + NWARP * STAGES * 8 + 16;
 
@@ -42,27 +44,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void * src, uint32
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src), "r"(bytes),
                  "r"(bar)
                  : "memory");
-}
-
-// Two f16 pairs (elements 0,2 and 1,3 of each byte quad) of sc*q from one word's low nibbles, and the
-// same from its high nibbles. off_lo = -1024*sc, sc16 = sc/16, off_hi = -64*sc.
-struct Quad { uint32_t lo02, lo13, hi02, hi13; };
-__device__ __forceinline__ Quad word_to_frag(uint32_t w, __half2 sc2, __half2 off_lo, __half2 sc16, __half2 off_hi) {
-    const uint32_t u = w >> 8;
-    uint32_t a = (w & 0x000F000Fu) | 0x64006400u;     // 1024 + q          (bytes 0, 2; low nibbles)
-    uint32_t b = (u & 0x000F000Fu) | 0x64006400u;     //                   (bytes 1, 3)
-    uint32_t c = (w & 0x00F000F0u) | 0x64006400u;     // 1024 + 16 q       (bytes 0, 2; high nibbles)
-    uint32_t d = (u & 0x00F000F0u) | 0x64006400u;
-    const __half2 ha = __hfma2(*reinterpret_cast<__half2 *>(&a), sc2, off_lo);
-    const __half2 hb = __hfma2(*reinterpret_cast<__half2 *>(&b), sc2, off_lo);
-    const __half2 hc = __hfma2(*reinterpret_cast<__half2 *>(&c), sc16, off_hi);
-    const __half2 hd = __hfma2(*reinterpret_cast<__half2 *>(&d), sc16, off_hi);
-    Quad q;
-    q.lo02 = *reinterpret_cast<const uint32_t *>(&ha);
-    q.lo13 = *reinterpret_cast<const uint32_t *>(&hb);
-    q.hi02 = *reinterpret_cast<const uint32_t *>(&hc);
-    q.hi13 = *reinterpret_cast<const uint32_t *>(&hd);
-    return q;
 }
 
 struct UnitRaw {
@@ -75,7 +56,7 @@ template <bool PACK4>
 __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint8_t * __restrict__ Wt, int n_in, int n_out, SplitAct X, int T,
                                                                       float * __restrict__ partial, int units_per_cta, int * __restrict__ error_flag) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    float * red = reinterpret_cast<float *>(smem_raw);                       // [2][2][NWARP][128]
+    float * red = reinterpret_cast<float *>(smem_raw);                       // [2][UB * 2][NWARP][128]
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const uint32_t ring_base = smem_base + RED_BYTES;
     const uint32_t bar_base = ring_base + RING_BYTES;
@@ -158,50 +139,50 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
     // 2 tq and 2 tq + 1, and the byte selector that turns them into two f16 values 1024 + m
     const bool min_upper = tq >= 2;
     const uint32_t min_sel = 0x4040u | (((2 * tq) & 3) + 1) << 8 | ((2 * tq) & 3);
-    const __half2 k1024 = __float2half2_rn(1024.f), kn1024 = __float2half2_rn(-1024.f), k16th = __float2half2_rn(0.0625f),
-                  kn64 = __float2half2_rn(-64.f);
+    const __half2 k1024 = __float2half2_rn(1024.f);
 
     // the unit's contribution of this warp's 128 columns: rows g / g+8 x MMA columns 2tq, 2tq+1
     auto compute = [&](const UnitRaw & raw, float (&part)[4]) {
         // The four 6-bit scales of this half (sub-blocks 4 kh .. 4 kh + 3), one per byte, unpacked with
-        // byte-parallel logic. No integer-to-float conversion instructions: a byte b placed under the f16
-        // exponent pattern 0x64 reads as 1024 + b.
+        // byte-parallel logic; no integer-to-float conversion instructions anywhere.
         const uint32_t sc0 = kh ? ((raw.hdr0.w & 0x0F0F0F0Fu) | ((raw.hdr0.y >> 2) & 0x30303030u)) : (raw.hdr0.y & 0x3F3F3F3Fu);
         const uint32_t sc1 = kh ? ((raw.hdr1.w & 0x0F0F0F0Fu) | ((raw.hdr1.y >> 2) & 0x30303030u)) : (raw.hdr1.y & 0x3F3F3F3Fu);
-        auto scale2 = [&](uint32_t packed, int j) -> __half2 {       // (sc_j, sc_j) as f16
-            const uint32_t v = __byte_perm(packed, 0x64646464u, 0x4040u | (j << 8) | j);
-            return __hsub2(*reinterpret_cast<const __half2 *>(&v), k1024);
-        };
-        float tmp[4] = {0.f, 0.f, 0.f, 0.f}, tmq[4] = {0.f, 0.f, 0.f, 0.f};     // two independent MMA chains
+        // A scale byte placed in the low mantissa bits of the f32 2^23 reads as 2^23 + sc; under 2^19 as 2^19 + sc / 16.
+        auto scale_lo = [&](uint32_t packed, int j) -> float { return __uint_as_float(__byte_perm(packed, 0x4B000000u, 0x7540u | j)) - 8388608.f; };
+        auto scale_hi = [&](uint32_t packed, int j) -> float { return __uint_as_float(__byte_perm(packed, 0x49000000u, 0x7540u | j)) - 524288.f; };
+        float tot[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            // group j of the half: sub-block 2j in the low nibbles, 2j + 1 in the high nibbles
-            const __half2 s0 = scale2(sc0, 2 * j), u0 = scale2(sc0, 2 * j + 1);
-            const __half2 s1 = scale2(sc1, 2 * j), u1 = scale2(sc1, 2 * j + 1);
-            const __half2 o0 = __hmul2(s0, kn1024), t0 = __hmul2(u0, k16th), p0 = __hmul2(u0, kn64);
-            const __half2 o1 = __hmul2(s1, kn1024), t1 = __hmul2(u1, k16th), p1 = __hmul2(u1, kn64);
+            // group j of the half: sub-block 2j in the low nibbles, 2j + 1 in the high nibbles. The MMA's
+            // weight operand is the masked nibble itself: as an f16 bit pattern q in bits 0..3 is the
+            // subnormal q * 2^-24 and q in bits 4..7 is 16 q * 2^-24, both exact.
+            float alo[4] = {0.f, 0.f, 0.f, 0.f}, ahi[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-                const Quad a = word_to_frag(hh ? raw.q0[j].y : raw.q0[j].x, s0, o0, t0, p0);     // row g
-                const Quad b = word_to_frag(hh ? raw.q1[j].y : raw.q1[j].x, s1, o1, t1, p1);     // row g + 8
+                const uint32_t wa = hh ? raw.q0[j].y : raw.q0[j].x, wb = hh ? raw.q1[j].y : raw.q1[j].x;     // rows g, g + 8
+                const uint32_t ua = wa >> 8, ub = wb >> 8;
+                const uint32_t l0 = wa & 0x000F000Fu, l1 = wb & 0x000F000Fu, l2 = ua & 0x000F000Fu, l3 = ub & 0x000F000Fu;
+                const uint32_t h0 = wa & 0x00F000F0u, h1 = wb & 0x00F000F0u, h2 = ua & 0x00F000F0u, h3 = ub & 0x00F000F0u;
                 const int ks_lo = 4 * j + hh, ks_hi = 4 * j + 2 + hh;
-                if (PACK4) {
-                    mma_f16(tmp, a.lo02, b.lo02, a.lo13, b.lo13, bh[ks_lo][0], bh[ks_lo][1]);
-                    mma_f16(tmq, a.hi02, b.hi02, a.hi13, b.hi13, bh[ks_hi][0], bh[ks_hi][1]);
-                } else {
-                    mma_f16(tmp, a.lo02, b.lo02, a.lo13, b.lo13, bh[ks_lo][0], bh[ks_lo][1]);
-                    mma_f16(tmq, a.lo02, b.lo02, a.lo13, b.lo13, bl[ks_lo][0], bl[ks_lo][1]);
-                    mma_f16(tmp, a.hi02, b.hi02, a.hi13, b.hi13, bh[ks_hi][0], bh[ks_hi][1]);
-                    mma_f16(tmq, a.hi02, b.hi02, a.hi13, b.hi13, bl[ks_hi][0], bl[ks_hi][1]);
+                mma_f16(alo, l0, l1, l2, l3, bh[ks_lo][0], bh[ks_lo][1]);
+                mma_f16(ahi, h0, h1, h2, h3, bh[ks_hi][0], bh[ks_hi][1]);
+                if (!PACK4) {
+                    mma_f16(alo, l0, l1, l2, l3, bl[ks_lo][0], bl[ks_lo][1]);
+                    mma_f16(ahi, h0, h1, h2, h3, bl[ks_hi][0], bl[ks_hi][1]);
                 }
             }
+            const float sl0 = scale_lo(sc0, 2 * j), sl1 = scale_lo(sc1, 2 * j), sh0 = scale_hi(sc0, 2 * j + 1), sh1 = scale_hi(sc1, 2 * j + 1);
+            tot[0] += sl0 * alo[0] + sh0 * ahi[0];
+            tot[1] += sl0 * alo[1] + sh0 * ahi[1];
+            tot[2] += sl1 * alo[2] + sh1 * ahi[2];
+            tot[3] += sl1 * alo[3] + sh1 * ahi[3];
         }
         const __half2 dd0 = *reinterpret_cast<const __half2 *>(&raw.hdr0.x), dd1 = *reinterpret_cast<const __half2 *>(&raw.hdr1.x);
-        const float d0 = __low2float(dd0), d1 = __low2float(dd1);
-        part[0] = d0 * (tmp[0] + tmq[0]);
-        part[1] = d0 * (tmp[1] + tmq[1]);
-        part[2] = d1 * (tmp[2] + tmq[2]);
-        part[3] = d1 * (tmp[3] + tmq[3]);
+        const float d0 = __low2float(dd0) * 16777216.f, d1 = __low2float(dd1) * 16777216.f;      // undoes the 2^-24 of the nibbles
+        part[0] = d0 * tot[0];
+        part[1] = d0 * tot[1];
+        part[2] = d1 * tot[2];
+        part[3] = d1 * tot[3];
         if (kh == 0) {
             // minimum term of the whole super-block: A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]
             const uint32_t mnA0 = raw.hdr0.z & 0x3F3F3F3Fu, mnB0 = ((raw.hdr0.w >> 4) & 0x0F0F0F0Fu) | ((raw.hdr0.z >> 2) & 0x30303030u);
@@ -222,35 +203,41 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
 
     int buf = 0, it = 0;
     bool alive = true;
-    for (int u = u_begin; u < u_end; ++u) {
-        const bool work = sb_valid && alive;
-        const int stage = it % STAGES;
-        bool ok = true;
-        if (work) ok = tc5::mbar_wait(my_bars + stage * 8, (it / STAGES) & 1, abort_flag);
-        if (!__all_sync(0xffffffffu, ok)) alive = false;      // warp-uniform
+    for (int ub = u_begin; ub < u_end; ub += UB) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
-            if (work && alive) {
-                UnitRaw raw;
-                read_stage(stage, h, raw);
-                compute(raw, part);
+        for (int j = 0; j < UB; ++j) {
+            const int u = ub + j;
+            const bool work = u < u_end && sb_valid && alive;
+            const int stage = it % STAGES;
+            bool ok = true;
+            if (work) ok = tc5::mbar_wait(my_bars + stage * 8, (it / STAGES) & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, ok)) alive = false;      // warp-uniform
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+                if (work && alive) {
+                    UnitRaw raw;
+                    read_stage(stage, h, raw);
+                    compute(raw, part);
+                }
+                *reinterpret_cast<float4 *>(&red[(((buf * UB + j) * 2 + h) * NWARP + warp) * 128 + lane * 4]) = make_float4(part[0], part[1], part[2], part[3]);
             }
-            *reinterpret_cast<float4 *>(&red[((buf * 2 + h) * NWARP + warp) * 128 + lane * 4]) = make_float4(part[0], part[1], part[2], part[3]);
-        }
-        if (work) {
-            __syncwarp();       // every lane has read the stage before it is refilled
-            if (lane == 0 && alive && u + STAGES < u_end) issue(u + STAGES, stage);
-            ++it;
+            if (work) {
+                __syncwarp();       // every lane has read the stage before it is refilled
+                if (lane == 0 && alive && u + STAGES < u_end) issue(u + STAGES, stage);
+                ++it;
+            }
         }
         __syncthreads();
-        // add the sixteen warps' contributions in warp order and store the K chunk's partial sums
-        if (tid < 256) {
-            const int h = tid >> 7, v = tid & 127;
+        // add the sixteen warps' contributions in warp order and store the K chunk's partial sums:
+        // one thread per (unit of the batch, 16-row half, fragment slot)
+        {
+            const int jh = tid >> 7, v = tid & 127;
+            const int u = ub + (jh >> 1);
             const int ln = v >> 2, e = v & 3;
             const int t = 2 * (ln & 3) + (e & 1);
-            if (t < T) {
-                const float * src = &red[(buf * 2 + h) * NWARP * 128 + v];
+            if (u < u_end && t < T) {
+                const float * src = &red[(buf * UB * 2 + jh) * NWARP * 128 + v];
                 float sum = 0.f;
 #pragma unroll
                 for (int w = 0; w < NWARP; ++w) sum += src[w * 128];
@@ -260,11 +247,11 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
                     for (int w = 0; w < NWARP; ++w) lo += src[w * 128 + 8];
                     sum += lo;
                 }
-                const int o = u * 32 + h * 16 + (ln >> 2) + ((e >> 1) << 3);
+                const int o = u * 32 + (jh & 1) * 16 + (ln >> 2) + ((e >> 1) << 3);
                 if (o < n_out) partial[((size_t)kchunk * 8 + t) * n_out + o] = sum;
             }
         }
-        buf ^= 1;       // the next unit writes the other buffer; one barrier per unit is enough
+        buf ^= 1;       // the next batch writes the other buffer; one barrier per batch is enough
     }
     // A wait that gave up: say so, and give this warp's copies still in flight a bounded time to land
     // before the shared memory is released.

@@ -6,14 +6,19 @@
 //
 // One CTA computes 128 weight rows x 128 tokens. Warp roles (17 warps):
 //   0-3, 4-7   two producer groups, alternating pipeline stages: thread p decodes the 64 weights of
-//              row p into the K-major 128B-swizzled A tile; one thread of the group fetches the two
-//              activation tiles (hi and lo) with TMA, whose bytes complete on the stage's barrier;
+//              row p and stores them into lane p of the stage's A slot in TENSOR MEMORY (the MMA reads
+//              its A operand from there, so shared memory carries the activations only); one thread
+//              of the group fetches the two activation tiles (hi and lo) with TMA, whose bytes
+//              complete on the stage's barrier;
 //   16         lane 0 issues the MMAs (M 128, N 128, K 16) and commits them to the stage's
 //              "empty" barrier, and per super-block to the accumulator's "full" barrier;
 //   8-11,12-15 epilogue: each thread owns one weight row and 64 token columns, pulls both TMEM
 //              accumulators of a finished super-block with tcgen05.ld and folds them into its f32
 //              running sums while the tensor cores already work on the next super-block in the
-//              other TMEM buffer.
+//              other main buffer.
+// Tensor memory (512 columns): two main accumulators (2 x 128), one minimum-term accumulator (128; its
+// MMA is the last of a super-block, long after the epilogue has read the previous one), and four A
+// slots of 32 columns (128 rows x 64 f16).
 // A super-block is five pipeline stages: four of 64 columns each (eight MMAs: hi and lo), then one
 // that carries the minimum term as a single K=16 step (A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]).
 // Every mbarrier wait is bounded: after about a second without progress the CTA raises an error
@@ -30,11 +35,12 @@ namespace {
 
 constexpr int BM = 128, BN = 128;
 constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128;
-constexpr int STAGE_BYTES = A_BYTES + 2 * B_BYTES;
+constexpr int B_BYTES = BN * 128;
+constexpr int STAGE_BYTES = 2 * B_BYTES;          // activation tiles hi and lo; the weight tile lives in tensor memory
 constexpr int N_WARPS = 17;
 constexpr int THREADS = N_WARPS * 32;
-constexpr int TMEM_COLS = 512;                 // two buffers x (128 main + 128 min) columns
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_MIN = 256, TMEM_A = 384;    // column offsets: main buffers at 0 and 128
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 __device__ __forceinline__ void nibbles_times_scale(uint32_t word, int hi, __half2 sc2, __half2 off2, uint32_t & out01, uint32_t & out23) {
@@ -78,13 +84,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
-    // barriers: full[4], empty[4], tmem_full[2], tmem_empty[2]; then the TMEM base word and the abort flag
+    // barriers: full[4], empty[4], tmem_full[2], tmem_empty[2], min_empty; then the TMEM base word and the abort flag
     const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
-    uint32_t * tmem_word = reinterpret_cast<uint32_t *>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    const uint32_t tmin_empty_bar = bar_base + 8u * (2 * STAGES + 4);
+    uint32_t * tmem_word = reinterpret_cast<uint32_t *>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 5));
     volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_word + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -102,6 +109,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
             tc5::mbar_init(tfull_bar(b), 1);
             tc5::mbar_init(tempty_bar(b), 256);
         }
+        tc5::mbar_init(tmin_empty_bar, 256);
         *abort_flag = 0;
         tc5::fence_mbar_init();
     }
@@ -115,7 +123,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         // ------------------------------------------------------------------ producers
         const int group = warp >> 2;
         const int p = tid & 127;                       // weight row and token row of this thread
-        const bool a_valid = true;                     // the tiled layout is zero-padded to whole row tiles
+        // (the tiled layout is zero-padded to whole row tiles: every row p exists)
         const uint8_t * tile_base = W + (size_t)blockIdx.y * n_sb * kQ4kTileBytes;
         const int t = t0 + p;
         const bool t_valid = t < T;
@@ -143,10 +151,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         // returns false when the pipeline was aborted
         auto produce = [&](int it, Raw & raw) -> bool {
             const int stage = it % STAGES, use = it / STAGES;
-            if (!tc5::mbar_wait(empty_bar(stage), (use & 1) ^ 1, abort_flag)) return false;
+            // warp-uniform outcome: the tensor-memory stores below are warp-collective
+            if (!__all_sync(0xffffffffu, tc5::mbar_wait(empty_bar(stage), (use & 1) ^ 1, abort_flag))) return false;
+            tc5::fence_after_sync();
             const int sb = it / 5, r = it % 5;
-            uint8_t * a_s = smem + stage * STAGE_BYTES;
-            uint8_t * bh_s = a_s + A_BYTES;
+            uint8_t * bh_s = smem + stage * STAGE_BYTES;
+            const uint32_t a_slot = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + TMEM_A + stage * 32;
             if (r < 4) {
                 if (p == 0) {
                     // the activation tiles (hi and lo, 128 tokens x 64 columns each) arrive by TMA
@@ -155,53 +165,44 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
                     tc5::tma_load_2d(bh, &X.map_hi, sb * 256 + r * 64, t0, full_bar(stage));
                     tc5::tma_load_2d(bl, &X.map_lo, sb * 256 + r * 64, t0, full_bar(stage));
                 }
-                uint4 out[8];
-                if (a_valid) {
+                // 64 weights -> 32 columns of f16 pairs in K order: low nibbles (columns 0..31 of the group), then high
+                uint32_t out[32];
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint32_t sc, mn;
-                        q4k_scale_min_regs(raw.hdr, r * 2 + half, sc, mn);
-                        const __half2 sc2 = __half2half2(__ushort2half_rn((unsigned short)sc));
-                        const __half2 off2 = __half2half2(__float2half_rn(-1024.0f * (float)sc));
-                        uint4 * o = out + half * 4;
-                        nibbles_times_scale(raw.q0.x, half, sc2, off2, o[0].x, o[0].y);
-                        nibbles_times_scale(raw.q0.y, half, sc2, off2, o[0].z, o[0].w);
-                        nibbles_times_scale(raw.q0.z, half, sc2, off2, o[1].x, o[1].y);
-                        nibbles_times_scale(raw.q0.w, half, sc2, off2, o[1].z, o[1].w);
-                        nibbles_times_scale(raw.q1.x, half, sc2, off2, o[2].x, o[2].y);
-                        nibbles_times_scale(raw.q1.y, half, sc2, off2, o[2].z, o[2].w);
-                        nibbles_times_scale(raw.q1.z, half, sc2, off2, o[3].x, o[3].y);
-                        nibbles_times_scale(raw.q1.w, half, sc2, off2, o[3].z, o[3].w);
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) out[c] = make_uint4(0, 0, 0, 0);
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t sc, mn;
+                    q4k_scale_min_regs(raw.hdr, r * 2 + half, sc, mn);
+                    const __half2 sc2 = __half2half2(__ushort2half_rn((unsigned short)sc));
+                    const __half2 off2 = __half2half2(__float2half_rn(-1024.0f * (float)sc));
+                    uint32_t * o = out + half * 16;
+                    nibbles_times_scale(raw.q0.x, half, sc2, off2, o[0], o[1]);
+                    nibbles_times_scale(raw.q0.y, half, sc2, off2, o[2], o[3]);
+                    nibbles_times_scale(raw.q0.z, half, sc2, off2, o[4], o[5]);
+                    nibbles_times_scale(raw.q0.w, half, sc2, off2, o[6], o[7]);
+                    nibbles_times_scale(raw.q1.x, half, sc2, off2, o[8], o[9]);
+                    nibbles_times_scale(raw.q1.y, half, sc2, off2, o[10], o[11]);
+                    nibbles_times_scale(raw.q1.z, half, sc2, off2, o[12], o[13]);
+                    nibbles_times_scale(raw.q1.w, half, sc2, off2, o[14], o[15]);
                 }
-#pragma unroll
-                for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(a_s + swz(p, c)) = out[c];
+                tc5::tmem_st32(a_slot, out);
                 prefetch(it + 4, raw);
             } else {
                 // minimum-term stage: one K = 16 step, A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]
-                uint4 mv = make_uint4(0, 0, 0, 0);
-                if (a_valid) {
-                    uint32_t mw[4];
+                uint32_t mw[8];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        uint32_t s0, n0, s1, n1;
-                        q4k_scale_min_regs(raw.hdr, 2 * q, s0, n0);
-                        q4k_scale_min_regs(raw.hdr, 2 * q + 1, s1, n1);
-                        const __half2 pr = __halves2half2(__ushort2half_rn((unsigned short)n0), __ushort2half_rn((unsigned short)n1));
-                        mw[q] = *reinterpret_cast<const uint32_t *>(&pr);
-                    }
-                    mv = make_uint4(mw[0], mw[1], mw[2], mw[3]);
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t s0, n0, s1, n1;
+                    q4k_scale_min_regs(raw.hdr, 2 * q, s0, n0);
+                    q4k_scale_min_regs(raw.hdr, 2 * q + 1, s1, n1);
+                    const __half2 pr = __halves2half2(__ushort2half_rn((unsigned short)n0), __ushort2half_rn((unsigned short)n1));
+                    mw[q] = mw[q + 4] = *reinterpret_cast<const uint32_t *>(&pr);
                 }
-                *reinterpret_cast<uint4 *>(a_s + swz(p, 0)) = mv;
-                *reinterpret_cast<uint4 *>(a_s + swz(p, 1)) = mv;
+                tc5::tmem_st8(a_slot, mw);
                 *reinterpret_cast<uint4 *>(bh_s + swz(p, 0)) = raw.q0;
                 *reinterpret_cast<uint4 *>(bh_s + swz(p, 1)) = raw.q1;
+                tc5::fence_proxy_async();
                 prefetch(it + 4, raw);
             }
-            tc5::fence_proxy_async();
+            tc5::fence_before_sync();
             tc5::mbar_arrive(full_bar(stage));
             return true;
         };
@@ -215,32 +216,43 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
     } else if (warp == 16) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
+            // The issuing thread is a single dependent instruction stream: everything that can be is
+            // computed once here, so that a stage costs an add per operand and the MMAs themselves.
             const uint32_t idesc = tc5::instr_desc_f16(BM, BN);
-            for (int it = 0; it < n_it; ++it) {
-                const int stage = it % STAGES, use = it / STAGES;
-                const int sb = it / 5, r = it % 5;
-                const int buf = sb & 1, buse = sb >> 1;
-                if (r == 0) {
-                    if (!tc5::mbar_wait(tempty_bar(buf), (buse & 1) ^ 1, abort_flag)) break;
-                    tc5::fence_after_sync();
-                }
-                if (!tc5::mbar_wait(full_bar(stage), use & 1, abort_flag)) break;
+            const uint64_t desc0 = tc5::smem_desc_sw128(smem_base);
+            const uint32_t desc_lo0 = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
+            const uint32_t a_slot0 = tmem_base + TMEM_A, d_min = tmem_base + TMEM_MIN;
+            int stage = 0, full_parity = 0;
+            for (int sb = 0; sb < n_sb; ++sb) {
+                const int buf = sb & 1;
+                const uint32_t d_main = tmem_base + buf * 128;
+                if (!tc5::mbar_wait(tempty_bar(buf), ((sb >> 1) & 1) ^ 1, abort_flag)) break;
                 tc5::fence_after_sync();
-                const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
-                const uint32_t bh_addr = a_addr + A_BYTES, bl_addr = bh_addr + B_BYTES;
-                const uint32_t d_main = tmem_base + buf * 256, d_min = d_main + 128;
-                if (r < 4) {
+                bool alive = true;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint64_t ad = tc5::smem_desc_sw128(a_addr + k * 32);
-                        tc5::mma_f16_ss(d_main, ad, tc5::smem_desc_sw128(bh_addr + k * 32), idesc, (r | k) != 0);
-                        tc5::mma_f16_ss(d_main, ad, tc5::smem_desc_sw128(bl_addr + k * 32), idesc, 1);
+                for (int r = 0; r < 5; ++r) {
+                    if (!tc5::mbar_wait(full_bar(stage), full_parity, abort_flag)) { alive = false; break; }
+                    tc5::fence_after_sync();
+                    const uint32_t bh = desc_lo0 + stage * (STAGE_BYTES >> 4), bl = bh + (B_BYTES >> 4);
+                    const uint32_t a_slot = a_slot0 + stage * 32;
+                    if (r < 4) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (r == 0 && k == 0) tc5::mma_f16_ts_lean<0>(d_main, a_slot, bh, desc_hi, idesc);
+                            else tc5::mma_f16_ts_lean<1>(d_main, a_slot + k * 8, bh + k * 2, desc_hi, idesc);
+                            tc5::mma_f16_ts_lean<1>(d_main, a_slot + k * 8, bl + k * 2, desc_hi, idesc);
+                        }
+                    } else {
+                        // the epilogue must have read the previous super-block's minimum term
+                        if (!tc5::mbar_wait(tmin_empty_bar, (sb & 1) ^ 1, abort_flag)) { alive = false; break; }
+                        tc5::fence_after_sync();
+                        tc5::mma_f16_ts_lean<0>(d_min, a_slot, bh, desc_hi, idesc);
                     }
-                } else {
-                    tc5::mma_f16_ss(d_min, tc5::smem_desc_sw128(a_addr), tc5::smem_desc_sw128(bh_addr), idesc, 0);
+                    tc5::commit(empty_bar(stage));
+                    if (r == 4) tc5::commit(tfull_bar(buf));
+                    if (++stage == STAGES) { stage = 0; full_parity ^= 1; }
                 }
-                tc5::commit(empty_bar(stage));
-                if (r == 4) tc5::commit(tfull_bar(buf));
+                if (!alive) break;
             }
         }
     } else {
@@ -265,16 +277,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
                 d = __low2float(h);
                 dmin = __high2float(h);
             }
-            const uint32_t t_main = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + colhalf * 64;
+            const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16) + colhalf * 64;
+            const uint32_t t_main = t_lane + buf * 128, t_min = t_lane + TMEM_MIN;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 float v[16], w[16];
-                tc5::tmem_ld16x2(t_main + c * 16, t_main + 128 + c * 16, v, w);
+                tc5::tmem_ld16x2(t_main + c * 16, t_min + c * 16, v, w);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) acc[c * 16 + i] += d * v[i] - dmin * w[i];
             }
             tc5::fence_before_sync();
             tc5::mbar_arrive(tempty_bar(buf));
+            tc5::mbar_arrive(tmin_empty_bar);
         }
         if (alive && o_valid) {
             const float b = bias ? bias[o] : 0.f;
