@@ -21,6 +21,9 @@
 // slots of 32 columns (128 rows x 64 f16).
 // A super-block is five pipeline stages: four of 64 columns each (eight MMAs: hi and lo), then one
 // that carries the minimum term as a single K=16 step (A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]).
+// The thread that issues the MMAs is one dependent instruction stream sharing its scheduler with four
+// busy warps, so its loop is kept to an add per operand and the MMA itself (descriptors are built
+// once), and every other wait sleeps in hardware (try_wait with a time hint) instead of spinning.
 // Every mbarrier wait is bounded: after about a second without progress the CTA raises an error
 // flag, drains its copies, frees its tensor memory and returns.
 
@@ -267,28 +270,41 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
         bool alive = true;
+        // d and dmin of the next super-block are fetched while the tensor cores still work on it
+        __half2 h_next = *reinterpret_cast<const __half2 *>(hdr_base);      // (rows are padded to whole tiles)
+        const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16) + colhalf * 64;
         for (int sb = 0; sb < n_sb && alive; ++sb) {
             const int buf = sb & 1, buse = sb >> 1;
+            const float d = __low2float(h_next), dmin = __high2float(h_next);
+            if (sb + 1 < n_sb) h_next = *reinterpret_cast<const __half2 *>(hdr_base + (size_t)(sb + 1) * kQ4kTileBytes);
             if (!tc5::mbar_wait(tfull_bar(buf), buse & 1, abort_flag)) { alive = false; break; }
             tc5::fence_after_sync();
-            float d = 0.f, dmin = 0.f;
-            if (o_valid) {
-                const __half2 h = *reinterpret_cast<const __half2 *>(hdr_base + (size_t)sb * kQ4kTileBytes);
-                d = __low2float(h);
-                dmin = __high2float(h);
-            }
-            const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16) + colhalf * 64;
             const uint32_t t_main = t_lane + buf * 128, t_min = t_lane + TMEM_MIN;
+            // the single minimum-term accumulator first, so the next super-block's MMA can have it back early
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 4; c += 2) {
                 float v[16], w[16];
-                tc5::tmem_ld16x2(t_main + c * 16, t_min + c * 16, v, w);
+                tc5::tmem_ld16x2(t_min + c * 16, t_min + (c + 1) * 16, v, w);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc[c * 16 + i] += d * v[i] - dmin * w[i];
+                for (int i = 0; i < 16; ++i) {
+                    acc[c * 16 + i] -= dmin * v[i];
+                    acc[(c + 1) * 16 + i] -= dmin * w[i];
+                }
+            }
+            tc5::fence_before_sync();
+            tc5::mbar_arrive(tmin_empty_bar);
+#pragma unroll
+            for (int c = 0; c < 4; c += 2) {
+                float v[16], w[16];
+                tc5::tmem_ld16x2(t_main + c * 16, t_main + (c + 1) * 16, v, w);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    acc[c * 16 + i] += d * v[i];
+                    acc[(c + 1) * 16 + i] += d * w[i];
+                }
             }
             tc5::fence_before_sync();
             tc5::mbar_arrive(tempty_bar(buf));
-            tc5::mbar_arrive(tmin_empty_bar);
         }
         if (alive && o_valid) {
             const float b = bias ? bias[o] : 0.f;
