@@ -172,7 +172,7 @@ class Driver:
                 n_prefill += n
             else:
                 n_decode += 1
-            ctx_tokens += row.pos0 * n + n * (n + 1) // 2
+            ctx_tokens += row.pos0 + n      # every resident KV entry of the row's sequence is read at least once
             if row.sample:
                 r.last = self.out.row(i).token
                 r.done += 1
@@ -407,6 +407,11 @@ def main():
         achieved = attn_bytes / (profile["attention"]["ms"] * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "traffic": None, "kernel": "paged ragged attention (all launches of the timed region)"}
+    # the paged attention kernels beside it: KV bytes the step's rows had to read / their device time
+    if profile["attention"]["ms"] > 0:
+        a_gbs = attn_bytes / (profile["attention"]["ms"] * 1e-3) / 1e9
+        roof["attention"] = {"bound": "hbm", "achieved": a_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": a_gbs / hbm_peak,
+                             "kv_bytes_per_step": attn_bytes / args.steps}
     roof["peak_source"] = f"of {peak_kind}"
     roof["launches"] = profile[top]["launches"]
     roof["avg_launch_ms"] = profile[top]["ms"] / max(profile[top]["launches"], 1)

@@ -359,6 +359,16 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
     ++last_launches;
 }
 
+// Whether linear() will read the split form of the activations for this weight and token count
+// (then the f32 copy of the activations need not be written at all).
+bool Engine::linear_reads_split(const WeightView & w, int ldx, int T, const SplitAct * xs) const {
+    if (!xs) return false;
+    if (T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) return true;
+    if (stream_gemm_ && gemm_q4k_stream_supported(w, *xs, T)) return true;
+    if (T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) return true;
+    return T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs);
+}
+
 void Engine::lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy) {
     if (!cur_any_adapter_) return;
     auto it = lora_targets_.find(target);
@@ -575,7 +585,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     std::vector<SampleDesc> descs(S);
     std::vector<LogitEdit> edits;
     size_t top_stride = 0;
-    bool any_v2 = false;
+    bool any_v2 = false;       // some row needs the working copy of the logits
+    int n_greedy_fast = 0;
     {
         size_t s = 0;
         for (size_t r = 0; r < R; ++r) {
@@ -601,7 +612,6 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 d.top_k = p.top_k;
                 d.min_p = p.min_p;
                 d.flags = 1u | (row.want_logprob ? 2u : 0u);
-                any_v2 = true;
                 // one merged edit per distinct id: summed bias, then the penalties of the window
                 std::map<int32_t, LogitEdit> merged;
                 for (uint32_t i = 0; i < p.n_logit_bias; ++i) {
@@ -623,6 +633,12 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 }
                 for (const auto & e : merged) edits.push_back(e.second);
                 d.edit_end = (uint32_t)edits.size();
+                if (p.top_k == 1 && merged.empty()) {
+                    d.flags |= 4u;      // plain greedy: arg-max of the raw row, no working copy
+                    ++n_greedy_fast;
+                } else {
+                    any_v2 = true;
+                }
             } else {
                 d.temperature = row.v1.temperature;
                 d.top_p = row.v1.top_p;
@@ -694,6 +710,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         hs_.ensure(S * (size_t)hp.d);
         hs_split_.ensure(S, hp.d);
         if (any_v2) logits_work_.ensure(S * (size_t)hp.vocab);
+        if (n_greedy_fast) sample_scratch_.ensure(sample_scratch_bytes((int)hp.vocab, (int)S));
     }
     if (any_adapter) lora_tmp_.ensure(T * (size_t)std::max<uint32_t>(r_max_, 1));
 
@@ -736,7 +753,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     for (uint32_t l = 0; l < hp.n_layer; ++l) {
         const LayerWeights & lw = model->layers[l];
         const std::string p = "blk." + std::to_string(l) + ".";
-        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, xn_.ptr, d, Ti, stream, xn_split_.get()));
+        // the f32 copy of an activation is written only when something other than a split-reading GEMM consumes it
+        const bool qkv_split = !any_adapter && lw.wqkv.data && linear_reads_split(lw.wqkv, d, Ti, xn_split_.get());
+        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, qkv_split ? nullptr : xn_.ptr, d, Ti, stream, xn_split_.get()));
         if (lw.wqkv.data) {
             linear(lw.wqkv, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0, xn_split_.get());
         } else {
@@ -768,7 +787,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         // x = x + Wo att
         linear(lw.wo, att_.ptr, dq, Ti, x_.ptr, d, nullptr, x_.ptr, d, att_split_.get());
         if (any_adapter) lora(p + "attn_output.weight", att_.ptr, dq, Ti, x_.ptr, d);
-        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, xn_.ptr, d, Ti, stream, xn_split_.get()));
+        const bool gu_split = !any_adapter && hp.n_expert == 0 && lw.wgu.data && linear_reads_split(lw.wgu, d, Ti, xn_split_.get());
+        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, gu_split ? nullptr : xn_.ptr, d, Ti, stream, xn_split_.get()));
         if (hp.n_expert == 0) {
             if (lw.wgu.data) {
                 linear(lw.wgu, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0, xn_split_.get());
@@ -780,7 +800,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 lora(p + "ffn_gate.weight", xn_.ptr, d, Ti, gu_.ptr, 2 * ff);
                 lora(p + "ffn_up.weight", xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff);
             }
-            RB_K(K_OTHER, 1, launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, hff_.ptr, ff, stream, hff_split_.get()));
+            const bool down_split = !any_adapter && linear_reads_split(lw.wdown, ff, Ti, hff_split_.get());
+            RB_K(K_OTHER, 1, launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, down_split ? nullptr : hff_.ptr, ff, stream, hff_split_.get()));
             linear(lw.wdown, hff_.ptr, ff, Ti, x_.ptr, d, nullptr, x_.ptr, d, hff_split_.get());
             if (any_adapter) lora(p + "ffn_down.weight", hff_.ptr, ff, Ti, x_.ptr, d);
         } else {
@@ -804,10 +825,10 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         if (any_v2) {
             RB_CUDA(cudaMemcpyAsync(logits_work_.ptr, logits.ptr, S * (size_t)hp.vocab * 4, cudaMemcpyDeviceToDevice, stream));
         }
-        RB_K(K_SAMPLE, 1, launch_sample(logits.ptr, any_v2 ? logits_work_.ptr : nullptr, (int)hp.vocab, (int)S,
+        RB_K(K_SAMPLE, (n_greedy_fast < (int)S ? 1 : 0) + (n_greedy_fast ? 2 : 0), launch_sample(logits.ptr, any_v2 ? logits_work_.ptr : nullptr, (int)hp.vocab, (int)S,
                                         reinterpret_cast<const SampleDesc *>(d_stage_.ptr + off_descs),
                                         reinterpret_cast<const LogitEdit *>(d_stage_.ptr + off_edits), d_out, d_top_ids, d_top_lps,
-                                        (int)std::max<size_t>(top_stride, 1), stream));
+                                        (int)std::max<size_t>(top_stride, 1), n_greedy_fast, sample_scratch_.ptr, stream));
     }
 #undef RB_K
     RB_CUDA(cudaEventRecord(ev_end_, stream));

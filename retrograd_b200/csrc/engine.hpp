@@ -246,6 +246,7 @@ private:
     void restack_adapters();
     void linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
                 const SplitAct * xs = nullptr);
+    bool linear_reads_split(const WeightView & w, int ldx, int T, const SplitAct * xs) const;
     void lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy);
     void flush_kv_updates();
     KvLayout kv_layout() const;
@@ -264,6 +265,7 @@ private:
     DeviceBuffer<int32_t> moe_ids_, d_aux_;
     DeviceBuffer<int> device_error_;
     DeviceBuffer<float> stream_scratch_;
+    DeviceBuffer<uint8_t> sample_scratch_;
     int n_sm_ = 148;
     bool stream_gemm_ = true;
     SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;

@@ -51,6 +51,28 @@ __device__ __forceinline__ void emit_split(const SplitAct & s, size_t row, int c
     }
 }
 
+// Four consecutive columns per thread (col % 4 == 0): eight neighbouring lanes cover one 32-column
+// sub-block. Every lane of the warp must call it; `active` masks the stores of lanes past the row.
+__device__ __forceinline__ void emit_split4(const SplitAct & s, size_t row, int col, float4 v, bool active) {
+    const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+    const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+    const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
+    float sum = active ? (v.x + v.y) + (v.z + v.w) : 0.f;
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    if (!active) return;
+    const size_t at = row * s.ld + col;
+    *reinterpret_cast<uint2 *>(s.hi + at) = make_uint2(*reinterpret_cast<const uint32_t *>(&h01), *reinterpret_cast<const uint32_t *>(&h23));
+    *reinterpret_cast<uint2 *>(s.lo + at) = make_uint2(*reinterpret_cast<const uint32_t *>(&l01), *reinterpret_cast<const uint32_t *>(&l23));
+    if ((threadIdx.x & 7) == 0) {
+        const __half sh = __float2half_rn(sum);
+        const size_t sat = row * (s.ld >> 5) + (col >> 5);
+        s.sum_hi[sat] = sh;
+        s.sum_lo[sat] = __float2half_rn(sum - __half2float(sh));
+    }
+}
+
 // Decodes 8 consecutive elements starting at k (k % 8 == 0) of a stored row.
 template <uint32_t TYPE>
 __device__ __forceinline__ void decode8(const uint8_t * __restrict__ row, uint32_t k, float (&w)[8]) {
@@ -270,6 +292,41 @@ __global__ void rms_norm_kernel(const float * __restrict__ x, int ldx, const int
     }
 }
 
+// The same with four columns per thread (n % 32 == 0, rows 16-byte aligned); y may be null when only
+// the split form is consumed.
+__global__ void rms_norm4_kernel(const float * __restrict__ x, int ldx, const int32_t * __restrict__ gather, const float * __restrict__ w, int n,
+                                 float eps, float * __restrict__ y, int ldy, SplitAct split) {
+    __shared__ float partial[32];
+    const int t = blockIdx.x;
+    const float * xr = x + (size_t)(gather ? gather[t] : t) * ldx;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(xr + i);
+        ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? partial[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0) partial[0] = v;
+    }
+    __syncthreads();
+    const float scale = 1.0f / sqrtf(partial[0] / (float)n + eps);
+    for (int base = 0; base < n; base += blockDim.x * 4) {
+        const int i = base + threadIdx.x * 4;
+        const bool active = i < n;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (active) {
+            const float4 a = *reinterpret_cast<const float4 *>(xr + i), b = *reinterpret_cast<const float4 *>(w + i);
+            v = make_float4(a.x * scale * b.x, a.y * scale * b.y, a.z * scale * b.z, a.w * scale * b.w);
+            if (y) *reinterpret_cast<float4 *>(y + (size_t)t * ldy + i) = v;
+        }
+        if (split.hi) emit_split4(split, t, i, v, active);
+    }
+}
+
 // One warp per output row, eight tokens per pass.
 template <uint32_t TYPE>
 __global__ void gemm_rows_kernel(WeightView w, const float * __restrict__ x, int ldx, int n_tokens, float * __restrict__ y, int ldy,
@@ -434,6 +491,28 @@ __global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, flo
     const float v = g / (1.0f + expf(-g)) * u;
     if (h) h[(size_t)t * ldh + i] = v;
     if (split.hi) emit_split(split, t, i, v);
+}
+
+__global__ void swiglu4_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh, SplitAct split) {
+    const int t = blockIdx.y;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const bool active = i < ff;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (active) {
+        const float4 g = *reinterpret_cast<const float4 *>(gu + (size_t)t * ld + i), u = *reinterpret_cast<const float4 *>(gu + (size_t)t * ld + ff + i);
+        v = make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y, g.z / (1.0f + expf(-g.z)) * u.z,
+                        g.w / (1.0f + expf(-g.w)) * u.w);
+        if (h) *reinterpret_cast<float4 *>(h + (size_t)t * ldh + i) = v;
+    }
+    if (split.hi) emit_split4(split, t, i, v, active);
+}
+
+__global__ void split_prep4_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split) {
+    const int t = blockIdx.y;
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const bool active = i < n;
+    const float4 v = active ? *reinterpret_cast<const float4 *>(x + (size_t)t * ldx + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    emit_split4(split, t, i, v, active);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -607,7 +686,10 @@ void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float *
 
 void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const float * w, int n, float eps, float * y, int ldy, int n_tokens,
                      cudaStream_t stream, const SplitAct * split) {
-    rms_norm_kernel<<<n_tokens, 256, 0, stream>>>(x, ldx, gather, w, n, eps, y, ldy, split && n % 32 == 0 ? *split : SplitAct{});
+    const SplitAct sa = split && n % 32 == 0 ? *split : SplitAct{};
+    const bool aligned = n % 32 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) % 16 == 0 && x != y;
+    if (aligned) rms_norm4_kernel<<<n_tokens, 256, 0, stream>>>(x, ldx, gather, w, n, eps, y, ldy, sa);
+    else rms_norm_kernel<<<n_tokens, 256, 0, stream>>>(x, ldx, gather, w, n, eps, y, ldy, sa);
 }
 
 void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
@@ -633,11 +715,15 @@ void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, K
 }
 
 void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream) {
-    split_prep_kernel<<<dim3((n + 255) / 256, n_tokens), 256, 0, stream>>>(x, ldx, n, split);
+    if (n % 32 == 0 && ldx % 4 == 0 && (uintptr_t)x % 16 == 0) split_prep4_kernel<<<dim3((n + 1023) / 1024, n_tokens), 256, 0, stream>>>(x, ldx, n, split);
+    else split_prep_kernel<<<dim3((n + 255) / 256, n_tokens), 256, 0, stream>>>(x, ldx, n, split);
 }
 
 void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split) {
-    swiglu_kernel<<<dim3((ff + 255) / 256, n_tokens), 256, 0, stream>>>(gu, ld, ff, h, ldh, split && ff % 32 == 0 ? *split : SplitAct{});
+    const SplitAct sa = split && ff % 32 == 0 ? *split : SplitAct{};
+    const bool aligned = ff % 32 == 0 && ld % 4 == 0 && ldh % 4 == 0 && ((uintptr_t)gu | (uintptr_t)h) % 16 == 0;
+    if (aligned) swiglu4_kernel<<<dim3((ff + 1023) / 1024, n_tokens), 256, 0, stream>>>(gu, ld, ff, h, ldh, sa);
+    else swiglu_kernel<<<dim3((ff + 255) / 256, n_tokens), 256, 0, stream>>>(gu, ld, ff, h, ldh, sa);
 }
 
 void launch_moe_route(const float * router_logits, int n_expert, int k, int n_tokens, int32_t * ids, float * weights, cudaStream_t stream) {

@@ -76,7 +76,7 @@ struct SampleDesc {
     uint32_t draw_lo;     // per-request draw counter
     uint32_t draw_hi;
     uint32_t n_top;       // top logprobs requested
-    uint32_t flags;       // bit0: v2 row (post-transform reporting), bit1: want sampled_logprob
+    uint32_t flags;       // bit0: v2 row (post-transform reporting), bit1: want sampled_logprob, bit2: greedy without edits
     uint32_t edit_begin;  // range in the logit-edit list
     uint32_t edit_end;
     uint32_t pad[5];
@@ -195,7 +195,10 @@ void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float
 
 // Sampling over logits rows [S][n_vocab]. v2 rows transform their row of `work_logits`, which must
 // then hold a copy of `raw_logits`; with v1 rows only, `work_logits` may be null.
+// Rows whose flags carry bit 2 (v2, top_k == 1, no logit edits) are served by chunked arg-max kernels
+// that need `scratch` (sample_scratch_bytes()); `n_greedy_fast` is how many rows carry the bit.
+size_t sample_scratch_bytes(int n_vocab, int n_rows);
 void launch_sample(const float * raw_logits, float * work_logits, int n_vocab, int n_rows, const SampleDesc * desc, const LogitEdit * edits, SampleOut * out,
-                   int32_t * top_ids, float * top_logprobs, int top_stride, cudaStream_t stream);
+                   int32_t * top_ids, float * top_logprobs, int top_stride, int n_greedy_fast, void * scratch, cudaStream_t stream);
 
 } // namespace rb200

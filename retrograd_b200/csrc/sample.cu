@@ -23,7 +23,7 @@ namespace rb200 {
 namespace {
 
 constexpr int kThreads = 1024;
-constexpr uint32_t kFlagV2 = 1u, kFlagWantLogprob = 2u;
+constexpr uint32_t kFlagV2 = 1u, kFlagWantLogprob = 2u, kFlagGreedyFast = 4u;
 
 struct Shared {
     double dwarp[32];
@@ -213,6 +213,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float * __restri
     __shared__ Shared sh;
     const int row = blockIdx.x;
     const SampleDesc d = descs[row];
+    if (d.flags & kFlagGreedyFast) return;      // served by the chunked arg-max kernels below
     const bool v2 = (d.flags & kFlagV2) != 0;
     // v2 rows transform a private copy of their row; v1 rows only read the raw one
     const float * raw = raw_logits + (size_t)row * V;
@@ -450,12 +451,127 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float * __restri
     }
 }
 
+
+// ---- greedy rows without logit edits (v2, top_k == 1): the token is the arg-max of the raw row and
+// the only statistics needed are the row's maximum and its double-precision sum of exponentials.
+// The row is cut into chunks of kChunk logits handled by separate blocks, so a handful of rows still
+// fills the GPU; a second tiny kernel merges the chunk results in chunk order.
+constexpr int kChunk = 4096, kChunkThreads = 256;
+
+struct ChunkStat {
+    double sum;      // sum of exp(l - max) over the chunk, fixed order
+    float max;
+    int32_t arg;     // lowest id holding the maximum
+};
+static_assert(sizeof(ChunkStat) == 16, "ChunkStat layout");
+
+__global__ void __launch_bounds__(kChunkThreads) greedy_chunk_kernel(const float * __restrict__ raw_logits, int V, const SampleDesc * __restrict__ descs,
+                                                                     ChunkStat * __restrict__ stats, int n_chunks) {
+    const int row = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    if (!(descs[row].flags & kFlagGreedyFast)) return;
+    __shared__ float s_max[kChunkThreads / 32];
+    __shared__ int32_t s_arg[kChunkThreads / 32];
+    __shared__ double s_sum[kChunkThreads / 32];
+    const float * l = raw_logits + (size_t)row * V;
+    const int base = chunk * kChunk;
+    float v[kChunk / kChunkThreads];
+    float m = -INFINITY;
+    int32_t a = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kChunk / kChunkThreads; ++j) {
+        const int i = base + j * kChunkThreads + tid;
+        v[j] = i < V ? l[i] : -INFINITY;
+        if (v[j] > m) { m = v[j]; a = i; }       // ascending ids: the first maximum wins
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m, o);
+        const int32_t oa = __shfl_xor_sync(0xffffffffu, a, o);
+        if (om > m || (om == m && oa < a)) { m = om; a = oa; }
+    }
+    if (lane == 0) { s_max[wid] = m; s_arg[wid] = a; }
+    __syncthreads();
+    m = s_max[0];
+    a = s_arg[0];
+#pragma unroll
+    for (int w = 1; w < kChunkThreads / 32; ++w)
+        if (s_max[w] > m || (s_max[w] == m && s_arg[w] < a)) { m = s_max[w]; a = s_arg[w]; }
+    double part = 0.0;
+#pragma unroll
+    for (int j = 0; j < kChunk / kChunkThreads; ++j) {
+        const int i = base + j * kChunkThreads + tid;
+        if (i < V) part += exp((double)v[j] - (double)m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) s_sum[wid] = part;
+    __syncthreads();
+    if (tid == 0) {
+        double sum = 0.0;
+#pragma unroll
+        for (int w = 0; w < kChunkThreads / 32; ++w) sum += s_sum[w];
+        ChunkStat st;
+        st.sum = sum;
+        st.max = m;
+        st.arg = a;
+        stats[(size_t)row * n_chunks + chunk] = st;
+    }
+}
+
+__global__ void greedy_finish_kernel(const float * __restrict__ raw_logits, int V, const SampleDesc * __restrict__ descs,
+                                     const ChunkStat * __restrict__ stats, int n_chunks, SampleOut * __restrict__ outs,
+                                     int32_t * __restrict__ top_ids, float * __restrict__ top_lps, int top_stride) {
+    const int row = blockIdx.x;
+    const SampleDesc d = descs[row];
+    if (!(d.flags & kFlagGreedyFast) || threadIdx.x != 0) return;
+    const ChunkStat * st = stats + (size_t)row * n_chunks;
+    float rmax = st[0].max;
+    int32_t token = st[0].arg;
+    for (int c = 1; c < n_chunks; ++c)
+        if (st[c].max > rmax) { rmax = st[c].max; token = st[c].arg; }      // chunks ascend in id: strict > keeps the lowest id
+    double total = 0.0;
+    for (int c = 0; c < n_chunks; ++c) total += st[c].sum * exp((double)st[c].max - (double)rmax);
+    const double rlog = log(total);
+    const float * raw = raw_logits + (size_t)row * V;
+    const double inv_t = 1.0 / (double)d.temperature;
+    // the one-token nucleus: its post-transformation logprob is log(exp(0 / T) / 1)
+    const float self_lp = (float)log(exp(((double)raw[token] - (double)rmax) * inv_t) / 1.0);
+    const uint32_t n_top = min(d.n_top, (uint32_t)min(top_stride, V));
+    int32_t next_id = 0;
+    for (uint32_t j = 0; j < n_top; ++j) {
+        if (j == 0) {
+            top_ids[(size_t)row * top_stride] = token;
+            top_lps[(size_t)row * top_stride] = self_lp;
+        } else {
+            // every other token was truncated away: ids in ascending order, probability zero
+            if (next_id == token) ++next_id;
+            top_ids[(size_t)row * top_stride + j] = next_id++;
+            top_lps[(size_t)row * top_stride + j] = (float)log(exp(-INFINITY * inv_t) / 1.0);
+        }
+    }
+    SampleOut o;
+    o.token = token;
+    o.logprob = (float)((double)raw[token] - (double)rmax - rlog);
+    o.sampled_logprob = (d.flags & kFlagWantLogprob) ? self_lp : 0.f;
+    o.n_top = n_top;
+    outs[row] = o;
+}
+
 } // namespace
 
+size_t sample_scratch_bytes(int n_vocab, int n_rows) { return (size_t)n_rows * ((n_vocab + kChunk - 1) / kChunk) * sizeof(ChunkStat); }
+
 void launch_sample(const float * raw_logits, float * work_logits, int n_vocab, int n_rows, const SampleDesc * desc, const LogitEdit * edits, SampleOut * out,
-                   int32_t * top_ids, float * top_logprobs, int top_stride, cudaStream_t stream) {
+                   int32_t * top_ids, float * top_logprobs, int top_stride, int n_greedy_fast, void * scratch, cudaStream_t stream) {
     if (n_rows <= 0) return;
-    sample_kernel<<<n_rows, kThreads, 0, stream>>>(raw_logits, work_logits, n_vocab, desc, edits, out, top_ids, top_logprobs, top_stride);
+    if (n_greedy_fast < n_rows)
+        sample_kernel<<<n_rows, kThreads, 0, stream>>>(raw_logits, work_logits, n_vocab, desc, edits, out, top_ids, top_logprobs, top_stride);
+    if (n_greedy_fast > 0) {
+        const int n_chunks = (n_vocab + kChunk - 1) / kChunk;
+        ChunkStat * stats = static_cast<ChunkStat *>(scratch);
+        greedy_chunk_kernel<<<dim3(n_chunks, n_rows), kChunkThreads, 0, stream>>>(raw_logits, n_vocab, desc, stats, n_chunks);
+        greedy_finish_kernel<<<n_rows, 32, 0, stream>>>(raw_logits, n_vocab, desc, stats, n_chunks, out, top_ids, top_logprobs, top_stride);
+    }
 }
 
 } // namespace rb200

@@ -290,3 +290,32 @@ def test_min_p_and_temperature_v2_rows_stay_inside_the_kept_set(rb, oracle, pair
         engine.step([rb.StepRow(300 + trial, 0, prompt, 0, sample=True, sampling=sp, want_logprob=True)], out)
         assert out.row(0).token in keep
         assert out.row(0).sampled_logprob <= 0.0
+
+
+def test_plain_greedy_rows_equal_the_general_sampler_and_the_oracle(rb, oracle, pair):
+    """Greedy rows without logit edits are served by a separate chunked arg-max path. A zero logit
+    bias sends the same row through the general sampler: both must report identical token,
+    logprobs and top lists, and both must equal the oracle on the raw logits."""
+    engine, _ = pair
+    out = rb.StepOutput()
+    plain = rb.SamplingParamsV2(top_k=1)
+    general = rb.SamplingParamsV2(top_k=1, logit_bias=[(5, 0.0)])
+    rows = []
+    for i in range(3):
+        prompt = _prompt(90 + i, 9 + 2 * i)
+        rows.append(rb.StepRow(2 * i, 2 * i, prompt, 0, sample=True, sampling=plain, want_logprob=True, n_top_logprobs=3))
+        rows.append(rb.StepRow(2 * i + 1, 2 * i + 1, prompt, 0, sample=True, sampling=general, want_logprob=True, n_top_logprobs=3))
+    engine.step(rows, out)
+    for i in range(3):
+        a, b = out.row(2 * i), out.row(2 * i + 1)
+        assert np.array_equal(engine.last_logits(2 * i), engine.last_logits(2 * i + 1))
+        assert (a.token, a.logprob, a.sampled_logprob) == (b.token, b.logprob, b.sampled_logprob)
+        ids_a, lps_a = out.top(2 * i)
+        ids_b, lps_b = out.top(2 * i + 1)
+        assert list(ids_a) == list(ids_b) and np.array_equal(np.asarray(lps_a), np.asarray(lps_b))
+        logits = engine.last_logits(2 * i)
+        assert a.token == int(np.argmax(logits))
+        assert a.logprob == oracle.token_logprob(logits, a.token)
+        assert a.sampled_logprob == 0.0 and lps_a[0] == 0.0 and lps_a[1] == -np.inf
+    for sid in range(6):
+        engine.seq_rm(sid)
