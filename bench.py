@@ -154,6 +154,14 @@ class Driver:
                 rows.append(rb.StepRow(r.rid, r.slot, r.prompt[r.pos : r.pos + take], r.pos, final, self.sampling))
                 kinds.append(r)
                 budget -= take
+        # The GEMM works on tiles of 128 tokens: when the step would end in a ragged tile, the last
+        # prefill chunk gives the remainder back (those tokens go into the next step instead).
+        total = self.cfg["n_batch"] - budget
+        rem = total % 128
+        if total > 128 and rem and rows and kinds[-1].last is None and len(rows[-1].tokens) > rem:
+            r, row = kinds[-1], rows[-1]
+            keep = len(row.tokens) - rem
+            rows[-1] = rb.StepRow(r.rid, r.slot, r.prompt[r.pos : r.pos + keep], r.pos, False, self.sampling)
         return rows, kinds
 
     def step(self, prefill_only=False):

@@ -29,7 +29,7 @@ template <int HD>
 __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer,
                                                                        const int2 * __restrict__ items, const int32_t * __restrict__ tok_slot,
                                                                        const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min,
-                                                                       float * __restrict__ out, int ldo) {
+                                                                       float * __restrict__ out, int ldo, int min_cols) {
     constexpr int PANELS = HD / 64;
     constexpr int KSTEPS = HD / 16;
     constexpr int NT = HD / 8;
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const flo
     const int G = n_head / kv.n_head_kv;
     const int2 item = items[blockIdx.x];
     const int i0 = item.x, ntok = item.y;
-    if (ntok * G > 16) return;                              // served by the tile kernel
+    if (ntok * G > 16 || ntok * G <= min_cols) return;      // served by the tile kernel / the eight-column kernel
     const int slot = tok_slot[i0], pos0 = tok_pos[i0], pmin = tok_pos_min[i0];
     const int last = pos0 + ntok - 1;
     const int32_t * table = kv.block_table + (size_t)slot * kv.max_blocks;
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const flo
 
 template <int HD>
 void launch_hd(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
-               const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream) {
+               const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int min_cols, cudaStream_t stream) {
     constexpr int smem = 2 * (HD / 64) * 16 * 128 + DEC_ROUNDS * 4 * 2 * (HD / 64) * 16 * 128;
     static_assert(DEC_ROUNDS * 4 * 2 * (HD / 64) * 16 * 128 >= (4 * 16 * HD + 128) * 4, "the merge buffers fit the K/V ring");
     static bool configured = false;
@@ -268,17 +268,17 @@ void launch_hd(const float * qkv, int ld, int n_head, KvLayout kv, int layer, co
         configured = true;
     }
     attention_decode_kernel<HD><<<dim3(n_items, kv.n_head_kv), DEC_THREADS, smem, stream>>>(qkv, ld, n_head, kv, layer, items, tok_slot, tok_pos,
-                                                                                          tok_pos_min, out, ldo);
+                                                                                          tok_pos_min, out, ldo, min_cols);
 }
 
 } // namespace
 
 void launch_attention_decode(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items,
-                             const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo,
+                             const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int min_cols,
                              cudaStream_t stream) {
     if (n_items <= 0) return;
-    if (kv.head_dim == 128) launch_hd<128>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, stream);
-    else launch_hd<64>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, stream);
+    if (kv.head_dim == 128) launch_hd<128>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, min_cols, stream);
+    else launch_hd<64>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, min_cols, stream);
 }
 
 } // namespace rb200

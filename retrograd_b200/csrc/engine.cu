@@ -278,6 +278,7 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&n_sm_, cudaDevAttrMultiProcessorCount, dev);
         if (const char * env = std::getenv("RB200_GEMM")) stream_gemm_ = std::string(env) != "rows";
+        if (const char * env = std::getenv("RB200_ATTENTION")) attn_decode8_ = std::string(env) != "decode16";
     }
     device_error_.ensure(1);
     RB_CUDA(cudaMemsetAsync(device_error_.ptr, 0, sizeof(int), stream));
@@ -737,12 +738,32 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         RB_K(K_OTHER, 1, launch_kv_block_copy(kvl, (int)hp.n_layer, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_copies), n_copies, stream));
     }
     RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, attn_tile_tokens_, maps, stream));
-    int n_attn_items = 0;
-    bool any_wide_item = false;
+    // Attention work items by width in query vectors (tokens x heads of the GQA group): more than 16 go
+    // to the tile kernel, 9..16 to the 16-row decode kernel, at most 8 to the eight-column kernel.
+    int n_attn_items = 0, n_small_items = 0, max_ctx = 1;
+    bool any_wide_item = false, any_mid_item = false;
     const int attn_group = (int)(hp.n_head / hp.n_head_kv);
+    const bool use_decode8 = attn_decode8_ && attention_decode8_supported((int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, kvl.block_tokens);
     for (size_t r = 0; r < R; ++r) {
-        n_attn_items += ((int)rows[r].n + attn_tile_tokens_ - 1) / attn_tile_tokens_;
-        any_wide_item = any_wide_item || (int)rows[r].n * attn_group > 16;
+        const int n = (int)rows[r].n, tail = n % attn_tile_tokens_;
+        n_attn_items += (n + attn_tile_tokens_ - 1) / attn_tile_tokens_;
+        if (n >= attn_tile_tokens_ && attn_tile_tokens_ * attn_group > 16) any_wide_item = true;
+        if (n >= attn_tile_tokens_ && attn_tile_tokens_ * attn_group <= 16) any_mid_item = true;
+        if (tail) {
+            const int cols = tail * attn_group;
+            if (cols > 16) any_wide_item = true;
+            else if (cols > 8 || !use_decode8) any_mid_item = true;
+            else ++n_small_items;
+        }
+        max_ctx = std::max(max_ctx, (int)rows[r].pos0 + n);
+    }
+    // few small items: cut each sequence's KV blocks over several CTAs so the GPU is still full
+    int attn_splits = 1;
+    if (n_small_items > 0) {
+        const int want = (2 * n_sm_ + n_small_items * (int)hp.n_head_kv - 1) / (n_small_items * (int)hp.n_head_kv);
+        attn_splits = std::max(1, std::min({want, 16, (max_ctx / kvl.block_tokens) / 8}));
+        if (attn_splits > 1)
+            attn_scratch_.ensure(attention_decode8_scratch_floats(n_attn_items, (int)hp.n_head_kv, attn_splits, (int)hp.head_dim));
     }
     cur_tok_adapter_ = maps.tok_adapter;
     cur_any_adapter_ = any_adapter;
@@ -775,10 +796,14 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         RB_K(K_OTHER, 1, launch_rope_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox,
                                            model->inv_freq.ptr, maps.tok_pos, maps.tok_cell, kvl, (int)l, stream));
         if (attn_mma_) {
-            RB_K(K_ATTN, 2, if (any_wide_item) launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
-                                                                    maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, true, stream);
-                 launch_attention_decode(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot, maps.tok_pos,
-                                         maps.tok_pos_min, att_.ptr, dq, stream));
+            RB_K(K_ATTN, (any_wide_item ? 1 : 0) + (any_mid_item ? 1 : 0) + (n_small_items ? (attn_splits > 1 ? 2 : 1) : 0),
+                 if (any_wide_item) launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
+                                                         maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, true, stream);
+                 if (any_mid_item) launch_attention_decode(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot,
+                                                           maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, use_decode8 ? 8 : 0, stream);
+                 if (n_small_items) launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
+                                                             maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, attn_splits,
+                                                             attn_scratch_.ptr, stream));
             if (att_split_.get()) RB_K(K_OTHER, 1, launch_split_prep(att_.ptr, dq, dq, Ti, att_split_.view, stream));
         } else {
             RB_K(K_ATTN, 1, launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min,

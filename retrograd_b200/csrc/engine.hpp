@@ -266,6 +266,8 @@ private:
     DeviceBuffer<int> device_error_;
     DeviceBuffer<float> stream_scratch_;
     DeviceBuffer<uint8_t> sample_scratch_;
+    DeviceBuffer<float> attn_scratch_;
+    bool attn_decode8_ = true;
     int n_sm_ = 148;
     bool stream_gemm_ = true;
     SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;

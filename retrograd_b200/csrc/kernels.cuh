@@ -173,10 +173,18 @@ bool attention_mma_supported(int n_head, int n_head_kv, int head_dim, int block_
 // `skip_small`: leave items of at most 16 query vectors to launch_attention_decode.
 void launch_attention_mma(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
                           const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, bool skip_small, cudaStream_t stream);
-// Items of at most 16 query vectors (decode rows): the CTA's four warps split the KV blocks.
+// Items of at most 16 query vectors (decode rows): the CTA's four warps split the KV blocks. Items of
+// at most `min_cols` query vectors are left to launch_attention_decode8.
 void launch_attention_decode(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items,
-                             const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo,
+                             const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int min_cols,
                              cudaStream_t stream);
+// Items of at most 8 query vectors, keys as the MMA's M dimension; `n_splits` CTAs share one item's KV
+// blocks and a merge kernel combines them (`scratch`: attention_decode8_scratch_floats() floats).
+bool attention_decode8_supported(int n_head, int n_head_kv, int head_dim, int block_tokens);
+size_t attention_decode8_scratch_floats(int n_items, int n_head_kv, int n_splits, int head_dim);
+void launch_attention_decode8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items,
+                              const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int n_splits,
+                              float * scratch, cudaStream_t stream);
 // h[t][i] = silu(gu[t][i]) * gu[t][ff + i]
 void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split = nullptr);
 
