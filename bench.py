@@ -401,7 +401,7 @@ def main():
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
     top = max(("gemm", "attention"), key=lambda k: profile[k]["ms"])
     bytes_per_weight = {"q4_k": 144 / 256, "q8_0": 34 / 32, "f16": 2.0, "f32": 4.0}.get(sp["dtype"], 1.0)
-    if top == "gemm" and step_tokens / args.steps / world <= 16:
+    if top == "gemm" and step_tokens / args.steps <= 16:
         # few tokens per step: the launches are bound by streaming every weight byte once per step
         weight_bytes = (sp["layers"] * w_elems_layer + sp["d"] * sp["vocab"]) * bytes_per_weight * args.steps
         achieved = weight_bytes / (profile["gemm"]["ms"] * 1e-3) / 1e9
@@ -430,7 +430,8 @@ def main():
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": cfg["name"], "n_batch": cfg["n_batch"], "n_ctx": cfg["n_ctx"], "parallelism": f"replicas x{world}",
                    "rows_per_step": statistics.mean(rows_per_step), "decode_tokens_per_step": decode_tokens / args.steps / world,
-                   "prefill_tokens_per_step": prefill_tokens / args.steps / world, "ramp_steps": ramp_steps,
+                   "prefill_tokens_per_step": prefill_tokens / args.steps / world, "tokens_per_step": step_tokens / args.steps,
+                   "ramp_steps": ramp_steps,
                    "l2": "inputs larger than L2: every step streams >4 GB of weights and the ragged KV"},
         "e2e": {"value": decode_tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps},
         "gpu_launches": int(launches),

@@ -231,28 +231,26 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_kernel(const flo
     }
 }
 
-// out = merge over the splits of one (item, kv head): grid (items, kv heads), HD threads
+// out = merge over the splits of one (item, kv head, column): grid (items, kv heads, 8), HD threads
 template <int HD>
 __global__ void attention_decode8_merge_kernel(const float * __restrict__ partial, int n_head, int n_head_kv, const int2 * __restrict__ items,
                                                float * __restrict__ out, int ldo, int n_splits) {
     const int G = n_head / n_head_kv;
     const int2 item = items[blockIdx.x];
-    const int cols = item.y * G;
-    if (cols > 8) return;
+    const int cols = item.y * G, c = blockIdx.z;
+    if (cols > 8 || c >= cols) return;
     const int hk = blockIdx.y, dcol = threadIdx.x;
-    const float * src = partial + ((size_t)blockIdx.x * n_head_kv + hk) * n_splits * 8 * (HD + 2);
-    for (int c = 0; c < cols; ++c) {
-        float M = -INFINITY;
-        for (int z = 0; z < n_splits; ++z) M = fmaxf(M, src[((size_t)z * 8 + c) * (HD + 2) + HD]);
-        float num = 0.f, den = 0.f;
-        for (int z = 0; z < n_splits; ++z) {
-            const float * p = src + ((size_t)z * 8 + c) * (HD + 2);
-            const float f = p[HD] == -INFINITY ? 0.f : expf(p[HD] - M);
-            num += f * p[dcol];
-            den += f * p[HD + 1];
-        }
-        out[(size_t)(item.x + c / G) * ldo + (size_t)(hk * G + c % G) * HD + dcol] = num / den;
+    const float * src = partial + (((size_t)blockIdx.x * n_head_kv + hk) * n_splits * 8 + c) * (HD + 2);
+    float M = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, src[(size_t)z * 8 * (HD + 2) + HD]);
+    float num = 0.f, den = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+        const float * p = src + (size_t)z * 8 * (HD + 2);
+        const float f = p[HD] == -INFINITY ? 0.f : expf(p[HD] - M);
+        num += f * p[dcol];
+        den += f * p[HD + 1];
     }
+    out[(size_t)(item.x + c / G) * ldo + (size_t)(hk * G + c % G) * HD + dcol] = num / den;
 }
 
 template <int HD>
@@ -268,7 +266,7 @@ void launch_hd8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, c
     attention_decode8_kernel<HD><<<dim3(n_items, kv.n_head_kv, n_splits), D8_THREADS, smem, stream>>>(qkv, ld, n_head, kv, layer, items, tok_slot,
                                                                                                       tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
     if (n_splits > 1)
-        attention_decode8_merge_kernel<HD><<<dim3(n_items, kv.n_head_kv), HD, 0, stream>>>(scratch, n_head, kv.n_head_kv, items, out, ldo, n_splits);
+        attention_decode8_merge_kernel<HD><<<dim3(n_items, kv.n_head_kv, 8), HD, 0, stream>>>(scratch, n_head, kv.n_head_kv, items, out, ldo, n_splits);
 }
 
 } // namespace

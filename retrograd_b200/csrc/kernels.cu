@@ -364,7 +364,9 @@ __global__ void gemm_rows_kernel(WeightView w, const float * __restrict__ x, int
     }
 }
 
-// qkv row layout: [q: n_head*hd | k: n_head_kv*hd | v: n_head_kv*hd]
+// qkv row layout: [q: n_head*hd | k: n_head_kv*hd | v: n_head_kv*hd]. Grid (tokens, groups of eight
+// rotated heads): a block rotates its heads in place, then stores the K heads among them into the
+// cache; the blocks of group 0 also store the token's V heads.
 __global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, int n_head_kv, int head_dim, int n_rot, int neox,
                                   const float * __restrict__ inv_freq, const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_cell,
                                   KvLayout kv, int layer) {
@@ -373,8 +375,9 @@ __global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, 
     const int pos = tok_pos[t];
     const int half_rot = n_rot / 2;
     const int n_rot_heads = n_head + n_head_kv;
-    for (int idx = threadIdx.x; idx < n_rot_heads * half_rot; idx += blockDim.x) {
-        const int h = idx / half_rot, i = idx % half_rot;
+    const int h_lo = blockIdx.y * 8, h_hi = min(n_rot_heads, h_lo + 8);
+    for (int idx = threadIdx.x; idx < (h_hi - h_lo) * half_rot; idx += blockDim.x) {
+        const int h = h_lo + idx / half_rot, i = idx % half_rot;
         float * p = row + (size_t)h * head_dim;   // k heads follow the q heads contiguously
         const float theta = (float)pos * inv_freq[i];
         float s, c;
@@ -391,11 +394,16 @@ __global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, 
     const float * vsrc = ksrc + (size_t)n_head_kv * head_dim;
     __half * kdst = kv.k + layer * kv.layer_stride;
     __half * vdst = kv.v + layer * kv.layer_stride;
-    for (int idx = threadIdx.x; idx < n_head_kv * head_dim; idx += blockDim.x) {
+    const int k_lo = max(h_lo, n_head) - n_head, k_hi = h_hi - n_head;       // K heads rotated by this block
+    for (int idx = threadIdx.x + k_lo * head_dim; idx < k_hi * head_dim; idx += blockDim.x) {
         const int h = idx / head_dim, i = idx % head_dim;
-        const size_t dst = (((size_t)blk * n_head_kv + h) * kv.block_tokens + off) * head_dim + i;
-        kdst[dst] = __float2half_rn(ksrc[idx]);
-        vdst[dst] = __float2half_rn(vsrc[idx]);
+        kdst[(((size_t)blk * n_head_kv + h) * kv.block_tokens + off) * head_dim + i] = __float2half_rn(ksrc[idx]);
+    }
+    if (blockIdx.y == 0) {
+        for (int idx = threadIdx.x; idx < n_head_kv * head_dim; idx += blockDim.x) {
+            const int h = idx / head_dim, i = idx % head_dim;
+            vdst[(((size_t)blk * n_head_kv + h) * kv.block_tokens + off) * head_dim + i] = __float2half_rn(vsrc[idx]);
+        }
     }
 }
 
@@ -703,8 +711,8 @@ void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, floa
 
 void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
                        const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream) {
-    rope_store_kernel<<<n_tokens, 256, 0, stream>>>(qkv, ld, n_head, n_head_kv, head_dim, n_rot, neox ? 1 : 0, inv_freq, tok_pos, tok_cell, kv,
-                                                    layer);
+    rope_store_kernel<<<dim3(n_tokens, (n_head + n_head_kv + 7) / 8), 256, 0, stream>>>(qkv, ld, n_head, n_head_kv, head_dim, n_rot, neox ? 1 : 0,
+                                                                                        inv_freq, tok_pos, tok_cell, kv, layer);
 }
 
 void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,
