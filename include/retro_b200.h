@@ -248,8 +248,10 @@ int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uin
 
 /* One dequant-fused GEMM on host data: y[t][o] = sum_k deq(w)[o][k] * x[t][k] with w stored as
  * `ggml_type` rows. path: 0 engine's choice, 1 f32 row kernel, 2 single-term f16 tensor-core
- * kernel, 3 exact tensor-core kernel. Runs `iters` timed launches after one warm-up; *out_ms is
- * the mean device time per launch. */
+ * kernel, 3 exact tensor-core kernel (mma.sync), 4 exact tcgen05 kernel, 5 exact weight-streaming
+ * kernel (at most 8 tokens). Runs `iters` timed launches after one warm-up; *out_ms is the mean
+ * device time per launch (operands smaller than 256 MB: a buffer larger than L2 is written before
+ * every timed launch). */
 int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, uint32_t n_in, const float * x, uint32_t n_tokens, float * y,
                        int path, uint32_t iters, float * out_ms);
 
