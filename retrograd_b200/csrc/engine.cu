@@ -93,6 +93,15 @@ void Engine::load_model(const std::string & path) {
             launch_q4k_retile(dev, w.n_out, w.n_in, w.row_bytes, static_cast<uint8_t *>(tiled), stream);
             w.tiled = static_cast<const uint8_t *>(tiled);
             m.tiled_bytes += bytes;
+        } else if (t.type == GGML_Q8_0 && t.ne.size() == 2 && w.n_in % 256 == 0 && rows >= 16) {
+            // second copy in MMA fragment order for the decode streaming kernel
+            void * tiled = nullptr;
+            const size_t bytes = q8_0_tiled_bytes(w.n_out, w.n_in);
+            RB_CUDA(cudaMalloc(&tiled, bytes));
+            m.allocations.push_back(tiled);
+            launch_q8_0_retile(dev, w.n_out, w.n_in, w.row_bytes, static_cast<uint8_t *>(tiled), stream);
+            w.tiled = static_cast<const uint8_t *>(tiled);
+            m.tiled_bytes += bytes;
         }
         return w;
     };
@@ -349,6 +358,10 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
         stream_scratch_.ensure(gemm_q4k_stream_scratch_floats(w.n_out, w.n_in));
         launch_gemm_q4k_stream(w, *xs, T, y, ldy, bias, residual, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
         ++last_launches;
+    } else if (xs && stream_gemm_ && gemm_q8_0_stream_supported(w, *xs, T)) {
+        stream_scratch_.ensure(gemm_q4k_stream_scratch_floats(w.n_out, w.n_in));
+        launch_gemm_q8_0_stream(w, *xs, T, y, ldy, bias, residual, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
+        ++last_launches;
     } else if (xs && T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) {
         launch_gemm_q4k_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, stream);
     } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {
@@ -365,7 +378,7 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
 bool Engine::linear_reads_split(const WeightView & w, int ldx, int T, const SplitAct * xs) const {
     if (!xs) return false;
     if (T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) return true;
-    if (stream_gemm_ && gemm_q4k_stream_supported(w, *xs, T)) return true;
+    if (stream_gemm_ && (gemm_q4k_stream_supported(w, *xs, T) || gemm_q8_0_stream_supported(w, *xs, T))) return true;
     if (T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) return true;
     return T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs);
 }

@@ -284,6 +284,11 @@ __global__ void gemm_q4k_stream_finish_kernel(const float * __restrict__ partial
 
 } // namespace
 
+void launch_gemm_stream_finish(const float * scratch, int n_chunks, int n_out, int n_tokens, float * y, int ldy, const float * bias,
+                               const float * residual, int ldr, cudaStream_t stream) {
+    gemm_q4k_stream_finish_kernel<<<dim3((n_out + 255) / 256, n_tokens), 256, 0, stream>>>(scratch, n_chunks, n_out, n_tokens, y, ldy, bias, residual, ldr);
+}
+
 bool gemm_q4k_stream_supported(const WeightView & w, const SplitAct & x, int n_tokens) {
     return w.type == GGML_Q4_K && w.tiled && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && n_tokens >= 1 && n_tokens <= 8;
 }
@@ -313,8 +318,7 @@ void launch_gemm_q4k_stream(const WeightView & w, const SplitAct & x, int n_toke
         gemm_q4k_stream_kernel<true><<<grid, STHREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
     else
         gemm_q4k_stream_kernel<false><<<grid, STHREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
-    gemm_q4k_stream_finish_kernel<<<dim3((w.n_out + 255) / 256, n_tokens), 256, 0, stream>>>(scratch, n_chunks, (int)w.n_out, n_tokens, y, ldy, bias,
-                                                                                          residual, ldr);
+    launch_gemm_stream_finish(scratch, n_chunks, (int)w.n_out, n_tokens, y, ldy, bias, residual, ldr, stream);
 }
 
 } // namespace rb200

@@ -15,8 +15,9 @@ struct WeightView {
     uint32_t n_in = 0;
     uint32_t n_out = 0;
     uint32_t row_bytes = 0;
-    // Q4_K only, optional: the same blocks in the tile-major layout described at kQ4kTileBytes, rows
-    // zero-padded to a multiple of 128. Read by the tcgen05 kernel and the weight-streaming kernel.
+    // Q4_K, optional: the same blocks in the tile-major layout described at kQ4kTileBytes, rows
+    // zero-padded to a multiple of 128 (read by the tcgen05 kernel and the weight-streaming kernel).
+    // Q8_0, optional: the layout described at kQ8TileBytes, rows padded to a multiple of 16.
     const uint8_t * tiled = nullptr;
 };
 
@@ -161,6 +162,17 @@ bool gemm_q4k_stream_supported(const WeightView & w, const SplitAct & x, int n_t
 size_t gemm_q4k_stream_scratch_floats(uint32_t n_out, uint32_t n_in);
 void launch_gemm_q4k_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
                             const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream);
+// y = sum over K chunks (in order) of the streaming kernels' partial sums + bias + residual
+void launch_gemm_stream_finish(const float * scratch, int n_chunks, int n_out, int n_tokens, float * y, int ldy, const float * bias,
+                               const float * residual, int ldr, cudaStream_t stream);
+// Q8_0 counterpart of the streaming kernel. Its tile-major copy: one 2176-byte tile per (16 rows,
+// 128 columns): the 16 x 4 block scales, then the int8 weights in MMA fragment order.
+constexpr size_t kQ8TileBytes = 2176;
+inline size_t q8_0_tiled_bytes(uint32_t n_out, uint32_t n_in) { return (size_t)((n_out + 15) / 16) * (n_in / 256) * 2 * kQ8TileBytes; }
+void launch_q8_0_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream);
+bool gemm_q8_0_stream_supported(const WeightView & w, const SplitAct & x, int n_tokens);
+void launch_gemm_q8_0_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
+                             const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream);
 // In-place RoPE on q and k (inside the fused qkv buffer) and the f16 store of k, v into the paged cache.
 void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
                        const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream);

@@ -48,6 +48,11 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             launch_q4k_retile(dw.ptr, n_out, n_in, (uint32_t)rb, dtiled.ptr, stream);
             wv.tiled = dtiled.ptr;
         }
+        if (ggml_type == GGML_Q8_0 && n_in % 256 == 0 && path == 5) {
+            dtiled.ensure(q8_0_tiled_bytes(n_out, n_in));
+            launch_q8_0_retile(dw.ptr, n_out, n_in, (uint32_t)rb, dtiled.ptr, stream);
+            wv.tiled = dtiled.ptr;
+        }
         const bool have_split = xs.get() != nullptr;
         if (have_split) launch_split_prep(dx.ptr, (int)n_in, (int)n_in, (int)n_tokens, xs.view, stream);
         int chosen = path;
@@ -63,7 +68,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
         }
         if (chosen == 5) {
-            if (!(have_split && gemm_q4k_stream_supported(wv, xs.view, (int)n_tokens))) {
+            if (!(have_split && (gemm_q4k_stream_supported(wv, xs.view, (int)n_tokens) || gemm_q8_0_stream_supported(wv, xs.view, (int)n_tokens)))) {
                 cudaStreamDestroy(stream);
                 set_error("op_gemm: the requested kernel does not cover this type or shape");
                 return STATUS_INVALID_ARGUMENT;
@@ -82,7 +87,8 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             return STATUS_INVALID_ARGUMENT;
         }
         auto run = [&]() {
-            if (chosen == 5) launch_gemm_q4k_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
+            if (chosen == 5 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
+            else if (chosen == 5) launch_gemm_q4k_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
             else if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, stream);
             else if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 2) launch_gemm_mma(wv, xs.view.hi, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);

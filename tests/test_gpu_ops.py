@@ -60,3 +60,23 @@ def test_q4k_streaming_gemm_against_float64(rb, oracle, n_out, n_in, T):
     assert err < 4e-6
     again, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=5)
     assert np.array_equal(got, again)
+
+
+@pytest.mark.parametrize("n_out,n_in,T", [(256, 512, 1), (384, 1024, 3), (200, 768, 8), (40, 256, 5), (1040, 4096, 8), (128, 14336, 2)])
+def test_q8_0_streaming_gemm_against_float64(rb, oracle, n_out, n_in, T):
+    """The Q8_0 weight-streaming kernel for at most eight tokens against the exact product of the
+    decoded weights, and against the f32 row kernel on the same bytes."""
+    rng = np.random.default_rng(13 * n_out + T)
+    w = rng.normal(0, 0.02, (n_out, n_in)).astype(np.float32)
+    raw = np.frombuffer(b"".join(rb.quantize_row(8, w[r]) for r in range(n_out)), dtype=np.uint8)
+    x = rng.normal(0, 1.5, (T, n_in)).astype(np.float32)
+    wd = oracle.dequantize_row(oracle.T_Q8_0, raw, n_out * n_in).reshape(n_out, n_in).astype(np.float64)
+    want = x.astype(np.float64) @ wd.T
+    got, _ = rb.op_gemm(8, raw, n_out, n_in, x, path=5)
+    rows, _ = rb.op_gemm(8, raw, n_out, n_in, x, path=1)
+    scale = float(np.abs(want).max())
+    err, err_rows = float(np.abs(got - want).max()) / scale, float(np.abs(rows - want).max()) / scale
+    print(f"q8_0 stream {n_out}x{n_in} T={T}: rel err {err:.2e} (row kernel {err_rows:.2e})")
+    assert err < 4e-6 and err_rows < 4e-6
+    again, _ = rb.op_gemm(8, raw, n_out, n_in, x, path=5)
+    assert np.array_equal(got, again)
