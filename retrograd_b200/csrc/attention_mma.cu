@@ -1,11 +1,11 @@
 // Paged attention over ragged sequences on the tensor cores: decode rows (one token) and prefill
 // chunk rows (many tokens) in one launch.
 //
-// A CTA serves one work item = (up to 64 / G consecutive tokens of one step row) x (one KV head),
-// G = query heads per KV head. Its 64 query vectors (token, head-in-group) form four m16 tiles,
-// one per warp. The KV blocks of the slot are found through the block table and streamed, 16
+// A CTA serves one work item = (up to 128 / G consecutive tokens of one step row) x (one KV head),
+// G = query heads per KV head. Its 128 query vectors (token, head-in-group) form eight m16 tiles,
+// one per warp (the wider the tile, the fewer times a prefill chunk re-reads its context). The KV blocks of the slot are found through the block table and streamed, 16
 // tokens at a time, into a four-stage cp.async ring of 128B-swizzled shared-memory tiles that all
-// four warps share; scores and the output are accumulated with mma.sync m16n8k16 (f16 operands,
+// eight warps share; scores and the output are accumulated with mma.sync m16n8k16 (f16 operands,
 // f32 accumulators) under a warp-level online softmax.
 //
 // Accuracy: K and V are f16 by storage, so they are exact operands. The query (pre-scaled by
@@ -23,9 +23,9 @@ namespace rb200 {
 
 namespace {
 
-constexpr int ATT_THREADS = 128;
+constexpr int ATT_THREADS = 256;
 constexpr int ATT_STAGES = 4;
-constexpr int ATT_ROWS = 64;       // query vectors per CTA
+constexpr int ATT_ROWS = kAttentionTileRows;       // query vectors per CTA: one m16 tile per warp
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -104,8 +104,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_mma_kernel(const float 
         const uint32_t k_s = smem_u32(kv_s + stage * 2 * TILE_BYTES);
         const uint32_t v_s = k_s + TILE_BYTES;
 #pragma unroll
-        for (int i = 0; i < 16 * HD / 8 / ATT_THREADS; ++i) {
+        for (int i = 0; i < (16 * HD / 8 + ATT_THREADS - 1) / ATT_THREADS; ++i) {
             const int c = tid + i * ATT_THREADS;                 // 16-byte chunk of the tile
+            if (c >= 16 * HD / 8) break;                         // fewer chunks than threads (head_dim 64)
             const int token = c / (HD / 8), dchunk = c % (HD / 8);
             const uint32_t off = (uint32_t)((dchunk >> 3) * (16 * 128)) + swz(token, dchunk & 7);
             cp_async16(k_s + off, kbase + base + (size_t)c * 8, 16);

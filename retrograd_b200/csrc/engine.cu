@@ -84,6 +84,11 @@ void Engine::load_model(const std::string & path) {
         w.n_in = (uint32_t)t.ne[0];
         w.n_out = (uint32_t)rows;
         w.row_bytes = (uint32_t)row_bytes(t.type, t.ne[0]);
+        const bool wants_tiled = t.ne.size() == 2 && w.n_in % 256 == 0 &&
+                                 ((t.type == GGML_Q4_K && rows >= 128) || (t.type == GGML_Q8_0 && rows >= 16));
+        // A blocking copy from pageable host memory may return while its last piece is still on its way
+        // to the device; the regrouping kernels run on another stream, so wait for the device first.
+        if (wants_tiled) RB_CUDA(cudaDeviceSynchronize());
         if (t.type == GGML_Q4_K && t.ne.size() == 2 && w.n_in % 256 == 0 && rows >= 128) {
             // second copy regrouped for the tcgen05 kernel's coalesced weight stream
             void * tiled = nullptr;
@@ -220,6 +225,8 @@ void Engine::load_model(const std::string & path) {
     m.bos = (int32_t)file.u32("tokenizer.ggml.bos_token_id", 1);
     m.add_bos = file.u32("tokenizer.ggml.add_bos_token", 1) != 0;
 
+    // every blocking upload above has reached the device before any stream's kernel reads the weights
+    RB_CUDA(cudaDeviceSynchronize());
     // fingerprint = FNV-1a(path || u64 file size), as the reference keys its prefix caches
     uint64_t h = fnv1a(path.data(), path.size());
     const uint64_t size = file.file_size();
@@ -247,6 +254,10 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     kv_layer_stride_ = (uint64_t)n_blocks * hp.n_head_kv * kBlockTokens * hp.head_dim;
     kcache_.ensure(kv_layer_stride_ * hp.n_layer);
     vcache_.ensure(kv_layer_stride_ * hp.n_layer);
+    // Cells past a sequence's end in its last block are read (and masked) by the attention kernels:
+    // a masked probability of zero times a leftover NaN bit pattern would still be NaN.
+    RB_CUDA(cudaMemset(kcache_.ptr, 0, kv_layer_stride_ * hp.n_layer * sizeof(*kcache_.ptr)));
+    RB_CUDA(cudaMemset(vcache_.ptr, 0, kv_layer_stride_ * hp.n_layer * sizeof(*vcache_.ptr)));
     RB_CUDA(cudaMemsetAsync(kcache_.ptr, 0, kcache_.count * sizeof(__half), stream));
     RB_CUDA(cudaMemsetAsync(vcache_.ptr, 0, vcache_.count * sizeof(__half), stream));
     block_table_.ensure((size_t)config.n_seq_max * max_blocks);
@@ -269,7 +280,7 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     maps.attn_items = reinterpret_cast<int2 *>(p);
     attn_mma_ = attention_mma_supported((int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)kBlockTokens);
     if (const char * env = std::getenv("RB200_ATTENTION")) attn_mma_ = attn_mma_ && std::string(env) != "ref";
-    attn_tile_tokens_ = attn_mma_ ? 64 / (int)(hp.n_head / hp.n_head_kv) : 64;
+    attn_tile_tokens_ = attn_mma_ ? kAttentionTileRows / (int)(hp.n_head / hp.n_head_kv) : 64;
 
     x_.ensure(T * hp.d);
     xn_.ensure(T * hp.d);
@@ -1235,6 +1246,7 @@ void Engine::restack_adapters() {
         stacked_bytes_ += (a.size() + b.size()) * 4;
         lora_targets_[sh.first] = std::move(target);
     }
+    RB_CUDA(cudaDeviceSynchronize());      // the blocking uploads have reached the device before the next step's kernels
 }
 
 void Engine::adapter_info(retro_adapter_rows_info * out) {

@@ -2,6 +2,7 @@
 // cache with its block tables, per-request sampler state, per-row adapters and the step executor.
 #pragma once
 
+#include <cstdlib>
 #include "common.hpp"
 #include "gguf.hpp"
 #include "kernels.cuh"
@@ -32,6 +33,10 @@ template <class T> struct DeviceBuffer {
         if (ptr) { cudaFree(ptr); ptr = nullptr; count = 0; }
         RB_CUDA(cudaMalloc(&ptr, n * sizeof(T)));
         count = n;
+        // RB200_POISON=1 fills every new work buffer with 0xFF bytes (NaN as f32/f16): a read of
+        // memory the step did not write then shows up in the results instead of depending on luck
+        static const bool poison = std::getenv("RB200_POISON") != nullptr;
+        if (poison) RB_CUDA(cudaMemset(ptr, 0xFF, n * sizeof(T)));
     }
 };
 

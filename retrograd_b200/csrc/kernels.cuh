@@ -180,7 +180,9 @@ void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, K
                           const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream,
                           const SplitAct * split = nullptr);
 void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream);
-// Tensor-core paged attention (head_dim 64 or 128, 16-token KV blocks, power-of-two GQA group).
+// Tensor-core paged attention (head_dim 64 or 128, 16-token KV blocks, power-of-two GQA group). Work
+// items hold at most kAttentionTileRows / G tokens.
+constexpr int kAttentionTileRows = 128;
 bool attention_mma_supported(int n_head, int n_head_kv, int head_dim, int block_tokens);
 // `skip_small`: leave items of at most 16 query vectors to launch_attention_decode.
 void launch_attention_mma(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,

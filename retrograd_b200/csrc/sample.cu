@@ -438,6 +438,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float * __restri
             pid = bi;
         }
     }
+    if (token < 0 || token >= V) token = 0;      // a row of NaNs has no arg-max: stay inside the row
     if (tid == 0) {
         SampleOut o;
         o.token = token;
@@ -532,6 +533,7 @@ __global__ void greedy_finish_kernel(const float * __restrict__ raw_logits, int 
     double total = 0.0;
     for (int c = 0; c < n_chunks; ++c) total += st[c].sum * exp((double)st[c].max - (double)rmax);
     const double rlog = log(total);
+    if (token < 0 || token >= V) token = 0;      // a row of NaNs has no arg-max: stay inside the row
     const float * raw = raw_logits + (size_t)row * V;
     const double inv_t = 1.0 / (double)d.temperature;
     // the one-token nucleus: its post-transformation logprob is log(exp(0 / T) / 1)
