@@ -55,6 +55,13 @@ WORKLOADS = {
         spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
         n_requests=8, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=65536,
     ),
+    # the 8B shape in Q8_0 (BASELINE config 3's weights), again eight long-running requests
+    "c3_decode8": dict(
+        name="llama3-8b-shape Q8_0, 8 requests, decode-only steps of 8 tokens",
+        model="c3",
+        spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q8_0", seed=3),
+        n_requests=8, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=65536,
+    ),
     # BASELINE config 1 (CPU-runnable shape; used to exercise this script quickly)
     "c1": dict(
         name="tiny llama-style Q8_0, 8 requests",

@@ -377,6 +377,8 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
         launch_gemm_q4k_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, stream);
     } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {
         launch_gemm_q4k_exact(w, *xs, T, y, ldy, bias, residual, ldr, stream);
+    } else if (xs && T > mma_min_tokens && gemm_q8_0_exact_supported(w, *xs)) {
+        launch_gemm_q8_0_exact(w, *xs, T, y, ldy, bias, residual, ldr, stream);
     } else {
         launch_gemm_rows(w, x, ldx, T, y, ldy, bias, residual, ldr, stream);
     }
@@ -391,7 +393,7 @@ bool Engine::linear_reads_split(const WeightView & w, int ldx, int T, const Spli
     if (T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) return true;
     if (stream_gemm_ && (gemm_q4k_stream_supported(w, *xs, T) || gemm_q8_0_stream_supported(w, *xs, T))) return true;
     if (T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) return true;
-    return T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs);
+    return T > mma_min_tokens && (gemm_q4k_exact_supported(w, *xs) || gemm_q8_0_exact_supported(w, *xs));
 }
 
 void Engine::lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy) {

@@ -173,6 +173,10 @@ void launch_q8_0_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uin
 bool gemm_q8_0_stream_supported(const WeightView & w, const SplitAct & x, int n_tokens);
 void launch_gemm_q8_0_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
                              const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream);
+// Exact tensor-core Q8_0 GEMM (mma.sync) for more than 8 tokens; reads the GGUF-layout rows.
+bool gemm_q8_0_exact_supported(const WeightView & w, const SplitAct & x);
+void launch_gemm_q8_0_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
+                            const float * residual, int ldr, cudaStream_t stream);
 // In-place RoPE on q and k (inside the fused qkv buffer) and the f16 store of k, v into the paged cache.
 void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
                        const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream);

@@ -80,7 +80,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             set_error("op_gemm: the requested kernel does not cover this type or shape");
             return STATUS_INVALID_ARGUMENT;
         }
-        if ((chosen == 3 && !(have_split && gemm_q4k_exact_supported(wv, xs.view))) ||
+        if ((chosen == 3 && !(have_split && (gemm_q4k_exact_supported(wv, xs.view) || gemm_q8_0_exact_supported(wv, xs.view)))) ||
             (chosen == 2 && !(have_split && gemm_mma_supported(wv, (int)n_in)))) {
             cudaStreamDestroy(stream);
             set_error("op_gemm: the requested kernel does not cover this type or shape");
@@ -90,6 +90,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             if (chosen == 5 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
             else if (chosen == 5) launch_gemm_q4k_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
             else if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, stream);
+            else if (chosen == 3 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 2) launch_gemm_mma(wv, xs.view.hi, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else launch_gemm_rows(wv, dx.ptr, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);

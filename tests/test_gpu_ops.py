@@ -80,3 +80,18 @@ def test_q8_0_streaming_gemm_against_float64(rb, oracle, n_out, n_in, T):
     assert err < 4e-6 and err_rows < 4e-6
     again, _ = rb.op_gemm(8, raw, n_out, n_in, x, path=5)
     assert np.array_equal(got, again)
+
+
+@pytest.mark.parametrize("n_out,n_in,T", [(256, 512, 9), (384, 1024, 16), (200, 768, 33), (512, 2048, 100), (256, 4096, 300), (130, 192, 70)])
+def test_q8_0_tensor_core_gemm_against_float64(rb, oracle, n_out, n_in, T):
+    """The exact Q8_0 tensor-core kernel (more than 8 tokens): per-block scales applied in f32."""
+    rng = np.random.default_rng(17 * n_out + T)
+    w = rng.normal(0, 0.02, (n_out, n_in)).astype(np.float32)
+    raw = np.frombuffer(b"".join(rb.quantize_row(8, w[r]) for r in range(n_out)), dtype=np.uint8)
+    x = rng.normal(0, 1.5, (T, n_in)).astype(np.float32)
+    wd = oracle.dequantize_row(oracle.T_Q8_0, raw, n_out * n_in).reshape(n_out, n_in).astype(np.float64)
+    want = x.astype(np.float64) @ wd.T
+    got, _ = rb.op_gemm(8, raw, n_out, n_in, x, path=3)
+    err = float(np.abs(got - want).max()) / float(np.abs(want).max())
+    print(f"q8_0 mma {n_out}x{n_in} T={T}: rel err {err:.2e}")
+    assert err < 4e-6
