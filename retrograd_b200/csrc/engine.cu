@@ -298,6 +298,7 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&n_sm_, cudaDevAttrMultiProcessorCount, dev);
         if (const char * env = std::getenv("RB200_GEMM")) stream_gemm_ = std::string(env) != "rows";
+        if (const char * env = std::getenv("RB200_GRAPHS")) graphs_enabled_ = std::string(env) != "0";
         if (const char * env = std::getenv("RB200_ATTENTION")) attn_decode8_ = std::string(env) != "decode16";
     }
     device_error_.ensure(1);
@@ -384,6 +385,74 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
     }
     prof_.end(K_GEMM, 1, stream);
     ++last_launches;
+}
+
+// Runs one step's device work: eagerly, or as a replayed / freshly captured CUDA graph.
+void Engine::run_step_work(const std::vector<uint64_t> & sig, const std::function<void()> & issue) {
+    const bool graphable = graphs_enabled_ && !prof_.enabled && model->hp.n_expert == 0;
+    if (graph_epoch_ != g_alloc_epoch.load()) {       // some buffer moved: every captured pointer is stale
+        for (auto & e : graphs_) if (e.second.exec) cudaGraphExecDestroy(e.second.exec);
+        graphs_.clear();
+        graph_epoch_ = g_alloc_epoch.load();
+    }
+    GraphEntry * entry = nullptr;
+    if (graphable) {
+        uint64_t key = 1469598103934665603ull;
+        for (uint64_t v : sig) key = (key ^ v) * 1099511628211ull;
+        auto it = graphs_.find(key);
+        if (it != graphs_.end() && it->second.sig != sig) {       // a collision: forget the old entry
+            if (it->second.exec) cudaGraphExecDestroy(it->second.exec);
+            graphs_.erase(it);
+            it = graphs_.end();
+        }
+        if (it == graphs_.end()) {
+            if (graphs_.size() >= 64) {
+                for (auto & e : graphs_) if (e.second.exec) cudaGraphExecDestroy(e.second.exec);
+                graphs_.clear();
+            }
+            it = graphs_.emplace(key, GraphEntry{sig, nullptr, 0, 0}).first;
+        }
+        entry = &it->second;
+    }
+    RB_CUDA(cudaEventRecord(ev_begin_, stream));
+    if (entry && entry->exec) {
+        RB_CUDA(cudaGraphLaunch(entry->exec, stream));
+        last_launches = entry->launches;
+        ++graph_replays_;
+    } else if (entry && entry->seen >= 1 && !entry->failed) {
+        // second occurrence: capture, instantiate, launch
+        const uint64_t epoch_before = g_alloc_epoch.load();
+        cudaGraph_t graph = nullptr;
+        bool ok = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess;
+        if (ok) {
+            try {
+                issue();
+            } catch (...) {
+                cudaStreamEndCapture(stream, &graph);
+                if (graph) cudaGraphDestroy(graph);
+                cudaGetLastError();
+                entry->failed = true;
+                throw;
+            }
+            ok = cudaStreamEndCapture(stream, &graph) == cudaSuccess && graph != nullptr;
+        }
+        if (ok && epoch_before == g_alloc_epoch.load()) ok = cudaGraphInstantiate(&entry->exec, graph, 0) == cudaSuccess;
+        else ok = false;
+        if (graph) cudaGraphDestroy(graph);
+        if (ok) {
+            entry->launches = last_launches;
+            RB_CUDA(cudaGraphLaunch(entry->exec, stream));
+        } else {
+            cudaGetLastError();
+            entry->exec = nullptr;
+            entry->failed = true;
+            issue();            // nothing ran during the failed capture
+        }
+    } else {
+        issue();
+        if (entry) ++entry->seen;
+    }
+    RB_CUDA(cudaEventRecord(ev_end_, stream));
 }
 
 // Whether linear() will read the split form of the activations for this weight and token count
@@ -741,35 +810,12 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     }
     if (any_adapter) lora_tmp_.ensure(T * (size_t)std::max<uint32_t>(r_max_, 1));
 
-    // ---- device work
-    last_launches = 0;
-    last_h2d_bytes = stage_total;
-    last_d2h_bytes = S ? res_total - 16 : 0;
-    RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
-    RB_CUDA(cudaEventRecord(ev_begin_, stream));
-    const RowDesc * d_rows = reinterpret_cast<const RowDesc *>(d_stage_.ptr + off_rows);
-    const int32_t * d_tokens = reinterpret_cast<const int32_t *>(d_stage_.ptr + off_tokens);
-    const KvLayout kvl = kv_layout();
-#define RB_K(cls, n, ...)            \
-    do {                             \
-        prof_.begin(cls, stream);    \
-        __VA_ARGS__;                 \
-        prof_.end(cls, n, stream);   \
-        last_launches += (n);        \
-    } while (0)
-    if (n_patches) {
-        RB_K(K_OTHER, 1, launch_block_table_patch(block_table_.ptr, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_patches), n_patches, stream));
-    }
-    if (n_copies) {
-        RB_K(K_OTHER, 1, launch_kv_block_copy(kvl, (int)hp.n_layer, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_copies), n_copies, stream));
-    }
-    RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, attn_tile_tokens_, maps, stream));
     // Attention work items by width in query vectors (tokens x heads of the GQA group): more than 16 go
     // to the tile kernel, 9..16 to the 16-row decode kernel, at most 8 to the eight-column kernel.
     int n_attn_items = 0, n_small_items = 0, max_ctx = 1;
     bool any_wide_item = false, any_mid_item = false;
     const int attn_group = (int)(hp.n_head / hp.n_head_kv);
-    const bool use_decode8 = attn_decode8_ && attention_decode8_supported((int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, kvl.block_tokens);
+    const bool use_decode8 = attn_decode8_ && attention_decode8_supported((int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)kBlockTokens);
     for (size_t r = 0; r < R; ++r) {
         const int n = (int)rows[r].n, tail = n % attn_tile_tokens_;
         n_attn_items += (n + attn_tile_tokens_ - 1) / attn_tile_tokens_;
@@ -787,10 +833,40 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     int attn_splits = 1;
     if (n_small_items > 0) {
         const int want = (2 * n_sm_ + n_small_items * (int)hp.n_head_kv - 1) / (n_small_items * (int)hp.n_head_kv);
-        attn_splits = std::max(1, std::min({want, 16, (max_ctx / kvl.block_tokens) / 8}));
+        attn_splits = std::max(1, std::min({want, 16, (max_ctx / (int)kBlockTokens) / 8}));
         if (attn_splits > 1)
             attn_scratch_.ensure(attention_decode8_scratch_floats(n_attn_items, (int)hp.n_head_kv, attn_splits, (int)hp.head_dim));
     }
+
+    // ---- device work. Everything the launches depend on besides the contents of the staging buffer
+    // is in `sig`: a step whose signature was seen before is replayed as a CUDA graph (one launch
+    // instead of hundreds), captured the second time the signature occurs - the first time runs
+    // eagerly, so every lazy allocation and kernel attribute is in place before a capture.
+    last_h2d_bytes = stage_total;
+    last_d2h_bytes = S ? res_total - 16 : 0;
+    const std::vector<uint64_t> sig = {R, T, S, (uint64_t)n_patches, (uint64_t)n_copies, edits.size(), top_stride, any_v2, (uint64_t)n_greedy_fast,
+                                       any_adapter, (uint64_t)n_attn_items, (uint64_t)n_small_items, any_wide_item, any_mid_item,
+                                       (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_};
+    auto issue = [&]() {
+    last_launches = 0;
+    RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
+    const RowDesc * d_rows = reinterpret_cast<const RowDesc *>(d_stage_.ptr + off_rows);
+    const int32_t * d_tokens = reinterpret_cast<const int32_t *>(d_stage_.ptr + off_tokens);
+    const KvLayout kvl = kv_layout();
+#define RB_K(cls, n, ...)            \
+    do {                             \
+        prof_.begin(cls, stream);    \
+        __VA_ARGS__;                 \
+        prof_.end(cls, n, stream);   \
+        last_launches += (n);        \
+    } while (0)
+    if (n_patches) {
+        RB_K(K_OTHER, 1, launch_block_table_patch(block_table_.ptr, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_patches), n_patches, stream));
+    }
+    if (n_copies) {
+        RB_K(K_OTHER, 1, launch_kv_block_copy(kvl, (int)hp.n_layer, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_copies), n_copies, stream));
+    }
+    RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, attn_tile_tokens_, maps, stream));
     cur_tok_adapter_ = maps.tok_adapter;
     cur_any_adapter_ = any_adapter;
 
@@ -834,6 +910,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         } else {
             RB_K(K_ATTN, 1, launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min,
                                                  att_.ptr, dq, stream, att_split_.get()));
+            // the reference kernel writes the split form itself only when a head is whole 32-column sub-blocks
+            if (att_split_.get() && hp.head_dim % 32 != 0) RB_K(K_OTHER, 1, launch_split_prep(att_.ptr, dq, dq, Ti, att_split_.view, stream));
         }
         // x = x + Wo att
         linear(lw.wo, att_.ptr, dq, Ti, x_.ptr, d, nullptr, x_.ptr, d, att_split_.get());
@@ -882,9 +960,10 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                                         (int)std::max<size_t>(top_stride, 1), n_greedy_fast, sample_scratch_.ptr, stream));
     }
 #undef RB_K
-    RB_CUDA(cudaEventRecord(ev_end_, stream));
     if (S) RB_CUDA(cudaMemcpyAsync(h_result_, d_result_.ptr, res_total - 16, cudaMemcpyDeviceToHost, stream));
     RB_CUDA(cudaMemcpyAsync(h_result_ + result_bytes_ - 16, device_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    };
+    run_step_work(sig, issue);
     const cudaError_t sync = cudaStreamSynchronize(stream);
     if (sync != cudaSuccess) {
         set_error(std::string("the decode failed on the device (") + cudaGetErrorString(sync) +

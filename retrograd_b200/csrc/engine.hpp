@@ -2,6 +2,8 @@
 // cache with its block tables, per-request sampler state, per-row adapters and the step executor.
 #pragma once
 
+#include <functional>
+#include <atomic>
 #include <cstdlib>
 #include "common.hpp"
 #include "gguf.hpp"
@@ -21,6 +23,9 @@ namespace rb200 {
 constexpr uint32_t kMaxSeq = 1024;        // sequence slots this backend accepts (the reference's fork caps at 256)
 constexpr uint32_t kBlockTokens = 16;     // KV cells per block
 
+// Bumped whenever a device work buffer is (re)allocated; captured step graphs are dropped when it moves.
+inline std::atomic<uint64_t> g_alloc_epoch{0};
+
 template <class T> struct DeviceBuffer {
     T * ptr = nullptr;
     size_t count = 0;
@@ -33,6 +38,7 @@ template <class T> struct DeviceBuffer {
         if (ptr) { cudaFree(ptr); ptr = nullptr; count = 0; }
         RB_CUDA(cudaMalloc(&ptr, n * sizeof(T)));
         count = n;
+        ++g_alloc_epoch;        // captured CUDA graphs hold the old pointer
         // RB200_POISON=1 fills every new work buffer with 0xFF bytes (NaN as f32/f16): a read of
         // memory the step did not write then shows up in the results instead of depending on luck
         static const bool poison = std::getenv("RB200_POISON") != nullptr;
@@ -251,6 +257,18 @@ private:
     void restack_adapters();
     void linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
                 const SplitAct * xs = nullptr);
+    struct GraphEntry {
+        std::vector<uint64_t> sig;
+        cudaGraphExec_t exec = nullptr;
+        uint32_t launches = 0;
+        int seen = 0;
+        bool failed = false;
+    };
+    std::unordered_map<uint64_t, GraphEntry> graphs_;
+    uint64_t graph_epoch_ = 0;
+    uint64_t graph_replays_ = 0;
+    bool graphs_enabled_ = true;
+    void run_step_work(const std::vector<uint64_t> & sig, const std::function<void()> & issue);
     bool linear_reads_split(const WeightView & w, int ldx, int T, const SplitAct * xs) const;
     void lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy);
     void flush_kv_updates();
