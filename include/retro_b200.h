@@ -269,6 +269,10 @@ int retro_b200_gemm_q4k_noalloc(const uint8_t * d_w, uint32_t n_out, uint32_t n_
 
 /* Bytes the last step copied host->device (the plan) and device->host (the sampled rows). */
 int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes);
+/* Steps served so far by replaying a captured CUDA graph, and graphs currently cached. A step shape
+ * (row count, token count, sampling rows, ...) seen twice is captured the second time and replayed
+ * afterwards; profiling, MoE models and RB200_GRAPHS=0 keep every step eager. */
+int retro_b200_engine_graph_stats(retro_engine * engine, uint64_t * out_replays, uint64_t * out_cached);
 /* Per-class kernel timing with CUDA events on the launching stream. Classes, in order:
  * gemm, attention, sample, pack, moe, lora, other (RETRO_B200_PROFILE_CLASSES entries).
  * `enabled` switches the bracketing on or off, `reset` clears the accumulated totals. */

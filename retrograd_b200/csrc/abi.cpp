@@ -742,6 +742,15 @@ int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uin
     });
 }
 
+int retro_b200_engine_graph_stats(retro_engine * engine, uint64_t * out_replays, uint64_t * out_cached) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        e->graph_stats(out_replays, out_cached);
+        return STATUS_OK;
+    });
+}
+
 int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes) {
     return boundary([&]() -> int {
         Engine * e = checked(engine);

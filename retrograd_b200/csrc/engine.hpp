@@ -269,6 +269,9 @@ private:
     uint64_t graph_replays_ = 0;
     bool graphs_enabled_ = true;
     void run_step_work(const std::vector<uint64_t> & sig, const std::function<void()> & issue);
+  public:
+    void graph_stats(uint64_t * replays, uint64_t * cached) const { if (replays) *replays = graph_replays_; if (cached) *cached = graphs_.size(); }
+  private:
     bool linear_reads_split(const WeightView & w, int ldx, int T, const SplitAct * xs) const;
     void lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy);
     void flush_kv_updates();

@@ -493,6 +493,12 @@ class Engine:
         _check(self._lib.retro_b200_engine_last_step_io(self._h, C.byref(a), C.byref(b)))
         return a.value, b.value
 
+    def graph_stats(self) -> tuple[int, int]:
+        """(steps replayed from a captured CUDA graph, graphs cached)."""
+        a, b = C.c_uint64(), C.c_uint64()
+        _check(self._lib.retro_b200_engine_graph_stats(self._h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     PROFILE_CLASSES = ("gemm", "attention", "sample", "pack", "moe", "lora", "other")
 
     def profile(self, enabled: bool, reset: bool = False) -> None:

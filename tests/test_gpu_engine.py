@@ -319,3 +319,31 @@ def test_plain_greedy_rows_equal_the_general_sampler_and_the_oracle(rb, oracle, 
         assert a.sampled_logprob == 0.0 and lps_a[0] == 0.0 and lps_a[1] == -np.inf
     for sid in range(6):
         engine.seq_rm(sid)
+
+
+def test_repeated_step_shapes_replay_as_cuda_graphs_with_identical_results(rb, oracle, c1_model, monkeypatch):
+    """A decode loop repeats one step shape: from its third occurrence on, the step is a replayed CUDA
+    graph. Tokens, logprobs and logits must equal the eager engine's bit for bit."""
+    def run(graphs: bool):
+        monkeypatch.setenv("RB200_GRAPHS", "1" if graphs else "0")
+        engine = rb.Engine(str(c1_model), rb.EngineConfig(n_ctx=1024, n_seq_max=4, n_batch=64, n_ubatch=64))
+        out = rb.StepOutput()
+        g = rb.SamplingParamsV2.greedy()
+        prompts = [_prompt(200 + i, 9 + i) for i in range(3)]
+        engine.step([rb.StepRow(i, i, p, 0, sample=True, sampling=g, want_logprob=True) for i, p in enumerate(prompts)], out)
+        last = [out.row(i).token for i in range(3)]
+        trace = []
+        for step in range(12):
+            rows = [rb.StepRow(i, i, [last[i]], len(prompts[i]) + step, sample=True, sampling=g, want_logprob=True) for i in range(3)]
+            engine.step(rows, out)
+            last = [out.row(i).token for i in range(3)]
+            trace.append(([out.row(i).token for i in range(3)], [out.row(i).logprob for i in range(3)], engine.last_logits(1).copy()))
+        stats = engine.graph_stats()
+        engine.close()
+        return trace, stats
+    eager, stats_eager = run(False)
+    graphed, stats_graphed = run(True)
+    assert stats_eager == (0, 0)
+    assert stats_graphed[0] >= 8 and stats_graphed[1] >= 1
+    for (t0, l0, x0), (t1, l1, x1) in zip(eager, graphed):
+        assert t0 == t1 and l0 == l1 and np.array_equal(x0, x1)
