@@ -415,6 +415,9 @@ def main():
     # whole job: the slowest rank's time, every rank's tokens (replicas, no data-path collective)
     (dev_ms, wall_s), (decode_tokens, prefill_tokens, launches) = aggregate(
         [dev_ms, wall_s], [decode_tokens, prefill_tokens, launches], dist, torch.device("cuda", local_rank))
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         engine.close()
         return
