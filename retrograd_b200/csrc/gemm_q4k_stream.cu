@@ -91,6 +91,10 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
         for (int s2 = 0; s2 < STAGES; ++s2)
             if (u_begin + s2 < u_end) issue(u_begin + s2, s2);
     }
+    // Launched with programmatic stream serialization: everything above touches only the weights, which
+    // no kernel writes, so it may run while the kernels before this one are still finishing. From here on
+    // the activations are read and results written: wait for every earlier kernel of the stream.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- this warp's activation fragments: MMA column g, K steps of its 128 columns
     uint32_t bh[8][2], bl[8][2], bmh = 0, bml = 0;
@@ -314,10 +318,19 @@ void launch_gemm_q4k_stream(const WeightView & w, const SplitAct & x, int n_toke
     const int units_per_cta = (n_units + ctas_x - 1) / ctas_x;
     ctas_x = (n_units + units_per_cta - 1) / units_per_cta;
     const dim3 grid(ctas_x, n_chunks);
-    if (n_tokens <= 4)
-        gemm_q4k_stream_kernel<true><<<grid, STHREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
-    else
-        gemm_q4k_stream_kernel<false><<<grid, STHREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
+    // the kernel may start while the stream's earlier kernels drain (it waits on the device before it reads activations)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(STHREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (n_tokens <= 4) cudaLaunchKernelEx(&cfg, gemm_q4k_stream_kernel<true>, w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
+    else cudaLaunchKernelEx(&cfg, gemm_q4k_stream_kernel<false>, w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
     launch_gemm_stream_finish(scratch, n_chunks, (int)w.n_out, n_tokens, y, ldy, bias, residual, ldr, stream);
 }
 

@@ -212,12 +212,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         Raw raw0, raw1;
         prefetch(group, raw0);
         prefetch(group + 2, raw1);
+        // programmatic stream serialization: only weights were touched so far; the activations follow
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int it = group; it < n_it; it += 4) {
             if (!produce(it, raw0)) break;
             if (it + 2 < n_it && !produce(it + 2, raw1)) break;
         }
     } else if (warp == 16) {
         // ------------------------------------------------------------------ MMA issue
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (lane == 0) {
             // The issuing thread is a single dependent instruction stream: everything that can be is
             // computed once here, so that a stage costs an add per operand and the MMAs themselves.
@@ -260,6 +263,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         }
     } else {
         // ------------------------------------------------------------------ epilogue
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int q = warp & 3;                         // TMEM lane quarter this warp may read
         const int colhalf = (warp - 8) >> 2;            // which 64 token columns
         const int o_local = q * 32 + lane;
@@ -379,12 +383,25 @@ void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens,
         configured = true;
     }
     const dim3 grid((n_tokens + BN - 1) / BN, (w.n_out + BM - 1) / BM);
+    // the kernel may start (barriers, tensor-memory allocation, first weight loads) while the stream's
+    // earlier kernels drain; every role waits on the device before it touches activations or outputs
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const float * no_residual = nullptr;
     if (residual) {
-        gemm_q4k_tc5_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
-                                                                        residual, ldr, error_flag);
+        cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<true>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias, residual, ldr,
+                           error_flag);
     } else {
-        gemm_q4k_tc5_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
-                                                                         nullptr, 0, error_flag);
+        cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<false>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias, no_residual, 0,
+                           error_flag);
     }
 }
 

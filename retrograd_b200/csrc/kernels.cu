@@ -270,6 +270,9 @@ __global__ void embed_kernel(WeightView e, const int32_t * __restrict__ tokens, 
 
 __global__ void rms_norm_kernel(const float * __restrict__ x, int ldx, const int32_t * __restrict__ gather, const float * __restrict__ w, int n,
                                 float eps, float * __restrict__ y, int ldy, SplitAct split) {
+    // lets a following kernel launched with programmatic stream serialization start its weight-only
+    // prologue now; it waits on the device for this kernel's completion before it reads activations
+    asm volatile("griddepcontrol.launch_dependents;");
     __shared__ float partial[32];
     const int t = blockIdx.x;
     const float * xr = x + (size_t)(gather ? gather[t] : t) * ldx;
@@ -296,6 +299,9 @@ __global__ void rms_norm_kernel(const float * __restrict__ x, int ldx, const int
 // the split form is consumed.
 __global__ void rms_norm4_kernel(const float * __restrict__ x, int ldx, const int32_t * __restrict__ gather, const float * __restrict__ w, int n,
                                  float eps, float * __restrict__ y, int ldy, SplitAct split) {
+    // lets a following kernel launched with programmatic stream serialization start its weight-only
+    // prologue now; it waits on the device for this kernel's completion before it reads activations
+    asm volatile("griddepcontrol.launch_dependents;");
     __shared__ float partial[32];
     const int t = blockIdx.x;
     const float * xr = x + (size_t)(gather ? gather[t] : t) * ldx;
@@ -485,6 +491,9 @@ __global__ void attention_ref_kernel(const float * __restrict__ qkv, int ld, int
 
 // x [t][ld] f32 -> its SplitAct (n a multiple of 32)
 __global__ void split_prep_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split) {
+    // lets a following kernel launched with programmatic stream serialization start its weight-only
+    // prologue now; it waits on the device for this kernel's completion before it reads activations
+    asm volatile("griddepcontrol.launch_dependents;");
     const int t = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -492,6 +501,9 @@ __global__ void split_prep_kernel(const float * __restrict__ x, int ldx, int n, 
 }
 
 __global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh, SplitAct split) {
+    // lets a following kernel launched with programmatic stream serialization start its weight-only
+    // prologue now; it waits on the device for this kernel's completion before it reads activations
+    asm volatile("griddepcontrol.launch_dependents;");
     const int t = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= ff) return;
@@ -502,6 +514,9 @@ __global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, flo
 }
 
 __global__ void swiglu4_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh, SplitAct split) {
+    // lets a following kernel launched with programmatic stream serialization start its weight-only
+    // prologue now; it waits on the device for this kernel's completion before it reads activations
+    asm volatile("griddepcontrol.launch_dependents;");
     const int t = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const bool active = i < ff;
@@ -516,6 +531,9 @@ __global__ void swiglu4_kernel(const float * __restrict__ gu, int ld, int ff, fl
 }
 
 __global__ void split_prep4_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split) {
+    // lets a following kernel launched with programmatic stream serialization start its weight-only
+    // prologue now; it waits on the device for this kernel's completion before it reads activations
+    asm volatile("griddepcontrol.launch_dependents;");
     const int t = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const bool active = i < n;
