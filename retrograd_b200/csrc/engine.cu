@@ -311,6 +311,8 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
         const size_t P = T * hp.n_expert_used;
         router_logits_.ensure(T * hp.n_expert);
         moe_ids_.ensure(P);
+        moe_offsets_.ensure(hp.n_expert + 1);
+        moe_sorted_.ensure(P);
         moe_w_.ensure(P);
         pair_gu_.ensure(P * 2 * hp.ff);
         pair_h_.ensure(P * hp.ff);
@@ -938,10 +940,12 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             linear(lw.router, xn_.ptr, d, Ti, router_logits_.ptr, E, nullptr, nullptr, 0);
             RB_K(K_MOE, 1, launch_moe_route(router_logits_.ptr, E, K, Ti, moe_ids_.ptr, moe_w_.ptr, stream));
             RB_CUDA(cudaMemcpyAsync(route_ids.ptr + (size_t)l * P, moe_ids_.ptr, (size_t)P * 4, cudaMemcpyDeviceToDevice, stream));
-            RB_K(K_MOE, 2, launch_moe_gemm_rows(lw.gate_exps, lw.gate_stride, moe_ids_.ptr, xn_.ptr, d, K, P, pair_gu_.ptr, 2 * ff, stream);
-                 launch_moe_gemm_rows(lw.up_exps, lw.up_stride, moe_ids_.ptr, xn_.ptr, d, K, P, pair_gu_.ptr + ff, 2 * ff, stream));
+            // pairs grouped by expert: every expert's weights are streamed once per eight of its pairs
+            RB_K(K_MOE, 3, launch_moe_group(moe_ids_.ptr, P, E, moe_offsets_.ptr, moe_sorted_.ptr, stream);
+                 launch_moe_gemm_grouped(lw.gate_exps, lw.gate_stride, E, moe_offsets_.ptr, moe_sorted_.ptr, xn_.ptr, d, K, pair_gu_.ptr, 2 * ff, stream);
+                 launch_moe_gemm_grouped(lw.up_exps, lw.up_stride, E, moe_offsets_.ptr, moe_sorted_.ptr, xn_.ptr, d, K, pair_gu_.ptr + ff, 2 * ff, stream));
             RB_K(K_OTHER, 1, launch_swiglu(pair_gu_.ptr, 2 * ff, ff, P, pair_h_.ptr, ff, stream));
-            RB_K(K_MOE, 2, launch_moe_gemm_rows(lw.down_exps, lw.down_stride, moe_ids_.ptr, pair_h_.ptr, ff, 1, P, pair_y_.ptr, d, stream);
+            RB_K(K_MOE, 2, launch_moe_gemm_grouped(lw.down_exps, lw.down_stride, E, moe_offsets_.ptr, moe_sorted_.ptr, pair_h_.ptr, ff, 1, pair_y_.ptr, d, stream);
                  launch_moe_combine(pair_y_.ptr, d, moe_ids_.ptr, moe_w_.ptr, K, d, Ti, x_.ptr, x_.ptr, stream));
         }
     }

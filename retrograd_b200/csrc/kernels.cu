@@ -595,25 +595,70 @@ __global__ void moe_route_kernel(const float * __restrict__ logits, int n_expert
     }
 }
 
-// One warp per (pair, output row): y[pair][o] = deq(W[expert(pair)])[o] . x[pair / x_div]
+// The (token, expert) pairs of every expert, in pair order: offsets[n_expert + 1] and sorted[n_pairs].
+// One block; thread e owns expert e (n_expert <= blockDim.x).
+__global__ void moe_group_kernel(const int32_t * __restrict__ pair_expert, int n_pairs, int n_expert, int32_t * __restrict__ offsets,
+                                 int32_t * __restrict__ sorted) {
+    __shared__ int32_t s_off[1025];
+    const int e = threadIdx.x;
+    int count = 0;
+    if (e < n_expert)
+        for (int p = 0; p < n_pairs; ++p) count += pair_expert[p] == e;
+    if (e < n_expert) s_off[e + 1] = count;
+    __syncthreads();
+    if (e == 0) {
+        s_off[0] = 0;
+        for (int i = 0; i < n_expert; ++i) s_off[i + 1] += s_off[i];
+        for (int i = 0; i <= n_expert; ++i) offsets[i] = s_off[i];
+    }
+    __syncthreads();
+    if (e < n_expert) {
+        int at = s_off[e];
+        for (int p = 0; p < n_pairs; ++p)
+            if (pair_expert[p] == e) sorted[at++] = p;
+    }
+}
+
+// Grouped expert GEMM: grid (output row groups, experts). One warp per output row of ITS expert; the row
+// is decoded once per eight of the expert's pairs: y[pair][o] = deq(W[expert])[o] . x[pair / x_div].
+// Every (pair, row) dot product keeps the lane-strided accumulation order of a single-pair pass.
 template <uint32_t TYPE>
-__global__ void moe_gemm_rows_kernel(WeightView w, uint64_t expert_stride, const int32_t * __restrict__ pair_expert,
-                                     const float * __restrict__ x, int ldx, int x_div, float * __restrict__ y, int ldy) {
+__global__ void moe_gemm_grouped_kernel(WeightView w, uint64_t expert_stride, const int32_t * __restrict__ offsets,
+                                        const int32_t * __restrict__ sorted, const float * __restrict__ x, int ldx, int x_div,
+                                        float * __restrict__ y, int ldy) {
     const int lane = threadIdx.x & 31;
     const uint32_t o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int pair = blockIdx.y;
-    if (o >= w.n_out) return;
-    const uint8_t * row = w.data + (size_t)pair_expert[pair] * expert_stride + (size_t)o * w.row_bytes;
-    const float * xr = x + (size_t)(pair / x_div) * ldx;
-    float acc = 0.f;
-    for (uint32_t k = lane * 8; k < w.n_in; k += 256) {
-        float wv[8];
-        decode8<TYPE>(row, k, wv);
+    const int e = blockIdx.y;
+    const int begin = offsets[e], end = offsets[e + 1];
+    if (o >= w.n_out || begin == end) return;
+    const uint8_t * row = w.data + (size_t)e * expert_stride + (size_t)o * w.row_bytes;
+    for (int p0 = begin; p0 < end; p0 += 8) {
+        int pair[8];
+        const float * xr[8];
+        float acc[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc += wv[i] * xr[k + i];
+        for (int tt = 0; tt < 8; ++tt) {
+            pair[tt] = p0 + tt < end ? sorted[p0 + tt] : -1;
+            xr[tt] = x + (size_t)((pair[tt] < 0 ? 0 : pair[tt]) / x_div) * ldx;
+            acc[tt] = 0.f;
+        }
+        for (uint32_t k = lane * 8; k < w.n_in; k += 256) {
+            float wv[8];
+            decode8<TYPE>(row, k, wv);
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) {
+                if (pair[tt] >= 0) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[tt] += wv[i] * xr[tt][k + i];
+                }
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            const float v = warp_sum(acc[tt]);
+            if (lane == 0 && pair[tt] >= 0) y[(size_t)pair[tt] * ldy + o] = v;
+        }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) y[(size_t)pair * ldy + o] = acc;
 }
 
 // out[t] = residual[t] + sum over the token's experts in ascending expert id of weight * y
@@ -756,12 +801,16 @@ void launch_moe_route(const float * router_logits, int n_expert, int k, int n_to
     moe_route_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(router_logits, n_expert, k, n_tokens, ids, weights);
 }
 
-void launch_moe_gemm_rows(WeightView w_all, uint64_t expert_stride_bytes, const int32_t * pair_expert, const float * x, int ldx, int x_div,
-                          int n_pairs, float * y, int ldy, cudaStream_t stream) {
+void launch_moe_group(const int32_t * pair_expert, int n_pairs, int n_expert, int32_t * offsets, int32_t * sorted, cudaStream_t stream) {
+    moe_group_kernel<<<1, 1024, 0, stream>>>(pair_expert, n_pairs, n_expert, offsets, sorted);
+}
+
+void launch_moe_gemm_grouped(WeightView w_all, uint64_t expert_stride_bytes, int n_expert, const int32_t * offsets, const int32_t * sorted,
+                             const float * x, int ldx, int x_div, float * y, int ldy, cudaStream_t stream) {
     const int warps = 8;
     dispatch_type(w_all.type, [&](auto tag) {
-        moe_gemm_rows_kernel<decltype(tag)::value><<<dim3((w_all.n_out + warps - 1) / warps, n_pairs), warps * 32, 0, stream>>>(
-            w_all, expert_stride_bytes, pair_expert, x, ldx, x_div, y, ldy);
+        moe_gemm_grouped_kernel<decltype(tag)::value><<<dim3((w_all.n_out + warps - 1) / warps, n_expert), warps * 32, 0, stream>>>(
+            w_all, expert_stride_bytes, offsets, sorted, x, ldx, x_div, y, ldy);
     });
 }
 

@@ -206,10 +206,13 @@ void launch_attention_decode8(const float * qkv, int ld, int n_head, KvLayout kv
 // h[t][i] = silu(gu[t][i]) * gu[t][ff + i]
 void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split = nullptr);
 
-// MoE (reference kernels): router softmax + top-k, per-pair expert GEMMs, fixed-order combine.
+// MoE (CUDA-core kernels): router softmax + top-k, expert GEMMs grouped by expert, fixed-order combine.
 void launch_moe_route(const float * router_logits, int n_expert, int k, int n_tokens, int32_t * ids, float * weights, cudaStream_t stream);
-void launch_moe_gemm_rows(WeightView w_all, uint64_t expert_stride_bytes, const int32_t * pair_expert, const float * x, int ldx, int x_div,
-                          int n_pairs, float * y, int ldy, cudaStream_t stream);
+// The pairs of every expert in pair order (offsets[n_expert + 1], sorted[n_pairs]; n_expert <= 1024), and the
+// grouped expert GEMM over them: an expert's rows are decoded once per eight of its pairs.
+void launch_moe_group(const int32_t * pair_expert, int n_pairs, int n_expert, int32_t * offsets, int32_t * sorted, cudaStream_t stream);
+void launch_moe_gemm_grouped(WeightView w_all, uint64_t expert_stride_bytes, int n_expert, const int32_t * offsets, const int32_t * sorted,
+                             const float * x, int ldx, int x_div, float * y, int ldy, cudaStream_t stream);
 void launch_moe_combine(const float * y_pairs, int ld, const int32_t * ids, const float * weights, int k, int d, int n_tokens,
                         const float * residual, float * out, cudaStream_t stream);
 
