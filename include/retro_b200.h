@@ -203,6 +203,27 @@ int retro_engine_seq_load(retro_engine * engine, int32_t slot, uint32_t flags, c
                           size_t * out_n_read);
 int retro_engine_seq_pos(retro_engine * engine, int32_t slot, int32_t * out_pos_min, int32_t * out_pos_max);
 int retro_engine_memory(retro_engine * engine, retro_engine_memory_info * out);
+/* Batched generators over the step path (retro_lora_train.h:1238-1242, 1845-1880, 2511-2534;
+ * retro_gen_core.cpp:1696-1877, 1878-2049). Outputs are row-major with a stride of n_out_max; a row
+ * stops at max_new_tokens, at an end-of-generation token (included), at n_out_max or when its
+ * context fills. out_logprobs (temperature-1 policy logprobs) and out_forced (always 0 here) may be
+ * NULL. Both calls forget every resident sequence before and after, as the reference does without
+ * its generation prefix cache. Sampling runs on the GPU: greedy-equivalent settings are exact, seeded
+ * rows follow this library's counter-based generator. */
+typedef struct retro_generation_sequence {
+    const int32_t * prompt_tokens;
+    size_t n_prompt;
+    retro_sampling_params sampling;
+} retro_generation_sequence;
+/* One prompt, n_sequences samples: the prompt is decoded once, its memory shared with every member. */
+int retro_engine_generate_batch(retro_engine * engine, const int32_t * prompt_tokens, size_t n_prompt, const retro_sampling_params * sampling,
+                                size_t n_sequences, int32_t * out_tokens, float * out_logprobs, size_t n_out_max, size_t * out_n_tokens,
+                                uint8_t * out_forced);
+/* One completion per (prompt, sampling) pair. */
+int retro_engine_generate_continuous_batch(retro_engine * engine, const retro_generation_sequence * sequences, size_t n_sequences,
+                                           int32_t * out_tokens, float * out_logprobs, size_t n_out_max, size_t * out_n_tokens,
+                                           uint8_t * out_forced);
+
 int retro_engine_request_free(retro_engine * engine, int32_t request);
 int retro_engine_kv_unified(retro_engine * engine, bool * out_unified);
 

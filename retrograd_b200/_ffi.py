@@ -11,6 +11,10 @@ class SamplingParamsC(C.Structure):
     _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("max_new_tokens", C.c_uint32), ("seed", C.c_uint32)]
 
 
+class GenerationSequence(C.Structure):
+    _fields_ = [("prompt_tokens", C.POINTER(C.c_int32)), ("n_prompt", C.c_size_t), ("sampling", SamplingParamsC)]
+
+
 class StepRowC(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32),
@@ -152,6 +156,10 @@ SYMBOLS = {
     "retro_engine_seq_pos": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_int32), _P(C.c_int32)]),
     "retro_engine_memory": (C.c_int, [C.c_void_p, _P(MemoryInfoC)]),
     "retro_engine_request_free": (C.c_int, [C.c_void_p, C.c_int32]),
+    "retro_engine_generate_batch": (C.c_int, [C.c_void_p, _P(C.c_int32), C.c_size_t, _P(SamplingParamsC), C.c_size_t, _P(C.c_int32), _P(C.c_float),
+                                              C.c_size_t, _P(C.c_size_t), _P(C.c_uint8)]),
+    "retro_engine_generate_continuous_batch": (C.c_int, [C.c_void_p, _P(GenerationSequence), C.c_size_t, _P(C.c_int32), _P(C.c_float),
+                                                         C.c_size_t, _P(C.c_size_t), _P(C.c_uint8)]),
     "retro_engine_kv_unified": (C.c_int, [C.c_void_p, _P(C.c_bool)]),
     "retro_engine_weights_version": (C.c_int, [C.c_void_p, _P(C.c_uint64)]),
     "retro_engine_model_fingerprint": (C.c_int, [C.c_void_p, _P(C.c_uint64)]),

@@ -2,6 +2,7 @@
 // same name (crates/retrograd-ffi/runtime/src/retro_engine.cpp:454-1709): struct_size-prefixed
 // config copy, validation messages, status codes, thread-local error, exception fence.
 
+#include <cmath>
 #include "engine.hpp"
 #include "blocks.hpp"
 
@@ -503,6 +504,220 @@ int retro_engine_memory(retro_engine * engine, retro_engine_memory_info * out) {
     return boundary([&]() -> int {
         Engine * e = checked(engine);
         return e ? e->memory(out) : STATUS_RUNTIME;
+    });
+}
+
+namespace {
+
+bool valid_v1_sampling(const retro_sampling_params & s) {
+    if (!(s.temperature > 0.0f) || !std::isfinite(s.temperature)) {
+        set_error("sampling temperature must be finite and greater than zero");
+        return false;
+    }
+    if (!(s.top_p > 0.0f && s.top_p <= 1.0f)) {
+        set_error("sampling top_p must be in (0, 1]");
+        return false;
+    }
+    if (s.max_new_tokens == 0) {
+        set_error("sampling max_new_tokens must be greater than zero");
+        return false;
+    }
+    return true;
+}
+
+struct GenItem {
+    const int32_t * prompt;
+    size_t n_prompt;
+    retro_sampling_params sampling;
+};
+
+// The shared loop of both generators. `shared_prompt`: every item has the same prompt; it is decoded
+// once into slot 0 up to its last token, and the other slots share those cells (seq_cp).
+int generate_over_steps(Engine * e, const std::vector<GenItem> & items, bool shared_prompt, int32_t * out_tokens, float * out_logprobs,
+                        size_t n_out_max, size_t * out_n_tokens, uint8_t * out_forced) {
+    const size_t n = items.size();
+    const size_t n_batch = e->config.n_batch, n_ctx = e->n_ctx_seq;
+    const int32_t request_base = 0x40000000;             // ids of this call's rows; freed before returning
+    auto forget = [&]() {
+        for (size_t i = 0; i < e->config.n_seq_max; ++i) e->seq_rm((int32_t)i, -1, -1);
+        for (size_t i = 0; i < n; ++i) e->requests.erase(request_base + (int32_t)i);
+    };
+    forget();
+    std::vector<size_t> limit(n), fed(n, 0);
+    std::vector<int32_t> last(n, 0);
+    std::vector<bool> live(n, true);
+    for (size_t i = 0; i < n; ++i) {
+        limit[i] = std::min<size_t>(std::min<size_t>(n_out_max, items[i].sampling.max_new_tokens), n_ctx - items[i].n_prompt);
+        out_n_tokens[i] = 0;
+    }
+    std::vector<EffRow> rows;
+    std::vector<OutRow> outs;
+    std::vector<size_t> row_item;
+    auto run = [&]() -> int {
+        outs.assign(rows.size(), OutRow{});
+        return e->step(rows.data(), rows.size(), outs.data(), nullptr, nullptr, 0);
+    };
+    auto row_of = [&](size_t i, const int32_t * tokens, size_t count, size_t pos0, bool sample) {
+        EffRow r{};
+        r.struct_size = sizeof(retro_step_row);
+        r.request = request_base + (int32_t)i;
+        r.slot = (int32_t)i;
+        r.tokens = tokens;
+        r.n = (uint32_t)count;
+        r.pos0 = (int32_t)pos0;
+        r.sample = sample;
+        r.v1 = items[i].sampling;
+        r.v2 = nullptr;
+        r.n_top_logprobs = 0;
+        r.want_logprob = false;
+        r.adapter = 0;
+        return r;
+    };
+    auto record = [&](size_t i, const OutRow & o) {
+        const size_t count = out_n_tokens[i];
+        out_tokens[i * n_out_max + count] = o.token;
+        if (out_logprobs) out_logprobs[i * n_out_max + count] = o.logprob;
+        if (out_forced) out_forced[i * n_out_max + count] = 0;
+        out_n_tokens[i] = count + 1;
+        last[i] = o.token;
+        if (o.token == e->model->eos || out_n_tokens[i] == limit[i]) live[i] = false;
+    };
+
+    // ---- prompts
+    if (shared_prompt) {
+        const GenItem & it = items[0];
+        for (size_t pos = 0; pos + 1 < it.n_prompt;) {          // everything but the last token, into slot 0
+            const size_t take = std::min(n_batch, it.n_prompt - 1 - pos);
+            rows.assign(1, row_of(0, it.prompt + pos, take, pos, false));
+            const int st = run();
+            if (st != 0) { forget(); return st; }
+            pos += take;
+        }
+        if (it.n_prompt > 1)
+            for (size_t i = 1; i < n; ++i) {
+                const int st = e->seq_cp(0, (int32_t)i, 0, (int32_t)it.n_prompt - 1);
+                if (st != 0) { forget(); return st; }
+            }
+        for (size_t i = 0; i < n; ++i) fed[i] = it.n_prompt - 1;
+    }
+    // remaining prompt tokens in chunks, several sequences per step while the token budget lasts;
+    // the row that carries a prompt's last token samples
+    while (true) {
+        rows.clear();
+        row_item.clear();
+        size_t budget = n_batch;
+        for (size_t i = 0; i < n && budget > 0; ++i) {
+            if (fed[i] >= items[i].n_prompt) continue;
+            const size_t take = std::min(budget, items[i].n_prompt - fed[i]);
+            rows.push_back(row_of(i, items[i].prompt + fed[i], take, fed[i], fed[i] + take == items[i].n_prompt));
+            row_item.push_back(i);
+            budget -= take;
+        }
+        if (rows.empty()) break;
+        const int st = run();
+        if (st != 0) { forget(); return st; }
+        for (size_t r = 0; r < rows.size(); ++r) {
+            const size_t i = row_item[r];
+            fed[i] += rows[r].n;
+            if (rows[r].sample) record(i, outs[r]);
+        }
+    }
+    // ---- decode: every live sequence feeds its last token back
+    while (true) {
+        rows.clear();
+        row_item.clear();
+        for (size_t i = 0; i < n; ++i) {
+            if (!live[i]) continue;
+            rows.push_back(row_of(i, &last[i], 1, items[i].n_prompt + out_n_tokens[i] - 1, true));
+            row_item.push_back(i);
+        }
+        if (rows.empty()) break;
+        const int st = run();
+        if (st != 0) { forget(); return st; }
+        for (size_t r = 0; r < rows.size(); ++r) record(row_item[r], outs[r]);
+    }
+    forget();
+    return STATUS_OK;
+}
+
+} // namespace
+
+int retro_engine_generate_batch(retro_engine * engine, const int32_t * prompt_tokens, size_t n_prompt, const retro_sampling_params * sampling,
+                                size_t n_sequences, int32_t * out_tokens, float * out_logprobs, size_t n_out_max, size_t * out_n_tokens,
+                                uint8_t * out_forced) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (!prompt_tokens || n_prompt == 0) {
+            set_error("prompt tokens are required");
+            return STATUS_RUNTIME;
+        }
+        if (!sampling || n_sequences == 0 || !out_tokens || !out_n_tokens || n_out_max == 0) {
+            set_error("sampling params and output buffers are required");
+            return STATUS_RUNTIME;
+        }
+        if (n_sequences > e->config.n_seq_max) {
+            set_error("generation batch has " + std::to_string(n_sequences) + " sequences but the context supports " +
+                      std::to_string(e->config.n_seq_max));
+            return STATUS_RUNTIME;
+        }
+        if (n_sequences > e->config.n_batch) {
+            set_error("generation batch exceeds the configured batch capacity");
+            return STATUS_RUNTIME;
+        }
+        if (n_sequences > SIZE_MAX / n_out_max) {
+            set_error("generation batch output shape overflows size_t");
+            return STATUS_RUNTIME;
+        }
+        for (size_t i = 0; i < n_sequences; ++i)
+            if (!valid_v1_sampling(sampling[i])) return STATUS_RUNTIME;
+        for (size_t i = 0; i < n_prompt; ++i)
+            if (prompt_tokens[i] < 0 || (uint32_t)prompt_tokens[i] >= e->model->hp.vocab) {
+                set_error("token id " + std::to_string(prompt_tokens[i]) + " is outside the vocabulary");
+                return STATUS_RUNTIME;
+            }
+        if (n_prompt >= e->n_ctx_seq) {
+            set_error("prompt of " + std::to_string(n_prompt) + " tokens leaves no room to generate in context " + std::to_string(e->n_ctx_seq));
+            return STATUS_RUNTIME;
+        }
+        std::vector<GenItem> items(n_sequences);
+        for (size_t i = 0; i < n_sequences; ++i) items[i] = GenItem{prompt_tokens, n_prompt, sampling[i]};
+        return generate_over_steps(e, items, true, out_tokens, out_logprobs, n_out_max, out_n_tokens, out_forced);
+    });
+}
+
+int retro_engine_generate_continuous_batch(retro_engine * engine, const retro_generation_sequence * sequences, size_t n_sequences,
+                                           int32_t * out_tokens, float * out_logprobs, size_t n_out_max, size_t * out_n_tokens,
+                                           uint8_t * out_forced) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (!sequences || n_sequences == 0 || !out_tokens || !out_n_tokens || n_out_max == 0) {
+            set_error("continuous generation inputs and output buffers are required");
+            return STATUS_RUNTIME;
+        }
+        if (n_sequences > e->config.n_seq_max || n_sequences > e->config.n_batch) {
+            set_error("continuous generation batch exceeds the configured sequence or batch capacity");
+            return STATUS_RUNTIME;
+        }
+        if (n_sequences > SIZE_MAX / n_out_max) {
+            set_error("continuous generation output shape overflows size_t");
+            return STATUS_RUNTIME;
+        }
+        std::vector<GenItem> items(n_sequences);
+        for (size_t i = 0; i < n_sequences; ++i) {
+            const retro_generation_sequence & s = sequences[i];
+            bool ok = s.prompt_tokens && s.n_prompt > 0 && s.n_prompt < e->n_ctx_seq;
+            set_error("");
+            if (ok) ok = valid_v1_sampling(s.sampling);
+            for (size_t k = 0; ok && k < s.n_prompt; ++k) ok = s.prompt_tokens[k] >= 0 && (uint32_t)s.prompt_tokens[k] < e->model->hp.vocab;
+            if (!ok) {
+                if (std::string(retro_last_error()).empty()) set_error("invalid continuous generation prompt");
+                return STATUS_RUNTIME;
+            }
+            items[i] = GenItem{s.prompt_tokens, s.n_prompt, s.sampling};
+        }
+        return generate_over_steps(e, items, false, out_tokens, out_logprobs, n_out_max, out_n_tokens, out_forced);
     });
 }
 

@@ -412,6 +412,45 @@ class Engine:
         _check(self._lib.retro_engine_memory(self._h, C.byref(m)))
         return EngineMemory(m.n_slots, m.cells_total, m.cells_used, m.kv_bytes, m.recurrent_bytes)
 
+    # ---- batched generators (retro_engine_generate_batch / _generate_continuous_batch)
+    def _generation_outputs(self, n: int, n_out_max: int):
+        tokens = np.zeros((n, n_out_max), dtype=np.int32)
+        logprobs = np.zeros((n, n_out_max), dtype=np.float32)
+        counts = (C.c_size_t * n)()
+        forced = np.zeros((n, n_out_max), dtype=np.uint8)
+        return tokens, logprobs, counts, forced
+
+    @staticmethod
+    def _v1(p: "SamplingParams"):
+        return _ffi.SamplingParamsC(p.temperature, p.top_p, p.max_new_tokens, p.seed)
+
+    def generate_batch(self, prompt: Sequence[int], samplings: Sequence["SamplingParams"], n_out_max: int):
+        """One prompt, len(samplings) samples. Returns (token lists, logprob lists)."""
+        n = len(samplings)
+        ptoks = np.ascontiguousarray(prompt, dtype=np.int32)
+        arr = (_ffi.SamplingParamsC * max(n, 1))(*[self._v1(p) for p in samplings])
+        tokens, logprobs, counts, forced = self._generation_outputs(max(n, 1), max(n_out_max, 1))
+        _check(self._lib.retro_engine_generate_batch(
+            self._h, ptoks.ctypes.data_as(C.POINTER(C.c_int32)) if ptoks.size else None, ptoks.size, arr if n else None, n,
+            tokens.ctypes.data_as(C.POINTER(C.c_int32)), logprobs.ctypes.data_as(C.POINTER(C.c_float)), n_out_max, counts,
+            forced.ctypes.data_as(C.POINTER(C.c_uint8))))
+        return [tokens[i, : counts[i]].tolist() for i in range(n)], [logprobs[i, : counts[i]].tolist() for i in range(n)]
+
+    def generate_continuous(self, sequences: Sequence[tuple[Sequence[int], "SamplingParams"]], n_out_max: int):
+        """One completion per (prompt, sampling) pair. Returns (token lists, logprob lists)."""
+        n = len(sequences)
+        keep = [np.ascontiguousarray(p, dtype=np.int32) for p, _ in sequences]
+        arr = (_ffi.GenerationSequence * max(n, 1))()
+        for i, (_, sp) in enumerate(sequences):
+            arr[i].prompt_tokens = keep[i].ctypes.data_as(C.POINTER(C.c_int32)) if keep[i].size else None
+            arr[i].n_prompt = keep[i].size
+            arr[i].sampling = self._v1(sp)
+        tokens, logprobs, counts, forced = self._generation_outputs(max(n, 1), max(n_out_max, 1))
+        _check(self._lib.retro_engine_generate_continuous_batch(
+            self._h, arr if n else None, n, tokens.ctypes.data_as(C.POINTER(C.c_int32)), logprobs.ctypes.data_as(C.POINTER(C.c_float)),
+            n_out_max, counts, forced.ctypes.data_as(C.POINTER(C.c_uint8))))
+        return [tokens[i, : counts[i]].tolist() for i in range(n)], [logprobs[i, : counts[i]].tolist() for i in range(n)]
+
     def request_free(self, request: int) -> None:
         _check(self._lib.retro_engine_request_free(self._h, request))
 

@@ -347,3 +347,57 @@ def test_repeated_step_shapes_replay_as_cuda_graphs_with_identical_results(rb, o
     assert stats_graphed[0] >= 8 and stats_graphed[1] >= 1
     for (t0, l0, x0), (t1, l1, x1) in zip(eager, graphed):
         assert t0 == t1 and l0 == l1 and np.array_equal(x0, x1)
+
+
+def _greedy_v1(n_new, seed=0):
+    # the serving layer's spelling of greedy for v1 rows: a nucleus that holds one token
+    return dict(temperature=1e-4, top_p=1e-6, max_new_tokens=n_new, seed=seed)
+
+
+def test_batched_generators_equal_the_step_loop_and_the_oracle(rb, oracle, pair):
+    """retro_engine_generate_continuous_batch / _generate_batch run the same steps a caller would:
+    greedy-equivalent rows must reproduce the oracle's arg-max chain, logprobs its temperature-1 policy
+    values, and nothing stays resident afterwards."""
+    engine, octx = pair
+    prompts = [_prompt(300 + i, 5 + 7 * i) for i in range(3)]
+    n_new = 6
+    got, lps = engine.generate_continuous([(p, rb.SamplingParams(**_greedy_v1(n_new, seed=i))) for i, p in enumerate(prompts)], n_out_max=8)
+    assert engine.memory().cells_used == 0
+    for i, p in enumerate(prompts):
+        seq = list(p)
+        octx.seq_rm(i)
+        logits = octx.step([(i, seq, 0, True, 0)])[0]
+        want, want_lp = [], []
+        for step in range(n_new):
+            tok = int(np.argmax(logits))
+            want.append(tok)
+            want_lp.append(float(oracle.token_logprob(logits, tok)))
+            if step + 1 < n_new:
+                logits = octx.step([(i, [tok], len(p) + step, True, 0)])[0]
+        assert got[i] == want
+        assert np.allclose(lps[i], want_lp, rtol=0, atol=2e-4)      # the two sides differ in their logits by up to ~1e-4
+        octx.seq_rm(i)
+    # one prompt, three members: identical greedy streams, equal to the first sequence above
+    members, _ = engine.generate_batch(prompts[0], [rb.SamplingParams(**_greedy_v1(n_new, seed=s)) for s in (1, 2, 3)], n_out_max=8)
+    assert members[0] == members[1] == members[2] == got[0]
+    assert engine.memory().cells_used == 0
+    # n_out_max caps a row before max_new_tokens does
+    short, _ = engine.generate_batch(prompts[1], [rb.SamplingParams(**_greedy_v1(n_new))], n_out_max=2)
+    assert short[0] == got[1][:2]
+
+
+def test_batched_generator_validation(rb, pair):
+    engine, _ = pair
+    good = rb.SamplingParams(temperature=1.0, top_p=1.0, max_new_tokens=2, seed=0)
+    with pytest.raises(rb.EngineError, match="prompt tokens are required"):
+        engine.generate_batch([], [good], 4)
+    with pytest.raises(rb.EngineError, match="sampling params and output buffers are required"):
+        engine.generate_batch([5, 6], [], 4)
+    with pytest.raises(rb.EngineError, match="sequences but the context supports 8"):
+        engine.generate_batch([5, 6], [good] * 9, 4)
+    with pytest.raises(rb.EngineError, match="temperature must be finite"):
+        engine.generate_batch([5, 6], [rb.SamplingParams(temperature=0.0, top_p=1.0, max_new_tokens=2)], 4)
+    with pytest.raises(rb.EngineError, match="continuous generation inputs and output buffers are required"):
+        engine.generate_continuous([], 4)
+    with pytest.raises(rb.EngineError, match="invalid continuous generation prompt"):
+        engine.generate_continuous([([], good)], 4)
