@@ -473,7 +473,11 @@ void Engine::lora(const std::string & target, const float * x, int ldx, int T, f
     if (it == lora_targets_.end() || !it->second->present) return;
     LoraTarget & t = *it->second;
     prof_.begin(K_LORA, stream);
-    launch_lora_shrink(t.a.ptr, (int)r_max_, (int)t.n_in, cur_tok_adapter_, x, ldx, T, lora_tmp_.ptr, stream);
+    if (t.n_in % 4 == 0 && ldx % 4 == 0 && adapters_.size() <= 1024)
+        launch_lora_shrink_grouped(t.a.ptr, (int)r_max_, (int)t.n_in, (int)adapters_.size(), lora_offsets_.ptr, lora_sorted_.ptr, x, ldx, lora_tmp_.ptr,
+                                   stream);
+    else
+        launch_lora_shrink(t.a.ptr, (int)r_max_, (int)t.n_in, cur_tok_adapter_, x, ldx, T, lora_tmp_.ptr, stream);
     launch_lora_expand(t.b.ptr, (int)r_max_, (int)t.n_out, lora_scales_.ptr, cur_tok_adapter_, lora_tmp_.ptr, T, y, ldy, stream);
     prof_.end(K_LORA, 2, stream);
     last_launches += 2;
@@ -810,7 +814,11 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         if (any_v2) logits_work_.ensure(S * (size_t)hp.vocab);
         if (n_greedy_fast) sample_scratch_.ensure(sample_scratch_bytes((int)hp.vocab, (int)S));
     }
-    if (any_adapter) lora_tmp_.ensure(T * (size_t)std::max<uint32_t>(r_max_, 1));
+    if (any_adapter) {
+        lora_tmp_.ensure(T * (size_t)std::max<uint32_t>(r_max_, 1));
+        lora_offsets_.ensure(adapters_.size() + 1);
+        lora_sorted_.ensure(T);
+    }
 
     // Attention work items by width in query vectors (tokens x heads of the GQA group): more than 16 go
     // to the tile kernel, 9..16 to the 16-row decode kernel, at most 8 to the eight-column kernel.
@@ -848,7 +856,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     last_d2h_bytes = S ? res_total - 16 : 0;
     const std::vector<uint64_t> sig = {R, T, S, (uint64_t)n_patches, (uint64_t)n_copies, edits.size(), top_stride, any_v2, (uint64_t)n_greedy_fast,
                                        any_adapter, (uint64_t)n_attn_items, (uint64_t)n_small_items, any_wide_item, any_mid_item,
-                                       (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_};
+                                       (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_, (uint64_t)adapters_.size()};
     auto issue = [&]() {
     last_launches = 0;
     RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
@@ -871,6 +879,10 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, attn_tile_tokens_, maps, stream));
     cur_tok_adapter_ = maps.tok_adapter;
     cur_any_adapter_ = any_adapter;
+    if (any_adapter && adapters_.size() <= 1024) {
+        // the step's tokens grouped by adapter, once for every target and layer
+        RB_K(K_LORA, 1, launch_moe_group(maps.tok_adapter, (int)T, (int)adapters_.size(), lora_offsets_.ptr, lora_sorted_.ptr, stream));
+    }
 
     const int d = (int)hp.d, dq = (int)hp.dq(), dkv = (int)hp.dkv(), ldqkv = dq + 2 * dkv, ff = (int)hp.ff;
     const int Ti = (int)T;

@@ -289,7 +289,7 @@ private:
     size_t result_bytes_ = 0;
     DeviceBuffer<float> x_, xn_, qkv_, att_, gu_, hff_, hs_, router_logits_, moe_w_, pair_gu_, pair_h_, pair_y_, lora_tmp_, logits_work_;
     DeviceBuffer<int32_t> moe_ids_, d_aux_;
-    DeviceBuffer<int32_t> moe_offsets_, moe_sorted_;
+    DeviceBuffer<int32_t> moe_offsets_, moe_sorted_, lora_offsets_, lora_sorted_;
     DeviceBuffer<int> device_error_;
     DeviceBuffer<float> stream_scratch_;
     DeviceBuffer<uint8_t> sample_scratch_;

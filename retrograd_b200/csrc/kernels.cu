@@ -700,6 +700,48 @@ __global__ void lora_shrink_kernel(const float * __restrict__ a_stack, int r_max
     if (lane == 0) tmp[(size_t)t * r_max + j] = acc;
 }
 
+// Segmented shrink: the tokens of every adapter are grouped (moe_group_kernel over tok_adapter; base
+// tokens, adapter -1, fall in no group). Grid (rank groups of four, adapters), four warps; a warp takes
+// eight tokens of its adapter at a time and computes 8 x 4 dot products per pass, so an A row is read
+// once per eight tokens and an x row once per four ranks: tmp[t][j] = A[a][j] . x[t].
+__global__ void lora_shrink_grouped_kernel(const float * __restrict__ a_stack, int r_max, int n_in, const int32_t * __restrict__ offsets,
+                                           const int32_t * __restrict__ sorted, const float * __restrict__ x, int ldx,
+                                           float * __restrict__ tmp) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int a = blockIdx.y, j0 = blockIdx.x * 4;
+    const int begin = offsets[a], end = offsets[a + 1];
+    const float * ar = a_stack + ((size_t)a * r_max + j0) * n_in;
+    for (int p0 = begin + warp * 8; p0 < end; p0 += 8 * (blockDim.x >> 5)) {
+        int tok[8];
+        float acc[8][4];
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+            tok[tt] = p0 + tt < end ? sorted[p0 + tt] : -1;
+            acc[tt][0] = acc[tt][1] = acc[tt][2] = acc[tt][3] = 0.f;
+        }
+        for (int k = lane * 4; k < n_in; k += 128) {
+            float4 av[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) av[r] = j0 + r < r_max ? *reinterpret_cast<const float4 *>(ar + (size_t)r * n_in + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int tt = 0; tt < 8; ++tt) {
+                if (tok[tt] < 0) continue;
+                const float4 xv = *reinterpret_cast<const float4 *>(x + (size_t)tok[tt] * ldx + k);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) acc[tt][r] += av[r].x * xv.x + av[r].y * xv.y + av[r].z * xv.z + av[r].w * xv.w;
+            }
+        }
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float v = warp_sum(acc[tt][r]);
+                if (lane == 0 && tok[tt] >= 0 && j0 + r < r_max) tmp[(size_t)tok[tt] * r_max + j0 + r] = v;
+            }
+        }
+    }
+}
+
 __global__ void lora_expand_kernel(const float * __restrict__ b_stack, int r_max, int n_out, const float * __restrict__ scales,
                                    const int32_t * __restrict__ tok_adapter, const float * __restrict__ tmp, float * __restrict__ y, int ldy) {
     const int t = blockIdx.y;
@@ -823,6 +865,11 @@ void launch_lora_shrink(const float * a_stack, int r_max, int n_in, const int32_
                         float * tmp, cudaStream_t stream) {
     const int warps = 4;
     lora_shrink_kernel<<<dim3((r_max + warps - 1) / warps, n_tokens), warps * 32, 0, stream>>>(a_stack, r_max, n_in, tok_adapter, x, ldx, tmp);
+}
+
+void launch_lora_shrink_grouped(const float * a_stack, int r_max, int n_in, int n_adapters, const int32_t * offsets, const int32_t * sorted,
+                                const float * x, int ldx, float * tmp, cudaStream_t stream) {
+    lora_shrink_grouped_kernel<<<dim3((r_max + 3) / 4, n_adapters), 128, 0, stream>>>(a_stack, r_max, n_in, offsets, sorted, x, ldx, tmp);
 }
 
 void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float * scales, const int32_t * tok_adapter, const float * tmp,

@@ -219,6 +219,10 @@ void launch_moe_combine(const float * y_pairs, int ld, const int32_t * ids, cons
 // Per-row LoRA (reference kernels): tmp[t][j] = A[a_t][j] . x[t]; y[t][o] += scale[a_t] * B[a_t][o] . tmp[t]
 void launch_lora_shrink(const float * a_stack, int r_max, int n_in, const int32_t * tok_adapter, const float * x, int ldx, int n_tokens,
                         float * tmp, cudaStream_t stream);
+// Segmented form of the shrink: tokens grouped by adapter with launch_moe_group(tok_adapter, n_tokens, n_adapters, ...);
+// needs n_in % 4 == 0 and 16-byte aligned rows.
+void launch_lora_shrink_grouped(const float * a_stack, int r_max, int n_in, int n_adapters, const int32_t * offsets, const int32_t * sorted,
+                                const float * x, int ldx, float * tmp, cudaStream_t stream);
 void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float * scales, const int32_t * tok_adapter, const float * tmp,
                         int n_tokens, float * y, int ldy, cudaStream_t stream);
 
