@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_mma_kernel(const float 
 
         const uint32_t k_s = smem_u32(kv_s + (bi % ATT_STAGES) * 2 * TILE_BYTES);
         const uint32_t v_s = k_s + TILE_BYTES;
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // four independent accumulator chains (two key octets x query hi / lo) instead of two twice as deep
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, sl[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
             uint32_t b0, b1, b2, b3;
@@ -155,9 +156,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_mma_kernel(const float 
             ldmatrix_x4(k_s + off, b0, b1, b2, b3);
             mma_f16(s[0], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], b0, b1);
             mma_f16(s[1], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], b2, b3);
-            mma_f16(s[0], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], b0, b1);
-            mma_f16(s[1], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], b2, b3);
+            mma_f16(sl[0], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], b0, b1);
+            mma_f16(sl[1], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], b2, b3);
         }
+#pragma unroll
+        for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[ni][e] += sl[ni][e];
         // causal mask by position within the slot
         const int pbase = (nb0 + bi) << 4;
         float mx0 = -INFINITY, mx1 = -INFINITY;
