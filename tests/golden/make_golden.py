@@ -1,8 +1,8 @@
 """Regenerates the golden files of this directory from the reference checkout.
 
-Run in a container that has the reference mounted (default /root/reference):
+Run where a checkout of the reference is available:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It executes the reference's own fixture generators (scripts/gen-tiny-fixture.py,
 scripts/gen-tiny-moe-fixture.py) unmodified and stores their OUTPUT here, then checks each file
@@ -32,7 +32,9 @@ def manifest(ref: Path, name: str) -> dict:
 
 
 def main() -> int:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference")
+    ref = Path(sys.argv[1])
     pinned = {}
     for toml in ("TINY_FIXTURE.toml", "TINY_F16_FIXTURE.toml", "TINY_Q8_FIXTURE.toml", "TINY_MOE_FIXTURE.toml"):
         m = manifest(ref, toml)
