@@ -55,6 +55,12 @@ WORKLOADS = {
         spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
         n_requests=8, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=65536,
     ),
+    "c2_decode16": dict(
+        name="llama3-8b-shape Q4_K, 16 requests, decode-only steps of 16 tokens",
+        model="c2",
+        spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
+        n_requests=16, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=131072,
+    ),
     # the 8B shape in Q8_0 (BASELINE config 3's weights), again eight long-running requests
     "c3_decode8": dict(
         name="llama3-8b-shape Q8_0, 8 requests, decode-only steps of 8 tokens",

@@ -368,14 +368,25 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
     prof_.begin(K_GEMM, stream);
     if (xs && T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) {
         launch_gemm_mma(w, xs->hi, ldx, T, y, ldy, bias, residual, ldr, stream);
-    } else if (xs && stream_gemm_ && gemm_q4k_stream_supported(w, *xs, T)) {
+    } else if (xs && stream_gemm_ && T <= kStreamMaxTokens &&
+               (gemm_q4k_stream_supported(w, *xs, std::min(T, 8)) || gemm_q8_0_stream_supported(w, *xs, std::min(T, 8)))) {
+        // at most 8 tokens per pass of the weight stream; up to 16 tokens two passes still beat the tensor-core kernels
         stream_scratch_.ensure(gemm_q4k_stream_scratch_floats(w.n_out, w.n_in));
-        launch_gemm_q4k_stream(w, *xs, T, y, ldy, bias, residual, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
-        ++last_launches;
-    } else if (xs && stream_gemm_ && gemm_q8_0_stream_supported(w, *xs, T)) {
-        stream_scratch_.ensure(gemm_q4k_stream_scratch_floats(w.n_out, w.n_in));
-        launch_gemm_q8_0_stream(w, *xs, T, y, ldy, bias, residual, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
-        ++last_launches;
+        for (int t0 = 0; t0 < T; t0 += 8) {
+            const int n = std::min(8, T - t0);
+            SplitAct part = *xs;
+            part.hi += (size_t)t0 * xs->ld;
+            part.lo += (size_t)t0 * xs->ld;
+            part.sum_hi += (size_t)t0 * (xs->ld / 32);
+            part.sum_lo += (size_t)t0 * (xs->ld / 32);
+            const float * res = residual ? residual + (size_t)t0 * ldr : nullptr;
+            if (w.type == GGML_Q4_K)
+                launch_gemm_q4k_stream(w, part, n, y + (size_t)t0 * ldy, ldy, bias, res, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
+            else
+                launch_gemm_q8_0_stream(w, part, n, y + (size_t)t0 * ldy, ldy, bias, res, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
+            last_launches += 2;
+        }
+        --last_launches;        // the common tail below counts one
     } else if (xs && T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) {
         launch_gemm_q4k_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, stream);
     } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {
@@ -462,7 +473,9 @@ void Engine::run_step_work(const std::vector<uint64_t> & sig, const std::functio
 bool Engine::linear_reads_split(const WeightView & w, int ldx, int T, const SplitAct * xs) const {
     if (!xs) return false;
     if (T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) return true;
-    if (stream_gemm_ && (gemm_q4k_stream_supported(w, *xs, T) || gemm_q8_0_stream_supported(w, *xs, T))) return true;
+    if (stream_gemm_ && T <= kStreamMaxTokens &&
+        (gemm_q4k_stream_supported(w, *xs, std::min(T, 8)) || gemm_q8_0_stream_supported(w, *xs, std::min(T, 8))))
+        return true;
     if (T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) return true;
     return T > mma_min_tokens && (gemm_q4k_exact_supported(w, *xs) || gemm_q8_0_exact_supported(w, *xs));
 }

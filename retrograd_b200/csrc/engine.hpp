@@ -22,6 +22,7 @@ namespace rb200 {
 
 constexpr uint32_t kMaxSeq = 1024;        // sequence slots this backend accepts (the reference's fork caps at 256)
 constexpr uint32_t kBlockTokens = 16;     // KV cells per block
+constexpr int kStreamMaxTokens = 16;      // steps of at most this many tokens run the weight-streaming GEMMs (8 tokens per pass)
 
 // Bumped whenever a device work buffer is (re)allocated; captured step graphs are dropped when it moves.
 inline std::atomic<uint64_t> g_alloc_epoch{0};
@@ -237,7 +238,7 @@ public:
     uint64_t last_launches = 0;
     // steps with more tokens than this take the tensor-core GEMM (f16 operands); fewer take the f32 row kernel
     int mma_min_tokens = 8;
-    int tc5_min_tokens = 64;      // above this the tcgen05 kernel (128-token tiles) takes over from mma.sync
+    int tc5_min_tokens = 16;      // above this the tcgen05 kernel (128-token tiles) takes over; measured faster than mma.sync from 17 tokens on
     bool gemm_fast_f16 = false;   // opt-in single-term f16 operands: faster, outside the 1e-2 logit tolerance on deep models
     uint64_t last_h2d_bytes = 0, last_d2h_bytes = 0;
     StepProfiler prof_;
