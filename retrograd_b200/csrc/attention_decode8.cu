@@ -15,6 +15,7 @@
 // f16 splits, f32 accumulation, online softmax per column.
 
 #include "kernels.cuh"
+#include "split_emit.cuh"
 #include "mma_common.cuh"
 
 #include <cfloat>
@@ -48,6 +49,8 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_kernel(const flo
     constexpr int MT = HD / 16;
     constexpr int TILE_BYTES = PANELS * 16 * 128;          // one K or V block
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_trigger();
+    pdl_wait();
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tq = lane & 3;
@@ -234,7 +237,9 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_kernel(const flo
 // out = merge over the splits of one (item, kv head, column): grid (items, kv heads, 8), HD threads
 template <int HD>
 __global__ void attention_decode8_merge_kernel(const float * __restrict__ partial, int n_head, int n_head_kv, const int2 * __restrict__ items,
-                                               float * __restrict__ out, int ldo, int n_splits) {
+                                               float * __restrict__ out, int ldo, int n_splits, SplitAct split) {
+    pdl_trigger();
+    pdl_wait();
     const int G = n_head / n_head_kv;
     const int2 item = items[blockIdx.x];
     const int cols = item.y * G, c = blockIdx.z;
@@ -250,12 +255,17 @@ __global__ void attention_decode8_merge_kernel(const float * __restrict__ partia
         num += f * p[dcol];
         den += f * p[HD + 1];
     }
-    out[(size_t)(item.x + c / G) * ldo + (size_t)(hk * G + c % G) * HD + dcol] = num / den;
+    const float v = num / den;
+    const int row = item.x + c / G, col = (hk * G + c % G) * HD + dcol;
+    out[(size_t)row * ldo + col] = v;
+    // a warp covers one 32-column sub-block of the head: the split form the output projection reads
+    if (split.hi) emit_split(split, row, col, v);
 }
 
 template <int HD>
 void launch_hd8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
-                const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int n_splits, float * scratch, cudaStream_t stream) {
+                const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int n_splits, float * scratch, cudaStream_t stream,
+                const SplitAct & split) {
     constexpr int smem = 4 * D8_SLOTS * 2 * (HD / 64) * 16 * 128;
     static_assert(smem >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the K/V rings");
     static bool configured = false;
@@ -263,10 +273,11 @@ void launch_hd8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, c
         cudaFuncSetAttribute(attention_decode8_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         configured = true;
     }
-    attention_decode8_kernel<HD><<<dim3(n_items, kv.n_head_kv, n_splits), D8_THREADS, smem, stream>>>(qkv, ld, n_head, kv, layer, items, tok_slot,
-                                                                                                      tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
+    launch_pdl(attention_decode8_kernel<HD>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem, stream, qkv, ld, n_head, kv, layer, items,
+               tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
     if (n_splits > 1)
-        attention_decode8_merge_kernel<HD><<<dim3(n_items, kv.n_head_kv, 8), HD, 0, stream>>>(scratch, n_head, kv.n_head_kv, items, out, ldo, n_splits);
+        launch_pdl(attention_decode8_merge_kernel<HD>, dim3(n_items, kv.n_head_kv, 8), dim3(HD), 0, stream, scratch, n_head, kv.n_head_kv, items, out,
+                   ldo, n_splits, split);
 }
 
 } // namespace
@@ -281,12 +292,13 @@ size_t attention_decode8_scratch_floats(int n_items, int n_head_kv, int n_splits
 
 void launch_attention_decode8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items,
                               const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int n_splits,
-                              float * scratch, cudaStream_t stream) {
+                              float * scratch, cudaStream_t stream, const SplitAct * split) {
     if (n_items <= 0) return;
+    const SplitAct sa = split && n_splits > 1 ? *split : SplitAct{};
     if (kv.head_dim == 128)
-        launch_hd8<128>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch, stream);
+        launch_hd8<128>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch, stream, sa);
     else
-        launch_hd8<64>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch, stream);
+        launch_hd8<64>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch, stream, sa);
 }
 
 } // namespace rb200

@@ -299,6 +299,7 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
         cudaDeviceGetAttribute(&n_sm_, cudaDevAttrMultiProcessorCount, dev);
         if (const char * env = std::getenv("RB200_GEMM")) stream_gemm_ = std::string(env) != "rows";
         if (const char * env = std::getenv("RB200_GRAPHS")) graphs_enabled_ = std::string(env) != "0";
+        if (const char * env = std::getenv("RB200_FUSED_FINISH")) fused_finish_ = std::string(env) != "0";
         if (const char * env = std::getenv("RB200_ATTENTION")) attn_decode8_ = std::string(env) != "decode16";
     }
     device_error_.ensure(1);
@@ -363,8 +364,10 @@ void Engine::flush_kv_updates() {
     copies.clear();
 }
 
-void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual,
-                    int ldr, const SplitAct * xs) {
+// Returns whether `tail` (the row-wise step that consumes y) was done by the GEMM's own finish kernel.
+bool Engine::linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual,
+                    int ldr, const SplitAct * xs, const FinishTail * tail) {
+    bool tail_done = false;
     prof_.begin(K_GEMM, stream);
     if (xs && T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) {
         launch_gemm_mma(w, xs->hi, ldx, T, y, ldy, bias, residual, ldr, stream);
@@ -372,6 +375,7 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
                (gemm_q4k_stream_supported(w, *xs, std::min(T, 8)) || gemm_q8_0_stream_supported(w, *xs, std::min(T, 8)))) {
         // at most 8 tokens per pass of the weight stream; up to 16 tokens two passes still beat the tensor-core kernels
         stream_scratch_.ensure(gemm_q4k_stream_scratch_floats(w.n_out, w.n_in));
+        tail_done = tail && fused_finish_ && finish_tail_supported(*tail, (int)w.n_out, y, ldy, bias, residual, ldr);
         for (int t0 = 0; t0 < T; t0 += 8) {
             const int n = std::min(8, T - t0);
             SplitAct part = *xs;
@@ -380,15 +384,33 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
             part.sum_hi += (size_t)t0 * (xs->ld / 32);
             part.sum_lo += (size_t)t0 * (xs->ld / 32);
             const float * res = residual ? residual + (size_t)t0 * ldr : nullptr;
+            FinishTail part_tail;
+            if (tail_done) {
+                part_tail = *tail;
+                if (part_tail.out) part_tail.out += (size_t)t0 * part_tail.ld_out;
+                if (part_tail.split.hi) {
+                    part_tail.split.hi += (size_t)t0 * part_tail.split.ld;
+                    part_tail.split.lo += (size_t)t0 * part_tail.split.ld;
+                    part_tail.split.sum_hi += (size_t)t0 * (part_tail.split.ld / 32);
+                    part_tail.split.sum_lo += (size_t)t0 * (part_tail.split.ld / 32);
+                }
+            }
+            const FinishTail * pass_tail = tail_done ? &part_tail : nullptr;
             if (w.type == GGML_Q4_K)
-                launch_gemm_q4k_stream(w, part, n, y + (size_t)t0 * ldy, ldy, bias, res, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
+                launch_gemm_q4k_stream(w, part, n, y + (size_t)t0 * ldy, ldy, bias, res, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream,
+                                       pass_tail);
             else
-                launch_gemm_q8_0_stream(w, part, n, y + (size_t)t0 * ldy, ldy, bias, res, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream);
+                launch_gemm_q8_0_stream(w, part, n, y + (size_t)t0 * ldy, ldy, bias, res, ldr, stream_scratch_.ptr, n_sm_, device_error_.ptr, stream,
+                                        pass_tail);
             last_launches += 2;
         }
         --last_launches;        // the common tail below counts one
     } else if (xs && T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) {
-        launch_gemm_q4k_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, stream);
+        const size_t need = gemm_q4k_tc5_scratch_floats(w.n_out, T, n_sm_);
+        if (need) stream_scratch_.ensure(need);
+        launch_gemm_q4k_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, need ? stream_scratch_.ptr : nullptr, stream_scratch_.count, n_sm_,
+                            stream);
+        if (need) ++last_launches;
     } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {
         launch_gemm_q4k_exact(w, *xs, T, y, ldy, bias, residual, ldr, stream);
     } else if (xs && T > mma_min_tokens && gemm_q8_0_exact_supported(w, *xs)) {
@@ -398,6 +420,7 @@ void Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
     }
     prof_.end(K_GEMM, 1, stream);
     ++last_launches;
+    return tail_done;
 }
 
 // Runs one step's device work: eagerly, or as a replayed / freshly captured CUDA graph.
@@ -900,12 +923,15 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     const int d = (int)hp.d, dq = (int)hp.dq(), dkv = (int)hp.dkv(), ldqkv = dq + 2 * dkv, ff = (int)hp.ff;
     const int Ti = (int)T;
     RB_K(K_OTHER, 1, launch_embed(model->token_embd, d_tokens, Ti, x_.ptr, stream));
+    bool norm_done = false;         // this layer's attention norm was already written by the previous layer's down projection
     for (uint32_t l = 0; l < hp.n_layer; ++l) {
         const LayerWeights & lw = model->layers[l];
         const std::string p = "blk." + std::to_string(l) + ".";
         // the f32 copy of an activation is written only when something other than a split-reading GEMM consumes it
         const bool qkv_split = !any_adapter && lw.wqkv.data && linear_reads_split(lw.wqkv, d, Ti, xn_split_.get());
-        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, qkv_split ? nullptr : xn_.ptr, d, Ti, stream, xn_split_.get()));
+        if (!norm_done)
+            RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, qkv_split ? nullptr : xn_.ptr, d, Ti, stream, xn_split_.get()));
+        norm_done = false;
         if (lw.wqkv.data) {
             linear(lw.wqkv, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0, xn_split_.get());
         } else {
@@ -925,6 +951,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         RB_K(K_OTHER, 1, launch_rope_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox,
                                            model->inv_freq.ptr, maps.tok_pos, maps.tok_cell, kvl, (int)l, stream));
         if (attn_mma_) {
+            // every row of the step goes through the split-KV kernel: its merge writes the split form as well
+            const bool merge_splits = fused_finish_ && att_split_.get() && !any_wide_item && !any_mid_item && n_small_items && attn_splits > 1 &&
+                                      hp.head_dim % 32 == 0;
             RB_K(K_ATTN, (any_wide_item ? 1 : 0) + (any_mid_item ? 1 : 0) + (n_small_items ? (attn_splits > 1 ? 2 : 1) : 0),
                  if (any_wide_item) launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
                                                          maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, true, stream);
@@ -932,22 +961,37 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                                                            maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, use_decode8 ? 8 : 0, stream);
                  if (n_small_items) launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
                                                              maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, attn_splits,
-                                                             attn_scratch_.ptr, stream));
-            if (att_split_.get()) RB_K(K_OTHER, 1, launch_split_prep(att_.ptr, dq, dq, Ti, att_split_.view, stream));
+                                                             attn_scratch_.ptr, stream, merge_splits ? att_split_.get() : nullptr));
+            if (att_split_.get() && !merge_splits) RB_K(K_OTHER, 1, launch_split_prep(att_.ptr, dq, dq, Ti, att_split_.view, stream));
         } else {
             RB_K(K_ATTN, 1, launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min,
                                                  att_.ptr, dq, stream, att_split_.get()));
             // the reference kernel writes the split form itself only when a head is whole 32-column sub-blocks
             if (att_split_.get() && hp.head_dim % 32 != 0) RB_K(K_OTHER, 1, launch_split_prep(att_.ptr, dq, dq, Ti, att_split_.view, stream));
         }
-        // x = x + Wo att
-        linear(lw.wo, att_.ptr, dq, Ti, x_.ptr, d, nullptr, x_.ptr, d, att_split_.get());
-        if (any_adapter) lora(p + "attn_output.weight", att_.ptr, dq, Ti, x_.ptr, d);
+        // x = x + Wo att, then the FFN's norm of x: by the projection's finish kernel where it has one
         const bool gu_split = !any_adapter && hp.n_expert == 0 && lw.wgu.data && linear_reads_split(lw.wgu, d, Ti, xn_split_.get());
-        RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, gu_split ? nullptr : xn_.ptr, d, Ti, stream, xn_split_.get()));
+        FinishTail ffn_norm_tail;
+        ffn_norm_tail.kind = 1;
+        ffn_norm_tail.norm_w = lw.ffn_norm;
+        ffn_norm_tail.eps = hp.eps;
+        ffn_norm_tail.out = gu_split ? nullptr : xn_.ptr;
+        ffn_norm_tail.ld_out = d;
+        if (xn_split_.get()) ffn_norm_tail.split = *xn_split_.get();
+        const bool ffn_normed = linear(lw.wo, att_.ptr, dq, Ti, x_.ptr, d, nullptr, x_.ptr, d, att_split_.get(), any_adapter ? nullptr : &ffn_norm_tail);
+        if (any_adapter) lora(p + "attn_output.weight", att_.ptr, dq, Ti, x_.ptr, d);
+        if (!ffn_normed)
+            RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.ffn_norm, d, hp.eps, gu_split ? nullptr : xn_.ptr, d, Ti, stream, xn_split_.get()));
         if (hp.n_expert == 0) {
+            const bool down_split = !any_adapter && linear_reads_split(lw.wdown, ff, Ti, hff_split_.get());
+            bool activated = false;
             if (lw.wgu.data) {
-                linear(lw.wgu, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0, xn_split_.get());
+                FinishTail act_tail;
+                act_tail.kind = 2;
+                act_tail.out = down_split ? nullptr : hff_.ptr;
+                act_tail.ld_out = ff;
+                if (hff_split_.get()) act_tail.split = *hff_split_.get();
+                activated = linear(lw.wgu, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0, xn_split_.get(), any_adapter ? nullptr : &act_tail);
             } else {
                 linear(lw.wgate, xn_.ptr, d, Ti, gu_.ptr, 2 * ff, nullptr, nullptr, 0);
                 linear(lw.wup, xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff, nullptr, nullptr, 0);
@@ -956,9 +1000,21 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 lora(p + "ffn_gate.weight", xn_.ptr, d, Ti, gu_.ptr, 2 * ff);
                 lora(p + "ffn_up.weight", xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff);
             }
-            const bool down_split = !any_adapter && linear_reads_split(lw.wdown, ff, Ti, hff_split_.get());
-            RB_K(K_OTHER, 1, launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, down_split ? nullptr : hff_.ptr, ff, stream, hff_split_.get()));
-            linear(lw.wdown, hff_.ptr, ff, Ti, x_.ptr, d, nullptr, x_.ptr, d, hff_split_.get());
+            if (!activated) RB_K(K_OTHER, 1, launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, down_split ? nullptr : hff_.ptr, ff, stream, hff_split_.get()));
+            // x = x + Wdown h, then the next layer's attention norm of x
+            FinishTail next_norm_tail;
+            const bool has_next = l + 1 < hp.n_layer && !any_adapter;
+            if (has_next) {
+                const LayerWeights & nw = model->layers[l + 1];
+                const bool next_qkv_split = nw.wqkv.data && linear_reads_split(nw.wqkv, d, Ti, xn_split_.get());
+                next_norm_tail.kind = 1;
+                next_norm_tail.norm_w = nw.attn_norm;
+                next_norm_tail.eps = hp.eps;
+                next_norm_tail.out = next_qkv_split ? nullptr : xn_.ptr;
+                next_norm_tail.ld_out = d;
+                if (xn_split_.get()) next_norm_tail.split = *xn_split_.get();
+            }
+            norm_done = linear(lw.wdown, hff_.ptr, ff, Ti, x_.ptr, d, nullptr, x_.ptr, d, hff_split_.get(), has_next ? &next_norm_tail : nullptr);
             if (any_adapter) lora(p + "ffn_down.weight", hff_.ptr, ff, Ti, x_.ptr, d);
         } else {
             const int E = (int)hp.n_expert, K = (int)hp.n_expert_used, P = Ti * K;

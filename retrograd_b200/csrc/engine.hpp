@@ -256,8 +256,8 @@ public:
 private:
     void load_model(const std::string & path);
     void restack_adapters();
-    void linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
-                const SplitAct * xs = nullptr);
+    bool linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
+                const SplitAct * xs = nullptr, const FinishTail * tail = nullptr);
     struct GraphEntry {
         std::vector<uint64_t> sig;
         cudaGraphExec_t exec = nullptr;
@@ -298,6 +298,7 @@ private:
     bool attn_decode8_ = true;
     int n_sm_ = 148;
     bool stream_gemm_ = true;
+    bool fused_finish_ = true;      // RB200_FUSED_FINISH=0: norm / SwiGLU always as kernels of their own
     SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
 

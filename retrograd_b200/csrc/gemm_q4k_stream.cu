@@ -94,7 +94,10 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
     // Launched with programmatic stream serialization: everything above touches only the weights, which
     // no kernel writes, so it may run while the kernels before this one are still finishing. From here on
     // the activations are read and results written: wait for every earlier kernel of the stream.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // The finish kernel that follows is launched the same way and may be scheduled from now on (it
+    // waits for this kernel's completion before it reads the partial sums).
+    pdl_trigger();
+    pdl_wait();
 
     // ---- this warp's activation fragments: MMA column g, K steps of its 128 columns
     uint32_t bh[8][2], bl[8][2], bmh = 0, bml = 0;
@@ -273,25 +276,7 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
     }
 }
 
-// y[t][o] = sum over K chunks (in order) of partial + bias + residual
-__global__ void gemm_q4k_stream_finish_kernel(const float * __restrict__ partial, int n_chunks, int n_out, int T, float * __restrict__ y, int ldy,
-                                              const float * __restrict__ bias, const float * __restrict__ residual, int ldr) {
-    const int o = blockIdx.x * blockDim.x + threadIdx.x;
-    const int t = blockIdx.y;
-    if (o >= n_out || t >= T) return;
-    float sum = 0.f;
-    for (int c = 0; c < n_chunks; ++c) sum += partial[((size_t)c * 8 + t) * n_out + o];
-    if (bias) sum += bias[o];
-    if (residual) sum += residual[(size_t)t * ldr + o];
-    y[(size_t)t * ldy + o] = sum;
-}
-
 } // namespace
-
-void launch_gemm_stream_finish(const float * scratch, int n_chunks, int n_out, int n_tokens, float * y, int ldy, const float * bias,
-                               const float * residual, int ldr, cudaStream_t stream) {
-    gemm_q4k_stream_finish_kernel<<<dim3((n_out + 255) / 256, n_tokens), 256, 0, stream>>>(scratch, n_chunks, n_out, n_tokens, y, ldy, bias, residual, ldr);
-}
 
 bool gemm_q4k_stream_supported(const WeightView & w, const SplitAct & x, int n_tokens) {
     return w.type == GGML_Q4_K && w.tiled && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && n_tokens >= 1 && n_tokens <= 8;
@@ -303,7 +288,8 @@ size_t gemm_q4k_stream_scratch_floats(uint32_t n_out, uint32_t n_in) {
 }
 
 void launch_gemm_q4k_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
-                            const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream) {
+                            const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream,
+                            const FinishTail * tail) {
     const int n_sb = (int)w.n_in / 256;
     const int n_chunks = (n_sb + SW - 1) / SW;
     const int n_units = ((int)w.n_out + 31) / 32;
@@ -331,7 +317,7 @@ void launch_gemm_q4k_stream(const WeightView & w, const SplitAct & x, int n_toke
     cfg.numAttrs = 1;
     if (n_tokens <= 4) cudaLaunchKernelEx(&cfg, gemm_q4k_stream_kernel<true>, w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
     else cudaLaunchKernelEx(&cfg, gemm_q4k_stream_kernel<false>, w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
-    launch_gemm_stream_finish(scratch, n_chunks, (int)w.n_out, n_tokens, y, ldy, bias, residual, ldr, stream);
+    launch_gemm_stream_finish(scratch, n_chunks, (int)w.n_out, n_tokens, 8, y, ldy, bias, residual, ldr, stream, tail);
 }
 
 } // namespace rb200

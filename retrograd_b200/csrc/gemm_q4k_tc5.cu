@@ -27,6 +27,8 @@
 // Every mbarrier wait is bounded: after about a second without progress the CTA raises an error
 // flag, drains its copies, frees its tensor memory and returns.
 
+#include <algorithm>
+
 #include "kernels.cuh"
 #include "blocks.hpp"
 #include "mma_common.cuh"
@@ -83,7 +85,8 @@ __global__ void q4k_retile_kernel(const uint8_t * __restrict__ rows, uint32_t n_
 template <bool RESIDUAL>
 __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes,
                                                                   const __grid_constant__ SplitAct X, int T, float * __restrict__ Y, int ldy, const float * __restrict__ bias,
-                                                                  const float * __restrict__ residual, int ldr, int * __restrict__ error_flag) {
+                                                                  const float * __restrict__ residual, int ldr, int * __restrict__ error_flag,
+                                                                  int sb_per_split, float * __restrict__ partial) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -99,7 +102,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.y * BM, t0 = blockIdx.x * BN;   // token tiles vary fastest: CTAs in flight share a weight tile in L2
-    const int n_sb = n_in / 256;
+    // split-K: blockIdx.z owns super-blocks [sb0, sb0 + n_sb) of the row and writes a partial result
+    const int n_sb_all = n_in / 256;
+    const int sb0 = blockIdx.z * sb_per_split;
+    const int n_sb = min(n_sb_all, sb0 + sb_per_split) - sb0;
     const int n_it = n_sb * 5;
     const int n_sub = n_in / 32;
 
@@ -127,7 +133,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         const int group = warp >> 2;
         const int p = tid & 127;                       // weight row and token row of this thread
         // (the tiled layout is zero-padded to whole row tiles: every row p exists)
-        const uint8_t * tile_base = W + (size_t)blockIdx.y * n_sb * kQ4kTileBytes;
+        const uint8_t * tile_base = W + ((size_t)blockIdx.y * n_sb_all + sb0) * kQ4kTileBytes;
         const int t = t0 + p;
         const bool t_valid = t < T;
         // Raw block bytes are prefetched into registers two own stages ahead, so the HBM latency of
@@ -146,8 +152,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
             } else {
                 raw.q0 = raw.q1 = make_uint4(0, 0, 0, 0);
                 if (t_valid) {
-                    raw.q0 = *reinterpret_cast<const uint4 *>(X.sum_hi + (size_t)t * n_sub + sb * 8);
-                    raw.q1 = *reinterpret_cast<const uint4 *>(X.sum_lo + (size_t)t * n_sub + sb * 8);
+                    raw.q0 = *reinterpret_cast<const uint4 *>(X.sum_hi + (size_t)t * n_sub + (sb0 + sb) * 8);
+                    raw.q1 = *reinterpret_cast<const uint4 *>(X.sum_lo + (size_t)t * n_sub + (sb0 + sb) * 8);
                 }
             }
         };
@@ -165,8 +171,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
                     // the activation tiles (hi and lo, 128 tokens x 64 columns each) arrive by TMA
                     const uint32_t bh = smem_u32(bh_s), bl = bh + B_BYTES;
                     tc5::mbar_expect_tx(full_bar(stage), 2 * B_BYTES);
-                    tc5::tma_load_2d(bh, &X.map_hi, sb * 256 + r * 64, t0, full_bar(stage));
-                    tc5::tma_load_2d(bl, &X.map_lo, sb * 256 + r * 64, t0, full_bar(stage));
+                    tc5::tma_load_2d(bh, &X.map_hi, (sb0 + sb) * 256 + r * 64, t0, full_bar(stage));
+                    tc5::tma_load_2d(bl, &X.map_lo, (sb0 + sb) * 256 + r * 64, t0, full_bar(stage));
                 }
                 // 64 weights -> 32 columns of f16 pairs in K order: low nibbles (columns 0..31 of the group), then high
                 uint32_t out[32];
@@ -269,7 +275,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
         const int o_local = q * 32 + lane;
         const int o = m0 + o_local;
         const bool o_valid = o < n_out;
-        const uint8_t * hdr_base = W + (size_t)blockIdx.y * n_sb * kQ4kTileBytes + q4k_tile_hdr_offset(o_local);
+        const uint8_t * hdr_base = W + ((size_t)blockIdx.y * n_sb_all + sb0) * kQ4kTileBytes + q4k_tile_hdr_offset(o_local);
         float acc[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
@@ -316,9 +322,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
             for (int i = 0; i < 64; ++i) {
                 const int t = t0 + colhalf * 64 + i;
                 if (t < T) {
-                    float v = acc[i] + b;
-                    if (RESIDUAL) v += residual[(size_t)t * ldr + o];
-                    Y[(size_t)t * ldy + o] = v;
+                    if (partial) {
+                        partial[((size_t)blockIdx.z * T + t) * n_out + o] = acc[i];      // bias and residual are added by the finish kernel
+                    } else {
+                        float v = acc[i] + b;
+                        if (RESIDUAL) v += residual[(size_t)t * ldr + o];
+                        Y[(size_t)t * ldy + o] = v;
+                    }
                 }
             }
         }
@@ -375,14 +385,28 @@ void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint
 }
 
 void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
-                         const float * residual, int ldr, int * error_flag, cudaStream_t stream) {
+                         const float * residual, int ldr, int * error_flag, float * scratch, size_t scratch_floats, int n_sm, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(gemm_q4k_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaFuncSetAttribute(gemm_q4k_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         configured = true;
     }
-    const dim3 grid((n_tokens + BN - 1) / BN, (w.n_out + BM - 1) / BM);
+    // few output tiles (few tokens and few rows): cut the reduction into splits of whole super-blocks so the
+    // grid still covers the GPU; the splits' partial results are added, in order, by the finish kernel
+    const int n_sb = (int)w.n_in / 256;
+    const int tiles = ((n_tokens + BN - 1) / BN) * (int)((w.n_out + BM - 1) / BM);
+    int splits = 1, sb_per_split = n_sb;
+    if (scratch && tiles * 2 <= n_sm) {
+        const int want = std::min(n_sm / tiles, n_sb / 2);
+        if (want > 1) {
+            sb_per_split = (n_sb + want - 1) / want;
+            splits = (n_sb + sb_per_split - 1) / sb_per_split;
+            if ((size_t)splits * n_tokens * w.n_out > scratch_floats) { splits = 1; sb_per_split = n_sb; }
+        }
+    }
+    float * partial = splits > 1 ? scratch : nullptr;
+    const dim3 grid((n_tokens + BN - 1) / BN, (w.n_out + BM - 1) / BM, splits);
     // the kernel may start (barriers, tensor-memory allocation, first weight loads) while the stream's
     // earlier kernels drain; every role waits on the device before it touches activations or outputs
     cudaLaunchConfig_t cfg = {};
@@ -398,11 +422,17 @@ void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens,
     const float * no_residual = nullptr;
     if (residual) {
         cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<true>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias, residual, ldr,
-                           error_flag);
+                           error_flag, sb_per_split, partial);
     } else {
         cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<false>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias, no_residual, 0,
-                           error_flag);
+                           error_flag, sb_per_split, partial);
     }
+    if (splits > 1) launch_gemm_stream_finish(scratch, splits, (int)w.n_out, n_tokens, n_tokens, y, ldy, bias, residual, ldr, stream);
+}
+
+size_t gemm_q4k_tc5_scratch_floats(uint32_t n_out, int n_tokens, int n_sm) {
+    const int tiles = ((n_tokens + BN - 1) / BN) * (int)((n_out + BM - 1) / BM);
+    return tiles * 2 <= n_sm ? (size_t)(n_sm / tiles) * n_tokens * n_out : 0;
 }
 
 } // namespace rb200

@@ -106,7 +106,10 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q8_0_stream_kernel(const uin
     // Launched with programmatic stream serialization: everything above touches only the weights, which
     // no kernel writes, so it may run while the kernels before this one are still finishing. From here on
     // the activations are read and results written: wait for every earlier kernel of the stream.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // The finish kernel that follows is launched the same way and may be scheduled from now on (it
+    // waits for this kernel's completion before it reads the partial sums).
+    pdl_trigger();
+    pdl_wait();
 
     // ---- activation fragments of MMA column g, and -128 * (sum of x) per block for this lane's two result columns
     uint32_t bh[8][2], bl[8][2];
@@ -253,7 +256,8 @@ bool gemm_q8_0_stream_supported(const WeightView & w, const SplitAct & x, int n_
 }
 
 void launch_gemm_q8_0_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
-                             const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream) {
+                             const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream,
+                             const FinishTail * tail) {
     const int n_sb = (int)w.n_in / 256;
     const int n_chunks = (n_sb + SW - 1) / SW;
     const int n_units = ((int)w.n_out + 15) / 16;
@@ -280,7 +284,7 @@ void launch_gemm_q8_0_stream(const WeightView & w, const SplitAct & x, int n_tok
     cfg.numAttrs = 1;
     if (n_tokens <= 4) cudaLaunchKernelEx(&cfg, gemm_q8_0_stream_kernel<true>, w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
     else cudaLaunchKernelEx(&cfg, gemm_q8_0_stream_kernel<false>, w.tiled, (int)w.n_in, (int)w.n_out, x, n_tokens, scratch, units_per_cta, error_flag);
-    launch_gemm_stream_finish(scratch, n_chunks, (int)w.n_out, n_tokens, y, ldy, bias, residual, ldr, stream);
+    launch_gemm_stream_finish(scratch, n_chunks, (int)w.n_out, n_tokens, 8, y, ldy, bias, residual, ldr, stream, tail);
 }
 
 } // namespace rb200

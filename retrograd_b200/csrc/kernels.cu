@@ -6,6 +6,7 @@
 
 #include "kernels.cuh"
 #include "blocks.hpp"
+#include "split_emit.cuh"
 
 #include <cfloat>
 #include <type_traits>
@@ -13,12 +14,6 @@
 namespace rb200 {
 
 namespace {
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -34,44 +29,6 @@ __device__ __forceinline__ float e8m0_half_dev(uint8_t x) {
 }
 
 __constant__ float c_fp4_doubled[16] = {0.f, 1.f, 2.f, 3.f, 4.f, 6.f, 8.f, 12.f, 0.f, -1.f, -2.f, -3.f, -4.f, -6.f, -8.f, -12.f};
-
-// Writes v as hi + lo and, once per warp, the sub-block sum of v as hi + lo. Every lane of the
-// warp must call it, with 32 consecutive columns starting at a multiple of 32.
-__device__ __forceinline__ void emit_split(const SplitAct & s, size_t row, int col, float v) {
-    const __half hi = __float2half_rn(v);
-    const size_t at = row * s.ld + col;
-    s.hi[at] = hi;
-    s.lo[at] = __float2half_rn(v - __half2float(hi));
-    const float sum = warp_sum(v);
-    if ((threadIdx.x & 31) == 0) {
-        const __half sh = __float2half_rn(sum);
-        const size_t sat = row * (s.ld >> 5) + (col >> 5);
-        s.sum_hi[sat] = sh;
-        s.sum_lo[sat] = __float2half_rn(sum - __half2float(sh));
-    }
-}
-
-// Four consecutive columns per thread (col % 4 == 0): eight neighbouring lanes cover one 32-column
-// sub-block. Every lane of the warp must call it; `active` masks the stores of lanes past the row.
-__device__ __forceinline__ void emit_split4(const SplitAct & s, size_t row, int col, float4 v, bool active) {
-    const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
-    const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-    const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
-    float sum = active ? (v.x + v.y) + (v.z + v.w) : 0.f;
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    if (!active) return;
-    const size_t at = row * s.ld + col;
-    *reinterpret_cast<uint2 *>(s.hi + at) = make_uint2(*reinterpret_cast<const uint32_t *>(&h01), *reinterpret_cast<const uint32_t *>(&h23));
-    *reinterpret_cast<uint2 *>(s.lo + at) = make_uint2(*reinterpret_cast<const uint32_t *>(&l01), *reinterpret_cast<const uint32_t *>(&l23));
-    if ((threadIdx.x & 7) == 0) {
-        const __half sh = __float2half_rn(sum);
-        const size_t sat = row * (s.ld >> 5) + (col >> 5);
-        s.sum_hi[sat] = sh;
-        s.sum_lo[sat] = __float2half_rn(sum - __half2float(sh));
-    }
-}
 
 // Decodes 8 consecutive elements starting at k (k % 8 == 0) of a stored row.
 template <uint32_t TYPE>
@@ -270,9 +227,8 @@ __global__ void embed_kernel(WeightView e, const int32_t * __restrict__ tokens, 
 
 __global__ void rms_norm_kernel(const float * __restrict__ x, int ldx, const int32_t * __restrict__ gather, const float * __restrict__ w, int n,
                                 float eps, float * __restrict__ y, int ldy, SplitAct split) {
-    // lets a following kernel launched with programmatic stream serialization start its weight-only
-    // prologue now; it waits on the device for this kernel's completion before it reads activations
-    asm volatile("griddepcontrol.launch_dependents;");
+    pdl_trigger();      // the next kernel's prologue (weight prefetch) may overlap this kernel
+    pdl_wait();
     __shared__ float partial[32];
     const int t = blockIdx.x;
     const float * xr = x + (size_t)(gather ? gather[t] : t) * ldx;
@@ -299,9 +255,8 @@ __global__ void rms_norm_kernel(const float * __restrict__ x, int ldx, const int
 // the split form is consumed.
 __global__ void rms_norm4_kernel(const float * __restrict__ x, int ldx, const int32_t * __restrict__ gather, const float * __restrict__ w, int n,
                                  float eps, float * __restrict__ y, int ldy, SplitAct split) {
-    // lets a following kernel launched with programmatic stream serialization start its weight-only
-    // prologue now; it waits on the device for this kernel's completion before it reads activations
-    asm volatile("griddepcontrol.launch_dependents;");
+    pdl_trigger();      // the next kernel's prologue (weight prefetch) may overlap this kernel
+    pdl_wait();
     __shared__ float partial[32];
     const int t = blockIdx.x;
     const float * xr = x + (size_t)(gather ? gather[t] : t) * ldx;
@@ -376,6 +331,8 @@ __global__ void gemm_rows_kernel(WeightView w, const float * __restrict__ x, int
 __global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, int n_head_kv, int head_dim, int n_rot, int neox,
                                   const float * __restrict__ inv_freq, const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_cell,
                                   KvLayout kv, int layer) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     float * row = qkv + (size_t)t * ld;
     const int pos = tok_pos[t];
@@ -491,9 +448,8 @@ __global__ void attention_ref_kernel(const float * __restrict__ qkv, int ld, int
 
 // x [t][ld] f32 -> its SplitAct (n a multiple of 32)
 __global__ void split_prep_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split) {
-    // lets a following kernel launched with programmatic stream serialization start its weight-only
-    // prologue now; it waits on the device for this kernel's completion before it reads activations
-    asm volatile("griddepcontrol.launch_dependents;");
+    pdl_trigger();      // the next kernel's prologue (weight prefetch) may overlap this kernel
+    pdl_wait();
     const int t = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -501,9 +457,8 @@ __global__ void split_prep_kernel(const float * __restrict__ x, int ldx, int n, 
 }
 
 __global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh, SplitAct split) {
-    // lets a following kernel launched with programmatic stream serialization start its weight-only
-    // prologue now; it waits on the device for this kernel's completion before it reads activations
-    asm volatile("griddepcontrol.launch_dependents;");
+    pdl_trigger();      // the next kernel's prologue (weight prefetch) may overlap this kernel
+    pdl_wait();
     const int t = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= ff) return;
@@ -514,9 +469,8 @@ __global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, flo
 }
 
 __global__ void swiglu4_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh, SplitAct split) {
-    // lets a following kernel launched with programmatic stream serialization start its weight-only
-    // prologue now; it waits on the device for this kernel's completion before it reads activations
-    asm volatile("griddepcontrol.launch_dependents;");
+    pdl_trigger();      // the next kernel's prologue (weight prefetch) may overlap this kernel
+    pdl_wait();
     const int t = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const bool active = i < ff;
@@ -531,9 +485,8 @@ __global__ void swiglu4_kernel(const float * __restrict__ gu, int ld, int ff, fl
 }
 
 __global__ void split_prep4_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split) {
-    // lets a following kernel launched with programmatic stream serialization start its weight-only
-    // prologue now; it waits on the device for this kernel's completion before it reads activations
-    asm volatile("griddepcontrol.launch_dependents;");
+    pdl_trigger();      // the next kernel's prologue (weight prefetch) may overlap this kernel
+    pdl_wait();
     const int t = blockIdx.y;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const bool active = i < n;
@@ -801,8 +754,8 @@ void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const flo
                      cudaStream_t stream, const SplitAct * split) {
     const SplitAct sa = split && n % 32 == 0 ? *split : SplitAct{};
     const bool aligned = n % 32 == 0 && ldx % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) % 16 == 0 && x != y;
-    if (aligned) rms_norm4_kernel<<<n_tokens, 256, 0, stream>>>(x, ldx, gather, w, n, eps, y, ldy, sa);
-    else rms_norm_kernel<<<n_tokens, 256, 0, stream>>>(x, ldx, gather, w, n, eps, y, ldy, sa);
+    if (aligned) launch_pdl(rms_norm4_kernel, dim3(n_tokens), dim3(256), 0, stream, x, ldx, gather, w, n, eps, y, ldy, sa);
+    else launch_pdl(rms_norm_kernel, dim3(n_tokens), dim3(256), 0, stream, x, ldx, gather, w, n, eps, y, ldy, sa);
 }
 
 void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
@@ -816,8 +769,8 @@ void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, floa
 
 void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
                        const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream) {
-    rope_store_kernel<<<dim3(n_tokens, (n_head + n_head_kv + 7) / 8), 256, 0, stream>>>(qkv, ld, n_head, n_head_kv, head_dim, n_rot, neox ? 1 : 0,
-                                                                                        inv_freq, tok_pos, tok_cell, kv, layer);
+    launch_pdl(rope_store_kernel, dim3(n_tokens, (n_head + n_head_kv + 7) / 8), dim3(256), 0, stream, qkv, ld, n_head, n_head_kv, head_dim, n_rot,
+               neox ? 1 : 0, inv_freq, tok_pos, tok_cell, kv, layer);
 }
 
 void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,
@@ -828,15 +781,17 @@ void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, K
 }
 
 void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream) {
-    if (n % 32 == 0 && ldx % 4 == 0 && (uintptr_t)x % 16 == 0) split_prep4_kernel<<<dim3((n + 1023) / 1024, n_tokens), 256, 0, stream>>>(x, ldx, n, split);
-    else split_prep_kernel<<<dim3((n + 255) / 256, n_tokens), 256, 0, stream>>>(x, ldx, n, split);
+    if (n % 32 == 0 && ldx % 4 == 0 && (uintptr_t)x % 16 == 0)
+        launch_pdl(split_prep4_kernel, dim3((n + 1023) / 1024, n_tokens), dim3(256), 0, stream, x, ldx, n, split);
+    else
+        launch_pdl(split_prep_kernel, dim3((n + 255) / 256, n_tokens), dim3(256), 0, stream, x, ldx, n, split);
 }
 
 void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split) {
     const SplitAct sa = split && ff % 32 == 0 ? *split : SplitAct{};
     const bool aligned = ff % 32 == 0 && ld % 4 == 0 && ldh % 4 == 0 && ((uintptr_t)gu | (uintptr_t)h) % 16 == 0;
-    if (aligned) swiglu4_kernel<<<dim3((ff + 1023) / 1024, n_tokens), 256, 0, stream>>>(gu, ld, ff, h, ldh, sa);
-    else swiglu_kernel<<<dim3((ff + 255) / 256, n_tokens), 256, 0, stream>>>(gu, ld, ff, h, ldh, sa);
+    if (aligned) launch_pdl(swiglu4_kernel, dim3((ff + 1023) / 1024, n_tokens), dim3(256), 0, stream, gu, ld, ff, h, ldh, sa);
+    else launch_pdl(swiglu_kernel, dim3((ff + 255) / 256, n_tokens), dim3(256), 0, stream, gu, ld, ff, h, ldh, sa);
 }
 
 void launch_moe_route(const float * router_logits, int n_expert, int k, int n_tokens, int32_t * ids, float * weights, cudaStream_t stream) {

@@ -37,6 +37,33 @@ inline size_t q4k_tiled_bytes(uint32_t n_out, uint32_t n_in) { return (size_t)((
 // Regroups GGUF-layout Q4_K rows into the tiled layout (device to device).
 void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream);
 
+#ifdef __CUDACC__
+// Programmatic dependent launch. A kernel launched with launch_pdl() may be scheduled while the
+// stream's previous kernel is still running; it must execute pdl_wait() before it reads or writes
+// anything an earlier kernel of the stream touches (the wait returns when the previous kernel has
+// completed and its writes are visible; without the launch attribute it is a no-op). pdl_trigger()
+// tells the scheduler that the kernels launched after this one may be scheduled from now on. Every
+// kernel launched this way executes pdl_wait() on every path, so completion stays transitive
+// along the stream.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // An activation matrix [t][ld] prepared for the exact tensor-core GEMM: the two-term f16 split
 // x = hi + lo, and per 32-element sub-block the sum of x, again as hi + lo ([t][ld / 32]).
 struct SplitAct {
@@ -54,6 +81,22 @@ struct SplitAct {
 // Fills the TMA descriptors of `s` for `rows` rows; returns false when the driver entry point is
 // unavailable (the kernels that need them are then not selected).
 bool split_act_encode_maps(SplitAct & s, size_t rows);
+
+// The step of the layer that consumes a streaming GEMM's result, done by the GEMM's finish kernel on the
+// row it has just summed (one launch and one pass over the row less):
+//   kind 1: y is written, then RMS-normalised with `norm_w` into `out` (f32, may be null) and `split`;
+//   kind 2: the row is [gate | up], two halves of n_out / 2 columns: silu(gate) * up goes to `out`
+//           (may be null) and `split`; y itself is not written.
+// The arithmetic and its order are those of the separate kernels, so results do not depend on the fusion.
+struct FinishTail {
+    int kind = 0;
+    const float * norm_w = nullptr;
+    float eps = 0.f;
+    float * out = nullptr;
+    int ld_out = 0;
+    SplitAct split{};
+};
+bool finish_tail_supported(const FinishTail & tail, int n_out, const float * y, int ldy, const float * bias, const float * residual, int ldr);
 
 // One row of a step plan as the packing kernel reads it (32 bytes).
 struct RowDesc {
@@ -153,18 +196,23 @@ void launch_gemm_q4k_exact(const WeightView & w, const SplitAct & x, int n_token
 // tcgen05 / tensor-memory variant of the exact GEMM (128 x 128 tiles). `error_flag` (device int) is
 // raised if a pipeline wait inside the kernel timed out.
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x);
+// With `scratch` (gemm_q4k_tc5_scratch_floats() floats) and few output tiles the reduction is cut into
+// splits of whole super-blocks (grid.z) whose partial results a finish kernel adds in order.
+size_t gemm_q4k_tc5_scratch_floats(uint32_t n_out, int n_tokens, int n_sm);
 void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
-                         const float * residual, int ldr, int * error_flag, cudaStream_t stream);
+                         const float * residual, int ldr, int * error_flag, float * scratch, size_t scratch_floats, int n_sm, cudaStream_t stream);
 // Weight-streaming exact GEMM for at most 8 tokens. `scratch` holds gemm_q4k_stream_scratch_floats()
 // floats of per-K-chunk partial sums; `n_sm` is the device's SM count (grid sizing); `error_flag` is set
 // to 1 if a bounded wait on a copy gave up.
 bool gemm_q4k_stream_supported(const WeightView & w, const SplitAct & x, int n_tokens);
 size_t gemm_q4k_stream_scratch_floats(uint32_t n_out, uint32_t n_in);
 void launch_gemm_q4k_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
-                            const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream);
-// y = sum over K chunks (in order) of the streaming kernels' partial sums + bias + residual
-void launch_gemm_stream_finish(const float * scratch, int n_chunks, int n_out, int n_tokens, float * y, int ldy, const float * bias,
-                               const float * residual, int ldr, cudaStream_t stream);
+                            const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream,
+                            const FinishTail * tail = nullptr);
+// y = sum over K chunks (in order) of partial sums laid out [chunk][t_stride tokens][n_out] + bias + residual,
+// then the tail, if one is given and finish_tail_supported() (the caller checks).
+void launch_gemm_stream_finish(const float * scratch, int n_chunks, int n_out, int n_tokens, int t_stride, float * y, int ldy, const float * bias,
+                               const float * residual, int ldr, cudaStream_t stream, const FinishTail * tail = nullptr);
 // Q8_0 counterpart of the streaming kernel. Its tile-major copy: one 2176-byte tile per (16 rows,
 // 128 columns): the 16 x 4 block scales, then the int8 weights in MMA fragment order.
 constexpr size_t kQ8TileBytes = 2176;
@@ -172,7 +220,8 @@ inline size_t q8_0_tiled_bytes(uint32_t n_out, uint32_t n_in) { return (size_t)(
 void launch_q8_0_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream);
 bool gemm_q8_0_stream_supported(const WeightView & w, const SplitAct & x, int n_tokens);
 void launch_gemm_q8_0_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
-                             const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream);
+                             const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream,
+                             const FinishTail * tail = nullptr);
 // Exact tensor-core Q8_0 GEMM (mma.sync) for more than 8 tokens; reads the GGUF-layout rows.
 bool gemm_q8_0_exact_supported(const WeightView & w, const SplitAct & x);
 void launch_gemm_q8_0_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
@@ -197,12 +246,14 @@ void launch_attention_decode(const float * qkv, int ld, int n_head, KvLayout kv,
                              const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int min_cols,
                              cudaStream_t stream);
 // Items of at most 8 query vectors, keys as the MMA's M dimension; `n_splits` CTAs share one item's KV
-// blocks and a merge kernel combines them (`scratch`: attention_decode8_scratch_floats() floats).
+// blocks and a merge kernel combines them (`scratch`: attention_decode8_scratch_floats() floats). With
+// more than one split and `split` given, the merge kernel also writes the output's split form (only
+// complete when every row of the step belongs to such an item and head_dim % 32 == 0).
 bool attention_decode8_supported(int n_head, int n_head_kv, int head_dim, int block_tokens);
 size_t attention_decode8_scratch_floats(int n_items, int n_head_kv, int n_splits, int head_dim);
 void launch_attention_decode8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items,
                               const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int n_splits,
-                              float * scratch, cudaStream_t stream);
+                              float * scratch, cudaStream_t stream, const SplitAct * split = nullptr);
 // h[t][i] = silu(gu[t][i]) * gu[t][ff + i]
 void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split = nullptr);
 

@@ -57,6 +57,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         if (have_split) launch_split_prep(dx.ptr, (int)n_in, (int)n_in, (int)n_tokens, xs.view, stream);
         int chosen = path;
         if (chosen == 0) chosen = have_split && n_tokens > 64 && gemm_q4k_tc5_supported(wv, xs.view) ? 4 : have_split && n_tokens > 8 && gemm_q4k_exact_supported(wv, xs.view) ? 3 : 1;
+        DeviceBuffer<float> tc5_scratch;
         DeviceBuffer<int> flag;
         flag.ensure(1);
         RB_CUDA(cudaMemsetAsync(flag.ptr, 0, sizeof(int), stream));
@@ -75,6 +76,10 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             }
             stream_scratch.ensure(gemm_q4k_stream_scratch_floats(n_out, n_in));
         }
+        if (chosen == 4) {
+            const size_t need = gemm_q4k_tc5_scratch_floats(wv.n_out, (int)n_tokens, n_sm);
+            if (need) tc5_scratch.ensure(need);
+        }
         if (chosen == 4 && !(have_split && gemm_q4k_tc5_supported(wv, xs.view))) {
             cudaStreamDestroy(stream);
             set_error("op_gemm: the requested kernel does not cover this type or shape");
@@ -89,7 +94,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         auto run = [&]() {
             if (chosen == 5 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
             else if (chosen == 5) launch_gemm_q4k_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
-            else if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, stream);
+            else if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, tc5_scratch.ptr, tc5_scratch.count, n_sm, stream);
             else if (chosen == 3 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 2) launch_gemm_mma(wv, xs.view.hi, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);

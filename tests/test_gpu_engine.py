@@ -349,6 +349,40 @@ def test_repeated_step_shapes_replay_as_cuda_graphs_with_identical_results(rb, o
         assert t0 == t1 and l0 == l1 and np.array_equal(x0, x1)
 
 
+@pytest.mark.parametrize("name,spec", [
+    ("tails_q4k", dict(arch="llama", layers=3, d=512, heads=8, kv_heads=2, ff=1024, vocab=1024, dtype="q4_k", seed=41)),
+    ("tails_q8", dict(arch="llama", layers=3, d=256, heads=4, kv_heads=2, ff=512, vocab=512, dtype="q8_0", seed=42)),
+])
+def test_finish_kernel_tails_equal_the_separate_kernels(rb, models, monkeypatch, name, spec):
+    """For at most 16 tokens a step the streaming GEMMs' finish kernels also do the RMS norm or the SwiGLU
+    that follows, and the attention merge writes the output projection's operand. The arithmetic and
+    its order are those of the separate kernels: tokens, logprobs and logits are equal bit for bit.
+    Steps of 3 tokens (one pass) and of 12 tokens (two passes of 8 and 4) cover both forms."""
+    def run(fused: bool):
+        monkeypatch.setenv("RB200_FUSED_FINISH", "1" if fused else "0")
+        engine = rb.Engine(str(models(name, **spec)), rb.EngineConfig(n_ctx=1024, n_seq_max=4, n_batch=128, n_ubatch=128))
+        out = rb.StepOutput()
+        g = rb.SamplingParamsV2.greedy()
+        prompts = [_prompt(300 + i, 20 + 3 * i, spec["vocab"]) for i in range(3)]
+        engine.step([rb.StepRow(i, i, p, 0, sample=True, sampling=g, want_logprob=True) for i, p in enumerate(prompts)], out)
+        last = [out.row(i).token for i in range(3)]
+        pos = [len(p) for p in prompts]
+        trace = []
+        for step in range(6):
+            n = 1 if step % 2 == 0 else 4          # 3 or 12 tokens in the step
+            rows = [rb.StepRow(i, i, [last[i]] + _prompt(400 + 10 * step + i, n - 1, spec["vocab"]), pos[i], sample=True, sampling=g, want_logprob=True)
+                    for i in range(3)]
+            engine.step(rows, out)
+            last = [out.row(i).token for i in range(3)]
+            pos = [q + n for q in pos]
+            trace.append(([out.row(i).token for i in range(3)], [out.row(i).logprob for i in range(3)], engine.last_logits(2).copy()))
+        engine.close()
+        return trace
+    separate, fused = run(False), run(True)
+    for (t0, l0, x0), (t1, l1, x1) in zip(separate, fused):
+        assert t0 == t1 and l0 == l1 and np.array_equal(x0, x1)
+
+
 def _greedy_v1(n_new, seed=0):
     # the serving layer's spelling of greedy for v1 rows: a nucleus that holds one token
     return dict(temperature=1e-4, top_p=1e-6, max_new_tokens=n_new, seed=seed)

@@ -31,9 +31,10 @@ def test_q4k_gemm_kernels_against_the_oracle(rb, oracle, n_out, n_in, T):
     assert e_fast < 3e-3
 
 
-@pytest.mark.parametrize("n_out,n_in,T", [(128, 256, 128), (256, 512, 130), (200, 768, 33), (512, 2048, 100), (256, 4096, 300)])
+@pytest.mark.parametrize("n_out,n_in,T", [(128, 256, 128), (256, 512, 130), (200, 768, 33), (512, 2048, 100), (256, 4096, 300), (384, 2816, 40)])
 def test_q4k_tcgen05_gemm_against_float64(rb, oracle, n_out, n_in, T):
-    """The tcgen05 / tensor-memory kernel computes the same exact products as the mma.sync one."""
+    """The tcgen05 / tensor-memory kernel computes the same exact products as the mma.sync one; the last
+    three shapes have few output tiles and run as splits of the reduction (the last with a short final split)."""
     rng = np.random.default_rng(7 * n_out + T)
     raw = _q4k_matrix(rb, rng, n_out, n_in)
     x = rng.normal(0, 1.5, (T, n_in)).astype(np.float32)
