@@ -364,6 +364,13 @@ void Engine::flush_kv_updates() {
     copies.clear();
 }
 
+// 9..16 tokens: a second pass of the weight stream costs more than the tcgen05 kernel when that one
+// can cut the reduction into splits (matrices with few 128-row tiles), measured on the 8B shapes.
+bool Engine::tc5_split_preferred(const WeightView & w, int T, const SplitAct * xs) const {
+    return xs && T > 8 && T <= kStreamMaxTokens && tc5_min_tokens <= kStreamMaxTokens && gemm_q4k_tc5_supported(w, *xs) &&
+           gemm_q4k_tc5_splits(w.n_out, w.n_in, T, n_sm_) > 1;
+}
+
 // Returns whether `tail` (the row-wise step that consumes y) was done by the GEMM's own finish kernel.
 bool Engine::linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual,
                     int ldr, const SplitAct * xs, const FinishTail * tail) {
@@ -371,7 +378,7 @@ bool Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
     prof_.begin(K_GEMM, stream);
     if (xs && T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) {
         launch_gemm_mma(w, xs->hi, ldx, T, y, ldy, bias, residual, ldr, stream);
-    } else if (xs && stream_gemm_ && T <= kStreamMaxTokens &&
+    } else if (xs && stream_gemm_ && T <= kStreamMaxTokens && !tc5_split_preferred(w, T, xs) &&
                (gemm_q4k_stream_supported(w, *xs, std::min(T, 8)) || gemm_q8_0_stream_supported(w, *xs, std::min(T, 8)))) {
         // at most 8 tokens per pass of the weight stream; up to 16 tokens two passes still beat the tensor-core kernels
         stream_scratch_.ensure(gemm_q4k_stream_scratch_floats(w.n_out, w.n_in));
@@ -385,8 +392,15 @@ bool Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
             part.sum_lo += (size_t)t0 * (xs->ld / 32);
             const float * res = residual ? residual + (size_t)t0 * ldr : nullptr;
             FinishTail part_tail;
+            RopeStoreArgs part_rope;
             if (tail_done) {
                 part_tail = *tail;
+                if (part_tail.rope) {
+                    part_rope = *part_tail.rope;
+                    part_rope.tok_pos += t0;
+                    part_rope.tok_cell += t0;
+                    part_tail.rope = &part_rope;
+                }
                 if (part_tail.out) part_tail.out += (size_t)t0 * part_tail.ld_out;
                 if (part_tail.split.hi) {
                     part_tail.split.hi += (size_t)t0 * part_tail.split.ld;
@@ -405,11 +419,12 @@ bool Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
             last_launches += 2;
         }
         --last_launches;        // the common tail below counts one
-    } else if (xs && T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) {
-        const size_t need = gemm_q4k_tc5_scratch_floats(w.n_out, T, n_sm_);
+    } else if (xs && (T > tc5_min_tokens || tc5_split_preferred(w, T, xs)) && gemm_q4k_tc5_supported(w, *xs)) {
+        const size_t need = gemm_q4k_tc5_scratch_floats(w.n_out, w.n_in, T, n_sm_);
         if (need) stream_scratch_.ensure(need);
+        tail_done = need && tail && fused_finish_ && finish_tail_supported(*tail, (int)w.n_out, y, ldy, bias, residual, ldr);
         launch_gemm_q4k_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, need ? stream_scratch_.ptr : nullptr, stream_scratch_.count, n_sm_,
-                            stream);
+                            stream, tail_done ? tail : nullptr);
         if (need) ++last_launches;
     } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {
         launch_gemm_q4k_exact(w, *xs, T, y, ldy, bias, residual, ldr, stream);
@@ -499,7 +514,7 @@ bool Engine::linear_reads_split(const WeightView & w, int ldx, int T, const Spli
     if (stream_gemm_ && T <= kStreamMaxTokens &&
         (gemm_q4k_stream_supported(w, *xs, std::min(T, 8)) || gemm_q8_0_stream_supported(w, *xs, std::min(T, 8))))
         return true;
-    if (T > tc5_min_tokens && gemm_q4k_tc5_supported(w, *xs)) return true;
+    if ((T > tc5_min_tokens || tc5_split_preferred(w, T, xs)) && gemm_q4k_tc5_supported(w, *xs)) return true;
     return T > mma_min_tokens && (gemm_q4k_exact_supported(w, *xs) || gemm_q8_0_exact_supported(w, *xs));
 }
 
@@ -932,8 +947,15 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         if (!norm_done)
             RB_K(K_OTHER, 1, launch_rms_norm(x_.ptr, d, nullptr, lw.attn_norm, d, hp.eps, qkv_split ? nullptr : xn_.ptr, d, Ti, stream, xn_split_.get()));
         norm_done = false;
+        const RopeStoreArgs rope_args{(int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox, model->inv_freq.ptr,
+                                      maps.tok_pos,   maps.tok_cell,     kvl,              (int)l};
+        bool roped = false;
         if (lw.wqkv.data) {
-            linear(lw.wqkv, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0, xn_split_.get());
+            // RoPE and the KV store by the projection's finish kernel when nothing else touches q, k, v in between
+            FinishTail rope_tail;
+            rope_tail.kind = 3;
+            rope_tail.rope = &rope_args;
+            roped = linear(lw.wqkv, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0, xn_split_.get(), any_adapter || lw.q_norm ? nullptr : &rope_tail);
         } else {
             linear(lw.wq, xn_.ptr, d, Ti, qkv_.ptr, ldqkv, lw.bqkv, nullptr, 0);
             linear(lw.wk, xn_.ptr, d, Ti, qkv_.ptr + dq, ldqkv, lw.bqkv ? lw.bqkv + dq : nullptr, nullptr, 0);
@@ -948,8 +970,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             RB_K(K_OTHER, 2, launch_rms_norm(qkv_.ptr, ldqkv, nullptr, lw.q_norm, dq, hp.eps, qkv_.ptr, ldqkv, Ti, stream);
                  launch_rms_norm(qkv_.ptr + dq, ldqkv, nullptr, lw.k_norm, dkv, hp.eps, qkv_.ptr + dq, ldqkv, Ti, stream));
         }
-        RB_K(K_OTHER, 1, launch_rope_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)hp.n_rot, hp.neox,
-                                           model->inv_freq.ptr, maps.tok_pos, maps.tok_cell, kvl, (int)l, stream));
+        if (!roped) RB_K(K_OTHER, 1, launch_rope_store(qkv_.ptr, ldqkv, Ti, rope_args, stream));
         if (attn_mma_) {
             // every row of the step goes through the split-KV kernel: its merge writes the split form as well
             const bool merge_splits = fused_finish_ && att_split_.get() && !any_wide_item && !any_mid_item && n_small_items && attn_splits > 1 &&

@@ -256,6 +256,7 @@ public:
 private:
     void load_model(const std::string & path);
     void restack_adapters();
+    bool tc5_split_preferred(const WeightView & w, int T, const SplitAct * xs) const;
     bool linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
                 const SplitAct * xs = nullptr, const FinishTail * tail = nullptr);
     struct GraphEntry {

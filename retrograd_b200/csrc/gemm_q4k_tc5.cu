@@ -385,7 +385,8 @@ void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint
 }
 
 void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
-                         const float * residual, int ldr, int * error_flag, float * scratch, size_t scratch_floats, int n_sm, cudaStream_t stream) {
+                         const float * residual, int ldr, int * error_flag, float * scratch, size_t scratch_floats, int n_sm, cudaStream_t stream,
+                         const FinishTail * tail) {
     static bool configured = false;
     if (!configured) {
         cudaFuncSetAttribute(gemm_q4k_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -395,16 +396,9 @@ void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens,
     // few output tiles (few tokens and few rows): cut the reduction into splits of whole super-blocks so the
     // grid still covers the GPU; the splits' partial results are added, in order, by the finish kernel
     const int n_sb = (int)w.n_in / 256;
-    const int tiles = ((n_tokens + BN - 1) / BN) * (int)((w.n_out + BM - 1) / BM);
-    int splits = 1, sb_per_split = n_sb;
-    if (scratch && tiles * 2 <= n_sm) {
-        const int want = std::min(n_sm / tiles, n_sb / 2);
-        if (want > 1) {
-            sb_per_split = (n_sb + want - 1) / want;
-            splits = (n_sb + sb_per_split - 1) / sb_per_split;
-            if ((size_t)splits * n_tokens * w.n_out > scratch_floats) { splits = 1; sb_per_split = n_sb; }
-        }
-    }
+    int splits = scratch ? gemm_q4k_tc5_splits(w.n_out, w.n_in, n_tokens, n_sm) : 1;
+    if ((size_t)splits * n_tokens * w.n_out > scratch_floats) splits = 1;
+    const int sb_per_split = (n_sb + splits - 1) / splits;
     float * partial = splits > 1 ? scratch : nullptr;
     const dim3 grid((n_tokens + BN - 1) / BN, (w.n_out + BM - 1) / BM, splits);
     // the kernel may start (barriers, tensor-memory allocation, first weight loads) while the stream's
@@ -427,12 +421,22 @@ void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens,
         cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<false>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias, no_residual, 0,
                            error_flag, sb_per_split, partial);
     }
-    if (splits > 1) launch_gemm_stream_finish(scratch, splits, (int)w.n_out, n_tokens, n_tokens, y, ldy, bias, residual, ldr, stream);
+    if (splits > 1) launch_gemm_stream_finish(scratch, splits, (int)w.n_out, n_tokens, n_tokens, y, ldy, bias, residual, ldr, stream, tail);
 }
 
-size_t gemm_q4k_tc5_scratch_floats(uint32_t n_out, int n_tokens, int n_sm) {
+int gemm_q4k_tc5_splits(uint32_t n_out, uint32_t n_in, int n_tokens, int n_sm) {
+    const int n_sb = (int)n_in / 256;
     const int tiles = ((n_tokens + BN - 1) / BN) * (int)((n_out + BM - 1) / BM);
-    return tiles * 2 <= n_sm ? (size_t)(n_sm / tiles) * n_tokens * n_out : 0;
+    if (tiles * 2 > n_sm) return 1;
+    const int want = std::min(n_sm / tiles, n_sb / 2);
+    if (want <= 1) return 1;
+    const int sb_per_split = (n_sb + want - 1) / want;
+    return (n_sb + sb_per_split - 1) / sb_per_split;
+}
+
+size_t gemm_q4k_tc5_scratch_floats(uint32_t n_out, uint32_t n_in, int n_tokens, int n_sm) {
+    const int splits = gemm_q4k_tc5_splits(n_out, n_in, n_tokens, n_sm);
+    return splits > 1 ? (size_t)splits * n_tokens * n_out : 0;
 }
 
 } // namespace rb200

@@ -330,7 +330,8 @@ __global__ void gemm_rows_kernel(WeightView w, const float * __restrict__ x, int
 // cache; the blocks of group 0 also store the token's V heads.
 __global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, int n_head_kv, int head_dim, int n_rot, int neox,
                                   const float * __restrict__ inv_freq, const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_cell,
-                                  KvLayout kv, int layer) {
+                                  KvLayout kv, int layer, const float * __restrict__ partial, int n_chunks, int t_stride, int ld_partial,
+                                  const float * __restrict__ bias) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -339,6 +340,35 @@ __global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, 
     const int half_rot = n_rot / 2;
     const int n_rot_heads = n_head + n_head_kv;
     const int h_lo = blockIdx.y * 8, h_hi = min(n_rot_heads, h_lo + 8);
+    if (partial) {
+        // the block's columns of the row (its heads; block 0 also the V heads) from the GEMM's partial
+        // sums, four columns per thread, every chunk's load issued before the first addition
+        const size_t chunk_stride = (size_t)t_stride * ld_partial;
+        const int v_lo = n_rot_heads * head_dim, v_hi = v_lo + n_head_kv * head_dim;
+        for (int part = 0; part < (blockIdx.y == 0 ? 2 : 1); ++part) {
+            const int c_lo = part ? v_lo : h_lo * head_dim, c_hi = part ? v_hi : h_hi * head_dim;
+            for (int col = c_lo + threadIdx.x * 4; col < c_hi; col += blockDim.x * 4) {
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int c0 = 0; c0 < n_chunks; c0 += 8) {
+                    float4 p[8];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        p[c] = c0 + c < n_chunks ? *reinterpret_cast<const float4 *>(partial + (size_t)(c0 + c) * chunk_stride + (size_t)t * ld_partial + col)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        if (c0 + c < n_chunks) { sum.x += p[c].x; sum.y += p[c].y; sum.z += p[c].z; sum.w += p[c].w; }
+                    }
+                }
+                if (bias) {
+                    const float4 b = *reinterpret_cast<const float4 *>(bias + col);
+                    sum.x += b.x; sum.y += b.y; sum.z += b.z; sum.w += b.w;
+                }
+                *reinterpret_cast<float4 *>(row + col) = sum;
+            }
+        }
+        __syncthreads();
+    }
     for (int idx = threadIdx.x; idx < (h_hi - h_lo) * half_rot; idx += blockDim.x) {
         const int h = h_lo + idx / half_rot, i = idx % half_rot;
         float * p = row + (size_t)h * head_dim;   // k heads follow the q heads contiguously
@@ -767,10 +797,17 @@ void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, floa
     });
 }
 
-void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
-                       const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream) {
-    launch_pdl(rope_store_kernel, dim3(n_tokens, (n_head + n_head_kv + 7) / 8), dim3(256), 0, stream, qkv, ld, n_head, n_head_kv, head_dim, n_rot,
-               neox ? 1 : 0, inv_freq, tok_pos, tok_cell, kv, layer);
+void launch_rope_store(float * qkv, int ld, int n_tokens, const RopeStoreArgs & a, cudaStream_t stream, const float * partial, int n_chunks,
+                       int t_stride, int ld_partial, const float * bias) {
+    launch_pdl(rope_store_kernel, dim3(n_tokens, (a.n_head + a.n_head_kv + 7) / 8), dim3(256), 0, stream, qkv, ld, a.n_head, a.n_head_kv, a.head_dim,
+               a.n_rot, a.neox ? 1 : 0, a.inv_freq, a.tok_pos, a.tok_cell, a.kv, a.layer, partial, n_chunks, t_stride, ld_partial, bias);
+}
+
+// The partial-sum form reads and writes four columns at a time and relies on the rotation touching
+// every q and k element's final value only after the block's own columns are formed.
+bool rope_store_from_partial_supported(const RopeStoreArgs & a, const float * qkv, int ld, int n_out, const float * bias) {
+    return a.head_dim % 4 == 0 && ld % 4 == 0 && (uintptr_t)qkv % 16 == 0 && (!bias || (uintptr_t)bias % 16 == 0) &&
+           n_out == (a.n_head + 2 * a.n_head_kv) * a.head_dim && n_out % 4 == 0;
 }
 
 void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,

@@ -87,9 +87,13 @@ bool split_act_encode_maps(SplitAct & s, size_t rows);
 //   kind 1: y is written, then RMS-normalised with `norm_w` into `out` (f32, may be null) and `split`;
 //   kind 2: the row is [gate | up], two halves of n_out / 2 columns: silu(gate) * up goes to `out`
 //           (may be null) and `split`; y itself is not written.
+//   kind 3: the row is a token's [q | k | v]: y is written, q and k are rotated in place and k, v
+//           stored into the paged cache (`rope`; y, ldy and the token count come from the GEMM).
 // The arithmetic and its order are those of the separate kernels, so results do not depend on the fusion.
+struct RopeStoreArgs;
 struct FinishTail {
     int kind = 0;
+    const RopeStoreArgs * rope = nullptr;
     const float * norm_w = nullptr;
     float eps = 0.f;
     float * out = nullptr;
@@ -198,9 +202,11 @@ void launch_gemm_q4k_exact(const WeightView & w, const SplitAct & x, int n_token
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x);
 // With `scratch` (gemm_q4k_tc5_scratch_floats() floats) and few output tiles the reduction is cut into
 // splits of whole super-blocks (grid.z) whose partial results a finish kernel adds in order.
-size_t gemm_q4k_tc5_scratch_floats(uint32_t n_out, int n_tokens, int n_sm);
+int gemm_q4k_tc5_splits(uint32_t n_out, uint32_t n_in, int n_tokens, int n_sm);      // 1: the reduction is not split
+size_t gemm_q4k_tc5_scratch_floats(uint32_t n_out, uint32_t n_in, int n_tokens, int n_sm);
 void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
-                         const float * residual, int ldr, int * error_flag, float * scratch, size_t scratch_floats, int n_sm, cudaStream_t stream);
+                         const float * residual, int ldr, int * error_flag, float * scratch, size_t scratch_floats, int n_sm, cudaStream_t stream,
+                         const FinishTail * tail = nullptr);      // the tail is done only when the reduction is split
 // Weight-streaming exact GEMM for at most 8 tokens. `scratch` holds gemm_q4k_stream_scratch_floats()
 // floats of per-K-chunk partial sums; `n_sm` is the device's SM count (grid sizing); `error_flag` is set
 // to 1 if a bounded wait on a copy gave up.
@@ -227,8 +233,20 @@ bool gemm_q8_0_exact_supported(const WeightView & w, const SplitAct & x);
 void launch_gemm_q8_0_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
                             const float * residual, int ldr, cudaStream_t stream);
 // In-place RoPE on q and k (inside the fused qkv buffer) and the f16 store of k, v into the paged cache.
-void launch_rope_store(float * qkv, int ld, int n_tokens, int n_head, int n_head_kv, int head_dim, int n_rot, bool neox,
-                       const float * inv_freq, const int32_t * tok_pos, const int32_t * tok_cell, KvLayout kv, int layer, cudaStream_t stream);
+struct RopeStoreArgs {
+    int n_head, n_head_kv, head_dim, n_rot;
+    bool neox;
+    const float * inv_freq;
+    const int32_t * tok_pos;
+    const int32_t * tok_cell;
+    KvLayout kv;
+    int layer;
+};
+// With `partial` the rows are first formed from a split-K GEMM's partial sums (laid out
+// [chunk][t_stride tokens][ld_partial], added in chunk order, plus bias), each block its own columns.
+void launch_rope_store(float * qkv, int ld, int n_tokens, const RopeStoreArgs & a, cudaStream_t stream, const float * partial = nullptr,
+                       int n_chunks = 0, int t_stride = 0, int ld_partial = 0, const float * bias = nullptr);
+bool rope_store_from_partial_supported(const RopeStoreArgs & a, const float * qkv, int ld, int n_out, const float * bias);
 void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,
                           const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream,
                           const SplitAct * split = nullptr);

@@ -77,7 +77,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             stream_scratch.ensure(gemm_q4k_stream_scratch_floats(n_out, n_in));
         }
         if (chosen == 4) {
-            const size_t need = gemm_q4k_tc5_scratch_floats(wv.n_out, (int)n_tokens, n_sm);
+            const size_t need = gemm_q4k_tc5_scratch_floats(wv.n_out, wv.n_in, (int)n_tokens, n_sm);
             if (need) tc5_scratch.ensure(need);
         }
         if (chosen == 4 && !(have_split && gemm_q4k_tc5_supported(wv, xs.view))) {
