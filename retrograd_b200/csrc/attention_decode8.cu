@@ -26,6 +26,7 @@ namespace {
 
 constexpr int D8_THREADS = 128;
 constexpr int D8_SLOTS = 3;          // K/V blocks resident per warp
+constexpr int D8_MAX_SPLITS = 16;    // CTAs sharing one item's KV blocks at most (the merge kernel holds that many triples in registers)
 
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
     const __half2 h = __floats2half2_rn(a, b);
@@ -246,14 +247,27 @@ __global__ void attention_decode8_merge_kernel(const float * __restrict__ partia
     if (cols > 8 || c >= cols) return;
     const int hk = blockIdx.y, dcol = threadIdx.x;
     const float * src = partial + (((size_t)blockIdx.x * n_head_kv + hk) * n_splits * 8 + c) * (HD + 2);
-    float M = -INFINITY;
-    for (int z = 0; z < n_splits; ++z) M = fmaxf(M, src[(size_t)z * 8 * (HD + 2) + HD]);
-    float num = 0.f, den = 0.f;
-    for (int z = 0; z < n_splits; ++z) {
+    // every split's (max, sum, value) is loaded before the first use: one memory latency, not one per split
+    float mz[D8_MAX_SPLITS], lz[D8_MAX_SPLITS], vz[D8_MAX_SPLITS];
+#pragma unroll
+    for (int z = 0; z < D8_MAX_SPLITS; ++z) {
         const float * p = src + (size_t)z * 8 * (HD + 2);
-        const float f = p[HD] == -INFINITY ? 0.f : expf(p[HD] - M);
-        num += f * p[dcol];
-        den += f * p[HD + 1];
+        const bool on = z < n_splits;
+        mz[z] = on ? p[HD] : -INFINITY;
+        lz[z] = on ? p[HD + 1] : 0.f;
+        vz[z] = on ? p[dcol] : 0.f;
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int z = 0; z < D8_MAX_SPLITS; ++z) M = fmaxf(M, mz[z]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int z = 0; z < D8_MAX_SPLITS; ++z) {
+        if (z < n_splits) {
+            const float f = mz[z] == -INFINITY ? 0.f : expf(mz[z] - M);
+            num += f * vz[z];
+            den += f * lz[z];
+        }
     }
     const float v = num / den;
     const int row = item.x + c / G, col = (hk * G + c % G) * HD + dcol;
@@ -286,6 +300,8 @@ bool attention_decode8_supported(int n_head, int n_head_kv, int head_dim, int bl
     return (head_dim == 64 || head_dim == 128) && block_tokens == 16 && n_head % n_head_kv == 0 && n_head / n_head_kv <= 8;
 }
 
+int attention_decode8_max_splits() { return D8_MAX_SPLITS; }
+
 size_t attention_decode8_scratch_floats(int n_items, int n_head_kv, int n_splits, int head_dim) {
     return n_splits > 1 ? (size_t)n_items * n_head_kv * n_splits * 8 * (head_dim + 2) : 0;
 }
@@ -294,6 +310,7 @@ void launch_attention_decode8(const float * qkv, int ld, int n_head, KvLayout kv
                               const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int n_splits,
                               float * scratch, cudaStream_t stream, const SplitAct * split) {
     if (n_items <= 0) return;
+    if (n_splits > D8_MAX_SPLITS) n_splits = D8_MAX_SPLITS;      // callers size the scratch with attention_decode8_max_splits()
     const SplitAct sa = split && n_splits > 1 ? *split : SplitAct{};
     if (kv.head_dim == 128)
         launch_hd8<128>(qkv, ld, n_head, kv, layer, items, n_items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch, stream, sa);

@@ -268,6 +268,7 @@ void launch_attention_decode(const float * qkv, int ld, int n_head, KvLayout kv,
 // more than one split and `split` given, the merge kernel also writes the output's split form (only
 // complete when every row of the step belongs to such an item and head_dim % 32 == 0).
 bool attention_decode8_supported(int n_head, int n_head_kv, int head_dim, int block_tokens);
+int attention_decode8_max_splits();
 size_t attention_decode8_scratch_floats(int n_items, int n_head_kv, int n_splits, int head_dim);
 void launch_attention_decode8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items,
                               const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int n_splits,
