@@ -288,6 +288,22 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
 int retro_b200_gemm_q4k_noalloc(const uint8_t * d_w, uint32_t n_out, uint32_t n_in, const float * d_x, uint32_t n_tokens, float * d_y,
                                 void * stream);
 
+/* Expert parallelism for mixture-of-experts models (the reference runs them on one GPU only:
+ * src/runtime/retro_experts.cpp:86-140 places expert banks on a single device). One engine per GPU;
+ * expert e is served by rank e / (n_expert / world). Rank 0 creates the 128-byte NCCL id, every rank
+ * passes it to retro_b200_engine_ep_init (collective). Afterwards every MoE layer of every step
+ * exchanges its (token, expert) pairs over NCCL, so all ranks must run the same number of steps; a rank
+ * without rows calls retro_b200_engine_ep_idle_step instead. Results equal the single-GPU engine's.
+ * retro_b200_ep_plan is the host arithmetic behind the exchange (all ranks' per-expert pair offsets
+ * [world][n_expert + 1] -> what this rank sends, receives and how the received rows group by expert);
+ * `sorted` needs room for *out_n_recv entries (-2 and the count when sorted_capacity is too small). */
+int retro_b200_nccl_unique_id(void * out_id_128);
+int retro_b200_engine_ep_init(retro_engine * engine, int rank, int world, const void * unique_id_128);
+int retro_b200_engine_ep_idle_step(retro_engine * engine);
+int retro_b200_ep_plan(const int32_t * all_offsets, int world, int rank, int n_expert, int32_t * send_begin, int32_t * send_count,
+                       int32_t * recv_begin, int32_t * recv_count, int32_t * offsets, int32_t * sorted, int32_t sorted_capacity,
+                       int32_t * out_n_recv);
+
 /* Bytes the last step copied host->device (the plan) and device->host (the sampled rows). */
 int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes);
 /* Steps served so far by replaying a captured CUDA graph, and graphs currently cached. A step shape

@@ -17,6 +17,8 @@ from .engine import (
     SamplingParamsV2,
     StepOutput,
     StepRow,
+    ep_plan,
+    nccl_unique_id,
     op_gemm,
     quantize_row,
     synth_gguf,
@@ -33,7 +35,9 @@ __all__ = [
     "SamplingParamsV2",
     "StepOutput",
     "StepRow",
+    "ep_plan",
     "load_library",
+    "nccl_unique_id",
     "op_gemm",
     "quantize_row",
     "synth_gguf",

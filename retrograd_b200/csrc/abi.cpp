@@ -966,6 +966,71 @@ int retro_b200_engine_graph_stats(retro_engine * engine, uint64_t * out_replays,
     });
 }
 
+namespace {
+int invalid(const std::string & message) {
+    set_error(message);
+    return STATUS_INVALID_ARGUMENT;
+}
+} // namespace
+
+int retro_b200_nccl_unique_id(void * out_id_128) {
+    return boundary([&]() -> int {
+        if (!out_id_128) return invalid("retro_b200_nccl_unique_id: null buffer");
+        const int status = nccl_api().GetUniqueId(out_id_128);
+        if (status != 0) throw std::runtime_error(std::string("NCCL: ") + nccl_api().GetErrorString(status));
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_ep_init(retro_engine * engine, int rank, int world, const void * unique_id_128) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        try {
+            e->ep_init(rank, world, unique_id_128);
+        } catch (const std::invalid_argument & err) {
+            return invalid(err.what());
+        }
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_engine_ep_idle_step(retro_engine * engine) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        try {
+            e->ep_idle_step();
+        } catch (const std::invalid_argument & err) {
+            return invalid(err.what());
+        }
+        return STATUS_OK;
+    });
+}
+
+int retro_b200_ep_plan(const int32_t * all_offsets, int world, int rank, int n_expert, int32_t * send_begin, int32_t * send_count, int32_t * recv_begin,
+                       int32_t * recv_count, int32_t * offsets, int32_t * sorted, int32_t sorted_capacity, int32_t * out_n_recv) {
+    return boundary([&]() -> int {
+        if (!all_offsets || world < 1 || rank < 0 || rank >= world || n_expert < 1 || n_expert % world != 0 || !send_begin || !send_count ||
+            !recv_begin || !recv_count || !offsets || !out_n_recv)
+            return invalid("retro_b200_ep_plan: bad arguments (the expert count must be a multiple of the world size)");
+        EpPlan plan;
+        ep_make_plan(all_offsets, world, rank, n_expert, plan);
+        *out_n_recv = plan.n_recv;
+        if (plan.n_recv > sorted_capacity || (plan.n_recv > 0 && !sorted)) {
+            set_error("retro_b200_ep_plan: the sorted buffer is too small");
+            return STATUS_BUFFER_TOO_SMALL;
+        }
+        std::copy(plan.send_begin.begin(), plan.send_begin.end(), send_begin);
+        std::copy(plan.send_count.begin(), plan.send_count.end(), send_count);
+        std::copy(plan.recv_begin.begin(), plan.recv_begin.end(), recv_begin);
+        std::copy(plan.recv_count.begin(), plan.recv_count.end(), recv_count);
+        std::copy(plan.offsets.begin(), plan.offsets.end(), offsets);
+        std::copy(plan.sorted.begin(), plan.sorted.end(), sorted);
+        return STATUS_OK;
+    });
+}
+
 int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes) {
     return boundary([&]() -> int {
         Engine * e = checked(engine);

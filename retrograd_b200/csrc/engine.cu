@@ -326,6 +326,10 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
 
 Engine::~Engine() {
     if (stream) cudaStreamSynchronize(stream);
+    if (ep_comm_) {
+        try { nccl_api().CommDestroy(ep_comm_); } catch (...) {}
+    }
+    if (h_ep_offsets_) cudaFreeHost(h_ep_offsets_);
     if (h_stage_) cudaFreeHost(h_stage_);
     if (h_result_) cudaFreeHost(h_result_);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
@@ -532,6 +536,99 @@ void Engine::lora(const std::string & target, const float * x, int ldx, int T, f
     launch_lora_expand(t.b.ptr, (int)r_max_, (int)t.n_out, lora_scales_.ptr, cur_tok_adapter_, lora_tmp_.ptr, T, y, ldy, stream);
     prof_.end(K_LORA, 2, stream);
     last_launches += 2;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Expert parallelism
+
+#define RB_NCCL(call)                                                                                          \
+    do {                                                                                                       \
+        const int rb_nccl_status = (call);                                                                     \
+        if (rb_nccl_status != 0) throw std::runtime_error(std::string("NCCL: ") + nccl_api().GetErrorString(rb_nccl_status)); \
+    } while (0)
+
+void Engine::ep_init(int rank, int world, const void * unique_id_128) {
+    const HParams & hp = model->hp;
+    if (hp.n_expert == 0) throw std::invalid_argument("expert parallelism needs a mixture-of-experts model");
+    if (ep_comm_) throw std::invalid_argument("expert parallelism is already initialised for this engine");
+    if (world < 1 || rank < 0 || rank >= world || !unique_id_128) throw std::invalid_argument("expert parallelism: bad rank / world size");
+    if (hp.n_expert % (uint32_t)world != 0) throw std::invalid_argument("expert parallelism: the expert count is not a multiple of the world size");
+    const NcclApi & nccl = nccl_api();
+    NcclId128 id;
+    std::memcpy(id.bytes, unique_id_128, sizeof(id.bytes));
+    RB_NCCL(nccl.CommInitRank(&ep_comm_, world, id, rank));
+    ep_rank_ = rank;
+    ep_world_ = world;
+    ep_all_offsets_.ensure((size_t)world * (hp.n_expert + 1));
+    ep_offsets_l_.ensure(hp.n_expert + 1);
+    RB_CUDA(cudaMallocHost(reinterpret_cast<void **>(&h_ep_offsets_), (size_t)world * (hp.n_expert + 1) * sizeof(int32_t)));
+}
+
+// Rows [begin[p], begin[p] + count[p]) of `send` go to rank p, rows from rank p land at recv_begin[p]. Both
+// sides derive the counts from the same all-gathered offsets, so every send has its receive.
+void Engine::ep_exchange(const float * send, const std::vector<int32_t> & send_begin, const std::vector<int32_t> & send_count, float * recv,
+                         const std::vector<int32_t> & recv_begin, const std::vector<int32_t> & recv_count, int d) {
+    const NcclApi & nccl = nccl_api();
+    if (send_count[ep_rank_] > 0) {
+        RB_CUDA(cudaMemcpyAsync(recv + (size_t)recv_begin[ep_rank_] * d, send + (size_t)send_begin[ep_rank_] * d, (size_t)send_count[ep_rank_] * d * 4,
+                                cudaMemcpyDeviceToDevice, stream));
+    }
+    RB_NCCL(nccl.GroupStart());
+    for (int p = 0; p < ep_world_; ++p) {
+        if (p == ep_rank_) continue;
+        if (send_count[p] > 0) RB_NCCL(nccl.Send(send + (size_t)send_begin[p] * d, (size_t)send_count[p] * d, kNcclFloat32, p, ep_comm_, stream));
+        if (recv_count[p] > 0) RB_NCCL(nccl.Recv(recv + (size_t)recv_begin[p] * d, (size_t)recv_count[p] * d, kNcclFloat32, p, ep_comm_, stream));
+    }
+    RB_NCCL(nccl.GroupEnd());
+}
+
+// One MoE layer under expert parallelism. On entry: xn_ holds the T normalised tokens, moe_ids_ / moe_w_ the
+// routing, moe_offsets_ / moe_sorted_ the pairs grouped by expert (T = 0: this rank only serves the others).
+void Engine::ep_moe_layer(const LayerWeights & lw, int T) {
+    const HParams & hp = model->hp;
+    const NcclApi & nccl = nccl_api();
+    const int E = (int)hp.n_expert, K = (int)hp.n_expert_used, P = T * K, d = (int)hp.d, ff = (int)hp.ff;
+    if (P == 0) RB_CUDA(cudaMemsetAsync(moe_offsets_.ptr, 0, (size_t)(E + 1) * 4, stream));
+    RB_NCCL(nccl.AllGather(moe_offsets_.ptr, ep_all_offsets_.ptr, (size_t)(E + 1), kNcclInt32, ep_comm_, stream));
+    RB_CUDA(cudaMemcpyAsync(h_ep_offsets_, ep_all_offsets_.ptr, (size_t)ep_world_ * (E + 1) * 4, cudaMemcpyDeviceToHost, stream));
+    RB_CUDA(cudaStreamSynchronize(stream));
+    EpPlan plan;
+    ep_make_plan(h_ep_offsets_, ep_world_, ep_rank_, E, plan);
+    const int n_recv = plan.n_recv;
+
+    ep_send_.ensure((size_t)std::max(P, 1) * d);
+    ep_back_.ensure((size_t)std::max(P, 1) * d);
+    ep_recv_.ensure((size_t)std::max(n_recv, 1) * d);
+    ep_gu_.ensure((size_t)std::max(n_recv, 1) * 2 * ff);
+    ep_h_.ensure((size_t)std::max(n_recv, 1) * ff);
+    ep_y_.ensure((size_t)std::max(n_recv, 1) * d);
+    ep_sorted_l_.ensure((size_t)std::max(n_recv, 1));
+
+    launch_ep_gather_rows(xn_.ptr, d, moe_sorted_.ptr, K, P, d, ep_send_.ptr, stream);
+    ep_exchange(ep_send_.ptr, plan.send_begin, plan.send_count, ep_recv_.ptr, plan.recv_begin, plan.recv_count, d);
+    if (n_recv > 0) {
+        RB_CUDA(cudaMemcpyAsync(ep_offsets_l_.ptr, plan.offsets.data(), (size_t)(E + 1) * 4, cudaMemcpyHostToDevice, stream));
+        RB_CUDA(cudaMemcpyAsync(ep_sorted_l_.ptr, plan.sorted.data(), (size_t)n_recv * 4, cudaMemcpyHostToDevice, stream));
+        launch_moe_gemm_grouped(lw.gate_exps, lw.gate_stride, E, ep_offsets_l_.ptr, ep_sorted_l_.ptr, ep_recv_.ptr, d, 1, ep_gu_.ptr, 2 * ff, stream);
+        launch_moe_gemm_grouped(lw.up_exps, lw.up_stride, E, ep_offsets_l_.ptr, ep_sorted_l_.ptr, ep_recv_.ptr, d, 1, ep_gu_.ptr + ff, 2 * ff, stream);
+        launch_swiglu(ep_gu_.ptr, 2 * ff, ff, n_recv, ep_h_.ptr, ff, stream);
+        launch_moe_gemm_grouped(lw.down_exps, lw.down_stride, E, ep_offsets_l_.ptr, ep_sorted_l_.ptr, ep_h_.ptr, ff, 1, ep_y_.ptr, d, stream);
+    }
+    // the results travel back along the same ranges, in the order the rows were sent
+    ep_exchange(ep_y_.ptr, plan.recv_begin, plan.recv_count, ep_back_.ptr, plan.send_begin, plan.send_count, d);
+    if (P > 0) {
+        launch_ep_scatter_rows(ep_back_.ptr, moe_sorted_.ptr, P, d, pair_y_.ptr, d, stream);
+        launch_moe_combine(pair_y_.ptr, d, moe_ids_.ptr, moe_w_.ptr, K, d, T, x_.ptr, x_.ptr, stream);
+    }
+    // the plan's host vectors were staged by the copies above; the next layer may reuse the buffers
+    RB_CUDA(cudaStreamSynchronize(stream));
+    last_launches += 8;
+}
+
+// A step of a rank that has no rows of its own: its experts still serve the other ranks' tokens.
+void Engine::ep_idle_step() {
+    if (!ep_comm_) throw std::invalid_argument("expert parallelism is not initialised for this engine");
+    for (uint32_t l = 0; l < model->hp.n_layer; ++l) ep_moe_layer(model->layers[l], 0);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1042,6 +1139,14 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             linear(lw.router, xn_.ptr, d, Ti, router_logits_.ptr, E, nullptr, nullptr, 0);
             RB_K(K_MOE, 1, launch_moe_route(router_logits_.ptr, E, K, Ti, moe_ids_.ptr, moe_w_.ptr, stream));
             RB_CUDA(cudaMemcpyAsync(route_ids.ptr + (size_t)l * P, moe_ids_.ptr, (size_t)P * 4, cudaMemcpyDeviceToDevice, stream));
+            if (ep_comm_) {
+                // expert parallelism: the pairs travel to their experts' ranks and back
+                RB_K(K_MOE, 1, launch_moe_group(moe_ids_.ptr, P, E, moe_offsets_.ptr, moe_sorted_.ptr, stream));
+                prof_.begin(K_MOE, stream);
+                ep_moe_layer(lw, Ti);
+                prof_.end(K_MOE, 8, stream);
+                continue;
+            }
             // pairs grouped by expert: every expert's weights are streamed once per eight of its pairs
             RB_K(K_MOE, 3, launch_moe_group(moe_ids_.ptr, P, E, moe_offsets_.ptr, moe_sorted_.ptr, stream);
                  launch_moe_gemm_grouped(lw.gate_exps, lw.gate_stride, E, moe_offsets_.ptr, moe_sorted_.ptr, xn_.ptr, d, K, pair_gu_.ptr, 2 * ff, stream);

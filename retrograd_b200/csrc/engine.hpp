@@ -8,6 +8,7 @@
 #include "common.hpp"
 #include "gguf.hpp"
 #include "kernels.cuh"
+#include "ep.hpp"
 #include "kv.hpp"
 
 #include <map>
@@ -253,9 +254,19 @@ public:
     cudaStream_t stream = nullptr;
     const int32_t * kv_block_table_device() const { return block_table_.ptr; }
 
+    // Expert parallelism (MoE models): joins an NCCL communicator of `world` engines, one per GPU;
+    // from then on every MoE layer exchanges its (token, expert) pairs with the experts' ranks, and
+    // all ranks must run the same number of steps (a rank without rows calls ep_idle_step()).
+    void ep_init(int rank, int world, const void * unique_id_128);
+    void ep_idle_step();
+    int ep_world() const { return ep_world_; }
+
 private:
     void load_model(const std::string & path);
     void restack_adapters();
+    void ep_moe_layer(const LayerWeights & lw, int T);
+    void ep_exchange(const float * send, const std::vector<int32_t> & send_begin, const std::vector<int32_t> & send_count, float * recv,
+                     const std::vector<int32_t> & recv_begin, const std::vector<int32_t> & recv_count, int d);
     bool tc5_split_preferred(const WeightView & w, int T, const SplitAct * xs) const;
     bool linear(const WeightView & w, const float * x, int ldx, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
                 const SplitAct * xs = nullptr, const FinishTail * tail = nullptr);
@@ -299,6 +310,11 @@ private:
     bool attn_decode8_ = true;
     int n_sm_ = 148;
     bool stream_gemm_ = true;
+    void * ep_comm_ = nullptr;
+    int ep_rank_ = 0, ep_world_ = 1;
+    int32_t * h_ep_offsets_ = nullptr;        // pinned: every rank's pair offsets of the layer
+    DeviceBuffer<int32_t> ep_all_offsets_, ep_offsets_l_, ep_sorted_l_;
+    DeviceBuffer<float> ep_send_, ep_recv_, ep_gu_, ep_h_, ep_y_, ep_back_;
     bool fused_finish_ = true;      // RB200_FUSED_FINISH=0: norm / SwiGLU always as kernels of their own
     SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;

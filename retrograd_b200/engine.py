@@ -206,6 +206,32 @@ def op_gemm(ggml_type: int, w_bytes, n_out: int, n_in: int, x, path: int = 0, it
     return y, ms.value
 
 
+def nccl_unique_id() -> bytes:
+    """The 128-byte NCCL id one rank creates and every rank passes to Engine.ep_init."""
+    buf = C.create_string_buffer(128)
+    _check(_ffi.load_library().retro_b200_nccl_unique_id(buf))
+    return buf.raw
+
+
+def ep_plan(all_offsets, rank: int):
+    """The exchange plan of one MoE layer for `rank`, from every rank's per-expert pair offsets
+    ([world, n_expert + 1], pairs sorted by expert). Host arithmetic only (no GPU needed). Returns a dict
+    of int32 arrays: send_begin, send_count, recv_begin, recv_count (per peer), offsets [n_expert + 1]
+    and sorted [n_recv] (rows of the receive buffer grouped by expert)."""
+    lib = _ffi.load_library()
+    off = np.ascontiguousarray(all_offsets, dtype=np.int32)
+    world, n_expert = off.shape[0], off.shape[1] - 1
+    per_peer = [np.zeros(world, dtype=np.int32) for _ in range(4)]
+    offsets = np.zeros(n_expert + 1, dtype=np.int32)
+    cap = int(off[:, -1].sum())
+    sorted_rows = np.zeros(max(cap, 1), dtype=np.int32)
+    n_recv = C.c_int32()
+    ptr = lambda a: a.ctypes.data_as(C.POINTER(C.c_int32))
+    _check(lib.retro_b200_ep_plan(ptr(off), world, rank, n_expert, *(ptr(a) for a in per_peer), ptr(offsets), ptr(sorted_rows), cap, C.byref(n_recv)))
+    return dict(send_begin=per_peer[0], send_count=per_peer[1], recv_begin=per_peer[2], recv_count=per_peer[3], offsets=offsets,
+                sorted=sorted_rows[: n_recv.value])
+
+
 class Engine:
     def __init__(self, model_path: str, config: EngineConfig | None = None) -> None:
         self._lib = _ffi.load_library()
@@ -531,6 +557,16 @@ class Engine:
         a, b = C.c_uint64(), C.c_uint64()
         _check(self._lib.retro_b200_engine_last_step_io(self._h, C.byref(a), C.byref(b)))
         return a.value, b.value
+
+    def ep_init(self, rank: int, world: int, unique_id: bytes) -> None:
+        """Joins the expert-parallel group (collective over all `world` engines, one per GPU)."""
+        if len(unique_id) != 128:
+            raise ValueError("the NCCL id is 128 bytes")
+        _check(self._lib.retro_b200_engine_ep_init(self._h, rank, world, C.create_string_buffer(unique_id, 128)))
+
+    def ep_idle_step(self) -> None:
+        """The step of a rank that has no rows of its own while other ranks of the group step."""
+        _check(self._lib.retro_b200_engine_ep_idle_step(self._h))
 
     def graph_stats(self) -> tuple[int, int]:
         """(steps replayed from a captured CUDA graph, graphs cached)."""
