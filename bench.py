@@ -68,6 +68,15 @@ WORKLOADS = {
         spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q8_0", seed=3),
         n_requests=8, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=65536,
     ),
+    # BASELINE config 5's shape cut to 6 of its 24 layers (the expert GEMMs still run on CUDA cores, and a
+    # full-depth model costs a quarter of an hour of GPU time per run): experts MXFP4, the rest Q8_0. With
+    # more than one GPU the ranks form an expert-parallel group: each serves 32 / N experts and its own requests.
+    "c5_ep": dict(
+        name="gpt-oss-20b-shape MoE cut to 6 layers (32 experts top-4, MXFP4), 128 requests per GPU, expert parallel",
+        spec=dict(arch="olmoe", layers=6, d=2880, heads=64, kv_heads=8, head_dim=64, ff=2880, vocab=201088, experts=32, experts_used=4,
+                  dtype="q8_0", expert_dtype="mxfp4", seed=5),
+        n_requests=128, prompt=(64, 1024), output=(128, 512), chunk=512, n_batch=1024, n_ctx=200_000, ep=True,
+    ),
     # BASELINE config 1 (CPU-runnable shape; used to exercise this script quickly)
     "c1": dict(
         name="tiny llama-style Q8_0, 8 requests",
@@ -139,6 +148,7 @@ class Driver:
         self.live: list[Request] = []
         self.out = rb.StepOutput(cfg["n_batch"], 0)
         self.reserved = 0
+        self.expert_parallel = False      # set when the engine joined an expert-parallel group: every rank steps in lock-step
 
     def admit(self, midflight=False):
         while self.free_slots:
@@ -180,7 +190,9 @@ class Driver:
     def step(self, prefill_only=False):
         rows, reqs = self.compose(prefill_only)
         if not rows:
-            return dict(decode=0, prefill=0, sampled=0, rows=rows)
+            if self.expert_parallel:
+                self.engine.ep_idle_step()      # this rank's experts still serve the other ranks' tokens
+            return dict(decode=0, prefill=0, sampled=0, rows=rows, wall=0.0, tokens=0, ctx_tokens=0, finished=[])
         self.engine.step(rows, self.out)
         wall = self.engine.last_call_s
         stamp = time.perf_counter()
@@ -347,12 +359,32 @@ def main():
     engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=cfg["n_ctx"], n_seq_max=cfg["n_requests"], n_batch=cfg["n_batch"], n_ubatch=cfg["n_batch"]))
     sampling = rb.SamplingParamsV2.greedy()
     driver = Driver(rb, engine, cfg, Workload(cfg, seed=1000 + rank), sampling)
+    expert_parallel = bool(cfg.get("ep")) and world > 1
+    if expert_parallel:
+        holder = [rb.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(holder, src=0)
+        engine.ep_init(rank, world, holder[0])
+        driver.expert_parallel = True
 
     # ---- ramp (untimed): a steady-state snapshot - every slot holds a request caught mid-flight
     driver.admit(midflight=True)
     ramp_steps = 0
-    while any(r.last is None for r in driver.live):
-        driver.step(prefill_only=True)     # no request advances its generation during the ramp
+    while True:
+        busy = any(r.last is None for r in driver.live)
+        if expert_parallel:
+            # every rank joins every step's exchange: ramp until the slowest rank is done
+            flag = torch.tensor([1 if busy else 0], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            if not int(flag.item()):
+                break
+            if busy:
+                driver.step(prefill_only=True)
+            else:
+                engine.ep_idle_step()
+        else:
+            if not busy:
+                break
+            driver.step(prefill_only=True)     # no request advances its generation during the ramp
         ramp_steps += 1
     for _ in range(args.warmup):
         driver.step()
@@ -374,6 +406,8 @@ def main():
     sp = cfg["spec"]
     hd = sp.get("head_dim") or sp["d"] // sp["heads"]
     w_elems_layer = sp["d"] * (sp["heads"] * hd + 2 * sp["kv_heads"] * hd) + sp["heads"] * hd * sp["d"] + 3 * sp["d"] * sp["ff"]
+    if sp.get("experts"):      # per token: the router and the experts it uses
+        w_elems_layer += sp["d"] * sp["experts"] + (sp["experts_used"] - 1) * 3 * sp["d"] * sp["ff"]
     for _ in range(args.steps):
         info = driver.step()
         ms, n_launch = engine.last_step_stats()
@@ -458,7 +492,7 @@ def main():
         "metric": "decode_tokens_per_s", "value": decode_tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": cfg["name"], "n_batch": cfg["n_batch"], "n_ctx": cfg["n_ctx"], "parallelism": f"replicas x{world}",
+        "config": {"workload": cfg["name"], "n_batch": cfg["n_batch"], "n_ctx": cfg["n_ctx"], "parallelism": f"expert parallel x{world}" if expert_parallel else f"replicas x{world}",
                    "rows_per_step": statistics.mean(rows_per_step), "decode_tokens_per_step": decode_tokens / args.steps / world,
                    "prefill_tokens_per_step": prefill_tokens / args.steps / world, "tokens_per_step": step_tokens / args.steps,
                    "ramp_steps": ramp_steps, "cuda_graphs": bool(args.graphs),
