@@ -298,6 +298,10 @@ int retro_b200_gemm_q4k_noalloc(const uint8_t * d_w, uint32_t n_out, uint32_t n_
  * [world][n_expert + 1] -> what this rank sends, receives and how the received rows group by expert);
  * `sorted` needs room for *out_n_recv entries (-2 and the count when sorted_capacity is too small). */
 int retro_b200_nccl_unique_id(void * out_id_128);
+/* GGML type codes the layer's gate / up / down expert banks are held in on the device. MXFP4 banks whose
+ * block scales an f16 holds are re-coded, exactly, as Q8_0 at load (type 8) so that the tensor-core GEMM
+ * serves them; RB200_MOE=rows keeps them MXFP4 (type 39) on the CUDA-core row kernel. */
+int retro_b200_engine_expert_storage(retro_engine * engine, int layer, uint32_t * out_types_3);
 int retro_b200_engine_ep_init(retro_engine * engine, int rank, int world, const void * unique_id_128);
 int retro_b200_engine_ep_idle_step(retro_engine * engine);
 int retro_b200_ep_plan(const int32_t * all_offsets, int world, int rank, int n_expert, int32_t * send_begin, int32_t * send_count,

@@ -973,6 +973,20 @@ int invalid(const std::string & message) {
 }
 } // namespace
 
+int retro_b200_engine_expert_storage(retro_engine * engine, int layer, uint32_t * out_types_3) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (!out_types_3 || layer < 0 || layer >= (int)e->model->hp.n_layer || e->model->hp.n_expert == 0)
+            return invalid("retro_b200_engine_expert_storage: not a layer of a mixture-of-experts model");
+        const LayerWeights & lw = e->model->layers[layer];
+        out_types_3[0] = lw.gate_exps.type;
+        out_types_3[1] = lw.up_exps.type;
+        out_types_3[2] = lw.down_exps.type;
+        return STATUS_OK;
+    });
+}
+
 int retro_b200_nccl_unique_id(void * out_id_128) {
     return boundary([&]() -> int {
         if (!out_id_128) return invalid("retro_b200_nccl_unique_id: null buffer");

@@ -38,7 +38,44 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // ---------------------------------------------------------------------------------------------
 // Model load
 
+namespace {
+
+// MXFP4 blocks (E8M0 byte + 16 bytes of nibbles; element i in the low nibble of byte i, element 16 + i in
+// its high nibble) -> Q8_0 blocks (f16 d + 32 int8) of the same values: d = 2^(x - 128) is half the E8M0
+// scale, the int8 is the doubled E2M1 value. False when a block's scale is outside what an f16 holds.
+bool mxfp4_to_q8_0(const void * src, size_t bytes, std::vector<uint8_t> & out) {
+    static const int8_t doubled[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+    const size_t n_blocks = bytes / 17;
+    const uint8_t * in = static_cast<const uint8_t *>(src);
+    bool ok = true;
+#pragma omp parallel for reduction(&& : ok)
+    for (long long b = 0; b < (long long)n_blocks; ++b) {
+        const int e = (int)in[b * 17] - 128;
+        if (e < -24 || e > 15) ok = false;
+    }
+    if (!ok) return false;
+    out.resize(n_blocks * 34);
+#pragma omp parallel for
+    for (long long b = 0; b < (long long)n_blocks; ++b) {
+        const uint8_t * blk = in + b * 17;
+        uint8_t * dst = out.data() + b * 34;
+        const int e = (int)blk[0] - 128;
+        // f16 bits of 2^e: normal for e >= -14, else the subnormal with mantissa bit e + 24
+        const uint16_t d = e >= -14 ? (uint16_t)((e + 15) << 10) : (uint16_t)(1u << (e + 24));
+        dst[0] = (uint8_t)(d & 0xFF);
+        dst[1] = (uint8_t)(d >> 8);
+        for (int i = 0; i < 16; ++i) {
+            dst[2 + i] = (uint8_t)doubled[blk[1 + i] & 0xF];
+            dst[2 + 16 + i] = (uint8_t)doubled[blk[1 + i] >> 4];
+        }
+    }
+    return true;
+}
+
+} // namespace
+
 void Engine::load_model(const std::string & path) {
+    if (const char * env = std::getenv("RB200_MOE")) moe_tensor_cores_ = std::string(env) != "rows";
     GgufFile file(path);
     model = std::make_unique<Model>();
     Model & m = *model;
@@ -198,7 +235,20 @@ void Engine::load_model(const std::string & path) {
                 if (t.ne.size() != 3 || t.ne[0] != n_in || t.ne[1] != n_out || t.ne[2] != hp.n_expert || n_in % 8 != 0) {
                     throw std::runtime_error("failed to load model GGUF: unexpected shape of " + name);
                 }
-                w = view_of(t, upload(t.data, t.n_bytes), n_out);
+                // MXFP4 experts whose block scales are powers of two an f16 holds are re-coded, exactly, as Q8_0
+                // (the doubled E2M1 value as the int8, half the E8M0 scale as d): the tensor-core Q8_0 GEMM
+                // then serves the experts. Twice the bytes per weight, an order of magnitude faster than the
+                // CUDA-core row kernel.
+                std::vector<uint8_t> recoded;
+                if (t.type == GGML_MXFP4 && moe_tensor_cores_ && n_in % 64 == 0 && mxfp4_to_q8_0(t.data, t.n_bytes, recoded)) {
+                    w.data = upload(recoded.data(), recoded.size());
+                    w.type = GGML_Q8_0;
+                    w.n_in = (uint32_t)n_in;
+                    w.n_out = (uint32_t)n_out;
+                    w.row_bytes = (uint32_t)row_bytes(GGML_Q8_0, n_in);
+                } else {
+                    w = view_of(t, upload(t.data, t.n_bytes), n_out);
+                }
                 stride = (uint64_t)w.row_bytes * n_out;
             };
             bank(p + "ffn_gate_exps.weight", hp.d, hp.ff, lw.gate_exps, lw.gate_stride);
@@ -330,6 +380,7 @@ Engine::~Engine() {
         try { nccl_api().CommDestroy(ep_comm_); } catch (...) {}
     }
     if (h_ep_offsets_) cudaFreeHost(h_ep_offsets_);
+    if (h_moe_offsets_) cudaFreeHost(h_moe_offsets_);
     if (h_stage_) cudaFreeHost(h_stage_);
     if (h_result_) cudaFreeHost(h_result_);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
@@ -539,6 +590,70 @@ void Engine::lora(const std::string & target, const float * x, int ldx, int T, f
 }
 
 // ---------------------------------------------------------------------------------------------
+// Expert FFNs on the tensor cores
+
+bool Engine::moe_experts_on_tensor_cores(const LayerWeights & lw) const {
+    const HParams & hp = model->hp;
+    return moe_tensor_cores_ && lw.gate_exps.type == GGML_Q8_0 && lw.up_exps.type == GGML_Q8_0 && lw.down_exps.type == GGML_Q8_0 &&
+           hp.d % 64 == 0 && hp.ff % 64 == 0;
+}
+
+// The experts' SwiGLU FFN over n (row, expert) pairs whose expert-sorted order is `gather`: pair i reads row
+// gather[i] / gather_div of `rows` and its result goes to row gather[i] of y_out. h_offsets (host,
+// n_expert + 1) delimits each expert's pairs. Every expert runs the exact Q8_0 tensor-core GEMM on its
+// contiguous pairs, whatever their number: an element's arithmetic does not depend on how many pairs
+// share the launch, which keeps results independent of the grouping (and of the expert-parallel world size).
+void Engine::moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_rows, const int32_t * gather, int gather_div,
+                            const int32_t * h_offsets, int n, float * y_out, int ld_out) {
+    const HParams & hp = model->hp;
+    const int E = (int)hp.n_expert, d = (int)hp.d, ff = (int)hp.ff;
+    if (n <= 0) return;
+    if ((size_t)n > moe_split_rows_) {
+        moe_split_rows_ = (size_t)n + (size_t)n / 2;
+        moe_x_split_.ensure(moe_split_rows_, d);
+        moe_h_split_.ensure(moe_split_rows_, ff);
+    }
+    moe_xs_.ensure((size_t)n * d);
+    moe_gu_s_.ensure((size_t)n * 2 * ff);
+    moe_y_s_.ensure((size_t)n * d);
+    launch_ep_gather_rows(rows, ld_rows, gather, gather_div, n, d, moe_xs_.ptr, stream);
+    launch_split_prep(moe_xs_.ptr, d, d, n, moe_x_split_.view, stream);
+    auto at_row = [](const SplitAct & s, int row) {
+        SplitAct part = s;
+        part.hi += (size_t)row * s.ld;
+        part.lo += (size_t)row * s.ld;
+        part.sum_hi += (size_t)row * (s.ld / 32);
+        part.sum_lo += (size_t)row * (s.ld / 32);
+        return part;
+    };
+    auto expert = [](const WeightView & bank, uint64_t stride, int e) {
+        WeightView w = bank;
+        w.data = bank.data + (size_t)e * stride;
+        w.tiled = nullptr;
+        return w;
+    };
+    for (int e = 0; e < E; ++e) {
+        const int begin = h_offsets[e], n_e = h_offsets[e + 1] - begin;
+        if (n_e <= 0) continue;
+        const SplitAct x = at_row(moe_x_split_.view, begin);
+        float * gu = moe_gu_s_.ptr + (size_t)begin * 2 * ff;
+        launch_gemm_q8_0_exact(expert(lw.gate_exps, lw.gate_stride, e), x, n_e, gu, 2 * ff, nullptr, nullptr, 0, stream);
+        launch_gemm_q8_0_exact(expert(lw.up_exps, lw.up_stride, e), x, n_e, gu + ff, 2 * ff, nullptr, nullptr, 0, stream);
+        last_launches += 2;
+    }
+    launch_swiglu(moe_gu_s_.ptr, 2 * ff, ff, n, nullptr, ff, stream, &moe_h_split_.view);
+    for (int e = 0; e < E; ++e) {
+        const int begin = h_offsets[e], n_e = h_offsets[e + 1] - begin;
+        if (n_e <= 0) continue;
+        launch_gemm_q8_0_exact(expert(lw.down_exps, lw.down_stride, e), at_row(moe_h_split_.view, begin), n_e, moe_y_s_.ptr + (size_t)begin * d, d, nullptr,
+                               nullptr, 0, stream);
+        ++last_launches;
+    }
+    launch_ep_scatter_rows(moe_y_s_.ptr, gather, n, d, y_out, ld_out, stream);
+    last_launches += 4;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Expert parallelism
 
 #define RB_NCCL(call)                                                                                          \
@@ -606,7 +721,10 @@ void Engine::ep_moe_layer(const LayerWeights & lw, int T) {
 
     launch_ep_gather_rows(xn_.ptr, d, moe_sorted_.ptr, K, P, d, ep_send_.ptr, stream);
     ep_exchange(ep_send_.ptr, plan.send_begin, plan.send_count, ep_recv_.ptr, plan.recv_begin, plan.recv_count, d);
-    if (n_recv > 0) {
+    if (n_recv > 0 && moe_experts_on_tensor_cores(lw)) {
+        RB_CUDA(cudaMemcpyAsync(ep_sorted_l_.ptr, plan.sorted.data(), (size_t)n_recv * 4, cudaMemcpyHostToDevice, stream));
+        moe_experts_tc(lw, ep_recv_.ptr, d, ep_sorted_l_.ptr, 1, plan.offsets.data(), n_recv, ep_y_.ptr, d);
+    } else if (n_recv > 0) {
         RB_CUDA(cudaMemcpyAsync(ep_offsets_l_.ptr, plan.offsets.data(), (size_t)(E + 1) * 4, cudaMemcpyHostToDevice, stream));
         RB_CUDA(cudaMemcpyAsync(ep_sorted_l_.ptr, plan.sorted.data(), (size_t)n_recv * 4, cudaMemcpyHostToDevice, stream));
         launch_moe_gemm_grouped(lw.gate_exps, lw.gate_stride, E, ep_offsets_l_.ptr, ep_sorted_l_.ptr, ep_recv_.ptr, d, 1, ep_gu_.ptr, 2 * ff, stream);
@@ -1145,6 +1263,19 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 prof_.begin(K_MOE, stream);
                 ep_moe_layer(lw, Ti);
                 prof_.end(K_MOE, 8, stream);
+                continue;
+            }
+            if (moe_experts_on_tensor_cores(lw)) {
+                // the pairs grouped by expert; the host needs the group sizes to launch one GEMM per expert
+                RB_K(K_MOE, 1, launch_moe_group(moe_ids_.ptr, P, E, moe_offsets_.ptr, moe_sorted_.ptr, stream));
+                if (!h_moe_offsets_) RB_CUDA(cudaMallocHost(reinterpret_cast<void **>(&h_moe_offsets_), (size_t)(E + 1) * sizeof(int32_t)));
+                RB_CUDA(cudaMemcpyAsync(h_moe_offsets_, moe_offsets_.ptr, (size_t)(E + 1) * 4, cudaMemcpyDeviceToHost, stream));
+                RB_CUDA(cudaStreamSynchronize(stream));
+                prof_.begin(K_MOE, stream);
+                moe_experts_tc(lw, xn_.ptr, d, moe_sorted_.ptr, K, h_moe_offsets_, P, pair_y_.ptr, d);
+                launch_moe_combine(pair_y_.ptr, d, moe_ids_.ptr, moe_w_.ptr, K, d, Ti, x_.ptr, x_.ptr, stream);
+                prof_.end(K_MOE, 8, stream);
+                ++last_launches;
                 continue;
             }
             // pairs grouped by expert: every expert's weights are streamed once per eight of its pairs

@@ -558,6 +558,12 @@ class Engine:
         _check(self._lib.retro_b200_engine_last_step_io(self._h, C.byref(a), C.byref(b)))
         return a.value, b.value
 
+    def expert_storage(self, layer: int) -> tuple[int, int, int]:
+        """GGML type codes of the layer's gate / up / down expert banks as held on the device."""
+        t = (C.c_uint32 * 3)()
+        _check(self._lib.retro_b200_engine_expert_storage(self._h, layer, t))
+        return t[0], t[1], t[2]
+
     def ep_init(self, rank: int, world: int, unique_id: bytes) -> None:
         """Joins the expert-parallel group (collective over all `world` engines, one per GPU)."""
         if len(unique_id) != 128:

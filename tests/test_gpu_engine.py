@@ -352,6 +352,8 @@ def test_repeated_step_shapes_replay_as_cuda_graphs_with_identical_results(rb, o
 @pytest.mark.parametrize("name,spec", [
     ("tails_q4k", dict(arch="llama", layers=3, d=512, heads=8, kv_heads=2, ff=1024, vocab=1024, dtype="q4_k", seed=41)),
     ("tails_q8", dict(arch="llama", layers=3, d=256, heads=4, kv_heads=2, ff=512, vocab=512, dtype="q8_0", seed=42)),
+    # q / k / v biases go through the RoPE tail, the half-split rotation of this architecture too
+    ("tails_q8_bias", dict(arch="qwen2", layers=2, d=256, heads=4, kv_heads=2, ff=512, vocab=512, dtype="q8_0", seed=43, bias=1)),
 ])
 def test_finish_kernel_tails_equal_the_separate_kernels(rb, models, monkeypatch, name, spec):
     """For at most 16 tokens a step the streaming GEMMs' finish kernels also do the RMS norm or the SwiGLU

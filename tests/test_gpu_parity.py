@@ -180,3 +180,40 @@ def test_full_8b_shape_logits_within_tolerance(rb, oracle):
         rows = [rb.StepRow.decode(i, i, out.row(i).token, len(prompts[i]) + step, greedy) for i in range(3)]
     print(f"8B shape: max|dlogit|={rep.max_logit_diff:.3e} min margin={rep.min_margin:.3e} ties={rep.tie_events}")
     engine.close()
+
+
+def test_moe_experts_recoded_for_the_tensor_cores_agree_with_the_row_kernel(rb, models, monkeypatch):
+    """MXFP4 expert banks are re-coded, value for value, as Q8_0 at load and served by the tensor-core GEMM,
+    one launch per expert; RB200_MOE=rows keeps the CUDA-core row kernel on the MXFP4 bytes. Same weights,
+    two summation orders: routing equal, logits within 2e-4, greedy tokens equal."""
+    spec = dict(arch="olmoe", layers=2, d=128, heads=4, kv_heads=4, ff=64, vocab=512, experts=8, experts_used=2,
+                dtype="q8_0", expert_dtype="mxfp4", seed=21)
+    path = models("moe_flat", **spec)
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(3, 512, 11 + 4 * i).tolist() for i in range(3)]
+    greedy = rb.SamplingParamsV2.greedy()
+
+    def run(rows_kernel: bool):
+        if rows_kernel:
+            monkeypatch.setenv("RB200_MOE", "rows")
+        else:
+            monkeypatch.delenv("RB200_MOE", raising=False)
+        engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=512, n_seq_max=4, n_batch=64, n_ubatch=64))
+        storage = engine.expert_storage(0)
+        out = rb.StepOutput()
+        engine.step([rb.StepRow(i, i, p, 0, sample=True, sampling=greedy) for i, p in enumerate(prompts)], out)
+        toks = [out.row(i).token for i in range(3)]
+        logits = np.stack([engine.last_logits(i) for i in range(3)])
+        routes = engine.last_routes().copy()
+        engine.step([rb.StepRow(i, i, [toks[i]], len(prompts[i]), sample=True, sampling=greedy) for i in range(3)], out)
+        logits2 = np.stack([engine.last_logits(i) for i in range(3)])
+        engine.close()
+        return storage, toks, logits, logits2, routes
+
+    s_tc, t_tc, l_tc, l2_tc, r_tc = run(False)
+    s_rows, t_rows, l_rows, l2_rows, r_rows = run(True)
+    assert s_tc == (8, 8, 8) and s_rows == (39, 39, 39)
+    assert np.array_equal(r_tc, r_rows) and t_tc == t_rows
+    err = max(float(np.abs(l_tc - l_rows).max()), float(np.abs(l2_tc - l2_rows).max()))
+    print(f"moe tensor-core vs row kernel: max|dlogit|={err:.3e}")
+    assert err < 2e-4
