@@ -380,7 +380,6 @@ Engine::~Engine() {
         try { nccl_api().CommDestroy(ep_comm_); } catch (...) {}
     }
     if (h_ep_offsets_) cudaFreeHost(h_ep_offsets_);
-    if (h_moe_offsets_) cudaFreeHost(h_moe_offsets_);
     if (h_stage_) cudaFreeHost(h_stage_);
     if (h_result_) cudaFreeHost(h_result_);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
@@ -599,12 +598,12 @@ bool Engine::moe_experts_on_tensor_cores(const LayerWeights & lw) const {
 }
 
 // The experts' SwiGLU FFN over n (row, expert) pairs whose expert-sorted order is `gather`: pair i reads row
-// gather[i] / gather_div of `rows` and its result goes to row gather[i] of y_out. h_offsets (host,
-// n_expert + 1) delimits each expert's pairs. Every expert runs the exact Q8_0 tensor-core GEMM on its
-// contiguous pairs, whatever their number: an element's arithmetic does not depend on how many pairs
-// share the launch, which keeps results independent of the grouping (and of the expert-parallel world size).
+// gather[i] / gather_div of `rows` and its result goes to row gather[i] of y_out. d_offsets (device,
+// n_expert + 1) delimits each expert's pairs. The exact Q8_0 tensor-core GEMM runs in its grouped form, one
+// launch for all experts with fixed token tiles: an element's arithmetic does not depend on how many pairs
+// its expert has, which keeps results independent of the grouping (and of the expert-parallel world size).
 void Engine::moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_rows, const int32_t * gather, int gather_div,
-                            const int32_t * h_offsets, int n, float * y_out, int ld_out) {
+                            const int32_t * d_offsets, int n, float * y_out, int ld_out) {
     const HParams & hp = model->hp;
     const int E = (int)hp.n_expert, d = (int)hp.d, ff = (int)hp.ff;
     if (n <= 0) return;
@@ -618,39 +617,12 @@ void Engine::moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_
     moe_y_s_.ensure((size_t)n * d);
     launch_ep_gather_rows(rows, ld_rows, gather, gather_div, n, d, moe_xs_.ptr, stream);
     launch_split_prep(moe_xs_.ptr, d, d, n, moe_x_split_.view, stream);
-    auto at_row = [](const SplitAct & s, int row) {
-        SplitAct part = s;
-        part.hi += (size_t)row * s.ld;
-        part.lo += (size_t)row * s.ld;
-        part.sum_hi += (size_t)row * (s.ld / 32);
-        part.sum_lo += (size_t)row * (s.ld / 32);
-        return part;
-    };
-    auto expert = [](const WeightView & bank, uint64_t stride, int e) {
-        WeightView w = bank;
-        w.data = bank.data + (size_t)e * stride;
-        w.tiled = nullptr;
-        return w;
-    };
-    for (int e = 0; e < E; ++e) {
-        const int begin = h_offsets[e], n_e = h_offsets[e + 1] - begin;
-        if (n_e <= 0) continue;
-        const SplitAct x = at_row(moe_x_split_.view, begin);
-        float * gu = moe_gu_s_.ptr + (size_t)begin * 2 * ff;
-        launch_gemm_q8_0_exact(expert(lw.gate_exps, lw.gate_stride, e), x, n_e, gu, 2 * ff, nullptr, nullptr, 0, stream);
-        launch_gemm_q8_0_exact(expert(lw.up_exps, lw.up_stride, e), x, n_e, gu + ff, 2 * ff, nullptr, nullptr, 0, stream);
-        last_launches += 2;
-    }
+    launch_gemm_q8_0_exact_grouped(lw.gate_exps, lw.gate_stride, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr, 2 * ff, stream);
+    launch_gemm_q8_0_exact_grouped(lw.up_exps, lw.up_stride, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr + ff, 2 * ff, stream);
     launch_swiglu(moe_gu_s_.ptr, 2 * ff, ff, n, nullptr, ff, stream, &moe_h_split_.view);
-    for (int e = 0; e < E; ++e) {
-        const int begin = h_offsets[e], n_e = h_offsets[e + 1] - begin;
-        if (n_e <= 0) continue;
-        launch_gemm_q8_0_exact(expert(lw.down_exps, lw.down_stride, e), at_row(moe_h_split_.view, begin), n_e, moe_y_s_.ptr + (size_t)begin * d, d, nullptr,
-                               nullptr, 0, stream);
-        ++last_launches;
-    }
+    launch_gemm_q8_0_exact_grouped(lw.down_exps, lw.down_stride, E, d_offsets, moe_h_split_.view, n, moe_y_s_.ptr, d, stream);
     launch_ep_scatter_rows(moe_y_s_.ptr, gather, n, d, y_out, ld_out, stream);
-    last_launches += 4;
+    last_launches += 7;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -722,8 +694,9 @@ void Engine::ep_moe_layer(const LayerWeights & lw, int T) {
     launch_ep_gather_rows(xn_.ptr, d, moe_sorted_.ptr, K, P, d, ep_send_.ptr, stream);
     ep_exchange(ep_send_.ptr, plan.send_begin, plan.send_count, ep_recv_.ptr, plan.recv_begin, plan.recv_count, d);
     if (n_recv > 0 && moe_experts_on_tensor_cores(lw)) {
+        RB_CUDA(cudaMemcpyAsync(ep_offsets_l_.ptr, plan.offsets.data(), (size_t)(E + 1) * 4, cudaMemcpyHostToDevice, stream));
         RB_CUDA(cudaMemcpyAsync(ep_sorted_l_.ptr, plan.sorted.data(), (size_t)n_recv * 4, cudaMemcpyHostToDevice, stream));
-        moe_experts_tc(lw, ep_recv_.ptr, d, ep_sorted_l_.ptr, 1, plan.offsets.data(), n_recv, ep_y_.ptr, d);
+        moe_experts_tc(lw, ep_recv_.ptr, d, ep_sorted_l_.ptr, 1, ep_offsets_l_.ptr, n_recv, ep_y_.ptr, d);
     } else if (n_recv > 0) {
         RB_CUDA(cudaMemcpyAsync(ep_offsets_l_.ptr, plan.offsets.data(), (size_t)(E + 1) * 4, cudaMemcpyHostToDevice, stream));
         RB_CUDA(cudaMemcpyAsync(ep_sorted_l_.ptr, plan.sorted.data(), (size_t)n_recv * 4, cudaMemcpyHostToDevice, stream));
@@ -1266,13 +1239,10 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 continue;
             }
             if (moe_experts_on_tensor_cores(lw)) {
-                // the pairs grouped by expert; the host needs the group sizes to launch one GEMM per expert
+                // the pairs grouped by expert, then one grouped tensor-core GEMM per projection
                 RB_K(K_MOE, 1, launch_moe_group(moe_ids_.ptr, P, E, moe_offsets_.ptr, moe_sorted_.ptr, stream));
-                if (!h_moe_offsets_) RB_CUDA(cudaMallocHost(reinterpret_cast<void **>(&h_moe_offsets_), (size_t)(E + 1) * sizeof(int32_t)));
-                RB_CUDA(cudaMemcpyAsync(h_moe_offsets_, moe_offsets_.ptr, (size_t)(E + 1) * 4, cudaMemcpyDeviceToHost, stream));
-                RB_CUDA(cudaStreamSynchronize(stream));
                 prof_.begin(K_MOE, stream);
-                moe_experts_tc(lw, xn_.ptr, d, moe_sorted_.ptr, K, h_moe_offsets_, P, pair_y_.ptr, d);
+                moe_experts_tc(lw, xn_.ptr, d, moe_sorted_.ptr, K, moe_offsets_.ptr, P, pair_y_.ptr, d);
                 launch_moe_combine(pair_y_.ptr, d, moe_ids_.ptr, moe_w_.ptr, K, d, Ti, x_.ptr, x_.ptr, stream);
                 prof_.end(K_MOE, 8, stream);
                 ++last_launches;

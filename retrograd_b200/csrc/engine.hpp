@@ -265,7 +265,7 @@ private:
     void load_model(const std::string & path);
     void restack_adapters();
     bool moe_experts_on_tensor_cores(const LayerWeights & lw) const;
-    void moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_rows, const int32_t * gather, int gather_div, const int32_t * h_offsets,
+    void moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_rows, const int32_t * gather, int gather_div, const int32_t * d_offsets,
                         int n, float * y_out, int ld_out);
     void ep_moe_layer(const LayerWeights & lw, int T);
     void ep_exchange(const float * send, const std::vector<int32_t> & send_begin, const std::vector<int32_t> & send_count, float * recv,
@@ -314,7 +314,6 @@ private:
     int n_sm_ = 148;
     bool stream_gemm_ = true;
     bool moe_tensor_cores_ = true;      // RB200_MOE=rows: experts stay MXFP4 on the CUDA-core row kernel
-    int32_t * h_moe_offsets_ = nullptr;     // pinned: the layer's pair offsets per expert
     DeviceBuffer<float> moe_xs_, moe_gu_s_, moe_y_s_;      // expert-contiguous rows: inputs, [gate | up], outputs
     SplitBuffer moe_x_split_, moe_h_split_;
     size_t moe_split_rows_ = 0;

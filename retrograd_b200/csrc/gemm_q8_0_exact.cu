@@ -30,7 +30,8 @@ struct Fetch {
 template <int BN, bool RESIDUAL>
 __global__ void __launch_bounds__(THREADS) gemm_q8_0_exact_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes, SplitAct X,
                                                                   int T, float * __restrict__ Y, int ldy, const float * __restrict__ bias,
-                                                                  const float * __restrict__ residual, int ldr) {
+                                                                  const float * __restrict__ residual, int ldr,
+                                                                  const int32_t * __restrict__ group_offsets, unsigned long long group_stride) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int A_BYTES = BM * 128;
     constexpr int B_BYTES = BN * 128;
@@ -48,6 +49,17 @@ __global__ void __launch_bounds__(THREADS) gemm_q8_0_exact_kernel(const uint8_t 
     const int g = lane >> 2, tq = lane & 3;
     const int m0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
     const int n_k = n_in / BK;
+    if (group_offsets) {
+        // grouped form: blockIdx.z is a group (an expert) with its own weight matrix and its own contiguous
+        // range of activation / result rows; the grid's token tiles are an upper bound
+        const int begin = group_offsets[blockIdx.z];
+        T = group_offsets[blockIdx.z + 1] - begin;
+        if (t0 >= T) return;
+        W += (size_t)blockIdx.z * group_stride;
+        X.hi += (size_t)begin * X.ld;
+        X.lo += (size_t)begin * X.ld;
+        Y += (size_t)begin * ldy;
+    }
 
     float * d_s = reinterpret_cast<float *>(smem + D_OFF);
 
@@ -214,7 +226,7 @@ void launch_one(const WeightView & w, const SplitAct & x, int T, float * y, int 
     }
     const dim3 grid((w.n_out + BM - 1) / BM, (T + BN - 1) / BN);
     gemm_q8_0_exact_kernel<BN, RESIDUAL><<<grid, THREADS, smem, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, T, y, ldy, bias,
-                                                                         residual, ldr);
+                                                                         residual, ldr, nullptr, 0ull);
 }
 
 template <int BN>
@@ -228,6 +240,21 @@ void launch_bn(const WeightView & w, const SplitAct & x, int T, float * y, int l
 
 bool gemm_q8_0_exact_supported(const WeightView & w, const SplitAct & x) {
     return w.type == GGML_Q8_0 && w.n_in % 64 == 0 && x.hi && x.ld == (int)w.n_in;
+}
+
+void launch_gemm_q8_0_exact_grouped(const WeightView & w, uint64_t group_stride_bytes, int n_groups, const int32_t * group_offsets, const SplitAct & x,
+                                    int max_group_rows, float * y, int ldy, cudaStream_t stream) {
+    constexpr int BN = 64;
+    constexpr int smem = STAGES * (BM * 128 + 2 * BN * 128) + STAGES * 2 * BM * (int)sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(gemm_q8_0_exact_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        configured = true;
+    }
+    if (n_groups <= 0 || max_group_rows <= 0) return;
+    const dim3 grid((w.n_out + BM - 1) / BM, (max_group_rows + BN - 1) / BN, n_groups);
+    gemm_q8_0_exact_kernel<BN, false><<<grid, THREADS, smem, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, 0, y, ldy, nullptr, nullptr,
+                                                                       0, group_offsets, (unsigned long long)group_stride_bytes);
 }
 
 void launch_gemm_q8_0_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,

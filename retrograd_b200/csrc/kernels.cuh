@@ -232,6 +232,12 @@ void launch_gemm_q8_0_stream(const WeightView & w, const SplitAct & x, int n_tok
 bool gemm_q8_0_exact_supported(const WeightView & w, const SplitAct & x);
 void launch_gemm_q8_0_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
                             const float * residual, int ldr, cudaStream_t stream);
+// Grouped form (expert banks): group g has its own matrix at w.data + g * group_stride_bytes (w describes one
+// group's matrix) and the contiguous rows [group_offsets[g], group_offsets[g + 1]) of x and y (offsets on
+// the device); max_group_rows bounds the largest group. One launch, 64-row token tiles whatever the
+// group sizes, so a row's result does not depend on how the rows are grouped.
+void launch_gemm_q8_0_exact_grouped(const WeightView & w, uint64_t group_stride_bytes, int n_groups, const int32_t * group_offsets, const SplitAct & x,
+                                    int max_group_rows, float * y, int ldy, cudaStream_t stream);
 // In-place RoPE on q and k (inside the fused qkv buffer) and the f16 store of k, v into the paged cache.
 struct RopeStoreArgs {
     int n_head, n_head_kv, head_dim, n_rot;
