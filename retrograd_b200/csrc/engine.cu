@@ -679,7 +679,9 @@ void Engine::ep_moe_layer(const LayerWeights & lw, int T) {
     RB_NCCL(nccl.AllGather(moe_offsets_.ptr, ep_all_offsets_.ptr, (size_t)(E + 1), kNcclInt32, ep_comm_, stream));
     RB_CUDA(cudaMemcpyAsync(h_ep_offsets_, ep_all_offsets_.ptr, (size_t)ep_world_ * (E + 1) * 4, cudaMemcpyDeviceToHost, stream));
     RB_CUDA(cudaStreamSynchronize(stream));
-    EpPlan plan;
+    // the plan outlives this call: its vectors are the source of host-to-device copies, and the next
+    // rewrite happens only after the next layer's stream synchronisation above
+    EpPlan & plan = ep_plan_;
     ep_make_plan(h_ep_offsets_, ep_world_, ep_rank_, E, plan);
     const int n_recv = plan.n_recv;
 
@@ -711,8 +713,6 @@ void Engine::ep_moe_layer(const LayerWeights & lw, int T) {
         launch_ep_scatter_rows(ep_back_.ptr, moe_sorted_.ptr, P, d, pair_y_.ptr, d, stream);
         launch_moe_combine(pair_y_.ptr, d, moe_ids_.ptr, moe_w_.ptr, K, d, T, x_.ptr, x_.ptr, stream);
     }
-    // the plan's host vectors were staged by the copies above; the next layer may reuse the buffers
-    RB_CUDA(cudaStreamSynchronize(stream));
     last_launches += 8;
 }
 
@@ -720,6 +720,7 @@ void Engine::ep_moe_layer(const LayerWeights & lw, int T) {
 void Engine::ep_idle_step() {
     if (!ep_comm_) throw std::invalid_argument("expert parallelism is not initialised for this engine");
     for (uint32_t l = 0; l < model->hp.n_layer; ++l) ep_moe_layer(model->layers[l], 0);
+    RB_CUDA(cudaStreamSynchronize(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

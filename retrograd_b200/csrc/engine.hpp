@@ -319,6 +319,7 @@ private:
     size_t moe_split_rows_ = 0;
     void * ep_comm_ = nullptr;
     int ep_rank_ = 0, ep_world_ = 1;
+    EpPlan ep_plan_;
     int32_t * h_ep_offsets_ = nullptr;        // pinned: every rank's pair offsets of the layer
     DeviceBuffer<int32_t> ep_all_offsets_, ep_offsets_l_, ep_sorted_l_;
     DeviceBuffer<float> ep_send_, ep_recv_, ep_gu_, ep_h_, ep_y_, ep_back_;

@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
                     bl[ks][1] = __byte_perm(vl.x, vl.y, 0x7632);
                 }
             }
-            if (kh == 0 && (!PACK4 || g < 4)) {
+            if (!PACK4 || g < 4) {
                 bmh = *reinterpret_cast<const uint32_t *>(X.sum_hi + (size_t)tok * n_sub + sb * 8 + 2 * tq);
                 bml = *reinterpret_cast<const uint32_t *>(X.sum_lo + (size_t)tok * n_sub + sb * 8 + 2 * tq);
             }
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
     const __half2 k1024 = __float2half2_rn(1024.f);
 
     // the unit's contribution of this warp's 128 columns: rows g / g+8 x MMA columns 2tq, 2tq+1
-    auto compute = [&](const UnitRaw & raw, float (&part)[4]) {
+    auto compute = [&](const UnitRaw & raw, int h, float (&part)[4]) {
         // The four 6-bit scales of this half (sub-blocks 4 kh .. 4 kh + 3), one per byte, unpacked with
         // byte-parallel logic; no integer-to-float conversion instructions anywhere.
         const uint32_t sc0 = kh ? ((raw.hdr0.w & 0x0F0F0F0Fu) | ((raw.hdr0.y >> 2) & 0x30303030u)) : (raw.hdr0.y & 0x3F3F3F3Fu);
@@ -179,10 +179,11 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
                 }
             }
             const float sl0 = scale_lo(sc0, 2 * j), sl1 = scale_lo(sc1, 2 * j), sh0 = scale_hi(sc0, 2 * j + 1), sh1 = scale_hi(sc1, 2 * j + 1);
-            tot[0] += sl0 * alo[0] + sh0 * ahi[0];
-            tot[1] += sl0 * alo[1] + sh0 * ahi[1];
-            tot[2] += sl1 * alo[2] + sh1 * ahi[2];
-            tot[3] += sl1 * alo[3] + sh1 * ahi[3];
+            // two fused multiply-adds per result (not a product, a fused multiply-add and an addition)
+            tot[0] = fmaf(sh0, ahi[0], fmaf(sl0, alo[0], tot[0]));
+            tot[1] = fmaf(sh0, ahi[1], fmaf(sl0, alo[1], tot[1]));
+            tot[2] = fmaf(sh1, ahi[2], fmaf(sl1, alo[2], tot[2]));
+            tot[3] = fmaf(sh1, ahi[3], fmaf(sl1, alo[3], tot[3]));
         }
         const __half2 dd0 = *reinterpret_cast<const __half2 *>(&raw.hdr0.x), dd1 = *reinterpret_cast<const __half2 *>(&raw.hdr1.x);
         const float d0 = __low2float(dd0) * 16777216.f, d1 = __low2float(dd1) * 16777216.f;      // undoes the 2^-24 of the nibbles
@@ -190,8 +191,9 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
         part[1] = d0 * tot[1];
         part[2] = d1 * tot[2];
         part[3] = d1 * tot[3];
-        if (kh == 0) {
-            // minimum term of the whole super-block: A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]
+        if (kh == h) {
+            // minimum term of the whole super-block: A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]. Both
+            // warps of the super-block hold the headers; each takes it for one of the unit's two 16-row halves.
             const uint32_t mnA0 = raw.hdr0.z & 0x3F3F3F3Fu, mnB0 = ((raw.hdr0.w >> 4) & 0x0F0F0F0Fu) | ((raw.hdr0.z >> 2) & 0x30303030u);
             const uint32_t mnA1 = raw.hdr1.z & 0x3F3F3F3Fu, mnB1 = ((raw.hdr1.w >> 4) & 0x0F0F0F0Fu) | ((raw.hdr1.z >> 2) & 0x30303030u);
             const uint32_t v0 = __byte_perm(min_upper ? mnB0 : mnA0, 0x64646464u, min_sel);
@@ -225,7 +227,7 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
                 if (work && alive) {
                     UnitRaw raw;
                     read_stage(stage, h, raw);
-                    compute(raw, part);
+                    compute(raw, h, part);
                 }
                 *reinterpret_cast<float4 *>(&red[(((buf * UB + j) * 2 + h) * NWARP + warp) * 128 + lane * 4]) = make_float4(part[0], part[1], part[2], part[3]);
             }
