@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
             // group j of the half: sub-block 2j in the low nibbles, 2j + 1 in the high nibbles. The MMA's
             // weight operand is the masked nibble itself: as an f16 bit pattern q in bits 0..3 is the
             // subnormal q * 2^-24 and q in bits 4..7 is 16 q * 2^-24, both exact.
-            float alo[4] = {0.f, 0.f, 0.f, 0.f}, ahi[4] = {0.f, 0.f, 0.f, 0.f};
+            float alo[4], ahi[4];
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const uint32_t wa = hh ? raw.q0[j].y : raw.q0[j].x, wb = hh ? raw.q1[j].y : raw.q1[j].x;     // rows g, g + 8
@@ -171,8 +171,13 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
                 const uint32_t l0 = wa & 0x000F000Fu, l1 = wb & 0x000F000Fu, l2 = ua & 0x000F000Fu, l3 = ub & 0x000F000Fu;
                 const uint32_t h0 = wa & 0x00F000F0u, h1 = wb & 0x00F000F0u, h2 = ua & 0x00F000F0u, h3 = ub & 0x00F000F0u;
                 const int ks_lo = 4 * j + hh, ks_hi = 4 * j + 2 + hh;
-                mma_f16(alo, l0, l1, l2, l3, bh[ks_lo][0], bh[ks_lo][1]);
-                mma_f16(ahi, h0, h1, h2, h3, bh[ks_hi][0], bh[ks_hi][1]);
+                if (hh == 0) {
+                    mma_f16_first(alo, l0, l1, l2, l3, bh[ks_lo][0], bh[ks_lo][1]);
+                    mma_f16_first(ahi, h0, h1, h2, h3, bh[ks_hi][0], bh[ks_hi][1]);
+                } else {
+                    mma_f16(alo, l0, l1, l2, l3, bh[ks_lo][0], bh[ks_lo][1]);
+                    mma_f16(ahi, h0, h1, h2, h3, bh[ks_hi][0], bh[ks_hi][1]);
+                }
                 if (!PACK4) {
                     mma_f16(alo, l0, l1, l2, l3, bl[ks_lo][0], bl[ks_lo][1]);
                     mma_f16(ahi, h0, h1, h2, h3, bl[ks_hi][0], bl[ks_hi][1]);
@@ -200,8 +205,8 @@ __global__ void __launch_bounds__(STHREADS, 1) gemm_q4k_stream_kernel(const uint
             const uint32_t v1 = __byte_perm(min_upper ? mnB1 : mnA1, 0x64646464u, min_sel);
             const __half2 h0 = __hsub2(*reinterpret_cast<const __half2 *>(&v0), k1024), h1 = __hsub2(*reinterpret_cast<const __half2 *>(&v1), k1024);
             const uint32_t am0 = *reinterpret_cast<const uint32_t *>(&h0), am1 = *reinterpret_cast<const uint32_t *>(&h1);
-            float tmin[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_f16(tmin, am0, am1, am0, am1, bmh, bml);
+            float tmin[4];
+            mma_f16_first(tmin, am0, am1, am0, am1, bmh, bml);
             const float dm0 = __high2float(dd0), dm1 = __high2float(dd1);
             part[0] -= dm0 * tmin[0];
             part[1] -= dm0 * tmin[1];
