@@ -24,7 +24,8 @@ constexpr int STAGES = 3;
 constexpr int THREADS = 256;
 
 struct Fetch {
-    uint16_t w[17];             // d, then 32 int8 as 16 pairs
+    uint32_t w[9];              // nine words covering the thread's 34-byte block (d, then 32 int8), which starts at
+                                // halfword 0 (first block of the stage) or halfword 1 (second block) of the window
 };
 
 template <int BN, bool RESIDUAL>
@@ -69,24 +70,32 @@ __global__ void __launch_bounds__(THREADS) gemm_q8_0_exact_kernel(const uint8_t 
 
     auto fetch_a = [&](int kt, Fetch & f) {
         if (!a_valid) return;
-        const uint16_t * blk = reinterpret_cast<const uint16_t *>(a_base + (size_t)(kt * 2 + a_half) * 34);
+        // a stage's two blocks of a row are 68 consecutive bytes starting on a 4-byte boundary (rows are whole
+        // pairs of blocks): the first block is words 0..8, the second the upper half of word 8 and words 9..16
+        const uint32_t * seg = reinterpret_cast<const uint32_t *>(a_base + (size_t)kt * 68) + a_half * 8;
 #pragma unroll
-        for (int i = 0; i < 17; ++i) f.w[i] = blk[i];
+        for (int i = 0; i < 9; ++i) f.w[i] = seg[i];
     };
     auto store_a = [&](int stage, const Fetch & f) {
         uint8_t * a_s = smem + stage * STAGE_BYTES;
         uint4 out[4];
         float d = 0.f;
         if (a_valid) {
-            const __half dh = __ushort_as_half(f.w[0]);
+            // the block's halfwords 2m, 2m + 1 as one word, whichever half of the window it starts in
+            uint32_t p[9];
+#pragma unroll
+            for (int m = 0; m < 8; ++m) p[m] = __funnelshift_r(f.w[m], f.w[m + 1], 16 * a_half);
+            p[8] = f.w[8] >> (16 * a_half);
+            const __half dh = __ushort_as_half((unsigned short)(p[0] & 0xFFFFu));
             d = __half2float(dh);
             const __half2 k1152 = __float2half2_rn(1152.f);
             uint32_t o[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 // bytes (q0, q1) -> (q0 + 128, q1 + 128) under the f16 exponent pattern 0x64 = 1024 + byte; minus 1152
-                const uint32_t u = (uint32_t)f.w[1 + i] ^ 0x8080u;
-                const uint32_t v = __byte_perm(u, 0x64646464u, 0x4140);
+                const int j = 1 + i;                                   // halfword of the block
+                const uint32_t u = p[j >> 1] ^ 0x80808080u;
+                const uint32_t v = __byte_perm(u, 0x64646464u, (j & 1) ? 0x4342 : 0x4140);
                 const __half2 h = __hsub2(*reinterpret_cast<const __half2 *>(&v), k1152);
                 o[i] = *reinterpret_cast<const uint32_t *>(&h);
             }
@@ -239,7 +248,9 @@ void launch_bn(const WeightView & w, const SplitAct & x, int T, float * y, int l
 } // namespace
 
 bool gemm_q8_0_exact_supported(const WeightView & w, const SplitAct & x) {
-    return w.type == GGML_Q8_0 && w.n_in % 64 == 0 && x.hi && x.ld == (int)w.n_in;
+    // rows of whole block pairs on 4-byte boundaries: the weight loads are 32-bit
+    return w.type == GGML_Q8_0 && w.n_in % 64 == 0 && x.hi && x.ld == (int)w.n_in && w.row_bytes % 4 == 0 &&
+           (reinterpret_cast<uintptr_t>(w.data) & 3) == 0;
 }
 
 void launch_gemm_q8_0_exact_grouped(const WeightView & w, uint64_t group_stride_bytes, int n_groups, const int32_t * group_offsets, const SplitAct & x,

@@ -8,6 +8,7 @@
 #include "blocks.hpp"
 #include "split_emit.cuh"
 
+#include <algorithm>
 #include <cfloat>
 #include <type_traits>
 
@@ -288,15 +289,16 @@ __global__ void rms_norm4_kernel(const float * __restrict__ x, int ldx, const in
     }
 }
 
-// One warp per output row, eight tokens per pass.
+// One warp per output row and group of eight tokens: grid (token groups, row blocks) - the token group is
+// the fastest grid dimension, so the CTAs that decode the same rows run together and share them in L2.
 template <uint32_t TYPE>
 __global__ void gemm_rows_kernel(WeightView w, const float * __restrict__ x, int ldx, int n_tokens, float * __restrict__ y, int ldy,
                                  const float * __restrict__ bias, const float * __restrict__ residual, int ldr) {
     const int lane = threadIdx.x & 31;
-    const uint32_t o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t o = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (o >= w.n_out) return;
     const uint8_t * row = w.data + (size_t)o * w.row_bytes;
-    for (int t0 = 0; t0 < n_tokens; t0 += 8) {
+    for (int t0 = blockIdx.x * 8; t0 < n_tokens; t0 += gridDim.x * 8) {
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -791,9 +793,11 @@ void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const flo
 void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
                       int ldr, cudaStream_t stream) {
     const int warps = 8;
+    if (n_tokens <= 0 || w.n_out == 0) return;
     dispatch_type(w.type, [&](auto tag) {
-        gemm_rows_kernel<decltype(tag)::value><<<(w.n_out + warps - 1) / warps, warps * 32, 0, stream>>>(w, x, ldx, n_tokens, y, ldy, bias,
-                                                                                                       residual, ldr);
+        // the kernel strides over token groups, so a capped grid.x still covers every token
+        const dim3 grid(std::min((n_tokens + 7) / 8, 1024), (w.n_out + warps - 1) / warps);
+        gemm_rows_kernel<decltype(tag)::value><<<grid, warps * 32, 0, stream>>>(w, x, ldx, n_tokens, y, ldy, bias, residual, ldr);
     });
 }
 
