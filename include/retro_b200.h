@@ -302,6 +302,10 @@ int retro_b200_nccl_unique_id(void * out_id_128);
  * block scales an f16 holds are re-coded, exactly, as Q8_0 at load (type 8) so that the tensor-core GEMM
  * serves them; RB200_MOE=rows keeps them MXFP4 (type 39) on the CUDA-core row kernel. */
 int retro_b200_engine_expert_storage(retro_engine * engine, int layer, uint32_t * out_types_3);
+/* The load-time re-coding itself (host only, no GPU): n_blocks MXFP4 blocks (17 B each) -> Q8_0 blocks
+ * (34 B each) holding the same values; *out_recoded = 0 and nothing written when a block's scale is not
+ * a power of two an f16 holds (2^-24 .. 2^15). */
+int retro_b200_recode_mxfp4_as_q8_0(const void * mxfp4, size_t n_blocks, void * out_q8_0, int * out_recoded);
 int retro_b200_engine_ep_init(retro_engine * engine, int rank, int world, const void * unique_id_128);
 int retro_b200_engine_ep_idle_step(retro_engine * engine);
 int retro_b200_ep_plan(const int32_t * all_offsets, int world, int rank, int n_expert, int32_t * send_begin, int32_t * send_count,

@@ -21,6 +21,7 @@ from .engine import (
     nccl_unique_id,
     op_gemm,
     quantize_row,
+    recode_mxfp4_as_q8_0,
     synth_gguf,
 )
 
@@ -40,5 +41,6 @@ __all__ = [
     "nccl_unique_id",
     "op_gemm",
     "quantize_row",
+    "recode_mxfp4_as_q8_0",
     "synth_gguf",
 ]

@@ -184,6 +184,7 @@ SYMBOLS = {
     "retro_b200_engine_graph_stats": (C.c_int, [C.c_void_p, _P(C.c_uint64), _P(C.c_uint64)]),
     "retro_b200_nccl_unique_id": (C.c_int, [C.c_void_p]),
     "retro_b200_engine_expert_storage": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_uint32)]),
+    "retro_b200_recode_mxfp4_as_q8_0": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, _P(C.c_int)]),
     "retro_b200_engine_ep_init": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     "retro_b200_engine_ep_idle_step": (C.c_int, [C.c_void_p]),
     "retro_b200_ep_plan": (C.c_int, [_P(C.c_int32), C.c_int, C.c_int, C.c_int, _P(C.c_int32), _P(C.c_int32), _P(C.c_int32), _P(C.c_int32),

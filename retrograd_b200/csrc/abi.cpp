@@ -973,6 +973,16 @@ int invalid(const std::string & message) {
 }
 } // namespace
 
+int retro_b200_recode_mxfp4_as_q8_0(const void * mxfp4, size_t n_blocks, void * out_q8_0, int * out_recoded) {
+    return boundary([&]() -> int {
+        if (!mxfp4 || !out_q8_0 || !out_recoded) return invalid("retro_b200_recode_mxfp4_as_q8_0: null argument");
+        std::vector<uint8_t> out;
+        *out_recoded = mxfp4_to_q8_0(mxfp4, n_blocks * 17, out) ? 1 : 0;
+        if (*out_recoded) std::memcpy(out_q8_0, out.data(), out.size());
+        return STATUS_OK;
+    });
+}
+
 int retro_b200_engine_expert_storage(retro_engine * engine, int layer, uint32_t * out_types_3) {
     return boundary([&]() -> int {
         Engine * e = checked(engine);

@@ -38,8 +38,6 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // ---------------------------------------------------------------------------------------------
 // Model load
 
-namespace {
-
 // MXFP4 blocks (E8M0 byte + 16 bytes of nibbles; element i in the low nibble of byte i, element 16 + i in
 // its high nibble) -> Q8_0 blocks (f16 d + 32 int8) of the same values: d = 2^(x - 128) is half the E8M0
 // scale, the int8 is the doubled E2M1 value. False when a block's scale is outside what an f16 holds.
@@ -71,8 +69,6 @@ bool mxfp4_to_q8_0(const void * src, size_t bytes, std::vector<uint8_t> & out) {
     }
     return true;
 }
-
-} // namespace
 
 void Engine::load_model(const std::string & path) {
     if (const char * env = std::getenv("RB200_MOE")) moe_tensor_cores_ = std::string(env) != "rows";

@@ -117,6 +117,9 @@ struct SplitBuffer {
     const SplitAct * get() const { return view.hi ? &view : nullptr; }
 };
 
+// MXFP4 blocks re-coded as Q8_0 blocks of the same values (see engine.cu); false when a block scale does not fit an f16.
+bool mxfp4_to_q8_0(const void * src, size_t bytes, std::vector<uint8_t> & out);
+
 struct HParams {
     std::string arch;
     uint32_t n_layer = 0, d = 0, n_head = 0, n_head_kv = 0, head_dim = 0, ff = 0, vocab = 0;

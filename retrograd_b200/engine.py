@@ -206,6 +206,17 @@ def op_gemm(ggml_type: int, w_bytes, n_out: int, n_in: int, x, path: int = 0, it
     return y, ms.value
 
 
+def recode_mxfp4_as_q8_0(blocks: bytes) -> bytes | None:
+    """MXFP4 blocks (17 B each) as Q8_0 blocks (34 B each) of the same values, as the engine does with expert
+    banks at load; None when a block's scale is outside what an f16 holds. Host arithmetic only."""
+    n = len(blocks) // 17
+    src = C.create_string_buffer(bytes(blocks), len(blocks))
+    dst = C.create_string_buffer(max(n * 34, 1))
+    ok = C.c_int()
+    _check(_ffi.load_library().retro_b200_recode_mxfp4_as_q8_0(src, n, dst, C.byref(ok)))
+    return dst.raw[: n * 34] if ok.value else None
+
+
 def nccl_unique_id() -> bytes:
     """The 128-byte NCCL id one rank creates and every rank passes to Engine.ep_init."""
     buf = C.create_string_buffer(128)

@@ -4,6 +4,7 @@ import re
 import subprocess
 from pathlib import Path
 
+import numpy as np
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
@@ -117,3 +118,23 @@ def test_kv_bookkeeping(tmp_path):
     subprocess.run(["g++", "-std=c++17", "-O1", "-o", str(exe), str(ROOT / "tests" / "cpp" / "kv_manager_test.cpp")], check=True)
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0, out.stderr
+
+
+def test_mxfp4_expert_blocks_recode_exactly_as_q8_0(rb, oracle):
+    """The engine holds MXFP4 expert banks as Q8_0 for the tensor cores: the doubled E2M1 value as the int8,
+    half the E8M0 scale as the f16 d. Every value must decode to the same f32; a scale an f16 cannot hold
+    (below 2^-24 or above 2^15) refuses the whole tensor."""
+    rng = np.random.default_rng(17)
+    n_blocks = 4096
+    blocks = rng.integers(0, 256, (n_blocks, 17), dtype=np.uint8)
+    blocks[:, 0] = rng.integers(104, 144, n_blocks)          # scales 2^-24 .. 2^15 after halving, subnormal f16 included
+    blocks[:40, 0] = np.arange(104, 144)                       # every admissible scale at least once
+    raw = blocks.tobytes()
+    recoded = rb.recode_mxfp4_as_q8_0(raw)
+    assert recoded is not None and len(recoded) == n_blocks * 34
+    want = oracle.dequantize_row(oracle.T_MXFP4, raw, n_blocks * 32)
+    got = oracle.dequantize_row(oracle.T_Q8_0, recoded, n_blocks * 32)
+    assert np.array_equal(want, got)
+    for bad in (0, 1, 103, 144, 255):
+        blocks[7, 0] = bad
+        assert rb.recode_mxfp4_as_q8_0(blocks.tobytes()) is None
