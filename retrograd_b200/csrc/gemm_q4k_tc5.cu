@@ -82,7 +82,10 @@ __global__ void q4k_retile_kernel(const uint8_t * __restrict__ rows, uint32_t n_
     }
 }
 
-template <bool RESIDUAL>
+// SPLIT: the split-K form (blockIdx.z ranges over the reduction, results go to `partial`); a separate
+// instantiation, so that the plain form keeps exactly the code it had before the split form existed
+// (sharing one body cost the plain form 10 % in the engine).
+template <bool RESIDUAL, bool SPLIT>
 __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes,
                                                                   const __grid_constant__ SplitAct X, int T, float * __restrict__ Y, int ldy, const float * __restrict__ bias,
                                                                   const float * __restrict__ residual, int ldr, int * __restrict__ error_flag,
@@ -104,8 +107,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
     const int m0 = blockIdx.y * BM, t0 = blockIdx.x * BN;   // token tiles vary fastest: CTAs in flight share a weight tile in L2
     // split-K: blockIdx.z owns super-blocks [sb0, sb0 + n_sb) of the row and writes a partial result
     const int n_sb_all = n_in / 256;
-    const int sb0 = blockIdx.z * sb_per_split;
-    const int n_sb = min(n_sb_all, sb0 + sb_per_split) - sb0;
+    const int sb0 = SPLIT ? blockIdx.z * sb_per_split : 0;
+    const int n_sb = SPLIT ? min(n_sb_all, sb0 + sb_per_split) - sb0 : n_sb_all;
     const int n_it = n_sb * 5;
     const int n_sub = n_in / 32;
 
@@ -322,7 +325,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
             for (int i = 0; i < 64; ++i) {
                 const int t = t0 + colhalf * 64 + i;
                 if (t < T) {
-                    if (partial) {
+                    if (SPLIT) {
                         partial[((size_t)blockIdx.z * T + t) * n_out + o] = acc[i];      // bias and residual are added by the finish kernel
                     } else {
                         float v = acc[i] + b;
@@ -389,8 +392,9 @@ void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens,
                          const FinishTail * tail) {
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(gemm_q4k_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        cudaFuncSetAttribute(gemm_q4k_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_q4k_tc5_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_q4k_tc5_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_q4k_tc5_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         configured = true;
     }
     // few output tiles (few tokens and few rows): cut the reduction into splits of whole super-blocks so the
@@ -414,12 +418,16 @@ void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens,
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const float * no_residual = nullptr;
-    if (residual) {
-        cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<true>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias, residual, ldr,
-                           error_flag, sb_per_split, partial);
+    if (splits > 1) {
+        // bias and residual are the finish kernel's
+        cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<false, true>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
+                           no_residual, 0, error_flag, sb_per_split, partial);
+    } else if (residual) {
+        cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<true, false>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias, residual,
+                           ldr, error_flag, sb_per_split, partial);
     } else {
-        cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<false>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias, no_residual, 0,
-                           error_flag, sb_per_split, partial);
+        cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<false, false>, w.tiled, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, n_tokens, y, ldy, bias,
+                           no_residual, 0, error_flag, sb_per_split, partial);
     }
     if (splits > 1) launch_gemm_stream_finish(scratch, splits, (int)w.n_out, n_tokens, n_tokens, y, ldy, bias, residual, ldr, stream, tail);
 }

@@ -1,6 +1,8 @@
 // Device-side views and launch wrappers of the decode step's kernels.
 #pragma once
 
+#include <cstdlib>
+
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -48,6 +50,15 @@ void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
 
+// RB200_PDL=0: the kernels launched through launch_pdl() are serialised like plain launches.
+inline bool pdl_enabled() {
+    static const bool on = [] {
+        const char * env = std::getenv("RB200_PDL");
+        return !(env && env[0] == '0');
+    }();
+    return on;
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&... args) {
     cudaLaunchConfig_t cfg = {};
@@ -59,7 +70,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #endif
