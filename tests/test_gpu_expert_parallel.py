@@ -78,7 +78,10 @@ def _rank_main(rank: int, world: int, workdir: Path) -> None:
 
 
 @pytest.mark.gpu
-def test_two_ranks_with_half_the_experts_each_equal_the_plain_engine(tmp_path):
+@pytest.mark.parametrize("experts", ["tensor_cores", "rows"])
+def test_two_ranks_with_half_the_experts_each_equal_the_plain_engine(tmp_path, experts):
+    """Both forms of the expert FFN: banks re-coded for the grouped tensor-core GEMM, and (RB200_MOE=rows)
+    the MXFP4 bytes on the CUDA-core grouped kernel."""
     import torch
 
     if torch.cuda.device_count() < 2:
@@ -86,6 +89,10 @@ def test_two_ranks_with_half_the_experts_each_equal_the_plain_engine(tmp_path):
     procs = []
     for rank in range(2):
         env = dict(os.environ, CUDA_VISIBLE_DEVICES=str(rank), NCCL_NVLS_ENABLE="0")
+        if experts == "rows":
+            env["RB200_MOE"] = "rows"
+        else:
+            env.pop("RB200_MOE", None)
         procs.append(subprocess.Popen([sys.executable, __file__, str(rank), "2", str(tmp_path)], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
     outputs = []
