@@ -1078,7 +1078,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     // few small items: cut each sequence's KV blocks over several CTAs so the GPU is still full
     int attn_splits = 1;
     if (n_small_items > 0) {
-        const int want = (2 * n_sm_ + n_small_items * (int)hp.n_head_kv - 1) / (n_small_items * (int)hp.n_head_kv);
+        // two CTAs of the split-KV kernel fit an SM (shared memory): as many splits as keep the grid within one
+        // wave - rounding up left a second, nearly empty wave (16 requests: 384 CTAs on 296 places, 6.0 -> 5.7 ms per step)
+        const int want = (2 * n_sm_) / (n_small_items * (int)hp.n_head_kv);
         attn_splits = std::max(1, std::min({want, attention_decode8_max_splits(), (max_ctx / (int)kBlockTokens) / 8}));
         if (attn_splits > 1)
             attn_scratch_.ensure(attention_decode8_scratch_floats(n_attn_items, (int)hp.n_head_kv, attn_splits, (int)hp.head_dim));
