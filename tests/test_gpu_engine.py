@@ -437,3 +437,61 @@ def test_batched_generator_validation(rb, pair):
         engine.generate_continuous([], 4)
     with pytest.raises(rb.EngineError, match="invalid continuous generation prompt"):
         engine.generate_continuous([([], good)], 4)
+
+
+def test_scheduler_composed_steps_reproduce_the_generators(rb, pair):
+    """Plans composed the way the reference's scheduler does (retrograd_b200/scheduler.py): a merged group of
+    three members (leader prefill of all but the last prompt token, prefix copied to the members, one terminal
+    row each, then decode) beside two single requests, under continuous admission with a budget small
+    enough that prefill is chunked, a token is kept for it, and the decode cursor rotates. Every request's
+    greedy stream must equal what the engine's own generators produce for it."""
+    from retrograd_b200.scheduler import CONTINUOUS, ComposeState, Group, Member, compose
+
+    engine, _ = pair
+    n_new = 5
+    greedy = rb.SamplingParamsV2.greedy()
+    shared = _prompt(500, 23)
+    singles = [_prompt(501, 17), _prompt(502, 9)]
+    want_shared, _ = engine.generate_batch(shared, [rb.SamplingParams(**_greedy_v1(n_new, seed=s)) for s in range(3)], n_out_max=n_new)
+    want_single, _ = engine.generate_continuous([(p, rb.SamplingParams(**_greedy_v1(n_new))) for p in singles], n_out_max=n_new)
+
+    live = [Group(prompt=shared, members=[Member(request_id=10 + i, slot=i, sampling=greedy) for i in range(3)], prefix_end=len(shared) - 1)]
+    live += [Group(prompt=p, members=[Member(request_id=20 + i, slot=3 + i, sampling=greedy)], prefix_end=len(p)) for i, p in enumerate(singles)]
+    streams = {m.request_id: [] for g in live for m in g.members}
+    state, out = ComposeState(), rb.StepOutput()
+    for _ in range(200):
+        if all(not m.live for g in live for m in g.members):
+            break
+        rows, used = compose(live, 6, CONTINUOUS, state)
+        assert 0 < used <= 6
+        engine.step([rb.StepRow(r.request, r.slot, r.tokens, r.pos0, r.sample, r.sampling) for r in rows], out)
+        for i, r in enumerate(rows):
+            g = live[r.kind[1]]
+            if r.kind[0] == "prefill":
+                g.pos = r.kind[2]
+                member = g.members[0] if r.kind[3] is not None else None
+            else:
+                member = g.members[r.kind[2]]
+                if r.kind[0] == "terminal":
+                    g.next_member = r.kind[2] + 1
+            if member is not None:
+                tok = out.row(i).token
+                streams[member.request_id].append(tok)
+                member.next_token, member.generated = tok, member.generated + 1
+                if member.generated >= n_new:
+                    member.live = False
+                    engine.seq_rm(member.slot)
+        # phase changes between steps: a finished prefix is copied to the other members; a finished terminal wave decodes
+        for g in live:
+            if g.phase == "prefill" and g.pos == g.prefix_end:
+                if len(g.members) > 1:
+                    for m in g.members[1:]:
+                        engine.seq_cp(g.members[0].slot, m.slot, 0, g.prefix_end)
+                    g.phase = "terminal"
+                else:
+                    g.phase = "decode"
+            if g.phase == "terminal" and g.next_member >= len(g.members):
+                g.phase = "decode"
+    assert [streams[10 + i] for i in range(3)] == want_shared
+    assert [streams[20 + i] for i in range(2)] == want_single
+    assert engine.memory().cells_used == 0
