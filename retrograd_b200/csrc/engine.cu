@@ -287,6 +287,10 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
         throw std::runtime_error("device=gpu requested but no GPU backend is available; this library has no CPU path");
     }
     RB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    RB_CUDA(cudaStreamCreateWithFlags(&side_stream_, cudaStreamNonBlocking));
+    RB_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
+    RB_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
+    if (const char * env = std::getenv("RB200_ATTN_OVERLAP")) attn_overlap_ = std::string(env) != "0";
     RB_CUDA(cudaEventCreate(&ev_begin_));
     RB_CUDA(cudaEventCreate(&ev_end_));
     load_model(path);
@@ -378,6 +382,9 @@ Engine::~Engine() {
     if (h_ep_offsets_) cudaFreeHost(h_ep_offsets_);
     if (h_stage_) cudaFreeHost(h_stage_);
     if (h_result_) cudaFreeHost(h_result_);
+    if (ev_fork_) cudaEventDestroy(ev_fork_);
+    if (ev_join_) cudaEventDestroy(ev_join_);
+    if (side_stream_) cudaStreamDestroy(side_stream_);
     if (ev_begin_) cudaEventDestroy(ev_begin_);
     if (ev_end_) cudaEventDestroy(ev_end_);
     if (stream) cudaStreamDestroy(stream);
@@ -1162,14 +1169,27 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             // every row of the step goes through the split-KV kernel: its merge writes the split form as well
             const bool merge_splits = fused_finish_ && att_split_.get() && !any_wide_item && !any_mid_item && n_small_items && attn_splits > 1 &&
                                       hp.head_dim % 32 == 0;
+            // Decode rows (HBM-bound, many small CTAs) and prefill tiles (tensor-bound, one CTA per SM and a ragged
+            // last wave) touch disjoint rows: with both in a step the decode kernel runs on a second stream
+            // beside the tile kernel and fills the SMs its tail leaves idle.
+            const bool overlap = attn_overlap_ && any_wide_item && n_small_items > 0;
+            cudaStream_t small_stream = overlap ? side_stream_ : stream;
             RB_K(K_ATTN, (any_wide_item ? 1 : 0) + (any_mid_item ? 1 : 0) + (n_small_items ? (attn_splits > 1 ? 2 : 1) : 0),
+                 if (overlap) {
+                     RB_CUDA(cudaEventRecord(ev_fork_, stream));
+                     RB_CUDA(cudaStreamWaitEvent(side_stream_, ev_fork_, 0));
+                     launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot, maps.tok_pos,
+                                              maps.tok_pos_min, att_.ptr, dq, attn_splits, attn_scratch_.ptr, small_stream, nullptr);
+                     RB_CUDA(cudaEventRecord(ev_join_, side_stream_));
+                 }
                  if (any_wide_item) launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
                                                          maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, true, stream);
                  if (any_mid_item) launch_attention_decode(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot,
                                                            maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, use_decode8 ? 8 : 0, stream);
-                 if (n_small_items) launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
-                                                             maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, attn_splits,
-                                                             attn_scratch_.ptr, stream, merge_splits ? att_split_.get() : nullptr));
+                 if (n_small_items && !overlap) launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
+                                                                         maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, attn_splits,
+                                                                         attn_scratch_.ptr, stream, merge_splits ? att_split_.get() : nullptr);
+                 if (overlap) RB_CUDA(cudaStreamWaitEvent(stream, ev_join_, 0)));
             if (att_split_.get() && !merge_splits) RB_K(K_OTHER, 1, launch_split_prep(att_.ptr, dq, dq, Ti, att_split_.view, stream));
         } else {
             RB_K(K_ATTN, 1, launch_attention_ref(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_slot, maps.tok_pos, maps.tok_pos_min,

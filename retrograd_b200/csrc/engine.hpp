@@ -329,6 +329,9 @@ private:
     bool fused_finish_ = true;      // RB200_FUSED_FINISH=0: norm / SwiGLU always as kernels of their own
     SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;
     cudaEvent_t ev_begin_ = nullptr, ev_end_ = nullptr;
+    cudaStream_t side_stream_ = nullptr;                 // decode-row attention beside the prefill tiles
+    cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
+    bool attn_overlap_ = true;                           // RB200_ATTN_OVERLAP=0: every attention kernel on the step's stream
 
     std::map<int32_t, Adapter> adapters_;
     std::map<int32_t, int32_t> adapter_index_;   // id -> stack index
