@@ -495,3 +495,32 @@ def test_scheduler_composed_steps_reproduce_the_generators(rb, pair):
     assert [streams[10 + i] for i in range(3)] == want_shared
     assert [streams[20 + i] for i in range(2)] == want_single
     assert engine.memory().cells_used == 0
+
+
+def test_mixed_steps_with_the_attention_overlap_replay_as_graphs(rb, c1_model, monkeypatch):
+    """A step with decode rows and a prefill chunk forks the decode-row attention onto a second stream. The
+    same step shape repeated is captured (fork and join included) and replayed: results equal the eager run."""
+    def run(graphs: bool):
+        monkeypatch.setenv("RB200_GRAPHS", "1" if graphs else "0")
+        engine = rb.Engine(str(c1_model), rb.EngineConfig(n_ctx=2048, n_seq_max=4, n_batch=128, n_ubatch=128))
+        out = rb.StepOutput()
+        g = rb.SamplingParamsV2.greedy()
+        prompts = [_prompt(700 + i, 12 + i) for i in range(2)]
+        engine.step([rb.StepRow(i, i, p, 0, sample=True, sampling=g) for i, p in enumerate(prompts)], out)
+        last = [out.row(i).token for i in range(2)]
+        trace = []
+        for step in range(8):
+            engine.seq_rm(2)
+            rows = [rb.StepRow(i, i, [last[i]], len(prompts[i]) + step, sample=True, sampling=g, want_logprob=True) for i in range(2)]
+            rows.append(rb.StepRow(2, 2, _prompt(800 + step, 40), 0, sample=True, sampling=g, want_logprob=True))
+            engine.step(rows, out)
+            last = [out.row(i).token for i in range(2)]
+            trace.append(([out.row(i).token for i in range(3)], [out.row(i).logprob for i in range(3)], engine.last_logits(2).copy()))
+        stats = engine.graph_stats()
+        engine.close()
+        return trace, stats
+    eager, _ = run(False)
+    graphed, stats = run(True)
+    assert stats[0] >= 4
+    for (t0, l0, x0), (t1, l1, x1) in zip(eager, graphed):
+        assert t0 == t1 and l0 == l1 and np.array_equal(x0, x1)
