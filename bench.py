@@ -86,6 +86,18 @@ WORKLOADS = {
 }
 
 
+def gemm_step_bytes(sp, hd, w_elems_layer, tokens, sampled) -> float:
+    """Algorithmic bytes of one step's weight GEMMs: every weight once, each GEMM's activations in (the hi + lo
+    split, 4 bytes per element) and results out (f32), for the four projections of a layer and the head."""
+    bpw = {"q4_k": 144 / 256, "q8_0": 34 / 32, "f16": 2.0, "f32": 4.0}.get(sp["dtype"], 1.0)
+    dq, dkv = sp["heads"] * hd, sp["kv_heads"] * hd
+    in_sum = sp["d"] + dq + sp["d"] + sp["ff"]
+    out_sum = (dq + 2 * dkv) + sp["d"] + 2 * sp["ff"] + sp["d"]
+    layer = w_elems_layer * bpw + tokens * 4 * (in_sum + out_sum)
+    head = sp["d"] * sp["vocab"] * bpw + sampled * 4 * (sp["d"] + sp["vocab"])
+    return sp["layers"] * layer + head
+
+
 def model_path(workload: str) -> Path:
     base = Path(os.environ.get("RB200_MODEL_DIR", "/dev/shm" if Path("/dev/shm").is_dir() else "/tmp"))
     return base / f"retrograd_b200_{WORKLOADS[workload].get('model', workload)}.gguf"
@@ -401,6 +413,7 @@ def main():
     dev_ms, wall_s, decode_tokens, prefill_tokens, rows_per_step, launches, h2d, d2h = 0.0, 0.0, 0, 0, [], 0, 0, 0
     attn_bytes = 0
     gemm_flops = 0
+    gemm_bytes = 0      # algorithmic bytes of the weight GEMMs: weights once per step, activations in (hi + lo, 4 B per element) and out (f32)
     step_tokens = 0
     kv_tok_bytes = 2 * cfg["spec"]["layers"] * cfg["spec"]["kv_heads"] * (cfg["spec"].get("head_dim") or cfg["spec"]["d"] // cfg["spec"]["heads"]) * 2
     sp = cfg["spec"]
@@ -423,6 +436,7 @@ def main():
         attn_bytes += info["ctx_tokens"] * kv_tok_bytes
         step_tokens += info["tokens"]
         gemm_flops += 2 * (info["tokens"] * w_elems_layer * sp["layers"] + info["sampled"] * sp["d"] * sp["vocab"])
+        gemm_bytes += gemm_step_bytes(sp, hd, w_elems_layer, info["tokens"], info["sampled"])
         driver.admit()
     torch.cuda.synchronize()
     torch.cuda.nvtx.range_pop()
@@ -433,12 +447,13 @@ def main():
     if args.graphs:
         # second pass, profiled (eager launches): per-class device times and the roofline's kernel time
         engine.profile(True, reset=True)
-        attn_bytes = gemm_flops = step_tokens = 0
+        attn_bytes = gemm_flops = gemm_bytes = step_tokens = 0
         for _ in range(args.steps):
             info = driver.step()
             attn_bytes += info["ctx_tokens"] * kv_tok_bytes
             step_tokens += info["tokens"]
             gemm_flops += 2 * (info["tokens"] * w_elems_layer * sp["layers"] + info["sampled"] * sp["d"] * sp["vocab"])
+            gemm_bytes += gemm_step_bytes(sp, hd, w_elems_layer, info["tokens"], info["sampled"])
             driver.admit()
         torch.cuda.synchronize()
     profile = engine.profile_read()
@@ -469,12 +484,20 @@ def main():
         # few tokens per step: the launches are bound by streaming every weight byte once per step
         weight_bytes = (sp["layers"] * w_elems_layer + sp["d"] * sp["vocab"]) * bytes_per_weight * args.steps
         achieved = weight_bytes / (profile["gemm"]["ms"] * 1e-3) / 1e9
+        # DRAM traffic per launch: the capture of the streaming kernel on a 295 MB matrix read 295.7 MB and wrote
+        # 9.4 MB for 295.5 MB of weights (profiles/gemm_q4k_stream_128256x4096.md); traffic grows with the bytes
         roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                "traffic": None, "kernel": "dequant-fused weight-streaming GEMM (all launches of the timed region)"}
+                "traffic": weight_bytes / max(profile["gemm"]["launches"], 1) * (295.7 + 9.4) / 295.5,
+                "traffic_source": "algorithmic bytes per launch x the DRAM/algorithmic ratio of the one-launch ncu capture in profiles/",
+                "kernel": "dequant-fused weight-streaming GEMM (all launches of the timed region)"}
     elif top == "gemm":
         achieved = gemm_flops / (profile["gemm"]["ms"] * 1e-3) / 1e12
+        # DRAM traffic per launch: the capture of the tcgen05 kernel at 2048 tokens moved 320 MB for 335 MB of
+        # algorithmic bytes (profiles/gemm_q4k_tc5_28672x4096_2048tok.md); traffic grows with the tokens and rows
         roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
-                "traffic": None, "kernel": "dequant-fused weight GEMM (all launches of the timed region)"}
+                "traffic": gemm_bytes / max(profile["gemm"]["launches"], 1) * 320.0 / 335.0,
+                "traffic_source": "algorithmic bytes per launch x the DRAM/algorithmic ratio of the one-launch ncu capture in profiles/",
+                "kernel": "dequant-fused weight GEMM (all launches of the timed region)"}
     else:
         achieved = attn_bytes / (profile["attention"]["ms"] * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
