@@ -524,3 +524,50 @@ def test_mixed_steps_with_the_attention_overlap_replay_as_graphs(rb, c1_model, m
     assert stats[0] >= 4
     for (t0, l0, x0), (t1, l1, x1) in zip(eager, graphed):
         assert t0 == t1 and l0 == l1 and np.array_equal(x0, x1)
+
+
+def test_prefix_tree_hits_become_block_table_copies(rb, pair):
+    """The caller's prefix index (retrograd_b200/prefix_tree.py) and the engine together: a finished request's
+    slot stays dormant under its token path; a later prompt that shares a prefix gets `[0, hit)` by
+    `seq_cp` - an exact boundary and a mid-sequence hit - prefills only the rest, and must produce the greedy
+    stream of a cold run. The last prompt token is always prefilled (a hit is a strict prefix)."""
+    from retrograd_b200.prefix_tree import PrefixTree
+
+    engine, _ = pair
+    g = rb.SamplingParamsV2.greedy()
+    out = rb.StepOutput()
+    tree = PrefixTree()
+
+    def run(slot, prompt, n_new, hit=0):
+        engine.step([rb.StepRow(slot, slot, prompt[hit:], hit, sample=True, sampling=g)], out)
+        toks = [out.row(0).token]
+        for step in range(1, n_new):
+            engine.step([rb.StepRow(slot, slot, [toks[-1]], len(prompt) + step - 1, sample=True, sampling=g)], out)
+            toks.append(out.row(0).token)
+        return toks
+
+    base = _prompt(900, 40)
+    first = run(0, base, 4)
+    # the finished sequence: prompt + generated tokens resident in slot 0 at depth len - 1 (the last token was never fed)
+    path = base + first[:-1]
+    engine.seq_rm(0, len(path), -1)
+    node, attached = tree.insert(0, path, 0)
+    assert attached and engine.seq_pos(0) == (0, len(path) - 1)
+
+    usable = lambda n, hit: n.slot is not None and engine.seq_pos(n.slot) == (0, n.depth - 1)
+    for slot, prompt in ((1, path + _prompt(901, 6)), (2, base[:25] + _prompt(902, 9))):
+        cold = run(3, prompt, 4)
+        engine.seq_rm(3)
+        found = tree.longest_prefix(0, prompt[:-1], True, usable)       # strict prefix: the last prompt token is prefilled
+        assert found is not None
+        holder, hit = found
+        assert hit == (len(path) if slot == 1 else 25)
+        tree.touch(holder)
+        engine.seq_cp(holder.slot, slot, 0, hit)
+        assert run(slot, prompt, 4, hit=hit) == cold
+        engine.seq_rm(slot)
+    # eviction: the dormant slot is released and its node pruned
+    victim = tree.eviction_candidate()
+    engine.seq_rm(victim.slot)
+    tree.remove(victim)
+    assert tree.node_count() == 0 and engine.memory().cells_used == 0
