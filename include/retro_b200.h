@@ -268,8 +268,8 @@ int retro_b200_engine_blocks(retro_engine * engine, uint64_t * out_used, uint64_
 int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uint64_t * out_launches);
 
 /* One dequant-fused GEMM on host data: y[t][o] = sum_k deq(w)[o][k] * x[t][k] with w stored as
- * `ggml_type` rows. path: 0 engine's choice, 1 f32 row kernel, 2 single-term f16 tensor-core
- * kernel, 3 exact tensor-core kernel (mma.sync), 4 exact tcgen05 kernel, 5 exact weight-streaming
+ * `ggml_type` rows. path: 0 engine's choice, 1 f32 row kernel, 3 exact
+ * tensor-core kernel (mma.sync), 4 exact tcgen05 kernel, 5 exact weight-streaming
  * kernel (at most 8 tokens). Runs `iters` timed launches after one warm-up; *out_ms is the mean
  * device time per launch (operands smaller than 256 MB: a buffer larger than L2 is written before
  * every timed launch). */

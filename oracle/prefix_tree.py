@@ -16,6 +16,8 @@ Behaviour restated (line numbers in kv.rs):
     unpinned nodes that own a slot (or, for host bytes, only a snapshot) (:371-435).
   * `remove` drops a node's payload and prunes it and every ancestor left without children, payload and
     pins (:437-460); namespaces share nothing and can be dropped alone (:492-524).
+
+Test infrastructure, like the rest of this folder: the shipped library never imports it.
 """
 from __future__ import annotations
 

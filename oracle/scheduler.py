@@ -16,6 +16,8 @@ Rules restated (line numbers in scheduler.rs):
     prompt (:1020-1055).
   * After the prefix was copied to the members, each live member gets a terminal row: the last prompt
     token at position `len(prompt) - 1`, sampled (:1056-1083).
+
+Test infrastructure, like the rest of this folder: the shipped library never imports it.
 """
 from __future__ import annotations
 

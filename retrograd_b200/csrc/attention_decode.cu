@@ -262,10 +262,9 @@ void launch_hd(const float * qkv, int ld, int n_head, KvLayout kv, int layer, co
                const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int min_cols, cudaStream_t stream) {
     constexpr int smem = 2 * (HD / 64) * 16 * 128 + DEC_ROUNDS * 4 * 2 * (HD / 64) * 16 * 128;
     static_assert(DEC_ROUNDS * 4 * 2 * (HD / 64) * 16 * 128 >= (4 * 16 * HD + 128) * 4, "the merge buffers fit the K/V ring");
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;   // function attributes are per device
+    if (configured.first()) {
         cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured = true;
     }
     attention_decode_kernel<HD><<<dim3(n_items, kv.n_head_kv), DEC_THREADS, smem, stream>>>(qkv, ld, n_head, kv, layer, items, tok_slot, tok_pos,
                                                                                           tok_pos_min, out, ldo, min_cols);

@@ -282,10 +282,9 @@ void launch_hd8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, c
                 const SplitAct & split) {
     constexpr int smem = 4 * D8_SLOTS * 2 * (HD / 64) * 16 * 128;
     static_assert(smem >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the K/V rings");
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;   // function attributes are per device
+    if (configured.first()) {
         cudaFuncSetAttribute(attention_decode8_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured = true;
     }
     launch_pdl(attention_decode8_kernel<HD>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem, stream, qkv, ld, n_head, kv, layer, items,
                tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);

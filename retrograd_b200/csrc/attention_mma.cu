@@ -250,10 +250,9 @@ template <int HD>
 void launch_hd(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
                const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, int skip_small, cudaStream_t stream) {
     constexpr int smem = 2 * (HD / 64) * ATT_ROWS * 128 + ATT_STAGES * 2 * (HD / 64) * 16 * 128;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;   // function attributes are per device
+    if (configured.first()) {
         cudaFuncSetAttribute(attention_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured = true;
     }
     attention_mma_kernel<HD><<<dim3(n_items, kv.n_head_kv), ATT_THREADS, smem, stream>>>(qkv, ld, n_head, kv, layer, items, tok_slot, tok_pos,
                                                                                        tok_pos_min, out, ldo, skip_small);

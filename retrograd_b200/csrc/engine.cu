@@ -110,8 +110,9 @@ void Engine::load_model(const std::string & path) {
         if (!t) throw std::runtime_error("failed to load model GGUF: missing tensor " + name);
         return *t;
     };
-    auto view_of = [&](const GgufTensor & t, const uint8_t * dev, uint64_t rows) {
+    auto view_of = [&](const GgufTensor & t, const uint8_t * dev, uint64_t rows, bool min_fold) {
         WeightView w;
+        w.min_fold = min_fold;
         w.data = dev;
         w.type = t.type;
         w.n_in = (uint32_t)t.ne[0];
@@ -147,7 +148,7 @@ void Engine::load_model(const std::string & path) {
         const GgufTensor & t = need(name);
         if (t.ne.size() != 2 || t.ne[0] != n_in || t.ne[1] != n_out) throw std::runtime_error("failed to load model GGUF: unexpected shape of " + name);
         if (n_in % 8 != 0) throw std::runtime_error("failed to load model GGUF: row length of " + name + " is not a multiple of 8");
-        return view_of(t, upload(t.data, t.n_bytes), n_out);
+        return view_of(t, upload(t.data, t.n_bytes), n_out, t.type == GGML_Q4_K && n_in % 256 == 0 && q4k_min_fold_ok(t.data, t.n_bytes / 144));
     };
     auto vector_f32 = [&](const std::string & name, uint64_t n, bool optional) -> const float * {
         const GgufTensor * t = file.find(name);
@@ -173,21 +174,24 @@ void Engine::load_model(const std::string & path) {
         m.allocations.push_back(p);
         size_t off = 0;
         uint64_t rows = 0;
+        bool min_fold = type == GGML_Q4_K && n_in % 256 == 0;
         for (size_t i = 0; i < names.size(); ++i) {
             const GgufTensor & t = need(names[i]);
+            min_fold = min_fold && q4k_min_fold_ok(t.data, t.n_bytes / 144);
             RB_CUDA(cudaMemcpy(static_cast<uint8_t *>(p) + off, t.data, t.n_bytes, cudaMemcpyHostToDevice));
             off += t.n_bytes;
             rows += n_out[i];
         }
         m.weight_bytes += total;
-        out = view_of(need(names[0]), static_cast<uint8_t *>(p), rows);
+        out = view_of(need(names[0]), static_cast<uint8_t *>(p), rows, min_fold);
         return true;
     };
 
     const GgufTensor & embd = need("token_embd.weight");
     hp.vocab = (uint32_t)embd.ne[1];
     if (embd.ne[0] != hp.d) throw std::runtime_error("failed to load model GGUF: token_embd width differs from embedding_length");
-    m.token_embd = view_of(embd, upload(embd.data, embd.n_bytes), hp.vocab);
+    m.token_embd = view_of(embd, upload(embd.data, embd.n_bytes), hp.vocab,
+                           embd.type == GGML_Q4_K && hp.d % 256 == 0 && q4k_min_fold_ok(embd.data, embd.n_bytes / 144));
 
     const uint64_t dq = hp.dq(), dkv = hp.dkv();
     m.layers.resize(hp.n_layer);
@@ -243,7 +247,7 @@ void Engine::load_model(const std::string & path) {
                     w.n_out = (uint32_t)n_out;
                     w.row_bytes = (uint32_t)row_bytes(GGML_Q8_0, n_in);
                 } else {
-                    w = view_of(t, upload(t.data, t.n_bytes), n_out);
+                    w = view_of(t, upload(t.data, t.n_bytes), n_out, false);
                 }
                 stride = (uint64_t)w.row_bytes * n_out;
             };
@@ -306,8 +310,6 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     vcache_.ensure(kv_layer_stride_ * hp.n_layer);
     // Cells past a sequence's end in its last block are read (and masked) by the attention kernels:
     // a masked probability of zero times a leftover NaN bit pattern would still be NaN.
-    RB_CUDA(cudaMemset(kcache_.ptr, 0, kv_layer_stride_ * hp.n_layer * sizeof(*kcache_.ptr)));
-    RB_CUDA(cudaMemset(vcache_.ptr, 0, kv_layer_stride_ * hp.n_layer * sizeof(*vcache_.ptr)));
     RB_CUDA(cudaMemsetAsync(kcache_.ptr, 0, kcache_.count * sizeof(__half), stream));
     RB_CUDA(cudaMemsetAsync(vcache_.ptr, 0, vcache_.count * sizeof(__half), stream));
     block_table_.ensure((size_t)config.n_seq_max * max_blocks);
@@ -340,7 +342,6 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     att_split_.ensure(T, hp.dq());
     if (hp.n_expert == 0) hff_split_.ensure(T, hp.ff);
     if (const char * env = std::getenv("RB200_GEMM")) {
-        gemm_fast_f16 = std::string(env) == "fast";
         if (std::string(env) == "mma") tc5_min_tokens = 1 << 30;     // keep the mma.sync kernels for every token count
     }
     {
@@ -433,9 +434,7 @@ bool Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
                     int ldr, const SplitAct * xs, const FinishTail * tail) {
     bool tail_done = false;
     prof_.begin(K_GEMM, stream);
-    if (xs && T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) {
-        launch_gemm_mma(w, xs->hi, ldx, T, y, ldy, bias, residual, ldr, stream);
-    } else if (xs && stream_gemm_ && T <= kStreamMaxTokens && !tc5_split_preferred(w, T, xs) &&
+    if (xs && stream_gemm_ && T <= kStreamMaxTokens && !tc5_split_preferred(w, T, xs) &&
                (gemm_q4k_stream_supported(w, *xs, std::min(T, 8)) || gemm_q8_0_stream_supported(w, *xs, std::min(T, 8)))) {
         // at most 8 tokens per pass of the weight stream; up to 16 tokens two passes still beat the tensor-core kernels
         stream_scratch_.ensure(gemm_q4k_stream_scratch_floats(w.n_out, w.n_in));
@@ -567,7 +566,6 @@ void Engine::run_step_work(const std::vector<uint64_t> & sig, const std::functio
 // (then the f32 copy of the activations need not be written at all).
 bool Engine::linear_reads_split(const WeightView & w, int ldx, int T, const SplitAct * xs) const {
     if (!xs) return false;
-    if (T > mma_min_tokens && gemm_fast_f16 && gemm_mma_supported(w, ldx) && xs->ld == ldx) return true;
     if (stream_gemm_ && T <= kStreamMaxTokens &&
         (gemm_q4k_stream_supported(w, *xs, std::min(T, 8)) || gemm_q8_0_stream_supported(w, *xs, std::min(T, 8))))
         return true;

@@ -243,7 +243,6 @@ public:
     // steps with more tokens than this take the tensor-core GEMM (f16 operands); fewer take the f32 row kernel
     int mma_min_tokens = 8;
     int tc5_min_tokens = 16;      // above this the tcgen05 kernel (128-token tiles) takes over; measured faster than mma.sync from 17 tokens on
-    bool gemm_fast_f16 = false;   // opt-in single-term f16 operands: faster, outside the 1e-2 logit tolerance on deep models
     uint64_t last_h2d_bytes = 0, last_d2h_bytes = 0;
     StepProfiler prof_;
     uint64_t graphs_reused = 0;

@@ -264,10 +264,9 @@ template <int BN, bool RESIDUAL>
 void launch_one(const WeightView & w, const SplitAct & x, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
                 cudaStream_t stream) {
     constexpr int smem = STAGES * (BM * 128 + 2 * BN * 128) + 2 * BM * (int)sizeof(float2) + 2 * BM * 8 * (int)sizeof(__half);
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;   // function attributes are per device
+    if (configured.first()) {
         cudaFuncSetAttribute(gemm_q4k_exact_kernel<BN, RESIDUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured = true;
     }
     const dim3 grid((w.n_out + BM - 1) / BM, (T + BN - 1) / BN);
     gemm_q4k_exact_kernel<BN, RESIDUAL><<<grid, THREADS, smem, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, T, y, ldy, bias,

@@ -300,11 +300,10 @@ void launch_gemm_q4k_stream(const WeightView & w, const SplitAct & x, int n_toke
     const int n_sb = (int)w.n_in / 256;
     const int n_chunks = (n_sb + SW - 1) / SW;
     const int n_units = ((int)w.n_out + 31) / 32;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;   // function attributes are per device
+    if (configured.first()) {
         cudaFuncSetAttribute(gemm_q4k_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaFuncSetAttribute(gemm_q4k_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        configured = true;
     }
     // one CTA per SM in total
     int ctas_x = max(1, n_sm / n_chunks);

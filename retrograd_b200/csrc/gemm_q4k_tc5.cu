@@ -1,29 +1,41 @@
 // Dequant-fused Q4_K weight GEMM on the 5th-generation tensor cores (tcgen05, accumulators in
-// tensor memory), with the same exact arithmetic as gemm_q4k_exact.cu:
-//   per 256-element super-block   acc += d * (sum_k (sc*q)_k * (x_hi + x_lo)_k) - dmin * (sum_sub m_sub * sum_x_sub)
-// The tensor cores only ever see values f16 holds exactly (integers sc*q <= 945, integer mins,
-// two-term activation splits); d and dmin are applied in f32 by the epilogue warps.
+// tensor memory). Per 256-element super-block of a weight row
+//   acc += d * ( sum_k (sc*q)_k * (x_hi + x_lo)_k  -  sum_sub (rho * m_sub) * sum_x_sub ),   rho = dmin / d.
+// The tensor cores only ever see values f16 holds exactly: the integers sc*q <= 945, the two-term
+// activation splits, and the minimum term's factor rho * m_sub as an f16 pair (hi + lo, 22 bits; rho is
+// one f32 division per row and super-block, so the minimum term carries a relative error of ~3e-7
+// instead of none - far below the f32 rounding of the sum it joins). d is applied in f32 by the
+// epilogue warps. Folding the minimum term into the main accumulator this way (instead of giving it an
+// accumulator of its own, scaled by dmin) frees a quarter of the tensor memory for pipeline slots. A
+// matrix qualifies when every super-block has d != 0 or dmin * m == 0, and |rho * m| stays far inside
+// the f16 range (q4k_min_fold_ok, checked once at load); other matrices take the mma.sync kernel.
 //
-// One CTA computes 128 weight rows x 128 tokens. Warp roles (17 warps):
-//   0-3, 4-7   two producer groups, alternating pipeline stages: thread p decodes the 64 weights of
+// One CTA computes 128 weight rows x 128 tokens. Warp roles (21 warps):
+//   0-11       three producer groups of four warps, taking pipeline stages in turn (the decode is a
+//              dependent instruction chain per thread: with two groups the producers were busy 92 % of
+//              the time and the issuing warp waited for them a third of it); thread p decodes the 64 weights of
 //              row p and stores them into lane p of the stage's A slot in TENSOR MEMORY (the MMA reads
 //              its A operand from there, so shared memory carries the activations only); one thread
 //              of the group fetches the two activation tiles (hi and lo) with TMA, whose bytes
 //              complete on the stage's barrier;
-//   16         lane 0 issues the MMAs (M 128, N 128, K 16) and commits them to the stage's
-//              "empty" barrier, and per super-block to the accumulator's "full" barrier;
-//   8-11,12-15 epilogue: each thread owns one weight row and 64 token columns, pulls both TMEM
-//              accumulators of a finished super-block with tcgen05.ld and folds them into its f32
-//              running sums while the tensor cores already work on the next super-block in the
-//              other main buffer.
-// Tensor memory (512 columns): two main accumulators (2 x 128), one minimum-term accumulator (128; its
-// MMA is the last of a super-block, long after the epilogue has read the previous one), and four A
-// slots of 32 columns (128 rows x 64 f16).
+//   20         walks the pipeline as a whole warp (uniform address arithmetic); one elected lane issues
+//              the MMAs (M 128, N 128, K 16) and commits them to the stage's "empty" barrier, and per
+//              super-block to the accumulator's "full" barrier;
+//   12-19      epilogue: each thread owns one weight row and 64 token columns, pulls the TMEM
+//              accumulator of a finished super-block with tcgen05.ld and folds it, times d, into its
+//              f32 running sums while the tensor cores already work on the next super-block in the
+//              other buffer.
+// Tensor memory (512 columns): two accumulators (2 x 128) and the pipeline's A slots of 32 columns
+// (128 rows x 64 f16). The pipeline is five stages deep (shared memory: 5 x 32 KB of activation
+// tiles); measured on 28 672 x 4096 x 2048 with three producer groups: three stages 0.88 ms, four
+// 0.77, five 0.75-0.76, six 0.79, seven 0.81.
 // A super-block is five pipeline stages: four of 64 columns each (eight MMAs: hi and lo), then one
-// that carries the minimum term as a single K=16 step (A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]).
-// The thread that issues the MMAs is one dependent instruction stream sharing its scheduler with four
+// that carries the minimum term as two K=16 steps (A = [-rho*m hi | -rho*m lo], B = [sum_hi | sum_hi],
+// then the same A with B = [sum_lo | sum_lo]).
+// The warp that issues the MMAs is one dependent instruction stream sharing its scheduler with four
 // busy warps, so its loop is kept to an add per operand and the MMA itself (descriptors are built
 // once), and every other wait sleeps in hardware (try_wait with a time hint) instead of spinning.
+// Barrier arrivals are one per warp (after a warp-level synchronisation), not one per thread.
 // Every mbarrier wait is bounded: after about a second without progress the CTA raises an error
 // flag, drains its copies, frees its tensor memory and returns.
 
@@ -39,13 +51,22 @@ namespace rb200 {
 namespace {
 
 constexpr int BM = 128, BN = 128;
-constexpr int STAGES = 4;
+#ifndef RB200_TC5_STAGES
+#define RB200_TC5_STAGES 5
+#endif
+constexpr int STAGES = RB200_TC5_STAGES;
 constexpr int B_BYTES = BN * 128;
 constexpr int STAGE_BYTES = 2 * B_BYTES;          // activation tiles hi and lo; the weight tile lives in tensor memory
-constexpr int N_WARPS = 17;
+#ifndef RB200_TC5_GROUPS
+#define RB200_TC5_GROUPS 3
+#endif
+constexpr int GROUPS = RB200_TC5_GROUPS;          // producer groups of four warps
+constexpr int EPI_WARP0 = 4 * GROUPS, MMA_WARP = EPI_WARP0 + 8;
+constexpr int N_WARPS = MMA_WARP + 1;
 constexpr int THREADS = N_WARPS * 32;
 constexpr int TMEM_COLS = 512;
-constexpr int TMEM_MIN = 256, TMEM_A = 384;    // column offsets: main buffers at 0 and 128
+constexpr int TMEM_A = 256;                    // column offsets: accumulators at 0 and 128, then the A slots
+static_assert(STAGES >= 2 && STAGES <= 8, "the A slots share 256 tensor-memory columns");
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 __device__ __forceinline__ void nibbles_times_scale(uint32_t word, int hi, __half2 sc2, __half2 off2, uint32_t & out01, uint32_t & out23) {
@@ -93,14 +114,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
-    // barriers: full[4], empty[4], tmem_full[2], tmem_empty[2], min_empty; then the TMEM base word and the abort flag
+    // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]; then the TMEM base word and the abort flag
     const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
-    const uint32_t tmin_empty_bar = bar_base + 8u * (2 * STAGES + 4);
-    uint32_t * tmem_word = reinterpret_cast<uint32_t *>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 5));
+    uint32_t * tmem_word = reinterpret_cast<uint32_t *>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
     volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_word + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -114,24 +134,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            tc5::mbar_init(full_bar(s), 128);   // the producer group's threads; the TMA bytes are tracked as transactions
+            tc5::mbar_init(full_bar(s), 4);     // the producer group's warps; the TMA bytes are tracked as transactions
             tc5::mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             tc5::mbar_init(tfull_bar(b), 1);
-            tc5::mbar_init(tempty_bar(b), 256);
+            tc5::mbar_init(tempty_bar(b), 8);   // the epilogue warps
         }
-        tc5::mbar_init(tmin_empty_bar, 256);
         *abort_flag = 0;
         tc5::fence_mbar_init();
     }
-    if (warp == 16) tc5::tmem_alloc(smem_u32(tmem_word), TMEM_COLS);
+    if (warp == MMA_WARP) tc5::tmem_alloc(smem_u32(tmem_word), TMEM_COLS);
     tc5::fence_before_sync();
     __syncthreads();
     tc5::fence_after_sync();
     const uint32_t tmem_base = *tmem_word;
 
-    if (warp < 8) {
+    if (warp < EPI_WARP0) {
         // ------------------------------------------------------------------ producers
         const int group = warp >> 2;
         const int p = tid & 127;                       // weight row and token row of this thread
@@ -196,85 +215,98 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
                     nibbles_times_scale(raw.q1.w, half, sc2, off2, o[14], o[15]);
                 }
                 tc5::tmem_st32(a_slot, out);
-                prefetch(it + 4, raw);
+                prefetch(it + 2 * GROUPS, raw);
             } else {
-                // minimum-term stage: one K = 16 step, A = [m_0..m_7 | m_0..m_7], B = [sum_hi | sum_lo]
+                // minimum-term stage: A = [-rho*m_0..7 hi | lo], B tiles [sum_hi | sum_hi] and [sum_lo | sum_lo]
+                const __half2 dd = *reinterpret_cast<const __half2 *>(&raw.hdr.x);
+                const float d = __low2float(dd), dmin = __high2float(dd);
+                const float nrho = d != 0.f ? -dmin / d : 0.f;
                 uint32_t mw[8];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     uint32_t s0, n0, s1, n1;
                     q4k_scale_min_regs(raw.hdr, 2 * q, s0, n0);
                     q4k_scale_min_regs(raw.hdr, 2 * q + 1, s1, n1);
-                    const __half2 pr = __halves2half2(__ushort2half_rn((unsigned short)n0), __ushort2half_rn((unsigned short)n1));
-                    mw[q] = mw[q + 4] = *reinterpret_cast<const uint32_t *>(&pr);
+                    const float v0 = nrho * (float)n0, v1 = nrho * (float)n1;
+                    const __half h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
+                    const __half2 hi2 = __halves2half2(h0, h1);
+                    const __half2 lo2 = __halves2half2(__float2half_rn(v0 - __half2float(h0)), __float2half_rn(v1 - __half2float(h1)));
+                    mw[q] = *reinterpret_cast<const uint32_t *>(&hi2);
+                    mw[q + 4] = *reinterpret_cast<const uint32_t *>(&lo2);
                 }
                 tc5::tmem_st8(a_slot, mw);
                 *reinterpret_cast<uint4 *>(bh_s + swz(p, 0)) = raw.q0;
-                *reinterpret_cast<uint4 *>(bh_s + swz(p, 1)) = raw.q1;
+                *reinterpret_cast<uint4 *>(bh_s + swz(p, 1)) = raw.q0;
+                *reinterpret_cast<uint4 *>(bh_s + B_BYTES + swz(p, 0)) = raw.q1;
+                *reinterpret_cast<uint4 *>(bh_s + B_BYTES + swz(p, 1)) = raw.q1;
                 tc5::fence_proxy_async();
-                prefetch(it + 4, raw);
+                prefetch(it + 2 * GROUPS, raw);
             }
             tc5::fence_before_sync();
-            tc5::mbar_arrive(full_bar(stage));
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive(full_bar(stage));
             return true;
         };
         Raw raw0, raw1;
         prefetch(group, raw0);
-        prefetch(group + 2, raw1);
+        prefetch(group + GROUPS, raw1);
         // programmatic stream serialization: only weights were touched so far; the activations follow
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        for (int it = group; it < n_it; it += 4) {
+        for (int it = group; it < n_it; it += 2 * GROUPS) {
             if (!produce(it, raw0)) break;
-            if (it + 2 < n_it && !produce(it + 2, raw1)) break;
+            if (it + GROUPS < n_it && !produce(it + GROUPS, raw1)) break;
         }
-    } else if (warp == 16) {
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (lane == 0) {
-            // The issuing thread is a single dependent instruction stream: everything that can be is
-            // computed once here, so that a stage costs an add per operand and the MMAs themselves.
+        {
+            // The whole warp walks this loop with warp-uniform values; the election's outcome rides on each MMA
+            // and commit as a predicate, so nothing here branches on it and the descriptor arithmetic stays
+            // uniform. (With a single thread inside a divergent branch the issuing thread - not the tensor
+            // pipe - set the pace: 0.94 -> 0.81 ms on 28 672 x 4096 x 2048.) Descriptors are built once; a
+            // stage costs an add per operand and the MMAs themselves.
             const uint32_t idesc = tc5::instr_desc_f16(BM, BN);
             const uint64_t desc0 = tc5::smem_desc_sw128(smem_base);
             const uint32_t desc_lo0 = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
-            const uint32_t a_slot0 = tmem_base + TMEM_A, d_min = tmem_base + TMEM_MIN;
+            const uint32_t a_slot0 = tmem_base + TMEM_A;
             int stage = 0, full_parity = 0;
-            for (int sb = 0; sb < n_sb; ++sb) {
+            bool alive = true;
+            for (int sb = 0; sb < n_sb && alive; ++sb) {
                 const int buf = sb & 1;
                 const uint32_t d_main = tmem_base + buf * 128;
-                if (!tc5::mbar_wait(tempty_bar(buf), ((sb >> 1) & 1) ^ 1, abort_flag)) break;
+                if (!__all_sync(0xffffffffu, tc5::mbar_wait(tempty_bar(buf), ((sb >> 1) & 1) ^ 1, abort_flag))) break;
                 tc5::fence_after_sync();
-                bool alive = true;
 #pragma unroll
                 for (int r = 0; r < 5; ++r) {
-                    if (!tc5::mbar_wait(full_bar(stage), full_parity, abort_flag)) { alive = false; break; }
+                    if (!__all_sync(0xffffffffu, tc5::mbar_wait(full_bar(stage), full_parity, abort_flag))) { alive = false; break; }
                     tc5::fence_after_sync();
                     const uint32_t bh = desc_lo0 + stage * (STAGE_BYTES >> 4), bl = bh + (B_BYTES >> 4);
                     const uint32_t a_slot = a_slot0 + stage * 32;
+                    const uint32_t issue = tc5::elect_one() ? 1u : 0u;
                     if (r < 4) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            if (r == 0 && k == 0) tc5::mma_f16_ts_lean<0>(d_main, a_slot, bh, desc_hi, idesc);
-                            else tc5::mma_f16_ts_lean<1>(d_main, a_slot + k * 8, bh + k * 2, desc_hi, idesc);
-                            tc5::mma_f16_ts_lean<1>(d_main, a_slot + k * 8, bl + k * 2, desc_hi, idesc);
+                            if (r == 0 && k == 0) tc5::mma_f16_ts_pred<0>(issue, d_main, a_slot, bh, desc_hi, idesc);
+                            else tc5::mma_f16_ts_pred<1>(issue, d_main, a_slot + k * 8, bh + k * 2, desc_hi, idesc);
+                            tc5::mma_f16_ts_pred<1>(issue, d_main, a_slot + k * 8, bl + k * 2, desc_hi, idesc);
                         }
+                        tc5::commit_pred(issue, empty_bar(stage));
                     } else {
-                        // the epilogue must have read the previous super-block's minimum term
-                        if (!tc5::mbar_wait(tmin_empty_bar, (sb & 1) ^ 1, abort_flag)) { alive = false; break; }
-                        tc5::fence_after_sync();
-                        tc5::mma_f16_ts_lean<0>(d_min, a_slot, bh, desc_hi, idesc);
+                        tc5::mma_f16_ts_pred<1>(issue, d_main, a_slot, bh, desc_hi, idesc);
+                        tc5::mma_f16_ts_pred<1>(issue, d_main, a_slot, bl, desc_hi, idesc);
+                        tc5::commit_pred(issue, empty_bar(stage));
+                        tc5::commit_pred(issue, tfull_bar(buf));
                     }
-                    tc5::commit(empty_bar(stage));
-                    if (r == 4) tc5::commit(tfull_bar(buf));
+                    __syncwarp();
                     if (++stage == STAGES) { stage = 0; full_parity ^= 1; }
                 }
-                if (!alive) break;
             }
         }
     } else {
         // ------------------------------------------------------------------ epilogue
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const int q = warp & 3;                         // TMEM lane quarter this warp may read
-        const int colhalf = (warp - 8) >> 2;            // which 64 token columns
+        const int colhalf = (warp - EPI_WARP0) >> 2;    // which 64 token columns
         const int o_local = q * 32 + lane;
         const int o = m0 + o_local;
         const bool o_valid = o < n_out;
@@ -283,29 +315,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
         bool alive = true;
-        // d and dmin of the next super-block are fetched while the tensor cores still work on it
+        // d of the next super-block is fetched while the tensor cores still work on it
         __half2 h_next = *reinterpret_cast<const __half2 *>(hdr_base);      // (rows are padded to whole tiles)
         const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16) + colhalf * 64;
         for (int sb = 0; sb < n_sb && alive; ++sb) {
             const int buf = sb & 1, buse = sb >> 1;
-            const float d = __low2float(h_next), dmin = __high2float(h_next);
+            const float d = __low2float(h_next);
             if (sb + 1 < n_sb) h_next = *reinterpret_cast<const __half2 *>(hdr_base + (size_t)(sb + 1) * kQ4kTileBytes);
-            if (!tc5::mbar_wait(tfull_bar(buf), buse & 1, abort_flag)) { alive = false; break; }
+            // warp-uniform outcome: the tensor-memory loads below are warp-collective
+            if (!__all_sync(0xffffffffu, tc5::mbar_wait(tfull_bar(buf), buse & 1, abort_flag))) { alive = false; break; }
             tc5::fence_after_sync();
-            const uint32_t t_main = t_lane + buf * 128, t_min = t_lane + TMEM_MIN;
-            // the single minimum-term accumulator first, so the next super-block's MMA can have it back early
-#pragma unroll
-            for (int c = 0; c < 4; c += 2) {
-                float v[16], w[16];
-                tc5::tmem_ld16x2(t_min + c * 16, t_min + (c + 1) * 16, v, w);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    acc[c * 16 + i] -= dmin * v[i];
-                    acc[(c + 1) * 16 + i] -= dmin * w[i];
-                }
-            }
-            tc5::fence_before_sync();
-            tc5::mbar_arrive(tmin_empty_bar);
+            const uint32_t t_main = t_lane + buf * 128;
 #pragma unroll
             for (int c = 0; c < 4; c += 2) {
                 float v[16], w[16];
@@ -317,7 +337,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
                 }
             }
             tc5::fence_before_sync();
-            tc5::mbar_arrive(tempty_bar(buf));
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive(tempty_bar(buf));
         }
         if (alive && o_valid) {
             const float b = bias ? bias[o] : 0.f;
@@ -339,7 +360,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
 
     tc5::fence_before_sync();
     __syncthreads();
-    if (warp == 16) {
+    if (warp == MMA_WARP) {
         tc5::fence_after_sync();
         tc5::tmem_dealloc(tmem_base, TMEM_COLS);
     }
@@ -380,7 +401,29 @@ bool split_act_encode_maps(SplitAct & s, size_t rows) {
 }
 
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x) {
-    return w.type == GGML_Q4_K && w.tiled && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
+    return w.type == GGML_Q4_K && w.tiled && w.min_fold && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
+}
+
+bool q4k_min_fold_ok(const uint8_t * blocks, size_t n_blocks) {
+    bool ok = true;
+#pragma omp parallel for reduction(&& : ok)
+    for (long long b = 0; b < (long long)n_blocks; ++b) {
+        const uint8_t * blk = blocks + (size_t)b * 144;
+        uint16_t hd, hm;
+        std::memcpy(&hd, blk, 2);
+        std::memcpy(&hm, blk + 2, 2);
+        const float d = half_to_float(hd), dmin = half_to_float(hm);
+        if (!std::isfinite(d) || !std::isfinite(dmin)) {
+            ok = false;
+            continue;
+        }
+        for (int j = 0; j < 8; ++j) {
+            uint8_t sc, mn;
+            q4k_scale_min(j, blk + 4, sc, mn);
+            if (d == 0.f ? dmin * (float)mn != 0.f : !(std::fabs(dmin / d * (float)mn) < 16384.f)) ok = false;
+        }
+    }
+    return ok;
 }
 
 void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream) {
@@ -390,12 +433,11 @@ void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint
 void launch_gemm_q4k_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
                          const float * residual, int ldr, int * error_flag, float * scratch, size_t scratch_floats, int n_sm, cudaStream_t stream,
                          const FinishTail * tail) {
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;   // function attributes are per device
+    if (configured.first()) {
         cudaFuncSetAttribute(gemm_q4k_tc5_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaFuncSetAttribute(gemm_q4k_tc5_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaFuncSetAttribute(gemm_q4k_tc5_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        configured = true;
     }
     // few output tiles (few tokens and few rows): cut the reduction into splits of whole super-blocks so the
     // grid still covers the GPU; the splits' partial results are added, in order, by the finish kernel

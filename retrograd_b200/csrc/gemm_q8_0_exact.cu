@@ -228,10 +228,9 @@ template <int BN, bool RESIDUAL>
 void launch_one(const WeightView & w, const SplitAct & x, int T, float * y, int ldy, const float * bias, const float * residual, int ldr,
                 cudaStream_t stream) {
     constexpr int smem = STAGES * (BM * 128 + 2 * BN * 128) + STAGES * 2 * BM * (int)sizeof(float);
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;   // function attributes are per device
+    if (configured.first()) {
         cudaFuncSetAttribute(gemm_q8_0_exact_kernel<BN, RESIDUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured = true;
     }
     const dim3 grid((w.n_out + BM - 1) / BM, (T + BN - 1) / BN);
     gemm_q8_0_exact_kernel<BN, RESIDUAL><<<grid, THREADS, smem, stream>>>(w.data, (int)w.n_in, (int)w.n_out, (int)w.row_bytes, x, T, y, ldy, bias,
@@ -257,10 +256,9 @@ void launch_gemm_q8_0_exact_grouped(const WeightView & w, uint64_t group_stride_
                                     int max_group_rows, float * y, int ldy, cudaStream_t stream) {
     constexpr int BN = 64;
     constexpr int smem = STAGES * (BM * 128 + 2 * BN * 128) + STAGES * 2 * BM * (int)sizeof(float);
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;   // function attributes are per device
+    if (configured.first()) {
         cudaFuncSetAttribute(gemm_q8_0_exact_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        configured = true;
     }
     if (n_groups <= 0 || max_group_rows <= 0) return;
     const dim3 grid((w.n_out + BM - 1) / BM, (max_group_rows + BN - 1) / BN, n_groups);

@@ -8,6 +8,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 namespace rb200 {
 
 // A weight matrix in device memory in its GGUF storage layout: n_out rows of n_in elements.
@@ -21,6 +23,9 @@ struct WeightView {
     // zero-padded to a multiple of 128 (read by the tcgen05 kernel and the weight-streaming kernel).
     // Q8_0, optional: the layout described at kQ8TileBytes, rows padded to a multiple of 16.
     const uint8_t * tiled = nullptr;
+    // Q4_K: every super-block lets the tcgen05 kernel fold the minimum term into the main accumulator
+    // (q4k_min_fold_ok over the matrix' blocks, checked on the host when the weights are uploaded).
+    bool min_fold = false;
 };
 
 // Tile-major copy of a Q4_K matrix: one 18432-byte tile per (128 rows, 256-column super-block), tiles
@@ -40,6 +45,18 @@ inline size_t q4k_tiled_bytes(uint32_t n_out, uint32_t n_in) { return (size_t)((
 void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream);
 
 #ifdef __CUDACC__
+// Kernel function attributes (the opt-in to more than 48 KB of dynamic shared memory) belong to a
+// device, not to the process: first() is true the first time it is called with a given device current.
+struct PerDeviceOnce {
+    std::atomic<uint64_t> done[4] = {};
+    bool first() {
+        int device = 0;
+        cudaGetDevice(&device);
+        const uint64_t bit = 1ull << (device & 63);
+        return (done[(device >> 6) & 3].fetch_or(bit) & bit) == 0;
+    }
+};
+
 // Programmatic dependent launch. A kernel launched with launch_pdl() may be scheduled while the
 // stream's previous kernel is still running; it must execute pdl_wait() before it reads or writes
 // anything an earlier kernel of the stream touches (the wait returns when the previous kernel has
@@ -200,10 +217,6 @@ void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const flo
 // y[t][o] = sum_i deq(W)[o][i] x[t][i] (+ bias[o]) (+ residual[t][o]); reference kernel, any T.
 void launch_gemm_rows(WeightView w, const float * x, int ldx, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
                       int ldr, cudaStream_t stream);
-// Tensor-core path of the same product for many tokens: f16 activations [t][ldx], Q4_K weights.
-bool gemm_mma_supported(const WeightView & w, int ldx);
-void launch_gemm_mma(const WeightView & w, const __half * x16, int ldx, int n_tokens, float * y, int ldy, const float * bias,
-                     const float * residual, int ldr, cudaStream_t stream);
 // Exact variant (f32-grade accuracy): integer weight operand, two-term activation split.
 bool gemm_q4k_exact_supported(const WeightView & w, const SplitAct & x);
 void launch_gemm_q4k_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
@@ -211,6 +224,10 @@ void launch_gemm_q4k_exact(const WeightView & w, const SplitAct & x, int n_token
 // tcgen05 / tensor-memory variant of the exact GEMM (128 x 128 tiles). `error_flag` (device int) is
 // raised if a pipeline wait inside the kernel timed out.
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x);
+// Whether the tcgen05 kernel's arithmetic covers these blocks (host memory, GGUF layout): it carries a row's
+// minimum term as (dmin / d) * m inside the sum that d scales, so a super-block needs d != 0 unless its
+// dmin * m are all zero, and |dmin / d * m| well inside the f16 range. Encoders produce nothing else.
+bool q4k_min_fold_ok(const uint8_t * blocks, size_t n_blocks);
 // With `scratch` (gemm_q4k_tc5_scratch_floats() floats) and few output tiles the reduction is cut into
 // splits of whole super-blocks (grid.z) whose partial results a finish kernel adds in order.
 int gemm_q4k_tc5_splits(uint32_t n_out, uint32_t n_in, int n_tokens, int n_sm);      // 1: the reduction is not split

@@ -61,7 +61,8 @@ extern "C" {
 // stream). The work is enqueued on that stream; the call does not wait for it.
 //
 // - Limit: n_tokens * n_in <= 1 048 576 and n_in a multiple of 256; larger shapes are refused
-//   with -3 and a message, nothing is launched.
+//   with -3 and a message, nothing is launched. d_w must be 16-byte aligned (the kernel reads
+//   weight blocks as 16-byte words); a misaligned pointer is refused the same way.
 // - The first call on a device resolves the scratch array's address for that device (with that
 //   device current). Make that first call before starting any stream capture.
 // - Every call on a device uses the same scratch array. Nothing in it has to start at zero: a call
@@ -79,20 +80,24 @@ int retro_b200_gemm_q4k_noalloc(const uint8_t * d_w, uint32_t n_out, uint32_t n_
             set_error("gemm_q4k_noalloc: n_in must be a multiple of 256 (whole Q4_K blocks)");
             return STATUS_INVALID_ARGUMENT;
         }
+        // the kernel reads weight blocks as 16-byte words (a Q4_K block is 144 bytes, so every block of an
+        // aligned matrix is aligned) and writes f32 results
+        if (reinterpret_cast<uintptr_t>(d_w) % 16 != 0 || reinterpret_cast<uintptr_t>(d_x) % 4 != 0 || reinterpret_cast<uintptr_t>(d_y) % 4 != 0) {
+            set_error("gemm_q4k_noalloc: d_w must be 16-byte aligned, d_x and d_y 4-byte aligned");
+            return STATUS_INVALID_ARGUMENT;
+        }
         if ((size_t)n_tokens * n_in > kNoAllocMaxElements) {
             set_error("gemm_q4k_noalloc: n_tokens * n_in exceeds the fixed scratch of 1048576 activation elements");
             return STATUS_INVALID_ARGUMENT;
         }
         unsigned char * scratch = scratch_for_current_device();
         if (!scratch) return STATUS_RUNTIME;
-        const size_t elems = (size_t)n_tokens * n_in;
         SplitAct split;
         split.hi = reinterpret_cast<__half *>(scratch);
         split.lo = reinterpret_cast<__half *>(scratch + kHalfBytes);
         split.sum_hi = reinterpret_cast<__half *>(scratch + 2 * kHalfBytes);
         split.sum_lo = reinterpret_cast<__half *>(scratch + 2 * kHalfBytes + kSumBytes);
         split.ld = (int)n_in;
-        (void)elems;
         WeightView w;
         w.data = d_w;
         w.type = GGML_Q4_K;

@@ -12,7 +12,7 @@ using namespace rb200;
 extern "C" {
 
 // y[t][o] = sum_k deq(w)[o][k] x[t][k]. `path`: 0 = what the engine would pick, 1 = f32 row kernel,
-// 2 = single-term f16 tensor-core kernel, 3 = exact tensor-core kernel (mma.sync), 4 = exact tcgen05 kernel, 5 = exact weight-streaming kernel (at most 8 tokens). The kernel runs `iters`
+// 3 = exact tensor-core kernel (mma.sync), 4 = exact tcgen05 kernel, 5 = exact weight-streaming kernel (at most 8 tokens). The kernel runs `iters`
 // times; *out_ms receives the mean device time per launch (CUDA events on the launching stream).
 int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, uint32_t n_in, const float * x, uint32_t n_tokens, float * y,
                        int path, uint32_t iters, float * out_ms) {
@@ -47,6 +47,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             dtiled.ensure(q4k_tiled_bytes(n_out, n_in));
             launch_q4k_retile(dw.ptr, n_out, n_in, (uint32_t)rb, dtiled.ptr, stream);
             wv.tiled = dtiled.ptr;
+            wv.min_fold = q4k_min_fold_ok(w, (size_t)n_out * (n_in / 256));
         }
         if (ggml_type == GGML_Q8_0 && n_in % 256 == 0 && path == 5) {
             dtiled.ensure(q8_0_tiled_bytes(n_out, n_in));
@@ -85,8 +86,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             set_error("op_gemm: the requested kernel does not cover this type or shape");
             return STATUS_INVALID_ARGUMENT;
         }
-        if ((chosen == 3 && !(have_split && (gemm_q4k_exact_supported(wv, xs.view) || gemm_q8_0_exact_supported(wv, xs.view)))) ||
-            (chosen == 2 && !(have_split && gemm_mma_supported(wv, (int)n_in)))) {
+        if ((chosen == 3 && !(have_split && (gemm_q4k_exact_supported(wv, xs.view) || gemm_q8_0_exact_supported(wv, xs.view)))) || chosen == 2) {
             cudaStreamDestroy(stream);
             set_error("op_gemm: the requested kernel does not cover this type or shape");
             return STATUS_INVALID_ARGUMENT;
@@ -97,7 +97,6 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             else if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, tc5_scratch.ptr, tc5_scratch.count, n_sm, stream);
             else if (chosen == 3 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
-            else if (chosen == 2) launch_gemm_mma(wv, xs.view.hi, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else launch_gemm_rows(wv, dx.ptr, (int)n_in, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
         };
         run();   // warm-up, also the launch whose output is returned

@@ -72,6 +72,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// True in exactly one lane of a converged warp (the same lane every time): the warp keeps uniform
+// control flow and uniform address arithmetic, and only the instruction itself is issued once.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -144,6 +158,32 @@ __device__ __forceinline__ void mma_f16_ts_lean(uint32_t d_tmem, uint32_t a_tmem
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n"
         "}\n" ::"r"(d_tmem),
         "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "n"(ACCUMULATE)
+        : "memory");
+}
+
+// The same, issued only where `issue` is non-zero (the elected lane): the predicate rides on the instruction,
+// so the code around it has no branch, the warp stays converged and the operand arithmetic stays uniform.
+template <int ACCUMULATE>
+__device__ __forceinline__ void mma_f16_ts_pred(uint32_t issue, uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t b_desc_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p, pe;\n"
+        ".reg .b64 bd;\n"
+        "setp.ne.b32 pe, %6, 0;\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "mov.b64 bd, {%2, %3};\n"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc), "n"(ACCUMULATE), "r"(issue)
+        : "memory");
+}
+__device__ __forceinline__ void commit_pred(uint32_t issue, uint32_t bar) {
+    asm volatile(
+        "{\n"
+        ".reg .pred pe;\n"
+        "setp.ne.b32 pe, %1, 0;\n"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+        "}\n" ::"r"(bar), "r"(issue)
         : "memory");
 }
 

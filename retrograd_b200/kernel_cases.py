@@ -5,7 +5,7 @@ profiler captures of a small case.
 
     python -m retrograd_b200.kernel_cases attention --mode decode --seqs 256 --ctx 1024 --iters 4
 
-`--path`: 0 engine's choice, 1 f32 row kernel, 2 single-term f16 tensor-core kernel, 3 exact
+`--path`: 0 engine's choice, 1 f32 row kernel, 3 exact
 tensor-core kernel (mma.sync), 4 exact tcgen05 kernel, 5 exact weight-streaming kernel (at most 8 tokens).
 Operands smaller than 256 MB are timed with a write of a buffer larger than L2 before every launch. Weights are random Q4_K blocks (scales pinned to small f16 values), the
 activations N(0, 1). `--type q8_0` runs the Q8_0 kernels (paths 1 and 5). Prints the mean device time per launch and the rates derived from it.

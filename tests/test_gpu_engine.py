@@ -445,7 +445,7 @@ def test_scheduler_composed_steps_reproduce_the_generators(rb, pair):
     row each, then decode) beside two single requests, under continuous admission with a budget small
     enough that prefill is chunked, a token is kept for it, and the decode cursor rotates. Every request's
     greedy stream must equal what the engine's own generators produce for it."""
-    from retrograd_b200.scheduler import CONTINUOUS, ComposeState, Group, Member, compose
+    from oracle.scheduler import CONTINUOUS, ComposeState, Group, Member, compose
 
     engine, _ = pair
     n_new = 5
@@ -531,7 +531,7 @@ def test_prefix_tree_hits_become_block_table_copies(rb, pair):
     slot stays dormant under its token path; a later prompt that shares a prefix gets `[0, hit)` by
     `seq_cp` - an exact boundary and a mid-sequence hit - prefills only the rest, and must produce the greedy
     stream of a cold run. The last prompt token is always prefilled (a hit is a strict prefix)."""
-    from retrograd_b200.prefix_tree import PrefixTree
+    from oracle.prefix_tree import PrefixTree
 
     engine, _ = pair
     g = rb.SamplingParamsV2.greedy()

@@ -24,11 +24,9 @@ def test_q4k_gemm_kernels_against_the_oracle(rb, oracle, n_out, n_in, T):
     assert float(np.abs(serial - want).max()) / scale < 4e-6
     rows, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=1)
     exact, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=3)
-    fast, _ = rb.op_gemm(12, raw, n_out, n_in, x, path=2)
-    e_rows, e_exact, e_fast = (float(np.abs(y - want).max()) / scale for y in (rows, exact, fast))
-    print(f"q4k {n_out}x{n_in} T={T}: rel err rows={e_rows:.2e} exact={e_exact:.2e} single-term f16={e_fast:.2e}")
+    e_rows, e_exact = (float(np.abs(y - want).max()) / scale for y in (rows, exact))
+    print(f"q4k {n_out}x{n_in} T={T}: rel err rows={e_rows:.2e} exact={e_exact:.2e}")
     assert e_rows < 4e-6 and e_exact < 4e-6
-    assert e_fast < 3e-3
 
 
 @pytest.mark.parametrize("n_out,n_in,T", [(128, 256, 128), (256, 512, 130), (200, 768, 33), (512, 2048, 100), (256, 4096, 300), (384, 2816, 40)])

@@ -1,7 +1,7 @@
 """Behaviour of the prefix cache index as restated in retrograd_b200/prefix_tree.py, on the scenarios the
 reference checks its own tree with (crates/retrograd-infer/src/kv.rs:549-690): edge walks and splits,
 exact and mid-sequence hits, pins and LRU eviction, pruning, namespaces."""
-from retrograd_b200.prefix_tree import PrefixTree
+from oracle.prefix_tree import PrefixTree
 
 
 def _tree(*paths):

@@ -1,6 +1,6 @@
 """The step-composition rules of the reference's scheduler (crates/retrograd-infer/src/scheduler.rs:933-1089)
 as restated in retrograd_b200/scheduler.py: which rows a step carries, in which order, within `n_batch`."""
-from retrograd_b200.scheduler import CONTINUOUS, LOCKSTEP, ComposeState, Group, Member, compose
+from oracle.scheduler import CONTINUOUS, LOCKSTEP, ComposeState, Group, Member, compose
 
 
 def _decoding(gid, n_members, prompt_len=6, generated=3):

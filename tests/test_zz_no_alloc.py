@@ -18,7 +18,7 @@ def _q4k_matrix(rb, rng, n_out, n_in):
     return np.frombuffer(b"".join(rb.quantize_row(12, w[r]) for r in range(n_out)), dtype=np.uint8)
 
 
-def test_no_alloc_gemm_matches_the_regular_entry_point_on_two_calls_in_a_row(rb):
+def test_no_alloc_gemm_matches_the_regular_entry_point_on_two_calls_in_a_row(rb, oracle):
     import torch
 
     lib = rb.load_library()
@@ -39,6 +39,10 @@ def test_no_alloc_gemm_matches_the_regular_entry_point_on_two_calls_in_a_row(rb)
         got = d_y.cpu().numpy()
         scale = float(np.abs(want).max())
         assert float(np.abs(got - want).max()) / scale < 4e-6
+        # and against the float64 product of the decoded weights, the yardstick of the other GEMM tests
+        w64 = oracle.dequantize_row(oracle.T_Q4_K, raw, n_out * n_in).reshape(n_out, n_in).astype(np.float64)
+        exact = x.astype(np.float64) @ w64.T
+        assert float(np.abs(got - exact).max()) / float(np.abs(exact).max()) < 4e-6
 
 
 def test_no_alloc_gemm_refuses_shapes_beyond_its_scratch(rb):
@@ -51,3 +55,6 @@ def test_no_alloc_gemm_refuses_shapes_beyond_its_scratch(rb):
     assert b"exceeds the fixed scratch" in lib.retro_last_error()
     assert lib.retro_b200_gemm_q4k_noalloc(d.data_ptr(), 256, 100, d.data_ptr(), 4, d.data_ptr(), None) == -3
     assert lib.retro_b200_gemm_q4k_noalloc(None, 256, 256, d.data_ptr(), 4, d.data_ptr(), None) == -3
+    # a weight pointer off the 16-byte grid would fault inside the kernel: refused on the host, nothing launched
+    assert lib.retro_b200_gemm_q4k_noalloc(d.data_ptr() + 4, 256, 256, d.data_ptr(), 4, d.data_ptr(), None) == -3
+    assert b"16-byte aligned" in lib.retro_last_error()
