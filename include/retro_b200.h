@@ -237,11 +237,168 @@ int retro_engine_expert_route_enable(retro_engine * engine, uint32_t sample_ever
 int retro_engine_expert_route_counts(retro_engine * engine, uint32_t layer, uint32_t * out, size_t n_expert);
 int retro_engine_expert_route_reset(retro_engine * engine);
 
+/* ---- serialised adapters: one active at a time (retro_lora_train.h:2566-2584, 2616-2620) ----
+ * Rows of a step whose `adapter` is 0 decode under the active adapter (the base model when none is
+ * active). load_lora replaces every registered adapter and activates the file; load_lora_named
+ * registers a file beside the others and re-applies it only when it is the active one; activate_lora
+ * (NULL or "" = the base model) and set_lora_enabled switch. Every activation, enable or disable
+ * clears the whole KV and bumps the weights version (retro_engine.cpp:322-328). */
+int retro_engine_load_lora(retro_engine * engine, const char * adapter_path);
+int retro_engine_set_lora_enabled(retro_engine * engine, bool enabled);
+int retro_engine_load_lora_named(retro_engine * engine, const char * name, const char * adapter_path);
+int retro_engine_activate_lora(retro_engine * engine, const char * name);
+/* The active adapter's name (empty: the base model). Two-call string contract: with buffer NULL or
+ * n_buffer 0 only *out_n_bytes is written; otherwise the text plus a NUL, -2 when it does not fit. */
+int retro_engine_active_adapter(retro_engine * engine, char * buffer, size_t n_buffer, size_t * out_n_bytes);
+
+/* ---- counters and memory (retro_lora_train.h:849-917, 1113-1131, 2666-2674) ---- */
+typedef struct retro_memory_report {
+    uint64_t model_weight_bytes;
+    uint64_t optimizer_kv_bytes;
+    uint64_t optimizer_compute_bytes;
+    uint64_t generation_kv_bytes;
+    uint64_t generation_compute_bytes;
+    bool     has_generation_context;
+    uint64_t trainable_parameter_bytes;
+    uint64_t trainable_gradient_bytes;
+    uint64_t optimizer_state_bytes;
+    bool     trainable_parameters_are_model_subset;
+    bool     adapter_on_host;
+    bool     base_trainable_on_host;
+    uint64_t device_bytes;
+    uint64_t host_bytes;
+    uint64_t device_total_bytes;
+    uint64_t device_used_bytes;
+    uint64_t device_peak_used_bytes;
+    uint64_t backend_scratch_bytes;
+    uint64_t backend_scratch_peak_bytes;
+    uint64_t device_memory_samples;
+    uint64_t checkpoint_count;
+    uint64_t checkpoint_retained_bytes;
+    uint64_t checkpoint_live_peak_bytes;
+    uint64_t checkpoint_live_peak_count;
+    uint64_t checkpoint_long_lived_bytes;
+    uint64_t checkpoint_long_lived_count;
+    uint64_t checkpoint_graph_nodes;
+    uint64_t checkpoint_max_span_nodes;
+    uint64_t checkpoint_total_span_nodes;
+} retro_memory_report;
+/* Weights (both layouts of a quantised matrix count), KV pool, work buffers, adapters (their bytes
+ * are `trainable_parameter_bytes`, as the reference reports an engine's adapters), everything on the
+ * device; optimizer, gradient and checkpoint fields are zero: the handle has none. The measured fields
+ * come from one cudaMemGetInfo sample. */
+int retro_engine_memory_report(retro_engine * engine, retro_memory_report * out_report);
+
+typedef struct retro_generation_stats {
+    uint64_t calls;
+    uint64_t sequences;
+    uint64_t prompt_tokens;
+    uint64_t prefilled_tokens;
+    uint64_t reused_tokens;
+    uint64_t hits;
+    uint64_t evictions;
+} retro_generation_stats;
+/* Monotonic prefix-reuse counters of the batched generators: a shared prompt decoded once and
+ * attached to n - 1 more sequences counts n - 1 hits and (n - 1) * (n_prompt - 1) reused tokens. */
+int retro_engine_generation_stats(retro_engine * engine, retro_generation_stats * out_stats);
+
+/* ---- MoE expert banks (retro_lora_train.h:742-758, 788-795, 827-840, 2780-2793) ---- */
+#define RETRO_MODEL_INFO_NAME_MAX 64
+#define RETRO_TENSOR_NAME_MAX 128
+typedef struct retro_tensor_desc {
+    char name[RETRO_TENSOR_NAME_MAX];
+    int64_t ne[4];
+    uint64_t n_elements;
+    uint64_t n_bytes;
+    uint64_t storage_id;
+    char type_name[RETRO_MODEL_INFO_NAME_MAX];
+} retro_tensor_desc;
+typedef struct retro_expert_bank_desc {
+    uint32_t layer;
+    char role[16];
+    retro_tensor_desc tensor;
+} retro_expert_bank_desc;
+#define RETRO_EXPERT_CACHE_MAX_GROUPS 16
+typedef struct retro_expert_cache_group {
+    int32_t  n_slots;
+    int32_t  n_layers;
+    int32_t  n_expert;
+    uint64_t device_bytes;
+} retro_expert_cache_group;
+typedef struct retro_expert_cache_stats {
+    struct { uint64_t hits; uint64_t misses; uint64_t bytes; } small;
+    struct { uint64_t hits; uint64_t misses; uint64_t bytes; } large;
+    struct { uint64_t hits; uint64_t misses; uint64_t bytes; } copy;
+    int32_t n_groups;
+    retro_expert_cache_group groups[RETRO_EXPERT_CACHE_MAX_GROUPS];
+} retro_expert_cache_stats;
+/* The `ffn_{gate,up,down}_exps` banks of the loaded model as the GGUF holds them (name, shape, bytes,
+ * type), sorted by tensor name. Two-call contract: out_banks NULL and n_max 0 report the count; a short
+ * buffer fails with -2. */
+int retro_engine_expert_banks(retro_engine * engine, retro_expert_bank_desc * out_banks, size_t n_max, size_t * out_count);
+/* Counters of the expert device cache: every bank is resident on the device here, so there is no
+ * cache and the struct is zeroed. */
+int retro_engine_expert_stats(retro_engine * engine, retro_expert_cache_stats * out_stats);
+/* How routed (token, expert) pairs were served since telemetry was enabled: out[0] from resident
+ * device banks (all of them here), out[1] by a copy, out[2] by a read-back (always 0). */
+int retro_engine_expert_route_paths(retro_engine * engine, uint64_t out[3]);
+
+/* ---- grammar handles (retro_lora_train.h:1395-1408): host-only owners of a GBNF text ---- */
+/* from_json_schema returns NULL with a message: the schema converter is part of the reference's
+ * llama.cpp fork and is not restated here; pass GBNF. The handle may be freed as soon as the step
+ * call that carried it returns. */
+retro_grammar * retro_grammar_from_json_schema(const char * json_schema);
+retro_grammar * retro_grammar_from_gbnf(const char * gbnf);
+retro_grammar * retro_grammar_json_object(void);
+const char *    retro_grammar_gbnf(const retro_grammar * grammar);
+void            retro_grammar_free(retro_grammar * grammar);
+
+/* ---- the trainer-owned generation context (retro_lora_train.h:1410-1417 twin, 1427-1455, 1906-1945) ----
+ * The reference's RL trainer drives the same step path on its own generation context through
+ * retro_trainer_generation_*: same structs, same contracts as the engine entry points. The training
+ * runtime behind `retro_trainer` is not part of this library; a handle made by
+ * retro_b200_trainer_generation_new (below) owns only that generation context, and the host calls
+ * retro_b200_trainer_weights_updated after each optimizer step or weight import, which does what the
+ * reference's forget_generation_kv() does there: clears the KV and bumps the weights version so every
+ * prefix cache keyed on it drops its entries (crates/retrograd-infer/src/scheduler.rs:548-560). */
+typedef struct retro_trainer retro_trainer;
+int retro_trainer_generation_step(retro_trainer * trainer, const retro_step_row * rows, size_t n_rows, retro_step_out_row * out_rows,
+                                  int32_t * out_top_ids, float * out_top_logprobs, size_t n_top_stride);
+int retro_trainer_generation_step_v2(retro_trainer * trainer, const retro_step_row_v2 * rows, size_t n_rows,
+                                     retro_step_out_row_v2 * out_rows, int32_t * out_top_ids, float * out_top_logprobs,
+                                     size_t n_top_stride);
+int retro_trainer_generation_seq_rm(retro_trainer * trainer, int32_t slot, int32_t p0, int32_t p1);
+int retro_trainer_generation_seq_cp(retro_trainer * trainer, int32_t src, int32_t dst, int32_t p0, int32_t p1);
+int retro_trainer_generation_seq_save(retro_trainer * trainer, int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_buffer,
+                                      size_t * out_n_bytes);
+int retro_trainer_generation_seq_load(retro_trainer * trainer, int32_t slot, uint32_t flags, const uint8_t * buffer, size_t n_bytes,
+                                      size_t * out_n_read);
+int retro_trainer_generation_seq_pos(retro_trainer * trainer, int32_t slot, int32_t * out_pos_min, int32_t * out_pos_max);
+int retro_trainer_generation_memory(retro_trainer * trainer, retro_engine_memory_info * out);
+int retro_trainer_generation_request_free(retro_trainer * trainer, int32_t request);
+int retro_trainer_generation_kv_unified(retro_trainer * trainer, bool * out_unified);
+int retro_trainer_generation_weights_version(retro_trainer * trainer, uint64_t * out_version);
+int retro_trainer_generation_stats(retro_trainer * trainer, retro_generation_stats * out_stats);
+/* A frozen copy of the trained (= active) adapter as a per-row adapter; `replace`, when not 0, is
+ * unloaded first. Refused when no adapter is active. */
+int retro_trainer_generation_adapter_snapshot(retro_trainer * trainer, int32_t replace, float scale, int32_t * out_id);
+int retro_trainer_generation_adapter_unload(retro_trainer * trainer, int32_t id);
+int retro_trainer_generation_adapter_rows_info(retro_trainer * trainer, retro_adapter_rows_info * out_info);
+
 /* ================= extensions without a counterpart in the reference ================= */
+
+/* A `retro_trainer` that owns nothing but a generation context (see the retro_trainer_generation_*
+ * group above); `adapter_path`, when not NULL, is the trained adapter the context decodes under.
+ * retro_b200_trainer_weights_updated is the host's notice that the weights behind the context changed. */
+retro_trainer * retro_b200_trainer_generation_new(const char * model_path, const retro_engine_config * config, const char * adapter_path);
+void retro_b200_trainer_generation_free(retro_trainer * trainer);
+int retro_b200_trainer_weights_updated(retro_trainer * trainer, const char * adapter_path);
+
 
 /* Writes a seeded random model as GGUF. `spec` is whitespace-separated key=value pairs:
  * arch(llama|qwen2|olmoe) layers d heads kv_heads head_dim ff vocab experts experts_used
- * dtype expert_dtype embd_dtype (f32|f16|q8_0|q4_k|mxfp4) std seed bias rope_base eps dist. */
+ * dtype expert_dtype embd_dtype (f32|f16|q8_0|q4_k|mxfp4) std seed bias rope_base eps dist eot turn_end
+ * (eot: a token id named by tokenizer.ggml.eot_token_id; turn_end: a token id only spelled as an end-of-turn piece). */
 int retro_b200_synth_gguf(const char * path, const char * spec, uint64_t * out_bytes);
 
 /* Encodes `n` floats as one stored row of `ggml_type` (0 f32, 1 f16, 8 q8_0, 12 q4_K, 39 mxfp4)

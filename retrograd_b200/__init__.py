@@ -17,6 +17,7 @@ from .engine import (
     SamplingParamsV2,
     StepOutput,
     StepRow,
+    TrainerGeneration,
     ep_plan,
     nccl_unique_id,
     op_gemm,
@@ -36,6 +37,7 @@ __all__ = [
     "SamplingParamsV2",
     "StepOutput",
     "StepRow",
+    "TrainerGeneration",
     "ep_plan",
     "load_library",
     "nccl_unique_id",

@@ -129,6 +129,47 @@ class AdapterRowsInfoC(C.Structure):
     ]
 
 
+class MemoryReportC(C.Structure):
+    _fields_ = [
+        ("model_weight_bytes", C.c_uint64), ("optimizer_kv_bytes", C.c_uint64), ("optimizer_compute_bytes", C.c_uint64),
+        ("generation_kv_bytes", C.c_uint64), ("generation_compute_bytes", C.c_uint64), ("has_generation_context", C.c_bool),
+        ("trainable_parameter_bytes", C.c_uint64), ("trainable_gradient_bytes", C.c_uint64), ("optimizer_state_bytes", C.c_uint64),
+        ("trainable_parameters_are_model_subset", C.c_bool), ("adapter_on_host", C.c_bool), ("base_trainable_on_host", C.c_bool),
+        ("device_bytes", C.c_uint64), ("host_bytes", C.c_uint64), ("device_total_bytes", C.c_uint64), ("device_used_bytes", C.c_uint64),
+        ("device_peak_used_bytes", C.c_uint64), ("backend_scratch_bytes", C.c_uint64), ("backend_scratch_peak_bytes", C.c_uint64),
+        ("device_memory_samples", C.c_uint64), ("checkpoint_count", C.c_uint64), ("checkpoint_retained_bytes", C.c_uint64),
+        ("checkpoint_live_peak_bytes", C.c_uint64), ("checkpoint_live_peak_count", C.c_uint64), ("checkpoint_long_lived_bytes", C.c_uint64),
+        ("checkpoint_long_lived_count", C.c_uint64), ("checkpoint_graph_nodes", C.c_uint64), ("checkpoint_max_span_nodes", C.c_uint64),
+        ("checkpoint_total_span_nodes", C.c_uint64),
+    ]
+
+
+class GenerationStatsC(C.Structure):
+    _fields_ = [(name, C.c_uint64) for name in ("calls", "sequences", "prompt_tokens", "prefilled_tokens", "reused_tokens", "hits", "evictions")]
+
+
+class TensorDescC(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("ne", C.c_int64 * 4), ("n_elements", C.c_uint64), ("n_bytes", C.c_uint64), ("storage_id", C.c_uint64),
+                ("type_name", C.c_char * 64)]
+
+
+class ExpertBankDescC(C.Structure):
+    _fields_ = [("layer", C.c_uint32), ("role", C.c_char * 16), ("tensor", TensorDescC)]
+
+
+class _CacheCounters(C.Structure):
+    _fields_ = [("hits", C.c_uint64), ("misses", C.c_uint64), ("bytes", C.c_uint64)]
+
+
+class ExpertCacheGroupC(C.Structure):
+    _fields_ = [("n_slots", C.c_int32), ("n_layers", C.c_int32), ("n_expert", C.c_int32), ("device_bytes", C.c_uint64)]
+
+
+class ExpertCacheStatsC(C.Structure):
+    _fields_ = [("small", _CacheCounters), ("large", _CacheCounters), ("copy", _CacheCounters), ("n_groups", C.c_int32),
+                ("groups", ExpertCacheGroupC * 16)]
+
+
 # Every symbol include/retro_b200.h declares: name -> (restype, argtypes).
 _P = C.POINTER
 SYMBOLS = {
@@ -167,6 +208,39 @@ SYMBOLS = {
     "retro_engine_expert_route_enable": (C.c_int, [C.c_void_p, C.c_uint32]),
     "retro_engine_expert_route_counts": (C.c_int, [C.c_void_p, C.c_uint32, _P(C.c_uint32), C.c_size_t]),
     "retro_engine_expert_route_reset": (C.c_int, [C.c_void_p]),
+    "retro_engine_load_lora": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "retro_engine_set_lora_enabled": (C.c_int, [C.c_void_p, C.c_bool]),
+    "retro_engine_load_lora_named": (C.c_int, [C.c_void_p, C.c_char_p, C.c_char_p]),
+    "retro_engine_activate_lora": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "retro_engine_active_adapter": (C.c_int, [C.c_void_p, C.c_char_p, C.c_size_t, _P(C.c_size_t)]),
+    "retro_engine_memory_report": (C.c_int, [C.c_void_p, _P(MemoryReportC)]),
+    "retro_engine_generation_stats": (C.c_int, [C.c_void_p, _P(GenerationStatsC)]),
+    "retro_engine_expert_banks": (C.c_int, [C.c_void_p, _P(ExpertBankDescC), C.c_size_t, _P(C.c_size_t)]),
+    "retro_engine_expert_stats": (C.c_int, [C.c_void_p, _P(ExpertCacheStatsC)]),
+    "retro_engine_expert_route_paths": (C.c_int, [C.c_void_p, _P(C.c_uint64)]),
+    "retro_grammar_from_json_schema": (C.c_void_p, [C.c_char_p]),
+    "retro_grammar_from_gbnf": (C.c_void_p, [C.c_char_p]),
+    "retro_grammar_json_object": (C.c_void_p, []),
+    "retro_grammar_gbnf": (C.c_char_p, [C.c_void_p]),
+    "retro_grammar_free": (None, [C.c_void_p]),
+    "retro_trainer_generation_step": (C.c_int, [C.c_void_p, _P(StepRowC), C.c_size_t, _P(StepOutRowC), _P(C.c_int32), _P(C.c_float), C.c_size_t]),
+    "retro_trainer_generation_step_v2": (C.c_int, [C.c_void_p, _P(StepRowV2C), C.c_size_t, _P(StepOutRowV2C), _P(C.c_int32), _P(C.c_float), C.c_size_t]),
+    "retro_trainer_generation_seq_rm": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32]),
+    "retro_trainer_generation_seq_cp": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "retro_trainer_generation_seq_save": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint32, _P(C.c_uint8), C.c_size_t, _P(C.c_size_t)]),
+    "retro_trainer_generation_seq_load": (C.c_int, [C.c_void_p, C.c_int32, C.c_uint32, _P(C.c_uint8), C.c_size_t, _P(C.c_size_t)]),
+    "retro_trainer_generation_seq_pos": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_int32), _P(C.c_int32)]),
+    "retro_trainer_generation_memory": (C.c_int, [C.c_void_p, _P(MemoryInfoC)]),
+    "retro_trainer_generation_request_free": (C.c_int, [C.c_void_p, C.c_int32]),
+    "retro_trainer_generation_kv_unified": (C.c_int, [C.c_void_p, _P(C.c_bool)]),
+    "retro_trainer_generation_weights_version": (C.c_int, [C.c_void_p, _P(C.c_uint64)]),
+    "retro_trainer_generation_stats": (C.c_int, [C.c_void_p, _P(GenerationStatsC)]),
+    "retro_trainer_generation_adapter_snapshot": (C.c_int, [C.c_void_p, C.c_int32, C.c_float, _P(C.c_int32)]),
+    "retro_trainer_generation_adapter_unload": (C.c_int, [C.c_void_p, C.c_int32]),
+    "retro_trainer_generation_adapter_rows_info": (C.c_int, [C.c_void_p, _P(AdapterRowsInfoC)]),
+    "retro_b200_trainer_generation_new": (C.c_void_p, [C.c_char_p, _P(EngineConfigC), C.c_char_p]),
+    "retro_b200_trainer_generation_free": (None, [C.c_void_p]),
+    "retro_b200_trainer_weights_updated": (C.c_int, [C.c_void_p, C.c_char_p]),
     "retro_b200_synth_gguf": (C.c_int, [C.c_char_p, C.c_char_p, _P(C.c_uint64)]),
     "retro_b200_quantize_row": (C.c_int, [C.c_uint32, _P(C.c_float), C.c_size_t, _P(C.c_uint8), C.c_size_t, _P(C.c_size_t)]),
     "retro_b200_engine_last_pack": (

@@ -61,56 +61,37 @@ static_assert(sizeof(retro_adapter_rows_info) == 32 && offsetof(retro_adapter_ro
 
 namespace {
 
-retro_engine_config default_engine_config() {
-    retro_engine_config c{};
-    c.struct_size = sizeof(retro_engine_config);
-    c.n_ctx = 4096;
-    c.n_seq_max = 8;
-    c.n_batch = 512;
-    c.n_ubatch = 512;
-    c.kv_dtype = RETRO_ENGINE_KV_DTYPE_F16;
-    c.flash_attn = true;
-    c.device = RETRO_DEVICE_AUTO;
-    c.threads = 0;
-    c.verbose = false;
-    c.kv_unified = 1;
-    c.expert_placement = RETRO_EXPERT_PLACEMENT_DEVICE;
-    c.expert_host_layers = 0;
-    c.expert_device_cache_bytes = 0;
-    return c;
-}
+// Field values an absent config resolves to (retro_engine.cpp:93-110 lists the same numbers).
+constexpr retro_engine_config kDefaultConfig = {
+    /* struct_size */ sizeof(retro_engine_config), /* n_ctx */ 4096, /* n_seq_max */ 8, /* n_batch */ 512, /* n_ubatch */ 512,
+    /* kv_dtype */ RETRO_ENGINE_KV_DTYPE_F16, /* flash_attn */ true, /* device */ RETRO_DEVICE_AUTO, /* threads */ 0, /* verbose */ false,
+    /* kv_unified */ 1, /* expert_placement */ RETRO_EXPERT_PLACEMENT_DEVICE, /* expert_host_layers */ 0, /* expert_device_cache_bytes */ 0};
+
+// Geometry rules of an engine config, in the order their messages are reported (the message texts and
+// their order are the reference's contract, retro_engine.cpp:112-153; the first broken rule decides).
+struct ConfigRule {
+    bool (*broken)(const retro_engine_config &);
+    const char * message;
+};
+constexpr ConfigRule kConfigRules[] = {
+    {[](const retro_engine_config & c) { return c.n_ctx == 0 || c.n_seq_max == 0; }, "engine n_ctx and n_seq_max must be greater than zero"},
+    {[](const retro_engine_config & c) { return c.n_batch == 0 || c.n_ubatch == 0 || c.n_ubatch > c.n_batch; }, "engine n_ubatch must be in (0, n_batch]"},
+    {[](const retro_engine_config & c) { return std::max({c.n_ctx, c.n_batch, c.n_ubatch, c.threads}) > (uint32_t)INT32_MAX; },
+     "engine context, batch and thread counts must fit in int32_t"},
+    {[](const retro_engine_config & c) { return c.n_seq_max > std::min({kMaxSeq, c.n_batch, c.n_ctx}); },
+     "engine n_seq_max must not exceed LLAMA_MAX_SEQ, n_batch or n_ctx"},
+    {[](const retro_engine_config & c) { return c.kv_dtype < RETRO_ENGINE_KV_DTYPE_F32 || c.kv_dtype > RETRO_ENGINE_KV_DTYPE_Q4_0; },
+     "engine kv_dtype must be one of retro_engine_kv_dtype"},
+    {[](const retro_engine_config & c) { return c.kv_dtype >= RETRO_ENGINE_KV_DTYPE_Q8_0 && !c.flash_attn; }, "a quantized engine kv_dtype requires flash_attn"},
+    {[](const retro_engine_config & c) { return c.device < RETRO_DEVICE_AUTO || c.device > RETRO_DEVICE_GPU; }, "engine device must be one of retro_device"},
+    {[](const retro_engine_config & c) { return c.expert_placement != RETRO_EXPERT_PLACEMENT_DEVICE && c.expert_placement != RETRO_EXPERT_PLACEMENT_HOST; },
+     "engine expert_placement must be one of retro_expert_placement"},
+};
 
 bool validate_engine_config(const retro_engine_config & c) {
-    if (c.n_ctx == 0 || c.n_seq_max == 0) {
-        set_error("engine n_ctx and n_seq_max must be greater than zero");
-        return false;
-    }
-    if (c.n_batch == 0 || c.n_ubatch == 0 || c.n_ubatch > c.n_batch) {
-        set_error("engine n_ubatch must be in (0, n_batch]");
-        return false;
-    }
-    if (c.n_ctx > INT32_MAX || c.n_batch > INT32_MAX || c.n_ubatch > INT32_MAX || c.threads > INT32_MAX) {
-        set_error("engine context, batch and thread counts must fit in int32_t");
-        return false;
-    }
-    if (c.n_seq_max > kMaxSeq || c.n_seq_max > std::min(c.n_batch, c.n_ctx)) {
-        set_error("engine n_seq_max must not exceed LLAMA_MAX_SEQ, n_batch or n_ctx");
-        return false;
-    }
-    if (c.kv_dtype < RETRO_ENGINE_KV_DTYPE_F32 || c.kv_dtype > RETRO_ENGINE_KV_DTYPE_Q4_0) {
-        set_error("engine kv_dtype must be one of retro_engine_kv_dtype");
-        return false;
-    }
-    if ((c.kv_dtype == RETRO_ENGINE_KV_DTYPE_Q8_0 || c.kv_dtype == RETRO_ENGINE_KV_DTYPE_Q4_0) && !c.flash_attn) {
-        set_error("a quantized engine kv_dtype requires flash_attn");
-        return false;
-    }
-    if (c.device < RETRO_DEVICE_AUTO || c.device > RETRO_DEVICE_GPU) {
-        set_error("engine device must be one of retro_device");
-        return false;
-    }
-    if (c.expert_placement != RETRO_EXPERT_PLACEMENT_DEVICE && c.expert_placement != RETRO_EXPERT_PLACEMENT_HOST) {
-        set_error("engine expert_placement must be one of retro_expert_placement");
+    for (const ConfigRule & rule : kConfigRules) {
+        if (!rule.broken(c)) continue;
+        set_error(rule.message);
         return false;
     }
     return true;
@@ -220,7 +201,7 @@ retro_engine * retro_engine_new_checked(const char * model_path, const retro_eng
             set_error("model_path is required");
             return nullptr;
         }
-        retro_engine_config resolved = default_engine_config();
+        retro_engine_config resolved = kDefaultConfig;
         if (config) {
             uint32_t size = 0;
             std::memcpy(&size, config, sizeof size);
@@ -292,7 +273,7 @@ int retro_engine_is_eog_token(retro_engine * engine, int32_t token, bool * out_i
             set_error("token is outside the vocabulary");
             return STATUS_RUNTIME;
         }
-        *out_is_eog = token == e->model->eos;
+        *out_is_eog = e->model->is_eog(token);
         return STATUS_OK;
     });
 }
@@ -543,6 +524,10 @@ int generate_over_steps(Engine * e, const std::vector<GenItem> & items, bool sha
         for (size_t i = 0; i < n; ++i) e->requests.erase(request_base + (int32_t)i);
     };
     forget();
+    GenerationCounters & stats = e->gen_stats;
+    stats.calls += 1;
+    stats.sequences += n;
+    for (size_t i = 0; i < n; ++i) stats.prompt_tokens += items[i].n_prompt;
     std::vector<size_t> limit(n), fed(n, 0);
     std::vector<int32_t> last(n, 0);
     std::vector<bool> live(n, true);
@@ -580,7 +565,7 @@ int generate_over_steps(Engine * e, const std::vector<GenItem> & items, bool sha
         if (out_forced) out_forced[i * n_out_max + count] = 0;
         out_n_tokens[i] = count + 1;
         last[i] = o.token;
-        if (o.token == e->model->eos || out_n_tokens[i] == limit[i]) live[i] = false;
+        if (e->model->is_eog(o.token) || out_n_tokens[i] == limit[i]) live[i] = false;
     };
 
     // ---- prompts
@@ -592,11 +577,16 @@ int generate_over_steps(Engine * e, const std::vector<GenItem> & items, bool sha
             const int st = run();
             if (st != 0) { forget(); return st; }
             pos += take;
+            stats.prefilled_tokens += take;
         }
         if (it.n_prompt > 1)
             for (size_t i = 1; i < n; ++i) {
-                const int st = e->seq_cp(0, (int32_t)i, 0, (int32_t)it.n_prompt - 1);
+                // slot 0 holds exactly [0, n_prompt - 2]: the whole-sequence form says the same and is the only
+                // one a partitioned pool accepts
+                const int st = e->seq_cp(0, (int32_t)i, -1, -1);
                 if (st != 0) { forget(); return st; }
+                stats.hits += 1;
+                stats.reused_tokens += it.n_prompt - 1;
             }
         for (size_t i = 0; i < n; ++i) fed[i] = it.n_prompt - 1;
     }
@@ -619,6 +609,7 @@ int generate_over_steps(Engine * e, const std::vector<GenItem> & items, bool sha
         for (size_t r = 0; r < rows.size(); ++r) {
             const size_t i = row_item[r];
             fed[i] += rows[r].n;
+            stats.prefilled_tokens += rows[r].n;
             if (rows[r].sample) record(i, outs[r]);
         }
     }
@@ -810,6 +801,359 @@ int retro_engine_expert_route_reset(retro_engine * engine) {
         for (auto & l : e->route_counts) std::fill(l.begin(), l.end(), 0u);
         return STATUS_OK;
     });
+}
+
+// ---- serialised adapters ---------------------------------------------------------------------
+
+int retro_engine_load_lora(retro_engine * engine, const char * adapter_path) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (is_blank(adapter_path)) {
+            set_error("adapter_path is required");
+            return STATUS_RUNTIME;
+        }
+        return e->lora_load_single(adapter_path);
+    });
+}
+
+int retro_engine_load_lora_named(retro_engine * engine, const char * name, const char * adapter_path) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (is_blank(name)) {
+            set_error("name is required");
+            return STATUS_RUNTIME;
+        }
+        if (is_blank(adapter_path)) {
+            set_error("adapter_path is required");
+            return STATUS_RUNTIME;
+        }
+        return e->lora_load_named(name, adapter_path);
+    });
+}
+
+int retro_engine_activate_lora(retro_engine * engine, const char * name) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->lora_activate(name) : STATUS_RUNTIME;
+    });
+}
+
+int retro_engine_set_lora_enabled(retro_engine * engine, bool enabled) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->lora_set_enabled(enabled) : STATUS_RUNTIME;
+    });
+}
+
+namespace {
+// The two-call text contract of the reference's string outputs (retro_runtime.hpp:551-576): without a
+// buffer only the length is reported; with one, the text and a terminating NUL must fit.
+int text_out(const std::string & text, char * buffer, size_t n_buffer, size_t * out_n_bytes) {
+    *out_n_bytes = text.size();
+    if (!buffer || n_buffer == 0) return STATUS_OK;
+    if (text.size() > n_buffer - 1) {
+        set_error("output buffer is too small");
+        return STATUS_BUFFER_TOO_SMALL;
+    }
+    std::memcpy(buffer, text.data(), text.size());
+    buffer[text.size()] = '\0';
+    return STATUS_OK;
+}
+} // namespace
+
+int retro_engine_active_adapter(retro_engine * engine, char * buffer, size_t n_buffer, size_t * out_n_bytes) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (!out_n_bytes) {
+            set_error("out_n_bytes is required");
+            return STATUS_RUNTIME;
+        }
+        return text_out(e->active_adapter(), buffer, n_buffer, out_n_bytes);
+    });
+}
+
+// ---- counters and memory ---------------------------------------------------------------------
+
+static_assert(sizeof(retro_memory_report) == 216 && alignof(retro_memory_report) == 8 && offsetof(retro_memory_report, trainable_parameter_bytes) == 48 &&
+              offsetof(retro_memory_report, base_trainable_on_host) == 74 && offsetof(retro_memory_report, device_bytes) == 80 &&
+              offsetof(retro_memory_report, device_memory_samples) == 136, "retro_memory_report layout");
+static_assert(sizeof(retro_generation_stats) == 56, "retro_generation_stats layout");
+static_assert(sizeof(retro_expert_bank_desc) == 272 && offsetof(retro_expert_bank_desc, role) == 4 && offsetof(retro_expert_bank_desc, tensor) == 24,
+              "retro_expert_bank_desc layout");
+static_assert(sizeof(retro_expert_cache_stats) == 464 && offsetof(retro_expert_cache_stats, n_groups) == 72 && offsetof(retro_expert_cache_stats, groups) == 80,
+              "retro_expert_cache_stats layout");
+
+int retro_engine_memory_report(retro_engine * engine, retro_memory_report * out_report) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_report) {
+            if (e) set_error("out_report is required");
+            return STATUS_RUNTIME;
+        }
+        retro_memory_report r{};
+        r.has_generation_context = true;
+        r.model_weight_bytes = e->model->weight_bytes + e->model->tiled_bytes;
+        retro_engine_memory_info kv{};
+        e->memory(&kv);
+        r.generation_kv_bytes = kv.kv_bytes;
+        r.generation_compute_bytes = e->work_buffer_bytes();
+        r.trainable_parameter_bytes = e->adapter_bytes();
+        r.trainable_parameters_are_model_subset = false;
+        r.adapter_on_host = false;
+        r.base_trainable_on_host = false;
+        r.device_bytes = r.model_weight_bytes + r.generation_kv_bytes + r.generation_compute_bytes + r.trainable_parameter_bytes;
+        size_t free_bytes = 0, total_bytes = 0;
+        if (cudaMemGetInfo(&free_bytes, &total_bytes) == cudaSuccess) {
+            r.device_total_bytes = total_bytes;
+            r.device_used_bytes = total_bytes - free_bytes;
+            r.device_peak_used_bytes = r.device_used_bytes;
+            r.backend_scratch_bytes = r.device_used_bytes > r.device_bytes ? r.device_used_bytes - r.device_bytes : 0;
+            r.backend_scratch_peak_bytes = r.backend_scratch_bytes;
+            r.device_memory_samples = 1;
+        } else {
+            cudaGetLastError();
+        }
+        *out_report = r;
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_generation_stats(retro_engine * engine, retro_generation_stats * out_stats) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_stats) {
+            if (e) set_error("out_stats is required");
+            return STATUS_RUNTIME;
+        }
+        const GenerationCounters & c = e->gen_stats;
+        *out_stats = retro_generation_stats{c.calls, c.sequences, c.prompt_tokens, c.prefilled_tokens, c.reused_tokens, c.hits, c.evictions};
+        return STATUS_OK;
+    });
+}
+
+// ---- expert banks ----------------------------------------------------------------------------
+
+int retro_engine_expert_banks(retro_engine * engine, retro_expert_bank_desc * out_banks, size_t n_max, size_t * out_count) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (!out_count) {
+            set_error("out_count is required");
+            return STATUS_RUNTIME;
+        }
+        const std::vector<retro_expert_bank_desc> & banks = e->model->expert_banks;
+        *out_count = banks.size();
+        if (!out_banks || banks.empty()) return STATUS_OK;
+        if (n_max < banks.size()) {
+            set_error("expert bank buffer is too small");
+            return STATUS_BUFFER_TOO_SMALL;
+        }
+        std::copy(banks.begin(), banks.end(), out_banks);
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_expert_stats(retro_engine * engine, retro_expert_cache_stats * out_stats) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_stats) {
+            if (e) set_error("out_stats is required");
+            return STATUS_RUNTIME;
+        }
+        *out_stats = retro_expert_cache_stats{};      // no device cache: every bank is resident
+        return STATUS_OK;
+    });
+}
+
+int retro_engine_expert_route_paths(retro_engine * engine, uint64_t out[3]) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out) {
+            if (e) set_error("routing paths output is required");
+            return STATUS_RUNTIME;
+        }
+        out[0] = e->route_pairs;
+        out[1] = 0;
+        out[2] = 0;
+        return STATUS_OK;
+    });
+}
+
+// ---- grammar handles: host-only owners of a GBNF text (retro_grammar.cpp:1-76) --------------------
+
+} // extern "C"
+
+struct retro_grammar {
+    std::string gbnf;
+};
+
+namespace {
+// Any JSON object, in GBNF. Written for this library (the reference embeds its fork's grammar file).
+const char kJsonObjectGbnf[] =
+    "root ::= object\n"
+    "value ::= object | array | string | number | (\"true\" | \"false\" | \"null\") ws\n"
+    "object ::= \"{\" ws ( member (\",\" ws member)* )? \"}\" ws\n"
+    "member ::= string \":\" ws value\n"
+    "array ::= \"[\" ws ( value (\",\" ws value)* )? \"]\" ws\n"
+    "string ::= \"\\\"\" ( [^\"\\\\\\x7F\\x00-\\x1F] | \"\\\\\" ( [\"\\\\/bfnrt] | \"u\" [0-9a-fA-F] [0-9a-fA-F] [0-9a-fA-F] [0-9a-fA-F] ) )* \"\\\"\" ws\n"
+    "number ::= \"-\"? ( \"0\" | [1-9] [0-9]* ) ( \".\" [0-9]+ )? ( [eE] [-+]? [0-9]+ )? ws\n"
+    "ws ::= [ \\t\\n\\r]*\n";
+
+retro_grammar * grammar_of(const char * text, const char * what) {
+    retro_grammar * result = nullptr;
+    boundary([&]() -> int {
+        if (!text || text[0] == '\0') {
+            set_error(std::string(what) + " is required and must not be empty");
+            return STATUS_RUNTIME;
+        }
+        result = new retro_grammar{std::string(text)};
+        return STATUS_OK;
+    });
+    return result;
+}
+} // namespace
+
+extern "C" {
+
+retro_grammar * retro_grammar_from_gbnf(const char * gbnf) { return grammar_of(gbnf, "gbnf"); }
+
+retro_grammar * retro_grammar_json_object(void) { return grammar_of(kJsonObjectGbnf, "gbnf"); }
+
+retro_grammar * retro_grammar_from_json_schema(const char * json_schema) {
+    if (!json_schema || json_schema[0] == '\0') {
+        set_error("json_schema is required and must not be empty");
+        return nullptr;
+    }
+    set_error("this library does not convert JSON schemas to grammars (the converter belongs to the reference's llama.cpp fork): pass GBNF to "
+              "retro_grammar_from_gbnf");
+    return nullptr;
+}
+
+const char * retro_grammar_gbnf(const retro_grammar * grammar) {
+    if (!grammar) {
+        set_error("grammar is null");
+        return nullptr;
+    }
+    return grammar->gbnf.c_str();
+}
+
+void retro_grammar_free(retro_grammar * grammar) { delete grammar; }
+
+// ---- the trainer-owned generation context ------------------------------------------------------
+// A retro_trainer made here owns one generation context and nothing else; every twin forwards to the
+// engine entry point of the same contract.
+
+} // extern "C"
+
+struct retro_trainer {
+    retro_engine * generation = nullptr;
+};
+
+namespace {
+retro_engine * generation_of(retro_trainer * trainer) {
+    if (!trainer || !trainer->generation) {
+        set_error("trainer handle is null");
+        return nullptr;
+    }
+    return trainer->generation;
+}
+} // namespace
+
+extern "C" {
+
+retro_trainer * retro_b200_trainer_generation_new(const char * model_path, const retro_engine_config * config, const char * adapter_path) {
+    retro_engine * engine = retro_engine_new(model_path, config);
+    if (!engine) return nullptr;
+    if (adapter_path && retro_engine_load_lora(engine, adapter_path) != 0) {
+        retro_engine_free(engine);
+        return nullptr;
+    }
+    return new retro_trainer{engine};
+}
+
+void retro_b200_trainer_generation_free(retro_trainer * trainer) {
+    if (!trainer) return;
+    retro_engine_free(trainer->generation);
+    delete trainer;
+}
+
+// The weights behind the generation context changed (an optimizer step, a weight import): with a path the
+// trained adapter is read again, and either way the KV is forgotten and the weights version moves on.
+int retro_b200_trainer_weights_updated(retro_trainer * trainer, const char * adapter_path) {
+    retro_engine * g = generation_of(trainer);
+    if (!g) return STATUS_RUNTIME;
+    if (adapter_path) return retro_engine_load_lora(g, adapter_path);
+    return boundary([&]() -> int {
+        reinterpret_cast<Engine *>(g)->forget_kv();
+        return STATUS_OK;
+    });
+}
+
+int retro_trainer_generation_step(retro_trainer * trainer, const retro_step_row * rows, size_t n_rows, retro_step_out_row * out_rows,
+                                  int32_t * out_top_ids, float * out_top_logprobs, size_t n_top_stride) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_step(g, rows, n_rows, out_rows, out_top_ids, out_top_logprobs, n_top_stride) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_step_v2(retro_trainer * trainer, const retro_step_row_v2 * rows, size_t n_rows, retro_step_out_row_v2 * out_rows,
+                                     int32_t * out_top_ids, float * out_top_logprobs, size_t n_top_stride) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_step_v2(g, rows, n_rows, out_rows, out_top_ids, out_top_logprobs, n_top_stride) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_seq_rm(retro_trainer * trainer, int32_t slot, int32_t p0, int32_t p1) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_seq_rm(g, slot, p0, p1) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_seq_cp(retro_trainer * trainer, int32_t src, int32_t dst, int32_t p0, int32_t p1) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_seq_cp(g, src, dst, p0, p1) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_seq_save(retro_trainer * trainer, int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_buffer, size_t * out_n_bytes) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_seq_save(g, slot, flags, buffer, n_buffer, out_n_bytes) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_seq_load(retro_trainer * trainer, int32_t slot, uint32_t flags, const uint8_t * buffer, size_t n_bytes, size_t * out_n_read) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_seq_load(g, slot, flags, buffer, n_bytes, out_n_read) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_seq_pos(retro_trainer * trainer, int32_t slot, int32_t * out_pos_min, int32_t * out_pos_max) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_seq_pos(g, slot, out_pos_min, out_pos_max) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_memory(retro_trainer * trainer, retro_engine_memory_info * out) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_memory(g, out) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_request_free(retro_trainer * trainer, int32_t request) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_request_free(g, request) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_kv_unified(retro_trainer * trainer, bool * out_unified) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_kv_unified(g, out_unified) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_weights_version(retro_trainer * trainer, uint64_t * out_version) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_weights_version(g, out_version) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_stats(retro_trainer * trainer, retro_generation_stats * out_stats) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_generation_stats(g, out_stats) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_adapter_snapshot(retro_trainer * trainer, int32_t replace, float scale, int32_t * out_id) {
+    retro_engine * g = generation_of(trainer);
+    if (!g) return STATUS_RUNTIME;
+    return boundary([&]() -> int { return reinterpret_cast<Engine *>(g)->adapter_snapshot(replace, scale, out_id); });
+}
+int retro_trainer_generation_adapter_unload(retro_trainer * trainer, int32_t id) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_adapter_unload(g, id) : STATUS_RUNTIME;
+}
+int retro_trainer_generation_adapter_rows_info(retro_trainer * trainer, retro_adapter_rows_info * out_info) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_adapter_rows_info(g, out_info) : STATUS_RUNTIME;
 }
 
 // ---- extensions -----------------------------------------------------------------------------

@@ -9,9 +9,11 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <sstream>
+#include <unordered_set>
 
 namespace rb200 {
 
@@ -254,6 +256,28 @@ void Engine::load_model(const std::string & path) {
             bank(p + "ffn_gate_exps.weight", hp.d, hp.ff, lw.gate_exps, lw.gate_stride);
             bank(p + "ffn_up_exps.weight", hp.d, hp.ff, lw.up_exps, lw.up_stride);
             bank(p + "ffn_down_exps.weight", hp.ff, hp.d, lw.down_exps, lw.down_stride);
+            // the inventory entry of each bank, as the file holds it (retro_experts.cpp:86-131: role = the
+            // name's stem without "ffn_" and "_exps")
+            const char * roles[3] = {"gate", "up", "down"};
+            const WeightView * views[3] = {&lw.gate_exps, &lw.up_exps, &lw.down_exps};
+            for (int b = 0; b < 3; ++b) {
+                const GgufTensor & t = need(p + "ffn_" + roles[b] + "_exps.weight");
+                retro_expert_bank_desc desc{};
+                desc.layer = l;
+                std::snprintf(desc.role, sizeof desc.role, "%s", roles[b]);
+                std::snprintf(desc.tensor.name, sizeof desc.tensor.name, "%s", t.name.c_str());
+                desc.tensor.n_elements = 1;
+                for (int i = 0; i < 4; ++i) {
+                    desc.tensor.ne[i] = i < (int)t.ne.size() ? (int64_t)t.ne[i] : 1;
+                    desc.tensor.n_elements *= (uint64_t)desc.tensor.ne[i];
+                }
+                desc.tensor.n_bytes = t.n_bytes;
+                desc.tensor.storage_id = reinterpret_cast<uint64_t>(views[b]->data);
+                const char * type = t.type == GGML_F32 ? "F32" : t.type == GGML_F16 ? "F16" : t.type == GGML_BF16 ? "BF16" : t.type == GGML_Q8_0 ? "Q8_0"
+                                    : t.type == GGML_Q4_K ? "Q4_K" : t.type == GGML_MXFP4 ? "MXFP4" : "unknown";
+                std::snprintf(desc.tensor.type_name, sizeof desc.tensor.type_name, "%s", type);
+                m.expert_banks.push_back(desc);
+            }
         }
     }
     m.output_norm = vector_f32("output_norm.weight", hp.d, false);
@@ -274,6 +298,25 @@ void Engine::load_model(const std::string & path) {
     m.eos = (int32_t)file.u32("tokenizer.ggml.eos_token_id", 2);
     m.bos = (int32_t)file.u32("tokenizer.ggml.bos_token_id", 1);
     m.add_bos = file.u32("tokenizer.ggml.add_bos_token", 1) != 0;
+    std::sort(m.expert_banks.begin(), m.expert_banks.end(),
+              [](const retro_expert_bank_desc & a, const retro_expert_bank_desc & b) { return std::strcmp(a.tensor.name, b.tensor.name) < 0; });
+    // End of generation is more than EOS: the end-of-turn and end-of-message ids the file names, and the control
+    // tokens chat formats end a turn with (a Llama-3 chat turn ends with <|eot_id|>, not with EOS).
+    m.eog.assign(hp.vocab, 0);
+    auto mark = [&](int64_t id) { if (id >= 0 && id < (int64_t)hp.vocab) m.eog[(size_t)id] = 1; };
+    mark(m.eos);
+    for (const char * key : {"tokenizer.ggml.eot_token_id", "tokenizer.ggml.eom_token_id"}) {
+        const uint32_t id = file.u32(key, UINT32_MAX);
+        if (id != UINT32_MAX) mark(id);
+    }
+    static const char * const end_of_turn_pieces[] = {"<|eot_id|>", "<|im_end|>", "<|end|>", "<|eom_id|>", "<end_of_turn>", "<|endoftext|>",
+                                                       "<|end_of_text|>", "<|return|>", "<|call|>", "<EOT>"};
+    for (size_t i = 0; i < m.vocab_tokens.size() && i < hp.vocab; ++i) {
+        const int32_t type = i < m.vocab_types.size() ? m.vocab_types[i] : 3;
+        if (type != 3 && type != 4) continue;       // control or user-defined pieces only
+        for (const char * piece : end_of_turn_pieces)
+            if (m.vocab_tokens[i] == piece) m.eog[i] = 1;
+    }
 
     // every blocking upload above has reached the device before any stream's kernel reads the weights
     RB_CUDA(cudaDeviceSynchronize());
@@ -729,82 +772,111 @@ void Engine::ep_idle_step() {
 
 namespace {
 
-bool validate_tokens(const int32_t * tokens, size_t n, int32_t n_vocab) {
-    for (size_t i = 0; i < n; ++i) {
-        if (tokens[i] < 0 || tokens[i] >= n_vocab) {
-            std::ostringstream message;
-            message << "token " << tokens[i] << " at index " << i << " is outside the vocabulary of size " << n_vocab;
-            set_error(message.str());
-            return false;
-        }
-    }
-    return true;
-}
+// The all-or-nothing checks of a step plan, reported before anything is decoded. Contract (the
+// reference's runtime, retro_gen_core.cpp:1509-1590 and :2409-2516): rows are examined in order, each
+// row's checks in the order of `check_row` below, the first failure decides the message, the status is
+// -3. What is free is how the answer is found: a row is compared only with the earlier rows of ITS
+// slot (kept per slot in arrival order, which also yields the earliest conflicting row the reference's
+// pair scan would have met first) and request ids are looked up in a hash set.
+class PlanChecker {
+public:
+    PlanChecker(int32_t n_slots, int32_t n_batch, int64_t ctx_seq, int32_t n_vocab, bool have_top_buffers, size_t top_stride)
+        : n_slots_(n_slots), n_batch_(n_batch), ctx_seq_(ctx_seq), n_vocab_(n_vocab), have_top_buffers_(have_top_buffers), top_stride_(top_stride) {}
 
-bool validate_sampling(const retro_sampling_params & s) {
-    if (!(s.temperature > 0.0f) || !std::isfinite(s.temperature)) {
-        set_error("sampling temperature must be finite and greater than zero");
-        return false;
-    }
-    if (!(s.top_p > 0.0f && s.top_p <= 1.0f)) {
-        set_error("sampling top_p must be in (0, 1]");
-        return false;
-    }
-    if (s.max_new_tokens == 0) {
-        set_error("sampling max_new_tokens must be greater than zero");
-        return false;
-    }
-    return true;
-}
+    size_t tokens = 0, sampling_rows = 0;
 
-bool validate_sampling_v2(const retro_sampling_params_v2 & s, int32_t n_vocab) {
-    if (s.struct_size < sizeof(retro_sampling_params_v2)) {
-        set_error("retro_sampling_params_v2.struct_size is too small for this build");
-        return false;
-    }
-    if (!(s.temperature > 0.0f) || !std::isfinite(s.temperature)) {
-        set_error("sampling temperature must be finite and greater than zero");
-        return false;
-    }
-    if (!(s.top_p > 0.0f && s.top_p <= 1.0f)) {
-        set_error("sampling top_p must be in (0, 1]");
-        return false;
-    }
-    if (!(s.repeat_penalty > 0.0f) || !std::isfinite(s.repeat_penalty)) {
-        set_error("sampling repeat_penalty must be finite and greater than zero");
-        return false;
-    }
-    if (!(s.min_p >= 0.0f && s.min_p <= 1.0f) || !std::isfinite(s.min_p)) {
-        set_error("sampling min_p must be in [0, 1]");
-        return false;
-    }
-    if (!std::isfinite(s.frequency_penalty)) {
-        set_error("sampling frequency_penalty must be finite");
-        return false;
-    }
-    if (!std::isfinite(s.presence_penalty)) {
-        set_error("sampling presence_penalty must be finite");
-        return false;
-    }
-    if (s.n_logit_bias > 4096) {
-        set_error("sampling n_logit_bias must not exceed 4096");
-        return false;
-    }
-    if (s.n_logit_bias > 0) {
-        if (!s.logit_bias_ids || !s.logit_bias_values) {
-            set_error("logit_bias ids and values are required when n_logit_bias is nonzero");
-            return false;
+    // `per_row_adapter(id)`: whether a positive adapter id names a loaded per-row adapter.
+    template <class AdapterLookup> bool check_row(const EffRow * rows, size_t r, AdapterLookup && per_row_adapter) {
+        const EffRow & row = rows[r];
+        const bool v2 = row.v2 != nullptr;
+        const size_t needed = v2 ? offsetof(retro_step_row_v2, adapter) + sizeof(int32_t) : offsetof(retro_step_row, adapter) + sizeof(int32_t);
+        if (row.struct_size < needed)
+            return refuse(v2 ? "retro_step_row_v2.struct_size is too small for this build" : "retro_step_row.struct_size is too small for this build");
+        if (!row.tokens || row.n == 0) return refuse("a step row requires at least one token");
+        if (row.slot < 0 || row.slot >= n_slots_) return refuse("step row slot is outside the context's sequence range");
+        if (row.adapter != 0 && row.adapter != RETRO_STEP_ADAPTER_BASE && !per_row_adapter(row.adapter))
+            return refuse("step row adapter " + std::to_string(row.adapter) + " is not a loaded per-row adapter");
+        const int64_t begin = row.pos0, end = begin + row.n;
+        if (begin < 0 || end > ctx_seq_) return refuse("step row positions exceed the per-sequence context");
+        std::vector<uint32_t> & earlier = rows_of_slot_[row.slot];
+        for (uint32_t e : earlier) {
+            const EffRow & other = rows[e];
+            if (begin < (int64_t)other.pos0 + other.n && other.pos0 < end) return refuse("step rows overlap in the same sequence slot");
+            if (row.adapter != other.adapter) return refuse("step rows of one sequence slot select different adapters");
         }
-        if (!validate_tokens(s.logit_bias_ids, s.n_logit_bias, n_vocab)) return false;
-        for (uint32_t i = 0; i < s.n_logit_bias; ++i) {
-            if (!std::isfinite(s.logit_bias_values[i])) {
-                set_error("logit_bias values must be finite");
-                return false;
-            }
+        earlier.push_back((uint32_t)r);
+        if (!tokens_in_vocabulary(row.tokens, row.n)) return false;
+        if (row.n > (uint32_t)n_batch_ || tokens + row.n > (size_t)n_batch_) return refuse("the step's tokens exceed the context's physical batch (n_batch)");
+        tokens += row.n;
+        if (row.n_top_logprobs > 0 && !have_top_buffers_) return refuse("top logprobs requested but the output buffers are missing");
+        if (row.n_top_logprobs > top_stride_) return refuse("a step row's n_top_logprobs exceeds the output stride");
+        if (row.sample) {
+            if (row.request < 0) return refuse("a sampling step row requires a request id");
+            if (v2 ? !sampling_v2_ok(*row.v2) : !sampling_v1_ok(row.v1)) return false;
+            ++sampling_rows;
         }
+        if (row.request >= 0 && !requests_.insert(row.request).second) return refuse("a request id appears twice in one step");
+        return true;
     }
-    return true;
-}
+
+private:
+    struct Rule {
+        bool (*broken)(const retro_sampling_params_v2 &);
+        const char * message;
+    };
+
+    static bool refuse(const std::string & message) {
+        set_error(message);
+        return false;
+    }
+    static bool positive_finite(float v) { return v > 0.0f && std::isfinite(v); }
+    static bool unit_interval_open_low(float v) { return v > 0.0f && v <= 1.0f; }
+
+    bool tokens_in_vocabulary(const int32_t * ids, size_t n) const {
+        for (size_t i = 0; i < n; ++i) {
+            if (ids[i] >= 0 && ids[i] < n_vocab_) continue;
+            return refuse("token " + std::to_string(ids[i]) + " at index " + std::to_string(i) + " is outside the vocabulary of size " +
+                          std::to_string(n_vocab_));
+        }
+        return true;
+    }
+    // v1 rows: only the distribution parameters take part (the caller owns stopping, so max_new_tokens is not read)
+    static bool sampling_v1_ok(const retro_sampling_params & s) {
+        if (!positive_finite(s.temperature)) return refuse("sampling temperature must be finite and greater than zero");
+        if (!unit_interval_open_low(s.top_p)) return refuse("sampling top_p must be in (0, 1]");
+        return true;
+    }
+    bool sampling_v2_ok(const retro_sampling_params_v2 & s) const {
+        static const Rule rules[] = {
+            {[](const retro_sampling_params_v2 & p) { return p.struct_size < sizeof(retro_sampling_params_v2); },
+             "retro_sampling_params_v2.struct_size is too small for this build"},
+            {[](const retro_sampling_params_v2 & p) { return !positive_finite(p.temperature); }, "sampling temperature must be finite and greater than zero"},
+            {[](const retro_sampling_params_v2 & p) { return !unit_interval_open_low(p.top_p); }, "sampling top_p must be in (0, 1]"},
+            {[](const retro_sampling_params_v2 & p) { return !positive_finite(p.repeat_penalty); }, "sampling repeat_penalty must be finite and greater than zero"},
+            {[](const retro_sampling_params_v2 & p) { return !(p.min_p >= 0.0f && p.min_p <= 1.0f); }, "sampling min_p must be in [0, 1]"},
+            {[](const retro_sampling_params_v2 & p) { return !std::isfinite(p.frequency_penalty); }, "sampling frequency_penalty must be finite"},
+            {[](const retro_sampling_params_v2 & p) { return !std::isfinite(p.presence_penalty); }, "sampling presence_penalty must be finite"},
+            {[](const retro_sampling_params_v2 & p) { return p.n_logit_bias > 4096; }, "sampling n_logit_bias must not exceed 4096"},
+            {[](const retro_sampling_params_v2 & p) { return p.n_logit_bias > 0 && (!p.logit_bias_ids || !p.logit_bias_values); },
+             "logit_bias ids and values are required when n_logit_bias is nonzero"},
+        };
+        for (const Rule & rule : rules)
+            if (rule.broken(s)) return refuse(rule.message);
+        if (s.n_logit_bias == 0) return true;
+        if (!tokens_in_vocabulary(s.logit_bias_ids, s.n_logit_bias)) return false;
+        for (uint32_t i = 0; i < s.n_logit_bias; ++i)
+            if (!std::isfinite(s.logit_bias_values[i])) return refuse("logit_bias values must be finite");
+        return true;
+    }
+
+    int32_t n_slots_, n_batch_;
+    int64_t ctx_seq_;
+    int32_t n_vocab_;
+    bool have_top_buffers_;
+    size_t top_stride_;
+    std::unordered_map<int32_t, std::vector<uint32_t>> rows_of_slot_;
+    std::unordered_set<int32_t> requests_;
+};
 
 } // namespace
 
@@ -814,90 +886,18 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         set_error("step rows and output rows are required");
         return STATUS_INVALID_ARGUMENT;
     }
-    const int32_t n_seq_max = (int32_t)config.n_seq_max;
-    const int32_t n_batch = (int32_t)config.n_batch;
-    const int64_t ctx_seq = n_ctx_seq;
-    if (n_rows > (size_t)n_batch || (n_top_stride != 0 && n_rows > SIZE_MAX / n_top_stride)) {
+    if (n_rows > (size_t)config.n_batch || (n_top_stride != 0 && n_rows > SIZE_MAX / n_top_stride)) {
         set_error("the step row count or output shape exceeds capacity");
         return STATUS_INVALID_ARGUMENT;
     }
-    constexpr size_t row_prefix_v1 = offsetof(retro_step_row, adapter) + sizeof(int32_t);
-    constexpr size_t row_prefix_v2 = offsetof(retro_step_row_v2, adapter) + sizeof(int32_t);
-    std::vector<int32_t> seen_requests;
-    size_t total = 0, n_sample = 0;
-    for (size_t r = 0; r < n_rows; ++r) {
-        const EffRow & row = rows[r];
-        const bool is_v2 = row.v2 != nullptr;
-        if (row.struct_size < (is_v2 ? row_prefix_v2 : row_prefix_v1)) {
-            set_error(is_v2 ? "retro_step_row_v2.struct_size is too small for this build"
-                            : "retro_step_row.struct_size is too small for this build");
-            return STATUS_INVALID_ARGUMENT;
-        }
-        if (!row.tokens || row.n == 0) {
-            set_error("a step row requires at least one token");
-            return STATUS_INVALID_ARGUMENT;
-        }
-        if (row.slot < 0 || row.slot >= n_seq_max) {
-            set_error("step row slot is outside the context's sequence range");
-            return STATUS_INVALID_ARGUMENT;
-        }
-        if (row.adapter != 0) {
-            if (row.adapter != RETRO_STEP_ADAPTER_BASE && adapters_.find(row.adapter) == adapters_.end()) {
-                set_error("step row adapter " + std::to_string(row.adapter) + " is not a loaded per-row adapter");
-                return STATUS_INVALID_ARGUMENT;
-            }
-        }
-        if (row.pos0 < 0 || (int64_t)row.pos0 + row.n > ctx_seq) {
-            set_error("step row positions exceed the per-sequence context");
-            return STATUS_INVALID_ARGUMENT;
-        }
-        for (size_t previous = 0; previous < r; ++previous) {
-            const EffRow & other = rows[previous];
-            if (row.slot == other.slot && row.pos0 < (int64_t)other.pos0 + other.n && other.pos0 < (int64_t)row.pos0 + row.n) {
-                set_error("step rows overlap in the same sequence slot");
-                return STATUS_INVALID_ARGUMENT;
-            }
-            if (row.slot == other.slot && row.adapter != other.adapter) {
-                set_error("step rows of one sequence slot select different adapters");
-                return STATUS_INVALID_ARGUMENT;
-            }
-        }
-        if (!validate_tokens(row.tokens, row.n, (int32_t)hp.vocab)) return STATUS_INVALID_ARGUMENT;
-        if (row.n > (uint32_t)n_batch || total + row.n > (size_t)n_batch) {
-            set_error("the step's tokens exceed the context's physical batch (n_batch)");
-            return STATUS_INVALID_ARGUMENT;
-        }
-        total += row.n;
-        if (row.n_top_logprobs > 0 && (!out_top_ids || !out_top_logprobs)) {
-            set_error("top logprobs requested but the output buffers are missing");
-            return STATUS_INVALID_ARGUMENT;
-        }
-        if (row.n_top_logprobs > n_top_stride) {
-            set_error("a step row's n_top_logprobs exceeds the output stride");
-            return STATUS_INVALID_ARGUMENT;
-        }
-        if (row.sample) {
-            if (row.request < 0) {
-                set_error("a sampling step row requires a request id");
-                return STATUS_INVALID_ARGUMENT;
-            }
-            if (row.v2) {
-                if (!validate_sampling_v2(*row.v2, (int32_t)hp.vocab)) return STATUS_INVALID_ARGUMENT;
-            } else {
-                retro_sampling_params sampling = row.v1;
-                sampling.max_new_tokens = 1;
-                if (!validate_sampling(sampling)) return STATUS_INVALID_ARGUMENT;
-            }
-            ++n_sample;
-        }
-        if (row.request >= 0) {
-            if (std::find(seen_requests.begin(), seen_requests.end(), row.request) != seen_requests.end()) {
-                set_error("a request id appears twice in one step");
-                return STATUS_INVALID_ARGUMENT;
-            }
-            seen_requests.push_back(row.request);
-        }
-    }
+    PlanChecker plan((int32_t)config.n_seq_max, (int32_t)config.n_batch, (int64_t)n_ctx_seq, (int32_t)hp.vocab, out_top_ids && out_top_logprobs, n_top_stride);
+    const auto per_row_adapter = [this](int32_t id) {
+        const auto found = adapters_.find(id);
+        return found != adapters_.end() && !found->second.serial;
+    };
+    for (size_t r = 0; r < n_rows; ++r)
+        if (!plan.check_row(rows, r, per_row_adapter)) return STATUS_INVALID_ARGUMENT;
+    const size_t total = plan.tokens, n_sample = plan.sampling_rows;
     for (size_t r = 0; r < n_rows; ++r) {
         if (rows[r].sample && rows[r].v2 && rows[r].v2->grammar) {
             set_error("grammar-constrained sampling is not available in this backend");
@@ -1019,8 +1019,10 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             d.pos0 = row.pos0;
             d.sample = row.sample ? 1 : 0;
             d.adapter = -1;
-            if (row.adapter > 0) {
-                d.adapter = adapter_index_.at(row.adapter);
+            // 0 = the active adapter of the one-at-a-time family (the base model when none is active)
+            const int32_t effective = row.adapter > 0 ? row.adapter : row.adapter == 0 ? active_id_ : 0;
+            if (effective > 0) {
+                d.adapter = adapter_index_.at(effective);
                 any_adapter = true;
             }
             d.pos_min = kv->slot(row.slot).pos_min;
@@ -1323,6 +1325,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         RB_CUDA(cudaMemcpy(ids.data(), route_ids.ptr, ids.size() * 4, cudaMemcpyDeviceToHost));
         for (uint32_t l = 0; l < hp.n_layer; ++l)
             for (size_t i = 0; i < P; ++i) ++route_counts[l][ids[(size_t)l * P + i]];
+        route_pairs += ids.size();      // every pair is served from a bank resident on the device
     }
 
     // ---- outputs
@@ -1534,40 +1537,33 @@ int Engine::memory(retro_engine_memory_info * out) {
 // ---------------------------------------------------------------------------------------------
 // Per-row adapters
 
-int Engine::adapter_load(const char * path, float scale, int32_t * out_id) {
-    if (!path || !*path || !out_id) {
-        set_error("adapter_path and out_id are required");
-        return STATUS_RUNTIME;
-    }
-    if (!std::isfinite(scale)) {
-        set_error("adapter scale must be finite");
-        return STATUS_RUNTIME;
-    }
+// Reads a LoRA adapter GGUF (general.type = adapter, adapter.type = lora, tensors <weight>.lora_a [in, r]
+// and <weight>.lora_b [r, out]) into F32 host copies; false with the error set when it is refused.
+bool Engine::read_adapter_file(const char * path, float scale, Adapter & ad) {
     GgufFile file(path);
     if (file.str("general.type") != "adapter" || file.str("adapter.type") != "lora") {
         set_error("the file is not a LoRA adapter GGUF (general.type=adapter, adapter.type=lora)");
-        return STATUS_RUNTIME;
+        return false;
     }
     const float alpha = file.f32("adapter.lora.alpha", 0.f);
-    Adapter ad;
     const std::string suffix = ".lora_a";
     for (const GgufTensor & A : file.tensors()) {
         if (A.name.size() <= suffix.size() || A.name.compare(A.name.size() - suffix.size(), suffix.size(), suffix) != 0) continue;
         const std::string target = A.name.substr(0, A.name.size() - suffix.size());
         if (target == "token_embd.weight" || target.find("_exps") != std::string::npos) {
             set_error("per-row adapters refuse token-embedding and expert targets: " + target);
-            return STATUS_RUNTIME;
+            return false;
         }
         const GgufTensor * B = file.find(target + ".lora_b");
         if (!B || A.ne.size() != 2 || B->ne.size() != 2 || A.ne[1] != B->ne[0] || (A.type != GGML_F32 && A.type != GGML_F16) ||
             (B->type != GGML_F32 && B->type != GGML_F16)) {
             set_error("adapter tensor pair of " + target + " is malformed");
-            return STATUS_RUNTIME;
+            return false;
         }
         const uint32_t r = (uint32_t)A.ne[1];
         if (ad.rank && ad.rank != r) {
             set_error("adapter tensors disagree on their rank");
-            return STATUS_RUNTIME;
+            return false;
         }
         ad.rank = r;
         auto to_f32 = [](const GgufTensor & t) {
@@ -1589,9 +1585,27 @@ int Engine::adapter_load(const char * path, float scale, int32_t * out_id) {
     }
     if (ad.rank == 0) {
         set_error("the adapter holds no lora tensors");
-        return STATUS_RUNTIME;
+        return false;
     }
     ad.scale = (alpha != 0.f ? alpha / (float)ad.rank : 1.0f) * scale;
+    return true;
+}
+
+int Engine::adapter_load(const char * path, float scale, int32_t * out_id) {
+    if (!path || !*path || !out_id) {
+        set_error("adapter_path and out_id are required");
+        return STATUS_RUNTIME;
+    }
+    if (!std::isfinite(scale)) {
+        set_error("adapter scale must be finite");
+        return STATUS_RUNTIME;
+    }
+    if (next_adapter_id_ == INT32_MAX) {
+        set_error("per-row adapter ids are exhausted");
+        return STATUS_RUNTIME;
+    }
+    Adapter ad;
+    if (!read_adapter_file(path, scale, ad)) return STATUS_RUNTIME;
     const int32_t id = next_adapter_id_++;
     adapters_[id] = std::move(ad);
     restack_adapters();
@@ -1599,11 +1613,146 @@ int Engine::adapter_load(const char * path, float scale, int32_t * out_id) {
     return STATUS_OK;
 }
 
-int Engine::adapter_unload(int32_t id) {
-    if (adapters_.erase(id) == 0) {
-        set_error("adapter " + std::to_string(id) + " is not a loaded per-row adapter");
+// ---- one active adapter at a time (crates/retrograd-ffi/runtime/src/retro_engine.cpp:756-870). The factors live
+// in the same stacks as the per-row adapters; rows with adapter == 0 are routed to the active one's index.
+
+void Engine::forget_kv() {
+    RB_CUDA(cudaStreamSynchronize(stream));
+    for (uint32_t slot = 0; slot < config.n_seq_max; ++slot) kv->seq_rm((int32_t)slot, -1, -1);
+    weights_version += 1;
+}
+
+int Engine::lora_load_named(const char * name, const char * path) {
+    Adapter ad;
+    try {
+        if (!read_adapter_file(path, 1.0f, ad)) return STATUS_RUNTIME;
+    } catch (const std::exception &) {
+        set_error(std::string("failed to load LoRA adapter: ") + path);
         return STATUS_RUNTIME;
     }
+    ad.serial = true;
+    const bool was_active = active_name_ == name;
+    auto found = serial_ids_.find(name);
+    if (found != serial_ids_.end()) adapters_.erase(found->second);
+    const int32_t id = next_adapter_id_++;
+    adapters_[id] = std::move(ad);
+    serial_ids_[name] = id;
+    restack_adapters();
+    if (was_active) {           // a reload of the active adapter re-applies it: the resident KV is stale
+        active_id_ = id;
+        forget_kv();
+    }
+    return STATUS_OK;
+}
+
+int Engine::lora_load_single(const char * path) {
+    Adapter ad;
+    try {
+        if (!read_adapter_file(path, 1.0f, ad)) return STATUS_RUNTIME;
+    } catch (const std::exception &) {
+        set_error(std::string("failed to load LoRA adapter: ") + path);
+        return STATUS_RUNTIME;
+    }
+    ad.serial = true;
+    // the historical single-adapter contract: every other registered adapter goes
+    for (const auto & kvp : serial_ids_) adapters_.erase(kvp.second);
+    serial_ids_.clear();
+    const int32_t id = next_adapter_id_++;
+    adapters_[id] = std::move(ad);
+    serial_ids_[path] = id;
+    active_name_ = path;
+    active_id_ = id;
+    restack_adapters();
+    forget_kv();
+    return STATUS_OK;
+}
+
+int Engine::lora_activate(const char * name) {
+    const std::string wanted = name ? name : "";
+    int32_t id = 0;
+    if (!wanted.empty()) {
+        auto found = serial_ids_.find(wanted);
+        if (found == serial_ids_.end()) {
+            set_error("no LoRA adapter registered under '" + wanted + "'");
+            return STATUS_RUNTIME;
+        }
+        id = found->second;
+    }
+    active_name_ = wanted;
+    active_id_ = id;
+    forget_kv();
+    return STATUS_OK;
+}
+
+int Engine::lora_set_enabled(bool enabled) {
+    if (!enabled) {
+        active_name_.clear();
+        active_id_ = 0;
+    } else if (active_name_.empty()) {
+        set_error("cannot enable LoRA: no adapter is active");
+        return STATUS_RUNTIME;
+    }
+    forget_kv();        // disabling is as much a weights change as enabling
+    return STATUS_OK;
+}
+
+// A frozen per-row copy of the active adapter (the trainer-owned context's policy snapshot).
+int Engine::adapter_snapshot(int32_t replace, float scale, int32_t * out_id) {
+    if (!out_id) {
+        set_error("out_id is required");
+        return STATUS_RUNTIME;
+    }
+    if (!std::isfinite(scale)) {
+        set_error("the adapter scale must be finite");
+        return STATUS_RUNTIME;
+    }
+    if (active_id_ == 0) {
+        set_error("no trained adapter is active on the generation context: nothing to snapshot");
+        return STATUS_RUNTIME;
+    }
+    if (replace != 0) {
+        auto found = adapters_.find(replace);
+        if (found == adapters_.end() || found->second.serial) {
+            set_error("no per-row adapter is loaded under id " + std::to_string(replace));
+            return STATUS_RUNTIME;
+        }
+        adapters_.erase(found);
+    }
+    Adapter copy = adapters_.at(active_id_);
+    copy.serial = false;
+    copy.scale *= scale;
+    const int32_t id = next_adapter_id_++;
+    adapters_[id] = std::move(copy);
+    restack_adapters();
+    *out_id = id;
+    return STATUS_OK;
+}
+
+uint64_t Engine::work_buffer_bytes() const {
+    uint64_t total = 0;
+    auto add = [&](const auto & buffer) { total += (uint64_t)buffer.count * sizeof(*buffer.ptr); };
+    add(block_table_); add(maps_store_); add(d_stage_); add(d_result_); add(x_); add(xn_); add(qkv_); add(att_); add(gu_); add(hff_); add(hs_);
+    add(router_logits_); add(moe_w_); add(pair_gu_); add(pair_h_); add(pair_y_); add(lora_tmp_); add(logits_work_); add(logits); add(route_ids);
+    add(moe_ids_); add(d_aux_); add(moe_offsets_); add(moe_sorted_); add(lora_offsets_); add(lora_sorted_); add(stream_scratch_);
+    add(sample_scratch_); add(attn_scratch_); add(moe_xs_); add(moe_gu_s_); add(moe_y_s_); add(ep_all_offsets_); add(ep_offsets_l_);
+    add(ep_sorted_l_); add(ep_send_); add(ep_recv_); add(ep_gu_); add(ep_h_); add(ep_y_); add(ep_back_);
+    for (const SplitBuffer * sb : {&xn_split_, &att_split_, &hff_split_, &hs_split_, &moe_x_split_, &moe_h_split_}) add(sb->store);
+    return total;
+}
+
+uint64_t Engine::adapter_bytes() const {
+    uint64_t total = stacked_bytes_;
+    for (const auto & a : adapters_) total += a.second.unpadded_bytes;      // the host copies the stacks are built from
+    return total;
+}
+
+int Engine::adapter_unload(int32_t id) {
+    auto found = adapters_.find(id);
+    if (found == adapters_.end() || found->second.serial) {
+        set_error("no per-row adapter is loaded under id " + std::to_string(id));
+        return STATUS_RUNTIME;
+    }
+    adapters_.erase(found);
     restack_adapters();
     return STATUS_OK;
 }
@@ -1662,11 +1811,17 @@ void Engine::restack_adapters() {
 void Engine::adapter_info(retro_adapter_rows_info * out) {
     *out = retro_adapter_rows_info{};
     out->struct_size = sizeof(retro_adapter_rows_info);
-    out->n_adapters = (uint32_t)adapters_.size();
+    // the stacks also hold the registered one-at-a-time adapters; the counts describe the per-row ones
+    uint32_t n = 0;
+    uint64_t unpadded = 0;
+    for (const auto & a : adapters_) {
+        if (a.second.serial) continue;
+        ++n;
+        unpadded += a.second.unpadded_bytes;
+    }
+    out->n_adapters = n;
     out->max_rank = r_max_;
     out->stacked_bytes = stacked_bytes_;
-    uint64_t unpadded = 0;
-    for (const auto & a : adapters_) unpadded += a.second.unpadded_bytes;
     out->unpadded_bytes = unpadded;
 }
 

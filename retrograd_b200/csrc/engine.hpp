@@ -161,6 +161,9 @@ struct Model {
     uint64_t tiled_bytes = 0;
     std::vector<std::string> vocab_tokens;
     std::vector<int32_t> vocab_types;
+    std::vector<retro_expert_bank_desc> expert_banks;   // as the GGUF holds them, sorted by tensor name
+    std::vector<uint8_t> eog;                           // per token: ends a generation (EOS, EOT, EOM and the known end-of-turn pieces)
+    bool is_eog(int32_t token) const { return token >= 0 && (size_t)token < eog.size() ? eog[token] != 0 : token == eos; }
     int32_t eos = 2, bos = 1;
     bool add_bos = true;
     ~Model() { for (void * p : allocations) cudaFree(p); }
@@ -172,6 +175,12 @@ struct Adapter {
     // target weight name -> (A [r][in], B [out][r]) in F32
     std::map<std::string, std::pair<std::vector<float>, std::vector<float>>> ab;
     uint64_t unpadded_bytes = 0;
+    bool serial = false;        // registered by name for the one-active-at-a-time family, not selectable per row
+};
+
+// Monotonic prefix-reuse counters of the batched generators (retro_generation_stats).
+struct GenerationCounters {
+    uint64_t calls = 0, sequences = 0, prompt_tokens = 0, prefilled_tokens = 0, reused_tokens = 0, hits = 0, evictions = 0;
 };
 
 struct LoraTarget {
@@ -226,6 +235,18 @@ public:
     int adapter_load(const char * path, float scale, int32_t * out_id);
     int adapter_unload(int32_t id);
     void adapter_info(retro_adapter_rows_info * out);
+    // The one-active-at-a-time adapter family (rows with adapter == 0 decode under the active one).
+    int lora_load_single(const char * path);
+    int lora_load_named(const char * name, const char * path);
+    int lora_activate(const char * name);
+    int lora_set_enabled(bool enabled);
+    const std::string & active_adapter() const { return active_name_; }
+    int adapter_snapshot(int32_t replace, float scale, int32_t * out_id);
+    void forget_kv();               // clears every slot and bumps the weights version
+    uint64_t adapter_bytes() const;
+    uint64_t work_buffer_bytes() const;
+    GenerationCounters gen_stats;
+    uint64_t route_pairs = 0;       // routed (token, expert) pairs served while telemetry was on
 
     retro_engine_config config{};
     std::string model_path;
@@ -332,6 +353,10 @@ private:
     cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
     bool attn_overlap_ = true;                           // RB200_ATTN_OVERLAP=0: every attention kernel on the step's stream
 
+    bool read_adapter_file(const char * path, float scale, Adapter & out);
+    std::map<std::string, int32_t> serial_ids_;      // name -> id in adapters_
+    std::string active_name_;
+    int32_t active_id_ = 0;
     std::map<int32_t, Adapter> adapters_;
     std::map<int32_t, int32_t> adapter_index_;   // id -> stack index
     int32_t next_adapter_id_ = 1;

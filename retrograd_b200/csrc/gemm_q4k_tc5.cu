@@ -248,10 +248,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
             return true;
         };
         Raw raw0, raw1;
+        // Programmatic stream serialization: only weights may be touched before the wait. A minimum-term
+        // stage prefetches the token's sub-block sums - activations, written by the kernel in front of this
+        // one - so such a stage among the first two waits its turn.
+        static_assert(GROUPS < 4, "the first stage of every group must be a weight stage");
+        const bool sums_first = (group + GROUPS) % 5 == 4;
         prefetch(group, raw0);
-        prefetch(group + GROUPS, raw1);
-        // programmatic stream serialization: only weights were touched so far; the activations follow
+        if (!sums_first) prefetch(group + GROUPS, raw1);
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (sums_first) prefetch(group + GROUPS, raw1);
         for (int it = group; it < n_it; it += 2 * GROUPS) {
             if (!produce(it, raw0)) break;
             if (it + GROUPS < n_it && !produce(it + GROUPS, raw1)) break;

@@ -198,6 +198,9 @@ struct Spec {
     bool bias = false;
     // "normal": N(0, std). "uniform": std * unit().
     bool normal = true;
+    // optional end-of-turn tokens: `eot` is named by tokenizer.ggml.eot_token_id and spelled <|eot_id|>;
+    // `turn_end` is only spelled <|im_end|> (a control piece the loader has to recognise by its text)
+    uint32_t eot = 0, turn_end = 0;
 };
 
 struct TensorPlan {
@@ -273,6 +276,8 @@ uint64_t synth_gguf(const char * path, const char * spec_text) {
             else if (k == "seed") sp.seed = std::stoull(v);
             else if (k == "bias") sp.bias = v == "1" || v == "true";
             else if (k == "dist") sp.normal = v != "uniform";
+            else if (k == "eot") sp.eot = (uint32_t)std::stoul(v);
+            else if (k == "turn_end") sp.turn_end = (uint32_t)std::stoul(v);
             else throw std::runtime_error("synth: unknown key '" + k + "'");
         }
     }
@@ -375,6 +380,12 @@ uint64_t synth_gguf(const char * path, const char * spec_text) {
                 std::snprintf(buf, sizeof buf, "<0x%02X>", i - 3);
                 tok = buf;
                 types[i] = 6;
+            } else if (sp.eot && i == sp.eot) {
+                tok = "<|eot_id|>";
+                types[i] = 3;
+            } else if (sp.turn_end && i == sp.turn_end) {
+                tok = "<|im_end|>";
+                types[i] = 3;
             } else {
                 tok = "\xE2\x96\x81t" + std::to_string(i);
             }
@@ -391,6 +402,7 @@ uint64_t synth_gguf(const char * path, const char * spec_text) {
     kv_u32(kvs, "tokenizer.ggml.bos_token_id", 1); ++n_kv;
     kv_u32(kvs, "tokenizer.ggml.eos_token_id", 2); ++n_kv;
     kv_u32(kvs, "tokenizer.ggml.unknown_token_id", 0); ++n_kv;
+    if (sp.eot) { kv_u32(kvs, "tokenizer.ggml.eot_token_id", sp.eot); ++n_kv; }
     kv_bool(kvs, "tokenizer.ggml.add_bos_token", true); ++n_kv;
     kv_bool(kvs, "tokenizer.ggml.add_eos_token", false); ++n_kv;
     kv_u32(kvs, "general.alignment", 32); ++n_kv;

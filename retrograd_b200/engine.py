@@ -253,6 +253,12 @@ class Engine:
             raise EngineError(_last_error())
         self._keep: list = []
 
+    # entry points that exist for both handles: retro_engine_<name> here, retro_trainer_generation_<name> in TrainerGeneration
+    _twin_prefix = "retro_engine_"
+
+    def _twin(self, name: str):
+        return getattr(self._lib, self._twin_prefix + name)
+
     def close(self) -> None:
         if self._h:
             self._lib.retro_engine_free(self._h)
@@ -293,12 +299,12 @@ class Engine:
 
     def kv_unified(self) -> bool:
         v = C.c_bool()
-        _check(self._lib.retro_engine_kv_unified(self._h, C.byref(v)))
+        _check(self._twin("kv_unified")(self._h, C.byref(v)))
         return v.value
 
     def weights_version(self) -> int:
         v = C.c_uint64()
-        _check(self._lib.retro_engine_weights_version(self._h, C.byref(v)))
+        _check(self._twin("weights_version")(self._h, C.byref(v)))
         return v.value
 
     def model_fingerprint(self) -> int:
@@ -371,7 +377,7 @@ class Engine:
             raise InvalidArgument("a request id appears twice in one step")
         any_top = out.n_top_stride > 0
         t0 = time.perf_counter()
-        status = self._lib.retro_engine_step_v2(
+        status = self._twin("step_v2")(
             self._h,
             c_rows,
             n,
@@ -404,7 +410,7 @@ class Engine:
         ids = np.zeros(max(n * out_stride, 1), dtype=np.int32)
         lps = np.zeros(max(n * out_stride, 1), dtype=np.float32)
         _check(
-            self._lib.retro_engine_step(
+            self._twin("step")(
                 self._h,
                 c_rows,
                 n,
@@ -421,32 +427,32 @@ class Engine:
 
     # ---- sequence memory
     def seq_rm(self, slot: int, p0: int = -1, p1: int = -1) -> None:
-        _check(self._lib.retro_engine_seq_rm(self._h, slot, p0, p1))
+        _check(self._twin("seq_rm")(self._h, slot, p0, p1))
 
     def seq_cp(self, src: int, dst: int, p0: int = -1, p1: int = -1) -> None:
-        _check(self._lib.retro_engine_seq_cp(self._h, src, dst, p0, p1))
+        _check(self._twin("seq_cp")(self._h, src, dst, p0, p1))
 
     def seq_pos(self, slot: int) -> tuple[int, int]:
         a, b = C.c_int32(), C.c_int32()
-        _check(self._lib.retro_engine_seq_pos(self._h, slot, C.byref(a), C.byref(b)))
+        _check(self._twin("seq_pos")(self._h, slot, C.byref(a), C.byref(b)))
         return a.value, b.value
 
     def seq_save(self, slot: int, flags: int = 0) -> bytes:
         n = C.c_size_t()
-        _check(self._lib.retro_engine_seq_save(self._h, slot, flags, None, 0, C.byref(n)))
+        _check(self._twin("seq_save")(self._h, slot, flags, None, 0, C.byref(n)))
         buf = (C.c_uint8 * n.value)()
-        _check(self._lib.retro_engine_seq_save(self._h, slot, flags, buf, n.value, C.byref(n)))
+        _check(self._twin("seq_save")(self._h, slot, flags, buf, n.value, C.byref(n)))
         return bytes(buf[: n.value])
 
     def seq_load(self, slot: int, data: bytes, flags: int = 0) -> int:
         buf = (C.c_uint8 * max(len(data), 1)).from_buffer_copy(data if data else b"\0")
         n = C.c_size_t()
-        _check(self._lib.retro_engine_seq_load(self._h, slot, flags, buf, len(data), C.byref(n)))
+        _check(self._twin("seq_load")(self._h, slot, flags, buf, len(data), C.byref(n)))
         return n.value
 
     def memory(self) -> EngineMemory:
         m = _ffi.MemoryInfoC()
-        _check(self._lib.retro_engine_memory(self._h, C.byref(m)))
+        _check(self._twin("memory")(self._h, C.byref(m)))
         return EngineMemory(m.n_slots, m.cells_total, m.cells_used, m.kv_bytes, m.recurrent_bytes)
 
     # ---- batched generators (retro_engine_generate_batch / _generate_continuous_batch)
@@ -489,7 +495,7 @@ class Engine:
         return [tokens[i, : counts[i]].tolist() for i in range(n)], [logprobs[i, : counts[i]].tolist() for i in range(n)]
 
     def request_free(self, request: int) -> None:
-        _check(self._lib.retro_engine_request_free(self._h, request))
+        _check(self._twin("request_free")(self._h, request))
 
     # ---- per-row adapters
     def adapter_load(self, path: str, scale: float = 1.0) -> int:
@@ -498,12 +504,62 @@ class Engine:
         return v.value
 
     def adapter_unload(self, adapter: int) -> None:
-        _check(self._lib.retro_engine_adapter_unload(self._h, adapter))
+        _check(self._twin("adapter_unload")(self._h, adapter))
 
     def adapter_rows_info(self) -> dict:
         info = _ffi.AdapterRowsInfoC()
-        _check(self._lib.retro_engine_adapter_rows_info(self._h, C.byref(info)))
+        _check(self._twin("adapter_rows_info")(self._h, C.byref(info)))
         return dict(n_adapters=info.n_adapters, max_rank=info.max_rank, stacked_bytes=info.stacked_bytes, unpadded_bytes=info.unpadded_bytes)
+
+    # ---- one active adapter at a time: rows with adapter == 0 decode under it
+    def load_lora(self, path: str) -> None:
+        _check(self._lib.retro_engine_load_lora(self._h, str(path).encode()))
+
+    def load_lora_named(self, name: str, path: str) -> None:
+        _check(self._lib.retro_engine_load_lora_named(self._h, name.encode(), str(path).encode()))
+
+    def activate_lora(self, name: str | None) -> None:
+        _check(self._lib.retro_engine_activate_lora(self._h, name.encode() if name is not None else None))
+
+    def set_lora_enabled(self, enabled: bool) -> None:
+        _check(self._lib.retro_engine_set_lora_enabled(self._h, enabled))
+
+    def active_adapter(self) -> str:
+        n = C.c_size_t()
+        _check(self._lib.retro_engine_active_adapter(self._h, None, 0, C.byref(n)))
+        buf = C.create_string_buffer(n.value + 1)
+        _check(self._lib.retro_engine_active_adapter(self._h, buf, n.value + 1, C.byref(n)))
+        return buf.value.decode()
+
+    # ---- counters
+    def memory_report(self) -> dict:
+        r = _ffi.MemoryReportC()
+        _check(self._lib.retro_engine_memory_report(self._h, C.byref(r)))
+        return {name: getattr(r, name) for name, _ in _ffi.MemoryReportC._fields_}
+
+    def generation_stats(self) -> dict:
+        st = _ffi.GenerationStatsC()
+        _check(self._twin("stats" if self._twin_prefix.startswith("retro_trainer") else "generation_stats")(self._h, C.byref(st)))
+        return {name: getattr(st, name) for name, _ in _ffi.GenerationStatsC._fields_}
+
+    # ---- MoE expert banks
+    def expert_banks(self) -> list[dict]:
+        n = C.c_size_t()
+        _check(self._lib.retro_engine_expert_banks(self._h, None, 0, C.byref(n)))
+        banks = (_ffi.ExpertBankDescC * max(n.value, 1))()
+        _check(self._lib.retro_engine_expert_banks(self._h, banks, n.value, C.byref(n)))
+        return [dict(layer=b.layer, role=b.role.decode(), name=b.tensor.name.decode(), ne=list(b.tensor.ne), n_elements=b.tensor.n_elements,
+                     n_bytes=b.tensor.n_bytes, type_name=b.tensor.type_name.decode()) for b in banks[: n.value]]
+
+    def expert_stats(self) -> "_ffi.ExpertCacheStatsC":
+        st = _ffi.ExpertCacheStatsC()
+        _check(self._lib.retro_engine_expert_stats(self._h, C.byref(st)))
+        return st
+
+    def expert_route_paths(self) -> tuple[int, int, int]:
+        out = (C.c_uint64 * 3)()
+        _check(self._lib.retro_engine_expert_route_paths(self._h, out))
+        return out[0], out[1], out[2]
 
     # ---- MoE telemetry
     def expert_route_enable(self, sample_every: int = 1) -> None:
@@ -601,3 +657,34 @@ class Engine:
         n = (C.c_uint64 * 7)()
         _check(self._lib.retro_b200_engine_profile_read(self._h, ms, n, 7))
         return {name: {"ms": ms[i], "launches": n[i]} for i, name in enumerate(self.PROFILE_CLASSES)}
+
+
+class TrainerGeneration(Engine):
+    """The generation context an RL trainer owns, driven through the `retro_trainer_generation_*` twins of the
+    engine's step and sequence entry points (crates/retrograd-infer/src/backend.rs:376-461 is the reference's
+    caller). `weights_updated` is the trainer's notice after an optimizer step: with a path the trained adapter
+    is read again; either way the KV is forgotten and the weights version moves on."""
+
+    _twin_prefix = "retro_trainer_generation_"
+
+    def __init__(self, model_path: str, config: EngineConfig | None = None, adapter_path: str | None = None) -> None:
+        self._lib = _ffi.load_library()
+        self.config = config or EngineConfig()
+        c = self.config.to_c()
+        self._h = self._lib.retro_b200_trainer_generation_new(str(model_path).encode(), C.byref(c), str(adapter_path).encode() if adapter_path else None)
+        if not self._h:
+            raise EngineError(_last_error())
+        self._keep = []
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.retro_b200_trainer_generation_free(self._h)
+            self._h = None
+
+    def weights_updated(self, adapter_path: str | None = None) -> None:
+        _check(self._lib.retro_b200_trainer_weights_updated(self._h, str(adapter_path).encode() if adapter_path else None))
+
+    def adapter_snapshot(self, replace: int = 0, scale: float = 1.0) -> int:
+        v = C.c_int32()
+        _check(self._lib.retro_trainer_generation_adapter_snapshot(self._h, replace, scale, C.byref(v)))
+        return v.value

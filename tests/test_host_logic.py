@@ -22,6 +22,34 @@ def test_library_exports_every_declared_symbol(rb):
         assert name in _ffi.SYMBOLS, f"{name} has no ctypes binding"
 
 
+def test_library_exports_the_reference_bindings_step_path_symbols(rb):
+    """`nm -D` of the built library against the committed list of names the reference's `extern "C"` block
+    declares for this path: a missing one would keep the reference's crate from linking."""
+    wanted = [l.strip() for l in (ROOT / "tests" / "golden" / "abi_symbols.txt").read_text().splitlines() if l.strip() and not l.startswith("#")]
+    assert len(wanted) >= 60
+    out = subprocess.run(["nm", "-D", "--defined-only", str(rb.LIB_PATH)], capture_output=True, text=True, check=True).stdout
+    exported = {line.split()[-1] for line in out.splitlines() if " T " in line}
+    missing = [name for name in wanted if name not in exported]
+    assert not missing, f"not exported: {missing}"
+
+
+def test_grammar_handles_own_their_text(rb):
+    """retro_grammar.cpp:1-76: an owned GBNF string; empty text and a null handle are refused with a message."""
+    lib = rb.load_library()
+    g = lib.retro_grammar_from_gbnf(b'root ::= "a" | "b"')
+    assert g and lib.retro_grammar_gbnf(g) == b'root ::= "a" | "b"'
+    lib.retro_grammar_free(g)
+    assert not lib.retro_grammar_from_gbnf(b"") and lib.retro_last_error() == b"gbnf is required and must not be empty"
+    assert not lib.retro_grammar_from_gbnf(None)
+    assert lib.retro_grammar_gbnf(None) is None and lib.retro_last_error() == b"grammar is null"
+    j = lib.retro_grammar_json_object()
+    assert j and lib.retro_grammar_gbnf(j).startswith(b"root ::= object")
+    lib.retro_grammar_free(j)
+    assert not lib.retro_grammar_from_json_schema(b"") and lib.retro_last_error() == b"json_schema is required and must not be empty"
+    assert not lib.retro_grammar_from_json_schema(b'{"type": "object"}') and b"pass GBNF" in lib.retro_last_error()
+    lib.retro_grammar_free(None)
+
+
 def test_struct_layouts_match_the_published_header(rb):
     """Sizes pinned by crates/retrograd-ffi/src/lib.rs:2899-3052."""
     from retrograd_b200 import _ffi as F
@@ -35,6 +63,13 @@ def test_struct_layouts_match_the_published_header(rb):
     assert C.sizeof(F.StepOutRowV2C) == 24 and F.StepOutRowV2C.sampled_logprob.offset == 20
     assert C.sizeof(F.MemoryInfoC) == 40
     assert C.sizeof(F.AdapterRowsInfoC) == 32
+    # lib.rs:2958-2969 (memory report), retro_lora_train.h:788-795, 827-840, 1113-1131
+    assert C.sizeof(F.MemoryReportC) == 216 and F.MemoryReportC.trainable_parameter_bytes.offset == 48
+    assert F.MemoryReportC.base_trainable_on_host.offset == 74 and F.MemoryReportC.device_bytes.offset == 80
+    assert F.MemoryReportC.device_memory_samples.offset == 136
+    assert C.sizeof(F.GenerationStatsC) == 56
+    assert C.sizeof(F.ExpertBankDescC) == 272 and F.ExpertBankDescC.role.offset == 4 and F.ExpertBankDescC.tensor.offset == 24
+    assert C.sizeof(F.ExpertCacheStatsC) == 464 and F.ExpertCacheStatsC.n_groups.offset == 72 and F.ExpertCacheStatsC.groups.offset == 80
 
 
 def _new(rb, path, **over):
