@@ -41,7 +41,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 WORKLOADS = {
-    # BASELINE config 2
+    # the headline workload: 8B-shape Q4_K, 256 concurrent ragged requests, 512-token prefill chunks
     "c2": dict(
         name="llama3-8b-shape Q4_K, 256 ragged requests, continuous batching, 512-token prefill chunks",
         spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
@@ -61,23 +61,23 @@ WORKLOADS = {
         spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
         n_requests=16, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=131072,
     ),
-    # the 8B shape in Q8_0 (BASELINE config 3's weights), again eight long-running requests
+    # the 8B shape in Q8_0 (the rollout workload's weights), again eight long-running requests
     "c3_decode8": dict(
         name="llama3-8b-shape Q8_0, 8 requests, decode-only steps of 8 tokens",
         model="c3",
         spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q8_0", seed=3),
         n_requests=8, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=65536,
     ),
-    # BASELINE config 5's shape cut to 6 of its 24 layers (the expert GEMMs still run on CUDA cores, and a
-    # full-depth model costs a quarter of an hour of GPU time per run): experts MXFP4, the rest Q8_0. With
-    # more than one GPU the ranks form an expert-parallel group: each serves 32 / N experts and its own requests.
+    # the gpt-oss-20b-like MoE shape cut to 6 of its 24 layers (a full-depth model costs a quarter of an hour of
+    # GPU time per run): experts MXFP4, the rest Q8_0. With more than one GPU the ranks form an expert-parallel
+    # group: each serves 32 / N experts and its own requests.
     "c5_ep": dict(
         name="gpt-oss-20b-shape MoE cut to 6 layers (32 experts top-4, MXFP4), 128 requests per GPU, expert parallel",
         spec=dict(arch="olmoe", layers=6, d=2880, heads=64, kv_heads=8, head_dim=64, ff=2880, vocab=201088, experts=32, experts_used=4,
                   dtype="q8_0", expert_dtype="mxfp4", seed=5),
         n_requests=128, prompt=(64, 1024), output=(128, 512), chunk=512, n_batch=1024, n_ctx=200_000, ep=True,
     ),
-    # BASELINE config 1 (CPU-runnable shape; used to exercise this script quickly)
+    # the tiny CPU-runnable shape (used to exercise this script quickly)
     "c1": dict(
         name="tiny llama-style Q8_0, 8 requests",
         spec=dict(arch="llama", layers=2, d=256, heads=4, kv_heads=4, ff=688, vocab=4096, dtype="q8_0", seed=20261125),
@@ -103,13 +103,20 @@ def model_path(workload: str) -> Path:
     return base / f"retrograd_b200_{WORKLOADS[workload].get('model', workload)}.gguf"
 
 
-def ensure_model(workload: str, rank: int) -> Path:
-    import retrograd_b200 as rb
-
+def ensure_model(workload: str, rank: int, host_only: bool = False) -> Path:
+    """The workload's seeded GGUF, written once per box. `host_only`: through the oracle folder's copy of the
+    writer, so that the CPU arm never loads the GPU library (the two writers give the same bytes)."""
     path = model_path(workload)
     done = path.with_suffix(".done")
     if rank == 0 and not done.exists():
-        rb.synth_gguf(path, **WORKLOADS[workload]["spec"])
+        if host_only:
+            from oracle import oracle as O
+
+            O.synth_gguf(path, **WORKLOADS[workload]["spec"])
+        else:
+            import retrograd_b200 as rb
+
+            rb.synth_gguf(path, **WORKLOADS[workload]["spec"])
         done.write_text("ok")
     while not done.exists():
         time.sleep(0.5)
@@ -172,35 +179,28 @@ class Driver:
             r.slot = self.free_slots.pop()
             self.live.append(r)
 
-    def compose(self, prefill_only=False):
+    def compose(self, prefill_only=False, decode_only=0):
+        """`decode_only` = n > 0: only the first n decoding requests' rows (the decode-only measurement)."""
         rb = self.rb
         rows, kinds, budget = [], [], self.cfg["n_batch"]
         for r in self.live:
-            if prefill_only:
+            if prefill_only or (decode_only and len(rows) >= decode_only):
                 break
             if r.last is not None and budget > 0:
                 rows.append(rb.StepRow(r.rid, r.slot, [r.last], len(r.prompt) + r.done - 1, True, self.sampling))
                 kinds.append(r)
                 budget -= 1
         for r in self.live:
-            if r.last is None and budget > 0:
+            if r.last is None and budget > 0 and not decode_only:
                 take = min(budget, self.cfg["chunk"], len(r.prompt) - r.pos)
                 final = r.pos + take == len(r.prompt)
                 rows.append(rb.StepRow(r.rid, r.slot, r.prompt[r.pos : r.pos + take], r.pos, final, self.sampling))
                 kinds.append(r)
                 budget -= take
-        # The GEMM works on tiles of 128 tokens: when the step would end in a ragged tile, the last
-        # prefill chunk gives the remainder back (those tokens go into the next step instead).
-        total = self.cfg["n_batch"] - budget
-        rem = total % 128
-        if total > 128 and rem and rows and kinds[-1].last is None and len(rows[-1].tokens) > rem:
-            r, row = kinds[-1], rows[-1]
-            keep = len(row.tokens) - rem
-            rows[-1] = rb.StepRow(r.rid, r.slot, r.prompt[r.pos : r.pos + keep], r.pos, False, self.sampling)
         return rows, kinds
 
-    def step(self, prefill_only=False):
-        rows, reqs = self.compose(prefill_only)
+    def step(self, prefill_only=False, decode_only=0):
+        rows, reqs = self.compose(prefill_only, decode_only)
         if not rows:
             if self.expert_parallel:
                 self.engine.ep_idle_step()      # this rank's experts still serve the other ranks' tokens
@@ -223,7 +223,7 @@ class Driver:
                 r.done += 1
                 r.times.append(stamp)
                 sampled += 1
-        finished = [r for r in self.live if r.done >= r.n_out]
+        finished = [] if decode_only else [r for r in self.live if r.done >= r.n_out]
         for r in finished:
             self.engine.seq_rm(r.slot)
             self.engine.request_free(r.rid)
@@ -275,11 +275,20 @@ def measured_peaks():
     return 6650.0, 1590.0, "fallback"
 
 
+def host_cores() -> int:
+    """The host cores this process may run on (a launcher may have narrowed the affinity mask)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_baseline(path: Path, cfg, steps: int = 2, rows: int = 8, prompt: int = 4):
     """The CPU oracle (vectorised accumulation, all host threads) on a bounded sample: `rows`
     concurrent requests, a `prompt`-token prefill each, then `steps` decode steps."""
     from oracle import oracle as O
 
+    cores = O.threads(host_cores())
     m = O.Model(str(path), fast=True)
     ctx = O.Context(m, rows, 64)
     rng = np.random.default_rng(1)
@@ -292,7 +301,7 @@ def cpu_baseline(path: Path, cfg, steps: int = 2, rows: int = 8, prompt: int = 4
         times.append(time.perf_counter() - t0)
     ctx.close()
     m.close()
-    return rows / statistics.median(times), times
+    return rows / statistics.median(times), times, cores
 
 
 def run_reference(args, cfg, rank, world):
@@ -300,9 +309,11 @@ def run_reference(args, cfg, rank, world):
     one bounded decode step per timed step."""
     if rank != 0:
         return
-    path = ensure_model(args.workload, 0)
+    path = ensure_model(args.workload, 0, host_only=True)
     from oracle import oracle as O
 
+    # the thread count is set here, not inherited: torchrun exports OMP_NUM_THREADS=1 to its children
+    cores = O.threads(host_cores())
     rows, prompt = 8, 4
     m = O.Model(str(path), fast=True)
     ctx = O.Context(m, rows, 64 + args.steps + args.warmup)
@@ -317,8 +328,8 @@ def run_reference(args, cfg, rank, world):
             times.append(time.perf_counter() - t0)
     total = sum(times)
     value = rows * len(times) / total
-    cores = os.cpu_count() or 1
-    sample = f"{rows} concurrent requests, {prompt}-token prompts, {len(times)} decode steps of the same GGUF"
+    sample = (f"{rows} concurrent requests, {prompt}-token prompts, {len(times)} decode steps of the same GGUF on {cores} OpenMP threads: the CPU "
+              "restatement of the path (the reference itself cannot be built here), a bounded decode-only sample, not the GPU arm's 256-request mix")
     print(json.dumps({
         "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -348,6 +359,10 @@ def main():
         run_reference(args, cfg, rank, world)
         return
 
+    if world > 1:
+        # the two-rank expert-parallel check below runs on plain NCCL paths (read when the library first
+        # initialises in this process, so before the process group exists)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch
 
     torch.cuda.set_device(local_rank)
@@ -366,6 +381,32 @@ def main():
         dist.barrier()
     path = ensure_model(args.workload, local_rank if world > 1 else 0)
     if dist:
+        dist.barrier()
+
+    # ---- two GPUs or more: ranks 0 and 1 first compare an expert-parallel pair of engines with plain engines on
+    # the same rows (a tiny MoE model, every rank of the pair stepping the same number of times); the outcome
+    # travels in the line as "ep_parity"
+    ep_parity = None
+    if world > 1:
+        from retrograd_b200.ep_check import plain_vs_expert_parallel
+
+        holder = [rb.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(holder, src=0)
+        mine = None
+        if rank < 2:
+            try:
+                result = plain_vs_expert_parallel(rb, rank, 2, holder[0], path.parent)
+                result["engine"].close()
+                mine = {"steps": result["steps"], "bit_exact": result["bit_exact"]}
+            except Exception as err:      # reported, not fatal: the replica measurement below does not depend on it
+                mine = {"steps": 0, "bit_exact": False, "error": str(err)[:200]}
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        pair = [g for g in gathered[:2] if g]
+        ep_parity = {"ranks": 2, "steps": min(g["steps"] for g in pair), "bit_exact": all(g["bit_exact"] for g in pair)}
+        errors = [g["error"] for g in pair if "error" in g]
+        if errors:
+            ep_parity["error"] = errors[0]
         dist.barrier()
 
     engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=cfg["n_ctx"], n_seq_max=cfg["n_requests"], n_batch=cfg["n_batch"], n_ubatch=cfg["n_batch"]))
@@ -459,6 +500,26 @@ def main():
     profile = engine.profile_read()
     engine.profile(False)
 
+    # ---- decode-only steps on the same engine and model (untimed for `value`): the weight stream of a whole
+    # step against the measured HBM rate. No admissions, no prefill rows; repeated shapes replay as CUDA graphs.
+    decode_only = []
+    weight_bytes_step = None
+    if not sp.get("experts"):
+        bpw = {"q4_k": 144 / 256, "q8_0": 34 / 32, "f16": 2.0, "f32": 4.0}.get(sp["dtype"], 1.0)
+        weight_bytes_step = (sp["layers"] * w_elems_layer + sp["d"] * sp["vocab"]) * bpw
+        decoders = sum(1 for r in driver.live if r.last is not None)
+        for want in (8, cfg["n_requests"]):
+            n_rows = min(want, decoders)
+            if n_rows == 0 or any(d["rows"] == n_rows for d in decode_only):
+                continue
+            times = []
+            for i in range(3 + 10):
+                driver.step(decode_only=n_rows)
+                if i >= 3:
+                    times.append(engine.last_step_stats()[0])
+            ms = statistics.mean(times)
+            decode_only.append({"rows": n_rows, "ms_per_step": ms, "tok_s": n_rows / (ms * 1e-3)})
+
     # inter-token gaps of every request that sampled more than once in the timed region
     gaps = []
     for r in driver.live:
@@ -467,9 +528,16 @@ def main():
 
     from retrograd_b200.replicas import aggregate
 
+    # every rank's own step time, so that a slow whole-job step can be attributed (imbalance of the seeded
+    # request streams, or one GPU's clocks)
+    rank_ms = [dev_ms / args.steps]
+    if dist:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, dev_ms / args.steps)
+        rank_ms = [float(x) for x in gathered]
     # whole job: the slowest rank's time, every rank's tokens (replicas, no data-path collective)
-    (dev_ms, wall_s), (decode_tokens, prefill_tokens, launches) = aggregate(
-        [dev_ms, wall_s], [decode_tokens, prefill_tokens, launches], dist, torch.device("cuda", local_rank))
+    (dev_ms, wall_s), (decode_tokens, prefill_tokens, launches, step_tokens_all) = aggregate(
+        [dev_ms, wall_s], [decode_tokens, prefill_tokens, launches, step_tokens], dist, torch.device("cuda", local_rank))
     if dist:
         dist.barrier()
         dist.destroy_process_group()
@@ -516,21 +584,30 @@ def main():
         "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": cfg["name"], "n_batch": cfg["n_batch"], "n_ctx": cfg["n_ctx"], "parallelism": f"expert parallel x{world}" if expert_parallel else f"replicas x{world}",
+                   "arrivals": "closed loop: a new request is admitted the moment a slot frees (the saturated steady state of the arrival process)",
                    "rows_per_step": statistics.mean(rows_per_step), "decode_tokens_per_step": decode_tokens / args.steps / world,
-                   "prefill_tokens_per_step": prefill_tokens / args.steps / world, "tokens_per_step": step_tokens / args.steps,
+                   "prefill_tokens_per_step": prefill_tokens / args.steps / world, "tokens_per_step": step_tokens_all / args.steps / world,
                    "ramp_steps": ramp_steps, "cuda_graphs": bool(args.graphs),
                    "l2": "inputs larger than L2: every step streams >4 GB of weights and the ragged KV"},
         "e2e": {"value": decode_tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps},
         "gpu_launches": int(launches),
         "p50_inter_token_ms": statistics.median(gaps) if gaps else None,
         "clocks": clocks.summary(),
+        "rank_ms_per_step": {"min": min(rank_ms), "median": statistics.median(rank_ms), "max": max(rank_ms)},
         "roofline": roof,
         "kernel_classes_ms": {k: round(v["ms"], 3) for k, v in profile.items()},
     }
+    if decode_only:
+        for d in decode_only:
+            d["weight_gbs"] = weight_bytes_step / (d["ms_per_step"] * 1e-3) / 1e9
+            d["frac"] = d["weight_gbs"] / hbm_peak
+        line["decode_only"] = decode_only
+    if ep_parity is not None:
+        line["ep_parity"] = ep_parity
     if world == 1 and not args.no_cpu_baseline:
         engine.close()
-        value, times = cpu_baseline(path, cfg)
-        line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+        value, times, cores = cpu_baseline(path, cfg)
+        line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
                                 "sample": f"8 concurrent requests, 4-token prompts, {len(times)} decode steps of the same GGUF"}
     else:
         engine.close()

@@ -22,6 +22,7 @@
 // h / (Hq/Hkv); attention scale 1/sqrt(head_dim); causal mask by position within the slot; K/V
 // are rounded to f16 when stored; activations stay f32 (the in-tree GEMV oracles' semantics).
 
+#include <omp.h>
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
@@ -826,6 +827,13 @@ double philox_uniform(uint32_t seed, uint64_t draw) {
 // C API
 
 extern "C" {
+
+// Sets (n > 0) and reports the number of OpenMP threads the forward pass uses. A launcher may export
+// OMP_NUM_THREADS=1 to its children; a timed baseline states its thread count instead of inheriting one.
+int ora_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+}
 
 const char * ora_last_error(void) { return g_error.c_str(); }
 

@@ -12,15 +12,43 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 LIB = HERE / "liboracle.so"
+MODELGEN = HERE / "libmodelgen.so"
 
 T_F32, T_F16, T_Q8_0, T_Q4_K, T_BF16, T_MXFP4 = 0, 1, 8, 12, 30, 39
 
 
 def build(force: bool = False) -> Path:
+    """Compiles the oracle and the host-only model writer when a source is newer than its library."""
     src = HERE / "oracle.cpp"
     if force or not LIB.exists() or LIB.stat().st_mtime < src.stat().st_mtime:
         subprocess.run(["make", "-C", str(HERE), "-B", "liboracle.so"], check=True, capture_output=True)
+    _build_modelgen(force)
     return LIB
+
+
+def _build_modelgen(force: bool = False) -> Path:
+    sources = [HERE / "modelgen.cpp", HERE.parent / "retrograd_b200" / "csrc" / "synth.cpp", HERE.parent / "retrograd_b200" / "csrc" / "blocks.hpp"]
+    if force or not MODELGEN.exists() or MODELGEN.stat().st_mtime < max(s.stat().st_mtime for s in sources):
+        subprocess.run(["make", "-C", str(HERE), "-B", "libmodelgen.so"], check=True, capture_output=True)
+    return MODELGEN
+
+
+def synth_gguf(path, **spec) -> int:
+    """Writes the seeded synthetic model `spec` describes (the keys of the GPU library's retro_b200_synth_gguf)
+    without loading the GPU library: the same writer, compiled into a host-only helper."""
+    gen = C.CDLL(str(_build_modelgen()))
+    gen.ora_modelgen_last_error.restype = C.c_char_p
+    gen.ora_synth_gguf.argtypes = [C.c_char_p, C.c_char_p, C.POINTER(C.c_uint64)]
+    n = C.c_uint64()
+    text = " ".join(f"{k}={v}" for k, v in spec.items())
+    if gen.ora_synth_gguf(str(path).encode(), text.encode(), C.byref(n)) != 0:
+        raise RuntimeError(gen.ora_modelgen_last_error().decode())
+    return n.value
+
+
+def threads(n: int = 0) -> int:
+    """Sets (n > 0) and returns the OpenMP thread count of the forward pass."""
+    return lib().ora_threads(n)
 
 
 _lib = None
@@ -33,6 +61,8 @@ def lib() -> C.CDLL:
         build()
         l = C.CDLL(str(LIB))
         l.ora_last_error.restype = C.c_char_p
+        l.ora_threads.restype = C.c_int
+        l.ora_threads.argtypes = [C.c_int]
         l.ora_model_load.restype = C.c_void_p
         l.ora_model_load.argtypes = [C.c_char_p]
         l.ora_model_free.argtypes = [C.c_void_p]

@@ -692,7 +692,8 @@ void Engine::ep_init(int rank, int world, const void * unique_id_128) {
     ep_world_ = world;
     ep_all_offsets_.ensure((size_t)world * (hp.n_expert + 1));
     ep_offsets_l_.ensure(hp.n_expert + 1);
-    RB_CUDA(cudaMallocHost(reinterpret_cast<void **>(&h_ep_offsets_), (size_t)world * (hp.n_expert + 1) * sizeof(int32_t)));
+    ep_flags_.ensure((size_t)world + 1);
+    RB_CUDA(cudaMallocHost(reinterpret_cast<void **>(&h_ep_offsets_), ((size_t)world * (hp.n_expert + 1) + world + 1) * sizeof(int32_t)));
 }
 
 // Rows [begin[p], begin[p] + count[p]) of `send` go to rank p, rows from rank p land at recv_begin[p]. Both
@@ -760,9 +761,28 @@ void Engine::ep_moe_layer(const LayerWeights & lw, int T) {
     last_launches += 8;
 }
 
+// Every step under expert parallelism opens with this exchange: each rank says whether its own plan passed
+// validation and KV reservation, and the step runs only if all of them did. A rank whose plan was refused
+// returns its ordinary error; the others undo their reservation and return a runtime error of their own.
+// Without it a refused rank would leave its peers waiting in the first layer's exchange for a partner that
+// never comes. True when every rank is ready.
+bool Engine::ep_agree(bool ready) {
+    const NcclApi & nccl = nccl_api();
+    int32_t * h_flags = h_ep_offsets_ + (size_t)ep_world_ * (model->hp.n_expert + 1);
+    h_flags[ep_world_] = ready ? 1 : 0;
+    RB_CUDA(cudaMemcpyAsync(ep_flags_.ptr + ep_world_, h_flags + ep_world_, sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    RB_NCCL(nccl.AllGather(ep_flags_.ptr + ep_world_, ep_flags_.ptr, 1, kNcclInt32, ep_comm_, stream));
+    RB_CUDA(cudaMemcpyAsync(h_flags, ep_flags_.ptr, (size_t)ep_world_ * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    RB_CUDA(cudaStreamSynchronize(stream));
+    for (int r = 0; r < ep_world_; ++r)
+        if (!h_flags[r]) return false;
+    return true;
+}
+
 // A step of a rank that has no rows of its own: its experts still serve the other ranks' tokens.
 void Engine::ep_idle_step() {
     if (!ep_comm_) throw std::invalid_argument("expert parallelism is not initialised for this engine");
+    if (!ep_agree(true)) return;        // a peer refused its step: nobody exchanges anything
     for (uint32_t l = 0; l < model->hp.n_layer; ++l) ep_moe_layer(model->layers[l], 0);
     RB_CUDA(cudaStreamSynchronize(stream));
 }
@@ -882,13 +902,23 @@ private:
 
 int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t * out_top_ids, float * out_top_logprobs, size_t n_top_stride) {
     const HParams & hp = model->hp;
+    // Under expert parallelism a refused plan still takes part in the step's opening exchange (ep_agree), so that
+    // the peers skip the step instead of waiting for this rank; the message set before it is kept.
+    auto refused = [&](int status) {
+        if (ep_comm_) {
+            const std::string message = last_error();
+            try { ep_agree(false); } catch (...) {}
+            set_error(message);
+        }
+        return status;
+    };
     if (!rows || n_rows == 0 || !out_rows) {
         set_error("step rows and output rows are required");
-        return STATUS_INVALID_ARGUMENT;
+        return refused(STATUS_INVALID_ARGUMENT);
     }
     if (n_rows > (size_t)config.n_batch || (n_top_stride != 0 && n_rows > SIZE_MAX / n_top_stride)) {
         set_error("the step row count or output shape exceeds capacity");
-        return STATUS_INVALID_ARGUMENT;
+        return refused(STATUS_INVALID_ARGUMENT);
     }
     PlanChecker plan((int32_t)config.n_seq_max, (int32_t)config.n_batch, (int64_t)n_ctx_seq, (int32_t)hp.vocab, out_top_ids && out_top_logprobs, n_top_stride);
     const auto per_row_adapter = [this](int32_t id) {
@@ -896,12 +926,12 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         return found != adapters_.end() && !found->second.serial;
     };
     for (size_t r = 0; r < n_rows; ++r)
-        if (!plan.check_row(rows, r, per_row_adapter)) return STATUS_INVALID_ARGUMENT;
+        if (!plan.check_row(rows, r, per_row_adapter)) return refused(STATUS_INVALID_ARGUMENT);
     const size_t total = plan.tokens, n_sample = plan.sampling_rows;
     for (size_t r = 0; r < n_rows; ++r) {
         if (rows[r].sample && rows[r].v2 && rows[r].v2->grammar) {
             set_error("grammar-constrained sampling is not available in this backend");
-            return STATUS_RUNTIME;
+            return refused(STATUS_RUNTIME);
         }
     }
 
@@ -916,8 +946,13 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             } else {
                 set_error("the KV cache is full: no free block for the step's tokens (query the extent with the seq_pos entry point)");
             }
-            return STATUS_RUNTIME;
+            return refused(STATUS_RUNTIME);
         }
+    }
+    if (ep_comm_ && !ep_agree(true)) {
+        kv->rollback();
+        set_error("another rank of the expert-parallel group refused its step: this rank's step was skipped and nothing was decoded");
+        return STATUS_RUNTIME;
     }
     kv->commit();
 
@@ -1035,9 +1070,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     if (!copies.empty()) std::memcpy(h_stage_ + off_copies, copies.data(), copies.size() * 4);
     if (S) std::memcpy(h_stage_ + off_descs, descs.data(), S * sizeof(SampleDesc));
     if (!edits.empty()) std::memcpy(h_stage_ + off_edits, edits.data(), edits.size() * sizeof(LogitEdit));
+    // (the two lists are cleared once the step's work is enqueued: if anything on the host fails before that,
+    // they are still queued and travel with the next step, so the device table cannot fall behind the host's)
     const int n_patches = (int)(patches.size() / 2), n_copies = (int)(copies.size() / 2);
-    patches.clear();
-    copies.clear();
 
     // result buffer: [SampleOut x S][top ids S x stride][top logprobs S x stride]
     const size_t res_ids = align_up(S * sizeof(SampleOut), 16);
@@ -1295,6 +1330,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     RB_CUDA(cudaMemcpyAsync(h_result_ + result_bytes_ - 16, device_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream));
     };
     run_step_work(sig, issue);
+    patches.clear();
+    copies.clear();
     const cudaError_t sync = cudaStreamSynchronize(stream);
     if (sync != cudaSuccess) {
         set_error(std::string("the decode failed on the device (") + cudaGetErrorString(sync) +
@@ -1454,6 +1491,7 @@ int Engine::seq_save(int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_bu
     h.payload_bytes = payload;
     if (n_pos) {
         DeviceBuffer<__half> dense;
+        dense.in_graphs = false;
         dense.ensure(payload / sizeof(__half));
         launch_kv_snapshot(kv_layout(), (int)hp.n_layer, block_table_.ptr + (size_t)slot * kv->max_blocks(), s.pos_min, (int)n_pos, dense.ptr, false,
                            stream);
@@ -1510,6 +1548,7 @@ int Engine::seq_load(int32_t slot, uint32_t flags, const uint8_t * buffer, size_
         kv->commit();
         flush_kv_updates();
         DeviceBuffer<__half> dense;
+        dense.in_graphs = false;
         dense.ensure(h.payload_bytes / sizeof(__half));
         RB_CUDA(cudaMemcpyAsync(dense.ptr, buffer + sizeof h, h.payload_bytes, cudaMemcpyHostToDevice, stream));
         launch_kv_snapshot(kv_layout(), (int)hp.n_layer, block_table_.ptr + (size_t)slot * kv->max_blocks(), h.pos_min, (int)n_pos, dense.ptr, true,

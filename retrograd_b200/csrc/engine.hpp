@@ -31,6 +31,7 @@ inline std::atomic<uint64_t> g_alloc_epoch{0};
 template <class T> struct DeviceBuffer {
     T * ptr = nullptr;
     size_t count = 0;
+    bool in_graphs = true;      // false for a temporary no captured step graph can hold: growing it leaves the graphs alone
     DeviceBuffer() = default;
     DeviceBuffer(const DeviceBuffer &) = delete;
     DeviceBuffer & operator=(const DeviceBuffer &) = delete;
@@ -40,7 +41,7 @@ template <class T> struct DeviceBuffer {
         if (ptr) { cudaFree(ptr); ptr = nullptr; count = 0; }
         RB_CUDA(cudaMalloc(&ptr, n * sizeof(T)));
         count = n;
-        ++g_alloc_epoch;        // captured CUDA graphs hold the old pointer
+        if (in_graphs) ++g_alloc_epoch;        // captured CUDA graphs hold the old pointer
         // RB200_POISON=1 fills every new work buffer with 0xFF bytes (NaN as f32/f16): a read of
         // memory the step did not write then shows up in the results instead of depending on luck
         static const bool poison = std::getenv("RB200_POISON") != nullptr;
@@ -291,6 +292,7 @@ private:
     void moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_rows, const int32_t * gather, int gather_div, const int32_t * d_offsets,
                         int n, float * y_out, int ld_out);
     void ep_moe_layer(const LayerWeights & lw, int T);
+    bool ep_agree(bool ready);
     void ep_exchange(const float * send, const std::vector<int32_t> & send_begin, const std::vector<int32_t> & send_count, float * recv,
                      const std::vector<int32_t> & recv_begin, const std::vector<int32_t> & recv_count, int d);
     bool tc5_split_preferred(const WeightView & w, int T, const SplitAct * xs) const;
@@ -344,7 +346,7 @@ private:
     int ep_rank_ = 0, ep_world_ = 1;
     EpPlan ep_plan_;
     int32_t * h_ep_offsets_ = nullptr;        // pinned: every rank's pair offsets of the layer
-    DeviceBuffer<int32_t> ep_all_offsets_, ep_offsets_l_, ep_sorted_l_;
+    DeviceBuffer<int32_t> ep_all_offsets_, ep_offsets_l_, ep_sorted_l_, ep_flags_;
     DeviceBuffer<float> ep_send_, ep_recv_, ep_gu_, ep_h_, ep_y_, ep_back_;
     bool fused_finish_ = true;      // RB200_FUSED_FINISH=0: norm / SwiGLU always as kernels of their own
     SplitBuffer xn_split_, att_split_, hff_split_, hs_split_;

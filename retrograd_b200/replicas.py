@@ -40,3 +40,16 @@ def aggregate(times_ms: Sequence[float], counts: Sequence[float], dist=None, dev
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dist.all_reduce(c, op=dist.ReduceOp.SUM)
     return t.tolist(), c.tolist()
+
+
+def all_ranks_ready(ready: bool, dist=None) -> bool:
+    """The rule every expert-parallel step opens with, for a caller that wants the answer on the host before it
+    submits anything: each rank says whether it has a valid step to run, and the step runs only if all of them
+    do. (The engine applies the same rule inside `retro_engine_step*` over its own communicator: a rank whose
+    plan is refused still joins the exchange, its peers skip the step with a runtime error, nobody waits for a
+    partner that never comes.) `dist` is torch.distributed, initialised, or None for one process."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return bool(ready)
+    flags = [None] * dist.get_world_size()
+    dist.all_gather_object(flags, bool(ready))
+    return all(flags)

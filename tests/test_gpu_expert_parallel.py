@@ -10,50 +10,16 @@ import sys
 import time
 from pathlib import Path
 
-import numpy as np
 import pytest
 
-SPEC = dict(arch="olmoe", layers=2, d=128, heads=4, kv_heads=4, ff=64, vocab=512, experts=8, experts_used=2,
-            dtype="q8_0", expert_dtype="mxfp4", seed=21)
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
 
-
-def _steps(rb, rank):
-    """The rows of each lock-step step of `rank` (None: the rank has nothing to run in that step)."""
-    greedy = rb.SamplingParamsV2.greedy()
-    rng = np.random.default_rng(50 + rank)
-    prompts = [rng.integers(3, 512, 7 + 5 * i + 2 * rank).tolist() for i in range(2 + rank)]
-    return prompts, greedy
-
-
-def _run(rb, engine, rank, idle_last, ep):
-    prompts, greedy = _steps(rb, rank)
-    out = rb.StepOutput()
-    trace = []
-    engine.step([rb.StepRow(i, i, p, 0, sample=True, sampling=greedy, want_logprob=True) for i, p in enumerate(prompts)], out)
-    last = [out.row(i).token for i in range(len(prompts))]
-    trace.append((list(last), [out.row(i).logprob for i in range(len(prompts))], [engine.last_logits(i).copy() for i in range(len(prompts))]))
-    for step in range(3):
-        if idle_last and step == 2:
-            if ep:
-                engine.ep_idle_step()
-            continue
-        rows = [rb.StepRow(i, i, [last[i]], len(p) + step, sample=True, sampling=greedy, want_logprob=True) for i, p in enumerate(prompts)]
-        engine.step(rows, out)
-        last = [out.row(i).token for i in range(len(prompts))]
-        trace.append((list(last), [out.row(i).logprob for i in range(len(prompts))], [engine.last_logits(i).copy() for i in range(len(prompts))]))
-    return trace
+from retrograd_b200.ep_check import SPEC
 
 
 def _rank_main(rank: int, world: int, workdir: Path) -> None:
-    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
     import retrograd_b200 as rb
-
-    model = workdir / f"moe_rank{rank}.gguf"
-    rb.synth_gguf(model, **SPEC)
-    cfg = rb.EngineConfig(n_ctx=512, n_seq_max=4, n_batch=64, n_ubatch=64)
-    plain = rb.Engine(str(model), cfg)
-    want = _run(rb, plain, rank, idle_last=(rank == 1), ep=False)
-    plain.close()
+    from retrograd_b200.ep_check import plain_vs_expert_parallel
 
     id_path = workdir / "nccl_id.bin"
     if rank == 0:
@@ -65,16 +31,27 @@ def _rank_main(rank: int, world: int, workdir: Path) -> None:
         if time.time() > deadline:
             raise SystemExit("no NCCL id from rank 0")
         time.sleep(0.05)
-    engine = rb.Engine(str(model), cfg)
-    engine.ep_init(rank, world, id_path.read_bytes())
-    got = _run(rb, engine, rank, idle_last=(rank == 1), ep=True)
+    result = plain_vs_expert_parallel(rb, rank, world, id_path.read_bytes(), workdir)
+    engine = result["engine"]
+    assert result["bit_exact"], "expert-parallel results differ from the plain engine's"
+    # A plan refused on one rank: rank 1 submits a row in a slot the context does not have. It gets its own -3,
+    # rank 0 (whose plan is fine) gets a runtime error instead of waiting for a partner that never comes, nothing
+    # of rank 0's step becomes resident, and the next common step runs as usual.
+    greedy = rb.SamplingParamsV2.greedy()
+    out = rb.StepOutput()
+    before = engine.seq_pos(3)
+    try:
+        engine.step([rb.StepRow(90, 99 if rank == 1 else 3, [5, 6, 7], 0, sample=True, sampling=greedy)], out)
+        raise SystemExit("the refused step was not reported")
+    except rb.InvalidArgument as err:
+        assert rank == 1 and "slot is outside" in str(err)
+    except rb.EngineError as err:
+        assert rank == 0 and "another rank of the expert-parallel group refused its step" in str(err)
+    assert engine.seq_pos(3) == before == (-1, -1)
+    engine.step([rb.StepRow(91, 3, [5, 6, 7], 0, sample=True, sampling=greedy)], out)
+    assert engine.seq_pos(3) == (0, 2)
     engine.close()
-    assert len(got) == len(want)
-    for (t0, l0, x0), (t1, l1, x1) in zip(want, got):
-        assert t0 == t1 and l0 == l1
-        for a, b in zip(x0, x1):
-            assert np.array_equal(a, b)
-    print(f"rank {rank}: {len(got)} steps equal to the plain engine")
+    print(f"rank {rank}: {result['steps']} steps equal to the plain engine")
 
 
 @pytest.mark.gpu

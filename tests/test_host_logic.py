@@ -138,6 +138,18 @@ def test_synth_models_are_deterministic_and_readable(rb, tmp_path, oracle):
     assert (m.n_layer, m.d, m.n_head, m.n_head_kv, m.head_dim, m.ff, m.vocab) == (1, 256, 4, 2, 64, 512, 512)
 
 
+def test_the_oracle_folders_model_writer_gives_the_same_bytes(rb, oracle, tmp_path):
+    """The benchmark's CPU arm writes its model without loading the GPU library; both arms must run the same file."""
+    for i, spec in enumerate((dict(arch="llama", layers=1, d=256, heads=4, kv_heads=2, ff=512, vocab=512, dtype="q4_k", seed=5),
+                              dict(arch="olmoe", layers=1, d=256, heads=4, kv_heads=4, ff=128, vocab=512, experts=8, experts_used=2, dtype="q8_0",
+                                   expert_dtype="mxfp4", seed=21))):
+        a, b = tmp_path / f"a{i}.gguf", tmp_path / f"b{i}.gguf"
+        rb.synth_gguf(a, **spec)
+        oracle.synth_gguf(b, **spec)
+        assert a.read_bytes() == b.read_bytes()
+    assert oracle.threads(2) == 2 and oracle.threads() == 2
+
+
 @pytest.mark.parametrize("ggml_type,rel", [(8, 0.01), (12, 0.12), (39, 0.3)])
 def test_encoders_round_trip_within_their_step(rb, oracle, ggml_type, rel):
     import numpy as np

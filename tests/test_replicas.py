@@ -59,3 +59,40 @@ def test_routing_keeps_shared_prefixes_together():
     spread = {route(rng.integers(3, 1000, 12).tolist(), 8) for _ in range(200)}
     assert spread == set(range(8))
     assert route([], 4) == route([], 4)
+
+
+def _agreement_worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    from retrograd_b200.replicas import all_ranks_ready
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ran = []
+    for step in range(4):
+        # rank 1's plan for step 2 is refused on the host (an invalid row): it still joins the exchange
+        local_ok = not (rank == 1 and step == 2)
+        if all_ranks_ready(local_ok, dist):
+            ran.append(step)
+    out.put((rank, ran))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_a_refused_step_on_one_rank_is_skipped_by_all_ranks():
+    """Expert-parallel ranks step in lock-step: a refusal on one rank must make every rank skip that step, and
+    the steps after it stay aligned."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_agreement_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results == {0: [0, 1, 3], 1: [0, 1, 3]}
