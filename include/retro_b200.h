@@ -387,6 +387,15 @@ int retro_trainer_generation_adapter_rows_info(retro_trainer * trainer, retro_ad
 
 /* ================= extensions without a counterpart in the reference ================= */
 
+/* The bounds-checked build (libretro_b200_checked.so, compiled with -DRETRO_B200_CHECKED): every index a kernel
+ * reads from device memory (token ids, slots, positions, block-table entries, block ids, adapter indices) is
+ * compared with its range before use; a violation skips the access, is recorded, and makes the step return -1
+ * with the value and its range in the message. retro_b200_checked_build() tells which build is loaded (1 / 0);
+ * retro_b200_engine_check_word() returns {code, value, limit, violations} of the last step (all zero in the
+ * normal build and after a clean step). */
+int retro_b200_checked_build(void);
+int retro_b200_engine_check_word(retro_engine * engine, int32_t out_word_4[4]);
+
 /* A `retro_trainer` that owns nothing but a generation context (see the retro_trainer_generation_*
  * group above); `adapter_path`, when not NULL, is the trained adapter the context decodes under.
  * retro_b200_trainer_weights_updated is the host's notice that the weights behind the context changed. */

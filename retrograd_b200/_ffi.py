@@ -4,7 +4,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libretro_b200.so"
+import os
+
+# RB200_CHECKED=1 selects the bounds-checked build of the same sources (see retro_b200_checked_build in the header)
+LIB_PATH = Path(__file__).resolve().parent / ("libretro_b200_checked.so" if os.environ.get("RB200_CHECKED") == "1" else "libretro_b200.so")
 
 
 class SamplingParamsC(C.Structure):
@@ -255,6 +258,8 @@ SYMBOLS = {
     "retro_b200_op_gemm": (C.c_int, [C.c_uint32, _P(C.c_uint8), C.c_uint32, C.c_uint32, _P(C.c_float), C.c_uint32, _P(C.c_float), C.c_int, C.c_uint32, _P(C.c_float)]),
     "retro_b200_gemm_q4k_noalloc": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]),
     "retro_b200_engine_last_step_io": (C.c_int, [C.c_void_p, _P(C.c_uint64), _P(C.c_uint64)]),
+    "retro_b200_checked_build": (C.c_int, []),
+    "retro_b200_engine_check_word": (C.c_int, [C.c_void_p, _P(C.c_int32)]),
     "retro_b200_engine_graph_stats": (C.c_int, [C.c_void_p, _P(C.c_uint64), _P(C.c_uint64)]),
     "retro_b200_nccl_unique_id": (C.c_int, [C.c_void_p]),
     "retro_b200_engine_expert_storage": (C.c_int, [C.c_void_p, C.c_int, _P(C.c_uint32)]),

@@ -1,6 +1,6 @@
 """Builds libretro_b200.so (the C-ABI library with the sm_100a kernels) in-tree with nvcc.
 
-Usage: python -m retrograd_b200.build [--force]
+Usage: python -m retrograd_b200.build [--force] [--checked]
 Objects are cached under retrograd_b200/build/ and rebuilt when a source or header is newer.
 """
 from __future__ import annotations
@@ -45,9 +45,22 @@ def _newest_header() -> float:
     return max(h.stat().st_mtime for h in headers)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, checked: bool = False) -> Path:
+    """`checked`: the bounds-checked build (-DRETRO_B200_CHECKED) into libretro_b200_checked.so."""
+    global OBJ, OUT
+    if checked:
+        saved = OBJ, OUT
+        OBJ, OUT = HERE / "build_checked", HERE / "libretro_b200_checked.so"
+        try:
+            return _build(force, verbose, ["-DRETRO_B200_CHECKED=1"])
+        finally:
+            OBJ, OUT = saved
+    return _build(force, verbose, [])
+
+
+def _build(force: bool, verbose: bool, defines: list[str]) -> Path:
     OBJ.mkdir(exist_ok=True)
-    flags = _flags()
+    flags = _flags() + defines
     header_time = _newest_header()
     jobs = []
     objects = []
@@ -80,5 +93,5 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, checked="--checked" in sys.argv)
     print(path)

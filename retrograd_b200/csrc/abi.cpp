@@ -1399,6 +1399,26 @@ int retro_b200_ep_plan(const int32_t * all_offsets, int world, int rank, int n_e
     });
 }
 
+int retro_b200_checked_build(void) {
+#ifdef RETRO_B200_CHECKED
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+int retro_b200_engine_check_word(retro_engine * engine, int32_t out_word_4[4]) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e || !out_word_4) {
+            if (e) set_error("out_word_4 is required");
+            return STATUS_RUNTIME;
+        }
+        for (int i = 0; i < 4; ++i) out_word_4[i] = e->last_check[i];
+        return STATUS_OK;
+    });
+}
+
 int retro_b200_engine_last_step_io(retro_engine * engine, uint64_t * out_h2d_bytes, uint64_t * out_d2h_bytes) {
     return boundary([&]() -> int {
         Engine * e = checked(engine);

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(DEC_THREADS) attention_decode_kernel(const flo
         for (int w = 0; w < 4; ++w) {
             const int bi = r * 4 + w;
             if (bi < n_blocks) {
-                const int blk = table[nb0 + bi];
+                const int blk = rb_block(kv, table[nb0 + bi]);
                 const size_t base = ((size_t)blk * kv.n_head_kv + hk) * 16 * HD;
                 const uint32_t k_s = smem_u32(kv_s + ((r % DEC_ROUNDS) * 4 + w) * 2 * TILE_BYTES);
                 const uint32_t v_s = k_s + TILE_BYTES;

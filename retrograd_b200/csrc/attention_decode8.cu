@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_kernel(const flo
 
     uint8_t * ring = smem + (size_t)warp * D8_SLOTS * 2 * TILE_BYTES;
     auto load_block = [&](int j) {
-        const int blk = table[nb0 + b_lo + warp + 4 * j];
+        const int blk = rb_block(kv, table[nb0 + b_lo + warp + 4 * j]);
         const size_t base = ((size_t)blk * kv.n_head_kv + hk) * 16 * HD;
         const uint32_t k_s = smem_u32(ring + (j % D8_SLOTS) * 2 * TILE_BYTES), v_s = k_s + TILE_BYTES;
 #pragma unroll

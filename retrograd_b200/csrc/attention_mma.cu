@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_mma_kernel(const float 
     const int nb0 = pmin >> 4, nb1 = last >> 4;
     const int n_blocks = nb1 - nb0 + 1;
     auto load_block = [&](int bi, int stage) {
-        const int blk = table[nb0 + bi];
+        const int blk = rb_block(kv, table[nb0 + bi]);
         const size_t base = ((size_t)blk * kv.n_head_kv + hk) * 16 * HD;
         const uint32_t k_s = smem_u32(kv_s + stage * 2 * TILE_BYTES);
         const uint32_t v_s = k_s + TILE_BYTES;

@@ -398,6 +398,13 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     }
     device_error_.ensure(1);
     RB_CUDA(cudaMemsetAsync(device_error_.ptr, 0, sizeof(int), stream));
+#ifdef RETRO_B200_CHECKED
+    check_word_.ensure(4);
+    RB_CUDA(cudaMemsetAsync(check_word_.ptr, 0, 4 * sizeof(int), stream));
+    maps.check = check_word_.ptr;
+#endif
+    maps.n_slots = (int32_t)config.n_seq_max;
+    maps.n_blocks = (int32_t)n_blocks;
     if (const char * env = std::getenv("RB200_MMA_MIN_TOKENS")) mma_min_tokens = std::atoi(env);
     if (hp.n_expert == 0) {
         gu_.ensure(T * 2 * hp.ff);
@@ -444,6 +451,8 @@ KvLayout Engine::kv_layout() const {
     l.block_tokens = (int32_t)kBlockTokens;
     l.block_table = block_table_.ptr;
     l.max_blocks = (int32_t)kv->max_blocks();
+    l.n_blocks = (int32_t)kv->n_blocks();
+    l.check = check_word_.ptr;
     return l;
 }
 
@@ -458,7 +467,7 @@ void Engine::flush_kv_updates() {
     std::vector<int32_t> host(patches);
     host.insert(host.end(), copies.begin(), copies.end());
     RB_CUDA(cudaMemcpyAsync(d_aux_.ptr, host.data(), n * 4, cudaMemcpyHostToDevice, stream));
-    launch_block_table_patch(block_table_.ptr, d_aux_.ptr, (int)(patches.size() / 2), stream);
+    launch_block_table_patch(block_table_.ptr, d_aux_.ptr, (int)(patches.size() / 2), stream, (int)block_table_.count, (int)kv->n_blocks(), check_word_.ptr);
     launch_kv_block_copy(kv_layout(), (int)model->hp.n_layer, d_aux_.ptr + patches.size(), (int)(copies.size() / 2), stream);
     RB_CUDA(cudaStreamSynchronize(stream));
     patches.clear();
@@ -1066,6 +1075,15 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             t += row.n;
         }
     }
+#ifdef RETRO_B200_CHECKED
+    // Test hook of the bounds-checked build only: RB200_CHECK_INJECT=token puts an id past the vocabulary into
+    // the staged plan AFTER validation, =block a block id past the pool into the first queued table patch, so
+    // that a test can watch the device-side checks catch them (the accesses are skipped, nothing faults).
+    if (const char * inject = std::getenv("RB200_CHECK_INJECT")) {
+        if (std::string(inject) == "token") h_tokens[0] = (int32_t)hp.vocab + 7;
+        if (std::string(inject) == "block" && patches.size() >= 2) patches[1] = (int32_t)kv->n_blocks() + 3;
+    }
+#endif
     if (!patches.empty()) std::memcpy(h_stage_ + off_patches, patches.data(), patches.size() * 4);
     if (!copies.empty()) std::memcpy(h_stage_ + off_copies, copies.data(), copies.size() * 4);
     if (S) std::memcpy(h_stage_ + off_descs, descs.data(), S * sizeof(SampleDesc));
@@ -1151,11 +1169,13 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         last_launches += (n);        \
     } while (0)
     if (n_patches) {
-        RB_K(K_OTHER, 1, launch_block_table_patch(block_table_.ptr, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_patches), n_patches, stream));
+        RB_K(K_OTHER, 1, launch_block_table_patch(block_table_.ptr, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_patches), n_patches, stream,
+                                                  (int)block_table_.count, (int)kv->n_blocks(), check_word_.ptr));
     }
     if (n_copies) {
         RB_K(K_OTHER, 1, launch_kv_block_copy(kvl, (int)hp.n_layer, reinterpret_cast<const int32_t *>(d_stage_.ptr + off_copies), n_copies, stream));
     }
+    maps.n_adapters = (int32_t)adapters_.size();
     RB_K(K_PACK, 2, launch_pack(d_rows, (int)R, (int)T, block_table_.ptr, kvl.max_blocks, kvl.block_tokens, attn_tile_tokens_, maps, stream));
     cur_tok_adapter_ = maps.tok_adapter;
     cur_any_adapter_ = any_adapter;
@@ -1166,7 +1186,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
 
     const int d = (int)hp.d, dq = (int)hp.dq(), dkv = (int)hp.dkv(), ldqkv = dq + 2 * dkv, ff = (int)hp.ff;
     const int Ti = (int)T;
-    RB_K(K_OTHER, 1, launch_embed(model->token_embd, d_tokens, Ti, x_.ptr, stream));
+    RB_K(K_OTHER, 1, launch_embed(model->token_embd, d_tokens, Ti, x_.ptr, stream, check_word_.ptr));
     bool norm_done = false;         // this layer's attention norm was already written by the previous layer's down projection
     for (uint32_t l = 0; l < hp.n_layer; ++l) {
         const LayerWeights & lw = model->layers[l];
@@ -1329,6 +1349,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     if (S) RB_CUDA(cudaMemcpyAsync(h_result_, d_result_.ptr, res_total - 16, cudaMemcpyDeviceToHost, stream));
     RB_CUDA(cudaMemcpyAsync(h_result_ + result_bytes_ - 16, device_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream));
     };
+#ifdef RETRO_B200_CHECKED
+    graphs_enabled_ = false;        // the check word is read back after every step, outside any captured graph
+#endif
     run_step_work(sig, issue);
     patches.clear();
     copies.clear();
@@ -1350,6 +1373,18 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                   "the submitted tokens (query it with the seq_pos entry point)");
         return STATUS_RUNTIME;
     }
+#ifdef RETRO_B200_CHECKED
+    RB_CUDA(cudaMemcpy(last_check, check_word_.ptr, sizeof last_check, cudaMemcpyDeviceToHost));
+    if (last_check[0] != 0) {
+        static const char * const what[] = {"", "a token id", "a slot", "a position", "a block-table index", "a physical block id", "a KV cell", "an adapter index"};
+        const int code = last_check[0] >= 1 && last_check[0] <= 7 ? last_check[0] : 0;
+        RB_CUDA(cudaMemset(check_word_.ptr, 0, 4 * sizeof(int)));
+        set_error(std::string("bounds-checked build: ") + what[code] + " read on the device was " + std::to_string(last_check[1]) + ", outside [0, " +
+                  std::to_string(last_check[2]) + ") (" + std::to_string(last_check[3]) + " violations in this step); the accesses were skipped, the KV may hold a "
+                  "prefix of the submitted tokens");
+        return STATUS_RUNTIME;
+    }
+#endif
     cudaEventElapsedTime(&last_ms, ev_begin_, ev_end_);
     prof_.collect();
     last_T = T;

@@ -248,6 +248,7 @@ public:
     uint64_t work_buffer_bytes() const;
     GenerationCounters gen_stats;
     uint64_t route_pairs = 0;       // routed (token, expert) pairs served while telemetry was on
+    int last_check[4] = {0, 0, 0, 0};       // bounds-checked build: the check word after the last step
 
     retro_engine_config config{};
     std::string model_path;
@@ -332,6 +333,7 @@ private:
     DeviceBuffer<int32_t> moe_ids_, d_aux_;
     DeviceBuffer<int32_t> moe_offsets_, moe_sorted_, lora_offsets_, lora_sorted_;
     DeviceBuffer<int> device_error_;
+    DeviceBuffer<int> check_word_;      // bounds-checked build: {code, value, limit, count} of the first violation
     DeviceBuffer<float> stream_scratch_;
     DeviceBuffer<uint8_t> sample_scratch_;
     DeviceBuffer<float> attn_scratch_;

@@ -162,26 +162,35 @@ __global__ void pack_fill_kernel(const RowDesc * __restrict__ rows, int n_rows, 
     const RowDesc row = rows[lo];
     const int j = i - maps.cu_rows[lo];
     const int pos = row.pos0 + j;
-    maps.tok_slot[i] = row.slot;
+    RB_CHECK(maps.check, CHECK_SLOT, row.slot, maps.n_slots, return);
+    RB_CHECK(maps.check, CHECK_ADAPTER, row.adapter + 1, maps.n_adapters + 1, return);      // -1 = none
+    RB_CHECK(maps.check, CHECK_POSITION, pos, (long long)max_blocks * block_tokens, return);
     maps.tok_pos[i] = pos;
     maps.tok_row[i] = lo;
     maps.tok_adapter[i] = row.adapter;
     maps.tok_pos_min[i] = row.pos_min;
     const int blk = block_table[(size_t)row.slot * max_blocks + pos / block_tokens];
+    RB_CHECK(maps.check, CHECK_BLOCK, blk, maps.n_blocks, return);
     maps.tok_cell[i] = blk * block_tokens + pos % block_tokens;
     if (row.sample && j == row.n - 1) maps.out_index[maps.out_rank[lo]] = i;
     if (j % tile_tokens == 0) maps.attn_items[maps.tile_rank[lo] + j / tile_tokens] = make_int2(i, min(tile_tokens, row.n - j));
 }
 
-__global__ void block_table_patch_kernel(int32_t * __restrict__ table, const int32_t * __restrict__ patches, int n) {
+__global__ void block_table_patch_kernel(int32_t * __restrict__ table, const int32_t * __restrict__ patches, int n, int table_entries, int n_blocks,
+                                         int * check) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) table[patches[2 * i]] = patches[2 * i + 1];
+    if (i >= n) return;
+    RB_CHECK(check, CHECK_TABLE_INDEX, patches[2 * i], table_entries, return);
+    RB_CHECK(check, CHECK_BLOCK, patches[2 * i + 1], n_blocks, return);
+    table[patches[2 * i]] = patches[2 * i + 1];
 }
 
 // Copies whole KV blocks (all layers, K and V) for copy-on-write of a shared boundary block.
 __global__ void kv_block_copy_kernel(KvLayout kv, int n_layer, const int32_t * __restrict__ pairs) {
     const int pair = blockIdx.x, layer = blockIdx.y;
     const int32_t src = pairs[2 * pair], dst = pairs[2 * pair + 1];
+    RB_CHECK(kv.check, CHECK_BLOCK, src, kv.n_blocks, return);
+    RB_CHECK(kv.check, CHECK_BLOCK, dst, kv.n_blocks, return);
     const size_t block_elems = (size_t)kv.n_head_kv * kv.block_tokens * kv.head_dim;
     const uint4 * ks = reinterpret_cast<const uint4 *>(kv.k + layer * kv.layer_stride + src * block_elems);
     uint4 * kd = reinterpret_cast<uint4 *>(kv.k + layer * kv.layer_stride + dst * block_elems);
@@ -201,7 +210,9 @@ __global__ void kv_snapshot_kernel(KvLayout kv, const int32_t * __restrict__ tab
                                    int to_cache) {
     const int p = blockIdx.x, layer = blockIdx.y >> 1, is_v = blockIdx.y & 1;
     const int pos = pos_first + p;
+    RB_CHECK(kv.check, CHECK_POSITION, pos, (long long)kv.max_blocks * kv.block_tokens, return);
     const int blk = table[pos / kv.block_tokens], off = pos % kv.block_tokens;
+    RB_CHECK(kv.check, CHECK_BLOCK, blk, kv.n_blocks, return);
     __half * cache = (is_v ? kv.v : kv.k) + layer * kv.layer_stride;
     const int row = kv.n_head_kv * kv.head_dim;
     __half * d = dense + ((size_t)blockIdx.y * n_pos + p) * row;
@@ -215,8 +226,9 @@ __global__ void kv_snapshot_kernel(KvLayout kv, const int32_t * __restrict__ tab
 // ------------------------------------------------------------------------------------------
 
 template <uint32_t TYPE>
-__global__ void embed_kernel(WeightView e, const int32_t * __restrict__ tokens, float * __restrict__ x) {
+__global__ void embed_kernel(WeightView e, const int32_t * __restrict__ tokens, float * __restrict__ x, int * check) {
     const int t = blockIdx.x;
+    RB_CHECK(check, CHECK_TOKEN, tokens[t], e.n_out, return);
     const uint8_t * row = e.data + (size_t)tokens[t] * e.row_bytes;
     for (uint32_t k = threadIdx.x * 8; k < e.n_in; k += blockDim.x * 8) {
         float w[8];
@@ -384,6 +396,7 @@ __global__ void rope_store_kernel(float * __restrict__ qkv, int ld, int n_head, 
     }
     __syncthreads();
     const int cell = tok_cell[t];
+    RB_CHECK(kv.check, CHECK_CELL, cell, (long long)kv.n_blocks * kv.block_tokens, return);
     const int blk = cell / kv.block_tokens, off = cell % kv.block_tokens;
     const float * ksrc = row + (size_t)n_head * head_dim;
     const float * vsrc = ksrc + (size_t)n_head_kv * head_dim;
@@ -435,7 +448,7 @@ __global__ void attention_ref_kernel(const float * __restrict__ qkv, int ld, int
             s[u] = 0.f;
             vp[u] = nullptr;
             if (p <= p_last) {
-                const int blk = table[p / B];
+                const int blk = rb_block(kv, table[p / B]);
                 const size_t base = (((size_t)blk * kv.n_head_kv + hk) * B + p % B) * hd;
                 const __half * kp = kbase + base;
                 vp[u] = vbase + base;
@@ -760,9 +773,10 @@ void launch_pack(const RowDesc * rows, int n_rows, int n_tokens, const int32_t *
     pack_fill_kernel<<<(n_tokens + 255) / 256, 256, 0, stream>>>(rows, n_rows, n_tokens, block_table, max_blocks, block_tokens, tile_tokens, maps);
 }
 
-void launch_block_table_patch(int32_t * block_table, const int32_t * patches, int n_patches, cudaStream_t stream) {
+void launch_block_table_patch(int32_t * block_table, const int32_t * patches, int n_patches, cudaStream_t stream, int table_entries, int n_blocks,
+                              int * check) {
     if (n_patches <= 0) return;
-    block_table_patch_kernel<<<(n_patches + 255) / 256, 256, 0, stream>>>(block_table, patches, n_patches);
+    block_table_patch_kernel<<<(n_patches + 255) / 256, 256, 0, stream>>>(block_table, patches, n_patches, table_entries, n_blocks, check);
 }
 
 void launch_kv_block_copy(KvLayout kv, int n_layer, const int32_t * pairs, int n_pairs, cudaStream_t stream) {
@@ -776,9 +790,9 @@ void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int
     kv_snapshot_kernel<<<dim3(n_pos, n_layer * 2), 128, 0, stream>>>(kv, table_row, pos_first, dense, n_pos, to_cache ? 1 : 0);
 }
 
-void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream) {
+void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream, int * check) {
     dispatch_type(embd.type, [&](auto tag) {
-        embed_kernel<decltype(tag)::value><<<n_tokens, 128, 0, stream>>>(embd, tokens, x);
+        embed_kernel<decltype(tag)::value><<<n_tokens, 128, 0, stream>>>(embd, tokens, x, check);
     });
 }
 

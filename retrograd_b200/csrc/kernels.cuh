@@ -92,6 +92,35 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 #endif
 
+// The bounds-checked build (-DRETRO_B200_CHECKED, libretro_b200_checked.so). Every index a kernel takes from
+// device memory - a token id, a slot, a position, a block-table entry, a physical block id, an adapter index -
+// is compared with its range before it is used. The first violation is recorded in the engine's check word
+// {code, value, limit, count} and the access it would have addressed is skipped; the step then returns -1 with
+// the word spelled out. It stands in for a memory checker on machines where none can be run. In the normal
+// build RB_CHECK compiles to nothing and the `check` pointers below stay null.
+enum CheckCode : int { CHECK_OK = 0, CHECK_TOKEN = 1, CHECK_SLOT = 2, CHECK_POSITION = 3, CHECK_TABLE_INDEX = 4, CHECK_BLOCK = 5, CHECK_CELL = 6, CHECK_ADAPTER = 7 };
+#ifdef __CUDACC__
+#ifdef RETRO_B200_CHECKED
+__device__ __forceinline__ bool rb_check_in_range(int * word, int code, long long value, long long limit) {
+    if (value >= 0 && value < limit) return true;
+    if (word) {
+        if (atomicCAS(word, 0, code) == 0) {
+            word[1] = (int)value;
+            word[2] = (int)limit;
+        }
+        atomicAdd(word + 3, 1);
+    }
+    return false;
+}
+#define RB_CHECK(word, code, value, limit, on_fail)                              \
+    do {                                                                         \
+        if (!rb_check_in_range((word), (code), (long long)(value), (long long)(limit))) { on_fail; } \
+    } while (0)
+#else
+#define RB_CHECK(word, code, value, limit, on_fail) do { } while (0)
+#endif
+#endif
+
 // An activation matrix [t][ld] prepared for the exact tensor-core GEMM: the two-term f16 split
 // x = hi + lo, and per 32-element sub-block the sum of x, again as hi + lo ([t][ld / 32]).
 struct SplitAct {
@@ -186,6 +215,9 @@ struct PackMaps {
     int32_t * out_index;   // [S]
     int32_t * tile_rank;   // [R + 1] exclusive scan of the rows' attention tile counts
     int2 * attn_items;     // [sum of tiles] (first token index, tokens in the tile)
+    // ranges for the bounds-checked build
+    int32_t n_slots = 0, n_blocks = 0, n_adapters = 0;
+    int * check = nullptr;
 };
 
 struct KvLayout {
@@ -197,19 +229,34 @@ struct KvLayout {
     int32_t block_tokens;
     const int32_t * block_table;  // [n_slots][max_blocks]
     int32_t max_blocks;
+    // ranges for the bounds-checked build
+    int32_t n_blocks = 0;
+    int * check = nullptr;
 };
+
+#ifdef __CUDACC__
+// A physical block id read from a block table: itself, or - in the bounds-checked build, when it is outside the
+// pool - block 0 with the violation recorded (the kernel keeps its control flow and reads memory it owns).
+__device__ __forceinline__ int rb_block(const KvLayout & kv, int blk) {
+#ifdef RETRO_B200_CHECKED
+    if (!rb_check_in_range(kv.check, CHECK_BLOCK, blk, kv.n_blocks)) return 0;
+#endif
+    return blk;
+}
+#endif
 
 // `tile_tokens`: tokens per attention work item (a row of n tokens yields ceil(n / tile_tokens) items).
 void launch_pack(const RowDesc * rows, int n_rows, int n_tokens, const int32_t * block_table, int max_blocks, int block_tokens,
                  int tile_tokens, PackMaps maps, cudaStream_t stream);
-void launch_block_table_patch(int32_t * block_table, const int32_t * patches, int n_patches, cudaStream_t stream);
+void launch_block_table_patch(int32_t * block_table, const int32_t * patches, int n_patches, cudaStream_t stream, int table_entries = 0, int n_blocks = 0,
+                              int * check = nullptr);
 void launch_kv_block_copy(KvLayout kv, int n_layer, const int32_t * pairs, int n_pairs, cudaStream_t stream);
 
 // Sequence snapshots: dense is [layer][K|V][pos][head][dim] f16 for positions pos_first .. pos_first + n_pos - 1.
 void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int pos_first, int n_pos, __half * dense, bool to_cache,
                         cudaStream_t stream);
 
-void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream);
+void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream, int * check = nullptr);
 // y[t] = x[gather ? gather[t] : t] * rsqrt(mean(x^2) + eps) * w
 // `split`, when given (n a multiple of 32), also receives the row prepared for the tensor-core GEMM.
 void launch_rms_norm(const float * x, int ldx, const int32_t * gather, const float * w, int n, float eps, float * y, int ldy, int n_tokens,
