@@ -387,6 +387,11 @@ int retro_trainer_generation_adapter_rows_info(retro_trainer * trainer, retro_ad
 
 /* ================= extensions without a counterpart in the reference ================= */
 
+/* Host-only check of a text against a GBNF grammar with the engine the step path uses for grammar rows:
+ * *out_state = 0 the text is rejected, 1 it is a valid prefix, 2 it matches the root rule completely; -3 and the
+ * parser's message for an invalid grammar. */
+int retro_b200_grammar_check(const char * gbnf, const char * text, int * out_state);
+
 /* The bounds-checked build (libretro_b200_checked.so, compiled with -DRETRO_B200_CHECKED): every index a kernel
  * reads from device memory (token ids, slots, positions, block-table entries, block ids, adapter indices) is
  * compared with its range before use; a violation skips the access, is recorded, and makes the step return -1
@@ -464,9 +469,10 @@ int retro_b200_gemm_q4k_noalloc(const uint8_t * d_w, uint32_t n_out, uint32_t n_
  * [world][n_expert + 1] -> what this rank sends, receives and how the received rows group by expert);
  * `sorted` needs room for *out_n_recv entries (-2 and the count when sorted_capacity is too small). */
 int retro_b200_nccl_unique_id(void * out_id_128);
-/* GGML type codes the layer's gate / up / down expert banks are held in on the device. MXFP4 banks whose
- * block scales an f16 holds are re-coded, exactly, as Q8_0 at load (type 8) so that the tensor-core GEMM
- * serves them; RB200_MOE=rows keeps them MXFP4 (type 39) on the CUDA-core row kernel. */
+/* GGML type codes the layer's gate / up / down expert banks are held in on the device. MXFP4 banks (type 39)
+ * stay MXFP4: the grouped tcgen05 GEMM decodes the 17-byte blocks itself when every block's E8M0 byte is in
+ * 104..128 (every weight then is an f16); banks outside that range whose scales an f16 still holds are re-coded,
+ * exactly, as Q8_0 (type 8) for the mma.sync grouped GEMM; RB200_MOE=rows keeps the CUDA-core row kernel. */
 int retro_b200_engine_expert_storage(retro_engine * engine, int layer, uint32_t * out_types_3);
 /* The load-time re-coding itself (host only, no GPU): n_blocks MXFP4 blocks (17 B each) -> Q8_0 blocks
  * (34 B each) holding the same values; *out_recoded = 0 and nothing written when a block's scale is not

@@ -12,6 +12,7 @@ from .engine import (
     Engine,
     EngineConfig,
     EngineError,
+    Grammar,
     InvalidArgument,
     SamplingParams,
     SamplingParamsV2,
@@ -19,6 +20,7 @@ from .engine import (
     StepRow,
     TrainerGeneration,
     ep_plan,
+    grammar_check,
     nccl_unique_id,
     op_gemm,
     quantize_row,
@@ -31,6 +33,7 @@ __all__ = [
     "Engine",
     "EngineConfig",
     "EngineError",
+    "Grammar",
     "InvalidArgument",
     "LIB_PATH",
     "SamplingParams",
@@ -39,6 +42,7 @@ __all__ = [
     "StepRow",
     "TrainerGeneration",
     "ep_plan",
+    "grammar_check",
     "load_library",
     "nccl_unique_id",
     "op_gemm",

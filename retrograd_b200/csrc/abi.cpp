@@ -126,27 +126,6 @@ int write_string_out(const std::string & s, char * buffer, size_t n_buffer, size
     return STATUS_OK;
 }
 
-// Byte-fallback SentencePiece-style pieces: `<0xNN>` is one byte, U+2581 is a space.
-std::string piece_bytes(const Model & m, int32_t token, bool unparse_special) {
-    if (token < 0 || (size_t)token >= m.vocab_tokens.size()) return "";
-    const std::string & t = m.vocab_tokens[token];
-    const int32_t type = (size_t)token < m.vocab_types.size() ? m.vocab_types[token] : 1;
-    if (type == 6 && t.size() == 6 && t[0] == '<' && t[1] == '0' && t[2] == 'x') {
-        return std::string(1, (char)std::stoi(t.substr(3, 2), nullptr, 16));
-    }
-    if (type == 3 || type == 2) return unparse_special ? t : "";
-    std::string out;
-    for (size_t i = 0; i < t.size();) {
-        if (i + 2 < t.size() && (uint8_t)t[i] == 0xE2 && (uint8_t)t[i + 1] == 0x96 && (uint8_t)t[i + 2] == 0x81) {
-            out.push_back(' ');
-            i += 3;
-        } else {
-            out.push_back(t[i++]);
-        }
-    }
-    return out;
-}
-
 int tokenize_into(Engine & e, const char * text, bool add_special, int32_t * tokens, size_t n_max, size_t * out_n) {
     if (!text || !out_n) {
         set_error("text and out_n_tokens are required");
@@ -309,7 +288,7 @@ int retro_engine_detokenize(retro_engine * engine, const int32_t * tokens, size_
                 set_error("token is outside the vocabulary");
                 return STATUS_RUNTIME;
             }
-            text += piece_bytes(*e->model, tokens[i], unparse_special);
+            text += e->model->piece(tokens[i], unparse_special);
         }
         return write_string_out(text, buffer, n_buffer, out_n_bytes);
     });
@@ -986,10 +965,6 @@ int retro_engine_expert_route_paths(retro_engine * engine, uint64_t out[3]) {
 
 } // extern "C"
 
-struct retro_grammar {
-    std::string gbnf;
-};
-
 namespace {
 // Any JSON object, in GBNF. Written for this library (the reference embeds its fork's grammar file).
 const char kJsonObjectGbnf[] =
@@ -1041,6 +1016,31 @@ const char * retro_grammar_gbnf(const retro_grammar * grammar) {
 }
 
 void retro_grammar_free(retro_grammar * grammar) { delete grammar; }
+
+// Host-only: how a text stands in a grammar. *out_state = 0 rejected, 1 a valid prefix, 2 complete (the whole
+// text matches the root rule). -3 with the parser's message for an invalid grammar.
+int retro_b200_grammar_check(const char * gbnf, const char * text, int * out_state) {
+    return boundary([&]() -> int {
+        if (!gbnf || !text || !out_state) {
+            set_error("gbnf, text and out_state are required");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        try {
+            GrammarState state;
+            state.grammar = std::make_shared<const Grammar>(gbnf);
+            state.stacks = state.grammar->initial();
+            if (!state.advance(text, false) || !state.pending.empty()) {
+                *out_state = 0;
+            } else {
+                *out_state = Grammar::complete(state.stacks) ? 2 : 1;
+            }
+        } catch (const std::invalid_argument & err) {
+            set_error(err.what());
+            return STATUS_INVALID_ARGUMENT;
+        }
+        return STATUS_OK;
+    });
+}
 
 // ---- the trainer-owned generation context ------------------------------------------------------
 // A retro_trainer made here owns one generation context and nothing else; every twin forwards to the

@@ -232,10 +232,38 @@ void Engine::load_model(const std::string & path) {
         } else {
             lw.router = matrix(p + "ffn_gate_inp.weight", hp.d, hp.n_expert);
             if (lw.router.type != GGML_F32) throw std::runtime_error("failed to load model GGUF: the router must be F32");
+            // MXFP4 banks whose every weight is an f16 (E8M0 bytes 104..128) and whose rows are whole 64-column groups are
+            // held ONLY in the tiled layout of the grouped tcgen05 GEMM: the format's own 17 bytes per 32 weights.
+            bool mxfp4_direct = moe_tensor_cores_ && tensor_maps_available() && hp.d % 64 == 0 && hp.ff % 64 == 0;
+            for (const char * stem : {"ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"}) {
+                const GgufTensor & t = need(p + stem);
+                mxfp4_direct = mxfp4_direct && t.type == GGML_MXFP4 && t.ne.size() == 3 && mxfp4_scales_are_f16(t.data, t.n_bytes / 17);
+            }
             auto bank = [&](const std::string & name, uint64_t n_in, uint64_t n_out, WeightView & w, uint64_t & stride) {
                 const GgufTensor & t = need(name);
                 if (t.ne.size() != 3 || t.ne[0] != n_in || t.ne[1] != n_out || t.ne[2] != hp.n_expert || n_in % 8 != 0) {
                     throw std::runtime_error("failed to load model GGUF: unexpected shape of " + name);
+                }
+                if (mxfp4_direct) {
+                    void * raw = nullptr, * tiled = nullptr;
+                    RB_CUDA(cudaMalloc(&raw, align_up(t.n_bytes, 256)));
+                    RB_CUDA(cudaMemcpy(raw, t.data, t.n_bytes, cudaMemcpyHostToDevice));
+                    const size_t bytes = mxfp4_tiled_bytes(hp.n_expert, (uint32_t)n_out, (uint32_t)n_in);
+                    RB_CUDA(cudaMalloc(&tiled, bytes));
+                    m.allocations.push_back(tiled);
+                    RB_CUDA(cudaDeviceSynchronize());       // the blocking upload has reached the device
+                    launch_mxfp4_retile(static_cast<const uint8_t *>(raw), hp.n_expert, (uint32_t)n_out, (uint32_t)n_in, static_cast<uint8_t *>(tiled), stream);
+                    RB_CUDA(cudaStreamSynchronize(stream));
+                    RB_CUDA(cudaFree(raw));
+                    w = WeightView{};
+                    w.type = GGML_MXFP4;
+                    w.n_in = (uint32_t)n_in;
+                    w.n_out = (uint32_t)n_out;
+                    w.row_bytes = (uint32_t)row_bytes(GGML_MXFP4, n_in);
+                    w.tiled = static_cast<const uint8_t *>(tiled);
+                    m.weight_bytes += bytes;
+                    stride = 0;
+                    return;
                 }
                 // MXFP4 experts whose block scales are powers of two an f16 holds are re-coded, exactly, as Q8_0
                 // (the doubled E2M1 value as the int8, half the E8M0 scale as d): the tensor-core Q8_0 GEMM
@@ -324,6 +352,24 @@ void Engine::load_model(const std::string & path) {
     uint64_t h = fnv1a(path.data(), path.size());
     const uint64_t size = file.file_size();
     fingerprint = fnv1a(&size, sizeof size, h);
+}
+
+std::string Model::piece(int32_t token, bool unparse_special) const {
+    if (token < 0 || (size_t)token >= vocab_tokens.size()) return "";
+    const std::string & t = vocab_tokens[token];
+    const int32_t type = (size_t)token < vocab_types.size() ? vocab_types[token] : 1;
+    if (type == 6 && t.size() == 6 && t[0] == '<' && t[1] == '0' && t[2] == 'x') return std::string(1, (char)std::stoi(t.substr(3, 2), nullptr, 16));
+    if (type == 3 || type == 2) return unparse_special ? t : "";
+    std::string out;
+    for (size_t i = 0; i < t.size();) {
+        if (i + 2 < t.size() && (uint8_t)t[i] == 0xE2 && (uint8_t)t[i + 1] == 0x96 && (uint8_t)t[i + 2] == 0x81) {
+            out.push_back(' ');
+            i += 3;
+        } else {
+            out.push_back(t[i++]);
+        }
+    }
+    return out;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -646,6 +692,7 @@ void Engine::lora(const std::string & target, const float * x, int ldx, int T, f
 
 bool Engine::moe_experts_on_tensor_cores(const LayerWeights & lw) const {
     const HParams & hp = model->hp;
+    if (lw.gate_exps.type == GGML_MXFP4 && lw.gate_exps.tiled) return true;        // the tiled MXFP4 banks of the grouped tcgen05 GEMM
     return moe_tensor_cores_ && lw.gate_exps.type == GGML_Q8_0 && lw.up_exps.type == GGML_Q8_0 && lw.down_exps.type == GGML_Q8_0 &&
            hp.d % 64 == 0 && hp.ff % 64 == 0;
 }
@@ -670,10 +717,18 @@ void Engine::moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_
     moe_y_s_.ensure((size_t)n * d);
     launch_ep_gather_rows(rows, ld_rows, gather, gather_div, n, d, moe_xs_.ptr, stream);
     launch_split_prep(moe_xs_.ptr, d, d, n, moe_x_split_.view, stream);
-    launch_gemm_q8_0_exact_grouped(lw.gate_exps, lw.gate_stride, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr, 2 * ff, stream);
-    launch_gemm_q8_0_exact_grouped(lw.up_exps, lw.up_stride, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr + ff, 2 * ff, stream);
-    launch_swiglu(moe_gu_s_.ptr, 2 * ff, ff, n, nullptr, ff, stream, &moe_h_split_.view);
-    launch_gemm_q8_0_exact_grouped(lw.down_exps, lw.down_stride, E, d_offsets, moe_h_split_.view, n, moe_y_s_.ptr, d, stream);
+    if (gemm_mxfp4_tc5_supported(lw.gate_exps, moe_x_split_.view) && gemm_mxfp4_tc5_supported(lw.down_exps, moe_h_split_.view)) {
+        launch_gemm_mxfp4_tc5_grouped(lw.gate_exps, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr, 2 * ff, device_error_.ptr, stream);
+        launch_gemm_mxfp4_tc5_grouped(lw.up_exps, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr + ff, 2 * ff, device_error_.ptr, stream);
+        launch_swiglu(moe_gu_s_.ptr, 2 * ff, ff, n, nullptr, ff, stream, &moe_h_split_.view);
+        launch_gemm_mxfp4_tc5_grouped(lw.down_exps, E, d_offsets, moe_h_split_.view, n, moe_y_s_.ptr, d, device_error_.ptr, stream);
+    } else {
+        if (!lw.gate_exps.data) throw std::runtime_error("the expert banks are held for the tcgen05 kernel only, but its activation descriptors are unavailable");
+        launch_gemm_q8_0_exact_grouped(lw.gate_exps, lw.gate_stride, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr, 2 * ff, stream);
+        launch_gemm_q8_0_exact_grouped(lw.up_exps, lw.up_stride, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr + ff, 2 * ff, stream);
+        launch_swiglu(moe_gu_s_.ptr, 2 * ff, ff, n, nullptr, ff, stream, &moe_h_split_.view);
+        launch_gemm_q8_0_exact_grouped(lw.down_exps, lw.down_stride, E, d_offsets, moe_h_split_.view, n, moe_y_s_.ptr, d, stream);
+    }
     launch_ep_scatter_rows(moe_y_s_.ptr, gather, n, d, y_out, ld_out, stream);
     last_launches += 7;
 }
@@ -937,10 +992,21 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     for (size_t r = 0; r < n_rows; ++r)
         if (!plan.check_row(rows, r, per_row_adapter)) return refused(STATUS_INVALID_ARGUMENT);
     const size_t total = plan.tokens, n_sample = plan.sampling_rows;
+    // Grammars are compiled before anything is decoded, once per request and text (retro_gen_core.cpp:2518-2537):
+    // a request keeps its place in its grammar from step to step as long as its rows carry the same GBNF.
+    std::vector<std::shared_ptr<const Grammar>> fresh_grammars(n_rows);
+    bool any_grammar = false;
     for (size_t r = 0; r < n_rows; ++r) {
-        if (rows[r].sample && rows[r].v2 && rows[r].v2->grammar) {
-            set_error("grammar-constrained sampling is not available in this backend");
-            return refused(STATUS_RUNTIME);
+        if (!rows[r].sample || !rows[r].v2 || !rows[r].v2->grammar) continue;
+        any_grammar = true;
+        const std::string & gbnf = rows[r].v2->grammar->gbnf;
+        const auto known = requests.find(rows[r].request);
+        if (known != requests.end() && known->second.grammar && known->second.grammar->gbnf == gbnf) continue;
+        try {
+            fresh_grammars[r] = std::make_shared<const Grammar>(gbnf);
+        } catch (const std::invalid_argument & err) {
+            set_error(std::string("failed to compile the request's grammar (invalid GBNF): ") + err.what());
+            return refused(STATUS_INVALID_ARGUMENT);
         }
     }
 
@@ -971,6 +1037,15 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     std::vector<int32_t> & copies = kv->copies();
     std::vector<SampleDesc> descs(S);
     std::vector<LogitEdit> edits;
+    // grammar rows: one bit per token, staged with the plan (the mask depends on the grammar's state, not on the logits)
+    const size_t mask_words = (hp.vocab + 31) / 32;
+    std::vector<uint32_t> masks;
+    std::vector<std::unique_ptr<GrammarState>> row_grammar(n_rows);     // the state a row samples under; installed on success
+    bool grammar_dead_end = false;
+    if (any_grammar && token_pieces_.empty()) {
+        token_pieces_.resize(hp.vocab);
+        for (uint32_t t = 0; t < hp.vocab; ++t) token_pieces_[t] = model->piece((int32_t)t, false);
+    }
     size_t top_stride = 0;
     bool any_v2 = false;       // some row needs the working copy of the logits
     int n_greedy_fast = 0;
@@ -999,6 +1074,30 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 d.top_k = p.top_k;
                 d.min_p = p.min_p;
                 d.flags = 1u | (row.want_logprob ? 2u : 0u);
+                if (p.grammar) {
+                    auto state = std::make_unique<GrammarState>();
+                    if (fresh_grammars[r]) {
+                        state->grammar = fresh_grammars[r];
+                        state->gbnf = p.grammar->gbnf;
+                        state->stacks = state->grammar->initial();
+                    } else {
+                        *state = *req.grammar;
+                    }
+                    d.pad[0] = (uint32_t)masks.size() + 1;       // word offset of this row's mask, plus one
+                    masks.resize(masks.size() + mask_words, 0u);
+                    uint32_t * bits = masks.data() + masks.size() - mask_words;
+                    const GrammarState & g = *state;
+                    bool any_allowed = false;
+#pragma omp parallel for schedule(static) reduction(|| : any_allowed)
+                    for (long long t = 0; t < (long long)hp.vocab; ++t) {
+                        if (!g.allows(token_pieces_[t], model->is_eog((int32_t)t))) continue;
+#pragma omp atomic
+                        bits[t >> 5] |= 1u << (t & 31);
+                        any_allowed = true;
+                    }
+                    grammar_dead_end = grammar_dead_end || !any_allowed;
+                    row_grammar[r] = std::move(state);
+                }
                 // one merged edit per distinct id: summed bias, then the penalties of the window
                 std::map<int32_t, LogitEdit> merged;
                 for (uint32_t i = 0; i < p.n_logit_bias; ++i) {
@@ -1020,7 +1119,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 }
                 for (const auto & e : merged) edits.push_back(e.second);
                 d.edit_end = (uint32_t)edits.size();
-                if (p.top_k == 1 && merged.empty()) {
+                if (p.top_k == 1 && merged.empty() && !p.grammar) {
                     d.flags |= 4u;      // plain greedy: arg-max of the raw row, no working copy
                     ++n_greedy_fast;
                 } else {
@@ -1042,7 +1141,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     size_t off_copies = align_up(off_patches + patches.size() * 4, 16);
     size_t off_descs = align_up(off_copies + copies.size() * 4, 16);
     size_t off_edits = align_up(off_descs + S * sizeof(SampleDesc), 16);
-    size_t stage_total = align_up(off_edits + edits.size() * sizeof(LogitEdit), 16);
+    size_t off_masks = align_up(off_edits + edits.size() * sizeof(LogitEdit), 16);
+    size_t stage_total = align_up(off_masks + masks.size() * sizeof(uint32_t), 16);
     if (stage_total > stage_bytes_) {
         if (h_stage_) cudaFreeHost(h_stage_);
         h_stage_ = nullptr;
@@ -1088,6 +1188,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     if (!copies.empty()) std::memcpy(h_stage_ + off_copies, copies.data(), copies.size() * 4);
     if (S) std::memcpy(h_stage_ + off_descs, descs.data(), S * sizeof(SampleDesc));
     if (!edits.empty()) std::memcpy(h_stage_ + off_edits, edits.data(), edits.size() * sizeof(LogitEdit));
+    if (!masks.empty()) std::memcpy(h_stage_ + off_masks, masks.data(), masks.size() * sizeof(uint32_t));
     // (the two lists are cleared once the step's work is enqueued: if anything on the host fails before that,
     // they are still queued and travel with the next step, so the device table cannot fall behind the host's)
     const int n_patches = (int)(patches.size() / 2), n_copies = (int)(copies.size() / 2);
@@ -1154,7 +1255,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     last_d2h_bytes = S ? res_total - 16 : 0;
     const std::vector<uint64_t> sig = {R, T, S, (uint64_t)n_patches, (uint64_t)n_copies, edits.size(), top_stride, any_v2, (uint64_t)n_greedy_fast,
                                        any_adapter, (uint64_t)n_attn_items, (uint64_t)n_small_items, any_wide_item, any_mid_item,
-                                       (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_, (uint64_t)adapters_.size()};
+                                       (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_, (uint64_t)adapters_.size(), (uint64_t)masks.size()};
     auto issue = [&]() {
     last_launches = 0;
     RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
@@ -1342,7 +1443,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         }
         RB_K(K_SAMPLE, (n_greedy_fast < (int)S ? 1 : 0) + (n_greedy_fast ? 2 : 0), launch_sample(logits.ptr, any_v2 ? logits_work_.ptr : nullptr, (int)hp.vocab, (int)S,
                                         reinterpret_cast<const SampleDesc *>(d_stage_.ptr + off_descs),
-                                        reinterpret_cast<const LogitEdit *>(d_stage_.ptr + off_edits), d_out, d_top_ids, d_top_lps,
+                                        reinterpret_cast<const LogitEdit *>(d_stage_.ptr + off_edits),
+                                        masks.empty() ? nullptr : reinterpret_cast<const uint32_t *>(d_stage_.ptr + off_masks), d_out, d_top_ids, d_top_lps,
                                         (int)std::max<size_t>(top_stride, 1), n_greedy_fast, sample_scratch_.ptr, stream));
     }
 #undef RB_K
@@ -1400,6 +1502,12 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         route_pairs += ids.size();      // every pair is served from a bank resident on the device
     }
 
+    if (grammar_dead_end) {
+        // as in the reference, the decode has happened by the time a grammar turns out to allow nothing (retro_gen_core.cpp:790-797)
+        set_error("grammar allows no token at this position");
+        return STATUS_RUNTIME;
+    }
+
     // ---- outputs
     const SampleOut * h_out = reinterpret_cast<const SampleOut *>(h_result_);
     const int32_t * h_ids = reinterpret_cast<const int32_t *>(h_result_ + res_ids);
@@ -1424,6 +1532,13 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         RequestState & req = requests[row.request];
         ++req.draws;
         if (row.v2) req.history.push_back(so.token);
+        // the request's grammar follows the emitted token; a row without one drops what the request had
+        if (row_grammar[r]) {
+            row_grammar[r]->advance(model->piece(so.token, false), model->is_eog(so.token));
+            req.grammar = std::move(row_grammar[r]);
+        } else if (row.v2) {
+            req.grammar.reset();
+        }
         ++s;
     }
     return STATUS_OK;

@@ -10,6 +10,7 @@
 #include "kernels.cuh"
 #include "ep.hpp"
 #include "kv.hpp"
+#include "grammar.hpp"
 
 #include <map>
 #include <memory>
@@ -18,6 +19,11 @@
 #include <vector>
 
 #include "../../include/retro_b200.h"
+
+// A grammar handle of the C ABI: an owned GBNF text (retro_grammar.cpp:1-76 in the reference).
+struct retro_grammar {
+    std::string gbnf;
+};
 
 namespace rb200 {
 
@@ -165,6 +171,9 @@ struct Model {
     std::vector<retro_expert_bank_desc> expert_banks;   // as the GGUF holds them, sorted by tensor name
     std::vector<uint8_t> eog;                           // per token: ends a generation (EOS, EOT, EOM and the known end-of-turn pieces)
     bool is_eog(int32_t token) const { return token >= 0 && (size_t)token < eog.size() ? eog[token] != 0 : token == eos; }
+    // The text of a token: byte-fallback pieces `<0xNN>` are one byte, U+2581 is a space, control pieces are empty
+    // unless `unparse_special`.
+    std::string piece(int32_t token, bool unparse_special) const;
     int32_t eos = 2, bos = 1;
     bool add_bos = true;
     ~Model() { for (void * p : allocations) cudaFree(p); }
@@ -196,6 +205,7 @@ struct RequestState {
     uint32_t seed = 0;
     uint64_t draws = 0;
     std::vector<int32_t> history;
+    std::unique_ptr<GrammarState> grammar;      // v2 rows with a grammar: where the generation stands in it
 };
 
 // A step row normalised from either ABI version.
@@ -361,6 +371,7 @@ private:
     std::map<std::string, int32_t> serial_ids_;      // name -> id in adapters_
     std::string active_name_;
     int32_t active_id_ = 0;
+    std::vector<std::string> token_pieces_;         // every token's text, built when the first grammar row arrives
     std::map<int32_t, Adapter> adapters_;
     std::map<int32_t, int32_t> adapter_index_;   // id -> stack index
     int32_t next_adapter_id_ = 1;

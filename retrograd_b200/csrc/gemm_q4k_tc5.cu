@@ -374,13 +374,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
 
 } // namespace
 
-bool split_act_encode_maps(SplitAct & s, size_t rows) {
-    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                 CUtensorMapFloatOOBfill);
+namespace {
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                             const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn tensor_map_encoder() {
     static EncodeFn encode = nullptr;
     static bool looked = false;
-    s.has_maps = 0;
     if (!looked) {
         looked = true;
         void * fn = nullptr;
@@ -390,6 +389,15 @@ bool split_act_encode_maps(SplitAct & s, size_t rows) {
             encode = reinterpret_cast<EncodeFn>(fn);
         }
     }
+    return encode;
+}
+} // namespace
+
+bool tensor_maps_available() { return tensor_map_encoder() != nullptr; }
+
+bool split_act_encode_maps(SplitAct & s, size_t rows) {
+    const EncodeFn encode = tensor_map_encoder();
+    s.has_maps = 0;
     if (!encode || !s.hi || s.ld % 64 != 0 || rows == 0) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)s.ld, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)s.ld * sizeof(__half)};

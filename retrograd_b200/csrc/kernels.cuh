@@ -44,6 +44,17 @@ inline size_t q4k_tiled_bytes(uint32_t n_out, uint32_t n_in) { return (size_t)((
 // Regroups GGUF-layout Q4_K rows into the tiled layout (device to device).
 void launch_q4k_retile(const uint8_t * rows, uint32_t n_out, uint32_t n_in, uint32_t row_bytes, uint8_t * tiled, cudaStream_t stream);
 
+// Tile-major copy of an MXFP4 expert bank: one 4352-byte tile per (expert, 128 rows, 64 columns), tiles of a row
+// tile consecutive over the column groups: the rows' 32 nibble bytes (row p at 32 p), then their two E8M0 bytes.
+constexpr size_t kMxfp4TileBytes = 4352;
+size_t mxfp4_tiled_bytes(uint32_t n_expert, uint32_t n_out, uint32_t n_in);
+// Regroups a GGUF-layout MXFP4 bank [expert][row][blocks of 17 bytes] into the tiled layout (device to device).
+void launch_mxfp4_retile(const uint8_t * bank, uint32_t n_expert, uint32_t n_out, uint32_t n_in, uint8_t * tiled, cudaStream_t stream);
+// Whether every block's E8M0 byte is in 104..128, i.e. every weight of the bank is an f16 (host memory).
+bool mxfp4_scales_are_f16(const uint8_t * blocks, size_t n_blocks);
+// Whether the driver offers tensor-map encoding (the TMA descriptors of the activation operands).
+bool tensor_maps_available();
+
 #ifdef __CUDACC__
 // Kernel function attributes (the opt-in to more than 48 KB of dynamic shared memory) belong to a
 // device, not to the process: first() is true the first time it is called with a given device current.
@@ -271,6 +282,11 @@ void launch_gemm_q4k_exact(const WeightView & w, const SplitAct & x, int n_token
 // tcgen05 / tensor-memory variant of the exact GEMM (128 x 128 tiles). `error_flag` (device int) is
 // raised if a pipeline wait inside the kernel timed out.
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x);
+// The grouped MXFP4 expert GEMM on tcgen05: rows [offsets[g], offsets[g + 1]) of x (the pairs sorted by expert) times
+// expert g's bank (w.tiled, the tiled layout above; w.n_out rows per expert); y rows in the same order.
+bool gemm_mxfp4_tc5_supported(const WeightView & w, const SplitAct & x);
+void launch_gemm_mxfp4_tc5_grouped(const WeightView & w, int n_groups, const int32_t * group_offsets, const SplitAct & x, int max_group_rows, float * y,
+                                   int ldy, int * error_flag, cudaStream_t stream);
 // Whether the tcgen05 kernel's arithmetic covers these blocks (host memory, GGUF layout): it carries a row's
 // minimum term as (dmin / d) * m inside the sum that d scales, so a super-block needs d != 0 unless its
 // dmin * m are all zero, and |dmin / d * m| well inside the f16 range. Encoders produce nothing else.
@@ -382,7 +398,9 @@ void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float
 // Rows whose flags carry bit 2 (v2, top_k == 1, no logit edits) are served by chunked arg-max kernels
 // that need `scratch` (sample_scratch_bytes()); `n_greedy_fast` is how many rows carry the bit.
 size_t sample_scratch_bytes(int n_vocab, int n_rows);
-void launch_sample(const float * raw_logits, float * work_logits, int n_vocab, int n_rows, const SampleDesc * desc, const LogitEdit * edits, SampleOut * out,
-                   int32_t * top_ids, float * top_logprobs, int top_stride, int n_greedy_fast, void * scratch, cudaStream_t stream);
+// `masks`: grammar rows carry in desc.pad[0] the word offset (plus one) of their one-bit-per-token mask; null without such rows.
+void launch_sample(const float * raw_logits, float * work_logits, int n_vocab, int n_rows, const SampleDesc * desc, const LogitEdit * edits,
+                   const uint32_t * masks, SampleOut * out, int32_t * top_ids, float * top_logprobs, int top_stride, int n_greedy_fast, void * scratch,
+                   cudaStream_t stream);
 
 } // namespace rb200

@@ -208,7 +208,7 @@ __device__ void radix_select(Shared & sh, const float * __restrict__ l, int V, b
 
 __global__ void __launch_bounds__(kThreads) sample_kernel(const float * __restrict__ raw_logits, float * __restrict__ work_logits, int V,
                                                           const SampleDesc * __restrict__ descs, const LogitEdit * __restrict__ edits,
-                                                          SampleOut * __restrict__ outs,
+                                                          const uint32_t * __restrict__ masks, SampleOut * __restrict__ outs,
                                                           int32_t * __restrict__ top_ids, float * __restrict__ top_lps, int top_stride) {
     __shared__ Shared sh;
     const int row = blockIdx.x;
@@ -268,6 +268,13 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float * __restri
             l[ed.id] = t;
         }
         __syncthreads();
+        // grammar mask: one bit per token, tokens the grammar cannot continue with drop out here
+        if (d.pad[0] != 0 && masks) {
+            const uint32_t * bits = masks + (d.pad[0] - 1);
+            for (int i = tid; i < V; i += kThreads)
+                if (!((bits[i >> 5] >> (i & 31)) & 1u)) l[i] = -INFINITY;
+            __syncthreads();
+        }
         // top_k (count based, ties keep the lowest ids)
         if (d.top_k > 0 && d.top_k < V) {
             uint32_t thr;
@@ -563,11 +570,12 @@ __global__ void greedy_finish_kernel(const float * __restrict__ raw_logits, int 
 
 size_t sample_scratch_bytes(int n_vocab, int n_rows) { return (size_t)n_rows * ((n_vocab + kChunk - 1) / kChunk) * sizeof(ChunkStat); }
 
-void launch_sample(const float * raw_logits, float * work_logits, int n_vocab, int n_rows, const SampleDesc * desc, const LogitEdit * edits, SampleOut * out,
+void launch_sample(const float * raw_logits, float * work_logits, int n_vocab, int n_rows, const SampleDesc * desc, const LogitEdit * edits,
+                   const uint32_t * masks, SampleOut * out,
                    int32_t * top_ids, float * top_logprobs, int top_stride, int n_greedy_fast, void * scratch, cudaStream_t stream) {
     if (n_rows <= 0) return;
     if (n_greedy_fast < n_rows)
-        sample_kernel<<<n_rows, kThreads, 0, stream>>>(raw_logits, work_logits, n_vocab, desc, edits, out, top_ids, top_logprobs, top_stride);
+        sample_kernel<<<n_rows, kThreads, 0, stream>>>(raw_logits, work_logits, n_vocab, desc, edits, masks, out, top_ids, top_logprobs, top_stride);
     if (n_greedy_fast > 0) {
         const int n_chunks = (n_vocab + kChunk - 1) / kChunk;
         ChunkStat * stats = static_cast<ChunkStat *>(scratch);

@@ -63,6 +63,7 @@ class SamplingParamsV2:
     presence_penalty: float = 0.0
     penalty_window: int = 0
     logit_bias: Sequence[tuple[int, float]] = ()
+    grammar: "Grammar | None" = None
 
     @classmethod
     def greedy(cls) -> "SamplingParamsV2":
@@ -72,6 +73,42 @@ class SamplingParamsV2:
     @classmethod
     def from_v1(cls, p: SamplingParams) -> "SamplingParamsV2":
         return cls(temperature=p.temperature, top_p=p.top_p, max_new_tokens=p.max_new_tokens, seed=p.seed)
+
+
+class Grammar:
+    """An owned GBNF text (`retro_grammar_from_gbnf`); rows that carry it sample only tokens the grammar can
+    continue with. The handle may be dropped as soon as the step that carried it has returned."""
+
+    def __init__(self, gbnf: str) -> None:
+        self._lib = _ffi.load_library()
+        self._h = self._lib.retro_grammar_from_gbnf(gbnf.encode())
+        if not self._h:
+            raise EngineError(_last_error())
+
+    @classmethod
+    def json_object(cls) -> "Grammar":
+        g = cls.__new__(cls)
+        g._lib = _ffi.load_library()
+        g._h = g._lib.retro_grammar_json_object()
+        return g
+
+    def gbnf(self) -> str:
+        return self._lib.retro_grammar_gbnf(self._h).decode()
+
+    def __del__(self) -> None:  # pragma: no cover
+        try:
+            if self._h:
+                self._lib.retro_grammar_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+def grammar_check(gbnf: str, text: str) -> int:
+    """0 = the grammar rejects `text`, 1 = a valid prefix, 2 = a complete match (host only)."""
+    state = C.c_int()
+    _check(_ffi.load_library().retro_b200_grammar_check(gbnf.encode(), text.encode(), C.byref(state)))
+    return state.value
 
 
 @dataclass
@@ -371,6 +408,8 @@ class Engine:
                 c.sampling.n_logit_bias = ids.size
                 c.sampling.logit_bias_ids = ids.ctypes.data_as(C.POINTER(C.c_int32))
                 c.sampling.logit_bias_values = vals.ctypes.data_as(C.POINTER(C.c_float))
+            if s.grammar is not None:
+                c.sampling.grammar = s.grammar._h
             c.n_top_logprobs, c.want_logprob, c.adapter = r.n_top_logprobs, int(r.want_logprob), r.adapter
         requests = [r.request for r in rows if r.request >= 0]
         if len(requests) != len(set(requests)):

@@ -28,8 +28,8 @@ def _child() -> None:
     assert lib.retro_b200_checked_build() == 1 and rb.LIB_PATH.name == "libretro_b200_checked.so"
     model = Path(sys.argv[2]) / "c1.gguf"
     rb.synth_gguf(model, **C1_SPEC)
-    engine = rb.Engine(str(model), rb.EngineConfig(n_ctx=2048, n_seq_max=8, n_batch=256, n_ubatch=256))
-    octx = O.Context(O.Model(str(model)), 8, 2048)
+    engine = rb.Engine(str(model), rb.EngineConfig(n_ctx=4096, n_seq_max=8, n_batch=1024, n_ubatch=1024))
+    octx = O.Context(O.Model(str(model)), 8, 4096)
     out, rep, greedy = rb.StepOutput(), ParityReport(), rb.SamplingParamsV2.greedy()
     rng = np.random.default_rng(7)
     prefix = rng.integers(3, 4096, 32).tolist()

@@ -182,10 +182,10 @@ def test_full_8b_shape_logits_within_tolerance(rb, oracle):
     engine.close()
 
 
-def test_moe_experts_recoded_for_the_tensor_cores_agree_with_the_row_kernel(rb, models, monkeypatch):
-    """MXFP4 expert banks are re-coded, value for value, as Q8_0 at load and served by the tensor-core GEMM,
-    one launch per expert; RB200_MOE=rows keeps the CUDA-core row kernel on the MXFP4 bytes. Same weights,
-    two summation orders: routing equal, logits within 2e-4, greedy tokens equal."""
+def test_moe_experts_on_the_tensor_cores_agree_with_the_row_kernel(rb, models, monkeypatch):
+    """MXFP4 expert banks are decoded by the grouped tcgen05 GEMM straight from their 17-byte blocks (one launch
+    per projection for all experts); RB200_MOE=rows keeps the CUDA-core row kernel on the same bytes. Same
+    weights, two summation orders: routing equal, logits within 2e-4, greedy tokens equal."""
     spec = dict(arch="olmoe", layers=2, d=128, heads=4, kv_heads=4, ff=64, vocab=512, experts=8, experts_used=2,
                 dtype="q8_0", expert_dtype="mxfp4", seed=21)
     path = models("moe_flat", **spec)
@@ -212,7 +212,7 @@ def test_moe_experts_recoded_for_the_tensor_cores_agree_with_the_row_kernel(rb, 
 
     s_tc, t_tc, l_tc, l2_tc, r_tc = run(False)
     s_rows, t_rows, l_rows, l2_rows, r_rows = run(True)
-    assert s_tc == (8, 8, 8) and s_rows == (39, 39, 39)
+    assert s_tc == (39, 39, 39) and s_rows == (39, 39, 39)          # MXFP4 as stored, in both forms
     assert np.array_equal(r_tc, r_rows) and t_tc == t_rows
     err = max(float(np.abs(l_tc - l_rows).max()), float(np.abs(l2_tc - l2_rows).max()))
     print(f"moe tensor-core vs row kernel: max|dlogit|={err:.3e}")
