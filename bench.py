@@ -68,6 +68,30 @@ WORKLOADS = {
         spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q8_0", seed=3),
         n_requests=8, prompt=(64, 512), output=(2048, 4096), chunk=512, n_batch=512, n_ctx=65536,
     ),
+    # the rollout workload: the 8B shape in Q8_0, 64 prompts each sampled as a group of 8 whose members share the
+    # prompt's KV blocks (one prefill per group, then whole-sequence copies), temperature 1.0, top-p 1.0, seeded.
+    # All 512 samples start together, as a rollout batch does: the timed steps are decode steps of 512 rows.
+    "c3": dict(
+        name="llama3-8b-shape Q8_0 rollout, 64 prompts x groups of 8 sharing the prompt KV, temperature 1.0 seeded",
+        spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q8_0", seed=3),
+        n_requests=512, group=8, prompt=(256, 1024), output=(512, 512), chunk=512, n_batch=2048, n_ctx=340_000, temperature=1.0,
+    ),
+    # multi-adapter decode: the Q4_K base with 16 rank-16 adapters (alpha 32) on all seven projections, 128
+    # requests assigned to adapters by Zipf(1.1)
+    "c4": dict(
+        name="llama3-8b-shape Q4_K + 16 rank-16 LoRA adapters on q/k/v/o/gate/up/down, 128 requests assigned by Zipf(1.1)",
+        model="c2",
+        spec=dict(arch="llama", layers=32, d=4096, heads=32, kv_heads=8, ff=14336, vocab=128256, dtype="q4_k", seed=2),
+        n_requests=128, prompt=(128, 2048), output=(256, 256), chunk=512, n_batch=2048, n_ctx=300_000,
+        adapters=dict(n=16, rank=16, alpha=32.0, zipf=1.1),
+    ),
+    # the gpt-oss-20b-like MoE shape at its own size: 24 layers, 512 ragged requests
+    "c5": dict(
+        name="gpt-oss-20b-shape MoE (24 layers, 32 experts top-4, MXFP4 experts), 512 ragged requests per GPU",
+        spec=dict(arch="olmoe", layers=24, d=2880, heads=64, kv_heads=8, head_dim=64, ff=2880, vocab=201088, experts=32, experts_used=4,
+                  dtype="q8_0", expert_dtype="mxfp4", seed=5),
+        n_requests=512, prompt=(64, 2048), output=(128, 512), chunk=512, n_batch=2048, n_ctx=720_000, ep=True,
+    ),
     # the gpt-oss-20b-like MoE shape cut to 6 of its 24 layers (a full-depth model costs a quarter of an hour of
     # GPU time per run): experts MXFP4, the rest Q8_0. With more than one GPU the ranks form an expert-parallel
     # group: each serves 32 / N experts and its own requests.
@@ -123,12 +147,40 @@ def ensure_model(workload: str, rank: int, host_only: bool = False) -> Path:
     return path
 
 
+def write_adapter(path: Path, sp: dict, rank: int, alpha: float, seed: int) -> None:
+    """A seeded LoRA adapter GGUF (general.type = adapter) with A [rank, in] and B [out, rank] ~ N(0, 0.02) on the
+    seven projections of every layer, written with the gguf package of the image."""
+    import gguf
+
+    rng = np.random.default_rng(seed)
+    hd = sp.get("head_dim") or sp["d"] // sp["heads"]
+    d, dq, dkv, ff = sp["d"], sp["heads"] * hd, sp["kv_heads"] * hd, sp["ff"]
+    shapes = {"attn_q": (d, dq), "attn_k": (d, dkv), "attn_v": (d, dkv), "attn_output": (dq, d), "ffn_gate": (d, ff), "ffn_up": (d, ff), "ffn_down": (ff, d)}
+    w = gguf.GGUFWriter(str(path), "llama")
+    w.add_string("general.type", "adapter")
+    w.add_string("adapter.type", "lora")
+    w.add_float32("adapter.lora.alpha", float(alpha))
+    for layer in range(sp["layers"]):
+        for target, (n_in, n_out) in shapes.items():
+            w.add_tensor(f"blk.{layer}.{target}.weight.lora_a", rng.standard_normal((rank, n_in), dtype=np.float32) * np.float32(0.02))
+            w.add_tensor(f"blk.{layer}.{target}.weight.lora_b", rng.standard_normal((n_out, rank), dtype=np.float32) * np.float32(0.02))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+
 class Request:
-    __slots__ = ("rid", "prompt", "n_out", "slot", "pos", "done", "last", "times")
+    __slots__ = ("rid", "prompt", "n_out", "slot", "pos", "done", "last", "times", "adapter", "members", "waiting", "need", "sampling")
 
     def __init__(self, rid, prompt, n_out):
         self.rid, self.prompt, self.n_out = rid, prompt, n_out
         self.slot, self.pos, self.done, self.last, self.times = -1, 0, 0, None, []
+        self.adapter = 0            # index into the loaded adapters + 1; 0 = none
+        self.members = None         # a group leader's other members, until the prompt's blocks are shared with them
+        self.waiting = False        # a group member whose leader is still prefilling the shared prompt
+        self.need = len(prompt) + n_out
+        self.sampling = None
 
 
 class Workload:
@@ -139,6 +191,11 @@ class Workload:
         self.rng = np.random.default_rng(seed)
         self.next_id = 0
         self.vocab = cfg["spec"]["vocab"]
+        zipf = cfg.get("adapters")
+        self.adapter_p = None
+        if zipf:
+            w = 1.0 / np.arange(1, zipf["n"] + 1) ** zipf["zipf"]
+            self.adapter_p = w / w.sum()
 
     def request(self, midflight: bool = False) -> Request:
         lo, hi = self.cfg["prompt"]
@@ -152,8 +209,22 @@ class Workload:
             n_out -= produced
         prompt = self.rng.integers(3, self.vocab, n_prompt, dtype=np.int32)
         r = Request(self.next_id, prompt, max(n_out, 1))
+        if self.adapter_p is not None:
+            r.adapter = 1 + int(self.rng.choice(len(self.adapter_p), p=self.adapter_p))
         self.next_id += 1
         return r
+
+    def group(self, size: int) -> list:
+        """A prompt sampled `size` times: the leader carries the prompt, the members wait for its blocks."""
+        leader = self.request()
+        members = []
+        for _ in range(size - 1):
+            m = Request(self.next_id, leader.prompt, leader.n_out)
+            m.waiting, m.need = True, leader.n_out
+            self.next_id += 1
+            members.append(m)
+        leader.members = members
+        return [leader] + members
 
 
 class Driver:
@@ -168,8 +239,28 @@ class Driver:
         self.out = rb.StepOutput(cfg["n_batch"], 0)
         self.reserved = 0
         self.expert_parallel = False      # set when the engine joined an expert-parallel group: every rank steps in lock-step
+        self.adapter_ids = []             # engine ids of the loaded adapters, in the order Request.adapter counts them
+
+    def sampling_of(self, r):
+        if self.cfg.get("temperature") is None:
+            return self.sampling
+        if r.sampling is None:
+            r.sampling = self.rb.SamplingParamsV2(temperature=self.cfg["temperature"], top_p=1.0, seed=20261125 + r.rid)
+        return r.sampling
 
     def admit(self, midflight=False):
+        size = self.cfg.get("group")
+        while size and len(self.free_slots) >= size:
+            group = self.wl.group(size)
+            need = sum(r.need for r in group)
+            if self.reserved + need > self.cfg["n_ctx"]:
+                break
+            self.reserved += need
+            for r in group:
+                r.slot = self.free_slots.pop()
+                self.live.append(r)
+        if size:
+            return
         while self.free_slots:
             r = self.wl.request(midflight)
             need = len(r.prompt) + r.n_out
@@ -187,17 +278,33 @@ class Driver:
             if prefill_only or (decode_only and len(rows) >= decode_only):
                 break
             if r.last is not None and budget > 0:
-                rows.append(rb.StepRow(r.rid, r.slot, [r.last], len(r.prompt) + r.done - 1, True, self.sampling))
+                rows.append(rb.StepRow(r.rid, r.slot, [r.last], len(r.prompt) + r.done - 1, True, self.sampling_of(r), adapter=self.adapter_of(r)))
                 kinds.append(r)
                 budget -= 1
         for r in self.live:
-            if r.last is None and budget > 0 and not decode_only:
-                take = min(budget, self.cfg["chunk"], len(r.prompt) - r.pos)
+            if r.last is None and budget > 0 and not decode_only and not r.waiting:
+                # a group leader stops one token short: the last prompt token is every member's first own row
+                end = len(r.prompt) - (1 if r.members else 0)
+                take = min(budget, self.cfg["chunk"], end - r.pos)
+                if take <= 0:
+                    continue
                 final = r.pos + take == len(r.prompt)
-                rows.append(rb.StepRow(r.rid, r.slot, r.prompt[r.pos : r.pos + take], r.pos, final, self.sampling))
+                rows.append(rb.StepRow(r.rid, r.slot, r.prompt[r.pos : r.pos + take], r.pos, final, self.sampling_of(r), adapter=self.adapter_of(r)))
                 kinds.append(r)
                 budget -= take
         return rows, kinds
+
+    def adapter_of(self, r):
+        return self.adapter_ids[r.adapter - 1] if r.adapter and self.adapter_ids else 0
+
+    def share_prompts(self):
+        """Group leaders whose prompt is resident but for its last token hand its blocks to their members."""
+        for r in self.live:
+            if r.members and r.pos == len(r.prompt) - 1:
+                for m in r.members:
+                    self.engine.seq_cp(r.slot, m.slot)
+                    m.pos, m.waiting = r.pos, False
+                r.members = None
 
     def step(self, prefill_only=False, decode_only=0):
         rows, reqs = self.compose(prefill_only, decode_only)
@@ -223,12 +330,13 @@ class Driver:
                 r.done += 1
                 r.times.append(stamp)
                 sampled += 1
+        self.share_prompts()
         finished = [] if decode_only else [r for r in self.live if r.done >= r.n_out]
         for r in finished:
             self.engine.seq_rm(r.slot)
             self.engine.request_free(r.rid)
             self.free_slots.append(r.slot)
-            self.reserved -= len(r.prompt) + r.n_out
+            self.reserved -= r.need
             self.live.remove(r)
         return dict(decode=n_decode, prefill=n_prefill, sampled=sampled, wall=wall, tokens=n_decode + n_prefill,
                     ctx_tokens=ctx_tokens, finished=finished, rows=rows)
@@ -412,6 +520,13 @@ def main():
     engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=cfg["n_ctx"], n_seq_max=cfg["n_requests"], n_batch=cfg["n_batch"], n_ubatch=cfg["n_batch"]))
     sampling = rb.SamplingParamsV2.greedy()
     driver = Driver(rb, engine, cfg, Workload(cfg, seed=1000 + rank), sampling)
+    if cfg.get("adapters"):
+        ad = cfg["adapters"]
+        for a in range(ad["n"]):
+            apath = path.parent / f"retrograd_b200_adapter_rank{rank}_{a}.gguf"
+            write_adapter(apath, cfg["spec"], ad["rank"], ad["alpha"], seed=7000 + a)
+            driver.adapter_ids.append(engine.adapter_load(str(apath)))
+            apath.unlink()
     expert_parallel = bool(cfg.get("ep")) and world > 1
     if expert_parallel:
         holder = [rb.nccl_unique_id() if rank == 0 else None]

@@ -447,6 +447,13 @@ int retro_b200_engine_last_step_stats(retro_engine * engine, float * out_ms, uin
 int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, uint32_t n_in, const float * x, uint32_t n_tokens, float * y,
                        int path, uint32_t iters, float * out_ms);
 
+/* The grouped MXFP4 expert GEMM (tcgen05) on host data: `banks` = n_expert matrices of n_out rows x n_in
+ * weights in 17-byte MXFP4 blocks, x = the offsets[n_expert] activation rows sorted by expert, offsets
+ * [n_expert + 1] each expert's first row; y[r][o] = sum_k deq(bank[expert(r)])[o][k] * x[r][k]. -3 when the
+ * operands are outside what the kernel covers (n_in % 64, block scales that are not f16 powers of two). */
+int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, uint32_t n_out, uint32_t n_in, const float * x,
+                                     const int32_t * offsets, float * y);
+
 /* No counterpart in the reference. The same exact Q4_K GEMM for callers that must not allocate
  * device memory (a host whose own pool owns the whole device budget, a loop that cannot take the
  * synchronisation an allocation may cause): d_w (Q4_K rows), d_x (f32 [n_tokens][n_in]) and d_y

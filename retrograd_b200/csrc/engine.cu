@@ -74,6 +74,8 @@ bool mxfp4_to_q8_0(const void * src, size_t bytes, std::vector<uint8_t> & out) {
 
 void Engine::load_model(const std::string & path) {
     if (const char * env = std::getenv("RB200_MOE")) moe_tensor_cores_ = std::string(env) != "rows";
+    if (const char * env = std::getenv("RB200_LORA")) lora_tensor_cores_ = std::string(env) != "rows";
+    if (const char * env = std::getenv("RB200_Q8_TC5")) q8_tc5_ = std::string(env) != "0";
     GgufFile file(path);
     model = std::make_unique<Model>();
     Model & m = *model;
@@ -112,9 +114,15 @@ void Engine::load_model(const std::string & path) {
         if (!t) throw std::runtime_error("failed to load model GGUF: missing tensor " + name);
         return *t;
     };
-    auto view_of = [&](const GgufTensor & t, const uint8_t * dev, uint64_t rows, bool min_fold) {
+    // the host-side check the matrix' tcgen05 kernel asks for (see WeightView::tc5_exact)
+    auto tc5_check = [&](const GgufTensor & t, uint64_t n_in) {
+        if (t.type == GGML_Q4_K) return n_in % 256 == 0 && q4k_min_fold_ok(t.data, t.n_bytes / 144);
+        if (t.type == GGML_Q8_0) return n_in % 64 == 0 && q8_0_products_fit_f16(t.data, t.n_bytes / 34);
+        return false;
+    };
+    auto view_of = [&](const GgufTensor & t, const uint8_t * dev, uint64_t rows, bool tc5_exact) {
         WeightView w;
-        w.min_fold = min_fold;
+        w.tc5_exact = tc5_exact;
         w.data = dev;
         w.type = t.type;
         w.n_in = (uint32_t)t.ne[0];
@@ -150,7 +158,7 @@ void Engine::load_model(const std::string & path) {
         const GgufTensor & t = need(name);
         if (t.ne.size() != 2 || t.ne[0] != n_in || t.ne[1] != n_out) throw std::runtime_error("failed to load model GGUF: unexpected shape of " + name);
         if (n_in % 8 != 0) throw std::runtime_error("failed to load model GGUF: row length of " + name + " is not a multiple of 8");
-        return view_of(t, upload(t.data, t.n_bytes), n_out, t.type == GGML_Q4_K && n_in % 256 == 0 && q4k_min_fold_ok(t.data, t.n_bytes / 144));
+        return view_of(t, upload(t.data, t.n_bytes), n_out, tc5_check(t, n_in));
     };
     auto vector_f32 = [&](const std::string & name, uint64_t n, bool optional) -> const float * {
         const GgufTensor * t = file.find(name);
@@ -176,24 +184,23 @@ void Engine::load_model(const std::string & path) {
         m.allocations.push_back(p);
         size_t off = 0;
         uint64_t rows = 0;
-        bool min_fold = type == GGML_Q4_K && n_in % 256 == 0;
+        bool tc5_exact = true;
         for (size_t i = 0; i < names.size(); ++i) {
             const GgufTensor & t = need(names[i]);
-            min_fold = min_fold && q4k_min_fold_ok(t.data, t.n_bytes / 144);
+            tc5_exact = tc5_exact && tc5_check(t, n_in);
             RB_CUDA(cudaMemcpy(static_cast<uint8_t *>(p) + off, t.data, t.n_bytes, cudaMemcpyHostToDevice));
             off += t.n_bytes;
             rows += n_out[i];
         }
         m.weight_bytes += total;
-        out = view_of(need(names[0]), static_cast<uint8_t *>(p), rows, min_fold);
+        out = view_of(need(names[0]), static_cast<uint8_t *>(p), rows, tc5_exact);
         return true;
     };
 
     const GgufTensor & embd = need("token_embd.weight");
     hp.vocab = (uint32_t)embd.ne[1];
     if (embd.ne[0] != hp.d) throw std::runtime_error("failed to load model GGUF: token_embd width differs from embedding_length");
-    m.token_embd = view_of(embd, upload(embd.data, embd.n_bytes), hp.vocab,
-                           embd.type == GGML_Q4_K && hp.d % 256 == 0 && q4k_min_fold_ok(embd.data, embd.n_bytes / 144));
+    m.token_embd = view_of(embd, upload(embd.data, embd.n_bytes), hp.vocab, tc5_check(embd, hp.d));
 
     const uint64_t dq = hp.dq(), dkv = hp.dkv();
     m.layers.resize(hp.n_layer);
@@ -582,7 +589,9 @@ bool Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
         if (need) ++last_launches;
     } else if (xs && T > mma_min_tokens && gemm_q4k_exact_supported(w, *xs)) {
         launch_gemm_q4k_exact(w, *xs, T, y, ldy, bias, residual, ldr, stream);
-    } else if (xs && T > mma_min_tokens && gemm_q8_0_exact_supported(w, *xs)) {
+    } else if (xs && T > mma_min_tokens && q8_tc5_ && gemm_q8_0_tc5_supported(w, *xs)) {
+        launch_gemm_q8_0_tc5(w, *xs, T, y, ldy, bias, residual, ldr, device_error_.ptr, n_sm_, stream);
+} else if (xs && T > mma_min_tokens && gemm_q8_0_exact_supported(w, *xs)) {
         launch_gemm_q8_0_exact(w, *xs, T, y, ldy, bias, residual, ldr, stream);
     } else {
         launch_gemm_rows(w, x, ldx, T, y, ldy, bias, residual, ldr, stream);
@@ -668,7 +677,7 @@ bool Engine::linear_reads_split(const WeightView & w, int ldx, int T, const Spli
         (gemm_q4k_stream_supported(w, *xs, std::min(T, 8)) || gemm_q8_0_stream_supported(w, *xs, std::min(T, 8))))
         return true;
     if ((T > tc5_min_tokens || tc5_split_preferred(w, T, xs)) && gemm_q4k_tc5_supported(w, *xs)) return true;
-    return T > mma_min_tokens && (gemm_q4k_exact_supported(w, *xs) || gemm_q8_0_exact_supported(w, *xs));
+    return T > mma_min_tokens && (gemm_q4k_exact_supported(w, *xs) || gemm_q8_0_exact_supported(w, *xs) || (q8_tc5_ && gemm_q8_0_tc5_supported(w, *xs)));
 }
 
 void Engine::lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy) {
@@ -677,6 +686,13 @@ void Engine::lora(const std::string & target, const float * x, int ldx, int T, f
     if (it == lora_targets_.end() || !it->second->present) return;
     LoraTarget & t = *it->second;
     prof_.begin(K_LORA, stream);
+    if (lora_tensor_cores_ && adapters_.size() <= 1024 && lora_tc_supported((int)r_max_, (int)t.n_in, t.a.ptr, x, ldx)) {
+        launch_lora_tc(t.a.ptr, t.b.ptr, lora_scales_.ptr, (int)r_max_, (int)t.n_in, (int)t.n_out, (int)adapters_.size(), lora_offsets_.ptr,
+                       lora_sorted_.ptr, x, ldx, T, lora_tmp_.ptr, y, ldy, stream);
+        prof_.end(K_LORA, 2, stream);
+        last_launches += 2;
+        return;
+    }
     if (t.n_in % 4 == 0 && ldx % 4 == 0 && adapters_.size() <= 1024)
         launch_lora_shrink_grouped(t.a.ptr, (int)r_max_, (int)t.n_in, (int)adapters_.size(), lora_offsets_.ptr, lora_sorted_.ptr, x, ldx, lora_tmp_.ptr,
                                    stream);
@@ -1212,7 +1228,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         if (n_greedy_fast) sample_scratch_.ensure(sample_scratch_bytes((int)hp.vocab, (int)S));
     }
     if (any_adapter) {
-        lora_tmp_.ensure(T * (size_t)std::max<uint32_t>(r_max_, 1));
+        lora_tmp_.ensure((size_t)kLoraTcMaxSplits * T * (size_t)std::max<uint32_t>(r_max_, 1));
         lora_offsets_.ensure(adapters_.size() + 1);
         lora_sorted_.ensure(T);
     }

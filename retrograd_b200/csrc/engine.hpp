@@ -351,6 +351,8 @@ private:
     int n_sm_ = 148;
     bool stream_gemm_ = true;
     bool moe_tensor_cores_ = true;      // RB200_MOE=rows: experts stay MXFP4 on the CUDA-core row kernel
+    bool q8_tc5_ = true;                // RB200_Q8_TC5=0: Q8_0 above 16 tokens stays on the mma.sync kernel
+    bool lora_tensor_cores_ = true;     // RB200_LORA=rows: the CUDA-core shrink / expand kernels instead
     DeviceBuffer<float> moe_xs_, moe_gu_s_, moe_y_s_;      // expert-contiguous rows: inputs, [gate | up], outputs
     SplitBuffer moe_x_split_, moe_h_split_;
     size_t moe_split_rows_ = 0;

@@ -414,7 +414,7 @@ bool split_act_encode_maps(SplitAct & s, size_t rows) {
 }
 
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x) {
-    return w.type == GGML_Q4_K && w.tiled && w.min_fold && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
+    return w.type == GGML_Q4_K && w.tiled && w.tc5_exact && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
 }
 
 bool q4k_min_fold_ok(const uint8_t * blocks, size_t n_blocks) {

@@ -165,6 +165,7 @@ __global__ void pack_fill_kernel(const RowDesc * __restrict__ rows, int n_rows, 
     RB_CHECK(maps.check, CHECK_SLOT, row.slot, maps.n_slots, return);
     RB_CHECK(maps.check, CHECK_ADAPTER, row.adapter + 1, maps.n_adapters + 1, return);      // -1 = none
     RB_CHECK(maps.check, CHECK_POSITION, pos, (long long)max_blocks * block_tokens, return);
+    maps.tok_slot[i] = row.slot;
     maps.tok_pos[i] = pos;
     maps.tok_row[i] = lo;
     maps.tok_adapter[i] = row.adapter;

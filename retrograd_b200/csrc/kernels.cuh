@@ -23,9 +23,10 @@ struct WeightView {
     // zero-padded to a multiple of 128 (read by the tcgen05 kernel and the weight-streaming kernel).
     // Q8_0, optional: the layout described at kQ8TileBytes, rows padded to a multiple of 16.
     const uint8_t * tiled = nullptr;
-    // Q4_K: every super-block lets the tcgen05 kernel fold the minimum term into the main accumulator
-    // (q4k_min_fold_ok over the matrix' blocks, checked on the host when the weights are uploaded).
-    bool min_fold = false;
+    // The matrix passed the host-side check its tcgen05 kernel needs, made once when the weights are uploaded.
+    // Q4_K: every super-block lets the kernel fold the minimum term into the main accumulator (q4k_min_fold_ok).
+    // Q8_0: every block scale keeps d * q inside the f16 range, so a weight is an exact f16 pair (q8_0_products_fit_f16).
+    bool tc5_exact = false;
 };
 
 // Tile-major copy of a Q4_K matrix: one 18432-byte tile per (128 rows, 256-column super-block), tiles
@@ -319,6 +320,13 @@ bool gemm_q8_0_stream_supported(const WeightView & w, const SplitAct & x, int n_
 void launch_gemm_q8_0_stream(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
                              const float * residual, int ldr, float * scratch, int n_sm, int * error_flag, cudaStream_t stream,
                              const FinishTail * tail = nullptr);
+// Q8_0 GEMM on tcgen05 for more than 16 tokens (weights as exact f16 pairs, three MMAs per product, one accumulator
+// over the whole row); reads the GGUF-layout rows. q8_0_products_fit_f16 is the host-side check behind
+// WeightView::tc5_exact for Q8_0 matrices. *error_flag is set to 1 if a bounded pipeline wait gave up.
+bool q8_0_products_fit_f16(const uint8_t * blocks, size_t n_blocks);
+bool gemm_q8_0_tc5_supported(const WeightView & w, const SplitAct & x);
+void launch_gemm_q8_0_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
+                          int ldr, int * error_flag, int n_sm, cudaStream_t stream);
 // Exact tensor-core Q8_0 GEMM (mma.sync) for more than 8 tokens; reads the GGUF-layout rows.
 bool gemm_q8_0_exact_supported(const WeightView & w, const SplitAct & x);
 void launch_gemm_q8_0_exact(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias,
@@ -392,6 +400,16 @@ void launch_lora_shrink_grouped(const float * a_stack, int r_max, int n_in, int 
                                 const float * x, int ldx, float * tmp, cudaStream_t stream);
 void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float * scales, const int32_t * tok_adapter, const float * tmp,
                         int n_tokens, float * y, int ldy, cudaStream_t stream);
+
+// Segmented LoRA on the tensor cores (TF32 MMAs on split operands, F32-accurate): shrink over K splits into
+// tmp[split][t][r] (tmp holds kLoraTcMaxSplits * n_tokens * r_max floats), then expand into y. Tokens grouped by
+// adapter as for launch_lora_shrink_grouped.
+constexpr int kLoraTcMaxSplits = 8;
+int lora_tc_splits(int n_in);
+bool lora_tc_supported(int r_max, int n_in, const float * a_stack, const float * x, int ldx);
+void launch_lora_tc(const float * a_stack, const float * b_stack, const float * scales, int r_max, int n_in, int n_out, int n_adapters,
+                    const int32_t * offsets, const int32_t * sorted, const float * x, int ldx, int n_tokens, float * tmp, float * y, int ldy,
+                    cudaStream_t stream);
 
 // Sampling over logits rows [S][n_vocab]. v2 rows transform their row of `work_logits`, which must
 // then hold a copy of `raw_logits`; with v1 rows only, `work_logits` may be null.

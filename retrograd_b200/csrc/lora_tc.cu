@@ -1,0 +1,220 @@
+// Segmented multi-adapter LoRA on the tensor cores: y[t] += scale[a(t)] * B[a(t)] (A[a(t)] x[t]) for the
+// tokens of a step whose rows name different adapters (reference: per-row adapters of the batched step,
+// crates/retrograd-ffi/runtime/src/retro_gen_core.cpp:2539-2564, 2987-3006).
+//
+// The step's tokens are grouped by adapter once (offsets / sorted, built by the grouping kernel); a
+// segment is cut into tiles of 16 tokens, and each tile is one m16n8k8 TF32 MMA row block:
+//   shrink: tile [16 tokens x n_in] times A[a]^T [n_in x r]      -> tmp[split][t][r]   (K split over grid.y)
+//   expand: tile [16 tokens x r]    times B[a]^T [r x n_out]     -> y[t][o] += scale[a] * ...
+// Both operands are F32 in memory. Every value is split v = big + small with both parts TF32, and a product
+// is accumulated as big*small + small*big + big*big in F32, which keeps the result within a few units of
+// 2^-22 of the F32 product the CPU path computes; the K order inside an MMA is free, so a thread's four
+// consecutive columns (one 16-byte load) feed two MMAs directly.
+//
+// The partial results of the K splits are summed by the expand kernel in split order, and a token's row
+// is produced by exactly one tile: results do not depend on which other rows share the step.
+#include "kernels.cuh"
+
+namespace rb200 {
+
+namespace {
+
+__device__ __forceinline__ void split_tf32(float v, uint32_t & big, uint32_t & small) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(big) : "f"(v));
+    const float rest = v - __uint_as_float(big);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(small) : "f"(rest));
+}
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// three TF32 MMAs for one F32-accurate 16 x 8 x 8 product: the small cross terms first
+__device__ __forceinline__ void mma_3x(float (&c)[4], const uint32_t (&ab)[4], const uint32_t (&as)[4], uint32_t bb0, uint32_t bb1, uint32_t bs0,
+                                       uint32_t bs1) {
+    mma_tf32(c, ab[0], ab[1], ab[2], ab[3], bs0, bs1);
+    mma_tf32(c, as[0], as[1], as[2], as[3], bb0, bb1);
+    mma_tf32(c, ab[0], ab[1], ab[2], ab[3], bb0, bb1);
+}
+
+// The (adapter, 16-token tile) a CTA owns: tiles are numbered segment by segment. False past the last tile.
+__device__ __forceinline__ bool find_tile(int tile, int n_adapters, const int32_t * __restrict__ offsets, int & adapter, int & first, int & end) {
+    for (int a = 0; a < n_adapters; ++a) {
+        const int b = offsets[a], e = offsets[a + 1];
+        const int n = (e - b + 15) >> 4;
+        if (tile < n) {
+            adapter = a;
+            first = b + tile * 16;
+            end = e;
+            return true;
+        }
+        tile -= n;
+    }
+    return false;
+}
+
+// grid (tile bound, K splits), 4 warps: the warps take the CTA's columns in interleaved chunks of 16 and their
+// 16 x (8 NR) partial results are added in warp order through shared memory.
+template <int NR>
+__global__ void __launch_bounds__(128) lora_shrink_tc_kernel(const float * __restrict__ a_stack, int r_max, int n_in, int n_adapters,
+                                                             const int32_t * __restrict__ offsets, const int32_t * __restrict__ sorted,
+                                                             const float * __restrict__ x, int ldx, float * __restrict__ tmp, int n_tokens,
+                                                             int k_per_split) {
+    __shared__ float red[4][16][NR * 8 + 1];
+    int adapter, first, end;
+    if (!find_tile(blockIdx.x, n_adapters, offsets, adapter, first, end)) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int tok0 = first + g < end ? sorted[first + g] : -1, tok1 = first + g + 8 < end ? sorted[first + g + 8] : -1;
+    const float * x0 = x + (size_t)max(tok0, 0) * ldx + 4 * t;
+    const float * x1 = x + (size_t)max(tok1, 0) * ldx + 4 * t;
+    const float * ar = a_stack + ((size_t)adapter * r_max + g) * n_in + 4 * t;
+    const int k0 = blockIdx.y * k_per_split, k1 = min(n_in, k0 + k_per_split);
+    float acc[NR][4];
+#pragma unroll
+    for (int j = 0; j < NR; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+    for (int k = k0 + warp * 16; k < k1; k += 64) {
+        const float4 v0 = tok0 >= 0 ? *reinterpret_cast<const float4 *>(x0 + k) : zero;
+        const float4 v1 = tok1 >= 0 ? *reinterpret_cast<const float4 *>(x1 + k) : zero;
+        float4 av[NR];
+#pragma unroll
+        for (int j = 0; j < NR; ++j) av[j] = j * 8 + g < r_max ? *reinterpret_cast<const float4 *>(ar + (size_t)j * 8 * n_in + k) : zero;
+        uint32_t pb[4], ps[4], qb[4], qs[4];      // the chunk's columns 4t, 4t+1 (first MMA) and 4t+2, 4t+3 (second)
+        split_tf32(v0.x, pb[0], ps[0]);
+        split_tf32(v1.x, pb[1], ps[1]);
+        split_tf32(v0.y, pb[2], ps[2]);
+        split_tf32(v1.y, pb[3], ps[3]);
+        split_tf32(v0.z, qb[0], qs[0]);
+        split_tf32(v1.z, qb[1], qs[1]);
+        split_tf32(v0.w, qb[2], qs[2]);
+        split_tf32(v1.w, qb[3], qs[3]);
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+            uint32_t b0, s0, b1, s1;
+            split_tf32(av[j].x, b0, s0);
+            split_tf32(av[j].y, b1, s1);
+            mma_3x(acc[j], pb, ps, b0, b1, s0, s1);
+            split_tf32(av[j].z, b0, s0);
+            split_tf32(av[j].w, b1, s1);
+            mma_3x(acc[j], qb, qs, b0, b1, s0, s1);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        red[warp][g][j * 8 + 2 * t] = acc[j][0];
+        red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+        red[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+        red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+    }
+    __syncthreads();
+    float * out = tmp + (size_t)blockIdx.y * n_tokens * r_max;
+    for (int i = threadIdx.x; i < 16 * NR * 8; i += 128) {
+        const int row = i / (NR * 8), col = i % (NR * 8);
+        if (first + row >= end || col >= r_max) continue;
+        const float v = ((red[0][row][col] + red[1][row][col]) + red[2][row][col]) + red[3][row][col];
+        out[(size_t)sorted[first + row] * r_max + col] = v;
+    }
+}
+
+// grid (tile bound, column groups), 4 warps: a warp walks its group's columns eight at a time.
+template <int NR>
+__global__ void __launch_bounds__(128) lora_expand_tc_kernel(const float * __restrict__ b_stack, int r_max, int n_out, const float * __restrict__ scales,
+                                                             int n_adapters, const int32_t * __restrict__ offsets, const int32_t * __restrict__ sorted,
+                                                             const float * __restrict__ tmp, int n_splits, int n_tokens, float * __restrict__ y, int ldy,
+                                                             int cols_per_cta, int vec2) {
+    int adapter, first, end;
+    if (!find_tile(blockIdx.x, n_adapters, offsets, adapter, first, end)) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int tok0 = first + g < end ? sorted[first + g] : -1, tok1 = first + g + 8 < end ? sorted[first + g + 8] : -1;
+    // the tile's shrink results (K splits added in split order) as the A operand, split once
+    uint32_t ab[NR][4], as[NR][4];
+#pragma unroll
+    for (int kk = 0; kk < NR; ++kk) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int tok = (e & 1) ? tok1 : tok0, r = kk * 8 + t + ((e & 2) ? 4 : 0);
+            float v = 0.f;
+            if (tok >= 0 && r < r_max)
+                for (int s = 0; s < n_splits; ++s) v += tmp[((size_t)s * n_tokens + tok) * r_max + r];
+            split_tf32(v, ab[kk][e], as[kk][e]);
+        }
+    }
+    const float scale = scales[adapter];
+    const float * br = b_stack + (size_t)adapter * n_out * r_max;
+    const int o_end = min(n_out, ((int)blockIdx.y + 1) * cols_per_cta);
+    for (int o0 = blockIdx.y * cols_per_cta + warp * 8; o0 < o_end; o0 += 32) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        const bool row_ok = o0 + g < n_out;
+        const float * bo = br + (size_t)(o0 + g) * r_max;
+#pragma unroll
+        for (int kk = 0; kk < NR; ++kk) {
+            const int r0 = kk * 8 + t, r1 = r0 + 4;
+            uint32_t b0, s0, b1, s1;
+            split_tf32(row_ok && r0 < r_max ? bo[r0] : 0.f, b0, s0);
+            split_tf32(row_ok && r1 < r_max ? bo[r1] : 0.f, b1, s1);
+            mma_3x(c, ab[kk], as[kk], b0, b1, s0, s1);
+        }
+        const int col = o0 + 2 * t;
+        if (vec2 && col + 1 < n_out) {
+            if (tok0 >= 0) {
+                float2 * p = reinterpret_cast<float2 *>(y + (size_t)tok0 * ldy + col);
+                float2 v = *p;
+                v.x += scale * c[0];
+                v.y += scale * c[1];
+                *p = v;
+            }
+            if (tok1 >= 0) {
+                float2 * p = reinterpret_cast<float2 *>(y + (size_t)tok1 * ldy + col);
+                float2 v = *p;
+                v.x += scale * c[2];
+                v.y += scale * c[3];
+                *p = v;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int tok = e < 2 ? tok0 : tok1, cc = col + (e & 1);
+                if (tok >= 0 && cc < n_out) y[(size_t)tok * ldy + cc] += scale * c[e];
+            }
+        }
+    }
+}
+
+template <class F> void dispatch_rank_tiles(int r_max, F && f) {
+    const int tiles = (r_max + 7) / 8;
+    if (tiles <= 1) f(std::integral_constant<int, 1>{});
+    else if (tiles <= 2) f(std::integral_constant<int, 2>{});
+    else if (tiles <= 4) f(std::integral_constant<int, 4>{});
+    else f(std::integral_constant<int, 8>{});
+}
+
+} // namespace
+
+int lora_tc_splits(int n_in) { return std::max(1, std::min(kLoraTcMaxSplits, n_in / 2048)); }
+
+bool lora_tc_supported(int r_max, int n_in, const float * a_stack, const float * x, int ldx) {
+    return r_max >= 1 && r_max <= 64 && n_in % 16 == 0 && ldx % 4 == 0 && (uintptr_t)a_stack % 16 == 0 && (uintptr_t)x % 16 == 0;
+}
+
+void launch_lora_tc(const float * a_stack, const float * b_stack, const float * scales, int r_max, int n_in, int n_out, int n_adapters,
+                    const int32_t * offsets, const int32_t * sorted, const float * x, int ldx, int n_tokens, float * tmp, float * y, int ldy,
+                    cudaStream_t stream) {
+    if (n_tokens <= 0 || n_adapters <= 0) return;
+    const int tiles = (n_tokens + 15) / 16 + n_adapters;          // every segment may end in a partial tile
+    const int splits = lora_tc_splits(n_in);
+    const int k_per_split = ((n_in + splits - 1) / splits + 63) / 64 * 64;
+    const int cols_per_cta = 512;
+    const int vec2 = ldy % 2 == 0 && (uintptr_t)y % 8 == 0 ? 1 : 0;
+    dispatch_rank_tiles(r_max, [&](auto tag) {
+        constexpr int NR = decltype(tag)::value;
+        lora_shrink_tc_kernel<NR><<<dim3(tiles, splits), 128, 0, stream>>>(a_stack, r_max, n_in, n_adapters, offsets, sorted, x, ldx, tmp, n_tokens,
+                                                                         k_per_split);
+        lora_expand_tc_kernel<NR><<<dim3(tiles, (n_out + cols_per_cta - 1) / cols_per_cta), 128, 0, stream>>>(
+            b_stack, r_max, n_out, scales, n_adapters, offsets, sorted, tmp, splits, n_tokens, y, ldy, cols_per_cta, vec2);
+    });
+}
+
+} // namespace rb200

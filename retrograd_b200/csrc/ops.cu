@@ -47,13 +47,14 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             dtiled.ensure(q4k_tiled_bytes(n_out, n_in));
             launch_q4k_retile(dw.ptr, n_out, n_in, (uint32_t)rb, dtiled.ptr, stream);
             wv.tiled = dtiled.ptr;
-            wv.min_fold = q4k_min_fold_ok(w, (size_t)n_out * (n_in / 256));
+            wv.tc5_exact = q4k_min_fold_ok(w, (size_t)n_out * (n_in / 256));
         }
         if (ggml_type == GGML_Q8_0 && n_in % 256 == 0 && path == 5) {
             dtiled.ensure(q8_0_tiled_bytes(n_out, n_in));
             launch_q8_0_retile(dw.ptr, n_out, n_in, (uint32_t)rb, dtiled.ptr, stream);
             wv.tiled = dtiled.ptr;
         }
+        if (ggml_type == GGML_Q8_0 && n_in % 64 == 0) wv.tc5_exact = q8_0_products_fit_f16(w, (size_t)n_out * (n_in / 32));
         const bool have_split = xs.get() != nullptr;
         if (have_split) launch_split_prep(dx.ptr, (int)n_in, (int)n_in, (int)n_tokens, xs.view, stream);
         int chosen = path;
@@ -77,11 +78,11 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
             }
             stream_scratch.ensure(gemm_q4k_stream_scratch_floats(n_out, n_in));
         }
-        if (chosen == 4) {
+        if (chosen == 4 && ggml_type == GGML_Q4_K) {
             const size_t need = gemm_q4k_tc5_scratch_floats(wv.n_out, wv.n_in, (int)n_tokens, n_sm);
             if (need) tc5_scratch.ensure(need);
         }
-        if (chosen == 4 && !(have_split && gemm_q4k_tc5_supported(wv, xs.view))) {
+        if (chosen == 4 && !(have_split && (gemm_q4k_tc5_supported(wv, xs.view) || gemm_q8_0_tc5_supported(wv, xs.view)))) {
             cudaStreamDestroy(stream);
             set_error("op_gemm: the requested kernel does not cover this type or shape");
             return STATUS_INVALID_ARGUMENT;
@@ -94,6 +95,7 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         auto run = [&]() {
             if (chosen == 5 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
             else if (chosen == 5) launch_gemm_q4k_stream(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream_scratch.ptr, n_sm, flag.ptr, stream);
+            else if (chosen == 4 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, n_sm, stream);
             else if (chosen == 4) launch_gemm_q4k_tc5(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, flag.ptr, tc5_scratch.ptr, tc5_scratch.count, n_sm, stream);
             else if (chosen == 3 && ggml_type == GGML_Q8_0) launch_gemm_q8_0_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
             else if (chosen == 3) launch_gemm_q4k_exact(wv, xs.view, (int)n_tokens, dy.ptr, (int)n_out, nullptr, nullptr, 0, stream);
@@ -146,6 +148,71 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
         cudaEventDestroy(e0);
         cudaEventDestroy(e1);
         cudaStreamDestroy(stream);
+        return STATUS_OK;
+    });
+}
+
+// The grouped MXFP4 expert GEMM on tcgen05: `banks` holds n_expert matrices of n_out rows x n_in MXFP4 weights
+// (17-byte blocks, rows consecutive), x the n_rows = offsets[n_expert] activation rows sorted by expert, offsets
+// each expert's first row. y[r][o] = sum_k deq(bank[e(r)])[o][k] x[r][k].
+int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, uint32_t n_out, uint32_t n_in, const float * x,
+                                     const int32_t * offsets, float * y) {
+    return boundary([&]() -> int {
+        if (!banks || !x || !y || !offsets || n_expert == 0 || n_out == 0 || n_in == 0 || n_in % 64 != 0) {
+            set_error("op_gemm_mxfp4_grouped: bad arguments");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        const int n_rows = offsets[n_expert];
+        const size_t bank_bytes = (size_t)n_expert * n_out * (n_in / 32) * 17;
+        if (n_rows <= 0 || !tensor_maps_available() || !mxfp4_scales_are_f16(banks, bank_bytes / 17)) {
+            set_error("op_gemm_mxfp4_grouped: the kernel does not cover these operands");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        int max_rows = 0;
+        for (uint32_t e = 0; e < n_expert; ++e) max_rows = std::max(max_rows, offsets[e + 1] - offsets[e]);
+        DeviceBuffer<uint8_t> d_bank, d_tiled;
+        DeviceBuffer<float> dx, dy;
+        DeviceBuffer<int32_t> d_off;
+        DeviceBuffer<int> flag;
+        SplitBuffer xs;
+        d_bank.ensure(bank_bytes);
+        d_tiled.ensure(mxfp4_tiled_bytes(n_expert, n_out, n_in));
+        dx.ensure((size_t)n_rows * n_in);
+        dy.ensure((size_t)n_rows * n_out);
+        d_off.ensure(n_expert + 1);
+        flag.ensure(1);
+        xs.ensure((size_t)n_rows, n_in);
+        cudaStream_t stream;
+        RB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+        RB_CUDA(cudaMemcpyAsync(d_bank.ptr, banks, bank_bytes, cudaMemcpyHostToDevice, stream));
+        RB_CUDA(cudaMemcpyAsync(dx.ptr, x, (size_t)n_rows * n_in * 4, cudaMemcpyHostToDevice, stream));
+        RB_CUDA(cudaMemcpyAsync(d_off.ptr, offsets, (n_expert + 1) * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+        RB_CUDA(cudaMemsetAsync(flag.ptr, 0, sizeof(int), stream));
+        RB_CUDA(cudaMemsetAsync(dy.ptr, 0, (size_t)n_rows * n_out * 4, stream));
+        launch_mxfp4_retile(d_bank.ptr, n_expert, n_out, n_in, d_tiled.ptr, stream);
+        launch_split_prep(dx.ptr, (int)n_in, (int)n_in, n_rows, xs.view, stream);
+        WeightView wv;
+        wv.type = GGML_MXFP4;
+        wv.n_in = n_in;
+        wv.n_out = n_out;
+        wv.row_bytes = (n_in / 32) * 17;
+        wv.tiled = d_tiled.ptr;
+        if (!gemm_mxfp4_tc5_supported(wv, xs.view)) {
+            cudaStreamDestroy(stream);
+            set_error("op_gemm_mxfp4_grouped: the kernel does not cover these operands");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        launch_gemm_mxfp4_tc5_grouped(wv, (int)n_expert, d_off.ptr, xs.view, max_rows, dy.ptr, (int)n_out, flag.ptr, stream);
+        int h_flag = 0;
+        RB_CUDA(cudaMemcpyAsync(y, dy.ptr, (size_t)n_rows * n_out * 4, cudaMemcpyDeviceToHost, stream));
+        RB_CUDA(cudaMemcpyAsync(&h_flag, flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream));
+        RB_CUDA(cudaStreamSynchronize(stream));
+        RB_CUDA(cudaGetLastError());
+        cudaStreamDestroy(stream);
+        if (h_flag) {
+            set_error("op_gemm_mxfp4_grouped: a pipeline wait inside the tensor-core kernel timed out");
+            return STATUS_RUNTIME;
+        }
         return STATUS_OK;
     });
 }

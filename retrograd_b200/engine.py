@@ -243,6 +243,19 @@ def op_gemm(ggml_type: int, w_bytes, n_out: int, n_in: int, x, path: int = 0, it
     return y, ms.value
 
 
+def op_gemm_mxfp4_grouped(banks, n_expert: int, n_out: int, n_in: int, x, offsets):
+    """The grouped MXFP4 expert GEMM through retro_b200_op_gemm_mxfp4_grouped. Returns y [n_rows, n_out]."""
+    lib = _ffi.load_library()
+    w = np.ascontiguousarray(np.frombuffer(banks, dtype=np.uint8) if not isinstance(banks, np.ndarray) else banks)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, n_in)
+    off = np.ascontiguousarray(offsets, dtype=np.int32)
+    assert off.shape == (n_expert + 1,) and off[-1] == x.shape[0]
+    y = np.zeros((x.shape[0], n_out), dtype=np.float32)
+    _check(lib.retro_b200_op_gemm_mxfp4_grouped(w.ctypes.data_as(C.POINTER(C.c_uint8)), n_expert, n_out, n_in, x.ctypes.data_as(C.POINTER(C.c_float)),
+                                                off.ctypes.data_as(C.POINTER(C.c_int32)), y.ctypes.data_as(C.POINTER(C.c_float))))
+    return y
+
+
 def recode_mxfp4_as_q8_0(blocks: bytes) -> bytes | None:
     """MXFP4 blocks (17 B each) as Q8_0 blocks (34 B each) of the same values, as the engine does with expert
     banks at load; None when a block's scale is outside what an f16 holds. Host arithmetic only."""

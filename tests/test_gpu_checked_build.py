@@ -64,7 +64,7 @@ def _child() -> None:
     # the context is still usable: the other sequences continue and still follow the oracle
     engine.seq_rm(5)
     octx.seq_rm(5, -1, -1)
-    rows = [rb.StepRow.decode(i, i, out_tok, len(prompts[i]) + 6, greedy) for i, out_tok in enumerate([r.tokens[0] for r in rows][:5])]
+    rows = rows[:5]                      # the decode rows the loop above composed last and has not run yet
     toks = check_step(rb, engine, octx, O, rows, out, rep)
     expect_greedy(O, toks, rep)
     assert lib.retro_b200_engine_check_word(engine._h, word) == 0 and list(word) == [0, 0, 0, 0]

@@ -79,3 +79,36 @@ def test_mixed_adapter_rows_match_the_oracle_and_each_adapter_alone(rb, oracle, 
     engine.step([rb.StepRow(31, 7, [5, 6], 0, sample=True, sampling=g, adapter=idb)], out)
     assert engine.adapter_rows_info()["n_adapters"] == 1
     engine.close()
+
+
+def test_tensor_core_and_cuda_core_lora_kernels_agree(rb, models, tmp_path, monkeypatch):
+    """The segmented TF32 kernels (split operands, three MMAs per product) against the F32 CUDA-core kernels
+    (RB200_LORA=rows) on the same mixed step: ranks 8, 16 and 24 (three rank tiles with padding), segments that
+    end in partial 16-token tiles, base rows in between. Logits within 2e-5, the same greedy tokens."""
+    model = models("lora_base", **SPEC)
+    paths = []
+    for i, rank in enumerate((8, 16, 24)):
+        paths.append(tmp_path / f"r{rank}.gguf")
+        _write_adapter(paths[-1], rank=rank, alpha=32, seed=10 + i)
+    g = rb.SamplingParamsV2.greedy()
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(3, 512, n).tolist() for n in (37, 5, 18, 16, 1, 33, 9)]
+    which = [0, 1, None, 2, 1, 0, 2]
+    results = []
+    for form in ("tensor_cores", "rows"):
+        if form == "rows":
+            monkeypatch.setenv("RB200_LORA", "rows")
+        else:
+            monkeypatch.delenv("RB200_LORA", raising=False)
+        engine = rb.Engine(str(model), rb.EngineConfig(n_ctx=1024, n_seq_max=8, n_batch=128, n_ubatch=128))
+        ids = [engine.adapter_load(str(p)) for p in paths]
+        out = rb.StepOutput()
+        rows = [rb.StepRow(i, i, p, 0, sample=True, sampling=g, adapter=rb.ADAPTER_BASE if a is None else ids[a])
+                for i, (p, a) in enumerate(zip(prompts, which))]
+        engine.step(rows, out)
+        results.append(([out.row(i).token for i in range(len(rows))], np.stack([engine.last_logits(i) for i in range(len(rows))])))
+        engine.close()
+    assert results[0][0] == results[1][0]
+    diff = np.abs(results[0][1] - results[1][1]).max()
+    print(f"lora tensor-core vs CUDA-core kernels: max|dlogit|={diff:.3e}")
+    assert diff < 2e-5

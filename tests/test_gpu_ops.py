@@ -94,3 +94,51 @@ def test_q8_0_tensor_core_gemm_against_float64(rb, oracle, n_out, n_in, T):
     err = float(np.abs(got - want).max()) / float(np.abs(want).max())
     print(f"q8_0 mma {n_out}x{n_in} T={T}: rel err {err:.2e}")
     assert err < 4e-6
+
+
+@pytest.mark.parametrize("n_out,n_in,T", [(256, 512, 17), (384, 1024, 64), (200, 768, 65), (512, 2048, 130), (130, 192, 70), (256, 4096, 300),
+                                          (38016, 256, 600)])
+def test_q8_0_tcgen05_gemm_against_float64(rb, oracle, n_out, n_in, T):
+    """The Q8_0 tcgen05 kernel: weights as exact f16 pairs, three MMAs per product, one accumulator over the row.
+    Tiles of at most 64 tokens (N = 64 MMAs), ragged row and token counts, a reduction of three stages only, and a
+    shape with enough row tiles for the 256-token tile form. One matrix carries tiny and large block scales
+    (subnormal f16 products, and products near the top of the f16 range)."""
+    rng = np.random.default_rng(19 * n_out + T)
+    w = rng.normal(0, 0.02, (n_out, n_in)).astype(np.float32)
+    if n_out == 384:
+        w[::3] *= 1e-4          # block scales down to ~1e-8: w_hi and w_lo are f16 subnormals
+        w[1::3] *= 1e5          # block scales up to ~100: |d q| up to ~1e4
+    raw = np.frombuffer(b"".join(rb.quantize_row(8, w[r]) for r in range(n_out)), dtype=np.uint8)
+    x = rng.normal(0, 1.5, (T, n_in)).astype(np.float32)
+    wd = oracle.dequantize_row(oracle.T_Q8_0, raw, n_out * n_in).reshape(n_out, n_in).astype(np.float64)
+    want = x.astype(np.float64) @ wd.T
+    got, _ = rb.op_gemm(8, raw, n_out, n_in, x, path=4)
+    # row-wise yardstick: rows of very different scales share the matrix
+    scale = np.abs(wd).max(axis=1) * np.abs(x).max() * np.sqrt(n_in) + 1e-30
+    err = float((np.abs(got - want) / scale[None, :]).max())
+    print(f"q8_0 tcgen05 {n_out}x{n_in} T={T}: scaled err {err:.2e}")
+    assert err < 4e-6
+    again, _ = rb.op_gemm(8, raw, n_out, n_in, x, path=4)
+    assert np.array_equal(got, again)
+
+
+@pytest.mark.parametrize("n_expert,n_out,n_in,counts", [(4, 256, 128, (5, 0, 130, 40)), (3, 200, 576, (128, 1, 257)), (8, 2880, 2880, (70, 3, 0, 129, 12, 64, 300, 9))])
+def test_mxfp4_grouped_tcgen05_gemm_against_float64(rb, oracle, n_expert, n_out, n_in, counts):
+    """The grouped MXFP4 expert GEMM: empty experts, experts of more than one token tile, a ragged last row tile,
+    the 20B-class MoE's own widths. Against the exact product of the decoded weights."""
+    rng = np.random.default_rng(23 * n_out + n_in)
+    w = rng.normal(0, 0.02, (n_expert * n_out, n_in)).astype(np.float32)
+    raw = np.frombuffer(b"".join(rb.quantize_row(39, w[r]) for r in range(n_expert * n_out)), dtype=np.uint8)
+    wd = oracle.dequantize_row(oracle.T_MXFP4, raw, n_expert * n_out * n_in).reshape(n_expert, n_out, n_in).astype(np.float64)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    x = rng.normal(0, 1.5, (int(offsets[-1]), n_in)).astype(np.float32)
+    got = rb.op_gemm_mxfp4_grouped(raw, n_expert, n_out, n_in, x, offsets)
+    worst = 0.0
+    for e in range(n_expert):
+        rows = slice(int(offsets[e]), int(offsets[e + 1]))
+        if rows.start == rows.stop:
+            continue
+        want = x[rows].astype(np.float64) @ wd[e].T
+        worst = max(worst, float(np.abs(got[rows] - want).max()) / float(np.abs(want).max()))
+    print(f"mxfp4 grouped tcgen05 {n_expert}x{n_out}x{n_in} rows={counts}: rel err {worst:.2e}")
+    assert worst < 4e-6

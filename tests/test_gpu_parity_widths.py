@@ -183,10 +183,10 @@ def test_moe_20b_widths_mxfp4(rb, oracle, models, monkeypatch, experts):
     spec = dict(arch="olmoe", layers=2, d=2880, heads=64, kv_heads=8, head_dim=64, ff=2880, vocab=201088, experts=32, experts_used=4,
                 dtype="q8_0", expert_dtype="mxfp4", seed=5)
     path = models("moe_wide", **spec)
-    engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=8192, n_seq_max=24, n_batch=512, n_ubatch=512))
+    engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=8192, n_seq_max=24, n_batch=1024, n_ubatch=1024))
     om = oracle.Model(str(path), fast=True)
     octx = oracle.Context(om, 24, 1024)
-    out = rb.StepOutput(512, 0)
+    out = rb.StepOutput(1024, 0)
     rep = ParityReport()
     rng = np.random.default_rng(45)
     greedy = rb.SamplingParamsV2.greedy()
@@ -198,7 +198,7 @@ def test_moe_20b_widths_mxfp4(rb, oracle, models, monkeypatch, experts):
         T = sum(len(r.tokens) for r in rows)
         got = engine.last_routes().reshape(om.n_layer, T, 4)
         want = octx.last_routes().reshape(om.n_layer, T, 4)
-        assert np.array_equal(got, want)
+        assert np.array_equal(got, want), f"{int((got != want).sum())} of {got.size} routed expert ids differ (max|dlogit| so far {rep.max_logit_diff:.3e})"
         rows = [rb.StepRow.decode(i, i, out.row(i).token, len(prompts[i]) + step, greedy) for i in range(len(prompts))]
     assert len(np.unique(got)) > 8
     _summary(f"20B-MoE widths MXFP4 ({experts})", rep)
