@@ -128,6 +128,7 @@ typedef struct retro_engine_memory_info {
 /* ---- engine handle (retro_lora_train.h:2465-2509) ---- */
 
 typedef struct retro_engine retro_engine;
+typedef struct retro_trainer retro_trainer;   /* the trainer handle of the trainer-owned generation context (below) */
 
 enum retro_engine_kv_dtype {
     RETRO_ENGINE_KV_DTYPE_F32 = 0,
@@ -173,6 +174,30 @@ void retro_engine_free(retro_engine * engine);
 int retro_engine_eos_token(retro_engine * engine, int32_t * out_token);
 int retro_engine_vocab_size(retro_engine * engine, uint32_t * out_n_vocab);
 int retro_engine_is_eog_token(retro_engine * engine, int32_t token, bool * out_is_eog);
+
+/* Reasoning budget (reference: retro_engine_set_reasoning_budget, retro_lora_train.h:2622-2627, and the trainer's
+ * retro_trainer_set_reasoning_budget, :1680-1688): -1 lets the model decide, N >= 0 forces the reasoning block's
+ * end tag after N reasoning tokens; rows report forced tokens in `forced`. Each request carries its own machine,
+ * primed from the end of its prompt (retro_gen_core.cpp:890-1007, 2609-2680). The reference reads the tags out of
+ * the model's chat template; this library renders no templates: the caller's template layer passes them as token
+ * ids with retro_b200_engine_set_reasoning_tags first, and a budget >= 0 without tags fails with the reference's
+ * message for a template that declares no reasoning block. -1 on refusal, with the error set. */
+int retro_engine_set_reasoning_budget(retro_engine * engine, int32_t budget);
+int retro_trainer_set_reasoning_budget(retro_trainer * trainer, int32_t budget);
+/* No counterpart in the reference (there the tags come from common_chat_templates_apply,
+ * retro_chat_parser.cpp:558-640): the opening tag, the closing tags (the first one is the tag a spent budget
+ * forces) and the number of prompt tokens at the end of a prompt that are replayed into a fresh machine (the
+ * length of the template's generation prompt). */
+int retro_b200_engine_set_reasoning_tags(retro_engine * engine, const int32_t * start, size_t n_start, const int32_t * const * end_tags,
+                                         const size_t * n_end, size_t n_end_tags, size_t n_prompt_tail);
+int retro_b200_trainer_set_reasoning_tags(retro_trainer * trainer, const int32_t * start, size_t n_start, const int32_t * const * end_tags,
+                                          const size_t * n_end, size_t n_end_tags, size_t n_prompt_tail);
+/* Host logic only (no GPU): one request's budget machine, primed with the end of `prompt` and then fed the tokens
+ * a sampler drew; out_tokens[i] is what the step would emit in place of sampled[i], out_forced[i] whether the
+ * budget forced it. `incomplete` lists token ids whose text stops inside a UTF-8 sequence. */
+int retro_b200_reasoning_check(const int32_t * start, size_t n_start, const int32_t * const * end_tags, const size_t * n_end, size_t n_end_tags,
+                               int32_t budget, size_t n_prompt_tail, const int32_t * prompt, size_t n_prompt, const int32_t * incomplete,
+                               size_t n_incomplete, const int32_t * sampled, size_t n_sampled, int32_t * out_tokens, uint8_t * out_forced);
 int retro_engine_context_size(retro_engine * engine, uint32_t * out_n_ctx);
 int retro_engine_detokenize(retro_engine * engine, const int32_t * tokens, size_t n_tokens, bool unparse_special,
                             char * buffer, size_t n_buffer, size_t * out_n_bytes);

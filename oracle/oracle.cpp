@@ -406,6 +406,7 @@ struct Ctx {
     std::vector<SlotKV> slots;
     // filled by the last step when the model is MoE: [layer][token][k] expert ids
     std::vector<int32_t> last_routes;
+    std::vector<float> last_route_margins;      // per (layer, token): the smallest probability gap that decided the selection or its order
 };
 
 const float * vec_f32(const Model & m, const std::string & name) {
@@ -508,6 +509,7 @@ void forward(Ctx & c, size_t n_rows, const int32_t * slot, const uint32_t * n, c
     }
     const bool moe = m.n_expert > 0;
     if (moe) c.last_routes.assign((size_t)m.n_layer * T * m.n_expert_used, -1);
+    if (moe) c.last_route_margins.assign((size_t)m.n_layer * T, 0.f);
     const float att_scale = 1.0f / std::sqrt((float)hd);
     const uint32_t group = m.n_head / m.n_head_kv;
     for (uint32_t l = 0; l < m.n_layer; ++l) {
@@ -600,6 +602,9 @@ void forward(Ctx & c, size_t n_rows, const int32_t * slot, const uint32_t * n, c
                 std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return prob[a] > prob[b]; });
                 std::vector<int32_t> sel(order.begin(), order.begin() + K);
                 for (size_t j = 0; j < K; ++j) c.last_routes[((size_t)l * T + t) * K + j] = sel[j];
+                float margin = INFINITY;
+                for (size_t j = 0; j < K && j + 1 < E; ++j) margin = std::min(margin, prob[order[j]] - prob[order[j + 1]]);
+                c.last_route_margins[(size_t)l * T + t] = margin;
                 // accumulate in ascending expert id so the sum does not depend on how experts are placed
                 std::sort(sel.begin(), sel.end());
                 float * ot = &o[t * d];
@@ -985,6 +990,13 @@ int ora_step(void * cp, size_t n_rows, const int32_t * slot, const uint32_t * n,
 }
 
 // Expert ids the last step selected: [layer][token][k], selection order.
+size_t ora_last_route_margins(void * cp, float * out, size_t n_max) {
+    Ctx & c = *(Ctx *)cp;
+    const size_t n = std::min(n_max, c.last_route_margins.size());
+    if (out) std::memcpy(out, c.last_route_margins.data(), n * 4);
+    return c.last_route_margins.size();
+}
+
 size_t ora_last_routes(void * cp, int32_t * out, size_t n_max) {
     Ctx & c = *(Ctx *)cp;
     const size_t n = std::min(n_max, c.last_routes.size());

@@ -76,6 +76,8 @@ def lib() -> C.CDLL:
         l.ora_step.argtypes = [C.c_void_p, C.c_size_t, _P(C.c_int32), _P(C.c_uint32), _P(C.c_int32), _P(C.c_uint8), _P(C.c_int32), _P(C.c_int32), _P(C.c_float)]
         l.ora_pack.restype = C.c_size_t
         l.ora_pack.argtypes = [C.c_size_t, _P(C.c_int32), _P(C.c_uint32), _P(C.c_int32), _P(C.c_uint8)] + [_P(C.c_int32)] * 5 + [_P(C.c_size_t)]
+        l.ora_last_route_margins.restype = C.c_size_t
+        l.ora_last_route_margins.argtypes = [C.c_void_p, _P(C.c_float), C.c_size_t]
         l.ora_last_routes.restype = C.c_size_t
         l.ora_last_routes.argtypes = [C.c_void_p, _P(C.c_int32), C.c_size_t]
         l.ora_seq_pos.argtypes = [C.c_void_p, C.c_int32, _P(C.c_int32), _P(C.c_int32)]
@@ -212,6 +214,14 @@ class Context:
         if status != 0:
             raise RuntimeError(lib().ora_last_error().decode())
         return logits[:S]
+
+    def last_route_margins(self) -> np.ndarray:
+        """Per (layer, token) of the last step: the smallest gap between the routing probabilities that decided
+        which experts were chosen and in which order (a gap near zero is a tie a float reordering may flip)."""
+        n = lib().ora_last_route_margins(self._h, None, 0)
+        out = np.zeros(n, dtype=np.float32)
+        lib().ora_last_route_margins(self._h, out.ctypes.data_as(_P(C.c_float)), n)
+        return out
 
     def last_routes(self) -> np.ndarray:
         n = lib().ora_last_routes(self._h, None, 0)

@@ -23,6 +23,7 @@ from .engine import (
     grammar_check,
     nccl_unique_id,
     op_gemm,
+    reasoning_check,
     op_gemm_mxfp4_grouped,
     quantize_row,
     recode_mxfp4_as_q8_0,
@@ -47,6 +48,7 @@ __all__ = [
     "load_library",
     "nccl_unique_id",
     "op_gemm",
+    "reasoning_check",
     "op_gemm_mxfp4_grouped",
     "quantize_row",
     "recode_mxfp4_as_q8_0",

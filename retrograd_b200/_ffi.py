@@ -183,6 +183,12 @@ SYMBOLS = {
     "retro_engine_eos_token": (C.c_int, [C.c_void_p, _P(C.c_int32)]),
     "retro_engine_vocab_size": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
     "retro_engine_is_eog_token": (C.c_int, [C.c_void_p, C.c_int32, _P(C.c_bool)]),
+    "retro_engine_set_reasoning_budget": (C.c_int, [C.c_void_p, C.c_int32]),
+    "retro_b200_reasoning_check": (C.c_int, [_P(C.c_int32), C.c_size_t, _P(_P(C.c_int32)), _P(C.c_size_t), C.c_size_t, C.c_int32, C.c_size_t, _P(C.c_int32),
+                                             C.c_size_t, _P(C.c_int32), C.c_size_t, _P(C.c_int32), C.c_size_t, _P(C.c_int32), _P(C.c_uint8)]),
+    "retro_trainer_set_reasoning_budget": (C.c_int, [C.c_void_p, C.c_int32]),
+    "retro_b200_engine_set_reasoning_tags": (C.c_int, [C.c_void_p, _P(C.c_int32), C.c_size_t, _P(_P(C.c_int32)), _P(C.c_size_t), C.c_size_t, C.c_size_t]),
+    "retro_b200_trainer_set_reasoning_tags": (C.c_int, [C.c_void_p, _P(C.c_int32), C.c_size_t, _P(_P(C.c_int32)), _P(C.c_size_t), C.c_size_t, C.c_size_t]),
     "retro_engine_context_size": (C.c_int, [C.c_void_p, _P(C.c_uint32)]),
     "retro_engine_detokenize": (C.c_int, [C.c_void_p, _P(C.c_int32), C.c_size_t, C.c_bool, C.c_char_p, C.c_size_t, _P(C.c_size_t)]),
     "retro_engine_tokenize_text": (C.c_int, [C.c_void_p, C.c_char_p, _P(C.c_int32), C.c_size_t, _P(C.c_size_t)]),

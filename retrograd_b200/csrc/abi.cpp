@@ -1156,7 +1156,70 @@ int retro_trainer_generation_adapter_rows_info(retro_trainer * trainer, retro_ad
     return g ? retro_engine_adapter_rows_info(g, out_info) : STATUS_RUNTIME;
 }
 
+// Reasoning budget (retro_lora_train.h:1680-1688, 2622-2627): -1 lets the model decide, N >= 0 forces the block's end
+// tag after N reasoning tokens. The reference reads the tags out of the model's chat template; this library renders
+// no templates, so the caller's template layer hands the tags over as token ids first (the extension below) and a
+// budget without tags is refused with the reference's own message for a template without a reasoning block.
+int retro_engine_set_reasoning_budget(retro_engine * engine, int32_t budget) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        return e ? e->set_reasoning_budget(budget) : STATUS_RUNTIME;
+    });
+}
+int retro_trainer_set_reasoning_budget(retro_trainer * trainer, int32_t budget) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_engine_set_reasoning_budget(g, budget) : STATUS_RUNTIME;
+}
+int retro_b200_engine_set_reasoning_tags(retro_engine * engine, const int32_t * start, size_t n_start, const int32_t * const * end_tags,
+                                         const size_t * n_end, size_t n_end_tags, size_t n_prompt_tail) {
+    return boundary([&]() -> int {
+        Engine * e = checked(engine);
+        if (!e) return STATUS_RUNTIME;
+        if (n_end_tags && (!end_tags || !n_end)) {
+            set_error("end_tags and n_end are required");
+            return STATUS_RUNTIME;
+        }
+        return e->set_reasoning_tags(start, n_start, end_tags, n_end, n_end_tags, n_prompt_tail);
+    });
+}
+int retro_b200_trainer_set_reasoning_tags(retro_trainer * trainer, const int32_t * start, size_t n_start, const int32_t * const * end_tags,
+                                          const size_t * n_end, size_t n_end_tags, size_t n_prompt_tail) {
+    retro_engine * g = generation_of(trainer);
+    return g ? retro_b200_engine_set_reasoning_tags(g, start, n_start, end_tags, n_end, n_end_tags, n_prompt_tail) : STATUS_RUNTIME;
+}
+
 // ---- extensions -----------------------------------------------------------------------------
+
+// Host logic only: runs one request's budget machine - primed with the end of `prompt`, then fed the tokens a
+// sampler drew - and returns what the step would emit: out_tokens[i] and whether the budget forced it.
+// `incomplete` lists token ids whose text stops inside a UTF-8 sequence.
+int retro_b200_reasoning_check(const int32_t * start, size_t n_start, const int32_t * const * end_tags, const size_t * n_end, size_t n_end_tags,
+                               int32_t budget, size_t n_prompt_tail, const int32_t * prompt, size_t n_prompt, const int32_t * incomplete,
+                               size_t n_incomplete, const int32_t * sampled, size_t n_sampled, int32_t * out_tokens, uint8_t * out_forced) {
+    return boundary([&]() -> int {
+        if ((n_sampled && (!sampled || !out_tokens || !out_forced)) || (n_end_tags && (!end_tags || !n_end))) {
+            set_error("reasoning_check: bad arguments");
+            return STATUS_INVALID_ARGUMENT;
+        }
+        ReasoningPlan plan;
+        if (n_start) plan.starts.emplace_back(start, start + n_start);
+        for (size_t e = 0; e < n_end_tags; ++e)
+            if (n_end[e]) plan.ends.emplace_back(end_tags[e], end_tags[e] + n_end[e]);
+        if (!plan.ends.empty()) plan.forced = plan.ends.front();
+        plan.budget = budget;
+        plan.n_prompt_tail = n_prompt_tail;
+        plan.active = budget >= 0 && !plan.starts.empty() && !plan.ends.empty();
+        const std::vector<int32_t> partial(incomplete, incomplete + (incomplete ? n_incomplete : 0));
+        BudgetMachine machine(&plan, [&](int32_t token) { return std::find(partial.begin(), partial.end(), token) == partial.end(); });
+        machine.prime(prompt, prompt ? n_prompt : 0);
+        for (size_t i = 0; i < n_sampled; ++i) {
+            bool forced = false;
+            out_tokens[i] = machine.next(sampled[i], forced);
+            out_forced[i] = forced ? 1 : 0;
+        }
+        return STATUS_OK;
+    });
+}
 
 int retro_b200_synth_gguf(const char * path, const char * spec, uint64_t * out_bytes) {
     return boundary([&]() -> int {

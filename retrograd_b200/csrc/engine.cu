@@ -1062,6 +1062,28 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         token_pieces_.resize(hp.vocab);
         for (uint32_t t = 0; t < hp.vocab; ++t) token_pieces_[t] = model->piece((int32_t)t, false);
     }
+    // reasoning budget: every request's machine follows the engine's current plan, and until its first sampling
+    // row collects the end of its prompt across chunks (retro_gen_core.cpp:2609-2645)
+    if (reasoning_plan_.active || reasoning_seen_) {
+        reasoning_seen_ = true;
+        for (size_t r = 0; r < R; ++r) {
+            const EffRow & row = rows[r];
+            if (row.request < 0) continue;
+            RequestState & req = requests[row.request];
+            if (!req.plan || !(*req.plan == reasoning_plan_)) {
+                req.plan = std::make_unique<ReasoningPlan>(reasoning_plan_);
+                const Model * mdl = model.get();
+                req.budget = BudgetMachine(req.plan.get(), [mdl](int32_t token) { return utf8_is_complete(mdl->piece(token, true)); });
+                req.primed = false;
+                req.prompt_tail.clear();
+            }
+            if (!reasoning_plan_.active || req.primed) continue;
+            req.prompt_tail.insert(req.prompt_tail.end(), row.tokens, row.tokens + row.n);
+            if (req.prompt_tail.size() > reasoning_plan_.n_prompt_tail)
+                req.prompt_tail.erase(req.prompt_tail.begin(), req.prompt_tail.end() - (ptrdiff_t)reasoning_plan_.n_prompt_tail);
+        }
+    }
+    bool forced_outside_grammar = false;
     size_t top_stride = 0;
     bool any_v2 = false;       // some row needs the working copy of the logits
     int n_greedy_fast = 0;
@@ -1075,8 +1097,14 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 req.seed = row.v2 ? row.v2->seed : row.v1.seed;
                 req.seeded = true;
             }
+            if (req.budget.active() && !req.primed) {
+                req.budget.prime(req.prompt_tail.data(), req.prompt_tail.size());
+                req.primed = true;
+            }
+            const int32_t forced_token = req.budget.pending();
             SampleDesc & d = descs[s++];
             std::memset(&d, 0, sizeof d);
+            if (forced_token >= 0) d.pad[1] = (uint32_t)forced_token + 1;
             d.seed = req.seed;
             d.draw_lo = (uint32_t)req.draws;
             d.draw_hi = (uint32_t)(req.draws >> 32);
@@ -1112,6 +1140,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                         any_allowed = true;
                     }
                     grammar_dead_end = grammar_dead_end || !any_allowed;
+                    if (forced_token >= 0 && !g.allows(token_pieces_[forced_token], model->is_eog(forced_token))) forced_outside_grammar = true;
                     row_grammar[r] = std::move(state);
                 }
                 // one merged edit per distinct id: summed bias, then the penalties of the window
@@ -1135,7 +1164,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 }
                 for (const auto & e : merged) edits.push_back(e.second);
                 d.edit_end = (uint32_t)edits.size();
-                if (p.top_k == 1 && merged.empty() && !p.grammar) {
+                if (p.top_k == 1 && merged.empty() && !p.grammar && forced_token < 0) {
                     d.flags |= 4u;      // plain greedy: arg-max of the raw row, no working copy
                     ++n_greedy_fast;
                 } else {
@@ -1518,6 +1547,10 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         route_pairs += ids.size();      // every pair is served from a bank resident on the device
     }
 
+    if (forced_outside_grammar) {
+        set_error("the reasoning budget forced a token excluded by the grammar");
+        return STATUS_RUNTIME;
+    }
     if (grammar_dead_end) {
         // as in the reference, the decode has happened by the time a grammar turns out to allow nothing (retro_gen_core.cpp:790-797)
         set_error("grammar allows no token at this position");
@@ -1535,28 +1568,82 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         o = OutRow{};
         if (!row.sample) continue;
         const SampleOut & so = h_out[s];
-        o.token = so.token;
+        RequestState & req = requests[row.request];
+        // a forcing budget machine had its token reported by the sampling kernel; here it moves on
+        bool forced = false;
+        const int32_t emitted = req.budget.next(so.token, forced);
+        o.token = emitted;
         o.logprob = so.logprob;
         o.sampled = 1;
-        o.forced = 0;
+        o.forced = forced ? 1 : 0;
         o.n_top = so.n_top;
         o.sampled_logprob = row.v2 && row.want_logprob ? so.sampled_logprob : 0.f;
         for (uint32_t j = 0; j < so.n_top; ++j) {
             out_top_ids[r * n_top_stride + j] = h_ids[s * top_stride + j];
             out_top_logprobs[r * n_top_stride + j] = h_lps[s * top_stride + j];
         }
-        RequestState & req = requests[row.request];
         ++req.draws;
-        if (row.v2) req.history.push_back(so.token);
+        if (row.v2) req.history.push_back(emitted);
         // the request's grammar follows the emitted token; a row without one drops what the request had
         if (row_grammar[r]) {
-            row_grammar[r]->advance(model->piece(so.token, false), model->is_eog(so.token));
+            row_grammar[r]->advance(model->piece(emitted, false), model->is_eog(emitted));
             req.grammar = std::move(row_grammar[r]);
         } else if (row.v2) {
             req.grammar.reset();
         }
         ++s;
     }
+    return STATUS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Reasoning budget (reference: retro_engine_set_reasoning_budget, retro_chat_parser.cpp:544-640)
+
+int Engine::set_reasoning_tags(const int32_t * start, size_t n_start, const int32_t * const * ends, const size_t * n_ends, size_t n_end_tags,
+                               size_t n_prompt_tail) {
+    ReasoningPlan plan;
+    auto tag = [&](const int32_t * tokens, size_t n, std::vector<int32_t> & out) {
+        for (size_t i = 0; i < n; ++i) {
+            if (tokens[i] < 0 || (uint32_t)tokens[i] >= model->hp.vocab) return false;
+            out.push_back(tokens[i]);
+        }
+        return true;
+    };
+    std::vector<int32_t> one;
+    if (n_start && (!start || !tag(start, n_start, one))) {
+        set_error("a reasoning tag holds a token id outside the vocabulary");
+        return STATUS_RUNTIME;
+    }
+    if (!one.empty()) plan.starts.push_back(one);
+    for (size_t e = 0; e < n_end_tags; ++e) {
+        one.clear();
+        if (n_ends[e] && (!ends || !ends[e] || !tag(ends[e], n_ends[e], one))) {
+            set_error("a reasoning tag holds a token id outside the vocabulary");
+            return STATUS_RUNTIME;
+        }
+        if (!one.empty()) plan.ends.push_back(one);
+    }
+    plan.n_prompt_tail = n_prompt_tail;
+    plan.budget = reasoning_plan_.budget;
+    if (!plan.ends.empty()) plan.forced = plan.ends.front();
+    plan.active = plan.budget >= 0 && !plan.starts.empty() && !plan.ends.empty();
+    reasoning_plan_ = std::move(plan);
+    return STATUS_OK;
+}
+
+int Engine::set_reasoning_budget(int32_t budget) {
+    if (budget < -1) {
+        set_error("reasoning budget must be -1 (the model decides) or a token count");
+        return STATUS_RUNTIME;
+    }
+    if (budget >= 0 && (reasoning_plan_.starts.empty() || reasoning_plan_.ends.empty())) {
+        // the reference derives the tags from the model's chat template; here the caller's template layer hands
+        // them over first (retro_b200_engine_set_reasoning_tags), and without them there is nothing to limit
+        set_error("the chat template declares no reasoning block, so a reasoning budget has nothing to limit");
+        return STATUS_RUNTIME;
+    }
+    reasoning_plan_.budget = budget;
+    reasoning_plan_.active = budget >= 0;
     return STATUS_OK;
 }
 

@@ -11,6 +11,7 @@
 #include "ep.hpp"
 #include "kv.hpp"
 #include "grammar.hpp"
+#include "reasoning_budget.hpp"
 
 #include <map>
 #include <memory>
@@ -206,6 +207,12 @@ struct RequestState {
     uint64_t draws = 0;
     std::vector<int32_t> history;
     std::unique_ptr<GrammarState> grammar;      // v2 rows with a grammar: where the generation stands in it
+    // reasoning budget: the plan the request's machine reads (a snapshot, the engine's may change under it), the
+    // machine, and the end of the prompt collected across prefill chunks until the first sampling row primes it
+    std::unique_ptr<ReasoningPlan> plan;
+    BudgetMachine budget;
+    bool primed = false;
+    std::vector<int32_t> prompt_tail;
 };
 
 // A step row normalised from either ABI version.
@@ -268,6 +275,11 @@ public:
     std::unique_ptr<Model> model;
     std::unique_ptr<KvManager> kv;
     std::unordered_map<int32_t, RequestState> requests;
+    // Reasoning budget (retro_engine_set_reasoning_budget): the tags as token ids from the caller's chat-template
+    // layer, then the budget; -1 with the error set when the tags are unknown or outside the vocabulary.
+    int set_reasoning_tags(const int32_t * start, size_t n_start, const int32_t * const * ends, const size_t * n_ends, size_t n_end_tags,
+                           size_t n_prompt_tail);
+    int set_reasoning_budget(int32_t budget);
 
     // inspection state of the last step
     size_t last_T = 0, last_S = 0, last_R = 0;
@@ -373,6 +385,8 @@ private:
     std::map<std::string, int32_t> serial_ids_;      // name -> id in adapters_
     std::string active_name_;
     int32_t active_id_ = 0;
+    ReasoningPlan reasoning_plan_;                  // active when tags and a budget >= 0 are set
+    bool reasoning_seen_ = false;                   // some request may still hold a machine
     std::vector<std::string> token_pieces_;         // every token's text, built when the first grammar row arrives
     std::map<int32_t, Adapter> adapters_;
     std::map<int32_t, int32_t> adapter_index_;   // id -> stack index

@@ -289,9 +289,13 @@ bool gemm_q8_0_tc5_supported(const WeightView & w, const SplitAct & x) {
 void launch_gemm_q8_0_tc5(const WeightView & w, const SplitAct & x, int n_tokens, float * y, int ldy, const float * bias, const float * residual,
                           int ldr, int * error_flag, int n_sm, cudaStream_t stream) {
     if (n_tokens <= 0) return;
-    // 256-token tiles halve the decode work per product; taken when they still give every SM two tiles
+    // 256-token tiles halve the decode work per product, but the grid is whole waves of one CTA per SM: the form
+    // with the shorter estimated time wins (a stage of 64 columns is twelve MMAs: about 1536 cycles at N = 256,
+    // 852 at N = 128)
     const int row_tiles = (int)((w.n_out + BM - 1) / BM);
-    const bool wide = n_tokens >= 256 && row_tiles * ((n_tokens + 255) / 256) >= 2 * n_sm;
+    const long long waves_wide = ((long long)row_tiles * ((n_tokens + 255) / 256) + n_sm - 1) / n_sm;
+    const long long waves_narrow = ((long long)row_tiles * ((n_tokens + 127) / 128) + n_sm - 1) / n_sm;
+    const bool wide = n_tokens > 128 && waves_wide * 1536 < waves_narrow * 852;
     if (wide) {
         if (residual) launch_one<256, true>(w, x, n_tokens, y, ldy, bias, residual, ldr, error_flag, stream);
         else launch_one<256, false>(w, x, n_tokens, y, ldy, bias, nullptr, 0, error_flag, stream);

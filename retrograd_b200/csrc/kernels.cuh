@@ -196,7 +196,7 @@ struct SampleDesc {
     uint32_t flags;       // bit0: v2 row (post-transform reporting), bit1: want sampled_logprob, bit2: greedy without edits
     uint32_t edit_begin;  // range in the logit-edit list
     uint32_t edit_end;
-    uint32_t pad[5];
+    uint32_t pad[5];      // pad[0]: 1 + word offset of the row's grammar mask (0: none); pad[1]: 1 + the token a reasoning budget forces (0: none)
 };
 
 // One sparse change of a logits row before sampling (v2 rows): logit_bias adds, penalties.
@@ -404,7 +404,7 @@ void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float
 // Segmented LoRA on the tensor cores (TF32 MMAs on split operands, F32-accurate): shrink over K splits into
 // tmp[split][t][r] (tmp holds kLoraTcMaxSplits * n_tokens * r_max floats), then expand into y. Tokens grouped by
 // adapter as for launch_lora_shrink_grouped.
-constexpr int kLoraTcMaxSplits = 8;
+constexpr int kLoraTcMaxSplits = 16;
 int lora_tc_splits(int n_in);
 bool lora_tc_supported(int r_max, int n_in, const float * a_stack, const float * x, int ldx);
 void launch_lora_tc(const float * a_stack, const float * b_stack, const float * scales, int r_max, int n_in, int n_out, int n_adapters,

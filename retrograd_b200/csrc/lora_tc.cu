@@ -40,9 +40,14 @@ __device__ __forceinline__ void mma_3x(float (&c)[4], const uint32_t (&ab)[4], c
 }
 
 // The (adapter, 16-token tile) a CTA owns: tiles are numbered segment by segment. False past the last tile.
-__device__ __forceinline__ bool find_tile(int tile, int n_adapters, const int32_t * __restrict__ offsets, int & adapter, int & first, int & end) {
+// The segment offsets are fetched by the whole CTA at once (one load latency instead of one per adapter).
+constexpr int kMaxAdapters = 1024;
+__device__ __forceinline__ bool find_tile(int tile, int n_adapters, const int32_t * __restrict__ offsets, int * sh_offsets, int & adapter, int & first,
+                                          int & end) {
+    for (int i = threadIdx.x; i <= n_adapters; i += blockDim.x) sh_offsets[i] = offsets[i];
+    __syncthreads();
     for (int a = 0; a < n_adapters; ++a) {
-        const int b = offsets[a], e = offsets[a + 1];
+        const int b = sh_offsets[a], e = sh_offsets[a + 1];
         const int n = (e - b + 15) >> 4;
         if (tile < n) {
             adapter = a;
@@ -55,16 +60,19 @@ __device__ __forceinline__ bool find_tile(int tile, int n_adapters, const int32_
     return false;
 }
 
-// grid (tile bound, K splits), 4 warps: the warps take the CTA's columns in interleaved chunks of 16 and their
-// 16 x (8 NR) partial results are added in warp order through shared memory.
+// grid (tile bound, K splits), 8 warps: the warps take the CTA's columns in interleaved chunks of 16 and their
+// 16 x (8 NR) partial results are added in warp order through shared memory. The work is a few hundred KB per
+// launch, so the kernel is built for load parallelism: many short K ranges, four chunks' loads in flight per warp.
+constexpr int kShrinkWarps = 8;
 template <int NR>
-__global__ void __launch_bounds__(128) lora_shrink_tc_kernel(const float * __restrict__ a_stack, int r_max, int n_in, int n_adapters,
+__global__ void __launch_bounds__(kShrinkWarps * 32) lora_shrink_tc_kernel(const float * __restrict__ a_stack, int r_max, int n_in, int n_adapters,
                                                              const int32_t * __restrict__ offsets, const int32_t * __restrict__ sorted,
                                                              const float * __restrict__ x, int ldx, float * __restrict__ tmp, int n_tokens,
                                                              int k_per_split) {
-    __shared__ float red[4][16][NR * 8 + 1];
+    __shared__ float red[kShrinkWarps][16][NR * 8 + 1];
+    __shared__ int sh_offsets[kMaxAdapters + 1];
     int adapter, first, end;
-    if (!find_tile(blockIdx.x, n_adapters, offsets, adapter, first, end)) return;
+    if (!find_tile(blockIdx.x, n_adapters, offsets, sh_offsets, adapter, first, end)) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int tok0 = first + g < end ? sorted[first + g] : -1, tok1 = first + g + 8 < end ? sorted[first + g + 8] : -1;
     const float * x0 = x + (size_t)max(tok0, 0) * ldx + 4 * t;
@@ -75,8 +83,8 @@ __global__ void __launch_bounds__(128) lora_shrink_tc_kernel(const float * __res
 #pragma unroll
     for (int j = 0; j < NR; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 2
-    for (int k = k0 + warp * 16; k < k1; k += 64) {
+#pragma unroll 4
+    for (int k = k0 + warp * 16; k < k1; k += kShrinkWarps * 16) {
         const float4 v0 = tok0 >= 0 ? *reinterpret_cast<const float4 *>(x0 + k) : zero;
         const float4 v1 = tok1 >= 0 ? *reinterpret_cast<const float4 *>(x1 + k) : zero;
         float4 av[NR];
@@ -111,22 +119,26 @@ __global__ void __launch_bounds__(128) lora_shrink_tc_kernel(const float * __res
     }
     __syncthreads();
     float * out = tmp + (size_t)blockIdx.y * n_tokens * r_max;
-    for (int i = threadIdx.x; i < 16 * NR * 8; i += 128) {
+    for (int i = threadIdx.x; i < 16 * NR * 8; i += kShrinkWarps * 32) {
         const int row = i / (NR * 8), col = i % (NR * 8);
         if (first + row >= end || col >= r_max) continue;
-        const float v = ((red[0][row][col] + red[1][row][col]) + red[2][row][col]) + red[3][row][col];
+        float v = red[0][row][col];
+#pragma unroll
+        for (int w = 1; w < kShrinkWarps; ++w) v += red[w][row][col];
         out[(size_t)sorted[first + row] * r_max + col] = v;
     }
 }
 
-// grid (tile bound, column groups), 4 warps: a warp walks its group's columns eight at a time.
+// grid (tile bound, column groups of 128), 4 warps: a warp takes four column tiles of eight, with every load of
+// the four (B rows and the y values they update) issued before the first MMA.
 template <int NR>
 __global__ void __launch_bounds__(128) lora_expand_tc_kernel(const float * __restrict__ b_stack, int r_max, int n_out, const float * __restrict__ scales,
                                                              int n_adapters, const int32_t * __restrict__ offsets, const int32_t * __restrict__ sorted,
                                                              const float * __restrict__ tmp, int n_splits, int n_tokens, float * __restrict__ y, int ldy,
                                                              int cols_per_cta, int vec2) {
+    __shared__ int sh_offsets[kMaxAdapters + 1];
     int adapter, first, end;
-    if (!find_tile(blockIdx.x, n_adapters, offsets, adapter, first, end)) return;
+    if (!find_tile(blockIdx.x, n_adapters, offsets, sh_offsets, adapter, first, end)) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int tok0 = first + g < end ? sorted[first + g] : -1, tok1 = first + g + 8 < end ? sorted[first + g + 8] : -1;
     // the tile's shrink results (K splits added in split order) as the A operand, split once
@@ -144,41 +156,56 @@ __global__ void __launch_bounds__(128) lora_expand_tc_kernel(const float * __res
     }
     const float scale = scales[adapter];
     const float * br = b_stack + (size_t)adapter * n_out * r_max;
-    const int o_end = min(n_out, ((int)blockIdx.y + 1) * cols_per_cta);
-    for (int o0 = blockIdx.y * cols_per_cta + warp * 8; o0 < o_end; o0 += 32) {
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+    constexpr int CT = 4;                          // column tiles per warp
+    const int o_base = blockIdx.y * cols_per_cta + warp * (CT * 8);
+    float bv[CT][NR][2];
+    float2 y0[CT], y1[CT];
+#pragma unroll
+    for (int i = 0; i < CT; ++i) {
+        const int o0 = o_base + i * 8;
         const bool row_ok = o0 + g < n_out;
         const float * bo = br + (size_t)(o0 + g) * r_max;
 #pragma unroll
         for (int kk = 0; kk < NR; ++kk) {
             const int r0 = kk * 8 + t, r1 = r0 + 4;
-            uint32_t b0, s0, b1, s1;
-            split_tf32(row_ok && r0 < r_max ? bo[r0] : 0.f, b0, s0);
-            split_tf32(row_ok && r1 < r_max ? bo[r1] : 0.f, b1, s1);
-            mma_3x(c, ab[kk], as[kk], b0, b1, s0, s1);
+            bv[i][kk][0] = row_ok && r0 < r_max ? bo[r0] : 0.f;
+            bv[i][kk][1] = row_ok && r1 < r_max ? bo[r1] : 0.f;
         }
         const int col = o0 + 2 * t;
+        y0[i] = y1[i] = make_float2(0.f, 0.f);
         if (vec2 && col + 1 < n_out) {
-            if (tok0 >= 0) {
-                float2 * p = reinterpret_cast<float2 *>(y + (size_t)tok0 * ldy + col);
-                float2 v = *p;
-                v.x += scale * c[0];
-                v.y += scale * c[1];
-                *p = v;
-            }
-            if (tok1 >= 0) {
-                float2 * p = reinterpret_cast<float2 *>(y + (size_t)tok1 * ldy + col);
-                float2 v = *p;
-                v.x += scale * c[2];
-                v.y += scale * c[3];
-                *p = v;
-            }
+            if (tok0 >= 0) y0[i] = *reinterpret_cast<const float2 *>(y + (size_t)tok0 * ldy + col);
+            if (tok1 >= 0) y1[i] = *reinterpret_cast<const float2 *>(y + (size_t)tok1 * ldy + col);
         } else {
+            if (tok0 >= 0 && col < n_out) y0[i].x = y[(size_t)tok0 * ldy + col];
+            if (tok0 >= 0 && col + 1 < n_out) y0[i].y = y[(size_t)tok0 * ldy + col + 1];
+            if (tok1 >= 0 && col < n_out) y1[i].x = y[(size_t)tok1 * ldy + col];
+            if (tok1 >= 0 && col + 1 < n_out) y1[i].y = y[(size_t)tok1 * ldy + col + 1];
+        }
+    }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int tok = e < 2 ? tok0 : tok1, cc = col + (e & 1);
-                if (tok >= 0 && cc < n_out) y[(size_t)tok * ldy + cc] += scale * c[e];
-            }
+    for (int i = 0; i < CT; ++i) {
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int kk = 0; kk < NR; ++kk) {
+            uint32_t b0, s0, b1, s1;
+            split_tf32(bv[i][kk][0], b0, s0);
+            split_tf32(bv[i][kk][1], b1, s1);
+            mma_3x(c, ab[kk], as[kk], b0, b1, s0, s1);
+        }
+        const int col = o_base + i * 8 + 2 * t;
+        y0[i].x += scale * c[0];
+        y0[i].y += scale * c[1];
+        y1[i].x += scale * c[2];
+        y1[i].y += scale * c[3];
+        if (vec2 && col + 1 < n_out) {
+            if (tok0 >= 0) *reinterpret_cast<float2 *>(y + (size_t)tok0 * ldy + col) = y0[i];
+            if (tok1 >= 0) *reinterpret_cast<float2 *>(y + (size_t)tok1 * ldy + col) = y1[i];
+        } else {
+            if (tok0 >= 0 && col < n_out) y[(size_t)tok0 * ldy + col] = y0[i].x;
+            if (tok0 >= 0 && col + 1 < n_out) y[(size_t)tok0 * ldy + col + 1] = y0[i].y;
+            if (tok1 >= 0 && col < n_out) y[(size_t)tok1 * ldy + col] = y1[i].x;
+            if (tok1 >= 0 && col + 1 < n_out) y[(size_t)tok1 * ldy + col + 1] = y1[i].y;
         }
     }
 }
@@ -193,7 +220,7 @@ template <class F> void dispatch_rank_tiles(int r_max, F && f) {
 
 } // namespace
 
-int lora_tc_splits(int n_in) { return std::max(1, std::min(kLoraTcMaxSplits, n_in / 2048)); }
+int lora_tc_splits(int n_in) { return std::max(1, std::min(kLoraTcMaxSplits, n_in / 1024)); }
 
 bool lora_tc_supported(int r_max, int n_in, const float * a_stack, const float * x, int ldx) {
     return r_max >= 1 && r_max <= 64 && n_in % 16 == 0 && ldx % 4 == 0 && (uintptr_t)a_stack % 16 == 0 && (uintptr_t)x % 16 == 0;
@@ -205,12 +232,12 @@ void launch_lora_tc(const float * a_stack, const float * b_stack, const float * 
     if (n_tokens <= 0 || n_adapters <= 0) return;
     const int tiles = (n_tokens + 15) / 16 + n_adapters;          // every segment may end in a partial tile
     const int splits = lora_tc_splits(n_in);
-    const int k_per_split = ((n_in + splits - 1) / splits + 63) / 64 * 64;
-    const int cols_per_cta = 512;
+    const int k_per_split = ((n_in + splits - 1) / splits + 15) / 16 * 16;
+    const int cols_per_cta = 128;
     const int vec2 = ldy % 2 == 0 && (uintptr_t)y % 8 == 0 ? 1 : 0;
     dispatch_rank_tiles(r_max, [&](auto tag) {
         constexpr int NR = decltype(tag)::value;
-        lora_shrink_tc_kernel<NR><<<dim3(tiles, splits), 128, 0, stream>>>(a_stack, r_max, n_in, n_adapters, offsets, sorted, x, ldx, tmp, n_tokens,
+        lora_shrink_tc_kernel<NR><<<dim3(tiles, splits), kShrinkWarps * 32, 0, stream>>>(a_stack, r_max, n_in, n_adapters, offsets, sorted, x, ldx, tmp, n_tokens,
                                                                          k_per_split);
         lora_expand_tc_kernel<NR><<<dim3(tiles, (n_out + cols_per_cta - 1) / cols_per_cta), 128, 0, stream>>>(
             b_stack, r_max, n_out, scales, n_adapters, offsets, sorted, tmp, splits, n_tokens, y, ldy, cols_per_cta, vec2);

@@ -423,6 +423,11 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float * __restri
 
     // ---- outputs
     __syncthreads();
+    // A row whose reasoning budget is forcing reports the forced token in place of the drawn one (the draw still
+    // happened: the request's counter moves as in the reference, which samples first and replaces afterwards).
+    const int32_t drawn = token;
+    const bool forced = d.pad[1] != 0;
+    if (forced) token = (int32_t)d.pad[1] - 1;
     if (v2 && n_top > 0) {
         // post-transformation top-k: by probability desc (= transformed logit desc), id asc
         float pv = INFINITY;
@@ -432,7 +437,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float * __restri
             int32_t bi = 0x7fffffff;
             for (int i = tid; i < V; i += kThreads) {
                 float v = l[i];
-                if (single && i != token) v = -INFINITY;
+                if (single && i != drawn) v = -INFINITY;
                 const bool after = v < pv || (v == pv && i > pid);
                 if (after && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
             }
@@ -452,7 +457,8 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float * __restri
         o.logprob = (float)((double)raw[token] - (double)rmax - rlog);
         o.sampled_logprob = 0.f;
         if (v2 && (d.flags & kFlagWantLogprob)) {
-            o.sampled_logprob = (float)log(exp(((double)l[token] - (double)tmax) * inv_t) / kept);
+            // (a one-token nucleus gives every other token, a forced one included, probability zero)
+            o.sampled_logprob = single && token != drawn ? -INFINITY : (float)log(exp(((double)l[token] - (double)tmax) * inv_t) / kept);
         }
         o.n_top = n_top;
         outs[row] = o;

@@ -256,6 +256,21 @@ def op_gemm_mxfp4_grouped(banks, n_expert: int, n_out: int, n_in: int, x, offset
     return y
 
 
+def reasoning_check(start, ends, budget: int, n_prompt_tail: int, prompt, sampled, incomplete=()):
+    """One request's reasoning-budget machine on the host (retro_b200_reasoning_check): returns (emitted tokens,
+    forced flags) for the tokens a sampler drew after `prompt`."""
+    lib = _ffi.load_library()
+    arr = lambda v: (C.c_int32 * max(len(v), 1))(*v)
+    tags = [arr(t) for t in ends]
+    ptrs = (C.POINTER(C.c_int32) * max(len(tags), 1))(*[C.cast(t, C.POINTER(C.c_int32)) for t in tags])
+    lens = (C.c_size_t * max(len(tags), 1))(*[len(t) for t in ends])
+    out_t = (C.c_int32 * max(len(sampled), 1))()
+    out_f = (C.c_uint8 * max(len(sampled), 1))()
+    _check(lib.retro_b200_reasoning_check(arr(start), len(start), ptrs, lens, len(tags), budget, n_prompt_tail, arr(prompt), len(prompt),
+                                          arr(incomplete), len(incomplete), arr(sampled), len(sampled), out_t, out_f))
+    return list(out_t[: len(sampled)]), [bool(f) for f in out_f[: len(sampled)]]
+
+
 def recode_mxfp4_as_q8_0(blocks: bytes) -> bytes | None:
     """MXFP4 blocks (17 B each) as Q8_0 blocks (34 B each) of the same values, as the engine does with expert
     banks at load; None when a block's scale is outside what an f16 holds. Host arithmetic only."""
@@ -346,6 +361,20 @@ class Engine:
         v = C.c_bool()
         _check(self._lib.retro_engine_is_eog_token(self._h, token, C.byref(v)))
         return v.value
+
+    def set_reasoning_tags(self, start: Sequence[int], ends: Sequence[Sequence[int]], n_prompt_tail: int) -> None:
+        """The reasoning block's tags as token ids (from the caller's chat-template layer): the opening tag, the
+        closing tags (the first is what a spent budget forces) and how much of a prompt's end primes a request."""
+        s_arr = (C.c_int32 * max(len(start), 1))(*start)
+        tags = [(C.c_int32 * max(len(t), 1))(*t) for t in ends]
+        ptrs = (C.POINTER(C.c_int32) * max(len(tags), 1))(*[C.cast(t, C.POINTER(C.c_int32)) for t in tags])
+        lens = (C.c_size_t * max(len(tags), 1))(*[len(t) for t in ends])
+        name = "retro_b200_engine_set_reasoning_tags" if self._twin_prefix == "retro_engine_" else "retro_b200_trainer_set_reasoning_tags"
+        _check(getattr(self._lib, name)(self._h, s_arr, len(start), ptrs, lens, len(tags), n_prompt_tail))
+
+    def set_reasoning_budget(self, budget: int) -> None:
+        name = "retro_engine_set_reasoning_budget" if self._twin_prefix == "retro_engine_" else "retro_trainer_set_reasoning_budget"
+        _check(getattr(self._lib, name)(self._h, budget))
 
     def kv_unified(self) -> bool:
         v = C.c_bool()

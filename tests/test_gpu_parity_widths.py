@@ -192,14 +192,25 @@ def test_moe_20b_widths_mxfp4(rb, oracle, models, monkeypatch, experts):
     greedy = rb.SamplingParamsV2.greedy()
     prompts = [rng.integers(3, 201088, n).tolist() for n in (130, 64, 9, 33, 77, 21, 50, 18, 95, 40, 12, 27)]
     rows = [rb.StepRow(i, i, p, 0, sample=True, sampling=greedy) for i, p in enumerate(prompts)]
+    route_ties = 0
     for step in range(3):
         toks = check_step(rb, engine, octx, oracle, rows, out, rep)
         expect_greedy(oracle, toks, rep)
         T = sum(len(r.tokens) for r in rows)
         got = engine.last_routes().reshape(om.n_layer, T, 4)
         want = octx.last_routes().reshape(om.n_layer, T, 4)
-        assert np.array_equal(got, want), f"{int((got != want).sum())} of {got.size} routed expert ids differ (max|dlogit| so far {rep.max_logit_diff:.3e})"
+        # Routing must agree bit for bit wherever the oracle's own probabilities decide it: a token whose deciding
+        # gap is below 2e-6 in some layer is a tie that any reordering of an f32 sum may flip; it is counted, and
+        # from that layer on the token is not compared. None of them may be a row's sampled (last) token.
+        margins = octx.last_route_margins().reshape(om.n_layer, T)
+        clear = np.logical_and.accumulate(margins > 2e-6, axis=0)
+        route_ties += int((~clear).any(axis=0).sum())
+        assert np.array_equal(got[clear], want[clear]), f"{int((got[clear] != want[clear]).sum())} routed expert ids differ away from ties"
+        ends = np.cumsum([len(r.tokens) for r in rows]) - 1
+        assert clear[:, ends].all(), "a sampled row's token sits on a routing tie: pick another seed"
         rows = [rb.StepRow.decode(i, i, out.row(i).token, len(prompts[i]) + step, greedy) for i in range(len(prompts))]
     assert len(np.unique(got)) > 8
     _summary(f"20B-MoE widths MXFP4 ({experts})", rep)
+    print(f"routing: {route_ties} tokens on a tie (gap <= 2e-6)")
+    assert route_ties <= 6
     engine.close()
