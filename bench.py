@@ -505,13 +505,14 @@ def main():
             try:
                 result = plain_vs_expert_parallel(rb, rank, 2, holder[0], path.parent)
                 result["engine"].close()
-                mine = {"steps": result["steps"], "bit_exact": result["bit_exact"]}
+                mine = {"steps": result["steps"], "bit_exact": result["bit_exact"], "footprint_split": result["footprint_split"]}
             except Exception as err:      # reported, not fatal: the replica measurement below does not depend on it
                 mine = {"steps": 0, "bit_exact": False, "error": str(err)[:200]}
         gathered = [None] * world
         dist.all_gather_object(gathered, mine)
         pair = [g for g in gathered[:2] if g]
-        ep_parity = {"ranks": 2, "steps": min(g["steps"] for g in pair), "bit_exact": all(g["bit_exact"] for g in pair)}
+        ep_parity = {"ranks": 2, "steps": min(g["steps"] for g in pair), "bit_exact": all(g["bit_exact"] for g in pair),
+                     "footprint_split": all(g.get("footprint_split", False) for g in pair)}
         errors = [g["error"] for g in pair if "error" in g]
         if errors:
             ep_parity["error"] = errors[0]
@@ -531,8 +532,11 @@ def main():
     if expert_parallel:
         holder = [rb.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(holder, src=0)
+        weights_before = engine.memory_report()["model_weight_bytes"]
         engine.ep_init(rank, world, holder[0])
         driver.expert_parallel = True
+        ep_block = {"world": world, "experts_per_rank": cfg["spec"]["experts"] // world, "exchange": "NCCL send/recv of f32 rows, per MoE layer",
+                    "weight_bytes_per_rank_before": weights_before, "weight_bytes_per_rank": engine.memory_report()["model_weight_bytes"]}
 
     # ---- ramp (untimed): a steady-state snapshot - every slot holds a request caught mid-flight
     driver.admit(midflight=True)
@@ -719,6 +723,8 @@ def main():
         line["decode_only"] = decode_only
     if ep_parity is not None:
         line["ep_parity"] = ep_parity
+    if expert_parallel:
+        line["expert_parallel"] = ep_block
     if world == 1 and not args.no_cpu_baseline:
         engine.close()
         value, times, cores = cpu_baseline(path, cfg)

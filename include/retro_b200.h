@@ -475,9 +475,10 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
 /* The grouped MXFP4 expert GEMM (tcgen05) on host data: `banks` = n_expert matrices of n_out rows x n_in
  * weights in 17-byte MXFP4 blocks, x = the offsets[n_expert] activation rows sorted by expert, offsets
  * [n_expert + 1] each expert's first row; y[r][o] = sum_k deq(bank[expert(r)])[o][k] * x[r][k]. -3 when the
- * operands are outside what the kernel covers (n_in % 64, block scales that are not f16 powers of two). */
+ * operands are outside what the kernel covers (n_in % 64, block scales that are not f16 powers of two). `iters`
+ * further launches are timed, each behind a write of a buffer larger than L2; *out_ms is their mean device time. */
 int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, uint32_t n_out, uint32_t n_in, const float * x,
-                                     const int32_t * offsets, float * y);
+                                     const int32_t * offsets, float * y, uint32_t iters, float * out_ms);
 
 /* No counterpart in the reference. The same exact Q4_K GEMM for callers that must not allocate
  * device memory (a host whose own pool owns the whole device budget, a loop that cannot take the
@@ -485,7 +486,7 @@ int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, u
  * (f32 [n_tokens][n_out]) are DEVICE pointers of the caller, `stream` its cudaStream_t or NULL. The
  * scratch the kernel needs lives in a fixed array inside the library (about 4.1 MiB per GPU that
  * loads it). Limit: n_tokens * n_in <= 1 048 576, n_in % 256 == 0; beyond it the call returns -3.
- * The first call on a device resolves the array's address: make it before any stream capture.
+ * The first call on a device resolves the array's address on that device (a host-side lookup, no allocation).
  * All calls share the array, so calls that overlap on the GPU race; nothing needs clearing between
  * calls. The work is enqueued on `stream`; the call does not wait for it. */
 int retro_b200_gemm_q4k_noalloc(const uint8_t * d_w, uint32_t n_out, uint32_t n_in, const float * d_x, uint32_t n_tokens, float * d_y,

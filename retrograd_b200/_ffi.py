@@ -262,7 +262,8 @@ SYMBOLS = {
     "retro_b200_engine_blocks": (C.c_int, [C.c_void_p, _P(C.c_uint64), _P(C.c_uint64)]),
     "retro_b200_engine_last_step_stats": (C.c_int, [C.c_void_p, _P(C.c_float), _P(C.c_uint64)]),
     "retro_b200_op_gemm": (C.c_int, [C.c_uint32, _P(C.c_uint8), C.c_uint32, C.c_uint32, _P(C.c_float), C.c_uint32, _P(C.c_float), C.c_int, C.c_uint32, _P(C.c_float)]),
-    "retro_b200_op_gemm_mxfp4_grouped": (C.c_int, [_P(C.c_uint8), C.c_uint32, C.c_uint32, C.c_uint32, _P(C.c_float), _P(C.c_int32), _P(C.c_float)]),
+    "retro_b200_op_gemm_mxfp4_grouped": (C.c_int, [_P(C.c_uint8), C.c_uint32, C.c_uint32, C.c_uint32, _P(C.c_float), _P(C.c_int32), _P(C.c_float), C.c_uint32,
+                                                   _P(C.c_float)]),
     "retro_b200_gemm_q4k_noalloc": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]),
     "retro_b200_engine_last_step_io": (C.c_int, [C.c_void_p, _P(C.c_uint64), _P(C.c_uint64)]),
     "retro_b200_grammar_check": (C.c_int, [C.c_char_p, C.c_char_p, _P(C.c_int)]),

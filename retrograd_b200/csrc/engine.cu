@@ -774,6 +774,44 @@ void Engine::ep_init(int rank, int world, const void * unique_id_128) {
     ep_offsets_l_.ensure(hp.n_expert + 1);
     ep_flags_.ensure((size_t)world + 1);
     RB_CUDA(cudaMallocHost(reinterpret_cast<void **>(&h_ep_offsets_), ((size_t)world * (hp.n_expert + 1) + world + 1) * sizeof(int32_t)));
+    if (world > 1) ep_keep_local_experts();
+}
+
+// From here on this rank serves experts [rank * E / world, (rank + 1) * E / world) only: every bank is replaced by
+// a copy of that range and the full bank is freed, so the experts' footprint is divided by the world size like
+// their weight stream. The views keep indexing by GLOBAL expert id: their base address is moved back by the
+// bytes of the experts in front of the range. An expert outside the range never has rows on this rank (the
+// exchange plan sends every pair to its expert's owner), and every grouped kernel returns on an empty row range
+// before it forms a weight address.
+void Engine::ep_keep_local_experts() {
+    Model & m = *model;
+    const uint32_t per = m.hp.n_expert / (uint32_t)ep_world_, first = (uint32_t)ep_rank_ * per;
+    RB_CUDA(cudaStreamSynchronize(stream));
+    auto keep = [&](WeightView & w, uint64_t stride) {
+        const bool tiled_only = w.type == GGML_MXFP4 && w.tiled && !w.data;
+        const uint8_t * old = tiled_only ? w.tiled : w.data;
+        const size_t per_expert = tiled_only ? mxfp4_tiled_bytes(1, w.n_out, w.n_in) : (size_t)stride;
+        if (!old || per_expert == 0) return;
+        void * local = nullptr;
+        RB_CUDA(cudaMalloc(&local, align_up(per * per_expert, 256)));
+        RB_CUDA(cudaMemcpy(local, old + (size_t)first * per_expert, per * per_expert, cudaMemcpyDeviceToDevice));
+        auto it = std::find(m.allocations.begin(), m.allocations.end(), (void *)old);
+        if (it != m.allocations.end()) {
+            RB_CUDA(cudaFree(*it));
+            *it = local;
+        } else {
+            m.allocations.push_back(local);
+        }
+        const uint8_t * biased = reinterpret_cast<const uint8_t *>(reinterpret_cast<uintptr_t>(local) - (uintptr_t)first * per_expert);
+        (tiled_only ? w.tiled : w.data) = biased;
+        m.weight_bytes -= (size_t)(m.hp.n_expert - per) * per_expert;
+        ep_local_bank_bytes_ += per * per_expert;
+    };
+    for (LayerWeights & lw : m.layers) {
+        keep(lw.gate_exps, lw.gate_stride);
+        keep(lw.up_exps, lw.up_stride);
+        keep(lw.down_exps, lw.down_stride);
+    }
 }
 
 // Rows [begin[p], begin[p] + count[p]) of `send` go to rank p, rows from rank p land at recv_begin[p]. Both

@@ -306,6 +306,8 @@ public:
     // all ranks must run the same number of steps (a rank without rows calls ep_idle_step()).
     void ep_init(int rank, int world, const void * unique_id_128);
     void ep_idle_step();
+    void ep_keep_local_experts();
+    size_t ep_local_bank_bytes_ = 0;     // bytes of expert banks this rank holds once it joined an expert-parallel group
     int ep_world() const { return ep_world_; }
 
 private:

@@ -180,7 +180,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_mxfp4_tc5_kernel(const uint8_
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue
-        const uint32_t idesc = tc5::instr_desc_f16(BM, BN);
+        // a tile with fewer pairs than columns (the usual case in decode steps: a few dozen pairs per expert) only
+        // pays for the columns it has, in whole MMA widths of 16
+        const uint32_t idesc = tc5::instr_desc_f16(BM, min(BN, (n_rows - t0 + 15) & ~15));
         const uint64_t desc0 = tc5::smem_desc_sw128(smem_base);
         const uint32_t desc_lo0 = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
         const uint32_t d_acc = tmem_base, a_slot0 = tmem_base + TMEM_A;
@@ -217,6 +219,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_mxfp4_tc5_kernel(const uint8_
             const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + colhalf * 64;
 #pragma unroll
             for (int c = 0; c < 4; c += 2) {
+                if (t0 + colhalf * 64 + c * 16 >= n_rows) break;      // warp-uniform: columns past the expert's pairs were never computed
                 float v[16], w[16];
                 tc5::tmem_ld16x2(t_acc + c * 16, t_acc + (c + 1) * 16, v, w);
                 if (o < n_out) {

@@ -13,15 +13,17 @@
 // is read back from tensor memory until the row is done.
 //
 // One CTA: 128 weight rows x BN tokens (128, or 256 when the grid still fills the GPU). Warps: two producer
-// groups of four warps that take pipeline stages in turn - thread p reads the two blocks (68 bytes) of row p
-// for the stage's 64 columns straight from the GGUF row layout, decodes them and stores w_hi and w_lo into lane p
-// of the stage's two A slots in TENSOR MEMORY; one thread of the group fetches the activation tiles (hi and lo)
+// groups of four warps that take pipeline stages in turn - a warp reads the two blocks (68 bytes) of each of its 32
+// rows for the stage's 64 columns straight from the GGUF row layout (coalesced along the rows, then a row per
+// lane through shared memory), thread p decodes row p and stores w_hi and w_lo into lane p of the stage's two A
+// slots in TENSOR MEMORY; one thread of the group fetches the activation tiles (hi and lo)
 // with TMA -, eight epilogue warps, and one warp that walks the pipeline with warp-uniform values and issues
-// the MMAs from an elected lane. Steps of at most 64 tokens issue N = 64 MMAs on the same tiles.
+// the MMAs from an elected lane. A tile with fewer tokens than columns issues narrower MMAs (N in steps of 16).
 // Tensor memory: the accumulator (BN columns), then 64 columns per stage (w_hi | w_lo, 128 rows x 64 f16 each).
 // Every mbarrier wait is bounded; a wait that gives up raises the error flag and the CTA frees its tensor memory.
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "kernels.cuh"
@@ -34,17 +36,28 @@ namespace rb200 {
 namespace {
 
 constexpr int BM = 128;
-constexpr int GROUPS = 2;
+#ifndef RB200_Q8_TC5_GROUPS
+#define RB200_Q8_TC5_GROUPS 2
+#endif
+constexpr int GROUPS = RB200_Q8_TC5_GROUPS;        // producer groups of four warps
 constexpr int EPI_WARP0 = 4 * GROUPS, MMA_WARP = EPI_WARP0 + 8;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int TMEM_COLS = 512;
+
+// A producer warp reads the 32 x 68 bytes of its rows' stage segments as 544 consecutive-per-row words - lane after
+// lane along a row, so a load instruction touches two or three rows instead of 32 - and hands every lane its own
+// row's 17 words through this much shared memory (a row per lane straight from global memory costs one memory
+// wavefront per lane and instruction: measured 2400 cycles per stage, against 850 of tensor work).
+constexpr int kRowExchangeBytes = 32 * 17 * 4;
 
 template <int BN> struct Shape {
     static constexpr int STAGES = BN == 256 ? 3 : 5;
     static constexpr int B_BYTES = BN * 128;                 // BN tokens x 64 f16, 128-byte swizzled rows
     static constexpr int STAGE_BYTES = 2 * B_BYTES;          // activation tiles hi and lo
     static constexpr int TMEM_A = BN;                        // the accumulator at column 0, then the A slots
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int ROWS_OFF = STAGES * STAGE_BYTES + BAR_BYTES;          // the producer warps' row exchange areas
+    static constexpr int SMEM_BYTES = ROWS_OFF + 4 * GROUPS * kRowExchangeBytes + 1024 /* alignment slack */;
     static_assert(TMEM_A + STAGES * 64 <= TMEM_COLS, "tensor memory: accumulator and A slots");
 };
 
@@ -78,8 +91,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_0_tc5_kernel(const uint8_t
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.y * BM, t0 = blockIdx.x * BN;   // token tiles vary fastest: CTAs in flight share a weight tile in L2
     const int n_it = n_in / 64;
-    // at most 64 tokens in this tile: the MMAs cover 64 columns of the same tiles
-    const int mma_n = (BN == 128 && T - t0 <= 64) ? 64 : BN;
+    // a tile with fewer tokens than columns only pays for the columns it has, in whole MMA widths of 16
+    const int mma_n = min(BN, (T - t0 + 15) & ~15);
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -100,17 +113,30 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_0_tc5_kernel(const uint8_t
         // ------------------------------------------------------------------ producers
         const int group = warp >> 2;
         const int p = tid & 127;                       // weight row of this thread
-        const bool row_ok = m0 + p < n_out;
-        const uint8_t * row_base = W + (size_t)(row_ok ? m0 + p : 0) * row_bytes;
         // The stage's two blocks of a row are 68 consecutive bytes on a 4-byte boundary: words 0..8 hold the first
         // block (scale in the low half of word 0), the high half of word 8 the second block's scale, words 9..16 its
         // values. They are prefetched two own stages ahead, so the HBM latency never holds a pipeline slot.
         struct Raw { uint32_t w[17]; };
+        // word i of the warp's 544 (i = 32 k + lane) is word i % 17 of row i / 17
+        const uint8_t * warp_rows = W + (size_t)(m0 + (warp & 3) * 32) * row_bytes;
+        const int rows_left = n_out - (m0 + (warp & 3) * 32);
+        uint32_t * exchange = reinterpret_cast<uint32_t *>(smem + S::ROWS_OFF + warp * kRowExchangeBytes);
         auto prefetch = [&](int it, Raw & raw) {
             if (it >= n_it) return;
-            const uint32_t * seg = reinterpret_cast<const uint32_t *>(row_base + (size_t)it * 68);
 #pragma unroll
-            for (int i = 0; i < 17; ++i) raw.w[i] = row_ok ? seg[i] : 0u;
+            for (int k = 0; k < 17; ++k) {
+                const int i = k * 32 + lane, r = (i * 61681) >> 20, j = i - r * 17;      // r = i / 17 for i < 544
+                raw.w[k] = r < rows_left ? *reinterpret_cast<const uint32_t *>(warp_rows + (size_t)r * row_bytes + (size_t)it * 68 + j * 4) : 0u;
+            }
+        };
+        // the lane's own row out of the warp's words
+        auto own_row = [&](Raw & raw) {
+#pragma unroll
+            for (int k = 0; k < 17; ++k) exchange[k * 32 + lane] = raw.w[k];
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 17; ++k) raw.w[k] = exchange[lane * 17 + k];
+            __syncwarp();
         };
         auto decode_store = [&](const uint32_t (&q)[8], uint32_t d_bits, uint32_t slot_hi) {
             const uint32_t dd = d_bits | (d_bits << 16);
@@ -127,8 +153,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_0_tc5_kernel(const uint8_t
                 lo[2 * i] = *reinterpret_cast<const uint32_t *>(&la);
                 lo[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&lb);
             }
-            tc5::tmem_st16(slot_hi, hi);
-            tc5::tmem_st16(slot_hi + 32, lo);
+            tc5::tmem_st16_nowait(slot_hi, hi);
+            tc5::tmem_st16_nowait(slot_hi + 32, lo);
         };
         // returns false when the pipeline was aborted
         auto produce = [&](int it, Raw & raw) -> bool {
@@ -147,6 +173,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_0_tc5_kernel(const uint8_t
                 }
             }
             const uint32_t a_slot = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + S::TMEM_A + stage * 64;
+            own_row(raw);
             uint32_t q[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) q[i] = __byte_perm(raw.w[i], raw.w[i + 1], 0x5432);
@@ -155,6 +182,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q8_0_tc5_kernel(const uint8_t
             for (int i = 0; i < 8; ++i) q[i] = raw.w[9 + i];
             decode_store(q, raw.w[8] >> 16, a_slot + 16);
             prefetch(it + 2 * GROUPS, raw);
+            tc5::tmem_wait_st();                // the stage's four stores, before the barrier says they are there
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive(full_bar(stage));
@@ -290,12 +318,18 @@ void launch_gemm_q8_0_tc5(const WeightView & w, const SplitAct & x, int n_tokens
                           int ldr, int * error_flag, int n_sm, cudaStream_t stream) {
     if (n_tokens <= 0) return;
     // 256-token tiles halve the decode work per product, but the grid is whole waves of one CTA per SM: the form
-    // with the shorter estimated time wins (a stage of 64 columns is twelve MMAs: about 1536 cycles at N = 256,
-    // 852 at N = 128)
+    // with the shorter estimated time wins (measured per 64-column stage: about 1800 cycles at N = 256, where the
+    // twelve MMAs take 1536, and 1425 at N = 128, where the producers set the pace)
     const int row_tiles = (int)((w.n_out + BM - 1) / BM);
     const long long waves_wide = ((long long)row_tiles * ((n_tokens + 255) / 256) + n_sm - 1) / n_sm;
     const long long waves_narrow = ((long long)row_tiles * ((n_tokens + 127) / 128) + n_sm - 1) / n_sm;
-    const bool wide = n_tokens > 128 && waves_wide * 1536 < waves_narrow * 852;
+    bool wide = n_tokens > 128 && waves_wide * 1800 < waves_narrow * 1425;
+    static const int forced = [] {          // RB200_Q8_TC5_TILE=128|256 pins the form (measurements)
+        const char * env = std::getenv("RB200_Q8_TC5_TILE");
+        return env ? std::atoi(env) : 0;
+    }();
+    if (forced == 128) wide = false;
+    if (forced == 256 && n_tokens > 128) wide = true;
     if (wide) {
         if (residual) launch_one<256, true>(w, x, n_tokens, y, ldy, bias, residual, ldr, error_flag, stream);
         else launch_one<256, false>(w, x, n_tokens, y, ldy, bias, nullptr, 0, error_flag, stream);

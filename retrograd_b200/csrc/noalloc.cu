@@ -64,7 +64,7 @@ extern "C" {
 //   with -3 and a message, nothing is launched. d_w must be 16-byte aligned (the kernel reads
 //   weight blocks as 16-byte words); a misaligned pointer is refused the same way.
 // - The first call on a device resolves the scratch array's address for that device (with that
-//   device current). Make that first call before starting any stream capture.
+//   device current): a host-side symbol lookup, no allocation.
 // - Every call on a device uses the same scratch array. Nothing in it has to start at zero: a call
 //   rewrites every byte it later reads. For the same reason two calls whose work overlaps on
 //   the GPU (different streams, no ordering between them) race on it - order them.

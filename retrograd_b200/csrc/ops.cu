@@ -154,9 +154,10 @@ int retro_b200_op_gemm(uint32_t ggml_type, const uint8_t * w, uint32_t n_out, ui
 
 // The grouped MXFP4 expert GEMM on tcgen05: `banks` holds n_expert matrices of n_out rows x n_in MXFP4 weights
 // (17-byte blocks, rows consecutive), x the n_rows = offsets[n_expert] activation rows sorted by expert, offsets
-// each expert's first row. y[r][o] = sum_k deq(bank[e(r)])[o][k] x[r][k].
+// each expert's first row. y[r][o] = sum_k deq(bank[e(r)])[o][k] x[r][k]. `iters` further launches are timed
+// (CUDA events on the launching stream, L2 flushed before each); *out_ms is their mean.
 int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, uint32_t n_out, uint32_t n_in, const float * x,
-                                     const int32_t * offsets, float * y) {
+                                     const int32_t * offsets, float * y, uint32_t iters, float * out_ms) {
     return boundary([&]() -> int {
         if (!banks || !x || !y || !offsets || n_expert == 0 || n_out == 0 || n_in == 0 || n_in % 64 != 0) {
             set_error("op_gemm_mxfp4_grouped: bad arguments");
@@ -203,6 +204,28 @@ int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, u
             return STATUS_INVALID_ARGUMENT;
         }
         launch_gemm_mxfp4_tc5_grouped(wv, (int)n_expert, d_off.ptr, xs.view, max_rows, dy.ptr, (int)n_out, flag.ptr, stream);
+        // `iters` timed launches, each behind a write of a buffer larger than L2
+        float total_ms = 0.f;
+        if (iters) {
+            DeviceBuffer<uint8_t> flush_buf;
+            flush_buf.ensure((size_t)256 << 20);
+            cudaEvent_t e0, e1;
+            RB_CUDA(cudaEventCreate(&e0));
+            RB_CUDA(cudaEventCreate(&e1));
+            for (uint32_t i = 0; i < iters; ++i) {
+                RB_CUDA(cudaMemsetAsync(flush_buf.ptr, (int)i, (size_t)256 << 20, stream));
+                RB_CUDA(cudaEventRecord(e0, stream));
+                launch_gemm_mxfp4_tc5_grouped(wv, (int)n_expert, d_off.ptr, xs.view, max_rows, dy.ptr, (int)n_out, flag.ptr, stream);
+                RB_CUDA(cudaEventRecord(e1, stream));
+                RB_CUDA(cudaStreamSynchronize(stream));
+                float one = 0.f;
+                cudaEventElapsedTime(&one, e0, e1);
+                total_ms += one;
+            }
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+        }
+        if (out_ms) *out_ms = iters ? total_ms / iters : 0.f;
         int h_flag = 0;
         RB_CUDA(cudaMemcpyAsync(y, dy.ptr, (size_t)n_rows * n_out * 4, cudaMemcpyDeviceToHost, stream));
         RB_CUDA(cudaMemcpyAsync(&h_flag, flag.ptr, sizeof(int), cudaMemcpyDeviceToHost, stream));

@@ -243,17 +243,19 @@ def op_gemm(ggml_type: int, w_bytes, n_out: int, n_in: int, x, path: int = 0, it
     return y, ms.value
 
 
-def op_gemm_mxfp4_grouped(banks, n_expert: int, n_out: int, n_in: int, x, offsets):
-    """The grouped MXFP4 expert GEMM through retro_b200_op_gemm_mxfp4_grouped. Returns y [n_rows, n_out]."""
+def op_gemm_mxfp4_grouped(banks, n_expert: int, n_out: int, n_in: int, x, offsets, iters: int = 0):
+    """The grouped MXFP4 expert GEMM through retro_b200_op_gemm_mxfp4_grouped. Returns y [n_rows, n_out], or
+    (y, ms per launch) when `iters` timed launches are asked for."""
     lib = _ffi.load_library()
     w = np.ascontiguousarray(np.frombuffer(banks, dtype=np.uint8) if not isinstance(banks, np.ndarray) else banks)
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, n_in)
     off = np.ascontiguousarray(offsets, dtype=np.int32)
     assert off.shape == (n_expert + 1,) and off[-1] == x.shape[0]
     y = np.zeros((x.shape[0], n_out), dtype=np.float32)
+    ms = C.c_float()
     _check(lib.retro_b200_op_gemm_mxfp4_grouped(w.ctypes.data_as(C.POINTER(C.c_uint8)), n_expert, n_out, n_in, x.ctypes.data_as(C.POINTER(C.c_float)),
-                                                off.ctypes.data_as(C.POINTER(C.c_int32)), y.ctypes.data_as(C.POINTER(C.c_float))))
-    return y
+                                                off.ctypes.data_as(C.POINTER(C.c_int32)), y.ctypes.data_as(C.POINTER(C.c_float)), iters, C.byref(ms)))
+    return (y, ms.value) if iters else y
 
 
 def reasoning_check(start, ends, budget: int, n_prompt_tail: int, prompt, sampled, incomplete=()):

@@ -41,7 +41,7 @@ def _run(rb, engine, rank: int, idle_last: bool, expert_parallel: bool):
 
 def plain_vs_expert_parallel(rb, rank: int, world: int, unique_id: bytes, workdir: Path) -> dict:
     """Runs both passes on this rank (collective over the `world` ranks that share `unique_id`); returns
-    {"steps": compared steps, "bit_exact": bool} and leaves the expert-parallel engine closed."""
+    {"steps": compared steps, "bit_exact": bool, "footprint_split": bool} and leaves the expert-parallel engine closed."""
     model = Path(workdir) / f"ep_check_rank{rank}.gguf"
     rb.synth_gguf(model, **SPEC)
     cfg = rb.EngineConfig(n_ctx=512, n_seq_max=4, n_batch=64, n_ubatch=64)
@@ -50,9 +50,15 @@ def plain_vs_expert_parallel(rb, rank: int, world: int, unique_id: bytes, workdi
     want = _run(rb, plain, rank, idle_last, expert_parallel=False)
     plain.close()
     engine = rb.Engine(str(model), cfg)
+    banks = sum(b["n_bytes"] for b in engine.expert_banks())
+    before = engine.memory_report()["model_weight_bytes"]
     engine.ep_init(rank, world, unique_id)
+    # the rank now holds its own experts only: (world - 1) / world of the banks' bytes are gone (the banks are held
+    # in the format's own bytes or re-coded at up to twice that, hence the bounds)
+    freed = before - engine.memory_report()["model_weight_bytes"]
+    footprint_split = world == 1 or banks * (world - 1) / world * 0.95 <= freed <= 2.1 * banks
     got = _run(rb, engine, rank, idle_last, expert_parallel=True)
     equal = len(got) == len(want)
     for (t0, l0, x0), (t1, l1, x1) in zip(want, got):
         equal = equal and t0 == t1 and l0 == l1 and all(np.array_equal(a, b) for a, b in zip(x0, x1))
-    return {"steps": len(got), "bit_exact": bool(equal), "engine": engine}
+    return {"steps": len(got), "bit_exact": bool(equal), "footprint_split": bool(footprint_split), "engine": engine}

@@ -5,10 +5,12 @@ profiler captures of a small case.
 
     python -m retrograd_b200.kernel_cases attention --mode decode --seqs 256 --ctx 1024 --iters 4
 
+    python -m retrograd_b200.kernel_cases moe --experts 32 --n-out 2880 --n-in 2880 --tokens 2048 --iters 5
+
 `--path`: 0 engine's choice, 1 f32 row kernel, 3 exact
 tensor-core kernel (mma.sync), 4 exact tcgen05 kernel, 5 exact weight-streaming kernel (at most 8 tokens).
 Operands smaller than 256 MB are timed with a write of a buffer larger than L2 before every launch. Weights are random Q4_K blocks (scales pinned to small f16 values), the
-activations N(0, 1). `--type q8_0` runs the Q8_0 kernels (paths 1 and 5). Prints the mean device time per launch and the rates derived from it.
+activations N(0, 1). `--type q8_0` runs the Q8_0 kernels (paths 1, 3, 4 and 5). Prints the mean device time per launch and the rates derived from it.
 """
 from __future__ import annotations
 
@@ -17,7 +19,7 @@ import json
 
 import numpy as np
 
-from . import op_gemm
+from . import op_gemm, op_gemm_mxfp4_grouped
 
 
 def random_q4k(rng: np.random.Generator, n_out: int, n_in: int) -> np.ndarray:
@@ -33,6 +35,31 @@ def random_q8_0(rng: np.random.Generator, n_out: int, n_in: int) -> np.ndarray:
     raw = rng.integers(0, 256, (blocks, 34), dtype=np.uint8)
     raw[:, 0:2] = np.frombuffer(np.float16(2.0 ** -9).tobytes(), dtype=np.uint8)
     return raw.reshape(-1)
+
+
+def random_mxfp4(rng: np.random.Generator, n_rows: int, n_in: int) -> np.ndarray:
+    blocks = n_rows * n_in // 32
+    raw = rng.integers(0, 256, (blocks, 17), dtype=np.uint8)
+    raw[:, 0] = rng.integers(116, 124, blocks, dtype=np.uint8)       # block scales 2^-11 .. 2^-4
+    return raw.reshape(-1)
+
+
+def moe_case(args) -> None:
+    """The grouped MXFP4 expert GEMM alone: `--experts` banks of n_out x n_in, `--tokens` (token, expert) pairs spread
+    over the experts as a routed step would (multinomial with unequal shares)."""
+    rng = np.random.default_rng(args.seed)
+    banks = random_mxfp4(rng, args.experts * args.n_out, args.n_in)
+    shares = rng.dirichlet(np.full(args.experts, 4.0))
+    counts = rng.multinomial(args.tokens, shares)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    x = rng.normal(0, 1, (args.tokens, args.n_in)).astype(np.float32)
+    _, ms = op_gemm_mxfp4_grouped(banks, args.experts, args.n_out, args.n_in, x, offsets, iters=args.iters)
+    flops = 2.0 * args.tokens * args.n_in * args.n_out
+    weight_bytes = args.experts * args.n_out * args.n_in * 17 // 32
+    print(json.dumps({
+        "kernel": "gemm_mxfp4_grouped", "experts": args.experts, "n_out": args.n_out, "n_in": args.n_in, "pairs": args.tokens,
+        "pairs_per_expert": [int(c) for c in counts], "ms_per_launch": ms, "tflops": flops / ms / 1e9, "weight_gbs": weight_bytes / ms / 1e6,
+    }))
 
 
 def attention_case(args) -> None:
@@ -96,7 +123,8 @@ def attention_case(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "moe"])
+    ap.add_argument("--experts", type=int, default=32, help="moe: expert banks")
     ap.add_argument("--seqs", type=int, default=64, help="attention: sequences resident")
     ap.add_argument("--ctx", type=int, default=2048, help="attention: tokens resident per sequence before the measured steps")
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
@@ -111,6 +139,9 @@ def main() -> None:
     args = ap.parse_args()
     if args.kernel == "attention":
         attention_case(args)
+        return
+    if args.kernel == "moe":
+        moe_case(args)
         return
     rng = np.random.default_rng(args.seed)
     w = random_q4k(rng, args.n_out, args.n_in) if args.type == "q4_k" else random_q8_0(rng, args.n_out, args.n_in)

@@ -34,6 +34,7 @@ def _rank_main(rank: int, world: int, workdir: Path) -> None:
     result = plain_vs_expert_parallel(rb, rank, world, id_path.read_bytes(), workdir)
     engine = result["engine"]
     assert result["bit_exact"], "expert-parallel results differ from the plain engine's"
+    assert result["footprint_split"], "the rank still holds other ranks' expert banks"
     # A plan refused on one rank: rank 1 submits a row in a slot the context does not have. It gets its own -3,
     # rank 0 (whose plan is fine) gets a runtime error instead of waiting for a partner that never comes, nothing
     # of rank 0's step becomes resident, and the next common step runs as usual.
