@@ -679,10 +679,10 @@ def main():
                 "kernel": "dequant-fused weight-streaming GEMM (all launches of the timed region)"}
     elif top == "gemm":
         achieved = gemm_flops / (profile["gemm"]["ms"] * 1e-3) / 1e12
-        # DRAM traffic per launch: the capture of the tcgen05 kernel at 2048 tokens moved 320 MB for 335 MB of
+        # DRAM traffic per launch: the capture of the tcgen05 kernel at 2048 tokens moved 314 MB for 335 MB of
         # algorithmic bytes (profiles/gemm_q4k_tc5_28672x4096_2048tok.md); traffic grows with the tokens and rows
         roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
-                "traffic": gemm_bytes / max(profile["gemm"]["launches"], 1) * 320.0 / 335.0,
+                "traffic": gemm_bytes / max(profile["gemm"]["launches"], 1) * 314.0 / 334.6,
                 "traffic_source": "algorithmic bytes per launch x the DRAM/algorithmic ratio of the one-launch ncu capture in profiles/",
                 "kernel": "dequant-fused weight GEMM (all launches of the timed region)"}
     else:

@@ -429,6 +429,13 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     attn_mma_ = attention_mma_supported((int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)kBlockTokens);
     if (const char * env = std::getenv("RB200_ATTENTION")) attn_mma_ = attn_mma_ && std::string(env) != "ref";
     attn_tile_tokens_ = attn_mma_ ? kAttentionTileRows / (int)(hp.n_head / hp.n_head_kv) : 64;
+    // prefill tiles on tcgen05 with TMA-staged K/V (RB200_ATTN_TC5=0: the mma.sync tile kernel)
+    attn_tc5_ = attn_mma_;
+    if (const char * env = std::getenv("RB200_ATTN_TC5")) attn_tc5_ = attn_tc5_ && std::string(env) != "0";
+    if (attn_tc5_) {
+        attention_maps_encode(attn_maps_, kcache_.ptr, vcache_.ptr, (int)hp.head_dim, (uint64_t)hp.n_layer * (kv_layer_stride_ / hp.head_dim));
+        attn_tc5_ = attention_tc5_supported((int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)kBlockTokens, attn_maps_);
+    }
 
     x_.ensure(T * hp.d);
     xn_.ensure(T * hp.d);
@@ -1421,8 +1428,12 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                                               maps.tok_pos_min, att_.ptr, dq, attn_splits, attn_scratch_.ptr, small_stream, nullptr);
                      RB_CUDA(cudaEventRecord(ev_join_, side_stream_));
                  }
-                 if (any_wide_item) launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
-                                                         maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, true, stream);
+                 if (any_wide_item && attn_tc5_)
+                     launch_attention_tc5(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, attn_maps_, maps.attn_items, n_attn_items, maps.tok_slot,
+                                          maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, true, device_error_.ptr, stream);
+                 else if (any_wide_item)
+                     launch_attention_mma(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot, maps.tok_pos,
+                                          maps.tok_pos_min, att_.ptr, dq, true, stream);
                  if (any_mid_item) launch_attention_decode(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot,
                                                            maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, use_decode8 ? 8 : 0, stream);
                  if (n_small_items && !overlap) launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,

@@ -400,6 +400,8 @@ private:
     const int32_t * cur_tok_adapter_ = nullptr;
     bool cur_any_adapter_ = false;
     bool attn_mma_ = false;
+    bool attn_tc5_ = false;             // prefill tiles on the tcgen05 kernel (needs the K/V tensor maps)
+    AttentionMaps attn_maps_;
     int attn_tile_tokens_ = 64;
 };
 

@@ -17,8 +17,8 @@
 // One CTA: 128 weight rows of one expert x 128 of its pairs. Warp roles as in the Q4_K kernel: three producer
 // groups of four warps (thread p decodes the 64 weights of row p into lane p of the stage's A slot in tensor
 // memory; one thread fetches the activation tiles with TMA), eight epilogue warps, one issuing warp that walks
-// the pipeline with warp-uniform values and an elected-lane predicate. A CTA whose token tile lies past its
-// expert's pairs leaves at once. An element's arithmetic does not depend on the tile or the column it lands in,
+// the pipeline with warp-uniform values and an elected-lane predicate. The grid's x dimension numbers the
+// (expert, token tile) items; a CTA finds its own in the offsets array. An element's arithmetic does not depend on the tile or the column it lands in,
 // so results do not depend on how the pairs are grouped (nor on the expert-parallel world size).
 // Every mbarrier wait is bounded; a wait that gives up raises the error flag and the CTA frees its tensor memory.
 
@@ -41,6 +41,7 @@ constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_A = 128;                       // the accumulator at column 0, then the A slots of 32 columns
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int kMaxGroups = 1024;                  // experts per launch
 
 // grid (column groups of 64, row tiles, experts), 128 threads: thread p moves the two blocks of row p
 __global__ void mxfp4_retile_kernel(const uint8_t * __restrict__ bank, uint32_t n_out, uint32_t n_in, uint8_t * __restrict__ tiled) {
@@ -97,13 +98,31 @@ __device__ __forceinline__ void decode_block(const uint4 & q, __half2 scale, uin
     }
 }
 
-__global__ void __launch_bounds__(THREADS, 1) gemm_mxfp4_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, const int32_t * __restrict__ offsets,
-                                                                    const __grid_constant__ SplitAct X, float * __restrict__ Y, int ldy,
-                                                                    int * __restrict__ error_flag) {
-    const int expert = blockIdx.z;
-    const int row0 = offsets[expert], n_rows = offsets[expert + 1] - row0;
-    const int t0 = blockIdx.x * BN;
-    if (t0 >= n_rows) return;                       // this expert has fewer pairs: nothing was set up yet
+__global__ void __launch_bounds__(THREADS, 1) gemm_mxfp4_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int n_groups,
+                                                                    const int32_t * __restrict__ offsets, const __grid_constant__ SplitAct X,
+                                                                    float * __restrict__ Y, int ldy, int * __restrict__ error_flag) {
+    // blockIdx.x numbers the (expert, token tile) items expert by expert; the grid holds an upper bound of them
+    // (every expert may end in a partial tile), so only the few CTAs past the last item leave empty-handed. A
+    // grid of (most pairs of any expert) x experts would be mostly CTAs that find nothing to do, each of which
+    // still has to wait for a whole SM's shared memory before it can say so.
+    __shared__ int32_t sh_off[kMaxGroups + 1];
+    for (int i = threadIdx.x; i <= n_groups; i += THREADS) sh_off[i] = offsets[i];
+    __syncthreads();
+    int expert = -1, t0 = 0;
+    {
+        int item = blockIdx.x;
+        for (int e = 0; e < n_groups; ++e) {
+            const int tiles = (sh_off[e + 1] - sh_off[e] + BN - 1) / BN;
+            if (item < tiles) {
+                expert = e;
+                t0 = item * BN;
+                break;
+            }
+            item -= tiles;
+        }
+    }
+    if (expert < 0) return;
+    const int row0 = sh_off[expert], n_rows = sh_off[expert + 1] - row0;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -267,14 +286,14 @@ bool gemm_mxfp4_tc5_supported(const WeightView & w, const SplitAct & x) {
     return w.type == GGML_MXFP4 && w.tiled && w.n_in % 64 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
 }
 
-void launch_gemm_mxfp4_tc5_grouped(const WeightView & w, int n_groups, const int32_t * group_offsets, const SplitAct & x, int max_group_rows, float * y,
+void launch_gemm_mxfp4_tc5_grouped(const WeightView & w, int n_groups, const int32_t * group_offsets, const SplitAct & x, int total_rows, float * y,
                                    int ldy, int * error_flag, cudaStream_t stream) {
     static PerDeviceOnce configured;   // function attributes are per device
     if (configured.first()) cudaFuncSetAttribute(gemm_mxfp4_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (n_groups <= 0 || max_group_rows <= 0) return;
-    const dim3 grid((max_group_rows + BN - 1) / BN, (w.n_out + BM - 1) / BM, n_groups);
+    if (n_groups <= 0 || n_groups > kMaxGroups || total_rows <= 0) return;
+    const dim3 grid((total_rows + BN - 1) / BN + n_groups, (w.n_out + BM - 1) / BM);
     // a plain launch: the CTA reads its expert's offsets (written by the grouping kernel in front of it) before anything else
-    gemm_mxfp4_tc5_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, group_offsets, x, y, ldy, error_flag);
+    gemm_mxfp4_tc5_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, n_groups, group_offsets, x, y, ldy, error_flag);
 }
 
 } // namespace rb200

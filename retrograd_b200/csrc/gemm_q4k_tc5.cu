@@ -413,6 +413,24 @@ bool split_act_encode_maps(SplitAct & s, size_t rows) {
     return true;
 }
 
+bool attention_maps_encode(AttentionMaps & maps, const __half * k, const __half * v, int head_dim, uint64_t rows) {
+    const EncodeFn encode = tensor_map_encoder();
+    maps.valid = 0;
+    if (!encode || !k || !v || head_dim % 64 != 0 || rows == 0 || rows > 0x7fffffffull) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)head_dim * sizeof(__half)};
+    const cuuint32_t box[2] = {64, 16};
+    const cuuint32_t elem[2] = {1, 1};
+    for (int which = 0; which < 2; ++which) {
+        const CUresult r = encode(which ? &maps.v : &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, which ? (void *)v : (void *)k, dims, strides, box, elem,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return false;
+    }
+    maps.valid = 1;
+    return true;
+}
+
 bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x) {
     return w.type == GGML_Q4_K && w.tiled && w.tc5_exact && w.n_in % 256 == 0 && x.hi && x.ld == (int)w.n_in && x.has_maps;
 }

@@ -12,7 +12,7 @@
 // into ONE f32 accumulator that runs over the whole row: no per-block scale is left for an epilogue, so nothing
 // is read back from tensor memory until the row is done.
 //
-// One CTA: 128 weight rows x BN tokens (128, or 256 when the grid still fills the GPU). Warps: two producer
+// One CTA: 128 weight rows x BN tokens (128, or 256 when the grid still fills the GPU). Warps: two or three producer
 // groups of four warps that take pipeline stages in turn - a warp reads the two blocks (68 bytes) of each of its 32
 // rows for the stage's 64 columns straight from the GGUF row layout (coalesced along the rows, then a row per
 // lane through shared memory), thread p decodes row p and stores w_hi and w_lo into lane p of the stage's two A
@@ -36,12 +36,6 @@ namespace rb200 {
 namespace {
 
 constexpr int BM = 128;
-#ifndef RB200_Q8_TC5_GROUPS
-#define RB200_Q8_TC5_GROUPS 2
-#endif
-constexpr int GROUPS = RB200_Q8_TC5_GROUPS;        // producer groups of four warps
-constexpr int EPI_WARP0 = 4 * GROUPS, MMA_WARP = EPI_WARP0 + 8;
-constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int TMEM_COLS = 512;
 
 // A producer warp reads the 32 x 68 bytes of its rows' stage segments as 544 consecutive-per-row words - lane after
@@ -51,6 +45,12 @@ constexpr int TMEM_COLS = 512;
 constexpr int kRowExchangeBytes = 32 * 17 * 4;
 
 template <int BN> struct Shape {
+    // producer groups of four warps: with 128-token tiles the producers set the pace and a third group helps
+    // (0.96 against 1.05 ms on 28 672 x 4096 x 1792); with 256-token tiles the MMAs do, and a third group only
+    // takes issue slots from the issuing warp (0.74 against 0.69 ms)
+    static constexpr int GROUPS = BN == 256 ? 2 : 3;
+    static constexpr int EPI_WARP0 = 4 * GROUPS, MMA_WARP = EPI_WARP0 + 8;
+    static constexpr int THREADS = (MMA_WARP + 1) * 32;
     static constexpr int STAGES = BN == 256 ? 3 : 5;
     static constexpr int B_BYTES = BN * 128;                 // BN tokens x 64 f16, 128-byte swizzled rows
     static constexpr int STAGE_BYTES = 2 * B_BYTES;          // activation tiles hi and lo
@@ -71,12 +71,13 @@ __device__ __forceinline__ void int8x4_to_half2(uint32_t u, __half2 & a, __half2
 }
 
 template <int BN, bool RESIDUAL>
-__global__ void __launch_bounds__(THREADS, 1) gemm_q8_0_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes,
+__global__ void __launch_bounds__(Shape<BN>::THREADS, 1) gemm_q8_0_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int row_bytes,
                                                                    const __grid_constant__ SplitAct X, int T, float * __restrict__ Y, int ldy,
                                                                    const float * __restrict__ bias, const float * __restrict__ residual, int ldr,
                                                                    int * __restrict__ error_flag) {
     using S = Shape<BN>;
     constexpr int STAGES = S::STAGES, B_BYTES = S::B_BYTES, STAGE_BYTES = S::STAGE_BYTES;
+    constexpr int GROUPS = S::GROUPS, EPI_WARP0 = S::EPI_WARP0, MMA_WARP = S::MMA_WARP;
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -283,7 +284,7 @@ void launch_one(const WeightView & w, const SplitAct & x, int n_tokens, float * 
     // earlier kernels drain; every role waits on the device before it touches activations or outputs
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((n_tokens + BN - 1) / BN, (w.n_out + BM - 1) / BM);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(Shape<BN>::THREADS);
     cfg.dynamicSmemBytes = Shape<BN>::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -319,11 +320,11 @@ void launch_gemm_q8_0_tc5(const WeightView & w, const SplitAct & x, int n_tokens
     if (n_tokens <= 0) return;
     // 256-token tiles halve the decode work per product, but the grid is whole waves of one CTA per SM: the form
     // with the shorter estimated time wins (measured per 64-column stage: about 1800 cycles at N = 256, where the
-    // twelve MMAs take 1536, and 1425 at N = 128, where the producers set the pace)
+    // twelve MMAs take 1536, and 1300 at N = 128, where the producers set the pace)
     const int row_tiles = (int)((w.n_out + BM - 1) / BM);
     const long long waves_wide = ((long long)row_tiles * ((n_tokens + 255) / 256) + n_sm - 1) / n_sm;
     const long long waves_narrow = ((long long)row_tiles * ((n_tokens + 127) / 128) + n_sm - 1) / n_sm;
-    bool wide = n_tokens > 128 && waves_wide * 1800 < waves_narrow * 1425;
+    bool wide = n_tokens > 128 && waves_wide * 1800 < waves_narrow * 1300;
     static const int forced = [] {          // RB200_Q8_TC5_TILE=128|256 pins the form (measurements)
         const char * env = std::getenv("RB200_Q8_TC5_TILE");
         return env ? std::atoi(env) : 0;

@@ -595,38 +595,51 @@ __global__ void moe_route_kernel(const float * __restrict__ logits, int n_expert
 }
 
 // The (token, expert) pairs of every expert, in pair order: offsets[n_expert + 1] and sorted[n_pairs].
-// One block of 32 warps; warp w owns experts w, w + 32, ... and walks the pair list 32 pairs at a time: a ballot
-// marks the lanes that hold one of its expert's pairs, and a lane's place among them is a population count, so
-// the order inside an expert stays the pair order. Two such walks (count, then place) with a scan over the
-// experts in between; n_expert <= 1024.
+// One block of 32 warps. The pair list is staged in shared memory 8192 pairs at a time; warp w owns experts
+// w, w + 32, ... and walks the staged pairs 32 at a time: a ballot marks the lanes that hold one of its expert's
+// pairs, and a lane's place among them is a population count, so the order inside an expert stays the pair order.
+// Two such walks (count, then place) with a scan over the experts in between; n_expert <= 1024.
+constexpr int kGroupChunk = 8192;
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t * __restrict__ pair_expert, int n_pairs, int n_expert,
                                                          int32_t * __restrict__ offsets, int32_t * __restrict__ sorted) {
     __shared__ int32_t s_off[1025];
+    __shared__ int32_t s_pairs[kGroupChunk];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const unsigned below = (1u << lane) - 1u;
-    for (int e = warp; e < n_expert; e += 32) {
-        int count = 0;
-        for (int p0 = 0; p0 < n_pairs; p0 += 32) {
-            const int p = p0 + lane;
-            count += __popc(__ballot_sync(0xffffffffu, p < n_pairs && pair_expert[p] == e));
+    for (int i = threadIdx.x; i <= n_expert; i += blockDim.x) s_off[i] = 0;
+    for (int c0 = 0; c0 < n_pairs; c0 += kGroupChunk) {
+        const int n = min(kGroupChunk, n_pairs - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n; i += blockDim.x) s_pairs[i] = pair_expert[c0 + i];
+        __syncthreads();
+        for (int e = warp; e < n_expert; e += 32) {
+            int count = 0;
+            for (int p0 = 0; p0 < n; p0 += 32) count += __popc(__ballot_sync(0xffffffffu, p0 + lane < n && s_pairs[p0 + lane] == e));
+            if (lane == 0) s_off[e + 1] += count;
         }
-        if (lane == 0) s_off[e + 1] = count;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        s_off[0] = 0;
+    if (threadIdx.x == 0)
         for (int i = 0; i < n_expert; ++i) s_off[i + 1] += s_off[i];
-    }
     __syncthreads();
     for (int i = threadIdx.x; i <= n_expert; i += blockDim.x) offsets[i] = s_off[i];
-    for (int e = warp; e < n_expert; e += 32) {
-        int at = s_off[e];
-        for (int p0 = 0; p0 < n_pairs; p0 += 32) {
-            const int p = p0 + lane;
-            const bool mine = p < n_pairs && pair_expert[p] == e;
-            const unsigned hits = __ballot_sync(0xffffffffu, mine);
-            if (mine) sorted[at + __popc(hits & below)] = p;
-            at += __popc(hits);
+    // s_off[e] now walks forward as expert e's pairs are placed (its owner warp is the only writer)
+    for (int c0 = 0; c0 < n_pairs; c0 += kGroupChunk) {
+        const int n = min(kGroupChunk, n_pairs - c0);
+        __syncthreads();
+        if (n_pairs > kGroupChunk || c0 > 0)        // a single chunk is still staged from the counting walk
+            for (int i = threadIdx.x; i < n; i += blockDim.x) s_pairs[i] = pair_expert[c0 + i];
+        __syncthreads();
+        for (int e = warp; e < n_expert; e += 32) {
+            int at = s_off[e];
+            for (int p0 = 0; p0 < n; p0 += 32) {
+                const bool mine = p0 + lane < n && s_pairs[p0 + lane] == e;
+                const unsigned hits = __ballot_sync(0xffffffffu, mine);
+                if (mine) sorted[at + __popc(hits & below)] = c0 + p0 + lane;
+                at += __popc(hits);
+            }
+            __syncwarp();
+            if (lane == 0) s_off[e] = at;
         }
     }
 }

@@ -286,7 +286,7 @@ bool gemm_q4k_tc5_supported(const WeightView & w, const SplitAct & x);
 // The grouped MXFP4 expert GEMM on tcgen05: rows [offsets[g], offsets[g + 1]) of x (the pairs sorted by expert) times
 // expert g's bank (w.tiled, the tiled layout above; w.n_out rows per expert); y rows in the same order.
 bool gemm_mxfp4_tc5_supported(const WeightView & w, const SplitAct & x);
-void launch_gemm_mxfp4_tc5_grouped(const WeightView & w, int n_groups, const int32_t * group_offsets, const SplitAct & x, int max_group_rows, float * y,
+void launch_gemm_mxfp4_tc5_grouped(const WeightView & w, int n_groups, const int32_t * group_offsets, const SplitAct & x, int total_rows, float * y,
                                    int ldy, int * error_flag, cudaStream_t stream);
 // Whether the tcgen05 kernel's arithmetic covers these blocks (host memory, GGUF layout): it carries a row's
 // minimum term as (dmin / d) * m inside the sum that d scales, so a super-block needs d != 0 unless its
@@ -363,6 +363,18 @@ bool attention_mma_supported(int n_head, int n_head_kv, int head_dim, int block_
 // `skip_small`: leave items of at most 16 query vectors to launch_attention_decode.
 void launch_attention_mma(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items, const int32_t * tok_slot,
                           const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, bool skip_small, cudaStream_t stream);
+// The same work on tcgen05 with TMA-staged K/V tiles: tensor maps over the K and V pools (all layers; boxes of
+// one 16-token block x 64 columns, 128-byte swizzle), built once per engine. *error_flag is set to 1 if a bounded
+// pipeline wait gave up.
+struct AttentionMaps {
+    CUtensorMap k, v;
+    int valid = 0;
+};
+bool attention_maps_encode(AttentionMaps & maps, const __half * k, const __half * v, int head_dim, uint64_t rows);
+bool attention_tc5_supported(int n_head, int n_head_kv, int head_dim, int block_tokens, const AttentionMaps & maps);
+void launch_attention_tc5(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const AttentionMaps & maps, const int2 * items, int n_items,
+                          const int32_t * tok_slot, const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, bool skip_small,
+                          int * error_flag, cudaStream_t stream);
 // Items of at most 16 query vectors (decode rows): the CTA's four warps split the KV blocks. Items of
 // at most `min_cols` query vectors are left to launch_attention_decode8.
 void launch_attention_decode(const float * qkv, int ld, int n_head, KvLayout kv, int layer, const int2 * items, int n_items,

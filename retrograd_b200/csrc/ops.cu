@@ -169,8 +169,6 @@ int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, u
             set_error("op_gemm_mxfp4_grouped: the kernel does not cover these operands");
             return STATUS_INVALID_ARGUMENT;
         }
-        int max_rows = 0;
-        for (uint32_t e = 0; e < n_expert; ++e) max_rows = std::max(max_rows, offsets[e + 1] - offsets[e]);
         DeviceBuffer<uint8_t> d_bank, d_tiled;
         DeviceBuffer<float> dx, dy;
         DeviceBuffer<int32_t> d_off;
@@ -203,7 +201,7 @@ int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, u
             set_error("op_gemm_mxfp4_grouped: the kernel does not cover these operands");
             return STATUS_INVALID_ARGUMENT;
         }
-        launch_gemm_mxfp4_tc5_grouped(wv, (int)n_expert, d_off.ptr, xs.view, max_rows, dy.ptr, (int)n_out, flag.ptr, stream);
+        launch_gemm_mxfp4_tc5_grouped(wv, (int)n_expert, d_off.ptr, xs.view, n_rows, dy.ptr, (int)n_out, flag.ptr, stream);
         // `iters` timed launches, each behind a write of a buffer larger than L2
         float total_ms = 0.f;
         if (iters) {
@@ -215,7 +213,7 @@ int retro_b200_op_gemm_mxfp4_grouped(const uint8_t * banks, uint32_t n_expert, u
             for (uint32_t i = 0; i < iters; ++i) {
                 RB_CUDA(cudaMemsetAsync(flush_buf.ptr, (int)i, (size_t)256 << 20, stream));
                 RB_CUDA(cudaEventRecord(e0, stream));
-                launch_gemm_mxfp4_tc5_grouped(wv, (int)n_expert, d_off.ptr, xs.view, max_rows, dy.ptr, (int)n_out, flag.ptr, stream);
+                launch_gemm_mxfp4_tc5_grouped(wv, (int)n_expert, d_off.ptr, xs.view, n_rows, dy.ptr, (int)n_out, flag.ptr, stream);
                 RB_CUDA(cudaEventRecord(e1, stream));
                 RB_CUDA(cudaStreamSynchronize(stream));
                 float one = 0.f;
