@@ -735,11 +735,10 @@ void Engine::moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_
         moe_x_split_.ensure(moe_split_rows_, d);
         moe_h_split_.ensure(moe_split_rows_, ff);
     }
-    moe_xs_.ensure((size_t)n * d);
     moe_gu_s_.ensure((size_t)n * 2 * ff);
     moe_y_s_.ensure((size_t)n * d);
-    launch_ep_gather_rows(rows, ld_rows, gather, gather_div, n, d, moe_xs_.ptr, stream);
-    launch_split_prep(moe_xs_.ptr, d, d, n, moe_x_split_.view, stream);
+    // the pairs' activation rows, gathered into expert order and split in one pass
+    launch_split_prep(rows, ld_rows, d, n, moe_x_split_.view, stream, gather, gather_div);
     if (gemm_mxfp4_tc5_supported(lw.gate_exps, moe_x_split_.view) && gemm_mxfp4_tc5_supported(lw.down_exps, moe_h_split_.view)) {
         launch_gemm_mxfp4_tc5_grouped(lw.gate_exps, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr, 2 * ff, device_error_.ptr, stream);
         launch_gemm_mxfp4_tc5_grouped(lw.up_exps, E, d_offsets, moe_x_split_.view, n, moe_gu_s_.ptr + ff, 2 * ff, device_error_.ptr, stream);
@@ -753,7 +752,7 @@ void Engine::moe_experts_tc(const LayerWeights & lw, const float * rows, int ld_
         launch_gemm_q8_0_exact_grouped(lw.down_exps, lw.down_stride, E, d_offsets, moe_h_split_.view, n, moe_y_s_.ptr, d, stream);
     }
     launch_ep_scatter_rows(moe_y_s_.ptr, gather, n, d, y_out, ld_out, stream);
-    last_launches += 7;
+    last_launches += 6;
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -270,7 +270,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q4k_tc5_kernel(const uint8_t 
             // uniform. (With a single thread inside a divergent branch the issuing thread - not the tensor
             // pipe - set the pace: 0.94 -> 0.81 ms on 28 672 x 4096 x 2048.) Descriptors are built once; a
             // stage costs an add per operand and the MMAs themselves.
-            const uint32_t idesc = tc5::instr_desc_f16(BM, BN);
+            // the step's last token tile only pays for the columns it has, in whole MMA widths of 16
+            const uint32_t idesc = tc5::instr_desc_f16(BM, min(BN, (T - t0 + 15) & ~15));
             const uint64_t desc0 = tc5::smem_desc_sw128(smem_base);
             const uint32_t desc_lo0 = (uint32_t)desc0, desc_hi = (uint32_t)(desc0 >> 32);
             const uint32_t a_slot0 = tmem_base + TMEM_A;

@@ -493,13 +493,15 @@ __global__ void attention_ref_kernel(const float * __restrict__ qkv, int ld, int
 }
 
 // x [t][ld] f32 -> its SplitAct (n a multiple of 32)
-__global__ void split_prep_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split) {
+// Row t of the split form is row gather[t] / gather_div of x (or row t without a gather list).
+__global__ void split_prep_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split, const int32_t * __restrict__ gather, int gather_div) {
     pdl_trigger();      // the next kernel's prologue (weight prefetch) may overlap this kernel
     pdl_wait();
     const int t = blockIdx.y;
+    const int src = gather ? gather[t] / gather_div : t;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    emit_split(split, t, i, x[(size_t)t * ldx + i]);
+    emit_split(split, t, i, x[(size_t)src * ldx + i]);
 }
 
 __global__ void swiglu_kernel(const float * __restrict__ gu, int ld, int ff, float * __restrict__ h, int ldh, SplitAct split) {
@@ -530,13 +532,14 @@ __global__ void swiglu4_kernel(const float * __restrict__ gu, int ld, int ff, fl
     if (split.hi) emit_split4(split, t, i, v, active);
 }
 
-__global__ void split_prep4_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split) {
+__global__ void split_prep4_kernel(const float * __restrict__ x, int ldx, int n, SplitAct split, const int32_t * __restrict__ gather, int gather_div) {
     pdl_trigger();      // the next kernel's prologue (weight prefetch) may overlap this kernel
     pdl_wait();
     const int t = blockIdx.y;
+    const int src = gather ? gather[t] / gather_div : t;
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     const bool active = i < n;
-    const float4 v = active ? *reinterpret_cast<const float4 *>(x + (size_t)t * ldx + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 v = active ? *reinterpret_cast<const float4 *>(x + (size_t)src * ldx + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     emit_split4(split, t, i, v, active);
 }
 
@@ -862,11 +865,12 @@ void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, K
                                                                                                 tok_pos_min, out, ldo, split && kv.head_dim % 32 == 0 ? *split : SplitAct{});
 }
 
-void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream) {
+void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream, const int32_t * gather,
+                       int gather_div) {
     if (n % 32 == 0 && ldx % 4 == 0 && (uintptr_t)x % 16 == 0)
-        launch_pdl(split_prep4_kernel, dim3((n + 1023) / 1024, n_tokens), dim3(256), 0, stream, x, ldx, n, split);
+        launch_pdl(split_prep4_kernel, dim3((n + 1023) / 1024, n_tokens), dim3(256), 0, stream, x, ldx, n, split, gather, gather_div);
     else
-        launch_pdl(split_prep_kernel, dim3((n + 255) / 256, n_tokens), dim3(256), 0, stream, x, ldx, n, split);
+        launch_pdl(split_prep_kernel, dim3((n + 255) / 256, n_tokens), dim3(256), 0, stream, x, ldx, n, split, gather, gather_div);
 }
 
 void launch_swiglu(const float * gu, int ld, int ff, int n_tokens, float * h, int ldh, cudaStream_t stream, const SplitAct * split) {

@@ -355,7 +355,9 @@ bool rope_store_from_partial_supported(const RopeStoreArgs & a, const float * qk
 void launch_attention_ref(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_slot,
                           const int32_t * tok_pos, const int32_t * tok_pos_min, float * out, int ldo, cudaStream_t stream,
                           const SplitAct * split = nullptr);
-void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream);
+// With `gather`: row t of the split form is row gather[t] / gather_div of x.
+void launch_split_prep(const float * x, int ldx, int n, int n_tokens, const SplitAct & split, cudaStream_t stream, const int32_t * gather = nullptr,
+                       int gather_div = 1);
 // Tensor-core paged attention (head_dim 64 or 128, 16-token KV blocks, power-of-two GQA group). Work
 // items hold at most kAttentionTileRows / G tokens.
 constexpr int kAttentionTileRows = 128;

@@ -29,10 +29,12 @@ def test_q4k_gemm_kernels_against_the_oracle(rb, oracle, n_out, n_in, T):
     assert e_rows < 4e-6 and e_exact < 4e-6
 
 
-@pytest.mark.parametrize("n_out,n_in,T", [(128, 256, 128), (256, 512, 130), (200, 768, 33), (512, 2048, 100), (256, 4096, 300), (384, 2816, 40)])
+@pytest.mark.parametrize("n_out,n_in,T", [(128, 256, 128), (256, 512, 130), (200, 768, 33), (512, 2048, 100), (256, 4096, 300), (384, 2816, 40),
+                                          (1536, 1024, 1664), (1500, 1280, 1601)])
 def test_q4k_tcgen05_gemm_against_float64(rb, oracle, n_out, n_in, T):
-    """The tcgen05 / tensor-memory kernel computes the same exact products as the mma.sync one; the last
-    three shapes have few output tiles and run as splits of the reduction (the last with a short final split)."""
+    """The tcgen05 / tensor-memory kernel computes the same exact products as the mma.sync one; shapes three to six
+    have few output tiles and run as splits of the reduction (the sixth with a short final split); the last two have a
+    few more tiles than the GPU has SMs (156 on 148: a second, nearly empty wave), ragged rows and tokens in the second."""
     rng = np.random.default_rng(7 * n_out + T)
     raw = _q4k_matrix(rb, rng, n_out, n_in)
     x = rng.normal(0, 1.5, (T, n_in)).astype(np.float32)

@@ -41,7 +41,7 @@ def _prefill_both(rb, engine, octx, out, plans, chunk=512, n_batch=2048):
 
 def test_mixed_step_shape_at_8b_widths_q4k(rb, oracle, models):
     """The step shape of the headline workload: 16 decode rows over resident contexts of 64..2048 tokens in the SAME
-    step as a 512-token chunk continuing a sequence and a 333-token chunk (not a multiple of any tile), then decode
+    step as a 512-token chunk continuing a sequence and a 100-token chunk (not a multiple of any tile), then decode
     steps of 18 rows. Runs the tcgen05 GEMM with a ragged last tile, the prefill attention tiles, the 9..16-vector
     and the eight-column decode attention on two streams, and afterwards the split-K / two-pass forms."""
     path = models("wide_q4k", **WIDE, dtype="q4_k", seed=2)
@@ -55,12 +55,13 @@ def test_mixed_step_shape_at_8b_widths_q4k(rb, oracle, models):
     contexts = [64, 96, 128, 192, 256, 384, 512, 768, 1024, 1536, 2047, 80, 150, 300, 600, 1200]
     seqs = {slot: rng.integers(3, 128256, n).tolist() for slot, n in enumerate(contexts)}
     seqs[16] = rng.integers(3, 128256, 1024).tolist()      # 512 resident, 512 more in the mixed step
-    seqs[17] = rng.integers(3, 128256, 333).tolist()       # arrives whole in the mixed step
+    seqs[17] = rng.integers(3, 128256, 100).tolist()       # arrives whole in the mixed step
     _prefill_both(rb, engine, octx, out, [(s, seqs[s][:-1]) for s in range(16)] + [(16, seqs[16][:512])])
     rows = [rb.StepRow(s, s, [seqs[s][-1]], len(seqs[s]) - 1, sample=True, sampling=greedy) for s in range(16)]
     rows.append(rb.StepRow(16, 16, seqs[16][512:], 512, sample=True, sampling=greedy))
     rows.append(rb.StepRow(17, 17, seqs[17], 0, sample=True, sampling=greedy))
-    assert sum(len(r.tokens) for r in rows) == 16 + 512 + 333
+    # 628 tokens = five token tiles, the last one 116 tokens wide
+    assert sum(len(r.tokens) for r in rows) == 16 + 512 + 100
     for step in range(3):
         toks = check_step(rb, engine, octx, oracle, rows, out, rep)
         expect_greedy(oracle, toks, rep)
