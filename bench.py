@@ -725,13 +725,16 @@ def main():
         line["ep_parity"] = ep_parity
     if expert_parallel:
         line["expert_parallel"] = ep_block
+    engine.close()
+    # a correctness record beside the timing: the tiny CPU-runnable workload replayed through the same library, its
+    # greedy streams compared token for token with the streams the CPU oracle committed under tests/golden/
+    from retrograd_b200.golden_check import replay
+
+    line["golden_check"] = replay(rb)
     if world == 1 and not args.no_cpu_baseline:
-        engine.close()
         value, times, cores = cpu_baseline(path, cfg)
         line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
                                 "sample": f"8 concurrent requests, 4-token prompts, {len(times)} decode steps of the same GGUF"}
-    else:
-        engine.close()
     print(json.dumps(line))
 
 

@@ -688,26 +688,52 @@ bool Engine::linear_reads_split(const WeightView & w, int ldx, int T, const Spli
 }
 
 void Engine::lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy) {
+    lora_group({target}, {0}, x, ldx, T, y, ldy);
+}
+
+// The adapters' deltas of up to three targets that read the same rows x: y[:, offsets[i] + ...] += scale B_i (A_i x).
+void Engine::lora_group(const std::vector<std::string> & targets, const std::vector<int> & y_offsets, const float * x, int ldx, int T, float * y, int ldy) {
     if (!cur_any_adapter_) return;
-    auto it = lora_targets_.find(target);
-    if (it == lora_targets_.end() || !it->second->present) return;
-    LoraTarget & t = *it->second;
+    LoraGroup group;
+    std::vector<LoraTarget *> present;
+    std::vector<int> offsets_present;
+    for (size_t i = 0; i < targets.size(); ++i) {
+        auto it = lora_targets_.find(targets[i]);
+        if (it == lora_targets_.end() || !it->second->present) continue;
+        present.push_back(it->second.get());
+        offsets_present.push_back(y_offsets[i]);
+    }
+    if (present.empty()) return;
+    const uint32_t n_in = present[0]->n_in;
+    bool grouped = lora_tensor_cores_ && adapters_.size() <= 1024 && present.size() <= (size_t)kLoraTcMaxTargets &&
+                   lora_tc_supported((int)r_max_, (int)n_in, present[0]->a.ptr, x, ldx);
+    for (LoraTarget * t : present) grouped = grouped && t->n_in == n_in && (uintptr_t)t->a.ptr % 16 == 0;
     prof_.begin(K_LORA, stream);
-    if (lora_tensor_cores_ && adapters_.size() <= 1024 && lora_tc_supported((int)r_max_, (int)t.n_in, t.a.ptr, x, ldx)) {
-        launch_lora_tc(t.a.ptr, t.b.ptr, lora_scales_.ptr, (int)r_max_, (int)t.n_in, (int)t.n_out, (int)adapters_.size(), lora_offsets_.ptr,
-                       lora_sorted_.ptr, x, ldx, T, lora_tmp_.ptr, y, ldy, stream);
+    if (grouped) {
+        for (size_t i = 0; i < present.size(); ++i) {
+            group.a[i] = present[i]->a.ptr;
+            group.b[i] = present[i]->b.ptr;
+            group.n_out[i] = (int)present[i]->n_out;
+            group.y_offset[i] = offsets_present[i];
+        }
+        group.n = (int)present.size();
+        launch_lora_tc(group, lora_scales_.ptr, (int)r_max_, (int)n_in, (int)adapters_.size(), lora_offsets_.ptr, lora_sorted_.ptr, x, ldx, T,
+                       lora_tmp_.ptr, y, ldy, stream);
         prof_.end(K_LORA, 2, stream);
         last_launches += 2;
         return;
     }
-    if (t.n_in % 4 == 0 && ldx % 4 == 0 && adapters_.size() <= 1024)
-        launch_lora_shrink_grouped(t.a.ptr, (int)r_max_, (int)t.n_in, (int)adapters_.size(), lora_offsets_.ptr, lora_sorted_.ptr, x, ldx, lora_tmp_.ptr,
-                                   stream);
-    else
-        launch_lora_shrink(t.a.ptr, (int)r_max_, (int)t.n_in, cur_tok_adapter_, x, ldx, T, lora_tmp_.ptr, stream);
-    launch_lora_expand(t.b.ptr, (int)r_max_, (int)t.n_out, lora_scales_.ptr, cur_tok_adapter_, lora_tmp_.ptr, T, y, ldy, stream);
-    prof_.end(K_LORA, 2, stream);
-    last_launches += 2;
+    for (size_t i = 0; i < present.size(); ++i) {
+        LoraTarget & t = *present[i];
+        if (t.n_in % 4 == 0 && ldx % 4 == 0 && adapters_.size() <= 1024)
+            launch_lora_shrink_grouped(t.a.ptr, (int)r_max_, (int)t.n_in, (int)adapters_.size(), lora_offsets_.ptr, lora_sorted_.ptr, x, ldx, lora_tmp_.ptr,
+                                       stream);
+        else
+            launch_lora_shrink(t.a.ptr, (int)r_max_, (int)t.n_in, cur_tok_adapter_, x, ldx, T, lora_tmp_.ptr, stream);
+        launch_lora_expand(t.b.ptr, (int)r_max_, (int)t.n_out, lora_scales_.ptr, cur_tok_adapter_, lora_tmp_.ptr, T, y + offsets_present[i], ldy, stream);
+        last_launches += 2;
+    }
+    prof_.end(K_LORA, 2 * (uint32_t)present.size(), stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1301,7 +1327,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         if (n_greedy_fast) sample_scratch_.ensure(sample_scratch_bytes((int)hp.vocab, (int)S));
     }
     if (any_adapter) {
-        lora_tmp_.ensure((size_t)kLoraTcMaxSplits * T * (size_t)std::max<uint32_t>(r_max_, 1));
+        lora_tmp_.ensure((size_t)kLoraTcMaxTargets * kLoraTcMaxSplits * T * (size_t)std::max<uint32_t>(r_max_, 1));
         lora_offsets_.ensure(adapters_.size() + 1);
         lora_sorted_.ensure(T);
     }
@@ -1401,9 +1427,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             linear(lw.wv, xn_.ptr, d, Ti, qkv_.ptr + dq + dkv, ldqkv, lw.bqkv ? lw.bqkv + dq + dkv : nullptr, nullptr, 0);
         }
         if (any_adapter) {
-            lora(p + "attn_q.weight", xn_.ptr, d, Ti, qkv_.ptr, ldqkv);
-            lora(p + "attn_k.weight", xn_.ptr, d, Ti, qkv_.ptr + dq, ldqkv);
-            lora(p + "attn_v.weight", xn_.ptr, d, Ti, qkv_.ptr + dq + dkv, ldqkv);
+            lora_group({p + "attn_q.weight", p + "attn_k.weight", p + "attn_v.weight"}, {0, dq, dq + dkv}, xn_.ptr, d, Ti, qkv_.ptr, ldqkv);
         }
         if (lw.q_norm) {
             RB_K(K_OTHER, 2, launch_rms_norm(qkv_.ptr, ldqkv, nullptr, lw.q_norm, dq, hp.eps, qkv_.ptr, ldqkv, Ti, stream);
@@ -1474,8 +1498,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                 linear(lw.wup, xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff, nullptr, nullptr, 0);
             }
             if (any_adapter) {
-                lora(p + "ffn_gate.weight", xn_.ptr, d, Ti, gu_.ptr, 2 * ff);
-                lora(p + "ffn_up.weight", xn_.ptr, d, Ti, gu_.ptr + ff, 2 * ff);
+                lora_group({p + "ffn_gate.weight", p + "ffn_up.weight"}, {0, ff}, xn_.ptr, d, Ti, gu_.ptr, 2 * ff);
             }
             if (!activated) RB_K(K_OTHER, 1, launch_swiglu(gu_.ptr, 2 * ff, ff, Ti, down_split ? nullptr : hff_.ptr, ff, stream, hff_split_.get()));
             // x = x + Wdown h, then the next layer's attention norm of x

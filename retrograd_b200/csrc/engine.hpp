@@ -340,6 +340,7 @@ private:
   private:
     bool linear_reads_split(const WeightView & w, int ldx, int T, const SplitAct * xs) const;
     void lora(const std::string & target, const float * x, int ldx, int T, float * y, int ldy);
+    void lora_group(const std::vector<std::string> & targets, const std::vector<int> & y_offsets, const float * x, int ldx, int T, float * y, int ldy);
     void flush_kv_updates();
     KvLayout kv_layout() const;
 

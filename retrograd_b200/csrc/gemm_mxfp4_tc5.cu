@@ -31,17 +31,23 @@ namespace rb200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 128;
-constexpr int STAGES = 5;
-constexpr int B_BYTES = BN * 128;
-constexpr int STAGE_BYTES = 2 * B_BYTES;          // activation tiles hi and lo
+constexpr int BM = 128;
 constexpr int GROUPS = 3;
 constexpr int EPI_WARP0 = 4 * GROUPS, MMA_WARP = EPI_WARP0 + 8;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int TMEM_COLS = 512;
-constexpr int TMEM_A = 128;                       // the accumulator at column 0, then the A slots of 32 columns
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int kMaxGroups = 1024;                  // experts per launch
+
+// Token tiles are 128 pairs wide (five pipeline stages) or 256 wide (three stages of 64 KB): with a few hundred pairs
+// per expert the wide form decodes an expert's weight tile once instead of twice.
+template <int BN> struct Shape {
+    static constexpr int STAGES = BN == 256 ? 3 : 5;
+    static constexpr int B_BYTES = BN * 128;
+    static constexpr int STAGE_BYTES = 2 * B_BYTES;          // activation tiles hi and lo
+    static constexpr int TMEM_A = BN;                        // the accumulator at column 0, then the A slots of 32 columns
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(TMEM_A + STAGES * 32 <= TMEM_COLS, "tensor memory: accumulator and A slots");
+};
 
 // grid (column groups of 64, row tiles, experts), 128 threads: thread p moves the two blocks of row p
 __global__ void mxfp4_retile_kernel(const uint8_t * __restrict__ bank, uint32_t n_out, uint32_t n_in, uint8_t * __restrict__ tiled) {
@@ -98,6 +104,7 @@ __device__ __forceinline__ void decode_block(const uint4 & q, __half2 scale, uin
     }
 }
 
+template <int BN>
 __global__ void __launch_bounds__(THREADS, 1) gemm_mxfp4_tc5_kernel(const uint8_t * __restrict__ W, int n_in, int n_out, int n_groups,
                                                                     const int32_t * __restrict__ offsets, const __grid_constant__ SplitAct X,
                                                                     float * __restrict__ Y, int ldy, int * __restrict__ error_flag) {
@@ -124,6 +131,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_mxfp4_tc5_kernel(const uint8_
     if (expert < 0) return;
     const int row0 = sh_off[expert], n_rows = sh_off[expert + 1] - row0;
 
+    using S = Shape<BN>;
+    constexpr int STAGES = S::STAGES, B_BYTES = S::B_BYTES, STAGE_BYTES = S::STAGE_BYTES, TMEM_A = S::TMEM_A;
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -176,8 +185,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_mxfp4_tc5_kernel(const uint8_
             if (p == 0) {
                 const uint32_t bh = smem_base + stage * STAGE_BYTES, bl = bh + B_BYTES;
                 tc5::mbar_expect_tx(full_bar(stage), 2 * B_BYTES);
-                tc5::tma_load_2d(bh, &X.map_hi, it * 64, row0 + t0, full_bar(stage));
-                tc5::tma_load_2d(bl, &X.map_lo, it * 64, row0 + t0, full_bar(stage));
+#pragma unroll
+                for (int box = 0; box < BN / 128; ++box) {      // the tensor maps' boxes are 128 rows
+                    tc5::tma_load_2d(bh + box * 16384, &X.map_hi, it * 64, row0 + t0 + box * 128, full_bar(stage));
+                    tc5::tma_load_2d(bl + box * 16384, &X.map_lo, it * 64, row0 + t0 + box * 128, full_bar(stage));
+                }
             }
             uint32_t out[32];
             decode_block(raw.q0, block_scale(raw.sc & 0xFFu), out);
@@ -231,20 +243,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_mxfp4_tc5_kernel(const uint8_
     } else {
         // ------------------------------------------------------------------ epilogue
         const int q = warp & 3;                         // TMEM lane quarter this warp may read
-        const int colhalf = (warp - EPI_WARP0) >> 2;    // which 64 token columns
+        const int colhalf = (warp - EPI_WARP0) >> 2;    // which half of the token columns
         const int o = m0 + q * 32 + lane;
         if (__all_sync(0xffffffffu, tc5::mbar_wait(tfull_bar, 0, abort_flag))) {
             tc5::fence_after_sync();
-            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + colhalf * 64;
-#pragma unroll
-            for (int c = 0; c < 4; c += 2) {
-                if (t0 + colhalf * 64 + c * 16 >= n_rows) break;      // warp-uniform: columns past the expert's pairs were never computed
+            const int col0 = colhalf * (BN / 2);
+            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + col0;
+#pragma unroll 1
+            for (int c = 0; c < BN / 2; c += 32) {
+                if (t0 + col0 + c >= n_rows) break;      // warp-uniform: columns past the expert's pairs were never computed
                 float v[16], w[16];
-                tc5::tmem_ld16x2(t_acc + c * 16, t_acc + (c + 1) * 16, v, w);
+                tc5::tmem_ld16x2(t_acc + c, t_acc + c + 16, v, w);
                 if (o < n_out) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const int ta = t0 + colhalf * 64 + c * 16 + i, tb = ta + 16;
+                        const int ta = t0 + col0 + c + i, tb = ta + 16;
                         if (ta < n_rows) Y[(size_t)(row0 + ta) * ldy + o] = v[i];
                         if (tb < n_rows) Y[(size_t)(row0 + tb) * ldy + o] = w[i];
                     }
@@ -289,11 +302,22 @@ bool gemm_mxfp4_tc5_supported(const WeightView & w, const SplitAct & x) {
 void launch_gemm_mxfp4_tc5_grouped(const WeightView & w, int n_groups, const int32_t * group_offsets, const SplitAct & x, int total_rows, float * y,
                                    int ldy, int * error_flag, cudaStream_t stream) {
     static PerDeviceOnce configured;   // function attributes are per device
-    if (configured.first()) cudaFuncSetAttribute(gemm_mxfp4_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (configured.first()) {
+        cudaFuncSetAttribute(gemm_mxfp4_tc5_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<128>::SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_mxfp4_tc5_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape<256>::SMEM_BYTES);
+    }
     if (n_groups <= 0 || n_groups > kMaxGroups || total_rows <= 0) return;
-    const dim3 grid((total_rows + BN - 1) / BN + n_groups, (w.n_out + BM - 1) / BM);
-    // a plain launch: the CTA reads its expert's offsets (written by the grouping kernel in front of it) before anything else
-    gemm_mxfp4_tc5_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, n_groups, group_offsets, x, y, ldy, error_flag);
+    // plain launches: the CTA reads its expert's offsets (written by the grouping kernel in front of it) before anything
+    // else. The pairs per expert are known on the device only; their mean picks the tile width.
+    if (total_rows > 96 * n_groups) {
+        const dim3 grid((total_rows + 255) / 256 + n_groups, (w.n_out + BM - 1) / BM);
+        gemm_mxfp4_tc5_kernel<256><<<grid, THREADS, Shape<256>::SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, n_groups, group_offsets, x, y,
+                                                                                  ldy, error_flag);
+    } else {
+        const dim3 grid((total_rows + 127) / 128 + n_groups, (w.n_out + BM - 1) / BM);
+        gemm_mxfp4_tc5_kernel<128><<<grid, THREADS, Shape<128>::SMEM_BYTES, stream>>>(w.tiled, (int)w.n_in, (int)w.n_out, n_groups, group_offsets, x, y,
+                                                                                  ldy, error_flag);
+    }
 }
 
 } // namespace rb200

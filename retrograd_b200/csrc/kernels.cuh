@@ -416,14 +416,24 @@ void launch_lora_expand(const float * b_stack, int r_max, int n_out, const float
                         int n_tokens, float * y, int ldy, cudaStream_t stream);
 
 // Segmented LoRA on the tensor cores (TF32 MMAs on split operands, F32-accurate): shrink over K splits into
-// tmp[split][t][r] (tmp holds kLoraTcMaxSplits * n_tokens * r_max floats), then expand into y. Tokens grouped by
+// tmp[target][split][t][r], then expand into y. Tokens grouped by
 // adapter as for launch_lora_shrink_grouped.
 constexpr int kLoraTcMaxSplits = 16;
 int lora_tc_splits(int n_in);
 bool lora_tc_supported(int r_max, int n_in, const float * a_stack, const float * x, int ldx);
-void launch_lora_tc(const float * a_stack, const float * b_stack, const float * scales, int r_max, int n_in, int n_out, int n_adapters,
-                    const int32_t * offsets, const int32_t * sorted, const float * x, int ldx, int n_tokens, float * tmp, float * y, int ldy,
-                    cudaStream_t stream);
+// Up to three targets that read the same input rows: their A stacks [n_adapters][r_max][n_in], B stacks
+// [n_adapters][n_out][r_max], widths and the column of y each one's result is added at. tmp holds
+// kLoraTcMaxTargets * kLoraTcMaxSplits * n_tokens * r_max floats.
+constexpr int kLoraTcMaxTargets = 3;
+struct LoraGroup {
+    const float * a[kLoraTcMaxTargets];
+    const float * b[kLoraTcMaxTargets];
+    int n_out[kLoraTcMaxTargets];
+    int y_offset[kLoraTcMaxTargets];
+    int n = 0;
+};
+void launch_lora_tc(const LoraGroup & group, const float * scales, int r_max, int n_in, int n_adapters, const int32_t * offsets, const int32_t * sorted,
+                    const float * x, int ldx, int n_tokens, float * tmp, float * y, int ldy, cudaStream_t stream);
 
 // Sampling over logits rows [S][n_vocab]. v2 rows transform their row of `work_logits`, which must
 // then hold a copy of `raw_logits`; with v1 rows only, `work_logits` may be null.

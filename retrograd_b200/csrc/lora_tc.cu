@@ -13,6 +13,8 @@
 //
 // The partial results of the K splits are summed by the expand kernel in split order, and a token's row
 // is produced by exactly one tile: results do not depend on which other rows share the step.
+// Targets that read the same input rows (q, k, v; gate, up) go through ONE pair of launches (grid.z = target):
+// the kernels are bound by launch and load latency, not by their bytes.
 #include "kernels.cuh"
 
 namespace rb200 {
@@ -65,10 +67,13 @@ __device__ __forceinline__ bool find_tile(int tile, int n_adapters, const int32_
 // launch, so the kernel is built for load parallelism: many short K ranges, four chunks' loads in flight per warp.
 constexpr int kShrinkWarps = 8;
 template <int NR>
-__global__ void __launch_bounds__(kShrinkWarps * 32) lora_shrink_tc_kernel(const float * __restrict__ a_stack, int r_max, int n_in, int n_adapters,
+__global__ void __launch_bounds__(kShrinkWarps * 32) lora_shrink_tc_kernel(const LoraGroup group, int r_max, int n_in, int n_adapters,
                                                              const int32_t * __restrict__ offsets, const int32_t * __restrict__ sorted,
                                                              const float * __restrict__ x, int ldx, float * __restrict__ tmp, int n_tokens,
                                                              int k_per_split) {
+    // blockIdx.z: which of the group's targets (they share the input rows); each has its own region of tmp
+    const float * __restrict__ a_stack = group.a[blockIdx.z];
+    tmp += (size_t)blockIdx.z * gridDim.y * n_tokens * r_max;
     __shared__ float red[kShrinkWarps][16][NR * 8 + 1];
     __shared__ int sh_offsets[kMaxAdapters + 1];
     int adapter, first, end;
@@ -132,10 +137,15 @@ __global__ void __launch_bounds__(kShrinkWarps * 32) lora_shrink_tc_kernel(const
 // grid (tile bound, column groups of 128), 4 warps: a warp takes four column tiles of eight, with every load of
 // the four (B rows and the y values they update) issued before the first MMA.
 template <int NR>
-__global__ void __launch_bounds__(128) lora_expand_tc_kernel(const float * __restrict__ b_stack, int r_max, int n_out, const float * __restrict__ scales,
+__global__ void __launch_bounds__(128) lora_expand_tc_kernel(const LoraGroup group, int r_max, const float * __restrict__ scales,
                                                              int n_adapters, const int32_t * __restrict__ offsets, const int32_t * __restrict__ sorted,
                                                              const float * __restrict__ tmp, int n_splits, int n_tokens, float * __restrict__ y, int ldy,
                                                              int cols_per_cta, int vec2) {
+    const int n_out = group.n_out[blockIdx.z];
+    if ((int)blockIdx.y * cols_per_cta >= n_out) return;       // the grid's column groups cover the widest target
+    const float * __restrict__ b_stack = group.b[blockIdx.z];
+    tmp += (size_t)blockIdx.z * n_splits * n_tokens * r_max;
+    y += group.y_offset[blockIdx.z];
     __shared__ int sh_offsets[kMaxAdapters + 1];
     int adapter, first, end;
     if (!find_tile(blockIdx.x, n_adapters, offsets, sh_offsets, adapter, first, end)) return;
@@ -226,21 +236,24 @@ bool lora_tc_supported(int r_max, int n_in, const float * a_stack, const float *
     return r_max >= 1 && r_max <= 64 && n_in % 16 == 0 && ldx % 4 == 0 && (uintptr_t)a_stack % 16 == 0 && (uintptr_t)x % 16 == 0;
 }
 
-void launch_lora_tc(const float * a_stack, const float * b_stack, const float * scales, int r_max, int n_in, int n_out, int n_adapters,
-                    const int32_t * offsets, const int32_t * sorted, const float * x, int ldx, int n_tokens, float * tmp, float * y, int ldy,
-                    cudaStream_t stream) {
-    if (n_tokens <= 0 || n_adapters <= 0) return;
+void launch_lora_tc(const LoraGroup & group, const float * scales, int r_max, int n_in, int n_adapters, const int32_t * offsets, const int32_t * sorted,
+                    const float * x, int ldx, int n_tokens, float * tmp, float * y, int ldy, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_adapters <= 0 || group.n <= 0) return;
     const int tiles = (n_tokens + 15) / 16 + n_adapters;          // every segment may end in a partial tile
     const int splits = lora_tc_splits(n_in);
     const int k_per_split = ((n_in + splits - 1) / splits + 15) / 16 * 16;
     const int cols_per_cta = 128;
-    const int vec2 = ldy % 2 == 0 && (uintptr_t)y % 8 == 0 ? 1 : 0;
+    int widest = 0, vec2 = ldy % 2 == 0 && (uintptr_t)y % 8 == 0 ? 1 : 0;
+    for (int i = 0; i < group.n; ++i) {
+        widest = std::max(widest, group.n_out[i]);
+        if (group.y_offset[i] % 2 != 0) vec2 = 0;
+    }
     dispatch_rank_tiles(r_max, [&](auto tag) {
         constexpr int NR = decltype(tag)::value;
-        lora_shrink_tc_kernel<NR><<<dim3(tiles, splits), kShrinkWarps * 32, 0, stream>>>(a_stack, r_max, n_in, n_adapters, offsets, sorted, x, ldx, tmp, n_tokens,
-                                                                         k_per_split);
-        lora_expand_tc_kernel<NR><<<dim3(tiles, (n_out + cols_per_cta - 1) / cols_per_cta), 128, 0, stream>>>(
-            b_stack, r_max, n_out, scales, n_adapters, offsets, sorted, tmp, splits, n_tokens, y, ldy, cols_per_cta, vec2);
+        lora_shrink_tc_kernel<NR><<<dim3(tiles, splits, group.n), kShrinkWarps * 32, 0, stream>>>(group, r_max, n_in, n_adapters, offsets, sorted, x, ldx, tmp,
+                                                                                                n_tokens, k_per_split);
+        lora_expand_tc_kernel<NR><<<dim3(tiles, (widest + cols_per_cta - 1) / cols_per_cta, group.n), 128, 0, stream>>>(
+            group, r_max, scales, n_adapters, offsets, sorted, tmp, splits, n_tokens, y, ldy, cols_per_cta, vec2);
     });
 }
 

@@ -64,3 +64,37 @@ def test_f16_fixture_decodes_to_the_f32_fixture(oracle):
         raw = np.asarray(t.data).view(np.uint8).reshape(-1)
         got = oracle.dequantize_row(oracle.T_F16, raw, raw.size // 2)
         assert np.array_equal(got, np.asarray(f32[name].data, dtype=np.float32).reshape(-1)), name
+
+
+def test_committed_greedy_streams_are_what_the_oracle_produces():
+    """tests/golden/c1_greedy_tokens.json is the output of tests/golden/make_c1_tokens.py: regenerated here from the
+    oracle and compared with the committed file."""
+    import importlib.util
+    import json
+    import tempfile
+    from pathlib import Path
+
+    import numpy as np
+
+    from oracle import oracle as O
+
+    here = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_c1_tokens", here / "make_c1_tokens.py")
+    mk = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mk)
+    golden = json.loads((here / "c1_greedy_tokens.json").read_text())
+    assert golden["spec"] == mk.SPEC and golden["prompt_seed"] == mk.SEED and golden["min_top2_margin"] > 1e-3
+    with tempfile.TemporaryDirectory() as tmp:
+        path = Path(tmp) / "c1.gguf"
+        O.synth_gguf(path, **mk.SPEC)
+        ctx = O.Context(O.Model(str(path)), mk.N_REQUESTS, 4096)
+        ps = mk.prompts()
+        rows = [(i, list(p), 0, True, 0) for i, p in enumerate(ps)]
+        streams = [[] for _ in ps]
+        for step in range(mk.N_NEW):
+            logits = ctx.step(rows)
+            toks = [int(np.argsort(-row, kind="stable")[0]) for row in logits]
+            for i, t in enumerate(toks):
+                streams[i].append(t)
+            rows = [(i, [t], len(ps[i]) + step, True, 0) for i, t in enumerate(toks)]
+    assert streams == golden["streams"]

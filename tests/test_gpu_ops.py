@@ -126,10 +126,12 @@ def test_q8_0_tcgen05_gemm_against_float64(rb, oracle, n_out, n_in, T):
     assert np.array_equal(got, again)
 
 
-@pytest.mark.parametrize("n_expert,n_out,n_in,counts", [(4, 256, 128, (5, 0, 130, 40)), (3, 200, 576, (128, 1, 257)), (8, 2880, 2880, (70, 3, 0, 129, 12, 64, 300, 9))])
+@pytest.mark.parametrize("n_expert,n_out,n_in,counts", [(4, 256, 128, (5, 0, 130, 40)), (3, 200, 576, (128, 1, 257)), (8, 2880, 2880, (70, 3, 0, 129, 12, 64, 300, 9)),
+                                                        (4, 256, 128, (300, 5, 257, 128)), (3, 300, 2880, (513, 0, 255))])
 def test_mxfp4_grouped_tcgen05_gemm_against_float64(rb, oracle, n_expert, n_out, n_in, counts):
     """The grouped MXFP4 expert GEMM: empty experts, experts of more than one token tile, a ragged last row tile,
-    the 20B-class MoE's own widths. Against the exact product of the decoded weights."""
+    the 20B-class MoE's own widths; the last two cases average more than 96 pairs per expert and take the 256-pair
+    tile form (tiles of 256 + 44, 256 + 1, 2 x 256 + 1 and 255 pairs). Against the exact product of the decoded weights."""
     rng = np.random.default_rng(23 * n_out + n_in)
     w = rng.normal(0, 0.02, (n_expert * n_out, n_in)).astype(np.float32)
     raw = np.frombuffer(b"".join(rb.quantize_row(39, w[r]) for r in range(n_expert * n_out)), dtype=np.uint8)

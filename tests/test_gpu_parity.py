@@ -217,3 +217,12 @@ def test_moe_experts_on_the_tensor_cores_agree_with_the_row_kernel(rb, models, m
     err = max(float(np.abs(l_tc - l_rows).max()), float(np.abs(l2_tc - l2_rows).max()))
     print(f"moe tensor-core vs row kernel: max|dlogit|={err:.3e}")
     assert err < 2e-4
+
+
+def test_tiny_workload_reproduces_the_committed_oracle_streams(rb):
+    """The engine's greedy streams on the tiny CPU-runnable workload equal, token for token, the streams the CPU
+    oracle wrote into tests/golden/c1_greedy_tokens.json (256 tokens; smallest oracle top-2 margin 1.4e-3)."""
+    from retrograd_b200.golden_check import replay
+
+    result = replay(rb)
+    assert result["tokens"] == 256 and result["bit_exact"], result["first_mismatch"]
