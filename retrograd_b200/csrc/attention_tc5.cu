@@ -8,7 +8,7 @@
 // straight into the layouts the MMAs read: K as a K-major operand (keys x dims), V as an MN-major operand of the
 // same bytes (no transpose anywhere). Per tile:
 //   S = Q_hi K^T + Q_lo K^T          (SS MMAs, M 128, N 64, K 16 per step; Q staged once in shared memory)
-//   softmax threads (one per query vector) pull their row of S out of tensor memory, mask by position,
+//   softmax threads (two per query vector) pull their row of S out of tensor memory, mask by position,
 //   keep the running maximum and sum, and store P = exp(S - max) as the two-term split P_hi + P_lo back
 //   into tensor memory as the A operand of
 //   O += P_hi V + P_lo V             (TS MMAs, M 128, N head_dim, K 16 per step)
@@ -18,7 +18,9 @@
 //
 // Accuracy as in the mma.sync kernel it replaces: K and V are exact f16 operands by storage; the query
 // (pre-scaled by 1/sqrt(head_dim)) and the probabilities are two-term splits, so every product is exact in f32.
-// Warps: 0 fetches, 1 issues the MMAs, 2-5 are the softmax threads (tensor-memory lane quarter = warp % 4).
+// Warps: 0 fetches, 1 issues the MMAs, 2-9 are the softmax threads (tensor-memory lane quarter = warp % 4): two per
+// query vector, each with half of a tile's keys and half of O's columns; they exchange the halves' maxima per tile
+// (and the sums once, at the end) through shared memory and an mbarrier.
 // Every mbarrier wait is bounded; a wait that gives up raises the error flag and the CTA frees its tensor memory.
 
 #include "kernels.cuh"
@@ -34,7 +36,7 @@ namespace {
 constexpr int ROWS = kAttentionTileRows;     // 128 query vectors per CTA
 constexpr int KT = 64;                       // keys per tile: four KV blocks
 constexpr int STAGES = 3;
-constexpr int THREADS = 6 * 32;
+constexpr int THREADS = 10 * 32;              // warp 0 fetches, warp 1 issues, warps 2-9 are the softmax threads
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_S = 0, TMEM_P = 128, TMEM_O = 256;      // S: 2 x 64 columns, P: 2 x (32 hi + 32 lo), O: head_dim
 
@@ -44,7 +46,8 @@ template <int HD> struct Shape {
     static constexpr int KV_BYTES = PANELS * KT * 128;       // one of K, V of a stage
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
     static constexpr int BAR_OFF = 2 * Q_BYTES + STAGES * STAGE_BYTES;
-    static constexpr int SMEM_BYTES = BAR_OFF + 256 + 1024 /* alignment slack */;
+    static constexpr int XCH_OFF = BAR_OFF + 256;            // the softmax halves' exchange: 6 x 128 floats
+    static constexpr int SMEM_BYTES = XCH_OFF + 6 * ROWS * 4 + 1024 /* alignment slack */;
 };
 
 // MN-major operand of [K rows][64 x f16] panels with the 128-byte swizzle: `lbo` bytes between the 64-element
@@ -94,7 +97,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc5_kernel(const float *
     auto s_free = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
     auto p_full = [&](int b) { return bar_base + 8u * (2 * STAGES + 4 + b); };
     auto pv_done = [&](int b) { return bar_base + 8u * (2 * STAGES + 6 + b); };
-    uint32_t * tmem_word = reinterpret_cast<uint32_t *>(smem + S::BAR_OFF + 8 * (2 * STAGES + 8));
+    auto x_full = [&](int b) { return bar_base + 8u * (2 * STAGES + 8 + b); };
+    const uint32_t l_full = bar_base + 8u * (2 * STAGES + 10);
+    uint32_t * tmem_word = reinterpret_cast<uint32_t *>(smem + S::BAR_OFF + 8 * (2 * STAGES + 11));
     volatile int * abort_flag = reinterpret_cast<volatile int *>(tmem_word + 1);
 
     const int slot = tok_slot[i0], pos0 = tok_pos[i0], pmin = tok_pos_min[i0];
@@ -110,16 +115,18 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc5_kernel(const float *
         }
         for (int b = 0; b < 2; ++b) {
             tc5::mbar_init(s_full(b), 1);
-            tc5::mbar_init(s_free(b), 4);       // the softmax warps
-            tc5::mbar_init(p_full(b), 4);
+            tc5::mbar_init(s_free(b), 8);       // the softmax warps
+            tc5::mbar_init(p_full(b), 8);
             tc5::mbar_init(pv_done(b), 1);
+            tc5::mbar_init(x_full(b), 8);
         }
+        tc5::mbar_init(l_full, 8);
         *abort_flag = 0;
         tc5::fence_mbar_init();
     }
     if (warp == 1) tc5::tmem_alloc(smem_u32(tmem_word), TMEM_COLS);
 
-    // ---- stage the query tile as hi + lo f16 (every thread: 128 rows x two halves over 192 threads)
+    // ---- stage the query tile as hi + lo f16 (every thread: 128 rows x two halves)
     {
         const float scale = rsqrtf((float)HD);
         for (int u = tid; u < 2 * ROWS; u += THREADS) {
@@ -229,50 +236,60 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc5_kernel(const float *
             if (alive && n_tiles > 0) issue_pv(n_tiles - 1);
         }
     } else {
-        // ------------------------------------------------------------------ softmax, one query vector per thread
+        // ------------------------------------------------------------------ softmax: two threads per query vector,
+        // each with half of a tile's keys (warps 2-5 the first 32, warps 6-9 the last 32) and half of O's columns
+        const int grp = (warp - 2) >> 2;
         const int q = warp & 3;
         const int R = q * 32 + lane;
         const int tt = R / G, hg = R % G;
         const int prow = tt < ntok ? pos0 + tt : -1;        // last position this query vector may see
         const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+        float * xmax = reinterpret_cast<float *>(smem + S::XCH_OFF);     // [tile parity][group][row]: the halves' maxima
+        float * xsum = xmax + 4 * ROWS;                                  // [group][row]: the halves' sums, at the end
+        constexpr int KH = KT / 2, OH = HD / 2;
         float m = -INFINITY, l = 0.f;
         bool alive = true;
         for (int j = 0; j < n_tiles && alive; ++j) {
             const int b = j & 1;
             if (!__all_sync(0xffffffffu, tc5::mbar_wait(s_full(b), (j >> 1) & 1, abort_flag))) { alive = false; break; }
             tc5::fence_after_sync();
-            float s[KT];
-#pragma unroll
-            for (int c = 0; c < KT; c += 32) {
+            float s[KH];
+            {
                 float v[16], w[16];
-                tc5::tmem_ld16x2(t_lane + TMEM_S + b * 64 + c, t_lane + TMEM_S + b * 64 + c + 16, v, w);
+                tc5::tmem_ld16x2(t_lane + TMEM_S + b * 64 + grp * KH, t_lane + TMEM_S + b * 64 + grp * KH + 16, v, w);
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    s[c + i] = v[i];
-                    s[c + 16 + i] = w[i];
+                    s[i] = v[i];
+                    s[16 + i] = w[i];
                 }
             }
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive(s_free(b));
             // causal mask by position within the slot
-            const int pbase = (nb0 << 4) + j * KT;
+            const int pbase = (nb0 << 4) + j * KT + grp * KH;
             float mx = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < KT; ++i) {
+            for (int i = 0; i < KH; ++i) {
                 const int p = pbase + i;
                 if (p < pmin || p > prow) s[i] = -INFINITY;
                 mx = fmaxf(mx, s[i]);
             }
+            // the row's maximum over both halves
+            xmax[(b * 2 + grp) * ROWS + R] = mx;
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive(x_full(b));
+            if (!__all_sync(0xffffffffu, tc5::mbar_wait(x_full(b), (j >> 1) & 1, abort_flag))) { alive = false; break; }
+            mx = fmaxf(mx, xmax[(b * 2 + (grp ^ 1)) * ROWS + R]);
             const float mn = fmaxf(m, mx);
             const float ref = mn == -INFINITY ? 0.f : mn;
             const float corr = expf(m - ref);             // exp(-inf) = 0 before the row's first visible key
             const bool rose = mn > m;
             m = mn;
             float sum = 0.f;
-            uint32_t ph[KT / 2], pl[KT / 2];
+            uint32_t ph[KH / 2], pl[KH / 2];
 #pragma unroll
-            for (int i = 0; i < KT; i += 2) {
+            for (int i = 0; i < KH; i += 2) {
                 // (the fast exponential: one special-function instruction per probability, relative error ~2^-21,
                 // far inside what the f16 pair that follows keeps; the softmax threads are this kernel's critical path)
                 const float x0 = __expf(s[i] - ref), x1 = __expf(s[i + 1] - ref);
@@ -282,47 +299,54 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc5_kernel(const float *
                 ph[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
                 pl[i >> 1] = pack_half2(x0 - back.x, x1 - back.y);
             }
-            l = l * corr + sum;
+            l = l * corr + sum;                           // this half's share of the row's sum
             // O in tensor memory follows the new maximum: only when some row of the warp rose, and only once the
-            // previous tile's P V has landed
+            // previous tile's P V has landed; each half takes half of O's columns
             if (j > 0 && __any_sync(0xffffffffu, rose)) {
                 if (!__all_sync(0xffffffffu, tc5::mbar_wait(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag))) { alive = false; break; }
                 tc5::fence_after_sync();
 #pragma unroll
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = 0; c < OH; c += 32) {
                     float v[16], w[16];
-                    tc5::tmem_ld16x2(t_lane + TMEM_O + c, t_lane + TMEM_O + c + 16, v, w);
+                    tc5::tmem_ld16x2(t_lane + TMEM_O + grp * OH + c, t_lane + TMEM_O + grp * OH + c + 16, v, w);
                     uint32_t o[32];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         o[i] = __float_as_uint(v[i] * corr);
                         o[16 + i] = __float_as_uint(w[i] * corr);
                     }
-                    tc5::tmem_st32(t_lane + TMEM_O + c, o);
+                    tc5::tmem_st32(t_lane + TMEM_O + grp * OH + c, o);
                 }
             }
             // P buffer b was last read by the P V of tile j - 2
             if (!__all_sync(0xffffffffu, tc5::mbar_wait(pv_done(b), ((j >> 1) & 1) ^ 1, abort_flag))) { alive = false; break; }
             tc5::fence_after_sync();
-            tc5::tmem_st32(t_lane + TMEM_P + b * 64, ph);
-            tc5::tmem_st32(t_lane + TMEM_P + b * 64 + 32, pl);
+            tc5::tmem_st16(t_lane + TMEM_P + b * 64 + grp * (KH / 2), ph);
+            tc5::tmem_st16(t_lane + TMEM_P + b * 64 + 32 + grp * (KH / 2), pl);
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive(p_full(b));
         }
         if (alive && n_tiles > 0 && __all_sync(0xffffffffu, tc5::mbar_wait(pv_done((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag))) {
             tc5::fence_after_sync();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            float * dst = out + (size_t)(i0 + (tt < ntok ? tt : 0)) * ldo + (size_t)(hk * G + hg) * HD;
+            // the row's sum over both halves
+            xsum[grp * ROWS + R] = l;
+            __syncwarp();
+            if (lane == 0) tc5::mbar_arrive(l_full);
+            if (__all_sync(0xffffffffu, tc5::mbar_wait(l_full, 0, abort_flag))) {
+                l += xsum[(grp ^ 1) * ROWS + R];
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                float * dst = out + (size_t)(i0 + (tt < ntok ? tt : 0)) * ldo + (size_t)(hk * G + hg) * HD + grp * OH;
 #pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-                float v[16], w[16];
-                tc5::tmem_ld16x2(t_lane + TMEM_O + c, t_lane + TMEM_O + c + 16, v, w);
-                if (tt < ntok) {
+                for (int c = 0; c < OH; c += 32) {
+                    float v[16], w[16];
+                    tc5::tmem_ld16x2(t_lane + TMEM_O + grp * OH + c, t_lane + TMEM_O + grp * OH + c + 16, v, w);
+                    if (tt < ntok) {
 #pragma unroll
-                    for (int i = 0; i < 16; i += 4) {
-                        *reinterpret_cast<float4 *>(dst + c + i) = make_float4(v[i] * inv, v[i + 1] * inv, v[i + 2] * inv, v[i + 3] * inv);
-                        *reinterpret_cast<float4 *>(dst + c + 16 + i) = make_float4(w[i] * inv, w[i + 1] * inv, w[i + 2] * inv, w[i + 3] * inv);
+                        for (int i = 0; i < 16; i += 4) {
+                            *reinterpret_cast<float4 *>(dst + c + i) = make_float4(v[i] * inv, v[i + 1] * inv, v[i + 2] * inv, v[i + 3] * inv);
+                            *reinterpret_cast<float4 *>(dst + c + 16 + i) = make_float4(w[i] * inv, w[i + 1] * inv, w[i + 2] * inv, w[i + 3] * inv);
+                        }
                     }
                 }
             }
