@@ -623,11 +623,18 @@ def main():
     # step against the measured HBM rate. No admissions, no prefill rows; repeated shapes replay as CUDA graphs.
     decode_only = []
     weight_bytes_step = None
-    if not sp.get("experts"):
-        bpw = {"q4_k": 144 / 256, "q8_0": 34 / 32, "f16": 2.0, "f32": 4.0}.get(sp["dtype"], 1.0)
-        weight_bytes_step = (sp["layers"] * w_elems_layer + sp["d"] * sp["vocab"]) * bpw
+    if not expert_parallel:
+        bpw_of = {"q4_k": 144 / 256, "q8_0": 34 / 32, "mxfp4": 17 / 32, "f16": 2.0, "f32": 4.0}
+        bpw = bpw_of.get(sp["dtype"], 1.0)
+        if sp.get("experts"):
+            # a decode step of hundreds of rows touches every expert: all banks once, the dense matrices once
+            dense = sp["d"] * (sp["heads"] * hd + 2 * sp["kv_heads"] * hd) + sp["heads"] * hd * sp["d"]
+            banks = sp["experts"] * 3 * sp["d"] * sp["ff"] * bpw_of.get(sp.get("expert_dtype", sp["dtype"]), 1.0)
+            weight_bytes_step = sp["layers"] * (dense * bpw + sp["d"] * sp["experts"] * 4 + banks) + sp["d"] * sp["vocab"] * bpw
+        else:
+            weight_bytes_step = (sp["layers"] * w_elems_layer + sp["d"] * sp["vocab"]) * bpw
         decoders = sum(1 for r in driver.live if r.last is not None)
-        for want in (8, cfg["n_requests"]):
+        for want in ((cfg["n_requests"],) if sp.get("experts") else (8, cfg["n_requests"])):
             n_rows = min(want, decoders)
             if n_rows == 0 or any(d["rows"] == n_rows for d in decode_only):
                 continue

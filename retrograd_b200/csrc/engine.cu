@@ -610,7 +610,8 @@ bool Engine::linear(const WeightView & w, const float * x, int ldx, int T, float
 
 // Runs one step's device work: eagerly, or as a replayed / freshly captured CUDA graph.
 void Engine::run_step_work(const std::vector<uint64_t> & sig, const std::function<void()> & issue) {
-    const bool graphable = graphs_enabled_ && !prof_.enabled && model->hp.n_expert == 0;
+    // (under expert parallelism every MoE layer synchronises with the host for its exchange plan: eager only)
+    const bool graphable = graphs_enabled_ && !prof_.enabled && !ep_comm_;
     if (graph_epoch_ != g_alloc_epoch.load()) {       // some buffer moved: every captured pointer is stale
         for (auto & e : graphs_) if (e.second.exec) cudaGraphExecDestroy(e.second.exec);
         graphs_.clear();

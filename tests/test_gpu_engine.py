@@ -349,6 +349,40 @@ def test_repeated_step_shapes_replay_as_cuda_graphs_with_identical_results(rb, o
         assert t0 == t1 and l0 == l1 and np.array_equal(x0, x1)
 
 
+def test_moe_decode_steps_replay_as_cuda_graphs_with_identical_results(rb, models, monkeypatch):
+    """Expert routing changes from step to step while the step shape does not: the grouped expert
+    launches size their grids from the step's token count, never from the routed counts, so one
+    captured graph serves every routing. Tokens, logits and routes must equal the eager engine's."""
+    spec = dict(arch="olmoe", layers=2, d=128, heads=4, kv_heads=4, ff=64, vocab=512, experts=8, experts_used=2,
+                dtype="q8_0", expert_dtype="mxfp4", seed=21)
+    path = models("moe_flat", **spec)
+
+    def run(graphs: bool):
+        monkeypatch.setenv("RB200_GRAPHS", "1" if graphs else "0")
+        engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=512, n_seq_max=4, n_batch=64, n_ubatch=64))
+        out = rb.StepOutput()
+        g = rb.SamplingParamsV2.greedy()
+        prompts = [_prompt(300 + i, 7 + 2 * i, vocab=512) for i in range(3)]
+        engine.step([rb.StepRow(i, i, p, 0, sample=True, sampling=g) for i, p in enumerate(prompts)], out)
+        last = [out.row(i).token for i in range(3)]
+        trace = []
+        for step in range(12):
+            rows = [rb.StepRow(i, i, [last[i]], len(prompts[i]) + step, sample=True, sampling=g) for i in range(3)]
+            engine.step(rows, out)
+            last = [out.row(i).token for i in range(3)]
+            trace.append((list(last), engine.last_logits(2).copy(), engine.last_routes().copy()))
+        stats = engine.graph_stats()
+        engine.close()
+        return trace, stats
+    eager, stats_eager = run(False)
+    graphed, stats_graphed = run(True)
+    assert stats_eager == (0, 0)
+    assert stats_graphed[0] >= 8 and stats_graphed[1] >= 1
+    assert len({r.tobytes() for _, _, r in eager}) > 1  # the routing really differs between steps
+    for (t0, x0, r0), (t1, x1, r1) in zip(eager, graphed):
+        assert t0 == t1 and np.array_equal(x0, x1) and np.array_equal(r0, r1)
+
+
 @pytest.mark.parametrize("name,spec", [
     ("tails_q4k", dict(arch="llama", layers=3, d=512, heads=8, kv_heads=2, ff=1024, vocab=1024, dtype="q4_k", seed=41)),
     ("tails_q8", dict(arch="llama", layers=3, d=256, heads=4, kv_heads=2, ff=512, vocab=512, dtype="q8_0", seed=42)),
