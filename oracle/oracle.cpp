@@ -402,7 +402,7 @@ struct SlotKV {
 struct Ctx {
     Model * m;
     uint32_t n_slots, n_ctx_seq;
-    bool kv_f16;
+    int kv_dtype;      // retro_engine_kv_dtype: 0 F32, 1 F16, 2 Q8_0, 3 Q4_0 - what a stored K / V row is rounded to
     std::vector<SlotKV> slots;
     // filled by the last step when the model is MoE: [layer][token][k] expert ids
     std::vector<int32_t> last_routes;
@@ -413,6 +413,38 @@ const float * vec_f32(const Model & m, const std::string & name) {
     const Tensor & t = m.need(name);
     if (t.type != T_F32) throw std::runtime_error(name + " must be F32");
     return (const float *)t.data;
+}
+
+// What the cache returns for a row stored under `kv_dtype`. The quantised types are ggml's block formats over 32
+// consecutive elements (published reference quantisers quantize_row_q8_0_ref / quantize_row_q4_0_ref of the
+// un-vendored llama.cpp fork, restated; the reference hands the type to that library at
+// crates/retrograd-ffi/runtime/src/retro_engine.cpp:84-90,251-266): the scale is kept as f16, a value reads back as
+// scale * quant in f32. Q8_0: d = amax / 127, q = round-half-away(x / d). Q4_0: d = (the element of largest
+// magnitude, the first of equals) / -8, q = min(15, trunc(x / d + 8.5)), value (q - 8) * d.
+void kv_store_row(int kv_dtype, const float * src, float * dst, size_t n) {
+    if (kv_dtype == 0) {
+        std::copy(src, src + n, dst);
+    } else if (kv_dtype == 1) {
+        for (size_t i = 0; i < n; ++i) dst[i] = round_to_half(src[i]);
+    } else if (kv_dtype == 2) {
+        for (size_t b = 0; b + 32 <= n; b += 32) {
+            float amax = 0.f;
+            for (int j = 0; j < 32; ++j) amax = std::max(amax, std::fabs(src[b + j]));
+            const float d = amax / 127.f, id = d != 0.f ? 1.0f / d : 0.f, dh = round_to_half(d);
+            for (int j = 0; j < 32; ++j) dst[b + j] = dh * (float)(int8_t)std::lround(src[b + j] * id);
+        }
+    } else {
+        for (size_t b = 0; b + 32 <= n; b += 32) {
+            float amax = 0.f, mx = 0.f;
+            for (int j = 0; j < 32; ++j)
+                if (amax < std::fabs(src[b + j])) { amax = std::fabs(src[b + j]); mx = src[b + j]; }
+            const float d = mx / -8.f, id = d != 0.f ? 1.0f / d : 0.f, dh = round_to_half(d);
+            for (int j = 0; j < 32; ++j) {
+                const int q = std::min(15, (int)(int8_t)(src[b + j] * id + 8.5f));
+                dst[b + j] = dh * (float)(q - 8);
+            }
+        }
+    }
 }
 
 void rope(float * v, uint32_t n_heads, uint32_t hd, uint32_t n_rot, bool neox, int32_t pos, const std::vector<float> & inv_freq) {
@@ -535,10 +567,8 @@ void forward(Ctx & c, size_t n_rows, const int32_t * slot, const uint32_t * n, c
             SlotKV & s = c.slots[tslot[t]];
             float * kd = &s.k[l][(size_t)tpos[t] * dkv];
             float * vd = &s.v[l][(size_t)tpos[t] * dkv];
-            for (size_t i = 0; i < dkv; ++i) {
-                kd[i] = c.kv_f16 ? round_to_half(k[t * dkv + i]) : k[t * dkv + i];
-                vd[i] = c.kv_f16 ? round_to_half(v[t * dkv + i]) : v[t * dkv + i];
-            }
+            kv_store_row(c.kv_dtype, &k[t * dkv], kd, dkv);
+            kv_store_row(c.kv_dtype, &v[t * dkv], vd, dkv);
         }
 #pragma omp parallel for schedule(dynamic)
         for (int64_t th = 0; th < (int64_t)(T * m.n_head); ++th) {
@@ -944,8 +974,9 @@ int32_t ora_lora_load(void * mp, const char * path, float scale) {
     }
 }
 
-void * ora_ctx_new(void * m, uint32_t n_slots, uint32_t n_ctx_seq, int kv_f16) {
-    Ctx * c = new Ctx{(Model *)m, n_slots, n_ctx_seq, kv_f16 != 0, {}, {}};
+// kv_dtype: retro_engine_kv_dtype (0 F32, 1 F16, 2 Q8_0, 3 Q4_0); the quantised types need head_dim % 32 == 0
+void * ora_ctx_new(void * m, uint32_t n_slots, uint32_t n_ctx_seq, int kv_dtype) {
+    Ctx * c = new Ctx{(Model *)m, n_slots, n_ctx_seq, kv_dtype, {}, {}};
     c->slots.resize(n_slots);
     return c;
 }

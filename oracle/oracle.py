@@ -193,9 +193,12 @@ class Model:
 class Context:
     """Per-slot contiguous KV (deep copies on seq_cp): the independent check of the paged cache."""
 
-    def __init__(self, model: Model, n_slots: int, n_ctx_seq: int, kv_f16: bool = True) -> None:
+    def __init__(self, model: Model, n_slots: int, n_ctx_seq: int, kv_f16: bool = True, kv_dtype: int | None = None) -> None:
+        """kv_dtype: a retro_engine_kv_dtype value (0 F32, 1 F16, 2 Q8_0, 3 Q4_0); default F16 (or F32 with kv_f16=False)."""
         self.model = model
-        self._h = lib().ora_ctx_new(model._h, n_slots, n_ctx_seq, 1 if kv_f16 else 0)
+        if kv_dtype is None:
+            kv_dtype = 1 if kv_f16 else 0
+        self._h = lib().ora_ctx_new(model._h, n_slots, n_ctx_seq, int(kv_dtype))
 
     def step(self, rows) -> np.ndarray:
         """rows: iterable of (slot, tokens, pos0, sample[, adapter]). Returns logits [S, vocab]."""

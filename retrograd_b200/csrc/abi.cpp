@@ -196,8 +196,8 @@ retro_engine * retro_engine_new_checked(const char * model_path, const retro_eng
             set_error("device=cpu requested but this library only runs on a CUDA GPU");
             return nullptr;
         }
-        if (resolved.kv_dtype != RETRO_ENGINE_KV_DTYPE_F16) {
-            set_error("this backend stores the KV cache as F16 only: engine kv_dtype must be RETRO_ENGINE_KV_DTYPE_F16");
+        if (resolved.kv_dtype == RETRO_ENGINE_KV_DTYPE_F32) {
+            set_error("this backend stores the KV cache as F16, Q8_0 or Q4_0: engine kv_dtype F32 is not supported");
             return nullptr;
         }
         if (resolved.expert_placement != RETRO_EXPERT_PLACEMENT_DEVICE) {

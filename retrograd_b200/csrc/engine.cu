@@ -402,8 +402,22 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     const uint32_t max_blocks = (n_ctx_seq + kBlockTokens - 1) / kBlockTokens;
     kv = std::make_unique<KvManager>(config.n_seq_max, n_blocks, kBlockTokens, max_blocks);
     kv_layer_stride_ = (uint64_t)n_blocks * hp.n_head_kv * kBlockTokens * hp.head_dim;
-    kcache_.ensure(kv_layer_stride_ * hp.n_layer);
-    vcache_.ensure(kv_layer_stride_ * hp.n_layer);
+    kv_storage_ = config.kv_dtype == RETRO_ENGINE_KV_DTYPE_Q8_0 ? KV_Q8_0 : config.kv_dtype == RETRO_ENGINE_KV_DTYPE_Q4_0 ? KV_Q4_0 : KV_F16;
+    if (config.kv_dtype == RETRO_ENGINE_KV_DTYPE_F32)
+        throw std::runtime_error("this backend stores the KV cache as F16, Q8_0 or Q4_0: engine kv_dtype F32 is not supported");
+    if (kv_storage_ != KV_F16) {
+        // The pool holds ggml's quantised rows; the attention kernels read one layer at a time from an f16 scratch
+        // with the pool's block numbering, which kv_dequant fills for the step's sequences.
+        if (hp.head_dim % 32 != 0) throw std::runtime_error("a quantized engine kv_dtype needs a head dimension that is a multiple of 32");
+        kv_q_layer_stride_ = (uint64_t)n_blocks * hp.n_head_kv * kBlockTokens * kv_row_bytes(kv_storage_, (int)hp.head_dim);
+        kq_.ensure(kv_q_layer_stride_ * hp.n_layer);
+        vq_.ensure(kv_q_layer_stride_ * hp.n_layer);
+        RB_CUDA(cudaMemsetAsync(kq_.ptr, 0, kq_.count, stream));
+        RB_CUDA(cudaMemsetAsync(vq_.ptr, 0, vq_.count, stream));
+    }
+    const uint64_t f16_layers = kv_storage_ == KV_F16 ? hp.n_layer : 1;
+    kcache_.ensure(kv_layer_stride_ * f16_layers);
+    vcache_.ensure(kv_layer_stride_ * f16_layers);
     // Cells past a sequence's end in its last block are read (and masked) by the attention kernels:
     // a masked probability of zero times a leftover NaN bit pattern would still be NaN.
     RB_CUDA(cudaMemsetAsync(kcache_.ptr, 0, kcache_.count * sizeof(__half), stream));
@@ -433,7 +447,7 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     attn_tc5_ = attn_mma_;
     if (const char * env = std::getenv("RB200_ATTN_TC5")) attn_tc5_ = attn_tc5_ && std::string(env) != "0";
     if (attn_tc5_) {
-        attention_maps_encode(attn_maps_, kcache_.ptr, vcache_.ptr, (int)hp.head_dim, (uint64_t)hp.n_layer * (kv_layer_stride_ / hp.head_dim));
+        attention_maps_encode(attn_maps_, kcache_.ptr, vcache_.ptr, (int)hp.head_dim, f16_layers * (kv_layer_stride_ / hp.head_dim));
         attn_tc5_ = attention_tc5_supported((int)hp.n_head, (int)hp.n_head_kv, (int)hp.head_dim, (int)kBlockTokens, attn_maps_);
     }
 
@@ -505,7 +519,12 @@ KvLayout Engine::kv_layout() const {
     KvLayout l;
     l.k = kcache_.ptr;
     l.v = vcache_.ptr;
-    l.layer_stride = kv_layer_stride_;
+    l.layer_stride = kv_storage_ == KV_F16 ? kv_layer_stride_ : 0;
+    l.kq = kq_.ptr;
+    l.vq = vq_.ptr;
+    l.q_layer_stride = kv_q_layer_stride_;
+    l.storage = kv_storage_;
+    l.q_row_bytes = kv_storage_ == KV_F16 ? 0 : kv_row_bytes(kv_storage_, (int)model->hp.head_dim);
     l.n_head_kv = (int32_t)model->hp.n_head_kv;
     l.head_dim = (int32_t)model->hp.head_dim;
     l.block_tokens = (int32_t)kBlockTokens;
@@ -1371,7 +1390,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     last_d2h_bytes = S ? res_total - 16 : 0;
     const std::vector<uint64_t> sig = {R, T, S, (uint64_t)n_patches, (uint64_t)n_copies, edits.size(), top_stride, any_v2, (uint64_t)n_greedy_fast,
                                        any_adapter, (uint64_t)n_attn_items, (uint64_t)n_small_items, any_wide_item, any_mid_item,
-                                       (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_, (uint64_t)adapters_.size(), (uint64_t)masks.size()};
+                                       (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_, (uint64_t)adapters_.size(), (uint64_t)masks.size(),
+                                       // a quantised pool's dequantisation grid covers the longest row's blocks
+                                       kv_storage_ != KV_F16 ? (uint64_t)((max_ctx + kBlockTokens - 1) / kBlockTokens) : 0};
     auto issue = [&]() {
     last_launches = 0;
     RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
@@ -1435,6 +1456,13 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                  launch_rms_norm(qkv_.ptr + dq, ldqkv, nullptr, lw.k_norm, dkv, hp.eps, qkv_.ptr + dq, ldqkv, Ti, stream));
         }
         if (!roped) RB_K(K_OTHER, 1, launch_rope_store(qkv_.ptr, ldqkv, Ti, rope_args, stream));
+        if (kv_storage_ != KV_F16) {
+            // the rotated K and the V rows are still in the qkv buffer: quantise them into the pool, then bring every
+            // block the step's rows attend to (the new cells included, now as the pool holds them) into the f16 scratch
+            RB_K(K_ATTN, 2, launch_kv_quant_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_cell, stream);
+                 launch_kv_dequant(kvl, (int)l, (int)R, (max_ctx + (int)kBlockTokens - 1) / (int)kBlockTokens, maps.cu_rows, maps.tok_slot, maps.tok_pos,
+                                   maps.tok_pos_min, stream));
+        }
         if (attn_mma_) {
             // every row of the step goes through the split-KV kernel: its merge writes the split form as well
             const bool merge_splits = fused_finish_ && att_split_.get() && !any_wide_item && !any_mid_item && n_small_items && attn_splits > 1 &&
@@ -1797,7 +1825,9 @@ int Engine::seq_save(int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_bu
     // A dense attention model has no partial (recurrent) state: a PARTIAL_ONLY snapshot is a bare header.
     const bool partial = (flags & RETRO_STATE_SEQ_FLAGS_PARTIAL_ONLY) != 0;
     const size_t n_pos = (s.empty() || partial) ? 0 : (size_t)(s.pos_max - s.pos_min + 1);
-    const size_t payload = n_pos * hp.n_layer * 2 * hp.dkv() * sizeof(__half);
+    // per position, layer and K | V: the heads' rows as the pool holds them (f16 values, or quantised rows)
+    const size_t pos_bytes = (size_t)hp.n_layer * 2 * hp.n_head_kv * kv_row_bytes(kv_storage_, (int)hp.head_dim);
+    const size_t payload = n_pos * pos_bytes;
     const size_t required = sizeof(SnapshotHeader) + payload;
     *out_n = required;
     if (!buffer) return STATUS_OK;
@@ -1807,7 +1837,7 @@ int Engine::seq_save(int32_t slot, uint32_t flags, uint8_t * buffer, size_t n_bu
     }
     SnapshotHeader h{};
     std::memcpy(h.magic, kSnapshotMagic, 8);
-    h.version = partial ? 2 : 1;
+    h.version = (partial ? 2 : 1) + 16 * (uint32_t)kv_storage_;       // a snapshot only loads into a pool of its storage type
     h.n_layer = hp.n_layer;
     h.n_head_kv = hp.n_head_kv;
     h.head_dim = hp.head_dim;
@@ -1851,13 +1881,13 @@ int Engine::seq_load(int32_t slot, uint32_t flags, const uint8_t * buffer, size_
     if (n_bytes < sizeof h) { set_error(refused); return STATUS_RUNTIME; }
     std::memcpy(&h, buffer, sizeof h);
     const bool partial = (flags & RETRO_STATE_SEQ_FLAGS_PARTIAL_ONLY) != 0;
-    if (std::memcmp(h.magic, kSnapshotMagic, 8) != 0 || h.version != (partial ? 2u : 1u) || h.n_layer != hp.n_layer ||
+    if (std::memcmp(h.magic, kSnapshotMagic, 8) != 0 || h.version != (partial ? 2u : 1u) + 16u * (uint32_t)kv_storage_ || h.n_layer != hp.n_layer ||
         h.n_head_kv != hp.n_head_kv || h.head_dim != hp.head_dim || n_bytes < sizeof h + h.payload_bytes) {
         set_error(refused);
         return STATUS_RUNTIME;
     }
     const size_t n_pos = h.pos_min < 0 ? 0 : (size_t)(h.pos_max - h.pos_min + 1);
-    if (h.payload_bytes != n_pos * hp.n_layer * 2 * hp.dkv() * sizeof(__half) || fnv1a(buffer + sizeof h, h.payload_bytes) != h.checksum ||
+    if (h.payload_bytes != n_pos * hp.n_layer * 2 * hp.n_head_kv * kv_row_bytes(kv_storage_, (int)hp.head_dim) || fnv1a(buffer + sizeof h, h.payload_bytes) != h.checksum ||
         (n_pos && (h.pos_min < 0 || (uint32_t)h.pos_max >= n_ctx_seq))) {
         set_error(refused);
         return STATUS_RUNTIME;
@@ -1893,7 +1923,7 @@ int Engine::memory(retro_engine_memory_info * out) {
     out->n_slots = config.n_seq_max;
     out->cells_total = config.n_ctx;
     out->cells_used = kv->cells_used();
-    out->kv_bytes = (kcache_.count + vcache_.count) * sizeof(__half);
+    out->kv_bytes = (kcache_.count + vcache_.count) * sizeof(__half) + kq_.count + vq_.count;
     out->recurrent_bytes = 0;
     return STATUS_OK;
 }

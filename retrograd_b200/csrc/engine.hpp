@@ -344,8 +344,11 @@ private:
     void flush_kv_updates();
     KvLayout kv_layout() const;
 
-    DeviceBuffer<__half> kcache_, vcache_;
+    DeviceBuffer<__half> kcache_, vcache_;             // the F16 pool (every layer), or - over a quantised pool - one layer of f16 scratch
     uint64_t kv_layer_stride_ = 0;
+    DeviceBuffer<uint8_t> kq_, vq_;                    // the quantised pool (kv_dtype Q8_0 / Q4_0)
+    uint64_t kv_q_layer_stride_ = 0;                   // bytes per layer
+    int32_t kv_storage_ = KV_F16;
     DeviceBuffer<int32_t> block_table_;
     DeviceBuffer<int32_t> maps_store_;
     DeviceBuffer<uint8_t> d_stage_;

@@ -192,35 +192,119 @@ __global__ void kv_block_copy_kernel(KvLayout kv, int n_layer, const int32_t * _
     const int32_t src = pairs[2 * pair], dst = pairs[2 * pair + 1];
     RB_CHECK(kv.check, CHECK_BLOCK, src, kv.n_blocks, return);
     RB_CHECK(kv.check, CHECK_BLOCK, dst, kv.n_blocks, return);
-    const size_t block_elems = (size_t)kv.n_head_kv * kv.block_tokens * kv.head_dim;
-    const uint4 * ks = reinterpret_cast<const uint4 *>(kv.k + layer * kv.layer_stride + src * block_elems);
-    uint4 * kd = reinterpret_cast<uint4 *>(kv.k + layer * kv.layer_stride + dst * block_elems);
-    const uint4 * vs = reinterpret_cast<const uint4 *>(kv.v + layer * kv.layer_stride + src * block_elems);
-    uint4 * vd = reinterpret_cast<uint4 *>(kv.v + layer * kv.layer_stride + dst * block_elems);
-    const size_t n16 = block_elems * 2 / 16;
-    for (size_t i = threadIdx.x; i < n16; i += blockDim.x) {
+    const bool quant = kv.storage != KV_F16;
+    // bytes of one block (rows are multiples of 8 bytes, a block holds block_tokens = 16 of them per head)
+    const size_t block_bytes = (size_t)kv.n_head_kv * kv.block_tokens * (quant ? (size_t)kv.q_row_bytes : (size_t)kv.head_dim * 2);
+    const uint8_t * kbase = quant ? kv.kq + layer * kv.q_layer_stride : reinterpret_cast<const uint8_t *>(kv.k + layer * kv.layer_stride);
+    const uint8_t * vbase = quant ? kv.vq + layer * kv.q_layer_stride : reinterpret_cast<const uint8_t *>(kv.v + layer * kv.layer_stride);
+    const uint2 * ks = reinterpret_cast<const uint2 *>(kbase + src * block_bytes);
+    uint2 * kd = reinterpret_cast<uint2 *>(const_cast<uint8_t *>(kbase) + dst * block_bytes);
+    const uint2 * vs = reinterpret_cast<const uint2 *>(vbase + src * block_bytes);
+    uint2 * vd = reinterpret_cast<uint2 *>(const_cast<uint8_t *>(vbase) + dst * block_bytes);
+    const size_t n8 = block_bytes / 8;
+    for (size_t i = threadIdx.x; i < n8; i += blockDim.x) {
         kd[i] = ks[i];
         vd[i] = vs[i];
     }
     (void)n_layer;
 }
 
-// Moves the cells of one slot between the paged cache and a dense [layer][K|V][pos][head][dim]
-// buffer (sequence snapshots). grid = (positions, layers * 2).
-__global__ void kv_snapshot_kernel(KvLayout kv, const int32_t * __restrict__ table, int pos_first, __half * __restrict__ dense, int n_pos,
+// Moves the cells of one slot between the paged cache and a dense [layer][K|V][pos][head][row]
+// buffer (sequence snapshots); a row is head_dim f16 values or the quantised pool's row bytes. grid = (positions, layers * 2).
+__global__ void kv_snapshot_kernel(KvLayout kv, const int32_t * __restrict__ table, int pos_first, uint16_t * __restrict__ dense, int n_pos,
                                    int to_cache) {
     const int p = blockIdx.x, layer = blockIdx.y >> 1, is_v = blockIdx.y & 1;
     const int pos = pos_first + p;
     RB_CHECK(kv.check, CHECK_POSITION, pos, (long long)kv.max_blocks * kv.block_tokens, return);
     const int blk = table[pos / kv.block_tokens], off = pos % kv.block_tokens;
     RB_CHECK(kv.check, CHECK_BLOCK, blk, kv.n_blocks, return);
-    __half * cache = (is_v ? kv.v : kv.k) + layer * kv.layer_stride;
-    const int row = kv.n_head_kv * kv.head_dim;
-    __half * d = dense + ((size_t)blockIdx.y * n_pos + p) * row;
+    const bool quant = kv.storage != KV_F16;
+    const int row_u16 = quant ? kv.q_row_bytes / 2 : kv.head_dim;         // 16-bit words per (cell, head) row
+    uint16_t * cache = quant ? reinterpret_cast<uint16_t *>((is_v ? kv.vq : kv.kq) + layer * kv.q_layer_stride)
+                             : reinterpret_cast<uint16_t *>((is_v ? kv.v : kv.k) + layer * kv.layer_stride);
+    const int row = kv.n_head_kv * row_u16;
+    uint16_t * d = dense + ((size_t)blockIdx.y * n_pos + p) * row;
     for (int idx = threadIdx.x; idx < row; idx += blockDim.x) {
-        const int h = idx / kv.head_dim, i = idx % kv.head_dim;
-        const size_t c = (((size_t)blk * kv.n_head_kv + h) * kv.block_tokens + off) * kv.head_dim + i;
+        const int h = idx / row_u16, i = idx % row_u16;
+        const size_t c = (((size_t)blk * kv.n_head_kv + h) * kv.block_tokens + off) * row_u16 + i;
         if (to_cache) cache[c] = d[idx]; else d[idx] = cache[c];
+    }
+}
+
+// Quantised KV pools: the step's K rows (after RoPE) and V rows from the qkv buffer into the pool. grid (tokens, 2 * kv
+// heads), one warp per 32-element block of the head row, lane j its element j: the arithmetic of ggml's reference
+// quantisers (quantize_row_q8_0_ref: d = amax / 127, q = roundf(x / d); quantize_row_q4_0_ref: d = the element of
+// largest magnitude (the first of equals) / -8, q = min(15, (int)(x / d + 8.5))), the scale stored as f16.
+__global__ void kv_quant_store_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer, const int32_t * __restrict__ tok_cell) {
+    const int t = blockIdx.x, is_v = blockIdx.y >= kv.n_head_kv ? 1 : 0, h = blockIdx.y - is_v * kv.n_head_kv;
+    const int lane = threadIdx.x & 31, b = threadIdx.x >> 5;            // block b of the head row
+    const int cell = tok_cell[t];
+    RB_CHECK(kv.check, CHECK_CELL, cell, (long long)kv.n_blocks * kv.block_tokens, return);
+    const int blk = cell / kv.block_tokens, off = cell % kv.block_tokens;
+    const float x = qkv[(size_t)t * ld + (size_t)(n_head + is_v * kv.n_head_kv + h) * kv.head_dim + b * 32 + lane];
+    uint8_t * row = (is_v ? kv.vq : kv.kq) + layer * kv.q_layer_stride + (((size_t)blk * kv.n_head_kv + h) * kv.block_tokens + off) * kv.q_row_bytes;
+    float a = fabsf(x);
+    int who = lane;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, a, o);
+        const int ow = __shfl_xor_sync(0xffffffffu, who, o);
+        if (oa > a || (oa == a && ow < who)) { a = oa; who = ow; }
+    }
+    if (kv.storage == KV_Q8_0) {
+        const float d = a / 127.f;
+        const float id = d != 0.f ? 1.0f / d : 0.f;
+        row[b * 32 + lane] = (uint8_t)(int8_t)(int)roundf(x * id);
+        if (lane == 0) reinterpret_cast<__half *>(row + kv.head_dim)[b] = __float2half_rn(d);
+    } else {
+        const float mx = __shfl_sync(0xffffffffu, x, who);
+        const float d = mx / -8.f;
+        const float id = d != 0.f ? 1.0f / d : 0.f;
+        const int q = min(15, (int)(int8_t)(x * id + 8.5f));
+        const int hi = __shfl_down_sync(0xffffffffu, q, 16);
+        if (lane < 16) row[b * 16 + lane] = (uint8_t)(q | (hi << 4));
+        if (lane == 0) reinterpret_cast<__half *>(row + kv.head_dim / 2)[b] = __float2half_rn(d);
+    }
+}
+
+// Quantised KV pools: every pool block row r of the step may attend to, dequantised (scale * quant in f32, rounded
+// to f16) into the one-layer f16 scratch under the same block number. grid (rows, blocks of the longest row).
+__global__ void kv_dequant_kernel(KvLayout kv, int layer, const int32_t * __restrict__ cu_rows, const int32_t * __restrict__ tok_slot,
+                                  const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min) {
+    const int i0 = cu_rows[blockIdx.x], n = cu_rows[blockIdx.x + 1] - i0;
+    if (n <= 0) return;
+    const int slot = tok_slot[i0], last = tok_pos[i0] + n - 1, pmin = tok_pos_min[i0];
+    const int bi = (pmin / kv.block_tokens) + blockIdx.y;
+    if (bi > last / kv.block_tokens) return;
+    const int blk = rb_block(kv, kv.block_table[(size_t)slot * kv.max_blocks + bi]);
+    const int hd = kv.head_dim, rows = kv.n_head_kv * kv.block_tokens;          // (head, cell) rows of the block
+    const bool q8 = kv.storage == KV_Q8_0;
+    const int words = q8 ? hd / 4 : hd / 8;                                      // 32-bit words of quants per row
+    for (int idx = threadIdx.x; idx < 2 * rows * words; idx += blockDim.x) {
+        const int w = idx % words, r = (idx / words) % rows, is_v = idx / (words * rows);
+        const uint8_t * row = (is_v ? kv.vq : kv.kq) + layer * kv.q_layer_stride + ((size_t)blk * rows + r) * kv.q_row_bytes;
+        __half * dst = (is_v ? kv.v : kv.k) + ((size_t)blk * rows + r) * hd;
+        const uint32_t word = reinterpret_cast<const uint32_t *>(row)[w];
+        if (q8) {
+            const float d = __half2float(reinterpret_cast<const __half *>(row + hd)[w / 8]);
+            __half2 o[2];
+            o[0] = __floats2half2_rn(d * (float)(int8_t)(word & 0xff), d * (float)(int8_t)((word >> 8) & 0xff));
+            o[1] = __floats2half2_rn(d * (float)(int8_t)((word >> 16) & 0xff), d * (float)(int8_t)(word >> 24));
+            *reinterpret_cast<uint2 *>(dst + 4 * w) = *reinterpret_cast<const uint2 *>(o);
+        } else {
+            // word w: bytes 4 (w % 4) .. + 3 of block w / 4; a byte's low nibble is element j, its high nibble element j + 16
+            const int b = w / 4, j = 4 * (w % 4);
+            const float d = __half2float(reinterpret_cast<const __half *>(row + hd / 2)[b]);
+            __half2 lo[2], hi[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t b0 = (word >> (16 * e)) & 0xff, b1 = (word >> (16 * e + 8)) & 0xff;
+                lo[e] = __floats2half2_rn(d * (float)((int)(b0 & 15) - 8), d * (float)((int)(b1 & 15) - 8));
+                hi[e] = __floats2half2_rn(d * (float)((int)(b0 >> 4) - 8), d * (float)((int)(b1 >> 4) - 8));
+            }
+            *reinterpret_cast<uint2 *>(dst + b * 32 + j) = *reinterpret_cast<const uint2 *>(lo);
+            *reinterpret_cast<uint2 *>(dst + b * 32 + 16 + j) = *reinterpret_cast<const uint2 *>(hi);
+        }
     }
 }
 
@@ -814,10 +898,21 @@ void launch_kv_block_copy(KvLayout kv, int n_layer, const int32_t * pairs, int n
     kv_block_copy_kernel<<<dim3(n_pairs, n_layer), 256, 0, stream>>>(kv, n_layer, pairs);
 }
 
-void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int pos_first, int n_pos, __half * dense, bool to_cache,
+void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int pos_first, int n_pos, void * dense, bool to_cache,
                         cudaStream_t stream) {
     if (n_pos <= 0) return;
-    kv_snapshot_kernel<<<dim3(n_pos, n_layer * 2), 128, 0, stream>>>(kv, table_row, pos_first, dense, n_pos, to_cache ? 1 : 0);
+    kv_snapshot_kernel<<<dim3(n_pos, n_layer * 2), 128, 0, stream>>>(kv, table_row, pos_first, static_cast<uint16_t *>(dense), n_pos, to_cache ? 1 : 0);
+}
+
+void launch_kv_quant_store(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_cell, cudaStream_t stream) {
+    if (n_tokens <= 0) return;
+    kv_quant_store_kernel<<<dim3(n_tokens, 2 * kv.n_head_kv), kv.head_dim, 0, stream>>>(qkv, ld, n_head, kv, layer, tok_cell);
+}
+
+void launch_kv_dequant(KvLayout kv, int layer, int n_rows, int max_row_blocks, const int32_t * cu_rows, const int32_t * tok_slot,
+                       const int32_t * tok_pos, const int32_t * tok_pos_min, cudaStream_t stream) {
+    if (n_rows <= 0 || max_row_blocks <= 0) return;
+    kv_dequant_kernel<<<dim3(n_rows, max_row_blocks), 256, 0, stream>>>(kv, layer, cu_rows, tok_slot, tok_pos, tok_pos_min);
 }
 
 void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream, int * check) {

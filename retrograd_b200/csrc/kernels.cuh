@@ -232,10 +232,21 @@ struct PackMaps {
     int * check = nullptr;
 };
 
+// Storage types of the KV pool. F16: the pool is what the attention kernels read. Q8_0 / Q4_0 (ggml's block formats:
+// per 32 elements an f16 scale and 32 int8, or 16 bytes of nibble pairs): the pool holds `q_row_bytes` per (block,
+// head, cell) - the row's quants, then its scales - and `k` / `v` point to a one-layer f16 scratch with the pool's
+// block numbering (`layer_stride` 0) that kv_dequant fills, per layer, for the sequences of the step.
+enum KvStorage : int32_t { KV_F16 = 0, KV_Q8_0 = 1, KV_Q4_0 = 2 };
+
 struct KvLayout {
     __half * k;            // [n_blocks][n_head_kv][block_tokens][head_dim] per layer, layers consecutive
     __half * v;
     uint64_t layer_stride; // elements per layer
+    uint8_t * kq = nullptr;      // quantised pool: [n_blocks][n_head_kv][block_tokens][q_row_bytes] per layer
+    uint8_t * vq = nullptr;
+    uint64_t q_layer_stride = 0; // bytes per layer
+    int32_t storage = KV_F16;
+    int32_t q_row_bytes = 0;
     int32_t n_head_kv;
     int32_t head_dim;
     int32_t block_tokens;
@@ -264,9 +275,21 @@ void launch_block_table_patch(int32_t * block_table, const int32_t * patches, in
                               int * check = nullptr);
 void launch_kv_block_copy(KvLayout kv, int n_layer, const int32_t * pairs, int n_pairs, cudaStream_t stream);
 
-// Sequence snapshots: dense is [layer][K|V][pos][head][dim] f16 for positions pos_first .. pos_first + n_pos - 1.
-void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int pos_first, int n_pos, __half * dense, bool to_cache,
+// Sequence snapshots: dense is [layer][K|V][pos][head][row] for positions pos_first .. pos_first + n_pos - 1, a row
+// being head_dim f16 values or the quantised pool's q_row_bytes.
+void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int pos_first, int n_pos, void * dense, bool to_cache,
                         cudaStream_t stream);
+// bytes of one (cell, head) row of the pool
+inline int kv_row_bytes(int storage, int head_dim) {
+    const int raw = storage == KV_Q8_0 ? head_dim + head_dim / 32 * 2 : storage == KV_Q4_0 ? head_dim / 2 + head_dim / 32 * 2 : head_dim * 2;
+    return (raw + 7) & ~7;      // rows start on 8-byte boundaries
+}
+// Quantised pools. Store: the step's K (rotated) and V rows from the qkv buffer, quantised per 32 elements as ggml's
+// quantize_row_q8_0_ref / quantize_row_q4_0_ref do. Dequant: every block that row r of the step may attend to
+// (cu_rows / tok_* are the packing maps; `max_row_blocks` bounds the blocks of any row), into the f16 scratch.
+void launch_kv_quant_store(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_cell, cudaStream_t stream);
+void launch_kv_dequant(KvLayout kv, int layer, int n_rows, int max_row_blocks, const int32_t * cu_rows, const int32_t * tok_slot,
+                       const int32_t * tok_pos, const int32_t * tok_pos_min, cudaStream_t stream);
 
 void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream, int * check = nullptr);
 // y[t] = x[gather ? gather[t] : t] * rsqrt(mean(x^2) + eps) * w
