@@ -455,6 +455,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kv-dtype", default="f16", choices=["f16", "q8_0", "q4_0"],
+                    help="storage type of the KV pool (engine kv_dtype); the headline workload is defined on f16")
     ap.add_argument("--graphs", action="store_true",
                     help="time the steps with the engine's profiler off, so repeated step shapes replay as CUDA graphs; the per-class "
                          "times and the roofline then come from a second, profiled pass of the same number of steps")
@@ -518,7 +520,8 @@ def main():
             ep_parity["error"] = errors[0]
         dist.barrier()
 
-    engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=cfg["n_ctx"], n_seq_max=cfg["n_requests"], n_batch=cfg["n_batch"], n_ubatch=cfg["n_batch"]))
+    engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=cfg["n_ctx"], n_seq_max=cfg["n_requests"], n_batch=cfg["n_batch"], n_ubatch=cfg["n_batch"],
+                                                  kv_dtype={"f16": rb.KV_DTYPE_F16, "q8_0": rb.KV_DTYPE_Q8_0, "q4_0": rb.KV_DTYPE_Q4_0}[args.kv_dtype]))
     sampling = rb.SamplingParamsV2.greedy()
     driver = Driver(rb, engine, cfg, Workload(cfg, seed=1000 + rank), sampling)
     if cfg.get("adapters"):
@@ -575,7 +578,9 @@ def main():
     gemm_flops = 0
     gemm_bytes = 0      # algorithmic bytes of the weight GEMMs: weights once per step, activations in (hi + lo, 4 B per element) and out (f32)
     step_tokens = 0
-    kv_tok_bytes = 2 * cfg["spec"]["layers"] * cfg["spec"]["kv_heads"] * (cfg["spec"].get("head_dim") or cfg["spec"]["d"] // cfg["spec"]["heads"]) * 2
+    # bytes of K and V one resident token holds over all layers: 2 per value in f16, 34 / 32 in Q8_0, 18 / 32 in Q4_0
+    kv_value_bytes = {"f16": 2.0, "q8_0": 34.0 / 32.0, "q4_0": 18.0 / 32.0}[args.kv_dtype]
+    kv_tok_bytes = 2 * cfg["spec"]["layers"] * cfg["spec"]["kv_heads"] * (cfg["spec"].get("head_dim") or cfg["spec"]["d"] // cfg["spec"]["heads"]) * kv_value_bytes
     sp = cfg["spec"]
     hd = sp.get("head_dim") or sp["d"] // sp["heads"]
     w_elems_layer = sp["d"] * (sp["heads"] * hd + 2 * sp["kv_heads"] * hd) + sp["heads"] * hd * sp["d"] + 3 * sp["d"] * sp["ff"]
@@ -713,7 +718,7 @@ def main():
                    "arrivals": "closed loop: a new request is admitted the moment a slot frees (the saturated steady state of the arrival process)",
                    "rows_per_step": statistics.mean(rows_per_step), "decode_tokens_per_step": decode_tokens / args.steps / world,
                    "prefill_tokens_per_step": prefill_tokens / args.steps / world, "tokens_per_step": step_tokens_all / args.steps / world,
-                   "ramp_steps": ramp_steps, "cuda_graphs": bool(args.graphs),
+                   "ramp_steps": ramp_steps, "cuda_graphs": bool(args.graphs), "kv_dtype": args.kv_dtype,
                    "l2": "inputs larger than L2: every step streams >4 GB of weights and the ragged KV"},
         "e2e": {"value": decode_tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": h2d / args.steps, "d2h_bytes_per_step": d2h / args.steps},
         "gpu_launches": int(launches),

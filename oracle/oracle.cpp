@@ -974,6 +974,9 @@ int32_t ora_lora_load(void * mp, const char * path, float scale) {
     }
 }
 
+// What a cache of `kv_dtype` returns for the row `src` of n values (n a multiple of 32 for the quantised types)
+void ora_kv_round(int kv_dtype, const float * src, float * dst, uint64_t n) { kv_store_row(kv_dtype, src, dst, (size_t)n); }
+
 // kv_dtype: retro_engine_kv_dtype (0 F32, 1 F16, 2 Q8_0, 3 Q4_0); the quantised types need head_dim % 32 == 0
 void * ora_ctx_new(void * m, uint32_t n_slots, uint32_t n_ctx_seq, int kv_dtype) {
     Ctx * c = new Ctx{(Model *)m, n_slots, n_ctx_seq, kv_dtype, {}, {}};

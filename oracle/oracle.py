@@ -73,6 +73,8 @@ def lib() -> C.CDLL:
         l.ora_ctx_new.restype = C.c_void_p
         l.ora_ctx_new.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_int]
         l.ora_ctx_free.argtypes = [C.c_void_p]
+        l.ora_kv_round.restype = None
+        l.ora_kv_round.argtypes = [C.c_int, _P(C.c_float), _P(C.c_float), C.c_uint64]
         l.ora_step.argtypes = [C.c_void_p, C.c_size_t, _P(C.c_int32), _P(C.c_uint32), _P(C.c_int32), _P(C.c_uint8), _P(C.c_int32), _P(C.c_int32), _P(C.c_float)]
         l.ora_pack.restype = C.c_size_t
         l.ora_pack.argtypes = [C.c_size_t, _P(C.c_int32), _P(C.c_uint32), _P(C.c_int32), _P(C.c_uint8)] + [_P(C.c_int32)] * 5 + [_P(C.c_size_t)]
@@ -266,6 +268,14 @@ def log_softmax_terms(logits: np.ndarray):
     mx, ls = C.c_float(), C.c_double()
     lib().ora_log_softmax_terms(_f32(logits), logits.size, C.byref(mx), C.byref(ls))
     return mx.value, ls.value
+
+
+def kv_round(kv_dtype: int, row: np.ndarray) -> np.ndarray:
+    """What a cache of `kv_dtype` (retro_engine_kv_dtype: 0 F32, 1 F16, 2 Q8_0, 3 Q4_0) returns for a stored row."""
+    row = np.ascontiguousarray(row, dtype=np.float32)
+    out = np.empty_like(row)
+    lib().ora_kv_round(int(kv_dtype), _f32(row), _f32(out), row.size)
+    return out
 
 
 def token_logprob(logits: np.ndarray, token: int) -> np.float32:

@@ -14,6 +14,10 @@ from .engine import (
     EngineError,
     Grammar,
     InvalidArgument,
+    KV_DTYPE_F16,
+    KV_DTYPE_F32,
+    KV_DTYPE_Q4_0,
+    KV_DTYPE_Q8_0,
     SamplingParams,
     SamplingParamsV2,
     StepOutput,
@@ -37,6 +41,10 @@ __all__ = [
     "EngineError",
     "Grammar",
     "InvalidArgument",
+    "KV_DTYPE_F16",
+    "KV_DTYPE_F32",
+    "KV_DTYPE_Q4_0",
+    "KV_DTYPE_Q8_0",
     "LIB_PATH",
     "SamplingParams",
     "SamplingParamsV2",

@@ -235,6 +235,270 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_kernel(const flo
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same work over a Q8_0 pool, read as stored: half the bytes per key of the f16 pool, no dequantised copy.
+// A pool row is [head_dim int8 | head_dim / 32 f16 scales] (kv_row_bytes); a block's 16 rows of K (or V) are one
+// contiguous run that the warp copies into its ring as it is. The int8 quants are exact f16 operands, the scales are
+// applied in f32:
+//   - S^T: one accumulator per 32-element quant block (two K = 16 steps each), then s = sum_b scale[key][b] * acc_b.
+//     The order of K inside an MMA step and of the keys among the MMA's rows is free as long as both operands agree,
+//     so a lane reads eight consecutive quants of a block with one 64-bit load (word w feeds step w: bytes 0, 1 as the
+//     k = 2 tq pair, bytes 2, 3 as the k = 2 tq + 8 pair) and MMA row m holds key pi(m) = 4 ((m & 7) >> 1) + (m & 1) +
+//     2 (m >> 3), which makes the probabilities' B operand (after the transpose) carry keys 4 tq .. 4 tq + 3 - the four
+//     V rows this lane reads;
+//   - O^T: per 32-wide chunk of the head dimension (one quant block of V) the probabilities are scaled by that chunk's
+//     scale of their key, split into two f16 terms and transposed; a lane reads one word (d = 4 g .. 4 g + 3 of the
+//     chunk) from each of its four keys and pairs the bytes of two keys into the f16 pairs of two M tiles whose rows
+//     are d = 4 g, 4 g + 1 (tile 2 c) and 4 g + 2, 4 g + 3 (tile 2 c + 1) - the merge below writes them back in order.
+// int8 -> f16: (q ^ 0x80) is q + 128 as an unsigned byte and 0x6400 | byte the f16 value 1152 + q. V subtracts the 1152
+// per element; K does not: its MMAs run on 1152 + q and the block's accumulator is corrected by 1152 times the sum of
+// the query's (two-term) elements of that block, which a lane computes once for the two columns it accumulates.
+template <int HD>
+__global__ void __launch_bounds__(D8_THREADS) attention_decode8_q8_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer,
+                                                                           const int2 * __restrict__ items, const int32_t * __restrict__ tok_slot,
+                                                                           const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min,
+                                                                           float * __restrict__ out, int ldo, int n_splits, float * __restrict__ partial) {
+    constexpr int ROWB = (HD + HD / 16 + 7) & ~7;          // bytes of a pool row (kv_row_bytes)
+    constexpr int NB = HD / 32;                            // quant blocks per row
+    constexpr int MT = HD / 16;
+    constexpr int TILE_BYTES = 16 * ROWB;                  // one K or V block of one head
+    extern __shared__ __align__(128) uint8_t smem[];
+    pdl_trigger();
+    pdl_wait();
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, tq = lane & 3;
+    const int hk = blockIdx.y, split = blockIdx.z;
+    const int G = n_head / kv.n_head_kv;
+    const int2 item = items[blockIdx.x];
+    const int i0 = item.x, ntok = item.y;
+    const int cols = ntok * G;
+    if (cols > 8) return;                                   // served by the wider kernels
+    const int slot = tok_slot[i0], pos0 = tok_pos[i0], pmin = tok_pos_min[i0];
+    const int last = pos0 + ntok - 1;
+    const int32_t * table = kv.block_table + (size_t)slot * kv.max_blocks;
+    const uint8_t * kbase = kv.kq + layer * kv.q_layer_stride;
+    const uint8_t * vbase = kv.vq + layer * kv.q_layer_stride;
+    const float scale = rsqrtf((float)HD);
+
+    const int nb0 = pmin >> 4, nb1 = last >> 4;
+    const int n_blocks = nb1 - nb0 + 1;
+    const int per = (n_blocks + n_splits - 1) / n_splits;
+    const int b_lo = split * per, b_hi = min(n_blocks, b_lo + per);
+    const int nw = b_hi > b_lo + warp ? (b_hi - b_lo - warp + 3) >> 2 : 0;      // this warp's blocks: b_lo + warp + 4 j
+
+    uint8_t * ring = smem + (size_t)warp * D8_SLOTS * 2 * TILE_BYTES;
+    auto load_block = [&](int j) {
+        const int blk = rb_block(kv, table[nb0 + b_lo + warp + 4 * j]);
+        const size_t base = ((size_t)blk * kv.n_head_kv + hk) * TILE_BYTES;
+        const uint32_t k_s = smem_u32(ring + (j % D8_SLOTS) * 2 * TILE_BYTES), v_s = k_s + TILE_BYTES;
+        for (int c = lane; c < TILE_BYTES / 16; c += 32) {
+            cp_async16(k_s + c * 16, kbase + base + (size_t)c * 16, 16);
+            cp_async16(v_s + c * 16, vbase + base + (size_t)c * 16, 16);
+        }
+    };
+#pragma unroll
+    for (int j = 0; j < D8_SLOTS - 1; ++j) {
+        if (j < nw) load_block(j);
+        cp_async_commit();
+    }
+
+    // ---- query fragments of column g = (token g / G, head g % G): step 2 b + w holds elements 32 b + 8 tq + 4 w .. + 3
+    uint32_t qh[2 * NB][2], ql[2 * NB][2];
+    {
+        const bool valid = g < cols;
+        const float * src = qkv + (size_t)(i0 + (valid ? g / G : 0)) * ld + (size_t)(hk * G + (valid ? g % G : 0)) * HD;
+#pragma unroll
+        for (int ks = 0; ks < 2 * NB; ++ks) {
+            const float4 v = valid ? *reinterpret_cast<const float4 *>(src + (ks >> 1) * 32 + 8 * tq + 4 * (ks & 1)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float e[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+                const __half2 hh = __floats2half2_rn(e[2 * hlf], e[2 * hlf + 1]);
+                const float2 back = __half22float2(hh);
+                qh[ks][hlf] = *reinterpret_cast<const uint32_t *>(&hh);
+                ql[ks][hlf] = pack_h2(e[2 * hlf] - back.x, e[2 * hlf + 1] - back.y);
+            }
+        }
+    }
+    const int colA = 2 * tq, colB = 2 * tq + 1;
+    const int prowA = colA < cols ? pos0 + colA / G : -1;
+    const int prowB = colB < cols ? pos0 + colB / G : -1;
+    const int key0 = 4 * (g >> 1) + (g & 1), key1 = key0 + 2;      // the keys of this lane's accumulator rows g and g + 8
+    // 1152 x the sum over quant block b of the query terms, for this lane's accumulator columns 2 tq and 2 tq + 1
+    float corrA[NB], corrB[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&qh[2 * b + w][hlf]));
+                const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&ql[2 * b + w][hlf]));
+                sum += (a.x + c.x) + (a.y + c.y);
+            }
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);       // the four lanes of column g hold the block's 32 elements
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        corrA[b] = 1152.f * __shfl_sync(0xffffffffu, sum, colA * 4);
+        corrB[b] = 1152.f * __shfl_sync(0xffffffffu, sum, colB * 4);
+    }
+    auto raw_lo = [](uint32_t w) { return __byte_perm(w, 0x64646464u, 0x4140); };     // f16 pair (1152 + q) of bytes 0, 1
+    auto raw_hi = [](uint32_t w) { return __byte_perm(w, 0x64646464u, 0x4342); };     // ... of bytes 2, 3
+    const __half2 bias2 = __floats2half2_rn(1152.f, 1152.f);
+    auto pair_lo = [&](uint32_t w) { const uint32_t t = __byte_perm(w, 0x64646464u, 0x4140); return __hsub2(*reinterpret_cast<const __half2 *>(&t), bias2); };
+    auto pair_hi = [&](uint32_t w) { const uint32_t t = __byte_perm(w, 0x64646464u, 0x4342); return __hsub2(*reinterpret_cast<const __half2 *>(&t), bias2); };
+    auto as_u32 = [](__half2 h) { return *reinterpret_cast<const uint32_t *>(&h); };
+
+    float o[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+
+    for (int j = 0; j < nw; ++j) {
+        cp_async_wait<D8_SLOTS - 2>();
+        __syncwarp();                                      // block j has landed; every lane is done with block j - 1
+        if (j + D8_SLOTS - 1 < nw) load_block(j + D8_SLOTS - 1);
+        cp_async_commit();
+        const uint8_t * k_s = ring + (j % D8_SLOTS) * 2 * TILE_BYTES, * v_s = k_s + TILE_BYTES;
+        // S^T: rows = keys (key0 | key1), columns = the (token, head) pairs; per quant block, then scaled
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        const __half * ks0 = reinterpret_cast<const __half *>(k_s + key0 * ROWB + HD), * ks1 = reinterpret_cast<const __half *>(k_s + key1 * ROWB + HD);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            uint2 r0 = *reinterpret_cast<const uint2 *>(k_s + key0 * ROWB + b * 32 + 8 * tq);
+            uint2 r1 = *reinterpret_cast<const uint2 *>(k_s + key1 * ROWB + b * 32 + 8 * tq);
+            r0.x ^= 0x80808080u; r0.y ^= 0x80808080u; r1.x ^= 0x80808080u; r1.y ^= 0x80808080u;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const uint32_t a0 = raw_lo(r0.x), a1 = raw_lo(r1.x), a2 = raw_hi(r0.x), a3 = raw_hi(r1.x);
+                mma_f16(acc, a0, a1, a2, a3, qh[2 * b][0], qh[2 * b][1]);
+                mma_f16(acc, a0, a1, a2, a3, ql[2 * b][0], ql[2 * b][1]);
+            }
+            {
+                const uint32_t a0 = raw_lo(r0.y), a1 = raw_lo(r1.y), a2 = raw_hi(r0.y), a3 = raw_hi(r1.y);
+                mma_f16(acc, a0, a1, a2, a3, qh[2 * b + 1][0], qh[2 * b + 1][1]);
+                mma_f16(acc, a0, a1, a2, a3, ql[2 * b + 1][0], ql[2 * b + 1][1]);
+            }
+            const float d0 = __half2float(ks0[b]), d1 = __half2float(ks1[b]);
+            s[0] += d0 * (acc[0] - corrA[b]);
+            s[1] += d0 * (acc[1] - corrB[b]);
+            s[2] += d1 * (acc[2] - corrA[b]);
+            s[3] += d1 * (acc[3] - corrB[b]);
+        }
+        const int p0 = ((nb0 + b_lo + warp + 4 * j) << 4) + key0, p1 = p0 + 2;
+        s[0] = (p0 < pmin || p0 > prowA) ? -INFINITY : s[0];
+        s[1] = (p0 < pmin || p0 > prowB) ? -INFINITY : s[1];
+        s[2] = (p1 < pmin || p1 > prowA) ? -INFINITY : s[2];
+        s[3] = (p1 < pmin || p1 > prowB) ? -INFINITY : s[3];
+        float mxA = fmaxf(s[0], s[2]), mxB = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int sh = 4; sh < 32; sh <<= 1) {
+            mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, sh));
+            mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, sh));
+        }
+        const float mnA = fmaxf(mA, mxA), mnB = fmaxf(mB, mxB);
+        const float refA = mnA == -INFINITY ? 0.f : mnA, refB = mnB == -INFINITY ? 0.f : mnB;
+        const float cA = expf(mA - refA), cB = expf(mB - refB);
+        mA = mnA;
+        mB = mnB;
+        const float e0 = expf(s[0] - refA), e1 = expf(s[1] - refB), e2 = expf(s[2] - refA), e3 = expf(s[3] - refB);
+        lA = lA * cA + (e0 + e2);
+        lB = lB * cB + (e1 + e3);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            o[mt][0] *= cA;
+            o[mt][1] *= cB;
+            o[mt][2] *= cA;
+            o[mt][3] *= cB;
+        }
+        const __half * vs0 = reinterpret_cast<const __half *>(v_s + key0 * ROWB + HD), * vs1 = reinterpret_cast<const __half *>(v_s + key1 * ROWB + HD);
+#pragma unroll
+        for (int c = 0; c < NB; ++c) {
+            // the probabilities times this chunk's V scale of their key, as two f16 terms, transposed into B operands
+            const float d0 = __half2float(vs0[c]), d1 = __half2float(vs1[c]);
+            const float f0 = e0 * d0, f1 = e1 * d0, f2 = e2 * d1, f3 = e3 * d1;
+            const __half2 h01 = __floats2half2_rn(f0, f1), h23 = __floats2half2_rn(f2, f3);
+            const float2 k01 = __half22float2(h01), k23 = __half22float2(h23);
+            const uint32_t bh0 = movmatrix_trans(as_u32(h01)), bh1 = movmatrix_trans(as_u32(h23));
+            const uint32_t bl0 = movmatrix_trans(pack_h2(f0 - k01.x, f1 - k01.y)), bl1 = movmatrix_trans(pack_h2(f2 - k23.x, f3 - k23.y));
+            // V words of keys 4 tq .. 4 tq + 3 at d = 32 c + 4 g .. + 3
+            const uint8_t * vrow = v_s + (4 * tq) * ROWB + c * 32 + 4 * g;
+            const uint32_t w0 = *reinterpret_cast<const uint32_t *>(vrow) ^ 0x80808080u, w1 = *reinterpret_cast<const uint32_t *>(vrow + ROWB) ^ 0x80808080u;
+            const uint32_t w2 = *reinterpret_cast<const uint32_t *>(vrow + 2 * ROWB) ^ 0x80808080u,
+                           w3 = *reinterpret_cast<const uint32_t *>(vrow + 3 * ROWB) ^ 0x80808080u;
+            // (key 4 tq, key 4 tq + 1) byte pairs of d offsets 0, 1 | 2, 3; the same for keys 4 tq + 2, 4 tq + 3
+            const uint32_t u01 = __byte_perm(w0, w1, 0x5140), u23 = __byte_perm(w0, w1, 0x7362);
+            const uint32_t x01 = __byte_perm(w2, w3, 0x5140), x23 = __byte_perm(w2, w3, 0x7362);
+            {
+                const uint32_t a0 = as_u32(pair_lo(u01)), a1 = as_u32(pair_hi(u01)), a2 = as_u32(pair_lo(x01)), a3 = as_u32(pair_hi(x01));
+                mma_f16(o[2 * c], a0, a1, a2, a3, bh0, bh1);
+                mma_f16(o[2 * c], a0, a1, a2, a3, bl0, bl1);
+            }
+            {
+                const uint32_t a0 = as_u32(pair_lo(u23)), a1 = as_u32(pair_hi(u23)), a2 = as_u32(pair_lo(x23)), a3 = as_u32(pair_hi(x23));
+                mma_f16(o[2 * c + 1], a0, a1, a2, a3, bh0, bh1);
+                mma_f16(o[2 * c + 1], a0, a1, a2, a3, bl0, bl1);
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int sh = 4; sh < 32; sh <<= 1) {
+        lA += __shfl_xor_sync(0xffffffffu, lA, sh);
+        lB += __shfl_xor_sync(0xffffffffu, lB, sh);
+    }
+    __syncthreads();                                        // every warp is done with its ring
+
+    // ---- merge the four warps: per warp [8 columns][HD] outputs, then max and sum per column
+    float * part_o = reinterpret_cast<float *>(smem);                       // [4][8][HD]
+    float * part_m = part_o + 4 * 8 * HD;                                   // [4][8]
+    float * part_l = part_m + 4 * 8;                                        // [4][8]
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        // M tile mt = 2 c + y: accumulator row g is d = 32 c + 4 g + 2 y, row g + 8 is d + 1
+        const int d = 32 * (mt >> 1) + 4 * g + 2 * (mt & 1);
+        float * dA = part_o + ((size_t)warp * 8 + colA) * HD + d;
+        float * dB = part_o + ((size_t)warp * 8 + colB) * HD + d;
+        dA[0] = o[mt][0];
+        dB[0] = o[mt][1];
+        dA[1] = o[mt][2];
+        dB[1] = o[mt][3];
+    }
+    if (g == 0) {
+        part_m[warp * 8 + colA] = mA;
+        part_m[warp * 8 + colB] = mB;
+        part_l[warp * 8 + colA] = lA;
+        part_l[warp * 8 + colB] = lB;
+    }
+    __syncthreads();
+    float * pdst = partial + (((size_t)blockIdx.x * kv.n_head_kv + hk) * n_splits + split) * 8 * (HD + 2);
+    for (int idx = tid; idx < cols * HD; idx += D8_THREADS) {
+        const int c = idx / HD, dcol = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, part_m[w * 8 + c]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = part_m[w * 8 + c];
+            const float f = mw == -INFINITY ? 0.f : expf(mw - M);
+            num += f * part_o[((size_t)w * 8 + c) * HD + dcol];
+            den += f * part_l[w * 8 + c];
+        }
+        if (n_splits == 1) {
+            out[(size_t)(i0 + c / G) * ldo + (size_t)(hk * G + c % G) * HD + dcol] = num / den;
+        } else {
+            pdst[(size_t)c * (HD + 2) + dcol] = num;
+            if (dcol == 0) {
+                pdst[(size_t)c * (HD + 2) + HD] = M;
+                pdst[(size_t)c * (HD + 2) + HD + 1] = den;
+            }
+        }
+    }
+}
+
 // out = merge over the splits of one (item, kv head, column): grid (items, kv heads, 8), HD threads
 template <int HD>
 __global__ void attention_decode8_merge_kernel(const float * __restrict__ partial, int n_head, int n_head_kv, const int2 * __restrict__ items,
@@ -282,12 +546,19 @@ void launch_hd8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, c
                 const SplitAct & split) {
     constexpr int smem = 4 * D8_SLOTS * 2 * (HD / 64) * 16 * 128;
     static_assert(smem >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the K/V rings");
+    constexpr int smem_q8 = 4 * D8_SLOTS * 2 * 16 * ((HD + HD / 16 + 7) & ~7);
+    static_assert(smem_q8 >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the quantised K/V rings");
     static PerDeviceOnce configured;   // function attributes are per device
     if (configured.first()) {
         cudaFuncSetAttribute(attention_decode8_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaFuncSetAttribute(attention_decode8_q8_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q8);
     }
-    launch_pdl(attention_decode8_kernel<HD>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem, stream, qkv, ld, n_head, kv, layer, items,
-               tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
+    if (kv.storage == KV_Q8_0)
+        launch_pdl(attention_decode8_q8_kernel<HD>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem_q8, stream, qkv, ld, n_head, kv, layer,
+                   items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
+    else
+        launch_pdl(attention_decode8_kernel<HD>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem, stream, qkv, ld, n_head, kv, layer, items,
+                   tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
     if (n_splits > 1)
         launch_pdl(attention_decode8_merge_kernel<HD>, dim3(n_items, kv.n_head_kv, 8), dim3(HD), 0, stream, scratch, n_head, kv.n_head_kv, items, out,
                    ldo, n_splits, split);

@@ -391,6 +391,7 @@ Engine::Engine(const std::string & path, const retro_engine_config & cfg) : conf
     RB_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
     RB_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
     if (const char * env = std::getenv("RB200_ATTN_OVERLAP")) attn_overlap_ = std::string(env) != "0";
+    if (const char * env = std::getenv("RB200_KV_Q8_NATIVE")) kv_q8_native_ = std::string(env) != "0";
     RB_CUDA(cudaEventCreate(&ev_begin_));
     RB_CUDA(cudaEventCreate(&ev_end_));
     load_model(path);
@@ -1399,6 +1400,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     const RowDesc * d_rows = reinterpret_cast<const RowDesc *>(d_stage_.ptr + off_rows);
     const int32_t * d_tokens = reinterpret_cast<const int32_t *>(d_stage_.ptr + off_tokens);
     const KvLayout kvl = kv_layout();
+    // what the decode-row kernel sees: the Q8_0 pool itself, or (storage F16) the pool / its dequantised scratch
+    KvLayout kv_rows = kvl;
+    if (kv_storage_ == KV_Q8_0 && !kv_q8_native_) kv_rows.storage = KV_F16;
 #define RB_K(cls, n, ...)            \
     do {                             \
         prof_.begin(cls, stream);    \
@@ -1459,9 +1463,13 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         if (kv_storage_ != KV_F16) {
             // the rotated K and the V rows are still in the qkv buffer: quantise them into the pool, then bring every
             // block the step's rows attend to (the new cells included, now as the pool holds them) into the f16 scratch
-            RB_K(K_ATTN, 2, launch_kv_quant_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_cell, stream);
-                 launch_kv_dequant(kvl, (int)l, (int)R, (max_ctx + (int)kBlockTokens - 1) / (int)kBlockTokens, maps.cu_rows, maps.tok_slot, maps.tok_pos,
-                                   maps.tok_pos_min, stream));
+            // (decode rows over a Q8_0 pool are read by attention_decode8's own Q8_0 kernel: only longer rows need the scratch)
+            const int pool_read_tokens = kv_storage_ == KV_Q8_0 && use_decode8 && kv_q8_native_ ? 8 / attn_group : 0;
+            const bool scratch_needed = any_wide_item || any_mid_item || pool_read_tokens == 0;
+            RB_K(K_ATTN, scratch_needed ? 2 : 1, launch_kv_quant_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_cell, stream);
+                 if (scratch_needed)
+                     launch_kv_dequant(kvl, (int)l, (int)R, (max_ctx + (int)kBlockTokens - 1) / (int)kBlockTokens, maps.cu_rows, maps.tok_slot,
+                                       maps.tok_pos, maps.tok_pos_min, pool_read_tokens, stream));
         }
         if (attn_mma_) {
             // every row of the step goes through the split-KV kernel: its merge writes the split form as well
@@ -1476,7 +1484,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                  if (overlap) {
                      RB_CUDA(cudaEventRecord(ev_fork_, stream));
                      RB_CUDA(cudaStreamWaitEvent(side_stream_, ev_fork_, 0));
-                     launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot, maps.tok_pos,
+                     launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kv_rows, (int)l, maps.attn_items, n_attn_items, maps.tok_slot, maps.tok_pos,
                                               maps.tok_pos_min, att_.ptr, dq, attn_splits, attn_scratch_.ptr, small_stream, nullptr);
                      RB_CUDA(cudaEventRecord(ev_join_, side_stream_));
                  }
@@ -1488,7 +1496,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                                           maps.tok_pos_min, att_.ptr, dq, true, stream);
                  if (any_mid_item) launch_attention_decode(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items, maps.tok_slot,
                                                            maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, use_decode8 ? 8 : 0, stream);
-                 if (n_small_items && !overlap) launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kvl, (int)l, maps.attn_items, n_attn_items,
+                 if (n_small_items && !overlap) launch_attention_decode8(qkv_.ptr, ldqkv, (int)hp.n_head, kv_rows, (int)l, maps.attn_items, n_attn_items,
                                                                          maps.tok_slot, maps.tok_pos, maps.tok_pos_min, att_.ptr, dq, attn_splits,
                                                                          attn_scratch_.ptr, stream, merge_splits ? att_split_.get() : nullptr);
                  if (overlap) RB_CUDA(cudaStreamWaitEvent(stream, ev_join_, 0)));

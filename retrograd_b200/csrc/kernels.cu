@@ -231,17 +231,21 @@ __global__ void kv_snapshot_kernel(KvLayout kv, const int32_t * __restrict__ tab
     }
 }
 
-// Quantised KV pools: the step's K rows (after RoPE) and V rows from the qkv buffer into the pool. grid (tokens, 2 * kv
-// heads), one warp per 32-element block of the head row, lane j its element j: the arithmetic of ggml's reference
+// Quantised KV pools: the step's K rows (after RoPE) and V rows from the qkv buffer into the pool. One CTA per token,
+// a warp per 32-element block of a head row in turn, lane j its element j: the arithmetic of ggml's reference
 // quantisers (quantize_row_q8_0_ref: d = amax / 127, q = roundf(x / d); quantize_row_q4_0_ref: d = the element of
 // largest magnitude (the first of equals) / -8, q = min(15, (int)(x / d + 8.5))), the scale stored as f16.
 __global__ void kv_quant_store_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer, const int32_t * __restrict__ tok_cell) {
-    const int t = blockIdx.x, is_v = blockIdx.y >= kv.n_head_kv ? 1 : 0, h = blockIdx.y - is_v * kv.n_head_kv;
-    const int lane = threadIdx.x & 31, b = threadIdx.x >> 5;            // block b of the head row
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, per_head = kv.head_dim / 32;
     const int cell = tok_cell[t];
     RB_CHECK(kv.check, CHECK_CELL, cell, (long long)kv.n_blocks * kv.block_tokens, return);
     const int blk = cell / kv.block_tokens, off = cell % kv.block_tokens;
-    const float x = qkv[(size_t)t * ld + (size_t)(n_head + is_v * kv.n_head_kv + h) * kv.head_dim + b * 32 + lane];
+    // the token's K heads, then its V heads, are one run of 2 * n_head_kv * head_dim values behind its q heads
+    for (int qb = threadIdx.x >> 5; qb < 2 * kv.n_head_kv * per_head; qb += blockDim.x >> 5) {
+    const int hh = qb / per_head, b = qb % per_head;                    // quant block b of head row hh (K heads, then V heads)
+    const int is_v = hh >= kv.n_head_kv ? 1 : 0, h = hh - is_v * kv.n_head_kv;
+    const float x = qkv[(size_t)t * ld + (size_t)(n_head + hh) * kv.head_dim + b * 32 + lane];
     uint8_t * row = (is_v ? kv.vq : kv.kq) + layer * kv.q_layer_stride + (((size_t)blk * kv.n_head_kv + h) * kv.block_tokens + off) * kv.q_row_bytes;
     float a = fabsf(x);
     int who = lane;
@@ -265,21 +269,21 @@ __global__ void kv_quant_store_kernel(const float * __restrict__ qkv, int ld, in
         if (lane < 16) row[b * 16 + lane] = (uint8_t)(q | (hi << 4));
         if (lane == 0) reinterpret_cast<__half *>(row + kv.head_dim / 2)[b] = __float2half_rn(d);
     }
+    }
 }
 
 // Quantised KV pools: every pool block row r of the step may attend to, dequantised (scale * quant in f32, rounded
-// to f16) into the one-layer f16 scratch under the same block number. grid (rows, blocks of the longest row).
+// to f16) into the one-layer f16 scratch under the same block number. grid (rows, block strides).
 __global__ void kv_dequant_kernel(KvLayout kv, int layer, const int32_t * __restrict__ cu_rows, const int32_t * __restrict__ tok_slot,
-                                  const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min) {
+                                  const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min, int skip_tokens) {
     const int i0 = cu_rows[blockIdx.x], n = cu_rows[blockIdx.x + 1] - i0;
-    if (n <= 0) return;
+    if (n <= skip_tokens) return;          // (rows this short are read from the pool by a kernel that decodes it itself)
     const int slot = tok_slot[i0], last = tok_pos[i0] + n - 1, pmin = tok_pos_min[i0];
-    const int bi = (pmin / kv.block_tokens) + blockIdx.y;
-    if (bi > last / kv.block_tokens) return;
-    const int blk = rb_block(kv, kv.block_table[(size_t)slot * kv.max_blocks + bi]);
     const int hd = kv.head_dim, rows = kv.n_head_kv * kv.block_tokens;          // (head, cell) rows of the block
     const bool q8 = kv.storage == KV_Q8_0;
     const int words = q8 ? hd / 4 : hd / 8;                                      // 32-bit words of quants per row
+    for (int bi = (pmin / kv.block_tokens) + blockIdx.y; bi <= last / kv.block_tokens; bi += gridDim.y) {
+    const int blk = rb_block(kv, kv.block_table[(size_t)slot * kv.max_blocks + bi]);
     for (int idx = threadIdx.x; idx < 2 * rows * words; idx += blockDim.x) {
         const int w = idx % words, r = (idx / words) % rows, is_v = idx / (words * rows);
         const uint8_t * row = (is_v ? kv.vq : kv.kq) + layer * kv.q_layer_stride + ((size_t)blk * rows + r) * kv.q_row_bytes;
@@ -305,6 +309,7 @@ __global__ void kv_dequant_kernel(KvLayout kv, int layer, const int32_t * __rest
             *reinterpret_cast<uint2 *>(dst + b * 32 + j) = *reinterpret_cast<const uint2 *>(lo);
             *reinterpret_cast<uint2 *>(dst + b * 32 + 16 + j) = *reinterpret_cast<const uint2 *>(hi);
         }
+    }
     }
 }
 
@@ -906,13 +911,14 @@ void launch_kv_snapshot(KvLayout kv, int n_layer, const int32_t * table_row, int
 
 void launch_kv_quant_store(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_cell, cudaStream_t stream) {
     if (n_tokens <= 0) return;
-    kv_quant_store_kernel<<<dim3(n_tokens, 2 * kv.n_head_kv), kv.head_dim, 0, stream>>>(qkv, ld, n_head, kv, layer, tok_cell);
+    kv_quant_store_kernel<<<dim3(n_tokens), 256, 0, stream>>>(qkv, ld, n_head, kv, layer, tok_cell);
 }
 
 void launch_kv_dequant(KvLayout kv, int layer, int n_rows, int max_row_blocks, const int32_t * cu_rows, const int32_t * tok_slot,
-                       const int32_t * tok_pos, const int32_t * tok_pos_min, cudaStream_t stream) {
+                       const int32_t * tok_pos, const int32_t * tok_pos_min, int skip_tokens, cudaStream_t stream) {
     if (n_rows <= 0 || max_row_blocks <= 0) return;
-    kv_dequant_kernel<<<dim3(n_rows, max_row_blocks), 256, 0, stream>>>(kv, layer, cu_rows, tok_slot, tok_pos, tok_pos_min);
+    // (a CTA walks its row's blocks in strides of grid.y: the rows that are skipped cost one short CTA each, not one per block)
+    kv_dequant_kernel<<<dim3(n_rows, std::min(max_row_blocks, 32)), 256, 0, stream>>>(kv, layer, cu_rows, tok_slot, tok_pos, tok_pos_min, skip_tokens);
 }
 
 void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream, int * check) {

@@ -75,7 +75,8 @@ def attention_case(args) -> None:
     path = os.path.join(tempfile.gettempdir(), "retrograd_b200_attention_case.gguf")
     synth_gguf(path, arch="llama", layers=1, d=4096, heads=32, kv_heads=8, ff=1024, vocab=1024, dtype="q4_k", seed=5)
     n_ctx = args.seqs * (args.ctx + 1024 + 64)
-    engine = Engine(path, EngineConfig(n_ctx=n_ctx, n_seq_max=args.seqs, n_batch=2048, n_ubatch=2048))
+    kv_code = {"f16": 1, "q8_0": 2, "q4_0": 3}[args.kv_dtype]
+    engine = Engine(path, EngineConfig(n_ctx=n_ctx, n_seq_max=args.seqs, n_batch=2048, n_ubatch=2048, kv_dtype=kv_code))
     out = StepOutput(2048, 0)
     rng = np.random.default_rng(args.seed)
     greedy = SamplingParamsV2.greedy()
@@ -95,7 +96,7 @@ def attention_case(args) -> None:
                 rest.append((s, left))
         engine.step(rows, out)
         pending = rest
-    kv_tok_bytes = 2 * 8 * 128 * 2          # one layer
+    kv_tok_bytes = 2 * 8 * 128 * {"f16": 2.0, "q8_0": 34 / 32, "q4_0": 18 / 32}[args.kv_dtype]          # one layer
     engine.profile(True, reset=True)
     kv_bytes = 0
     for it in range(args.iters):
@@ -114,7 +115,7 @@ def attention_case(args) -> None:
     prof = engine.profile_read()
     ms = prof["attention"]["ms"] / args.iters
     print(json.dumps({
-        "kernel": "attention", "mode": args.mode, "seqs": args.seqs, "ctx": args.ctx, "ms_per_step": ms,
+        "kernel": "attention", "mode": args.mode, "kv_dtype": args.kv_dtype, "seqs": args.seqs, "ctx": args.ctx, "ms_per_step": ms,
         "kv_gb_per_step": kv_bytes / args.iters / 1e9, "kv_gbs": kv_bytes / args.iters / ms / 1e6,
         "launches_per_step": prof["attention"]["launches"] / args.iters,
     }))
@@ -129,6 +130,7 @@ def main() -> None:
     ap.add_argument("--ctx", type=int, default=2048, help="attention: tokens resident per sequence before the measured steps")
     ap.add_argument("--mode", default="decode", choices=["decode", "prefill"],
                     help="attention: measured steps are one-token rows of every sequence, or 512-token chunks of two sequences")
+    ap.add_argument("--kv-dtype", default="f16", choices=["f16", "q8_0", "q4_0"], help="attention: storage type of the KV pool")
     ap.add_argument("--n-out", type=int, default=28672)
     ap.add_argument("--n-in", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)

@@ -31,19 +31,22 @@ def _prompt(seed, n, vocab=1024):
 
 
 @pytest.mark.parametrize("shape", list(SPECS))
-@pytest.mark.parametrize("dtype", list(KV))
-def test_quantised_kv_pool_matches_the_oracle(rb, oracle, models, monkeypatch, shape, dtype):
-    """Prefill chunks (tensor-core tiles), short rows, decode rows, a shared prefix with its copy-on-write block and a
-    second chunk over a resident context: every kernel that reads K / V, over a pool that holds quantised rows."""
+@pytest.mark.parametrize("dtype,native", [("q8_0", True), ("q8_0", False), ("q4_0", True)])
+def test_quantised_kv_pool_matches_the_oracle(rb, oracle, models, monkeypatch, shape, dtype, native):
+    """Prefill chunks (tensor-core tiles), short rows, decode rows (split over several CTAs: the longest context is
+    400 tokens), a shared prefix with its copy-on-write block and a second chunk over a resident context: every kernel
+    that reads K / V, over a pool that holds quantised rows. Decode rows over a Q8_0 pool are read by their own kernel
+    (`native`), or - like every other row - from the dequantised scratch."""
     path = models(f"kvq_{shape}", **SPECS[shape])
     monkeypatch.setattr(helpers, "LOGIT_TOL", TOL[dtype])
+    monkeypatch.setenv("RB200_KV_Q8_NATIVE", "1" if native else "0")
     engine = rb.Engine(str(path), rb.EngineConfig(n_ctx=2048, n_seq_max=5, n_batch=512, n_ubatch=512, kv_dtype=KV[dtype]))
     om = oracle.Model(str(path))
     octx = oracle.Context(om, 5, 2048, kv_dtype=KV[dtype])
     out = rb.StepOutput()
     rep = ParityReport()
     g = rb.SamplingParamsV2.greedy()
-    prompts = [_prompt(500, 150), _prompt(501, 70), _prompt(502, 5)]
+    prompts = [_prompt(500, 400), _prompt(501, 70), _prompt(502, 5)]
     rows = [rb.StepRow(i, i, p, 0, sample=True, sampling=g) for i, p in enumerate(prompts)]
     toks = check_step(rb, engine, octx, oracle, rows, out, rep)
     last = [toks[r][0].token for r in range(3)]
@@ -56,6 +59,7 @@ def test_quantised_kv_pool_matches_the_oracle(rb, oracle, models, monkeypatch, s
     # slot 3 shares slot 0's first 100 positions, then both go on: the boundary block is copied on write
     engine.seq_cp(0, 3, 0, 100)
     octx.seq_cp(0, 3, 0, 100)
+    assert engine.seq_pos(3) == (0, 99)
     rows = [rb.StepRow(0, 0, [last[0]], length[0], sample=True, sampling=g),
             rb.StepRow(9, 3, _prompt(503, 90), 100, sample=True, sampling=g),       # a chunk over a resident, quantised context
             rb.StepRow(1, 1, [last[1]], length[1], sample=True, sampling=g)]
@@ -63,7 +67,7 @@ def test_quantised_kv_pool_matches_the_oracle(rb, oracle, models, monkeypatch, s
     rows = [rb.StepRow(9, 3, [toks[1][0].token], 190, sample=True, sampling=g),
             rb.StepRow(0, 0, [toks[0][0].token], length[0] + 1, sample=True, sampling=g)]
     toks = check_step(rb, engine, octx, oracle, rows, out, rep)
-    print(f"kv {dtype} {shape}: max|dlogit|={rep.max_logit_diff:.3e} min margin={rep.min_margin:.3e} rows={rep.sampled}")
+    print(f"kv {dtype} {shape} native={native}: max|dlogit|={rep.max_logit_diff:.3e} min margin={rep.min_margin:.3e} rows={rep.sampled}")
     engine.close()
 
 

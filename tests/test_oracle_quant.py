@@ -112,3 +112,27 @@ def test_rms_norm_formula(oracle):
     got = oracle.rms_norm(x, w, 1e-5)
     want = x.astype(np.float64) / np.sqrt(np.mean(x.astype(np.float64) ** 2) + 1e-5) * w
     assert np.allclose(got, want, rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("name,code", [("Q8_0", 2), ("Q4_0", 3)])
+def test_kv_cache_rounding_is_the_published_row_quantiser(oracle, name, code):
+    """A quantised KV pool stores rows through ggml's reference quantisers (absent with the llama.cpp fork; the
+    reference selects the type at `crates/retrograd-ffi/runtime/src/retro_engine.cpp:84-90`). gguf-py carries the
+    same published arithmetic in numpy: quantise-then-dequantise there must equal the oracle's cache, value for value."""
+    import gguf
+    from gguf import quants
+
+    t = getattr(gguf.GGMLQuantizationType, name)
+    rng = np.random.default_rng(11 + code)
+    rows = [rng.standard_normal(256).astype(np.float32) * s for s in (1.0, 1e-3, 37.5)]
+    rows.append(np.zeros(64, dtype=np.float32))                               # d = 0: every quant decodes to 0
+    rows.append(np.array([1.0, -1.0] * 16 + [0.5, -2.0, 2.0] + [0.0] * 29, dtype=np.float32))   # equal magnitudes: the first one sets the sign
+    rows.append((np.arange(-64, 64, dtype=np.float32) + 0.5) / 7.0)              # values on rounding boundaries
+    for row in rows:
+        want = quants.dequantize(quants.quantize(row[None, :], t), t)[0]
+        got = oracle.kv_round(code, row)
+        assert np.array_equal(got, want)
+    # F16 and F32 pools
+    x = rows[0]
+    assert np.array_equal(oracle.kv_round(1, x), x.astype(np.float16).astype(np.float32))
+    assert np.array_equal(oracle.kv_round(0, x), x)
