@@ -273,7 +273,7 @@ __global__ void kv_quant_store_kernel(const float * __restrict__ qkv, int ld, in
 }
 
 // Quantised KV pools: every pool block row r of the step may attend to, dequantised (scale * quant in f32, rounded
-// to f16) into the one-layer f16 scratch under the same block number. grid (rows, block strides).
+// to f16) into the one-layer f16 scratch under the same block number. grid (rows, unit strides).
 __global__ void kv_dequant_kernel(KvLayout kv, int layer, const int32_t * __restrict__ cu_rows, const int32_t * __restrict__ tok_slot,
                                   const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min, int skip_tokens) {
     const int i0 = cu_rows[blockIdx.x], n = cu_rows[blockIdx.x + 1] - i0;
@@ -282,10 +282,13 @@ __global__ void kv_dequant_kernel(KvLayout kv, int layer, const int32_t * __rest
     const int hd = kv.head_dim, rows = kv.n_head_kv * kv.block_tokens;          // (head, cell) rows of the block
     const bool q8 = kv.storage == KV_Q8_0;
     const int words = q8 ? hd / 4 : hd / 8;                                      // 32-bit words of quants per row
-    for (int bi = (pmin / kv.block_tokens) + blockIdx.y; bi <= last / kv.block_tokens; bi += gridDim.y) {
+    // a unit of work: the 16 cells of one head of K or V of one block; the row's CTAs take units in strides of grid.y
+    const int b_first = pmin / kv.block_tokens, n_units = (last / kv.block_tokens - b_first + 1) * 2 * kv.n_head_kv;
+    for (int unit = blockIdx.y; unit < n_units; unit += gridDim.y) {
+    const int bi = b_first + unit / (2 * kv.n_head_kv), is_v = (unit / kv.n_head_kv) & 1, h = unit % kv.n_head_kv;
     const int blk = rb_block(kv, kv.block_table[(size_t)slot * kv.max_blocks + bi]);
-    for (int idx = threadIdx.x; idx < 2 * rows * words; idx += blockDim.x) {
-        const int w = idx % words, r = (idx / words) % rows, is_v = idx / (words * rows);
+    for (int idx = threadIdx.x; idx < kv.block_tokens * words; idx += blockDim.x) {
+        const int w = idx % words, r = h * kv.block_tokens + idx / words;
         const uint8_t * row = (is_v ? kv.vq : kv.kq) + layer * kv.q_layer_stride + ((size_t)blk * rows + r) * kv.q_row_bytes;
         __half * dst = (is_v ? kv.v : kv.k) + ((size_t)blk * rows + r) * hd;
         const uint32_t word = reinterpret_cast<const uint32_t *>(row)[w];
@@ -917,8 +920,9 @@ void launch_kv_quant_store(const float * qkv, int ld, int n_tokens, int n_head, 
 void launch_kv_dequant(KvLayout kv, int layer, int n_rows, int max_row_blocks, const int32_t * cu_rows, const int32_t * tok_slot,
                        const int32_t * tok_pos, const int32_t * tok_pos_min, int skip_tokens, cudaStream_t stream) {
     if (n_rows <= 0 || max_row_blocks <= 0) return;
-    // (a CTA walks its row's blocks in strides of grid.y: the rows that are skipped cost one short CTA each, not one per block)
-    kv_dequant_kernel<<<dim3(n_rows, std::min(max_row_blocks, 32)), 256, 0, stream>>>(kv, layer, cu_rows, tok_slot, tok_pos, tok_pos_min, skip_tokens);
+    // (a CTA walks its row's units in strides of grid.y: the rows that are skipped cost a few short CTAs each, not one per block)
+    kv_dequant_kernel<<<dim3(n_rows, std::min(max_row_blocks * 2 * kv.n_head_kv, 96)), 256, 0, stream>>>(kv, layer, cu_rows, tok_slot, tok_pos, tok_pos_min,
+                                                                                                        skip_tokens);
 }
 
 void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream, int * check) {
