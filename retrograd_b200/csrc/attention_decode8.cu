@@ -253,8 +253,8 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_kernel(const flo
 // int8 -> f16: (q ^ 0x80) is q + 128 as an unsigned byte and 0x6400 | byte the f16 value 1152 + q. V subtracts the 1152
 // per element; K does not: its MMAs run on 1152 + q and the block's accumulator is corrected by 1152 times the sum of
 // the query's (two-term) elements of that block, which a lane computes once for the two columns it accumulates.
-template <int HD>
-__global__ void __launch_bounds__(D8_THREADS) attention_decode8_q8_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer,
+template <int HD, int Q8_SLOTS, int MIN_CTAS>
+__global__ void __launch_bounds__(D8_THREADS, MIN_CTAS) attention_decode8_q8_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer,
                                                                            const int2 * __restrict__ items, const int32_t * __restrict__ tok_slot,
                                                                            const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min,
                                                                            float * __restrict__ out, int ldo, int n_splits, float * __restrict__ partial) {
@@ -287,18 +287,18 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_q8_kernel(const 
     const int b_lo = split * per, b_hi = min(n_blocks, b_lo + per);
     const int nw = b_hi > b_lo + warp ? (b_hi - b_lo - warp + 3) >> 2 : 0;      // this warp's blocks: b_lo + warp + 4 j
 
-    uint8_t * ring = smem + (size_t)warp * D8_SLOTS * 2 * TILE_BYTES;
+    uint8_t * ring = smem + (size_t)warp * Q8_SLOTS * 2 * TILE_BYTES;
     auto load_block = [&](int j) {
         const int blk = rb_block(kv, table[nb0 + b_lo + warp + 4 * j]);
         const size_t base = ((size_t)blk * kv.n_head_kv + hk) * TILE_BYTES;
-        const uint32_t k_s = smem_u32(ring + (j % D8_SLOTS) * 2 * TILE_BYTES), v_s = k_s + TILE_BYTES;
+        const uint32_t k_s = smem_u32(ring + (j % Q8_SLOTS) * 2 * TILE_BYTES), v_s = k_s + TILE_BYTES;
         for (int c = lane; c < TILE_BYTES / 16; c += 32) {
             cp_async16(k_s + c * 16, kbase + base + (size_t)c * 16, 16);
             cp_async16(v_s + c * 16, vbase + base + (size_t)c * 16, 16);
         }
     };
 #pragma unroll
-    for (int j = 0; j < D8_SLOTS - 1; ++j) {
+    for (int j = 0; j < Q8_SLOTS - 1; ++j) {
         if (j < nw) load_block(j);
         cp_async_commit();
     }
@@ -357,11 +357,11 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_q8_kernel(const 
     float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
 
     for (int j = 0; j < nw; ++j) {
-        cp_async_wait<D8_SLOTS - 2>();
+        cp_async_wait<Q8_SLOTS - 2>();
         __syncwarp();                                      // block j has landed; every lane is done with block j - 1
-        if (j + D8_SLOTS - 1 < nw) load_block(j + D8_SLOTS - 1);
+        if (j + Q8_SLOTS - 1 < nw) load_block(j + Q8_SLOTS - 1);
         cp_async_commit();
-        const uint8_t * k_s = ring + (j % D8_SLOTS) * 2 * TILE_BYTES, * v_s = k_s + TILE_BYTES;
+        const uint8_t * k_s = ring + (j % Q8_SLOTS) * 2 * TILE_BYTES, * v_s = k_s + TILE_BYTES;
         // S^T: rows = keys (key0 | key1), columns = the (token, head) pairs; per quant block, then scaled
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         const __half * ks0 = reinterpret_cast<const __half *>(k_s + key0 * ROWB + HD), * ks1 = reinterpret_cast<const __half *>(k_s + key1 * ROWB + HD);
@@ -546,17 +546,18 @@ void launch_hd8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, c
                 const SplitAct & split) {
     constexpr int smem = 4 * D8_SLOTS * 2 * (HD / 64) * 16 * 128;
     static_assert(smem >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the K/V rings");
-    constexpr int smem_q8 = 4 * D8_SLOTS * 2 * 16 * ((HD + HD / 16 + 7) & ~7);
-    static_assert(smem_q8 >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the quantised K/V rings");
     static PerDeviceOnce configured;   // function attributes are per device
-    if (configured.first()) {
-        cudaFuncSetAttribute(attention_decode8_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        cudaFuncSetAttribute(attention_decode8_q8_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q8);
-    }
-    if (kv.storage == KV_Q8_0)
-        launch_pdl(attention_decode8_q8_kernel<HD>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem_q8, stream, qkv, ld, n_head, kv, layer,
-                   items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
-    else
+    if (configured.first()) cudaFuncSetAttribute(attention_decode8_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (kv.storage == KV_Q8_0) {
+        // three ring slots and four CTAs per SM (128 registers): two slots with five or six CTAs (96 / 80 registers, spills)
+        // measured 7 % and 20 % slower on the ragged 256-request workload
+        constexpr int smem_q8 = 4 * D8_SLOTS * 2 * 16 * ((HD + HD / 16 + 7) & ~7);
+        static_assert(smem_q8 >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the quantised K/V rings");
+        static PerDeviceOnce once;
+        if (once.first()) cudaFuncSetAttribute(attention_decode8_q8_kernel<HD, D8_SLOTS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q8);
+        launch_pdl(attention_decode8_q8_kernel<HD, D8_SLOTS, 4>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem_q8, stream, qkv, ld, n_head,
+                   kv, layer, items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
+    } else
         launch_pdl(attention_decode8_kernel<HD>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem, stream, qkv, ld, n_head, kv, layer, items,
                    tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
     if (n_splits > 1)
