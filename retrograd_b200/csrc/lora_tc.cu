@@ -140,9 +140,9 @@ template <int NR>
 __global__ void __launch_bounds__(128) lora_expand_tc_kernel(const LoraGroup group, int r_max, const float * __restrict__ scales,
                                                              int n_adapters, const int32_t * __restrict__ offsets, const int32_t * __restrict__ sorted,
                                                              const float * __restrict__ tmp, int n_splits, int n_tokens, float * __restrict__ y, int ldy,
-                                                             int cols_per_cta, int vec2) {
+                                                             int groups_per_cta, int vec2) {
     const int n_out = group.n_out[blockIdx.z];
-    if ((int)blockIdx.y * cols_per_cta >= n_out) return;       // the grid's column groups cover the widest target
+    if ((int)blockIdx.y * groups_per_cta * 128 >= n_out) return;       // the grid's column groups cover the widest target
     const float * __restrict__ b_stack = group.b[blockIdx.z];
     tmp += (size_t)blockIdx.z * n_splits * n_tokens * r_max;
     y += group.y_offset[blockIdx.z];
@@ -166,56 +166,80 @@ __global__ void __launch_bounds__(128) lora_expand_tc_kernel(const LoraGroup gro
     }
     const float scale = scales[adapter];
     const float * br = b_stack + (size_t)adapter * n_out * r_max;
-    constexpr int CT = 4;                          // column tiles per warp
-    const int o_base = blockIdx.y * cols_per_cta + warp * (CT * 8);
-    float bv[CT][NR][2];
-    float2 y0[CT], y1[CT];
+    constexpr int CT = 4;                          // column tiles per warp and column group
+    struct Operands {
+        float bv[CT][NR][2];
+        float2 y0[CT], y1[CT];
+    };
+    // column group cg of this CTA: 128 columns, 32 per warp. Every load of a group is issued before its first MMA,
+    // and the next group's loads before this group's MMAs (the CTA's prologue - tile lookup, token ids, the shrink
+    // results - is paid once for `groups_per_cta` groups instead of once per group).
+    auto o_base_of = [&](int cg) { return ((int)blockIdx.y * groups_per_cta + cg) * 128 + warp * (CT * 8); };
+    auto load = [&](int cg, Operands & op) {
+        const int o_base = o_base_of(cg);
 #pragma unroll
-    for (int i = 0; i < CT; ++i) {
-        const int o0 = o_base + i * 8;
-        const bool row_ok = o0 + g < n_out;
-        const float * bo = br + (size_t)(o0 + g) * r_max;
+        for (int i = 0; i < CT; ++i) {
+            const int o0 = o_base + i * 8;
+            const bool row_ok = o0 + g < n_out;
+            const float * bo = br + (size_t)(o0 + g) * r_max;
 #pragma unroll
-        for (int kk = 0; kk < NR; ++kk) {
-            const int r0 = kk * 8 + t, r1 = r0 + 4;
-            bv[i][kk][0] = row_ok && r0 < r_max ? bo[r0] : 0.f;
-            bv[i][kk][1] = row_ok && r1 < r_max ? bo[r1] : 0.f;
+            for (int kk = 0; kk < NR; ++kk) {
+                const int r0 = kk * 8 + t, r1 = r0 + 4;
+                op.bv[i][kk][0] = row_ok && r0 < r_max ? bo[r0] : 0.f;
+                op.bv[i][kk][1] = row_ok && r1 < r_max ? bo[r1] : 0.f;
+            }
+            const int col = o0 + 2 * t;
+            op.y0[i] = op.y1[i] = make_float2(0.f, 0.f);
+            if (vec2 && col + 1 < n_out) {
+                if (tok0 >= 0) op.y0[i] = *reinterpret_cast<const float2 *>(y + (size_t)tok0 * ldy + col);
+                if (tok1 >= 0) op.y1[i] = *reinterpret_cast<const float2 *>(y + (size_t)tok1 * ldy + col);
+            } else {
+                if (tok0 >= 0 && col < n_out) op.y0[i].x = y[(size_t)tok0 * ldy + col];
+                if (tok0 >= 0 && col + 1 < n_out) op.y0[i].y = y[(size_t)tok0 * ldy + col + 1];
+                if (tok1 >= 0 && col < n_out) op.y1[i].x = y[(size_t)tok1 * ldy + col];
+                if (tok1 >= 0 && col + 1 < n_out) op.y1[i].y = y[(size_t)tok1 * ldy + col + 1];
+            }
         }
-        const int col = o0 + 2 * t;
-        y0[i] = y1[i] = make_float2(0.f, 0.f);
-        if (vec2 && col + 1 < n_out) {
-            if (tok0 >= 0) y0[i] = *reinterpret_cast<const float2 *>(y + (size_t)tok0 * ldy + col);
-            if (tok1 >= 0) y1[i] = *reinterpret_cast<const float2 *>(y + (size_t)tok1 * ldy + col);
-        } else {
-            if (tok0 >= 0 && col < n_out) y0[i].x = y[(size_t)tok0 * ldy + col];
-            if (tok0 >= 0 && col + 1 < n_out) y0[i].y = y[(size_t)tok0 * ldy + col + 1];
-            if (tok1 >= 0 && col < n_out) y1[i].x = y[(size_t)tok1 * ldy + col];
-            if (tok1 >= 0 && col + 1 < n_out) y1[i].y = y[(size_t)tok1 * ldy + col + 1];
-        }
-    }
+    };
+    auto finish = [&](int cg, Operands & op) {
+        const int o_base = o_base_of(cg);
 #pragma unroll
-    for (int i = 0; i < CT; ++i) {
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i = 0; i < CT; ++i) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int kk = 0; kk < NR; ++kk) {
-            uint32_t b0, s0, b1, s1;
-            split_tf32(bv[i][kk][0], b0, s0);
-            split_tf32(bv[i][kk][1], b1, s1);
-            mma_3x(c, ab[kk], as[kk], b0, b1, s0, s1);
+            for (int kk = 0; kk < NR; ++kk) {
+                uint32_t b0, s0, b1, s1;
+                split_tf32(op.bv[i][kk][0], b0, s0);
+                split_tf32(op.bv[i][kk][1], b1, s1);
+                mma_3x(c, ab[kk], as[kk], b0, b1, s0, s1);
+            }
+            const int col = o_base + i * 8 + 2 * t;
+            op.y0[i].x += scale * c[0];
+            op.y0[i].y += scale * c[1];
+            op.y1[i].x += scale * c[2];
+            op.y1[i].y += scale * c[3];
+            if (vec2 && col + 1 < n_out) {
+                if (tok0 >= 0) *reinterpret_cast<float2 *>(y + (size_t)tok0 * ldy + col) = op.y0[i];
+                if (tok1 >= 0) *reinterpret_cast<float2 *>(y + (size_t)tok1 * ldy + col) = op.y1[i];
+            } else {
+                if (tok0 >= 0 && col < n_out) y[(size_t)tok0 * ldy + col] = op.y0[i].x;
+                if (tok0 >= 0 && col + 1 < n_out) y[(size_t)tok0 * ldy + col + 1] = op.y0[i].y;
+                if (tok1 >= 0 && col < n_out) y[(size_t)tok1 * ldy + col] = op.y1[i].x;
+                if (tok1 >= 0 && col + 1 < n_out) y[(size_t)tok1 * ldy + col + 1] = op.y1[i].y;
+            }
         }
-        const int col = o_base + i * 8 + 2 * t;
-        y0[i].x += scale * c[0];
-        y0[i].y += scale * c[1];
-        y1[i].x += scale * c[2];
-        y1[i].y += scale * c[3];
-        if (vec2 && col + 1 < n_out) {
-            if (tok0 >= 0) *reinterpret_cast<float2 *>(y + (size_t)tok0 * ldy + col) = y0[i];
-            if (tok1 >= 0) *reinterpret_cast<float2 *>(y + (size_t)tok1 * ldy + col) = y1[i];
-        } else {
-            if (tok0 >= 0 && col < n_out) y[(size_t)tok0 * ldy + col] = y0[i].x;
-            if (tok0 >= 0 && col + 1 < n_out) y[(size_t)tok0 * ldy + col + 1] = y0[i].y;
-            if (tok1 >= 0 && col < n_out) y[(size_t)tok1 * ldy + col] = y1[i].x;
-            if (tok1 >= 0 && col + 1 < n_out) y[(size_t)tok1 * ldy + col + 1] = y1[i].y;
+    };
+    // groups of this CTA that start inside the target's columns
+    const int first_col = (int)blockIdx.y * groups_per_cta * 128;
+    const int n_groups = min(groups_per_cta, (n_out - first_col + 127) / 128);
+    Operands even, odd;
+    load(0, even);
+    for (int cg = 0; cg < n_groups; cg += 2) {
+        if (cg + 1 < n_groups) load(cg + 1, odd);
+        finish(cg, even);
+        if (cg + 1 < n_groups) {
+            if (cg + 2 < n_groups) load(cg + 2, even);
+            finish(cg + 1, odd);
         }
     }
 }
@@ -230,7 +254,10 @@ template <class F> void dispatch_rank_tiles(int r_max, F && f) {
 
 } // namespace
 
-int lora_tc_splits(int n_in) { return std::max(1, std::min(kLoraTcMaxSplits, n_in / 1024)); }
+int lora_tc_splits(int n_in) {
+    static const int k_per_split = [] { const char * e = std::getenv("RB200_LORA_SPLIT_K"); return e && std::atoi(e) >= 64 ? std::atoi(e) : 512; }();
+    return std::max(1, std::min(kLoraTcMaxSplits, n_in / k_per_split));
+}
 
 bool lora_tc_supported(int r_max, int n_in, const float * a_stack, const float * x, int ldx) {
     return r_max >= 1 && r_max <= 64 && n_in % 16 == 0 && ldx % 4 == 0 && (uintptr_t)a_stack % 16 == 0 && (uintptr_t)x % 16 == 0;
@@ -242,7 +269,6 @@ void launch_lora_tc(const LoraGroup & group, const float * scales, int r_max, in
     const int tiles = (n_tokens + 15) / 16 + n_adapters;          // every segment may end in a partial tile
     const int splits = lora_tc_splits(n_in);
     const int k_per_split = ((n_in + splits - 1) / splits + 15) / 16 * 16;
-    const int cols_per_cta = 128;
     int widest = 0, vec2 = ldy % 2 == 0 && (uintptr_t)y % 8 == 0 ? 1 : 0;
     for (int i = 0; i < group.n; ++i) {
         widest = std::max(widest, group.n_out[i]);
@@ -252,8 +278,13 @@ void launch_lora_tc(const LoraGroup & group, const float * scales, int r_max, in
         constexpr int NR = decltype(tag)::value;
         lora_shrink_tc_kernel<NR><<<dim3(tiles, splits, group.n), kShrinkWarps * 32, 0, stream>>>(group, r_max, n_in, n_adapters, offsets, sorted, x, ldx, tmp,
                                                                                                 n_tokens, k_per_split);
-        lora_expand_tc_kernel<NR><<<dim3(tiles, (widest + cols_per_cta - 1) / cols_per_cta, group.n), 128, 0, stream>>>(
-            group, r_max, scales, n_adapters, offsets, sorted, tmp, splits, n_tokens, y, ldy, cols_per_cta, vec2);
+        // column groups of 128 per CTA: as many as still leave a few waves of CTAs (a CTA's prologue is the larger part
+        // of a one-group CTA's life)
+        static const int forced = [] { const char * e = std::getenv("RB200_LORA_GROUPS_PER_CTA"); return e ? std::atoi(e) : 0; }();
+        const int groups = (widest + 127) / 128;
+        const int groups_per_cta = forced > 0 ? forced : std::max(1, std::min(8, tiles * groups * group.n / 600));
+        lora_expand_tc_kernel<NR><<<dim3(tiles, (groups + groups_per_cta - 1) / groups_per_cta, group.n), 128, 0, stream>>>(
+            group, r_max, scales, n_adapters, offsets, sorted, tmp, splits, n_tokens, y, ldy, groups_per_cta, vec2);
     });
 }
 
