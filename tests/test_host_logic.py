@@ -96,6 +96,9 @@ def test_engine_config_is_validated_before_anything_loads(rb):
     assert not h and msg == "a quantized engine kv_dtype requires flash_attn"
     h, msg = _new(rb, b"/nonexistent.gguf", device=7)
     assert not h and msg == "engine device must be one of retro_device"
+    # the pool is F16, Q8_0 or Q4_0 here; the reference's fourth type is refused in words before anything loads
+    h, msg = _new(rb, b"/nonexistent.gguf", kv_dtype=0)
+    assert not h and msg == "this backend stores the KV cache as F16, Q8_0 or Q4_0: engine kv_dtype F32 is not supported"
     cfg = rb.EngineConfig().to_c()
     cfg.struct_size = 8
     assert not lib.retro_engine_new(b"/nonexistent.gguf", C.byref(cfg))
