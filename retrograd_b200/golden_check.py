@@ -12,21 +12,24 @@ import numpy as np
 GOLDEN = Path(__file__).resolve().parent.parent / "tests" / "golden" / "c1_greedy_tokens.json"
 
 
-def golden_prompts(golden: dict) -> list[list[int]]:
-    rng = np.random.default_rng(golden["prompt_seed"])
+def golden_prompts(golden: dict, seed: int | None = None) -> list[list[int]]:
+    rng = np.random.default_rng(golden["prompt_seed"] if seed is None else seed)
     prefix = rng.integers(3, 4096, 32).tolist()
     return [prefix + rng.integers(3, 4096, int(rng.integers(16, 129))).tolist() for _ in range(golden["n_requests"])]
 
 
-def replay(rb, model_path: str | None = None) -> dict:
-    """Returns {"workload", "tokens", "bit_exact", "first_mismatch"}; synthesises the model when no path is given."""
+def replay(rb, model_path: str | None = None, kv: str = "f16") -> dict:
+    """Returns {"workload", "tokens", "bit_exact", "first_mismatch"}; synthesises the model when no path is given.
+    kv: "f16", or "q8_0" for the streams the oracle produced over a Q8_0 KV cache (their own prompts)."""
     golden = json.loads(GOLDEN.read_text())
-    prompts = golden_prompts(golden)
+    want_streams = golden["streams"] if kv == "f16" else golden["kv_" + kv]["streams"]
+    prompts = golden_prompts(golden, None if kv == "f16" else golden["kv_" + kv]["prompt_seed"])
+    kv_dtype = {"f16": rb.KV_DTYPE_F16, "q8_0": rb.KV_DTYPE_Q8_0}[kv]
     with tempfile.TemporaryDirectory() as tmp:
         if model_path is None:
             model_path = str(Path(tmp) / "c1.gguf")
             rb.synth_gguf(model_path, **golden["spec"])
-        engine = rb.Engine(model_path, rb.EngineConfig(n_ctx=4096, n_seq_max=len(prompts), n_batch=1024, n_ubatch=1024))
+        engine = rb.Engine(model_path, rb.EngineConfig(n_ctx=4096, n_seq_max=len(prompts), n_batch=1024, n_ubatch=1024, kv_dtype=kv_dtype))
         greedy = rb.SamplingParamsV2.greedy()
         out = rb.StepOutput(1024, 0)
         rows = [rb.StepRow(i, i, p, 0, sample=True, sampling=greedy) for i, p in enumerate(prompts)]
@@ -38,7 +41,7 @@ def replay(rb, model_path: str | None = None) -> dict:
             rows = [rb.StepRow.decode(i, i, streams[i][-1], len(prompts[i]) + step, greedy) for i in range(len(prompts))]
         engine.close()
     mismatch = None
-    for i, (got, want) in enumerate(zip(streams, golden["streams"])):
+    for i, (got, want) in enumerate(zip(streams, want_streams)):
         for j, (a, b) in enumerate(zip(got, want)):
             if a != b and mismatch is None:
                 mismatch = {"request": i, "position": j, "engine": a, "oracle": b}

@@ -84,6 +84,8 @@ def test_committed_greedy_streams_are_what_the_oracle_produces():
     spec.loader.exec_module(mk)
     golden = json.loads((here / "c1_greedy_tokens.json").read_text())
     assert golden["spec"] == mk.SPEC and golden["prompt_seed"] == mk.SEED and golden["min_top2_margin"] > 1e-3
+    q8 = golden["kv_q8_0"]
+    assert q8["prompt_seed"] == mk.SEED_KV_Q8_0 and q8["min_top2_margin"] > 1e-3
     with tempfile.TemporaryDirectory() as tmp:
         path = Path(tmp) / "c1.gguf"
         O.synth_gguf(path, **mk.SPEC)
@@ -97,4 +99,7 @@ def test_committed_greedy_streams_are_what_the_oracle_produces():
             for i, t in enumerate(toks):
                 streams[i].append(t)
             rows = [(i, [t], len(ps[i]) + step, True, 0) for i, t in enumerate(toks)]
+        q8_streams, q8_margin = mk.run(path, 2, mk.SEED_KV_Q8_0)
     assert streams == golden["streams"]
+    # the streams over a Q8_0 cache: other prompts, and a cache that changes the tokens
+    assert q8_streams == q8["streams"] and abs(q8_margin - q8["min_top2_margin"]) < 1e-6

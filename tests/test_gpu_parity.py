@@ -226,3 +226,12 @@ def test_tiny_workload_reproduces_the_committed_oracle_streams(rb):
 
     result = replay(rb)
     assert result["tokens"] == 256 and result["bit_exact"], result["first_mismatch"]
+
+
+def test_tiny_workload_over_a_q8_0_kv_pool_reproduces_the_committed_oracle_streams(rb):
+    """The same comparison with engine kv_dtype Q8_0 against the streams the oracle produced over a cache that returns
+    ggml's quantise-then-dequantise of every stored row (256 tokens; smallest oracle top-2 margin 1.2e-3)."""
+    from retrograd_b200.golden_check import replay
+
+    result = replay(rb, kv="q8_0")
+    assert result["tokens"] == 256 and result["bit_exact"], result["first_mismatch"]
