@@ -20,7 +20,11 @@
 // Conventions fixed here because the fork is absent: RoPE pairs are adjacent for
 // general.architecture=llama and half-split for qwen2/olmoe; GQA maps q head h to kv head
 // h / (Hq/Hkv); attention scale 1/sqrt(head_dim); causal mask by position within the slot; K/V
-// are rounded to f16 when stored; activations stay f32 (the in-tree GEMV oracles' semantics).
+// are rounded to f16 when stored (or, for a context of kv_dtype Q8_0 / Q4_0, pass through ggml's row quantisers);
+// activations stay f32 (the in-tree GEMV oracles' semantics, "act = f32": what parity is stated against). The
+// optional "act = q8" mode re-quantises activations in the weight matmuls the way the reference's CPU backend does
+// (tests/lora_rows.rs:16-20); it restates published ggml routines, is pinned by nothing in the reference's tree, and
+// is only ever reported beside act = f32.
 
 #include <omp.h>
 #include <algorithm>
@@ -345,6 +349,11 @@ struct Model {
     float eps = 1e-5f, rope_base = 10000.f;
     bool neox = false;
     bool fast = false;  // vectorisable accumulation for timing runs; parity runs keep serial order
+    // act = q8: the weight matmuls re-quantise every activation row to the 8-bit block format the weight type's dot
+    // product takes and multiply integers, as the reference's CPU backend does ("the quantized base re-quantizes every
+    // activation it reads", tests/lora_rows.rs:16-20). Default act = f32: the in-tree RIR oracles' semantics, which is
+    // what every parity claim of this project is made against.
+    bool act_q8 = false;
     std::map<int32_t, Lora> loras;
     int32_t next_lora = 1;
     std::vector<float> inv_freq;
@@ -359,10 +368,155 @@ struct Model {
     }
 };
 
+// ---- act = q8: ggml's CPU dot products over re-quantised activations. The library is absent with the un-vendored
+// llama.cpp fork; these restate its published reference routines (quantize_row_q8_0_ref, quantize_row_q8_K_ref,
+// ggml_vec_dot_q8_0_q8_0, ggml_vec_dot_q4_K_q8_K, ggml_vec_dot_mxfp4_q8_0 and the f16 dot for F16 weights, generic
+// forms) and are pinned by nothing here: PARITY UNPINNED, reported beside act = f32 results, never as the checker.
+struct ActQ80 { std::vector<float> d; std::vector<int8_t> q; };          // per 32 elements: f16-rounded scale, 32 quants
+struct ActQ8K { std::vector<float> d; std::vector<int8_t> q; std::vector<int16_t> bsums; };   // per 256: scale, quants, sums of 16
+
+void quantize_act_q8_0(const float * x, size_t n, ActQ80 & a) {
+    a.d.resize(n / 32);
+    a.q.resize(n);
+    for (size_t b = 0; b < n / 32; ++b) {
+        float amax = 0.f;
+        for (int j = 0; j < 32; ++j) amax = std::max(amax, std::fabs(x[b * 32 + j]));
+        const float d = amax / 127.f, id = d != 0.f ? 1.0f / d : 0.f;
+        a.d[b] = round_to_half(d);
+        for (int j = 0; j < 32; ++j) a.q[b * 32 + j] = (int8_t)std::lround(x[b * 32 + j] * id);
+    }
+}
+
+void quantize_act_q8_K(const float * x, size_t n, ActQ8K & a) {
+    a.d.resize(n / 256);
+    a.q.resize(n);
+    a.bsums.assign(n / 16, 0);
+    for (size_t b = 0; b < n / 256; ++b) {
+        float amax = 0.f, mx = 0.f;
+        for (int j = 0; j < 256; ++j) {
+            const float ax = std::fabs(x[b * 256 + j]);
+            if (ax > amax) { amax = ax; mx = x[b * 256 + j]; }
+        }
+        if (amax == 0.f) {
+            a.d[b] = 0.f;
+            for (int j = 0; j < 256; ++j) a.q[b * 256 + j] = 0;
+            continue;
+        }
+        const float iscale = -127.f / mx;
+        for (int j = 0; j < 256; ++j) {
+            const int v = (int)std::nearbyintf(iscale * x[b * 256 + j]);       // round to nearest, ties to even
+            a.q[b * 256 + j] = (int8_t)std::min(127, v);
+        }
+        for (int j = 0; j < 16; ++j) {
+            int sum = 0;
+            for (int i = 0; i < 16; ++i) sum += a.q[b * 256 + j * 16 + i];
+            a.bsums[b * 16 + j] = (int16_t)sum;
+        }
+        a.d[b] = 1.0f / iscale;
+    }
+}
+
+float dot_q8_0_q8_0(const uint8_t * w, const ActQ80 & a, size_t n) {
+    float sumf = 0.f;
+    for (size_t b = 0; b < n / 32; ++b) {
+        const uint8_t * p = w + b * 34;
+        uint16_t h;
+        std::memcpy(&h, p, 2);
+        int sumi = 0;
+        for (int j = 0; j < 32; ++j) sumi += (int)(int8_t)p[2 + j] * (int)a.q[b * 32 + j];
+        sumf += (float)sumi * (half_to_f32(h) * a.d[b]);
+    }
+    return sumf;
+}
+
+float dot_mxfp4_q8_0(const uint8_t * w, const ActQ80 & a, size_t n) {
+    float sumf = 0.f;
+    for (size_t b = 0; b < n / 32; ++b) {
+        const uint8_t * p = w + b * 17;
+        const float d = a.d[b] * e8m0_to_f32_half(p[0]);
+        int sumi = 0;
+        for (int j = 0; j < 16; ++j) {
+            sumi += (int)a.q[b * 32 + j] * KVALUES_FP4[p[1 + j] & 0x0F];
+            sumi += (int)a.q[b * 32 + j + 16] * KVALUES_FP4[p[1 + j] >> 4];
+        }
+        sumf += d * (float)sumi;
+    }
+    return sumf;
+}
+
+float dot_q4_K_q8_K(const uint8_t * w, const ActQ8K & a, size_t n) {
+    float sumf = 0.f;
+    for (size_t b = 0; b < n / 256; ++b) {
+        const uint8_t * p = w + b * 144;
+        uint16_t h0, h1;
+        std::memcpy(&h0, p, 2);
+        std::memcpy(&h1, p + 2, 2);
+        const float d = a.d[b] * half_to_f32(h0), dmin = a.d[b] * half_to_f32(h1);
+        const uint8_t * scales = p + 4, * qs = p + 16;
+        const int8_t * q8 = a.q.data() + b * 256;
+        int sum_main = 0, sum_min = 0;
+        for (int g = 0; g < 4; ++g) {
+            uint8_t sc1, m1, sc2, m2;
+            scale_min_k4(2 * g, scales, sc1, m1);
+            scale_min_k4(2 * g + 1, scales, sc2, m2);
+            int lo = 0, hi = 0;
+            for (int l = 0; l < 32; ++l) {
+                lo += (int)(qs[g * 32 + l] & 0xF) * (int)q8[g * 64 + l];
+                hi += (int)(qs[g * 32 + l] >> 4) * (int)q8[g * 64 + 32 + l];
+            }
+            sum_main += (int)sc1 * lo + (int)sc2 * hi;
+            sum_min += (int)m1 * ((int)a.bsums[b * 16 + 4 * g] + (int)a.bsums[b * 16 + 4 * g + 1]) +
+                       (int)m2 * ((int)a.bsums[b * 16 + 4 * g + 2] + (int)a.bsums[b * 16 + 4 * g + 3]);
+        }
+        sumf += d * (float)sum_main - dmin * (float)sum_min;
+    }
+    return sumf;
+}
+
+bool act_q8_applies(uint32_t type, size_t n_in) {
+    return ((type == T_Q8_0 || type == T_MXFP4) && n_in % 32 == 0) || (type == T_Q4_K && n_in % 256 == 0) || type == T_F16;
+}
+
+// Y = X W^T with the activations in the weight type's 8-bit (F16 weights: 16-bit) dot format
+void matmul_act_q8(const Tensor & w, const uint8_t * wdata, size_t n_out, const float * x, size_t T, size_t n_in, float * y, size_t y_stride) {
+    const size_t rb = w.row_bytes();
+    std::vector<ActQ80> a80(w.type == T_Q8_0 || w.type == T_MXFP4 ? T : 0);
+    std::vector<ActQ8K> a8k(w.type == T_Q4_K ? T : 0);
+    std::vector<float> xh(w.type == T_F16 ? T * n_in : 0);
+    for (size_t t = 0; t < T; ++t) {
+        if (!a80.empty()) quantize_act_q8_0(x + t * n_in, n_in, a80[t]);
+        if (!a8k.empty()) quantize_act_q8_K(x + t * n_in, n_in, a8k[t]);
+        if (!xh.empty())
+            for (size_t i = 0; i < n_in; ++i) xh[t * n_in + i] = round_to_half(x[t * n_in + i]);
+    }
+#pragma omp parallel
+    {
+        std::vector<float> row(w.type == T_F16 ? n_in : 0);
+#pragma omp for schedule(static)
+        for (int64_t o = 0; o < (int64_t)n_out; ++o) {
+            const uint8_t * wr = wdata + (size_t)o * rb;
+            if (w.type == T_F16) dequantize_row(w.type, wr, n_in, row.data());
+            for (size_t t = 0; t < T; ++t) {
+                float acc = 0.f;
+                if (w.type == T_Q8_0) acc = dot_q8_0_q8_0(wr, a80[t], n_in);
+                else if (w.type == T_MXFP4) acc = dot_mxfp4_q8_0(wr, a80[t], n_in);
+                else if (w.type == T_Q4_K) acc = dot_q4_K_q8_K(wr, a8k[t], n_in);
+                else
+                    for (size_t i = 0; i < n_in; ++i) acc += row[i] * xh[t * n_in + i];
+                y[t * y_stride + o] = acc;
+            }
+        }
+    }
+}
+
 // Y[t][o] = sum_i deq(W)[o][i] * X[t][i], f32, columns in serial order
 // (generated/rir/mul_mat_vec_q4_K/cpu.rs:52-121).
 void matmul(const Model & m, const Tensor & w, const uint8_t * wdata, size_t n_out, const float * x, size_t T, size_t n_in,
             float * y, size_t y_stride) {
+    if (m.act_q8 && act_q8_applies(w.type, n_in)) {
+        matmul_act_q8(w, wdata, n_out, x, T, n_in, y, y_stride);
+        return;
+    }
     const size_t rb = w.row_bytes();
 #pragma omp parallel
     {
@@ -881,6 +1035,18 @@ float ora_round_to_half(float v) { return round_to_half(v); }
 float ora_e8m0_half(uint8_t x) { return e8m0_to_f32_half(x); }
 
 // dst[row] = sum_col deq(a)[row][col] * b[col], serial f32
+// The act = q8 form of the GEMV below: b re-quantised to the 8-bit block format of `type`'s dot product (F16: to f16)
+int ora_mul_mat_vec_act_q8(uint32_t type, size_t n_row, size_t n_col, const uint8_t * a, const float * b, float * dst) {
+    size_t be, bb;
+    if (!geom(type, be, bb) || n_col % be || !act_q8_applies(type, n_col)) return -1;
+    Tensor w;
+    w.type = type;
+    w.ne = {n_col, n_row};
+    w.data = a;
+    matmul_act_q8(w, a, n_row, b, 1, n_col, dst, n_row);
+    return 0;
+}
+
 int ora_mul_mat_vec(uint32_t type, size_t n_row, size_t n_col, const uint8_t * a, const float * b, float * dst) {
     size_t be, bb;
     if (!geom(type, be, bb) || n_col % be) return -1;
@@ -929,6 +1095,9 @@ void * ora_model_load(const char * path) {
 void ora_model_free(void * m) { delete (Model *)m; }
 
 void ora_model_set_fast(void * m, int fast) { ((Model *)m)->fast = fast != 0; }
+
+// act = q8 (1) or act = f32 (0, the default): see Model::act_q8
+void ora_model_set_act_q8(void * m, int on) { ((Model *)m)->act_q8 = on != 0; }
 
 // out: n_layer, d, n_head, n_head_kv, head_dim, ff, vocab, n_expert, n_expert_used, neox
 void ora_model_info(void * mp, uint32_t * out) {

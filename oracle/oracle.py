@@ -67,6 +67,7 @@ def lib() -> C.CDLL:
         l.ora_model_load.argtypes = [C.c_char_p]
         l.ora_model_free.argtypes = [C.c_void_p]
         l.ora_model_set_fast.argtypes = [C.c_void_p, C.c_int]
+        l.ora_model_set_act_q8.argtypes = [C.c_void_p, C.c_int]
         l.ora_model_info.argtypes = [C.c_void_p, _P(C.c_uint32)]
         l.ora_lora_load.restype = C.c_int32
         l.ora_lora_load.argtypes = [C.c_void_p, C.c_char_p, C.c_float]
@@ -87,6 +88,7 @@ def lib() -> C.CDLL:
         l.ora_seq_cp.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32]
         l.ora_dequantize_row.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, _P(C.c_float)]
         l.ora_mul_mat_vec.argtypes = [C.c_uint32, C.c_size_t, C.c_size_t, C.c_void_p, _P(C.c_float), _P(C.c_float)]
+        l.ora_mul_mat_vec_act_q8.argtypes = [C.c_uint32, C.c_size_t, C.c_size_t, C.c_void_p, _P(C.c_float), _P(C.c_float)]
         l.ora_rms_norm.argtypes = [_P(C.c_float), _P(C.c_float), C.c_size_t, C.c_float, _P(C.c_float)]
         l.ora_half_to_f32.restype = C.c_float
         l.ora_half_to_f32.argtypes = [C.c_uint16]
@@ -141,6 +143,16 @@ def mul_mat_vec(ggml_type: int, a: np.ndarray, n_row: int, n_col: int, b: np.nda
     return out
 
 
+def mul_mat_vec_act_q8(ggml_type: int, a: np.ndarray, n_row: int, n_col: int, b: np.ndarray) -> np.ndarray:
+    """The GEMV with b re-quantised to the weight type's 8-bit dot format (integer products, per-block scales)."""
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    out = np.zeros(n_row, dtype=np.float32)
+    if lib().ora_mul_mat_vec_act_q8(ggml_type, n_row, n_col, a.ctypes.data, _f32(b), _f32(out)) != 0:
+        raise ValueError("mul_mat_vec_act_q8 refused the input")
+    return out
+
+
 def rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32)
     w = np.ascontiguousarray(w, dtype=np.float32)
@@ -169,7 +181,9 @@ def pack(rows):
 
 
 class Model:
-    def __init__(self, path: str, fast: bool = False) -> None:
+    def __init__(self, path: str, fast: bool = False, act_q8: bool = False) -> None:
+        """act_q8: the weight matmuls re-quantise activations to 8 bits and multiply integers, as the reference's CPU
+        backend does (parity unpinned; reported beside the default act = f32, which every parity claim is made against)."""
         self._h = lib().ora_model_load(str(path).encode())
         if not self._h:
             raise RuntimeError(lib().ora_last_error().decode())
@@ -179,6 +193,8 @@ class Model:
          self.n_expert_used, self.neox) = list(info)
         if fast:
             lib().ora_model_set_fast(self._h, 1)
+        if act_q8:
+            lib().ora_model_set_act_q8(self._h, 1)
 
     def lora_load(self, path: str, scale: float = 1.0) -> int:
         i = lib().ora_lora_load(self._h, str(path).encode(), scale)

@@ -58,3 +58,18 @@ def test_moe_fixture_routes_every_token_to_experts_0_and_1(oracle):
     assert np.array_equal(np.sort(routes, axis=-1), np.broadcast_to([0, 1], routes.shape))
     counts = np.bincount(routes[0].reshape(-1), minlength=8)
     assert list(counts) == [len(prompt), len(prompt), 0, 0, 0, 0, 0, 0]
+
+
+def test_act_q8_mode_is_near_but_outside_the_logit_tolerance_of_act_f32(oracle, c1_model):
+    """The oracle's two activation modes on the tiny model: act = f32 (the checker) and act = q8 (the weight matmuls
+    re-quantise activations to 8 bits as the reference's CPU backend does). They pick the same tokens here, and their
+    logits differ by more than the 1e-2 the engine is held to against act = f32 - which is why parity is stated
+    against act = f32 and the other mode is only reported."""
+    rng = np.random.default_rng(4)
+    rows = [(i, rng.integers(3, 4096, 20 + 7 * i).tolist(), 0, True) for i in range(4)]
+    exact = oracle.Context(oracle.Model(str(c1_model)), 4, 256).step(rows)
+    q8 = oracle.Context(oracle.Model(str(c1_model), act_q8=True), 4, 256).step(rows)
+    diff = float(np.abs(exact - q8).max())
+    print(f"act f32 vs act q8: max|dlogit|={diff:.3e} on logits of magnitude {float(np.abs(exact).max()):.2f}")
+    assert 1e-3 < diff < 0.1
+    assert np.array_equal(np.argmax(exact, axis=1), np.argmax(q8, axis=1))

@@ -136,3 +136,87 @@ def test_kv_cache_rounding_is_the_published_row_quantiser(oracle, name, code):
     x = rows[0]
     assert np.array_equal(oracle.kv_round(1, x), x.astype(np.float16).astype(np.float32))
     assert np.array_equal(oracle.kv_round(0, x), x)
+
+
+def _q8_0_act(x):
+    """Activation rows as ggml's quantize_row_q8_0_ref leaves them: per 32 values an f16 scale and round-half-away quants."""
+    x = x.reshape(-1, 32).astype(np.float32)
+    amax = np.abs(x).max(axis=1)
+    d = (amax / np.float32(127)).astype(np.float32)
+    inv = np.where(d != 0, np.float32(1) / np.where(d != 0, d, 1), 0).astype(np.float32)
+    v = x * inv[:, None]
+    q = (np.sign(v) * np.floor(np.abs(v) + np.float32(0.5))).astype(np.int32)
+    return d.astype(np.float16).astype(np.float32), q
+
+
+def _scale_min_k4(j, s):
+    if j < 4:
+        return s[j] & 63, s[j + 4] & 63
+    return (s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4), (s[j + 4] >> 4) | ((s[j] >> 6) << 4)
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "MXFP4", "Q4_K"])
+def test_act_q8_gemv_is_the_integer_dot_over_requantised_activations(oracle, name):
+    """The oracle's optional act = q8 mode (what the reference's CPU backend does to activations, `tests/lora_rows.rs:16-20`)
+    against an independent numpy restatement of the published block arithmetic: activations to Q8_0 (32) or Q8_K (256),
+    integer products, per-block scales, f32 accumulation over blocks. It stays near the f32 GEMV and is not equal to it."""
+    rng = np.random.default_rng(5)
+    n_row, n_col = 6, 512
+    b = rng.normal(0, 1, n_col).astype(np.float32)
+    kvalues = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], dtype=np.int32)
+    want = np.zeros(n_row, dtype=np.float32)
+    if name == "Q8_0":
+        t, raw = oracle.T_Q8_0, _random_blocks(34, n_row * n_col // 32, [0], seed=7)
+        ad, aq = _q8_0_act(b)
+        blocks = raw.reshape(n_row, n_col // 32, 34)
+        for r in range(n_row):
+            acc = np.float32(0)
+            for k in range(n_col // 32):
+                dw = np.frombuffer(blocks[r, k, :2].tobytes(), dtype=np.float16)[0].astype(np.float32)
+                qw = blocks[r, k, 2:].view(np.int8).astype(np.int32)
+                acc = np.float32(acc + np.float32(np.float32(int((qw * aq[k]).sum())) * np.float32(dw * ad[k])))
+            want[r] = acc
+    elif name == "MXFP4":
+        raw = _random_blocks(17, n_row * n_col // 32, [], seed=8).copy()
+        raw[0::17] = 120 + (raw[0::17] % 12)
+        t = oracle.T_MXFP4
+        ad, aq = _q8_0_act(b)
+        blocks = raw.reshape(n_row, n_col // 32, 17)
+        for r in range(n_row):
+            acc = np.float32(0)
+            for k in range(n_col // 32):
+                scale = np.float32(oracle.lib().ora_e8m0_half(int(blocks[r, k, 0])))
+                nib = blocks[r, k, 1:]
+                w = np.concatenate([kvalues[nib & 0xF], kvalues[nib >> 4]])
+                acc = np.float32(acc + np.float32(np.float32(ad[k] * scale) * np.float32(int((w * aq[k]).sum()))))
+            want[r] = acc
+    else:
+        t, raw = oracle.T_Q4_K, _random_blocks(144, n_row * n_col // 256, [0, 2], seed=9)
+        x = b.reshape(-1, 256)
+        idx = np.abs(x).argmax(axis=1)
+        mx = x[np.arange(x.shape[0]), idx]
+        iscale = (np.float32(-127) / mx).astype(np.float32)
+        aq = np.minimum(127, np.rint(x * iscale[:, None])).astype(np.int32)          # np.rint: ties to even, as nearest_int
+        ad = (np.float32(1) / iscale).astype(np.float32)
+        bsums = aq.reshape(-1, 16, 16).sum(axis=2)
+        blocks = raw.reshape(n_row, n_col // 256, 144)
+        for r in range(n_row):
+            acc = np.float32(0)
+            for k in range(n_col // 256):
+                blk = blocks[r, k]
+                d, dmin = np.frombuffer(blk[:4].tobytes(), dtype=np.float16).astype(np.float32)
+                scales, qs = blk[4:16].astype(np.int32), blk[16:].astype(np.int32)
+                main = mins = 0
+                for g in range(4):
+                    sc1, m1 = _scale_min_k4(2 * g, scales)
+                    sc2, m2 = _scale_min_k4(2 * g + 1, scales)
+                    q = qs[g * 32:(g + 1) * 32]
+                    main += int(sc1) * int(((q & 0xF) * aq[k, g * 64:g * 64 + 32]).sum()) + int(sc2) * int(((q >> 4) * aq[k, g * 64 + 32:g * 64 + 64]).sum())
+                    mins += int(m1) * int(bsums[k, 4 * g] + bsums[k, 4 * g + 1]) + int(m2) * int(bsums[k, 4 * g + 2] + bsums[k, 4 * g + 3])
+                acc = np.float32(acc + np.float32(np.float32(np.float32(ad[k] * d) * np.float32(main)) - np.float32(np.float32(ad[k] * dmin) * np.float32(mins))))
+            want[r] = acc
+    got = oracle.mul_mat_vec_act_q8(t, raw, n_row, n_col, b)
+    assert np.allclose(got, want, rtol=2e-6, atol=1e-6), (got, want)
+    exact = oracle.mul_mat_vec(t, raw, n_row, n_col, b)
+    scale = float(np.abs(exact).max())
+    assert 0 < float(np.abs(got - exact).max()) < 0.03 * scale
