@@ -392,12 +392,13 @@ def host_cores() -> int:
 
 
 def cpu_baseline(path: Path, cfg, steps: int = 2, rows: int = 8, prompt: int = 4):
-    """The CPU oracle (vectorised accumulation, all host threads) on a bounded sample: `rows`
+    """The CPU oracle (all host threads; activations re-quantised to 8-bit blocks and integer dot products, the
+    arithmetic of the reference's CPU backend and the faster of the oracle's two modes) on a bounded sample: `rows`
     concurrent requests, a `prompt`-token prefill each, then `steps` decode steps."""
     from oracle import oracle as O
 
     cores = O.threads(host_cores())
-    m = O.Model(str(path), fast=True)
+    m = O.Model(str(path), fast=True, act_q8=True)
     ctx = O.Context(m, rows, 64)
     rng = np.random.default_rng(1)
     vocab = cfg["spec"]["vocab"]
@@ -423,7 +424,7 @@ def run_reference(args, cfg, rank, world):
     # the thread count is set here, not inherited: torchrun exports OMP_NUM_THREADS=1 to its children
     cores = O.threads(host_cores())
     rows, prompt = 8, 4
-    m = O.Model(str(path), fast=True)
+    m = O.Model(str(path), fast=True, act_q8=True)
     ctx = O.Context(m, rows, 64 + args.steps + args.warmup)
     rng = np.random.default_rng(1)
     vocab = cfg["spec"]["vocab"]
@@ -437,7 +438,8 @@ def run_reference(args, cfg, rank, world):
     total = sum(times)
     value = rows * len(times) / total
     sample = (f"{rows} concurrent requests, {prompt}-token prompts, {len(times)} decode steps of the same GGUF on {cores} OpenMP threads: the CPU "
-              "restatement of the path (the reference itself cannot be built here), a bounded decode-only sample, not the GPU arm's 256-request mix")
+              "restatement of the path (the reference itself cannot be built here) with activations re-quantised to 8-bit blocks and integer dot "
+              "products as the reference's CPU backend computes, a bounded decode-only sample, not the GPU arm's 256-request mix")
     print(json.dumps({
         "impl": "reference", "metric": "decode_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -746,7 +748,7 @@ def main():
     if world == 1 and not args.no_cpu_baseline:
         value, times, cores = cpu_baseline(path, cfg)
         line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
-                                "sample": f"8 concurrent requests, 4-token prompts, {len(times)} decode steps of the same GGUF"}
+                                "sample": f"8 concurrent requests, 4-token prompts, {len(times)} decode steps of the same GGUF (CPU restatement, activations re-quantised to 8-bit blocks, integer dot products)"}
     print(json.dumps(line))
 
 
