@@ -1383,6 +1383,11 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             attn_scratch_.ensure(attention_decode8_scratch_floats(n_attn_items, (int)hp.n_head_kv, attn_splits, (int)hp.head_dim));
     }
 
+    // Quantised pools: decode rows over a Q8_0 pool are read by attention_decode8's own Q8_0 kernel; every other row needs
+    // its context in the f16 scratch.
+    const int pool_read_tokens = kv_storage_ == KV_Q8_0 && use_decode8 && kv_q8_native_ ? 8 / attn_group : 0;
+    const bool kv_scratch_needed = kv_storage_ != KV_F16 && (any_wide_item || any_mid_item || pool_read_tokens == 0);
+
     // ---- device work. Everything the launches depend on besides the contents of the staging buffer
     // is in `sig`: a step whose signature was seen before is replayed as a CUDA graph (one launch
     // instead of hundreds), captured the second time the signature occurs - the first time runs
@@ -1393,7 +1398,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                                        any_adapter, (uint64_t)n_attn_items, (uint64_t)n_small_items, any_wide_item, any_mid_item,
                                        (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_, (uint64_t)adapters_.size(), (uint64_t)masks.size(),
                                        // a quantised pool's dequantisation grid covers the longest row's blocks
-                                       kv_storage_ != KV_F16 ? (uint64_t)((max_ctx + kBlockTokens - 1) / kBlockTokens) : 0};
+                                       kv_scratch_needed ? (uint64_t)((max_ctx + kBlockTokens - 1) / kBlockTokens) : 0};
     auto issue = [&]() {
     last_launches = 0;
     RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
@@ -1463,11 +1468,8 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
         if (kv_storage_ != KV_F16) {
             // the rotated K and the V rows are still in the qkv buffer: quantise them into the pool, then bring every
             // block the step's rows attend to (the new cells included, now as the pool holds them) into the f16 scratch
-            // (decode rows over a Q8_0 pool are read by attention_decode8's own Q8_0 kernel: only longer rows need the scratch)
-            const int pool_read_tokens = kv_storage_ == KV_Q8_0 && use_decode8 && kv_q8_native_ ? 8 / attn_group : 0;
-            const bool scratch_needed = any_wide_item || any_mid_item || pool_read_tokens == 0;
-            RB_K(K_ATTN, scratch_needed ? 2 : 1, launch_kv_quant_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_cell, stream);
-                 if (scratch_needed)
+            RB_K(K_ATTN, kv_scratch_needed ? 2 : 1, launch_kv_quant_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_cell, stream);
+                 if (kv_scratch_needed)
                      launch_kv_dequant(kvl, (int)l, (int)R, (max_ctx + (int)kBlockTokens - 1) / (int)kBlockTokens, maps.cu_rows, maps.tok_slot,
                                        maps.tok_pos, maps.tok_pos_min, pool_read_tokens, stream));
         }
