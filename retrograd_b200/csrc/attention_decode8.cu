@@ -253,12 +253,21 @@ __global__ void __launch_bounds__(D8_THREADS) attention_decode8_kernel(const flo
 // int8 -> f16: (q ^ 0x80) is q + 128 as an unsigned byte and 0x6400 | byte the f16 value 1152 + q. V subtracts the 1152
 // per element; K does not: its MMAs run on 1152 + q and the block's accumulator is corrected by 1152 times the sum of
 // the query's (two-term) elements of that block, which a lane computes once for the two columns it accumulates.
-template <int HD, int Q8_SLOTS, int MIN_CTAS>
+// QBITS = 4, a Q4_0 pool (row = [head_dim / 2 bytes of nibble pairs | scales], value (q - 8) * scale, byte j of a
+// block holding element j in its low and element j + 16 in its high nibble): the same scheme with other index maps. A
+// lane's one word of a K block holds four low nibbles (step 2 b: elements 4 tq .. + 3) and four high ones (step
+// 2 b + 1: elements 16 + 4 tq .. + 3); masked to bytes, 0x6400 | q is 1024 + q, so K runs on 1024 + q with the correction
+// 1032 x the query sums, and V subtracts 1032. For V, lanes g and g + 4 read the same word of a key and take its low
+// and its high nibbles: the lane's four values of the chunk are d = 16 (g >> 2) + 4 (g & 3) .. + 3.
+template <int HD, int Q8_SLOTS, int MIN_CTAS, int QBITS>
 __global__ void __launch_bounds__(D8_THREADS, MIN_CTAS) attention_decode8_q8_kernel(const float * __restrict__ qkv, int ld, int n_head, KvLayout kv, int layer,
                                                                            const int2 * __restrict__ items, const int32_t * __restrict__ tok_slot,
                                                                            const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min,
                                                                            float * __restrict__ out, int ldo, int n_splits, float * __restrict__ partial) {
-    constexpr int ROWB = (HD + HD / 16 + 7) & ~7;          // bytes of a pool row (kv_row_bytes)
+    constexpr bool Q4 = QBITS == 4;
+    constexpr int QBYTES = Q4 ? HD / 2 : HD;               // bytes of quants in a pool row; the scales follow
+    constexpr int ROWB = (QBYTES + HD / 16 + 7) & ~7;      // bytes of a pool row (kv_row_bytes)
+    constexpr float OFFSET = Q4 ? 1032.f : 1152.f;         // what 0x6400 | byte reads as, minus the quant's value
     constexpr int NB = HD / 32;                            // quant blocks per row
     constexpr int MT = HD / 16;
     constexpr int TILE_BYTES = 16 * ROWB;                  // one K or V block of one head
@@ -310,7 +319,8 @@ __global__ void __launch_bounds__(D8_THREADS, MIN_CTAS) attention_decode8_q8_ker
         const float * src = qkv + (size_t)(i0 + (valid ? g / G : 0)) * ld + (size_t)(hk * G + (valid ? g % G : 0)) * HD;
 #pragma unroll
         for (int ks = 0; ks < 2 * NB; ++ks) {
-            const float4 v = valid ? *reinterpret_cast<const float4 *>(src + (ks >> 1) * 32 + 8 * tq + 4 * (ks & 1)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const int e0 = Q4 ? (ks >> 1) * 32 + 16 * (ks & 1) + 4 * tq : (ks >> 1) * 32 + 8 * tq + 4 * (ks & 1);
+            const float4 v = valid ? *reinterpret_cast<const float4 *>(src + e0) : make_float4(0.f, 0.f, 0.f, 0.f);
             const float e[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
 #pragma unroll
             for (int hlf = 0; hlf < 2; ++hlf) {
@@ -341,12 +351,12 @@ __global__ void __launch_bounds__(D8_THREADS, MIN_CTAS) attention_decode8_q8_ker
         }
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);       // the four lanes of column g hold the block's 32 elements
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        corrA[b] = 1152.f * __shfl_sync(0xffffffffu, sum, colA * 4);
-        corrB[b] = 1152.f * __shfl_sync(0xffffffffu, sum, colB * 4);
+        corrA[b] = OFFSET * __shfl_sync(0xffffffffu, sum, colA * 4);
+        corrB[b] = OFFSET * __shfl_sync(0xffffffffu, sum, colB * 4);
     }
     auto raw_lo = [](uint32_t w) { return __byte_perm(w, 0x64646464u, 0x4140); };     // f16 pair (1152 + q) of bytes 0, 1
     auto raw_hi = [](uint32_t w) { return __byte_perm(w, 0x64646464u, 0x4342); };     // ... of bytes 2, 3
-    const __half2 bias2 = __floats2half2_rn(1152.f, 1152.f);
+    const __half2 bias2 = __floats2half2_rn(OFFSET, OFFSET);
     auto pair_lo = [&](uint32_t w) { const uint32_t t = __byte_perm(w, 0x64646464u, 0x4140); return __hsub2(*reinterpret_cast<const __half2 *>(&t), bias2); };
     auto pair_hi = [&](uint32_t w) { const uint32_t t = __byte_perm(w, 0x64646464u, 0x4342); return __hsub2(*reinterpret_cast<const __half2 *>(&t), bias2); };
     auto as_u32 = [](__half2 h) { return *reinterpret_cast<const uint32_t *>(&h); };
@@ -364,12 +374,20 @@ __global__ void __launch_bounds__(D8_THREADS, MIN_CTAS) attention_decode8_q8_ker
         const uint8_t * k_s = ring + (j % Q8_SLOTS) * 2 * TILE_BYTES, * v_s = k_s + TILE_BYTES;
         // S^T: rows = keys (key0 | key1), columns = the (token, head) pairs; per quant block, then scaled
         float s[4] = {0.f, 0.f, 0.f, 0.f};
-        const __half * ks0 = reinterpret_cast<const __half *>(k_s + key0 * ROWB + HD), * ks1 = reinterpret_cast<const __half *>(k_s + key1 * ROWB + HD);
+        const __half * ks0 = reinterpret_cast<const __half *>(k_s + key0 * ROWB + QBYTES), * ks1 = reinterpret_cast<const __half *>(k_s + key1 * ROWB + QBYTES);
 #pragma unroll
         for (int b = 0; b < NB; ++b) {
-            uint2 r0 = *reinterpret_cast<const uint2 *>(k_s + key0 * ROWB + b * 32 + 8 * tq);
-            uint2 r1 = *reinterpret_cast<const uint2 *>(k_s + key1 * ROWB + b * 32 + 8 * tq);
-            r0.x ^= 0x80808080u; r0.y ^= 0x80808080u; r1.x ^= 0x80808080u; r1.y ^= 0x80808080u;
+            uint2 r0, r1;       // .x: the bytes of step 2 b, .y: of step 2 b + 1; rows key0 and key1
+            if (Q4) {
+                const uint32_t w0 = *reinterpret_cast<const uint32_t *>(k_s + key0 * ROWB + b * 16 + 4 * tq);
+                const uint32_t w1 = *reinterpret_cast<const uint32_t *>(k_s + key1 * ROWB + b * 16 + 4 * tq);
+                r0 = make_uint2(w0 & 0x0F0F0F0Fu, (w0 >> 4) & 0x0F0F0F0Fu);
+                r1 = make_uint2(w1 & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu);
+            } else {
+                r0 = *reinterpret_cast<const uint2 *>(k_s + key0 * ROWB + b * 32 + 8 * tq);
+                r1 = *reinterpret_cast<const uint2 *>(k_s + key1 * ROWB + b * 32 + 8 * tq);
+                r0.x ^= 0x80808080u; r0.y ^= 0x80808080u; r1.x ^= 0x80808080u; r1.y ^= 0x80808080u;
+            }
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             {
                 const uint32_t a0 = raw_lo(r0.x), a1 = raw_lo(r1.x), a2 = raw_hi(r0.x), a3 = raw_hi(r1.x);
@@ -413,7 +431,7 @@ __global__ void __launch_bounds__(D8_THREADS, MIN_CTAS) attention_decode8_q8_ker
             o[mt][2] *= cA;
             o[mt][3] *= cB;
         }
-        const __half * vs0 = reinterpret_cast<const __half *>(v_s + key0 * ROWB + HD), * vs1 = reinterpret_cast<const __half *>(v_s + key1 * ROWB + HD);
+        const __half * vs0 = reinterpret_cast<const __half *>(v_s + key0 * ROWB + QBYTES), * vs1 = reinterpret_cast<const __half *>(v_s + key1 * ROWB + QBYTES);
 #pragma unroll
         for (int c = 0; c < NB; ++c) {
             // the probabilities times this chunk's V scale of their key, as two f16 terms, transposed into B operands
@@ -423,11 +441,23 @@ __global__ void __launch_bounds__(D8_THREADS, MIN_CTAS) attention_decode8_q8_ker
             const float2 k01 = __half22float2(h01), k23 = __half22float2(h23);
             const uint32_t bh0 = movmatrix_trans(as_u32(h01)), bh1 = movmatrix_trans(as_u32(h23));
             const uint32_t bl0 = movmatrix_trans(pack_h2(f0 - k01.x, f1 - k01.y)), bl1 = movmatrix_trans(pack_h2(f2 - k23.x, f3 - k23.y));
-            // V words of keys 4 tq .. 4 tq + 3 at d = 32 c + 4 g .. + 3
-            const uint8_t * vrow = v_s + (4 * tq) * ROWB + c * 32 + 4 * g;
-            const uint32_t w0 = *reinterpret_cast<const uint32_t *>(vrow) ^ 0x80808080u, w1 = *reinterpret_cast<const uint32_t *>(vrow + ROWB) ^ 0x80808080u;
-            const uint32_t w2 = *reinterpret_cast<const uint32_t *>(vrow + 2 * ROWB) ^ 0x80808080u,
-                           w3 = *reinterpret_cast<const uint32_t *>(vrow + 3 * ROWB) ^ 0x80808080u;
+            // V words of keys 4 tq .. 4 tq + 3: four bytes (Q8_0: d = 32 c + 4 g .. + 3; Q4_0: the low or high nibbles of
+            // bytes 4 (g & 3) .. + 3 of the chunk, d = 32 c + 16 (g >> 2) + 4 (g & 3) .. + 3), each byte 0x6400-ready
+            uint32_t w0, w1, w2, w3;
+            if (Q4) {
+                const uint8_t * vrow = v_s + (4 * tq) * ROWB + c * 16 + 4 * (g & 3);
+                const int sh = 4 * (g >> 2);
+                w0 = (*reinterpret_cast<const uint32_t *>(vrow) >> sh) & 0x0F0F0F0Fu;
+                w1 = (*reinterpret_cast<const uint32_t *>(vrow + ROWB) >> sh) & 0x0F0F0F0Fu;
+                w2 = (*reinterpret_cast<const uint32_t *>(vrow + 2 * ROWB) >> sh) & 0x0F0F0F0Fu;
+                w3 = (*reinterpret_cast<const uint32_t *>(vrow + 3 * ROWB) >> sh) & 0x0F0F0F0Fu;
+            } else {
+                const uint8_t * vrow = v_s + (4 * tq) * ROWB + c * 32 + 4 * g;
+                w0 = *reinterpret_cast<const uint32_t *>(vrow) ^ 0x80808080u;
+                w1 = *reinterpret_cast<const uint32_t *>(vrow + ROWB) ^ 0x80808080u;
+                w2 = *reinterpret_cast<const uint32_t *>(vrow + 2 * ROWB) ^ 0x80808080u;
+                w3 = *reinterpret_cast<const uint32_t *>(vrow + 3 * ROWB) ^ 0x80808080u;
+            }
             // (key 4 tq, key 4 tq + 1) byte pairs of d offsets 0, 1 | 2, 3; the same for keys 4 tq + 2, 4 tq + 3
             const uint32_t u01 = __byte_perm(w0, w1, 0x5140), u23 = __byte_perm(w0, w1, 0x7362);
             const uint32_t x01 = __byte_perm(w2, w3, 0x5140), x23 = __byte_perm(w2, w3, 0x7362);
@@ -457,8 +487,8 @@ __global__ void __launch_bounds__(D8_THREADS, MIN_CTAS) attention_decode8_q8_ker
     float * part_l = part_m + 4 * 8;                                        // [4][8]
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-        // M tile mt = 2 c + y: accumulator row g is d = 32 c + 4 g + 2 y, row g + 8 is d + 1
-        const int d = 32 * (mt >> 1) + 4 * g + 2 * (mt & 1);
+        // M tile mt = 2 c + y: accumulator row g is d = 32 c + (the lane's first d of the chunk) + 2 y, row g + 8 is d + 1
+        const int d = 32 * (mt >> 1) + (Q4 ? 16 * (g >> 2) + 4 * (g & 3) : 4 * g) + 2 * (mt & 1);
         float * dA = part_o + ((size_t)warp * 8 + colA) * HD + d;
         float * dB = part_o + ((size_t)warp * 8 + colB) * HD + d;
         dA[0] = o[mt][0];
@@ -554,8 +584,18 @@ void launch_hd8(const float * qkv, int ld, int n_head, KvLayout kv, int layer, c
         constexpr int smem_q8 = 4 * D8_SLOTS * 2 * 16 * ((HD + HD / 16 + 7) & ~7);
         static_assert(smem_q8 >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the quantised K/V rings");
         static PerDeviceOnce once;
-        if (once.first()) cudaFuncSetAttribute(attention_decode8_q8_kernel<HD, D8_SLOTS, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q8);
-        launch_pdl(attention_decode8_q8_kernel<HD, D8_SLOTS, 4>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem_q8, stream, qkv, ld, n_head,
+        if (once.first()) cudaFuncSetAttribute(attention_decode8_q8_kernel<HD, D8_SLOTS, 4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q8);
+        launch_pdl(attention_decode8_q8_kernel<HD, D8_SLOTS, 4, 8>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem_q8, stream, qkv, ld, n_head,
+                   kv, layer, items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
+    } else if (kv.storage == KV_Q4_0) {
+        // the ring holds as many blocks as fit the merge buffers' bytes (a Q4_0 block of K and V is 2.3 KB at head_dim 128)
+        constexpr int tile = 16 * ((HD / 2 + HD / 16 + 7) & ~7);
+        constexpr int slots = (4 * 8 * HD + 64) * 4 > 4 * D8_SLOTS * 2 * tile ? ((4 * 8 * HD + 64) * 4 + 4 * 2 * tile - 1) / (4 * 2 * tile) : D8_SLOTS;
+        constexpr int smem_q4 = 4 * slots * 2 * tile;
+        static_assert(smem_q4 >= (4 * 8 * HD + 64) * 4, "the merge buffers fit the quantised K/V rings");
+        static PerDeviceOnce once;
+        if (once.first()) cudaFuncSetAttribute(attention_decode8_q8_kernel<HD, slots, 4, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q4);
+        launch_pdl(attention_decode8_q8_kernel<HD, slots, 4, 4>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem_q4, stream, qkv, ld, n_head,
                    kv, layer, items, tok_slot, tok_pos, tok_pos_min, out, ldo, n_splits, scratch);
     } else
         launch_pdl(attention_decode8_kernel<HD>, dim3(n_items, kv.n_head_kv, n_splits), dim3(D8_THREADS), smem, stream, qkv, ld, n_head, kv, layer, items,

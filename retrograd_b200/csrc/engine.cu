@@ -1383,9 +1383,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             attn_scratch_.ensure(attention_decode8_scratch_floats(n_attn_items, (int)hp.n_head_kv, attn_splits, (int)hp.head_dim));
     }
 
-    // Quantised pools: decode rows over a Q8_0 pool are read by attention_decode8's own Q8_0 kernel; every other row needs
-    // its context in the f16 scratch.
-    const int pool_read_tokens = kv_storage_ == KV_Q8_0 && use_decode8 && kv_q8_native_ ? 8 / attn_group : 0;
+    // Quantised pools: decode rows are read from the pool by attention_decode8's own Q8_0 / Q4_0 kernel; every other row
+    // needs its context in the f16 scratch.
+    const int pool_read_tokens = kv_storage_ != KV_F16 && use_decode8 && kv_q8_native_ ? 8 / attn_group : 0;
     const bool kv_scratch_needed = kv_storage_ != KV_F16 && (any_wide_item || any_mid_item || pool_read_tokens == 0);
 
     // ---- device work. Everything the launches depend on besides the contents of the staging buffer
@@ -1405,9 +1405,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     const RowDesc * d_rows = reinterpret_cast<const RowDesc *>(d_stage_.ptr + off_rows);
     const int32_t * d_tokens = reinterpret_cast<const int32_t *>(d_stage_.ptr + off_tokens);
     const KvLayout kvl = kv_layout();
-    // what the decode-row kernel sees: the Q8_0 pool itself, or (storage F16) the pool / its dequantised scratch
+    // what the decode-row kernel sees: the quantised pool itself, or (storage F16) the pool / its dequantised scratch
     KvLayout kv_rows = kvl;
-    if (kv_storage_ == KV_Q8_0 && !kv_q8_native_) kv_rows.storage = KV_F16;
+    if (!kv_q8_native_) kv_rows.storage = KV_F16;
 #define RB_K(cls, n, ...)            \
     do {                             \
         prof_.begin(cls, stream);    \

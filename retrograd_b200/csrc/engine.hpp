@@ -349,7 +349,7 @@ private:
     DeviceBuffer<uint8_t> kq_, vq_;                    // the quantised pool (kv_dtype Q8_0 / Q4_0)
     uint64_t kv_q_layer_stride_ = 0;                   // bytes per layer
     int32_t kv_storage_ = KV_F16;
-    bool kv_q8_native_ = true;                         // decode rows read a Q8_0 pool directly (RB200_KV_Q8_NATIVE=0: through the scratch)
+    bool kv_q8_native_ = true;                         // decode rows read a quantised pool directly (RB200_KV_Q8_NATIVE=0: through the scratch)
     DeviceBuffer<int32_t> block_table_;
     DeviceBuffer<int32_t> maps_store_;
     DeviceBuffer<uint8_t> d_stage_;

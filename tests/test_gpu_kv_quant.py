@@ -31,11 +31,11 @@ def _prompt(seed, n, vocab=1024):
 
 
 @pytest.mark.parametrize("shape", list(SPECS))
-@pytest.mark.parametrize("dtype,native", [("q8_0", True), ("q8_0", False), ("q4_0", True)])
+@pytest.mark.parametrize("dtype,native", [("q8_0", True), ("q8_0", False), ("q4_0", True), ("q4_0", False)])
 def test_quantised_kv_pool_matches_the_oracle(rb, oracle, models, monkeypatch, shape, dtype, native):
     """Prefill chunks (tensor-core tiles), short rows, decode rows (split over several CTAs: the longest context is
     400 tokens), a shared prefix with its copy-on-write block and a second chunk over a resident context: every kernel
-    that reads K / V, over a pool that holds quantised rows. Decode rows over a Q8_0 pool are read by their own kernel
+    that reads K / V, over a pool that holds quantised rows. Decode rows are read from the pool by their own kernel
     (`native`), or - like every other row - from the dequantised scratch."""
     path = models(f"kvq_{shape}", **SPECS[shape])
     monkeypatch.setattr(helpers, "LOGIT_TOL", TOL[dtype])
