@@ -243,6 +243,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc5_kernel(const float *
         const int R = q * 32 + lane;
         const int tt = R / G, hg = R % G;
         const int prow = tt < ntok ? pos0 + tt : -1;        // last position this query vector may see
+        const int warp_min_prow = __reduce_min_sync(0xffffffffu, prow);      // (-1 with a row past the item's tokens in the warp)
         const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
         float * xmax = reinterpret_cast<float *>(smem + S::XCH_OFF);     // [tile parity][group][row]: the halves' maxima
         float * xsum = xmax + 4 * ROWS;                                  // [group][row]: the halves' sums, at the end
@@ -266,14 +267,20 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc5_kernel(const float *
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc5::mbar_arrive(s_free(b));
-            // causal mask by position within the slot
+            // causal mask by position within the slot; a tile whose keys every row of the warp sees (all but the first
+            // and the last few tiles of a chunk) skips the per-key comparisons
             const int pbase = (nb0 << 4) + j * KT + grp * KH;
             float mx = -INFINITY;
+            if (pbase >= pmin && pbase + KH - 1 <= warp_min_prow) {
 #pragma unroll
-            for (int i = 0; i < KH; ++i) {
-                const int p = pbase + i;
-                if (p < pmin || p > prow) s[i] = -INFINITY;
-                mx = fmaxf(mx, s[i]);
+                for (int i = 0; i < KH; ++i) mx = fmaxf(mx, s[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < KH; ++i) {
+                    const int p = pbase + i;
+                    if (p < pmin || p > prow) s[i] = -INFINITY;
+                    mx = fmaxf(mx, s[i]);
+                }
             }
             // the row's maximum over both halves
             xmax[(b * 2 + grp) * ROWS + R] = mx;
