@@ -1387,6 +1387,9 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
     // needs its context in the f16 scratch.
     const int pool_read_tokens = kv_storage_ != KV_F16 && use_decode8 && kv_q8_native_ ? 8 / attn_group : 0;
     const bool kv_scratch_needed = kv_storage_ != KV_F16 && (any_wide_item || any_mid_item || pool_read_tokens == 0);
+    int n_scratch_rows = 0;
+    if (kv_scratch_needed)
+        for (size_t r = 0; r < R; ++r) n_scratch_rows += (int)rows[r].n > pool_read_tokens ? 1 : 0;
 
     // ---- device work. Everything the launches depend on besides the contents of the staging buffer
     // is in `sig`: a step whose signature was seen before is replayed as a CUDA graph (one launch
@@ -1398,7 +1401,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
                                        any_adapter, (uint64_t)n_attn_items, (uint64_t)n_small_items, any_wide_item, any_mid_item,
                                        (uint64_t)attn_splits, stage_total, res_total, (uint64_t)result_bytes_, (uint64_t)adapters_.size(), (uint64_t)masks.size(),
                                        // a quantised pool's dequantisation grid covers the longest row's blocks
-                                       kv_scratch_needed ? (uint64_t)((max_ctx + kBlockTokens - 1) / kBlockTokens) : 0};
+                                       kv_scratch_needed ? (uint64_t)((max_ctx + kBlockTokens - 1) / kBlockTokens) : 0, (uint64_t)n_scratch_rows};
     auto issue = [&]() {
     last_launches = 0;
     RB_CUDA(cudaMemcpyAsync(d_stage_.ptr, h_stage_, stage_total, cudaMemcpyHostToDevice, stream));
@@ -1470,7 +1473,7 @@ int Engine::step(const EffRow * rows, size_t n_rows, OutRow * out_rows, int32_t 
             // block the step's rows attend to (the new cells included, now as the pool holds them) into the f16 scratch
             RB_K(K_ATTN, kv_scratch_needed ? 2 : 1, launch_kv_quant_store(qkv_.ptr, ldqkv, Ti, (int)hp.n_head, kvl, (int)l, maps.tok_cell, stream);
                  if (kv_scratch_needed)
-                     launch_kv_dequant(kvl, (int)l, (int)R, (max_ctx + (int)kBlockTokens - 1) / (int)kBlockTokens, maps.cu_rows, maps.tok_slot,
+                     launch_kv_dequant(kvl, (int)l, (int)R, n_scratch_rows, (max_ctx + (int)kBlockTokens - 1) / (int)kBlockTokens, maps.cu_rows, maps.tok_slot,
                                        maps.tok_pos, maps.tok_pos_min, pool_read_tokens, stream));
         }
         if (attn_mma_) {

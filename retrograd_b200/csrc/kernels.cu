@@ -241,11 +241,21 @@ __global__ void kv_quant_store_kernel(const float * __restrict__ qkv, int ld, in
     const int cell = tok_cell[t];
     RB_CHECK(kv.check, CHECK_CELL, cell, (long long)kv.n_blocks * kv.block_tokens, return);
     const int blk = cell / kv.block_tokens, off = cell % kv.block_tokens;
-    // the token's K heads, then its V heads, are one run of 2 * n_head_kv * head_dim values behind its q heads
-    for (int qb = threadIdx.x >> 5; qb < 2 * kv.n_head_kv * per_head; qb += blockDim.x >> 5) {
+    // the token's K heads, then its V heads, are one run of 2 * n_head_kv * head_dim values behind its q heads; a warp
+    // takes four of the run's 32-value blocks per pass, their loads issued together
+    const int n_qb = 2 * kv.n_head_kv * per_head, n_warps = blockDim.x >> 5;
+    const float * run = qkv + (size_t)t * ld + (size_t)n_head * kv.head_dim;
+    for (int qb0 = threadIdx.x >> 5; qb0 < n_qb; qb0 += 4 * n_warps) {
+    float xs[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) xs[u] = qb0 + u * n_warps < n_qb ? run[(size_t)(qb0 + u * n_warps) * 32 + lane] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+    const int qb = qb0 + u * n_warps;
+    if (qb >= n_qb) break;
     const int hh = qb / per_head, b = qb % per_head;                    // quant block b of head row hh (K heads, then V heads)
     const int is_v = hh >= kv.n_head_kv ? 1 : 0, h = hh - is_v * kv.n_head_kv;
-    const float x = qkv[(size_t)t * ld + (size_t)(n_head + hh) * kv.head_dim + b * 32 + lane];
+    const float x = xs[u];
     uint8_t * row = (is_v ? kv.vq : kv.kq) + layer * kv.q_layer_stride + (((size_t)blk * kv.n_head_kv + h) * kv.block_tokens + off) * kv.q_row_bytes;
     float a = fabsf(x);
     int who = lane;
@@ -270,14 +280,34 @@ __global__ void kv_quant_store_kernel(const float * __restrict__ qkv, int ld, in
         if (lane == 0) reinterpret_cast<__half *>(row + kv.head_dim / 2)[b] = __float2half_rn(d);
     }
     }
+    }
 }
 
 // Quantised KV pools: every pool block row r of the step may attend to, dequantised (scale * quant in f32, rounded
-// to f16) into the one-layer f16 scratch under the same block number. grid (rows, unit strides).
-__global__ void kv_dequant_kernel(KvLayout kv, int layer, const int32_t * __restrict__ cu_rows, const int32_t * __restrict__ tok_slot,
+// to f16) into the one-layer f16 scratch under the same block number. grid (rows that need it, unit strides).
+__global__ void kv_dequant_kernel(KvLayout kv, int layer, int n_rows, const int32_t * __restrict__ cu_rows, const int32_t * __restrict__ tok_slot,
                                   const int32_t * __restrict__ tok_pos, const int32_t * __restrict__ tok_pos_min, int skip_tokens) {
-    const int i0 = cu_rows[blockIdx.x], n = cu_rows[blockIdx.x + 1] - i0;
-    if (n <= skip_tokens) return;          // (rows this short are read from the pool by a kernel that decodes it itself)
+    // blockIdx.x counts the rows of more than skip_tokens tokens (shorter rows are read from the pool by a kernel that
+    // decodes it itself): find that row - every warp the same way, 32 rows per ballot
+    int row = -1;
+    {
+        const int lane = threadIdx.x & 31;
+        int seen = 0;
+        for (int r0 = 0; r0 < n_rows && row < 0; r0 += 32) {
+            const int r = r0 + lane;
+            const bool needy = r < n_rows && cu_rows[r + 1] - cu_rows[r] > skip_tokens;
+            const unsigned mask = __ballot_sync(0xffffffffu, needy);
+            const int here = __popc(mask);
+            if (seen + here > (int)blockIdx.x) {
+                unsigned m = mask;
+                for (int k = (int)blockIdx.x - seen; k > 0; --k) m &= m - 1;        // drop the k lowest set bits
+                row = r0 + __ffs(m) - 1;
+            }
+            seen += here;
+        }
+    }
+    if (row < 0) return;
+    const int i0 = cu_rows[row], n = cu_rows[row + 1] - i0;
     const int slot = tok_slot[i0], last = tok_pos[i0] + n - 1, pmin = tok_pos_min[i0];
     const int hd = kv.head_dim, rows = kv.n_head_kv * kv.block_tokens;          // (head, cell) rows of the block
     const bool q8 = kv.storage == KV_Q8_0;
@@ -917,12 +947,14 @@ void launch_kv_quant_store(const float * qkv, int ld, int n_tokens, int n_head, 
     kv_quant_store_kernel<<<dim3(n_tokens), 256, 0, stream>>>(qkv, ld, n_head, kv, layer, tok_cell);
 }
 
-void launch_kv_dequant(KvLayout kv, int layer, int n_rows, int max_row_blocks, const int32_t * cu_rows, const int32_t * tok_slot,
+void launch_kv_dequant(KvLayout kv, int layer, int n_rows, int n_scratch_rows, int max_row_blocks, const int32_t * cu_rows, const int32_t * tok_slot,
                        const int32_t * tok_pos, const int32_t * tok_pos_min, int skip_tokens, cudaStream_t stream) {
-    if (n_rows <= 0 || max_row_blocks <= 0) return;
-    // (a CTA walks its row's units in strides of grid.y: the rows that are skipped cost a few short CTAs each, not one per block)
-    kv_dequant_kernel<<<dim3(n_rows, std::min(max_row_blocks * 2 * kv.n_head_kv, 96)), 256, 0, stream>>>(kv, layer, cu_rows, tok_slot, tok_pos, tok_pos_min,
-                                                                                                        skip_tokens);
+    if (n_rows <= 0 || n_scratch_rows <= 0 || max_row_blocks <= 0) return;
+    // grid.x: the rows that need the scratch; a row's CTAs walk its (block, K | V, head) units in strides of grid.y, a
+    // handful of units each
+    const int units = max_row_blocks * 2 * kv.n_head_kv;
+    kv_dequant_kernel<<<dim3(n_scratch_rows, std::max(1, std::min(units / 4, 512))), 256, 0, stream>>>(kv, layer, n_rows, cu_rows, tok_slot, tok_pos,
+                                                                                                      tok_pos_min, skip_tokens);
 }
 
 void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream, int * check) {

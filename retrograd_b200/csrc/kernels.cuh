@@ -287,9 +287,10 @@ inline int kv_row_bytes(int storage, int head_dim) {
 // Quantised pools. Store: the step's K (rotated) and V rows from the qkv buffer, quantised per 32 elements as ggml's
 // quantize_row_q8_0_ref / quantize_row_q4_0_ref do. Dequant: every block that row r of the step may attend to
 // (cu_rows / tok_* are the packing maps; `max_row_blocks` bounds the blocks of any row), into the f16 scratch; rows of
-// at most `skip_tokens` tokens are left out (their attention kernel reads the pool itself).
+// at most `skip_tokens` tokens are left out (their attention kernel reads the pool itself); `n_scratch_rows` is the number
+// of the other rows.
 void launch_kv_quant_store(const float * qkv, int ld, int n_tokens, int n_head, KvLayout kv, int layer, const int32_t * tok_cell, cudaStream_t stream);
-void launch_kv_dequant(KvLayout kv, int layer, int n_rows, int max_row_blocks, const int32_t * cu_rows, const int32_t * tok_slot,
+void launch_kv_dequant(KvLayout kv, int layer, int n_rows, int n_scratch_rows, int max_row_blocks, const int32_t * cu_rows, const int32_t * tok_slot,
                        const int32_t * tok_pos, const int32_t * tok_pos_min, int skip_tokens, cudaStream_t stream);
 
 void launch_embed(WeightView embd, const int32_t * tokens, int n_tokens, float * x, cudaStream_t stream, int * check = nullptr);
