@@ -17,6 +17,8 @@ Printed keys beyond the base contract:
   roofline     the dominant kernel class of the timed region, timed live with CUDA events on the
                launching stream, against the measured peak of MEASURED_PEAKS.json
   cpu_baseline the CPU oracle timed on this host's cores on a bounded sample (N=1, rank 0)
+  unprofiled   the K steps that follow the timed region, with the engine's profiler off (N=1): what a caller gets when
+               no events separate the kernel classes - repeated step shapes replay as CUDA graphs
 
 `--impl reference` times the reference's CPU path for the same metric. The reference itself cannot
 be built in this image (no Rust toolchain, and its compute library is an un-vendored submodule), so
@@ -659,6 +661,22 @@ def main():
         t = r.times[-(args.steps + 1):]
         gaps += [1e3 * (b - a) for a, b in zip(t, t[1:])]
 
+    # ---- the same workload going on for K more steps without the profiler's events between kernel classes (untimed for
+    # `value`): repeated step shapes replay as CUDA graphs and dependent launches overlap, as they do for a caller
+    unprofiled = None
+    if not args.graphs and world == 1:
+        u_ms, u_sampled, u_tokens = 0.0, 0, 0
+        for _ in range(args.steps):
+            info = driver.step()
+            u_ms += engine.last_step_stats()[0]
+            u_sampled += info["sampled"]
+            u_tokens += info["tokens"]
+            driver.admit()
+        torch.cuda.synchronize()
+        unprofiled = {"steps": args.steps, "tok_s": u_sampled / (u_ms * 1e-3), "ms_per_step": u_ms / args.steps,
+                      "tokens_per_step": u_tokens / args.steps,
+                      "note": "K later steps of the same request stream with the engine's profiler off (their own token mix)"}
+
     from retrograd_b200.replicas import aggregate
 
     # every rank's own step time, so that a slow whole-job step can be attributed (imbalance of the seeded
@@ -735,6 +753,8 @@ def main():
             d["weight_gbs"] = weight_bytes_step / (d["ms_per_step"] * 1e-3) / 1e9
             d["frac"] = d["weight_gbs"] / hbm_peak
         line["decode_only"] = decode_only
+    if unprofiled is not None:
+        line["unprofiled"] = unprofiled
     if ep_parity is not None:
         line["ep_parity"] = ep_parity
     if expert_parallel:
