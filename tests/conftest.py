@@ -53,7 +53,7 @@ def models(rb, tmp_path_factory):
     return get
 
 
-# BASELINE config 1: tiny llama-style decoder, Q8_0 (ffn_down rows of 688 cannot hold whole
+# The tiny CPU-runnable model: llama-style decoder, Q8_0 (ffn_down rows of 688 cannot hold whole
 # Q8_0 blocks and are stored as F16, which the synthesiser does for any indivisible row).
 C1_SPEC = dict(arch="llama", layers=2, d=256, heads=4, kv_heads=4, ff=688, vocab=4096, dtype="q8_0", seed=20261125)
 

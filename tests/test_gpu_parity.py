@@ -59,7 +59,7 @@ def _greedy_workload(rb, O, model_path, prompts, n_new, n_batch=256, n_ctx=4096,
 
 
 def test_c1_tiny_llama_q8_0_greedy_streams(rb, oracle, c1_model):
-    """BASELINE config 1: 8 requests = shared 32-token prefix + 16..128 unique tokens, 32 greedy
+    """The tiny CPU-runnable workload: 8 requests = shared 32-token prefix + 16..128 unique tokens, 32 greedy
     tokens each."""
     rng = np.random.default_rng(20261125)
     prefix = rng.integers(3, 4096, 32).tolist()
@@ -160,7 +160,7 @@ def test_tensor_core_gemm_path_wide_steps(rb, oracle, models):
 
 
 def test_full_8b_shape_logits_within_tolerance(rb, oracle):
-    """BASELINE config 2's model at full size (32 layers, d 4096, Q4_K): a ragged prefill step on
+    """The headline workload's model at full size (32 layers, d 4096, Q4_K): a ragged prefill step on
     the tensor-core path and decode steps on the row path, logits against the f32 CPU oracle."""
     import bench
 
